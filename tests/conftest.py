@@ -1,0 +1,29 @@
+"""Shared pytest configuration: the `gpu` marker, import path, and small helpers used by several test files."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+os.environ.setdefault("FAKE_NUMA_NODES", "1")
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    from oracle import oracle as O
+    return O
+
+
+@pytest.fixture(scope="session")
+def golden():
+    return np.load(GOLDEN / "hotpath_golden.npz")
