@@ -1,0 +1,97 @@
+"""ctypes binding of libhive_b200.so (the C ABI declared in include/hive_b200.h).
+
+The library is loaded from this directory; if it is missing, or a symbol the header declares is not exported, the import
+fails with an error — there is no Python, PyTorch or CPU stand-in for any entry point.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import re
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "libhive_b200.so"
+HEADER = HERE.parent / "include" / "hive_b200.h"
+
+HB_OK = 0
+HB_FLAG_NO_PDL = 1
+
+
+class HbError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"hive_b200 status {status}: {message}")
+        self.status = status
+
+
+class RecLayout(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("w1", "s1", "w3", "s3", "w2", "s2", "g", "total")]
+
+
+class Config(C.Structure):
+    _fields_ = [("device", C.c_int), ("max_ctas", C.c_int), ("flags", C.c_int)]
+
+
+class MoePair(C.Structure):
+    _fields_ = [("row", C.c_int32), ("rec", C.c_void_p), ("w", C.c_float)]
+
+
+class PfCombine(C.Structure):
+    _fields_ = [("shared", C.c_void_p), ("lg", C.c_void_p), ("ld", C.c_int), ("col", C.c_int), ("out", C.c_void_p)]
+
+
+class QMat(C.Structure):
+    _fields_ = [("fmt", C.c_int), ("N", C.c_int), ("K", C.c_int), ("w", C.c_void_p), ("s", C.c_void_p), ("zp", C.c_void_p), ("g", C.c_float)]
+
+
+assert C.sizeof(MoePair) == 24 and MoePair.rec.offset == 8 and MoePair.w.offset == 16
+
+
+def declared_symbols() -> list[str]:
+    """Every function name the public header declares with HB_API."""
+    text = HEADER.read_text()
+    return re.findall(r"HB_API\s+[\w\s\*]+?\b(hb_\w+)\s*\(", text)
+
+
+def load() -> C.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(f"{LIB_PATH} is missing: build it with `python eke_hive_b200/build.py` (needs nvcc); "
+                          "there is no fallback implementation")
+    lib = C.CDLL(str(LIB_PATH))
+    missing = [s for s in declared_symbols() if not hasattr(lib, s)]
+    if missing:
+        raise ImportError(f"{LIB_PATH} does not export {missing}; rebuild it")
+    vp, i, f, sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+    sig = {
+        "hb_create": (i, [C.POINTER(Config), C.POINTER(vp)]),
+        "hb_destroy": (None, [vp]),
+        "hb_last_error": (C.c_char_p, [vp]),
+        "hb_status_string": (C.c_char_p, [i]),
+        "hb_sm_count": (i, [vp]),
+        "hb_check_device": (i, [vp, vp]),
+        "hb_launch_count": (C.c_uint64, [vp]),
+        "hb_rec_layout_make": (i, [i, i, C.POINTER(RecLayout)]),
+        "hb_nvfp4_dequant": (i, [vp, vp, vp, f, i, i, vp, vp]),
+        "hb_nvfp4_gemv": (i, [vp, vp, vp, f, i, i, vp, i, i, vp, i, vp]),
+        "hb_nvfp4_quantize": (i, [vp, vp, i, i, vp, vp, vp, vp, vp]),
+        "hb_a4_quant": (i, [vp, vp, i, i, i, vp, vp, vp, vp]),
+        "hb_route_softmax_topk": (i, [vp, vp, i, i, i, i, i, i, vp, vp, vp]),
+        "hb_route_sigmoid_topk": (i, [vp, vp, vp, i, i, i, f, vp, vp, vp]),
+        "hb_build_moe_pairs": (i, [vp, vp, vp, i, i, vp, i, i, vp, vp]),
+        "hb_moe_combine": (i, [vp, vp, vp, vp, i, i, i, i, vp, vp]),
+        "hb_moe_decode_supported": (i, [i, i]),
+        "hb_moe_decode_ws_bytes": (sz, [i, i, i]),
+        "hb_moe_decode": (i, [vp, vp, i, vp, i, i, f, vp, vp, vp]),
+        "hb_moe_decode_routed": (i, [vp, vp, vp, i, i, vp, i, i, vp, i, i, f, C.POINTER(PfCombine), vp, vp]),
+        "hb_moe_layer_decode": (i, [vp, vp, i, i, i, i, i, i, vp, f, vp, i, vp, i, vp, i, i, f, vp, vp, vp, vp, vp]),
+        "hb_gather_rows": (i, [vp, vp, vp, i, i, vp, vp]),
+        "hb_swiglu_rows": (i, [vp, vp, i, i, f, vp, vp]),
+        "hb_scatter_add_rows": (i, [vp, vp, vp, vp, i, i, vp, vp]),
+        "hb_add_f32": (i, [vp, vp, vp, sz, vp]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name, None)
+        if fn is None:
+            continue
+        fn.restype = res
+        fn.argtypes = args
+    return lib

@@ -1,0 +1,240 @@
+// The C ABI: argument checks and conversion of every failure into a return code.  No entry point throws or aborts; none
+// falls back to host arithmetic — if the device or a kernel is unusable the call fails with a message.
+#include <new>
+
+#include "hb_common.cuh"
+#include "hb_kernels.h"
+
+namespace {
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+inline bool pdl_on(const hb_ctx* c) { return !(c->flags & HB_FLAG_NO_PDL); }
+}  // namespace
+
+#define HB_CTX(ctx) \
+  do { if (!(ctx)) return HB_ERR_INVALID; } while (0)
+#define HB_PTR(ctx, p) HB_REQUIRE(ctx, (p) != nullptr, HB_ERR_INVALID, "%s: %s is NULL", __func__, #p)
+#define HB_ALIGN16(ctx, p) HB_REQUIRE(ctx, hb_aligned((p), 16), HB_ERR_INVALID, "%s: %s must be 16-byte aligned", __func__, #p)
+
+extern "C" {
+
+int hb_create(const hb_config* cfg, hb_ctx** out) {
+  if (!out) return HB_ERR_INVALID;
+  *out = nullptr;
+  hb_ctx* c = new (std::nothrow) hb_ctx();
+  if (!c) return HB_ERR_CUDA;
+  c->device = cfg ? cfg->device : 0;
+  c->max_ctas = cfg ? cfg->max_ctas : 0;
+  c->flags = cfg ? cfg->flags : 0;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0 || c->device < 0 || c->device >= n) { delete c; cudaGetLastError(); return HB_ERR_NO_DEVICE; }
+  cudaDeviceProp prop;
+  if (cudaSetDevice(c->device) != cudaSuccess || cudaGetDeviceProperties(&prop, c->device) != cudaSuccess) { delete c; cudaGetLastError(); return HB_ERR_NO_DEVICE; }
+  if (prop.major != 10) { delete c; return HB_ERR_NO_DEVICE; }          // the kernels are sm_100a only
+  c->sm_count = prop.multiProcessorCount;
+  c->smem_optin = (int)prop.sharedMemPerBlockOptin;
+  if (cudaMalloc(&c->dev_err, 256) != cudaSuccess || cudaMemset(c->dev_err, 0, 256) != cudaSuccess) { delete c; cudaGetLastError(); return HB_ERR_CUDA; }
+  const int r = hbk_moe_decode_setup(c);
+  if (r != HB_OK) { cudaFree(c->dev_err); delete c; return r; }
+  *out = c;
+  return HB_OK;
+}
+
+void hb_destroy(hb_ctx* ctx) {
+  if (!ctx) return;
+  if (ctx->dev_err) cudaFree(ctx->dev_err);
+  delete ctx;
+}
+
+const char* hb_last_error(const hb_ctx* ctx) { return ctx ? ctx->err : "null context"; }
+
+const char* hb_status_string(int s) {
+  switch (s) {
+    case HB_OK: return "ok";
+    case HB_ERR_INVALID: return "invalid argument";
+    case HB_ERR_UNSUPPORTED: return "unsupported shape";
+    case HB_ERR_CUDA: return "CUDA error";
+    case HB_ERR_NO_DEVICE: return "no sm_100 device";
+    case HB_ERR_WORKSPACE: return "bad workspace";
+    case HB_ERR_DEVICE_FLAG: return "device-side bounded wait gave up";
+    default: return "unknown status";
+  }
+}
+
+int hb_sm_count(const hb_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
+uint64_t hb_launch_count(const hb_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int hb_check_device(hb_ctx* ctx, void* stream) {
+  HB_CTX(ctx);
+  uint32_t v = 0;
+  HB_CUDA(ctx, cudaMemcpyAsync(&v, ctx->dev_err, 4, cudaMemcpyDeviceToHost, as_stream(stream)));
+  HB_CUDA(ctx, cudaStreamSynchronize(as_stream(stream)));
+  if (v == 0) return HB_OK;
+  HB_CUDA(ctx, cudaMemsetAsync(ctx->dev_err, 0, 4, as_stream(stream)));
+  return hb_fail(ctx, HB_ERR_DEVICE_FLAG, "device error word 0x%x (1 = producer wait, 2 = consumer wait, 4 = drain)", v);
+}
+
+int hb_rec_layout_make(int H, int I, hb_rec_layout* L) {
+  if (!L || H <= 0 || I <= 0 || (H % 32) || (I % 32)) return HB_ERR_INVALID;
+  const uint64_t wgu = (uint64_t)I * H / 2, sgu = (uint64_t)I * H / 16;
+  L->w1 = 0; L->s1 = wgu; L->w3 = L->s1 + sgu; L->s3 = L->w3 + wgu; L->w2 = L->s3 + sgu; L->s2 = L->w2 + wgu; L->g = L->s2 + sgu;
+  L->total = (L->g + 16 + 4095) / 4096 * 4096;
+  return HB_OK;
+}
+
+int hb_nvfp4_dequant(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int N, int K, void* out, void* stream) {
+  HB_CTX(ctx); HB_PTR(ctx, w); HB_PTR(ctx, s); HB_PTR(ctx, out);
+  HB_REQUIRE(ctx, N > 0 && K > 0 && K % 16 == 0, HB_ERR_UNSUPPORTED, "nvfp4_dequant: N=%d K=%d (K %% 16)", N, K);
+  HB_REQUIRE(ctx, hb_aligned(w, 8) && hb_aligned(out, 16), HB_ERR_INVALID, "nvfp4_dequant: w 8-byte, out 16-byte aligned");
+  return hbk_nvfp4_dequant(ctx, w, s, g, N, K, out, as_stream(stream));
+}
+
+int hb_nvfp4_gemv(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int N, int K, const void* x, int ldx, int M, float* y, int ldy,
+                  void* stream) {
+  HB_CTX(ctx); HB_PTR(ctx, w); HB_PTR(ctx, s); HB_PTR(ctx, x); HB_PTR(ctx, y);
+  HB_REQUIRE(ctx, M >= 1 && M <= 16, HB_ERR_UNSUPPORTED, "nvfp4_gemv: M=%d outside 1..16", M);
+  HB_REQUIRE(ctx, N > 0 && K > 0 && K % 32 == 0, HB_ERR_UNSUPPORTED, "nvfp4_gemv: N=%d K=%d (K %% 32)", N, K);
+  HB_REQUIRE(ctx, ldx >= K && ldx % 8 == 0 && ldy >= N, HB_ERR_INVALID, "nvfp4_gemv: ldx=%d (≥K, %% 8) ldy=%d (≥N)", ldx, ldy);
+  HB_ALIGN16(ctx, w); HB_ALIGN16(ctx, x);
+  HB_REQUIRE(ctx, hb_aligned(s, 2), HB_ERR_INVALID, "nvfp4_gemv: s must be 2-byte aligned");
+  return hbk_nvfp4_gemv(ctx, w, s, g, N, K, x, ldx, M, y, ldy, as_stream(stream));
+}
+
+int hb_nvfp4_quantize(hb_ctx* ctx, const float* w, int N, int K, uint8_t* q, uint8_t* s, float* g_mul, float* amax, void* stream) {
+  HB_CTX(ctx); HB_PTR(ctx, w); HB_PTR(ctx, q); HB_PTR(ctx, s); HB_PTR(ctx, g_mul); HB_PTR(ctx, amax);
+  HB_REQUIRE(ctx, N > 0 && K > 0 && K % 16 == 0, HB_ERR_UNSUPPORTED, "nvfp4_quantize: N=%d K=%d (K %% 16)", N, K);
+  HB_ALIGN16(ctx, w);
+  HB_REQUIRE(ctx, hb_aligned(q, 8), HB_ERR_INVALID, "nvfp4_quantize: q must be 8-byte aligned");
+  return hbk_nvfp4_quantize(ctx, w, N, K, q, s, g_mul, amax, as_stream(stream));
+}
+
+int hb_a4_quant(hb_ctx* ctx, const void* x, int ld, int n, int K, uint8_t* q, uint8_t* s, float* g, void* stream) {
+  HB_CTX(ctx); HB_PTR(ctx, x); HB_PTR(ctx, q); HB_PTR(ctx, s); HB_PTR(ctx, g);
+  HB_REQUIRE(ctx, n > 0 && K > 0 && K % 16 == 0 && ld >= K, HB_ERR_UNSUPPORTED, "a4_quant: n=%d K=%d ld=%d", n, K, ld);
+  HB_REQUIRE(ctx, hb_aligned(q, 8), HB_ERR_INVALID, "a4_quant: q must be 8-byte aligned");
+  return hbk_a4_quant(ctx, x, ld, n, K, q, s, g, as_stream(stream));
+}
+
+int hb_route_softmax_topk(hb_ctx* ctx, const float* logits, int ld, int M, int E, int k, int renorm, int logits_bf16, int32_t* ids, float* w,
+                          void* stream) {
+  HB_CTX(ctx); HB_PTR(ctx, logits); HB_PTR(ctx, ids); HB_PTR(ctx, w);
+  HB_REQUIRE(ctx, M > 0 && E > 0 && E <= HB_MAX_EXPERTS && k >= 1 && k <= 16 && k <= E && ld >= E, HB_ERR_UNSUPPORTED,
+             "route_softmax_topk: M=%d E=%d (≤%d) k=%d (1..16) ld=%d", M, E, HB_MAX_EXPERTS, k, ld);
+  return hbk_route_softmax_topk(ctx, logits, ld, M, E, k, renorm, logits_bf16, ids, w, as_stream(stream), pdl_on(ctx));
+}
+
+int hb_route_sigmoid_topk(hb_ctx* ctx, const float* logits, const float* bias, int M, int E, int k, float scale, int32_t* ids, float* w,
+                          void* stream) {
+  HB_CTX(ctx); HB_PTR(ctx, logits); HB_PTR(ctx, ids); HB_PTR(ctx, w);
+  HB_REQUIRE(ctx, M > 0 && E > 0 && E <= HB_MAX_EXPERTS && k >= 1 && k <= 16 && k <= E, HB_ERR_UNSUPPORTED,
+             "route_sigmoid_topk: M=%d E=%d (≤%d) k=%d (1..16)", M, E, HB_MAX_EXPERTS, k);
+  return hbk_route_sigmoid_topk(ctx, logits, bias, M, E, k, scale, ids, w, as_stream(stream), pdl_on(ctx));
+}
+
+int hb_build_moe_pairs(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int K, const uint8_t* const* rec_tab, int li, int E,
+                       hb_moe_pair* pairs, void* stream) {
+  HB_CTX(ctx); HB_PTR(ctx, ids); HB_PTR(ctx, w); HB_PTR(ctx, rec_tab); HB_PTR(ctx, pairs);
+  HB_REQUIRE(ctx, M > 0 && K > 0 && E > 0 && li >= 0, HB_ERR_INVALID, "build_moe_pairs: M=%d K=%d E=%d li=%d", M, K, E, li);
+  return hbk_build_pairs(ctx, ids, w, M, K, rec_tab, li, E, pairs, as_stream(stream), pdl_on(ctx));
+}
+
+int hb_moe_combine(hb_ctx* ctx, const float* routed, const void* shared, const float* lg, int ld, int col, int M, int H, void* out,
+                   void* stream) {
+  HB_CTX(ctx); HB_PTR(ctx, routed); HB_PTR(ctx, shared); HB_PTR(ctx, out);
+  HB_REQUIRE(ctx, M > 0 && H > 0, HB_ERR_INVALID, "moe_combine: M=%d H=%d", M, H);
+  return hbk_moe_combine(ctx, routed, shared, lg, ld, col, M, H, out, as_stream(stream), pdl_on(ctx));
+}
+
+static int check_decode_shape(hb_ctx* ctx, const char* fn, int P, int H, int I, const void* x, const void* ws) {
+  HB_REQUIRE(ctx, H > 0 && I > 0 && H % 32 == 0 && I % 32 == 0, HB_ERR_UNSUPPORTED, "%s: H=%d I=%d must be multiples of 32", fn, H, I);
+  HB_REQUIRE(ctx, P <= HB_MAX_PAIRS, HB_ERR_UNSUPPORTED, "%s: %d pairs > %d", fn, P, HB_MAX_PAIRS);
+  HB_REQUIRE(ctx, ws != nullptr && hb_aligned(ws, 256), HB_ERR_WORKSPACE, "%s: ws NULL or not 256-byte aligned", fn);
+  HB_REQUIRE(ctx, hb_aligned(x, 16), HB_ERR_INVALID, "%s: x must be 16-byte aligned", fn);
+  return HB_OK;
+}
+
+int hb_moe_decode_supported(int H, int I) { return (H > 0 && I > 0 && H % 32 == 0 && I % 32 == 0) ? (hbk_moe_decode_fast(H, I) ? 2 : 1) : 0; }
+
+size_t hb_moe_decode_ws_bytes(int n_pairs, int H, int I) { return hbk_moe_decode_ws_bytes(n_pairs, H, I); }
+
+int hb_moe_decode(hb_ctx* ctx, const hb_moe_pair* pairs, int n_pairs, const void* x, int H, int I, float limit, float* out, void* ws,
+                  void* stream) {
+  HB_CTX(ctx);
+  if (n_pairs == 0) return HB_OK;
+  HB_PTR(ctx, pairs); HB_PTR(ctx, x); HB_PTR(ctx, out);
+  HB_REQUIRE(ctx, n_pairs > 0, HB_ERR_INVALID, "moe_decode: n_pairs=%d", n_pairs);
+  int r = check_decode_shape(ctx, "moe_decode", n_pairs, H, I, x, ws);
+  if (r) return r;
+  HB_REQUIRE(ctx, hb_aligned(out, 8), HB_ERR_INVALID, "moe_decode: out must be 8-byte aligned");
+  hbk_pair_src src; src.pairs = pairs; src.n_pairs = n_pairs;
+  hbk_reduce red; red.out_accum = out;
+  return hbk_moe_decode_run(ctx, src, x, H, I, limit, red, ws, as_stream(stream));
+}
+
+int hb_moe_decode_routed(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int K, const uint8_t* const* rec_tab, int li, int E,
+                         const void* x, int H, int I, float limit, const hb_pf_combine* cmb, void* ws, void* stream) {
+  HB_CTX(ctx);
+  if (M == 0) return HB_OK;
+  HB_PTR(ctx, ids); HB_PTR(ctx, w); HB_PTR(ctx, rec_tab); HB_PTR(ctx, x); HB_PTR(ctx, cmb); HB_PTR(ctx, cmb->out);
+  HB_REQUIRE(ctx, M > 0 && K > 0 && E > 0 && E <= HB_MAX_EXPERTS && li >= 0, HB_ERR_INVALID, "moe_decode_routed: M=%d K=%d E=%d li=%d", M, K, E, li);
+  int r = check_decode_shape(ctx, "moe_decode_routed", M * K, H, I, x, ws);
+  if (r) return r;
+  hbk_pair_src src; src.ids = ids; src.w = w; src.M = M; src.K = K; src.tab = rec_tab; src.li = li; src.E = E;
+  hbk_reduce red; red.shared = cmb->shared; red.lg = cmb->lg; red.ld = cmb->ld; red.col = cmb->col; red.out_bf16 = cmb->out;
+  return hbk_moe_decode_run(ctx, src, x, H, I, limit, red, ws, as_stream(stream));
+}
+
+int hb_moe_layer_decode(hb_ctx* ctx, const float* logits, int ld, int M, int E, int K, int renorm, int logits_bf16, const float* bias,
+                        float sigmoid_scale, const uint8_t* const* rec_tab, int li, const uint8_t* shared_rec, int gate_col, const void* x,
+                        int H, int I, float limit, int32_t* ids_out, float* w_out, void* out, void* ws, void* stream) {
+  HB_CTX(ctx);
+  if (M == 0) return HB_OK;
+  HB_PTR(ctx, logits); HB_PTR(ctx, rec_tab); HB_PTR(ctx, x); HB_PTR(ctx, ids_out); HB_PTR(ctx, w_out); HB_PTR(ctx, out);
+  HB_REQUIRE(ctx, M > 0 && K >= 1 && K <= 16 && E > 0 && E <= HB_MAX_EXPERTS && K <= E && ld >= E && li >= 0, HB_ERR_INVALID,
+             "moe_layer_decode: M=%d K=%d E=%d ld=%d li=%d", M, K, E, ld, li);
+  HB_REQUIRE(ctx, gate_col < ld, HB_ERR_INVALID, "moe_layer_decode: gate_col=%d outside the logits row (ld=%d)", gate_col, ld);
+  int r = check_decode_shape(ctx, "moe_layer_decode", M * (K + 1), H, I, x, ws);
+  if (r) return r;
+  const bool sigmoid = bias != nullptr || sigmoid_scale != 0.f;
+  if (sigmoid) {
+    HB_REQUIRE(ctx, ld == E, HB_ERR_INVALID, "moe_layer_decode: the sigmoid router takes dense logits rows (ld == E)");
+    r = hbk_route_sigmoid_topk(ctx, logits, bias, M, E, K, sigmoid_scale != 0.f ? sigmoid_scale : 1.f, ids_out, w_out, as_stream(stream), pdl_on(ctx));
+  } else {
+    r = hbk_route_softmax_topk(ctx, logits, ld, M, E, K, renorm, logits_bf16, ids_out, w_out, as_stream(stream), pdl_on(ctx));
+  }
+  if (r) return r;
+  hbk_pair_src src; src.ids = ids_out; src.w = w_out; src.M = M; src.K = K; src.tab = rec_tab; src.li = li; src.E = E; src.shared_rec = shared_rec;
+  hbk_reduce red; red.out_bf16 = out;
+  if (gate_col >= 0 && shared_rec) { red.lg = logits; red.ld = ld; red.col = gate_col; }
+  return hbk_moe_decode_run(ctx, src, x, H, I, limit, red, ws, as_stream(stream));
+}
+
+int hb_gather_rows(hb_ctx* ctx, const void* x, const int32_t* rows, int R, int H, void* out, void* stream) {
+  HB_CTX(ctx);
+  if (R == 0) return HB_OK;
+  HB_PTR(ctx, x); HB_PTR(ctx, rows); HB_PTR(ctx, out);
+  HB_REQUIRE(ctx, R > 0 && H > 0 && H % 8 == 0, HB_ERR_UNSUPPORTED, "gather_rows: R=%d H=%d (H %% 8)", R, H);
+  HB_ALIGN16(ctx, x); HB_ALIGN16(ctx, out);
+  return hbk_gather_rows(ctx, x, rows, R, H, out, as_stream(stream));
+}
+int hb_swiglu_rows(hb_ctx* ctx, const void* gu, int R, int I, float limit, void* y, void* stream) {
+  HB_CTX(ctx);
+  if (R == 0) return HB_OK;
+  HB_PTR(ctx, gu); HB_PTR(ctx, y);
+  HB_REQUIRE(ctx, R > 0 && I > 0, HB_ERR_INVALID, "swiglu_rows: R=%d I=%d", R, I);
+  return hbk_swiglu_rows(ctx, gu, R, I, limit, y, as_stream(stream));
+}
+int hb_scatter_add_rows(hb_ctx* ctx, const void* e, const int32_t* rows, const float* w, int R, int H, float* out, void* stream) {
+  HB_CTX(ctx);
+  if (R == 0) return HB_OK;
+  HB_PTR(ctx, e); HB_PTR(ctx, rows); HB_PTR(ctx, w); HB_PTR(ctx, out);
+  HB_REQUIRE(ctx, R > 0 && H > 0, HB_ERR_INVALID, "scatter_add_rows: R=%d H=%d", R, H);
+  return hbk_scatter_add_rows(ctx, e, rows, w, R, H, out, as_stream(stream));
+}
+int hb_add_f32(hb_ctx* ctx, float* a, const float* b, size_t n, void* stream) {
+  HB_CTX(ctx);
+  if (n == 0) return HB_OK;
+  HB_PTR(ctx, a); HB_PTR(ctx, b);
+  return hbk_add_f32(ctx, a, b, n, as_stream(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,52 @@
+// Internal launcher interface between the C-ABI translation unit (argument checks) and the kernel translation units.
+// Every function enqueues on `st` and returns HB_OK or a negative hb_status with the context's message set.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/hive_b200.h"
+
+int hbk_nvfp4_dequant(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int N, int K, void* out, cudaStream_t st);
+int hbk_nvfp4_gemv(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int N, int K, const void* x, int ldx, int M, float* y, int ldy,
+                   cudaStream_t st);
+int hbk_nvfp4_quantize(hb_ctx* ctx, const float* w, int N, int K, uint8_t* q, uint8_t* s, float* g_mul, float* amax, cudaStream_t st);
+int hbk_a4_quant(hb_ctx* ctx, const void* x, int ld, int n, int K, uint8_t* q, uint8_t* s, float* g, cudaStream_t st);
+
+int hbk_route_softmax_topk(hb_ctx* ctx, const float* logits, int ld, int M, int E, int k, int renorm, int logits_bf16, int32_t* ids, float* w,
+                           cudaStream_t st, bool pdl);
+int hbk_route_sigmoid_topk(hb_ctx* ctx, const float* logits, const float* bias, int M, int E, int k, float scale, int32_t* ids, float* w,
+                           cudaStream_t st, bool pdl);
+int hbk_build_pairs(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int K, const uint8_t* const* tab, int li, int E, hb_moe_pair* pairs,
+                    cudaStream_t st, bool pdl);
+int hbk_moe_combine(hb_ctx* ctx, const float* routed, const void* shared, const float* lg, int ld, int col, int M, int H, void* out, cudaStream_t st,
+                    bool pdl);
+int hbk_gather_rows(hb_ctx* ctx, const void* x, const int32_t* rows, int R, int H, void* out, cudaStream_t st);
+int hbk_swiglu_rows(hb_ctx* ctx, const void* gu, int R, int I, float limit, void* y, cudaStream_t st);
+int hbk_scatter_add_rows(hb_ctx* ctx, const void* e, const int32_t* rows, const float* w, int R, int H, float* out, cudaStream_t st);
+int hbk_add_f32(hb_ctx* ctx, float* a, const float* b, size_t n, cudaStream_t st);
+
+// ---- routed-expert decode ----
+constexpr int HB_MAX_PAIRS = 4096;     // pairs per call (M·K plus the shared expert's M)
+constexpr int HB_MAX_EXPERTS = 1024;
+bool hbk_moe_decode_fast(int H, int I);                 // shapes the streaming tensor-core path takes
+size_t hbk_moe_decode_ws_bytes(int n_pairs, int H, int I);
+int hbk_moe_decode_setup(hb_ctx* ctx);                  // one-time kernel attributes (dynamic shared memory)
+// Source of the pairs: either an explicit list, or router output (+ optionally the shared expert as M extra pairs of weight 1).
+struct hbk_pair_src {
+  const hb_moe_pair* pairs = nullptr; int n_pairs = 0;                       // list form
+  const int32_t* ids = nullptr; const float* w = nullptr; int M = 0, K = 0;  // routed form
+  const uint8_t* const* tab = nullptr; int li = 0, E = 0;
+  const uint8_t* shared_rec = nullptr;
+};
+// What the last kernel does with the per-pair outputs.
+struct hbk_reduce {
+  float* out_accum = nullptr;                 // list form: out[row] += Σ in pair order (fp32)
+  const void* shared = nullptr;               // routed form: external shared rows bf16 [M,H] (or the shared record's pairs when null)
+  const float* lg = nullptr; int ld = 0, col = 0;
+  void* out_bf16 = nullptr;                   // routed form with combine
+  float* out_f32 = nullptr;                   // routed form without combine: overwritten with Σ_k w·expert
+};
+int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int H, int I, float limit, const hbk_reduce& red, void* ws,
+                       cudaStream_t st);

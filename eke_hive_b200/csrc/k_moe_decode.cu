@@ -1,0 +1,663 @@
+// Routed-expert decode for NVFP4 expert records (1–16 tokens per expert): a memory-bound streaming path.
+//
+//   group   one CTA: sorts the (row, expert) pairs by expert into groups of ≤ 8 rows, so a record streams once per group
+//   gate/up persistent CTAs: item = (group, 8 gate + 8 up rows of I).  A producer warp streams the packed rows into a
+//           shared-memory ring with 1-D bulk asynchronous copies (mbarrier transaction counts); consumer warps split K,
+//           decode e2m1 → f16 in registers with the hardware converter, multiply by the exact f16 e4m3 block scale and
+//           feed m16n8k16 tensor-core tiles whose 8 columns are the group's activation rows (fp32 accumulation); split-K
+//           partials meet in shared memory in a fixed order; SwiGLU epilogue → y[pair, I] (bf16)
+//   down    same machinery over [H, I]: part[pair, H] = bf16(down · g2)
+//   reduce  out[row] = Σ_k w·part in k (or pair) order, fused with the shared-expert combine where asked
+//
+// HBM traffic per layer is the records touched plus O(pairs·(H+I)) bytes of activations; weights are read once per group.
+// Shapes the streaming path takes: H, I multiples of 256, at most 4096; anything else (H, I multiples of 32) runs on the
+// generic CUDA-core kernels at the end of this file.
+#include "hb_common.cuh"
+#include "hb_kernels.h"
+
+namespace hb {
+
+constexpr int kGroupRows = 8;         // activation rows per group = columns of one m16n8k16 tile
+constexpr int kSlice = 256;           // K elements per consumer warp
+constexpr int kMaxStages = 8;
+constexpr int kGroupThreads = 1024;
+
+struct Group { const uint8_t* rec; int start; int n; };
+static_assert(sizeof(Group) == 16, "Group layout");
+
+struct DecodeWs {
+  int* hdr;               // [0] number of groups, [1] number of valid pairs
+  Group* groups;          // [n_pairs]
+  int* s_row;             // [n_pairs] activation row of each sorted position
+  int* pos_of;            // [n_pairs] sorted position of each original pair, -1 = skipped (invalid id / null record)
+  int* prow;              // [n_pairs] activation row of each original pair
+  float* pw;              // [n_pairs] routing weight of each original pair
+  __nv_bfloat16* y;       // [n_pairs, I]
+  __nv_bfloat16* part;    // [n_pairs, H]
+};
+
+__host__ __device__ inline size_t al256(size_t b) { return (b + 255) / 256 * 256; }
+
+static DecodeWs carve(void* ws, int n, int H, int I) {
+  uint8_t* p = reinterpret_cast<uint8_t*>(ws);
+  DecodeWs w;
+  w.hdr = reinterpret_cast<int*>(p); p += 256;
+  w.groups = reinterpret_cast<Group*>(p); p += al256((size_t)n * sizeof(Group));
+  w.s_row = reinterpret_cast<int*>(p); p += al256((size_t)n * 4);
+  w.pos_of = reinterpret_cast<int*>(p); p += al256((size_t)n * 4);
+  w.prow = reinterpret_cast<int*>(p); p += al256((size_t)n * 4);
+  w.pw = reinterpret_cast<float*>(p); p += al256((size_t)n * 4);
+  w.y = reinterpret_cast<__nv_bfloat16*>(p); p += al256((size_t)n * I * 2);
+  w.part = reinterpret_cast<__nv_bfloat16*>(p);
+  return w;
+}
+
+// ================================================================================================ grouping
+struct GroupArgs {
+  const hb_moe_pair* pairs; int n_pairs;                 // list form (ids == nullptr)
+  const int32_t* ids; const float* w; int M, K;          // routed form
+  const uint8_t* const* tab; int li, E;
+  const uint8_t* shared_rec;
+  DecodeWs ws;
+};
+
+// Exclusive scan of two int arrays of length n in shared memory, by the whole block (blockDim.x == kGroupThreads).
+__device__ void block_scan2(int* a, int* b, int n, int* tot_a, int* tot_b, int* warp_tmp /* [2][32] */) {
+  const int per = (n + kGroupThreads - 1) / kGroupThreads;
+  const int i0 = threadIdx.x * per, i1 = min(n, i0 + per);
+  int sa = 0, sb = 0;
+  for (int i = i0; i < i1; ++i) { sa += a[i]; sb += b[i]; }
+  int xa = sa, xb = sb;                                  // inclusive warp scan of the per-thread sums
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int ta = __shfl_up_sync(0xffffffffu, xa, o), tb = __shfl_up_sync(0xffffffffu, xb, o);
+    if (lane >= o) { xa += ta; xb += tb; }
+  }
+  if (lane == 31) { warp_tmp[warp] = xa; warp_tmp[32 + warp] = xb; }
+  __syncthreads();
+  if (warp == 0) {
+    int va = warp_tmp[lane], vb = warp_tmp[32 + lane];
+    const int ia = va, ib = vb;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int ta = __shfl_up_sync(0xffffffffu, va, o), tb = __shfl_up_sync(0xffffffffu, vb, o);
+      if (lane >= o) { va += ta; vb += tb; }
+    }
+    warp_tmp[lane] = va - ia; warp_tmp[32 + lane] = vb - ib;          // exclusive warp offsets
+    if (lane == 31) { *tot_a = va; *tot_b = vb; }
+  }
+  __syncthreads();
+  int ba = warp_tmp[warp] + xa - sa, bb = warp_tmp[32 + warp] + xb - sb;
+  for (int i = i0; i < i1; ++i) { const int ca = a[i], cb = b[i]; a[i] = ba; b[i] = bb; ba += ca; bb += cb; }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kGroupThreads) moe_group_kernel(GroupArgs a) {
+  extern __shared__ __align__(16) uint8_t gsm[];
+  griddep_wait();
+  const bool routed = a.ids != nullptr;
+  const int P = routed ? a.M * a.K + (a.shared_rec ? a.M : 0) : a.n_pairs;
+  const int NK = routed ? a.E + 1 : P;                  // key space: expert id (E = the shared expert) or leader pair index
+  int* key = reinterpret_cast<int*>(gsm);               // [P]
+  int* cnt = key + P;                                   // [NK] → exclusive offsets
+  int* ngr = cnt + NK;                                  // [NK] → exclusive group bases
+  int* fill = ngr + NK;                                 // [NK]
+  int* misc = fill + NK;                                // [64 + 2]
+  const uint8_t** recs = reinterpret_cast<const uint8_t**>(gsm + ((size_t)(P + 3 * NK + 68) * 4 + 7) / 8 * 8);   // [P], list form only
+  for (int k = threadIdx.x; k < NK; k += blockDim.x) { cnt[k] = 0; fill[k] = 0; }
+  for (int i = threadIdx.x; i < P; i += blockDim.x) {
+    int row, kk = -1; float wv;
+    if (routed) {
+      if (i < a.M * a.K) {
+        const int e = a.ids[i];
+        row = i / a.K; wv = a.w[i];
+        if (e >= 0 && e < a.E && a.tab[(size_t)a.li * a.E + e] != nullptr) kk = e;
+      } else { row = i - a.M * a.K; wv = 1.f; kk = a.E; }
+    } else {
+      const hb_moe_pair p = a.pairs[i];
+      row = p.row; wv = p.w; recs[i] = p.rec;
+      kk = p.rec ? i : -1;                              // replaced by the leader index below
+    }
+    key[i] = kk; a.ws.prow[i] = row; a.ws.pw[i] = wv;
+  }
+  __syncthreads();
+  if (!routed) {
+    for (int i = threadIdx.x; i < P; i += blockDim.x) {
+      const uint8_t* r = recs[i];
+      if (!r) continue;
+      int l = i;
+      for (int j = 0; j < i; ++j) if (recs[j] == r) { l = j; break; }
+      key[i] = l;
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < P; i += blockDim.x) if (key[i] >= 0) atomicAdd(&cnt[key[i]], 1);
+  __syncthreads();
+  for (int k = threadIdx.x; k < NK; k += blockDim.x) ngr[k] = (cnt[k] + kGroupRows - 1) / kGroupRows;
+  __syncthreads();
+  // keep the counts: the scan overwrites cnt with offsets, so copy them into fill's slot first (fill is re-zeroed after)
+  for (int k = threadIdx.x; k < NK; k += blockDim.x) fill[k] = cnt[k];
+  __syncthreads();
+  block_scan2(cnt, ngr, NK, &misc[64], &misc[65], misc);
+  // groups of every key that has pairs
+  for (int k = threadIdx.x; k < NK; k += blockDim.x) {
+    const int c = fill[k];
+    if (c == 0) continue;
+    const uint8_t* rec = routed ? (k == a.E ? a.shared_rec : a.tab[(size_t)a.li * a.E + k]) : recs[k];
+    for (int j = 0; j * kGroupRows < c; ++j) a.ws.groups[ngr[k] + j] = Group{rec, cnt[k] + j * kGroupRows, min(kGroupRows, c - j * kGroupRows)};
+  }
+  __syncthreads();
+  for (int k = threadIdx.x; k < NK; k += blockDim.x) fill[k] = 0;
+  __syncthreads();
+  // slot inside the expert's run: any order gives the same results (columns of a tile are independent)
+  for (int i = threadIdx.x; i < P; i += blockDim.x) {
+    const int kk = key[i];
+    int pos = -1;
+    if (kk >= 0) { pos = cnt[kk] + atomicAdd(&fill[kk], 1); a.ws.s_row[pos] = a.ws.prow[i]; }
+    a.ws.pos_of[i] = pos;
+  }
+  if (threadIdx.x == 0) { a.ws.hdr[0] = misc[65]; a.ws.hdr[1] = misc[64]; }
+}
+
+static size_t group_smem(bool routed, int P, int E) {
+  const int NK = routed ? E + 1 : P;
+  size_t b = (size_t)P * 4 + (size_t)NK * 12 + 68 * 4;
+  b = (b + 7) / 8 * 8;
+  return b + (routed ? 0 : (size_t)P * 8);
+}
+
+// ================================================================================================ streaming kernels
+struct StreamArgs {
+  const int* hdr; const Group* groups; const int* s_row;
+  const __nv_bfloat16* act; int act_ld;        // gate/up: x rows (indexed through s_row); down: y (indexed by sorted position)
+  __nv_bfloat16* outp;                         // gate/up: y [pos, I]; down: part [pos, H]
+  int H, I; float limit;
+  uint32_t off_wa, off_sa, off_wb, off_sb, off_g;   // record offsets: gate/up = w1,s1,w3,s3 ; down = w2,s2 (wb/sb unused)
+  int stages;
+  uint32_t* err;
+};
+
+template <int WK, int WM, bool DOWN>
+struct StreamCfg {
+  static constexpr int NW = WK * WM;                       // consumer warps
+  static constexpr int THREADS = (NW + 1) * 32;            // + one producer warp
+  static constexpr int K = WK * kSlice;
+  static constexpr int RB = K / 2, RS = K / 16;            // bytes of one row: weights, scales
+  static constexpr int TR = (DOWN ? 16 : 8) * WM;          // matrix rows per item (gate/up: TR gate rows + TR up rows)
+  static constexpr int MAT = TR * (RB + RS);               // bytes of one matrix part of a stage
+  static constexpr int UP_OFF = MAT + 64;                  // the up part sits 64 B off a 128-B boundary: no bank overlap with gate
+  static constexpr int STAGE = DOWN ? MAT : ((UP_OFF + MAT + 127) / 128 * 128);
+  static constexpr int TX = DOWN ? MAT : 2 * MAT;          // bytes a full stage receives
+  static constexpr int RED = 2 * NW * 32 * 16;             // split-K exchange buffer, double buffered
+  static constexpr int HEAD = RED + 2 * kMaxStages * 8 + 64;
+  static size_t smem(int stages) { return (size_t)((HEAD + 127) / 128 * 128) + (size_t)stages * STAGE; }
+};
+
+// Loads this warp's 256-column slice of ≤ 8 activation rows as the B fragments of 16 m16n8k16 tiles (f16).  Each row slice is
+// scaled by a power of two so its largest magnitude lands in [2^14, 2^15) before the bf16 → f16 conversion (no overflow, small
+// values keep their bits); inv[0], inv[1] return the inverse factors of the two tile columns this lane accumulates.
+__device__ __forceinline__ void load_b_frags(const __nv_bfloat16* src /* row of column g, or nullptr */, int t, uint32_t (&b)[32], float (&inv)[2]) {
+  uint4 raw[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) raw[i] = make_uint4(0, 0, 0, 0);
+  if (src) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int v = 0; v < 4; ++v) raw[h * 4 + v] = __ldg(reinterpret_cast<const uint4*>(src + 32 * (t + 4 * h)) + v);
+  }
+  uint32_t am = 0;                                              // max |x| as bf16 bits (sign cleared): integer order = magnitude order
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { am = max(am, w[j] & 0x7fffu); am = max(am, (w[j] >> 16) & 0x7fffu); }
+  }
+  am = max(am, __shfl_xor_sync(0xffffffffu, am, 1));
+  am = max(am, __shfl_xor_sync(0xffffffffu, am, 2));
+  int e = (int)(am >> 7);                                       // biased exponent of the largest magnitude
+  e = min(max(e, 27), 254);                                     // tiny rows: keep the factor finite
+  const float fac = __int_as_float((uint32_t)(127 + 14 + 127 - e) << 23);       // 2^(14 - (e - 127))
+  const float myinv = __int_as_float((uint32_t)(e - 14) << 23);                 // 2^((e - 127) - 14)
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float lo = __uint_as_float(w[j] << 16) * fac, hi = __uint_as_float(w[j] & 0xffff0000u) * fac;
+      const __half2 hh = __floats2half2_rn(lo, hi);
+      b[i * 4 + j] = *reinterpret_cast<const uint32_t*>(&hh);
+    }
+  }
+  inv[0] = __shfl_sync(0xffffffffu, myinv, (2 * t) * 4);
+  inv[1] = __shfl_sync(0xffffffffu, myinv, (2 * t + 1) * 4);
+}
+
+// One warp: 16 tile rows (this lane: rowA for the low half, rowB for the high half) × 256 columns against the B fragments.
+__device__ __forceinline__ void warp_slice_mma(const uint8_t* wa, const uint8_t* wb, const uint8_t* sa, const uint8_t* sb, int t,
+                                               const uint32_t (&b)[32], float (&acc)[4], uint64_t* empty_bar) {
+  uint4 qa[2], qb[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    qa[h] = *reinterpret_cast<const uint4*>(wa + (t + 4 * h) * 16);
+    qb[h] = *reinterpret_cast<const uint4*>(wb + (t + 4 * h) * 16);
+  }
+  const uint4 sqa = *reinterpret_cast<const uint4*>(sa), sqb = *reinterpret_cast<const uint4*>(sb);
+  // everything this warp needs from the stage is in registers: hand the stage back before the arithmetic
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(empty_bar);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    // scale bytes 2c, 2c+1 of the slice's 16, c = t + 4h: half-word (t & 1) of word (t >> 1) + 2h
+    const uint32_t wsa = (t & 2) ? (h ? sqa.w : sqa.y) : (h ? sqa.z : sqa.x), wsb = (t & 2) ? (h ? sqb.w : sqb.y) : (h ? sqb.z : sqb.x);
+    const uint32_t fa = cvt_e4m3x2_f16x2((wsa >> (16 * (t & 1))) & 0xffffu), fb = cvt_e4m3x2_f16x2((wsb >> (16 * (t & 1))) & 0xffffu);
+    const uint32_t sa0 = __byte_perm(fa, 0, 0x1010), sa1 = __byte_perm(fa, 0, 0x3232);      // broadcast each f16 scale to both halves
+    const uint32_t sb0 = __byte_perm(fb, 0, 0x1010), sb1 = __byte_perm(fb, 0, 0x3232);
+    const uint32_t wqa[4] = {qa[h].x, qa[h].y, qa[h].z, qa[h].w}, wqb[4] = {qb[h].x, qb[h].y, qb[h].z, qb[h].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {                       // word j = 8 columns = two tiles
+      uint32_t ha[4], hb_[4];
+      cvt_e2m1x8_f16x2(wqa[j], ha);
+      cvt_e2m1x8_f16x2(wqb[j], hb_);
+      const uint32_t sca = j < 2 ? sa0 : sa1, scb = j < 2 ? sb0 : sb1;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { ha[i] = hmul2_u32(ha[i], sca); hb_[i] = hmul2_u32(hb_[i], scb); }
+      const int m0 = h * 8 + j * 2;                     // tile index inside the slice
+      { const uint32_t afr[4] = {ha[0], hb_[0], ha[1], hb_[1]}; mma_f16_16816(acc, afr, b[m0 * 2], b[m0 * 2 + 1]); }
+      { const uint32_t afr[4] = {ha[2], hb_[2], ha[3], hb_[3]}; mma_f16_16816(acc, afr, b[m0 * 2 + 2], b[m0 * 2 + 3]); }
+    }
+  }
+}
+
+template <int WK, int WM, bool DOWN>
+__global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK, WM, DOWN>::THREADS <= 512 ? 2 : 1) moe_stream_kernel(StreamArgs a) {
+  using C = StreamCfg<WK, WM, DOWN>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  float4* red = reinterpret_cast<float4*>(smem);                                   // [2][NW][32]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::RED);                     // [kMaxStages]
+  uint64_t* empty = full + kMaxStages;
+  uint8_t* ring = smem + (C::HEAD + 127) / 128 * 128;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = a.stages;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], C::NW); }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  // the group list was written by the grouping kernel two launches back (see hbk_moe_decode_run for why that is complete here);
+  // the activations of the down pass are not: consumers wait for the previous kernel before touching them
+  if (!DOWN) griddep_wait();
+  const int n_groups = a.hdr[0];
+  const int N = DOWN ? a.H : a.I;
+  const int tiles = N / C::TR;
+  const long long total = (long long)n_groups * tiles;
+  const long long i_begin = total * blockIdx.x / gridDim.x, i_end = total * (blockIdx.x + 1) / gridDim.x;
+  griddep_launch();
+
+  if (warp == C::NW) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      long long it = 0;
+      bool ok = true;
+      for (long long item = i_begin; item < i_end && ok; ++item, ++it) {
+        const int s = (int)(it % S);
+        const uint32_t ph = (uint32_t)((it / S) & 1);
+        ok = mbar_wait(&empty[s], ph ^ 1u, a.err, 1u);
+        if (!ok) break;
+        const Group g = a.groups[item / tiles];
+        const int tile = (int)(item % tiles);
+        uint8_t* st = ring + (size_t)s * C::STAGE;
+        mbar_expect_tx(&full[s], C::TX);
+        const size_t r0 = (size_t)tile * C::TR;
+        bulk_g2s(st, g.rec + a.off_wa + r0 * C::RB, C::TR * C::RB, &full[s]);
+        bulk_g2s(st + C::TR * C::RB, g.rec + a.off_sa + r0 * C::RS, C::TR * C::RS, &full[s]);
+        if (!DOWN) {
+          bulk_g2s(st + C::UP_OFF, g.rec + a.off_wb + r0 * C::RB, C::TR * C::RB, &full[s]);
+          bulk_g2s(st + C::UP_OFF + C::TR * C::RB, g.rec + a.off_sb + r0 * C::RS, C::TR * C::RS, &full[s]);
+        }
+      }
+      // copies still in flight land before the CTA leaves (immediate when the consumers took every stage)
+      const long long n_issued = it;
+      for (long long j = (n_issued > S ? n_issued - S : 0); j < n_issued; ++j)
+        mbar_wait(&full[j % S], (uint32_t)((j / S) & 1), a.err, 4u);
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------ consumers
+  if (DOWN) griddep_wait();
+  const int mt = warp / WK, ks = warp % WK;
+  const int g = lane >> 2, t = lane & 3;
+  int rowA, rowB, matoff = 0;
+  if (DOWN) { rowA = 16 * mt + g; rowB = rowA + 8; }
+  else { rowA = 8 * mt + (g >> 1); rowB = rowA + 4; matoff = (g & 1) ? C::UP_OFF : 0; }
+  const int wA = matoff + rowA * C::RB + ks * (kSlice / 2), wB = matoff + rowB * C::RB + ks * (kSlice / 2);
+  const int sA = matoff + C::TR * C::RB + rowA * C::RS + ks * (kSlice / 16), sB = matoff + C::TR * C::RB + rowB * C::RS + ks * (kSlice / 16);
+
+  uint32_t bfr[32];
+  float inv[2] = {1.f, 1.f};
+  float gl[3] = {1.f, 1.f, 1.f};
+  long long cur_group = -1;
+  Group grp = {nullptr, 0, 0};
+  long long it = 0;
+  for (long long item = i_begin; item < i_end; ++item, ++it) {
+    const long long gi = item / tiles;
+    const int tile = (int)(item % tiles);
+    if (gi != cur_group) {
+      cur_group = gi;
+      grp = a.groups[gi];
+      const __nv_bfloat16* src = nullptr;
+      if (g < grp.n) src = DOWN ? a.act + (size_t)(grp.start + g) * a.act_ld + ks * kSlice
+                                : a.act + (size_t)a.s_row[grp.start + g] * a.act_ld + ks * kSlice;
+      load_b_frags(src, t, bfr, inv);
+      const float* gp = reinterpret_cast<const float*>(grp.rec + a.off_g);
+      gl[0] = __ldg(gp); gl[1] = __ldg(gp + 1); gl[2] = __ldg(gp + 2);
+    }
+    const int s = (int)(it % S);
+    const uint32_t ph = (uint32_t)((it / S) & 1);
+    if (!mbar_wait(&full[s], ph, a.err, 2u)) break;
+    const uint8_t* st = ring + (size_t)s * C::STAGE;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    warp_slice_mma(st + wA, st + wB, st + sA, st + sB, t, bfr, acc, &empty[s]);
+    acc[0] *= inv[0]; acc[1] *= inv[1]; acc[2] *= inv[0]; acc[3] *= inv[1];
+    float4* rb = red + (size_t)(it & 1) * C::NW * 32;
+    if (WK > 1) {
+      rb[warp * 32 + lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      named_bar_sync(1, C::NW * 32);
+    }
+    const int epi = (int)(it % WK);
+    if (ks == epi) {
+      if (WK > 1) {
+        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+#pragma unroll
+        for (int k2 = 0; k2 < WK; ++k2) {                  // fixed order: deterministic
+          const float4 v = rb[(mt * WK + k2) * 32 + lane];
+          acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+        }
+      }
+      const int tok0 = 2 * t;
+      if (DOWN) {
+        const int n0 = tile * C::TR + 16 * mt + g;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int tok = tok0 + (c & 1), n = n0 + (c >> 1) * 8;
+          if (tok < grp.n) a.outp[(size_t)(grp.start + tok) * a.H + n] = __float2bfloat16(acc[c] * gl[2]);
+        }
+      } else {
+        float oth[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) oth[c] = __shfl_xor_sync(0xffffffffu, acc[c], 4);
+        const bool odd = g & 1;
+        const int i = tile * C::TR + 8 * mt + (g >> 1) + (odd ? 4 : 0);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          float gv = odd ? oth[2 + c] : acc[c], uv = odd ? acc[2 + c] : oth[c];
+          gv = bf16r(gv * gl[0]); uv = bf16r(uv * gl[1]);
+          if (a.limit > 0.f) { uv = fminf(fmaxf(uv, -a.limit), a.limit); gv = fminf(gv, a.limit); }
+          const float yv = gv / (1.f + __expf(-gv)) * uv;
+          const int tok = tok0 + c;
+          if (tok < grp.n) a.outp[(size_t)(grp.start + tok) * a.I + i] = __float2bfloat16(yv);
+        }
+      }
+    }
+  }
+}
+
+// ================================================================================================ reduce / combine
+// Routed form: out[m] = Σ_k w[m,k]·part[pos] in k order; then either fp32 (overwritten) or the shared-expert combine → bf16.
+__global__ void moe_reduce_routed_kernel(const __nv_bfloat16* __restrict__ part, const int* __restrict__ pos_of, const float* __restrict__ pw, int M, int K,
+                                         int H, int shared_pairs, const __nv_bfloat16* __restrict__ shared, const float* __restrict__ lg, int ld, int col,
+                                         __nv_bfloat16* __restrict__ out_bf16, float* __restrict__ out_f32) {
+  griddep_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;      // one thread per (row, 2 columns)
+  if (i >= (size_t)M * H / 2) return;
+  const int m = (int)(i / (H / 2)), d = (int)(i % (H / 2)) * 2;
+  float a0 = 0.f, a1 = 0.f;
+  for (int k = 0; k < K; ++k) {
+    const int pos = pos_of[m * K + k];
+    if (pos < 0) continue;
+    const float wv = pw[m * K + k];
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(part + (size_t)pos * H + d);
+    a0 = __fadd_rn(a0, __fmul_rn(wv, __bfloat162float(v.x)));
+    a1 = __fadd_rn(a1, __fmul_rn(wv, __bfloat162float(v.y)));
+  }
+  if (out_f32) { out_f32[(size_t)m * H + d] = a0; out_f32[(size_t)m * H + d + 1] = a1; }
+  if (!out_bf16) return;
+  float s0 = 0.f, s1 = 0.f;
+  bool have = false;
+  if (shared_pairs) {
+    const int pos = pos_of[M * K + m];
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(part + (size_t)pos * H + d);
+    s0 = __bfloat162float(v.x); s1 = __bfloat162float(v.y); have = true;
+  } else if (shared) {
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(shared + (size_t)m * H + d);
+    s0 = __bfloat162float(v.x); s1 = __bfloat162float(v.y); have = true;
+  }
+  if (have && lg) {
+    const float gt = bf16r(sigmoid_portable(bf16r(lg[(size_t)m * ld + col])));
+    s0 = bf16r(__fmul_rn(gt, s0)); s1 = bf16r(__fmul_rn(gt, s1));
+  }
+  __nv_bfloat162 o;
+  o.x = __float2bfloat16(__fadd_rn(bf16r(a0), s0)); o.y = __float2bfloat16(__fadd_rn(bf16r(a1), s1));
+  *reinterpret_cast<__nv_bfloat162*>(out_bf16 + (size_t)m * H + d) = o;
+}
+
+// List form: out[row] += w·part, pairs visited in list order.  One block column per pair that is the first of its row.
+__global__ void moe_reduce_list_kernel(const __nv_bfloat16* __restrict__ part, const int* __restrict__ pos_of, const int* __restrict__ prow,
+                                       const float* __restrict__ pw, int n_pairs, int H, float* __restrict__ out) {
+  griddep_wait();
+  const int p = blockIdx.y;
+  const int row = prow[p];
+  for (int j = 0; j < p; ++j) if (prow[j] == row) return;             // not the first pair of its row
+  const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (d >= H) return;
+  float2 v = *reinterpret_cast<float2*>(out + (size_t)row * H + d);
+  for (int q = p; q < n_pairs; ++q) {
+    if (prow[q] != row) continue;
+    const int pos = pos_of[q];
+    if (pos < 0) continue;
+    const __nv_bfloat162 e = *reinterpret_cast<const __nv_bfloat162*>(part + (size_t)pos * H + d);
+    const float wv = pw[q];
+    v.x = __fadd_rn(v.x, __fmul_rn(__bfloat162float(e.x), wv));
+    v.y = __fadd_rn(v.y, __fmul_rn(__bfloat162float(e.y), wv));
+  }
+  *reinterpret_cast<float2*>(out + (size_t)row * H + d) = v;
+}
+
+// ================================================================================================ generic shapes (CUDA cores)
+// One block per (sorted pair position, 8 output rows): a warp per output row, the activation row in shared memory as fp32.
+template <bool DOWN>
+__global__ void __launch_bounds__(256) moe_generic_kernel(StreamArgs a) {
+  extern __shared__ float xs[];
+  griddep_wait();
+  const int n_valid = a.hdr[1];
+  const int pos = blockIdx.y;
+  if (pos >= n_valid) return;
+  const int K = DOWN ? a.I : a.H, N = DOWN ? a.H : a.I;
+  // the group that holds this position
+  const int n_groups = a.hdr[0];
+  int gi = 0;
+  for (int lo = 0, hi = n_groups - 1; lo <= hi;) {
+    const int mid = (lo + hi) >> 1;
+    if (a.groups[mid].start <= pos) { gi = mid; lo = mid + 1; } else hi = mid - 1;
+  }
+  const uint8_t* rec = a.groups[gi].rec;
+  const __nv_bfloat16* src = DOWN ? a.act + (size_t)pos * a.act_ld : a.act + (size_t)a.s_row[pos] * a.act_ld;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = __bfloat162float(src[k]);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= N) return;
+  const float* gp = reinterpret_cast<const float*>(rec + a.off_g);
+  float res[2] = {0.f, 0.f};
+  for (int mat = 0; mat < (DOWN ? 1 : 2); ++mat) {
+    const uint8_t* wr = rec + (mat ? a.off_wb : a.off_wa) + (size_t)n * (K / 2);
+    const uint8_t* sr = rec + (mat ? a.off_sb : a.off_sa) + (size_t)n * (K / 16);
+    float acc = 0.f;
+    for (int b = lane; b < K / 16; b += 32) {
+      const uint2 q = *reinterpret_cast<const uint2*>(wr + b * 8);
+      const uint32_t w[2] = {q.x, q.y};
+      float d = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) d = fmaf(xs[b * 16 + j], e2m1_to_f32((w[j >> 3] >> (4 * (j & 7))) & 15), d);
+      acc = fmaf(d, e4m3_to_f32(sr[b]), acc);
+    }
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    res[mat] = acc;
+  }
+  if (lane != 0) return;
+  if (DOWN) {
+    a.outp[(size_t)pos * a.H + n] = __float2bfloat16(res[0] * gp[2]);
+  } else {
+    float gv = bf16r(res[0] * gp[0]), uv = bf16r(res[1] * gp[1]);
+    if (a.limit > 0.f) { uv = fminf(fmaxf(uv, -a.limit), a.limit); gv = fminf(gv, a.limit); }
+    a.outp[(size_t)pos * a.I + n] = __float2bfloat16(gv / (1.f + __expf(-gv)) * uv);
+  }
+}
+
+}  // namespace hb
+
+using namespace hb;
+
+// ================================================================================================ host side
+namespace {
+
+constexpr int kWkList[] = {1, 2, 3, 4, 6, 8, 12, 16};
+constexpr int wm_for(int wk) { return wk >= 8 ? 1 : (wk >= 4 ? 2 : (wk == 3 ? 2 : (wk == 2 ? 4 : 8))); }
+
+using StreamFn = void (*)(StreamArgs);
+struct StreamKernel { StreamFn fn; int threads; int stage; size_t (*smem)(int); int tr; };
+
+template <int WK, bool DOWN>
+StreamKernel make_kernel() {
+  constexpr int WM = wm_for(WK);
+  using C = StreamCfg<WK, WM, DOWN>;
+  return StreamKernel{moe_stream_kernel<WK, WM, DOWN>, C::THREADS, C::STAGE, &C::smem, C::TR};
+}
+template <bool DOWN>
+bool pick_kernel(int K, StreamKernel* out) {
+  if (K % kSlice) return false;
+  switch (K / kSlice) {
+    case 1: *out = make_kernel<1, DOWN>(); return true;
+    case 2: *out = make_kernel<2, DOWN>(); return true;
+    case 3: *out = make_kernel<3, DOWN>(); return true;
+    case 4: *out = make_kernel<4, DOWN>(); return true;
+    case 6: *out = make_kernel<6, DOWN>(); return true;
+    case 8: *out = make_kernel<8, DOWN>(); return true;
+    case 12: *out = make_kernel<12, DOWN>(); return true;
+    case 16: *out = make_kernel<16, DOWN>(); return true;
+    default: return false;
+  }
+}
+
+// stages and CTAs per SM for a streaming kernel: as deep a ring as the shared memory allows, two CTAs per SM when the
+// block is small enough
+void plan_stream(const hb_ctx* ctx, const StreamKernel& k, int* stages, int* ctas_per_sm) {
+  const int budget = ctx->smem_optin;                       // per block opt-in limit (227 KB on sm_100)
+  const int per_sm = 228 * 1024;
+  int cps = (k.threads <= 512) ? 2 : 1;
+  for (;; --cps) {
+    const int avail = (cps == 1 ? budget : per_sm / cps - 1024 - 1024);
+    int s = kMaxStages;
+    while (s > 2 && (long long)k.smem(s) > avail) --s;
+    if ((long long)k.smem(s) <= avail && (s >= 3 || cps == 1)) { *stages = s; *ctas_per_sm = cps; return; }
+  }
+}
+
+}  // namespace
+
+bool hbk_moe_decode_fast(int H, int I) {
+  StreamKernel a, b;
+  return H > 0 && I > 0 && pick_kernel<false>(H, &a) && pick_kernel<true>(I, &b) && I % a.tr == 0 && H % b.tr == 0;
+}
+
+size_t hbk_moe_decode_ws_bytes(int n, int H, int I) {
+  if (n < 1) n = 1;
+  return 256 + al256((size_t)n * sizeof(Group)) + 4 * al256((size_t)n * 4) + al256((size_t)n * I * 2) + al256((size_t)n * H * 2);
+}
+
+int hbk_moe_decode_setup(hb_ctx* ctx) {
+  for (int wk : kWkList) {
+    StreamKernel k[2];
+    pick_kernel<false>(wk * kSlice, &k[0]);
+    pick_kernel<true>(wk * kSlice, &k[1]);
+    for (auto& kk : k) {
+      int s, c;
+      plan_stream(ctx, kk, &s, &c);
+      HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(kk.fn), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kk.smem(s)));
+    }
+  }
+  HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_group_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)group_smem(false, HB_MAX_PAIRS, 0)));
+  return HB_OK;
+}
+
+int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int H, int I, float limit, const hbk_reduce& red, void* ws,
+                       cudaStream_t st) {
+  const bool routed = src.ids != nullptr;
+  const int P = routed ? src.M * src.K + (src.shared_rec ? src.M : 0) : src.n_pairs;
+  if (P <= 0) return HB_OK;
+  const bool pdl = !(ctx->flags & HB_FLAG_NO_PDL);
+  DecodeWs w = carve(ws, P, H, I);
+  hb_rec_layout L;
+  hb_rec_layout_make(H, I, &L);
+
+  GroupArgs ga{};
+  ga.pairs = src.pairs; ga.n_pairs = src.n_pairs; ga.ids = src.ids; ga.w = src.w; ga.M = src.M; ga.K = src.K;
+  ga.tab = src.tab; ga.li = src.li; ga.E = src.E; ga.shared_rec = src.shared_rec; ga.ws = w;
+  cudaError_t e = hb_launch_pdl(pdl, moe_group_kernel, dim3(1), dim3(kGroupThreads), group_smem(routed, P, src.E), st, ga);
+  if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_group: %s", cudaGetErrorString(e));
+  int r = hb_launched(ctx, "moe_group");
+  if (r) return r;
+
+  StreamArgs sa{};
+  sa.hdr = w.hdr; sa.groups = w.groups; sa.s_row = w.s_row; sa.H = H; sa.I = I; sa.limit = limit; sa.err = ctx->dev_err;
+  sa.off_g = (uint32_t)L.g;
+  StreamArgs sd = sa;
+  sa.act = reinterpret_cast<const __nv_bfloat16*>(x); sa.act_ld = H; sa.outp = w.y;
+  sa.off_wa = (uint32_t)L.w1; sa.off_sa = (uint32_t)L.s1; sa.off_wb = (uint32_t)L.w3; sa.off_sb = (uint32_t)L.s3;
+  sd.act = w.y; sd.act_ld = I; sd.outp = w.part;
+  sd.off_wa = (uint32_t)L.w2; sd.off_sa = (uint32_t)L.s2;
+
+  if (hbk_moe_decode_fast(H, I)) {
+    // PDL chain: group → gate/up → down → reduce.  Each streaming kernel calls griddepcontrol.launch_dependents only after its own
+    // griddepcontrol.wait returned (gate/up) or after reading the group list (down), so when the down kernel's producer starts,
+    // the grouping kernel has completed and its list is visible; the down consumers wait for gate/up before reading y.
+    StreamKernel kg, kd;
+    pick_kernel<false>(H, &kg);
+    pick_kernel<true>(I, &kd);
+    int s, c;
+    plan_stream(ctx, kg, &s, &c);
+    sa.stages = s;
+    int grid = ctx->sm_count * c;
+    if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
+    e = hb_launch_pdl(pdl, kg.fn, dim3(grid), dim3(kg.threads), kg.smem(s), st, sa);
+    if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_gate_up: %s", cudaGetErrorString(e));
+    if ((r = hb_launched(ctx, "moe_gate_up"))) return r;
+    plan_stream(ctx, kd, &s, &c);
+    sd.stages = s;
+    grid = ctx->sm_count * c;
+    if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
+    e = hb_launch_pdl(pdl, kd.fn, dim3(grid), dim3(kd.threads), kd.smem(s), st, sd);
+    if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_down: %s", cudaGetErrorString(e));
+    if ((r = hb_launched(ctx, "moe_down"))) return r;
+  } else {
+    e = hb_launch_pdl(pdl, moe_generic_kernel<false>, dim3((I + 7) / 8, P), dim3(256), (size_t)H * 4, st, sa);
+    if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_gate_up_generic: %s", cudaGetErrorString(e));
+    if ((r = hb_launched(ctx, "moe_gate_up_generic"))) return r;
+    e = hb_launch_pdl(pdl, moe_generic_kernel<true>, dim3((H + 7) / 8, P), dim3(256), (size_t)I * 4, st, sd);
+    if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_down_generic: %s", cudaGetErrorString(e));
+    if ((r = hb_launched(ctx, "moe_down_generic"))) return r;
+  }
+
+  if (routed) {
+    e = hb_launch_pdl(pdl, moe_reduce_routed_kernel, dim3((unsigned)(((size_t)src.M * H / 2 + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16*)w.part,
+                      (const int*)w.pos_of, (const float*)w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared),
+                      red.lg, red.ld, red.col, reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32);
+    if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_reduce_routed: %s", cudaGetErrorString(e));
+    return hb_launched(ctx, "moe_reduce_routed");
+  }
+  e = hb_launch_pdl(pdl, moe_reduce_list_kernel, dim3((H / 2 + 255) / 256, P), dim3(256), 0, st, (const __nv_bfloat16*)w.part, (const int*)w.pos_of,
+                    (const int*)w.prow, (const float*)w.pw, P, H, red.out_accum);
+  if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_reduce_list: %s", cudaGetErrorString(e));
+  return hb_launched(ctx, "moe_reduce_list");
+}

@@ -1,0 +1,219 @@
+// Routing and the small row kernels around the expert compute: softmax / sigmoid top-k routers, pair building, the
+// shared-expert combine, and the gather / SwiGLU / scatter-add helpers of the composed prefill path.
+#include "hb_common.cuh"
+#include "hb_kernels.h"
+
+namespace hb {
+
+// (value, id) maximum with ties to the smaller id, over the warp (16,8,4,2,1 butterfly)
+__device__ __forceinline__ void warp_argmax(float& best, int& bid) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bid, o);
+    if (ob > best || (ob == best && oi < bid)) { best = ob; bid = oi; }
+  }
+}
+
+// One warp per row.  p lives in shared memory (E floats per warp).  The exp is the portable polynomial form, the row sum is
+// taken per lane (e = lane, lane+32, …) and then by butterfly, the k picks are summed in pick order — the CPU oracle does
+// the same operations in the same order, so ids and weights agree to the bit.
+__global__ void router_softmax_kernel(const float* __restrict__ logits, int ld, int M, int E, int k, int renorm, int logits_bf16,
+                                      int32_t* __restrict__ ids, float* __restrict__ w) {
+  extern __shared__ float sm_p[];
+  griddep_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (m >= M) return;
+  float* p = sm_p + (size_t)warp * E;
+  const float* lr = logits + (size_t)m * ld;
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) {
+    const float v = logits_bf16 ? bf16r(lr[e]) : lr[e];
+    p[e] = v;
+    mx = fmaxf(mx, v);
+  }
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float v = exp_portable(__fsub_rn(p[e], mx));
+    p[e] = v;
+    sum = __fadd_rn(sum, v);
+  }
+  for (int o = 16; o > 0; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
+  const float inv = __fdiv_rn(1.f, sum);
+  __syncwarp();
+  float my_w = 0.f, tot = 0.f;
+  int my_id = 0;
+  for (int r = 0; r < k; ++r) {
+    float best = -1.f;
+    int bid = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = p[e];
+      if (v >= 0.f && v > best) { best = v; bid = e; }      // ascending e per lane: the first (smaller) id keeps a tie
+    }
+    warp_argmax(best, bid);
+    const float sw = __fmul_rn(best, inv);
+    tot = __fadd_rn(tot, sw);
+    if (lane == r) { my_id = bid; my_w = sw; }
+    if (bid != 0x7fffffff && (bid & 31) == lane) p[bid] = -1.f;
+    __syncwarp();
+  }
+  if (lane < k) {
+    const float sc = renorm ? __fdiv_rn(1.f, tot) : 1.f;
+    ids[(size_t)m * k + lane] = my_id;
+    w[(size_t)m * k + lane] = __fmul_rn(my_w, sc);
+  }
+}
+
+// One warp per row: s = sigmoid(logit), pick k maxima of s + bias (first maximum = smaller id), w = s/(Σs + 1e-20)·scale with
+// Σ in pick order.
+__global__ void router_sigmoid_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int M, int E, int k, float scale,
+                                      int32_t* __restrict__ ids, float* __restrict__ w) {
+  extern __shared__ float sm_p[];
+  griddep_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (m >= M) return;
+  float* s = sm_p + (size_t)warp * 2 * E;
+  float* c = s + E;
+  const float* lr = logits + (size_t)m * E;
+  for (int e = lane; e < E; e += 32) {
+    const float v = sigmoid_portable(lr[e]);
+    s[e] = v;
+    c[e] = bias ? __fadd_rn(v, bias[e]) : v;
+  }
+  __syncwarp();
+  float my_s = 0.f, sum = 0.f;
+  int my_id = 0;
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY;
+    int bid = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = c[e];
+      if (v > best) { best = v; bid = e; }
+    }
+    warp_argmax(best, bid);
+    if (bid == 0x7fffffff) bid = 0;                           // every candidate already taken or NaN: keep a valid id
+    const float sv = s[bid];
+    sum = __fadd_rn(sum, sv);
+    if (lane == j) { my_id = bid; my_s = sv; }
+    __syncwarp();
+    if ((bid & 31) == lane) c[bid] = -INFINITY;
+    __syncwarp();
+  }
+  if (lane < k) {
+    const float inv = __fdiv_rn(1.f, __fadd_rn(sum, 1e-20f));
+    ids[(size_t)m * k + lane] = my_id;
+    w[(size_t)m * k + lane] = __fmul_rn(__fmul_rn(my_s, inv), scale);
+  }
+}
+
+__global__ void build_pairs_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w, int M, int K, const uint8_t* const* __restrict__ tab,
+                                   int li, int E, hb_moe_pair* __restrict__ pairs) {
+  griddep_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= M * K) return;
+  const int e = ids[i];
+  hb_moe_pair p;
+  p.row = i / K;
+  p.rec = (e >= 0 && e < E) ? tab[(size_t)li * E + e] : nullptr;   // a null record is skipped by the decode kernels
+  p.w = p.rec ? w[i] : 0.f;
+  pairs[i] = p;
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ routed, const __nv_bfloat16* __restrict__ shared, const float* __restrict__ lg, int ld,
+                                   int col, int M, int H, __nv_bfloat16* __restrict__ out) {
+  griddep_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)M * H) return;
+  const int m = (int)(i / H);
+  float sh = __bfloat162float(shared[i]);
+  if (lg) sh = bf16r(__fmul_rn(bf16r(sigmoid_portable(bf16r(lg[(size_t)m * ld + col]))), sh));
+  out[i] = __float2bfloat16(__fadd_rn(bf16r(routed[i]), sh));
+}
+
+__global__ void gather_rows_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ rows, int R, int H8, uint4* __restrict__ out) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)R * H8; i += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / H8), c = (int)(i % H8);
+    out[i] = x[(size_t)rows[r] * H8 + c];
+  }
+}
+__global__ void swiglu_rows_kernel(const __nv_bfloat16* __restrict__ gu, int R, int I, float limit, __nv_bfloat16* __restrict__ y) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)R * I; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / I, c = i % I;
+    float g = __bfloat162float(gu[r * 2 * I + c]), u = __bfloat162float(gu[r * 2 * I + I + c]);
+    if (limit > 0.f) { u = fminf(fmaxf(u, -limit), limit); g = fminf(g, limit); }
+    y[i] = __float2bfloat16(__fmul_rn(silu_portable(g), u));
+  }
+}
+__global__ void scatter_add_rows_kernel(const __nv_bfloat16* __restrict__ e, const int32_t* __restrict__ rows, const float* __restrict__ w, int R, int H,
+                                        float* __restrict__ out) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)R * H; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / H, c = i % H;
+    float* o = out + (size_t)rows[r] * H + c;
+    *o = __fadd_rn(*o, __fmul_rn(w[r], __bfloat162float(e[i])));
+  }
+}
+__global__ void add_f32_kernel(float* __restrict__ a, const float* __restrict__ b, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) a[i] = __fadd_rn(a[i], b[i]);
+}
+
+}  // namespace hb
+
+using namespace hb;
+
+static inline int grid_for(hb_ctx* ctx, size_t n, int per_block) {
+  size_t b = (n + per_block - 1) / per_block;
+  const size_t cap = (size_t)ctx->sm_count * 16;
+  if (b > cap) b = cap;
+  return b ? (int)b : 1;
+}
+
+int hbk_route_softmax_topk(hb_ctx* ctx, const float* logits, int ld, int M, int E, int k, int renorm, int logits_bf16, int32_t* ids, float* w,
+                           cudaStream_t st, bool pdl) {
+  const int warps = 4;
+  cudaError_t e = hb_launch_pdl(pdl, router_softmax_kernel, dim3((M + warps - 1) / warps), dim3(warps * 32), (size_t)warps * E * 4, st, logits, ld, M,
+                                E, k, renorm, logits_bf16, ids, w);
+  if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch router_softmax: %s", cudaGetErrorString(e));
+  return hb_launched(ctx, "router_softmax");
+}
+int hbk_route_sigmoid_topk(hb_ctx* ctx, const float* logits, const float* bias, int M, int E, int k, float scale, int32_t* ids, float* w,
+                           cudaStream_t st, bool pdl) {
+  const int warps = 4;
+  cudaError_t e = hb_launch_pdl(pdl, router_sigmoid_kernel, dim3((M + warps - 1) / warps), dim3(warps * 32), (size_t)warps * 2 * E * 4, st, logits,
+                                bias, M, E, k, scale, ids, w);
+  if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch router_sigmoid: %s", cudaGetErrorString(e));
+  return hb_launched(ctx, "router_sigmoid");
+}
+int hbk_build_pairs(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int K, const uint8_t* const* tab, int li, int E, hb_moe_pair* pairs,
+                    cudaStream_t st, bool pdl) {
+  cudaError_t e = hb_launch_pdl(pdl, build_pairs_kernel, dim3((M * K + 255) / 256), dim3(256), 0, st, ids, w, M, K, tab, li, E, pairs);
+  if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch build_pairs: %s", cudaGetErrorString(e));
+  return hb_launched(ctx, "build_pairs");
+}
+int hbk_moe_combine(hb_ctx* ctx, const float* routed, const void* shared, const float* lg, int ld, int col, int M, int H, void* out, cudaStream_t st,
+                    bool pdl) {
+  cudaError_t e = hb_launch_pdl(pdl, moe_combine_kernel, dim3((unsigned)(((size_t)M * H + 255) / 256)), dim3(256), 0, st, routed,
+                                reinterpret_cast<const __nv_bfloat16*>(shared), lg, ld, col, M, H, reinterpret_cast<__nv_bfloat16*>(out));
+  if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_combine: %s", cudaGetErrorString(e));
+  return hb_launched(ctx, "moe_combine");
+}
+int hbk_gather_rows(hb_ctx* ctx, const void* x, const int32_t* rows, int R, int H, void* out, cudaStream_t st) {
+  gather_rows_kernel<<<grid_for(ctx, (size_t)R * (H / 8), 256), 256, 0, st>>>(reinterpret_cast<const uint4*>(x), rows, R, H / 8,
+                                                                             reinterpret_cast<uint4*>(out));
+  return hb_launched(ctx, "gather_rows");
+}
+int hbk_swiglu_rows(hb_ctx* ctx, const void* gu, int R, int I, float limit, void* y, cudaStream_t st) {
+  swiglu_rows_kernel<<<grid_for(ctx, (size_t)R * I, 256), 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(gu), R, I, limit,
+                                                                        reinterpret_cast<__nv_bfloat16*>(y));
+  return hb_launched(ctx, "swiglu_rows");
+}
+int hbk_scatter_add_rows(hb_ctx* ctx, const void* e, const int32_t* rows, const float* w, int R, int H, float* out, cudaStream_t st) {
+  scatter_add_rows_kernel<<<grid_for(ctx, (size_t)R * H, 256), 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(e), rows, w, R, H, out);
+  return hb_launched(ctx, "scatter_add_rows");
+}
+int hbk_add_f32(hb_ctx* ctx, float* a, const float* b, size_t n, cudaStream_t st) {
+  add_f32_kernel<<<grid_for(ctx, n, 256), 256, 0, st>>>(a, b, n);
+  return hb_launched(ctx, "add_f32");
+}

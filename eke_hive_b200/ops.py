@@ -1,0 +1,284 @@
+"""Host-side mirror of the reference engine's expert-compute operators over the C ABI.
+
+Names and argument meaning follow the reference's C++ free functions (engine/include/hive/glm/nvfp4.h, glm/glm_moe.h,
+qwen/fn_moe.h, qwen/qwen_kernels.h, glm/glm_kernels.h); tensors are torch CUDA tensors used as typed device pointers.
+Every call is asynchronous on the current torch CUDA stream and raises HbError on a negative status.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import Config, HbError, MoePair, PfCombine, RecLayout
+
+__all__ = ["Context", "context", "ExpertRecLayout", "nvfp4_dequant", "nvfp4_gemv", "nvfp4_quantize", "a4_quant", "router_softmax_topk",
+           "router_topk", "build_moe_pairs", "moe_combine", "moe_decode_ws_bytes", "moe_decode", "fn_moe_decode_routed", "moe_layer_decode",
+           "moe_decode_supported", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
+
+
+def _L():
+    from . import lib
+    return lib
+
+
+def _p(t):
+    if t is None:
+        return None
+    if isinstance(t, torch.Tensor):
+        assert t.is_cuda, "device tensors only"
+        return t.data_ptr()
+    return int(t)
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+class Context:
+    """One hb_ctx: a device, its SM count and the device error word.  Calls on one context must not overlap."""
+
+    def __init__(self, device: int | None = None, max_ctas: int = 0, flags: int = 0):
+        if not torch.cuda.is_available():
+            raise HbError(-4, "no CUDA device: the library has no CPU path")
+        self.device = torch.cuda.current_device() if device is None else device
+        self._h = C.c_void_p()
+        cfg = Config(self.device, max_ctas, flags)
+        st = _L().hb_create(C.byref(cfg), C.byref(self._h))
+        if st != 0:
+            raise HbError(st, _L().hb_status_string(st).decode())
+
+    def check(self, st: int):
+        if st != 0:
+            raise HbError(st, _L().hb_last_error(self._h).decode())
+
+    @property
+    def handle(self):
+        return self._h
+
+    @property
+    def sm_count(self) -> int:
+        return _L().hb_sm_count(self._h)
+
+    @property
+    def launches(self) -> int:
+        return int(_L().hb_launch_count(self._h))
+
+    def check_device(self):
+        self.check(_L().hb_check_device(self._h, _stream()))
+
+    def close(self):
+        if self._h:
+            _L().hb_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+_CTX: dict[int, Context] = {}
+
+
+def context(device: int | None = None) -> Context:
+    d = torch.cuda.current_device() if device is None else device
+    if d not in _CTX:
+        _CTX[d] = Context(d)
+    return _CTX[d]
+
+
+class ExpertRecLayout:
+    """hive::glm::ExpertRecLayout (engine/include/hive/glm/glm_moe.h:13-22)."""
+
+    def __init__(self, H: int, I: int):
+        r = RecLayout()
+        st = _L().hb_rec_layout_make(H, I, C.byref(r))
+        if st != 0:
+            raise HbError(st, f"bad expert shape H={H} I={I}")
+        self.H, self.I = H, I
+        for n, _ in RecLayout._fields_:
+            setattr(self, n, int(getattr(r, n)))
+
+    @staticmethod
+    def make(H: int, I: int) -> "ExpertRecLayout":
+        return ExpertRecLayout(H, I)
+
+
+# ---------------------------------------------------------------------------------------------------- formats
+def nvfp4_dequant(w: torch.Tensor, s: torch.Tensor, g: float, N: int, K: int, out: torch.Tensor | None = None, ctx: Context | None = None):
+    ctx = ctx or context()
+    out = torch.empty((N, K), dtype=torch.bfloat16, device=w.device) if out is None else out
+    ctx.check(_L().hb_nvfp4_dequant(ctx.handle, _p(w), _p(s), g, N, K, _p(out), _stream()))
+    return out
+
+
+def nvfp4_gemv(w, s, g: float, N: int, K: int, x: torch.Tensor, y: torch.Tensor | None = None, ctx: Context | None = None):
+    """y[m, n] = g·Σ_k x[m, k]·W[n, k]; x bf16 [M, K] (row stride x.stride(0)), M ≤ 16; y fp32 [M, N]."""
+    ctx = ctx or context()
+    M = x.shape[0]
+    y = torch.empty((M, N), dtype=torch.float32, device=x.device) if y is None else y
+    ctx.check(_L().hb_nvfp4_gemv(ctx.handle, _p(w), _p(s), g, N, K, _p(x), x.stride(0), M, _p(y), y.stride(0), _stream()))
+    return y
+
+
+def nvfp4_quantize(w: torch.Tensor, q=None, s=None, g=None, ctx: Context | None = None):
+    """fp32 [N, K] → (codes u8 [N, K/2], scales u8 [N, K/16], g_mul fp32 [1]) by the reference's device rule."""
+    ctx = ctx or context()
+    N, K = w.shape
+    q = torch.empty((N, K // 2), dtype=torch.uint8, device=w.device) if q is None else q
+    s = torch.empty((N, K // 16), dtype=torch.uint8, device=w.device) if s is None else s
+    g = torch.empty(1, dtype=torch.float32, device=w.device) if g is None else g
+    amax = torch.empty(1, dtype=torch.float32, device=w.device)
+    ctx.check(_L().hb_nvfp4_quantize(ctx.handle, _p(w), N, K, _p(q), _p(s), _p(g), _p(amax), _stream()))
+    return q, s, g
+
+
+def a4_quant(x: torch.Tensor, ctx: Context | None = None):
+    ctx = ctx or context()
+    n, K = x.shape
+    q = torch.empty((n, K // 2), dtype=torch.uint8, device=x.device)
+    s = torch.empty((n, K // 16), dtype=torch.uint8, device=x.device)
+    g = torch.empty(n, dtype=torch.float32, device=x.device)
+    ctx.check(_L().hb_a4_quant(ctx.handle, _p(x), x.stride(0), n, K, _p(q), _p(s), _p(g), _stream()))
+    return q, s, g
+
+
+# ---------------------------------------------------------------------------------------------------- routing
+def router_softmax_topk(logits: torch.Tensor, k: int, renorm: bool = True, logits_bf16: bool = True, E: int | None = None, ids=None, w=None,
+                        ctx: Context | None = None):
+    """hive::qwen::router_softmax_topk: logits fp32 [M, ld]; returns ids int32 [M, k], w fp32 [M, k]."""
+    ctx = ctx or context()
+    M, ld = logits.shape[0], logits.stride(0)
+    E = logits.shape[1] if E is None else E
+    ids = torch.empty((M, k), dtype=torch.int32, device=logits.device) if ids is None else ids
+    w = torch.empty((M, k), dtype=torch.float32, device=logits.device) if w is None else w
+    ctx.check(_L().hb_route_softmax_topk(ctx.handle, _p(logits), ld, M, E, k, int(renorm), int(logits_bf16), _p(ids), _p(w), _stream()))
+    return ids, w
+
+
+def router_topk(logits: torch.Tensor, bias: torch.Tensor | None, k: int, scale: float = 1.0, ctx: Context | None = None):
+    """hive::glm::router_topk: sigmoid scores, selection on score + bias."""
+    ctx = ctx or context()
+    M, E = logits.shape
+    ids = torch.empty((M, k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((M, k), dtype=torch.float32, device=logits.device)
+    ctx.check(_L().hb_route_sigmoid_topk(ctx.handle, _p(logits), _p(bias), M, E, k, scale, _p(ids), _p(w), _stream()))
+    return ids, w
+
+
+def rec_table(recs: list[torch.Tensor | None]) -> torch.Tensor:
+    """Device array of record pointers (int64), 0 for a missing record."""
+    dev = next(r.device for r in recs if r is not None)
+    return torch.tensor([0 if r is None else r.data_ptr() for r in recs], dtype=torch.int64, device=dev)
+
+
+def make_pairs(rows, recs, weights, device) -> torch.Tensor:
+    """Packs (row, record pointer, weight) triples into a device array with the hb_moe_pair / hive::glm::MoePair layout."""
+    n = len(rows)
+    a = np.zeros(n, dtype=np.dtype([("row", "<i4"), ("pad", "<i4"), ("rec", "<u8"), ("w", "<f4"), ("pad2", "<i4")]))
+    a["row"] = np.asarray(rows, np.int32)
+    a["rec"] = np.asarray([0 if r is None else (r.data_ptr() if isinstance(r, torch.Tensor) else int(r)) for r in recs], np.uint64)
+    a["w"] = np.asarray(weights, np.float32)
+    return torch.from_numpy(a.view(np.uint8).reshape(n, 24).copy()).to(device)
+
+
+def build_moe_pairs(ids, w, rec_tab, li: int, E: int, ctx: Context | None = None):
+    ctx = ctx or context()
+    M, K = ids.shape
+    pairs = torch.empty((M * K, 24), dtype=torch.uint8, device=ids.device)
+    ctx.check(_L().hb_build_moe_pairs(ctx.handle, _p(ids), _p(w), M, K, _p(rec_tab), li, E, _p(pairs), _stream()))
+    return pairs
+
+
+def moe_combine(routed, shared, lg=None, col: int = 0, out=None, ctx: Context | None = None):
+    ctx = ctx or context()
+    M, H = routed.shape
+    out = torch.empty((M, H), dtype=torch.bfloat16, device=routed.device) if out is None else out
+    ctx.check(_L().hb_moe_combine(ctx.handle, _p(routed), _p(shared), _p(lg), 0 if lg is None else lg.stride(0), col, M, H, _p(out), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------- decode
+def moe_decode_supported(H: int, I: int) -> int:
+    """0 = not accepted, 1 = generic kernels, 2 = streaming tensor-core path."""
+    return int(_L().hb_moe_decode_supported(H, I))
+
+
+def moe_decode_ws_bytes(n_pairs: int, H: int, I: int) -> int:
+    return int(_L().hb_moe_decode_ws_bytes(n_pairs, H, I))
+
+
+def _ws(n_pairs, H, I, device, ws):
+    if ws is None:
+        ws = torch.empty(moe_decode_ws_bytes(n_pairs, H, I), dtype=torch.uint8, device=device)
+    return ws
+
+
+def moe_decode(pairs: torch.Tensor, x: torch.Tensor, H: int, I: int, limit: float, out: torch.Tensor, ws=None, ctx: Context | None = None):
+    """hive::glm::moe_decode: out[row] += Σ_pairs w·expert(x[row]); out fp32 [M, H] accumulated in place."""
+    ctx = ctx or context()
+    n = pairs.shape[0]
+    ws = _ws(n, H, I, x.device, ws)
+    ctx.check(_L().hb_moe_decode(ctx.handle, _p(pairs), n, _p(x), H, I, limit, _p(out), _p(ws), _stream()))
+    return out
+
+
+def fn_moe_decode_routed(ids, w, rec_tab, li: int, E: int, x, H: int, I: int, shared=None, lg=None, col: int = 0, out=None, limit: float = 0.0,
+                         ws=None, ctx: Context | None = None):
+    """hive::qwen::fn_moe_decode_routed: routed sum fused with the shared-expert combine → bf16 [M, H]."""
+    ctx = ctx or context()
+    M, K = ids.shape
+    out = torch.empty((M, H), dtype=torch.bfloat16, device=x.device) if out is None else out
+    ws = _ws(M * K, H, I, x.device, ws)
+    cmb = PfCombine(_p(shared), _p(lg), 0 if lg is None else lg.stride(0), col, _p(out))
+    ctx.check(_L().hb_moe_decode_routed(ctx.handle, _p(ids), _p(w), M, K, _p(rec_tab), li, E, _p(x), H, I, limit, C.byref(cmb), _p(ws), _stream()))
+    return out
+
+
+def moe_layer_decode(logits, x, rec_tab, li: int, E: int, K: int, H: int, I: int, shared_rec=None, gate_col: int = -1, renorm: bool = True,
+                     logits_bf16: bool = True, bias=None, sigmoid_scale: float = 0.0, limit: float = 0.0, ids=None, w=None, out=None, ws=None,
+                     ctx: Context | None = None):
+    """Router → routed experts → NVFP4 shared expert → combine, one call.  Returns (ids, w, out bf16 [M, H])."""
+    ctx = ctx or context()
+    M = x.shape[0]
+    ids = torch.empty((M, K), dtype=torch.int32, device=x.device) if ids is None else ids
+    w = torch.empty((M, K), dtype=torch.float32, device=x.device) if w is None else w
+    out = torch.empty((M, H), dtype=torch.bfloat16, device=x.device) if out is None else out
+    ws = _ws(M * (K + 1), H, I, x.device, ws)
+    ctx.check(_L().hb_moe_layer_decode(ctx.handle, _p(logits), logits.stride(0), M, E, K, int(renorm), int(logits_bf16), _p(bias), sigmoid_scale,
+                                       _p(rec_tab), li, _p(shared_rec), gate_col, _p(x), H, I, limit, _p(ids), _p(w), _p(out), _p(ws), _stream()))
+    return ids, w, out
+
+
+# ---------------------------------------------------------------------------------------------------- prefill helpers
+def gather_rows(x, rows, out=None, ctx: Context | None = None):
+    ctx = ctx or context()
+    R, H = rows.shape[0], x.shape[1]
+    out = torch.empty((R, H), dtype=torch.bfloat16, device=x.device) if out is None else out
+    ctx.check(_L().hb_gather_rows(ctx.handle, _p(x), _p(rows), R, H, _p(out), _stream()))
+    return out
+
+
+def swiglu_rows(gu, limit: float = 0.0, ctx: Context | None = None):
+    ctx = ctx or context()
+    R, I = gu.shape[0], gu.shape[1] // 2
+    y = torch.empty((R, I), dtype=torch.bfloat16, device=gu.device)
+    ctx.check(_L().hb_swiglu_rows(ctx.handle, _p(gu), R, I, limit, _p(y), _stream()))
+    return y
+
+
+def scatter_add_rows(e, rows, w, out, ctx: Context | None = None):
+    ctx = ctx or context()
+    R, H = e.shape
+    ctx.check(_L().hb_scatter_add_rows(ctx.handle, _p(e), _p(rows), _p(w), R, H, _p(out), _stream()))
+    return out
+
+
+def add_f32(a, b, ctx: Context | None = None):
+    ctx = ctx or context()
+    ctx.check(_L().hb_add_f32(ctx.handle, _p(a), _p(b), a.numel(), _stream()))
+    return a

@@ -1,0 +1,154 @@
+/* hive_b200.h — C ABI of the B200 (sm_100a) quantized routed-expert path.
+ *
+ * One shared library, plain pointers and sizes, no C++ or framework types.  Every compute entry point is
+ * stream-ordered and asynchronous: it takes DEVICE pointers, enqueues work on `stream` (a cudaStream_t passed as
+ * void*; NULL = the legacy default stream) and returns without synchronising.  The caller owns every buffer,
+ * including scratch (`ws`), whose size the matching *_ws_bytes function gives.  Nothing is allocated after
+ * hb_create.  Return value: HB_OK (0) or a negative hb_status; hb_last_error() gives the message of the last failure
+ * on that context.  No entry point throws, aborts or falls back to a CPU path.  Calls on one context must not overlap.
+ *
+ * Each declaration cites the operator of the reference engine it stands in for (paths inside the reference project).
+ * The C++ engine's namespaces (hive::glm, hive::qwen, hive::q27::k) are mirrored over this ABI by
+ * eke_hive_b200/csrc/hive_compat.hpp, so reference call sites compile unchanged against this library.
+ */
+#ifndef HIVE_B200_H
+#define HIVE_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define HB_API
+#else
+#define HB_API __attribute__((visibility("default")))
+#endif
+
+typedef enum hb_status {
+  HB_OK = 0,
+  HB_ERR_INVALID = -1,      /* bad argument (null pointer, negative size, misaligned buffer) */
+  HB_ERR_UNSUPPORTED = -2,  /* shape outside what the kernels accept (see hb_*_supported) */
+  HB_ERR_CUDA = -3,         /* a CUDA runtime call failed; message holds cudaGetErrorString */
+  HB_ERR_NO_DEVICE = -4,    /* no usable sm_100 device */
+  HB_ERR_WORKSPACE = -5,    /* ws NULL or not 256-byte aligned */
+  HB_ERR_DEVICE_FLAG = -6   /* a kernel gave up on a bounded wait and set the context's error word */
+} hb_status;
+
+typedef struct hb_ctx hb_ctx;
+
+typedef struct hb_config {
+  int device;       /* CUDA device ordinal */
+  int max_ctas;     /* 0 = one CTA set per SM of the device; >0 caps the persistent grids (tests) */
+  int flags;        /* HB_FLAG_* */
+} hb_config;
+#define HB_FLAG_NO_PDL 1   /* launch every kernel fully serialised (no programmatic dependent launch) */
+
+/* Expert record layout, byte-identical to hive::glm::ExpertRecLayout::make (engine/include/hive/glm/glm_moe.h:13-22):
+ * [w1 gate e2m1 [I,H/2]][s1 e4m3 [I,H/16]][w3 up][s3][w2 down e2m1 [H,I/2]][s2 e4m3 [H,I/16]][g1 g3 g2 fp32], total 4096-aligned. */
+typedef struct hb_rec_layout {
+  uint64_t w1, s1, w3, s3, w2, s2, g, total;
+} hb_rec_layout;
+
+/* One (row, expert) pair — same ABI as hive::glm::MoePair (glm_moe.h:25): row at 0, rec at 8, w at 16, 24 bytes. */
+typedef struct hb_moe_pair {
+  int32_t row;
+  const uint8_t* rec;
+  float w;
+} hb_moe_pair;
+
+/* Shared-expert + gate combine of the routed operators — hive::qwen::FnPfCombine (engine/include/hive/qwen/fn_moe.h:59). */
+typedef struct hb_pf_combine {
+  const void* shared;  /* bf16 [M,H] */
+  const float* lg;     /* gate logit of row m at lg[m*ld + col]; NULL = no gate: out = bf16(bf16(routed)+bf16(shared)) */
+  int ld, col;
+  void* out;           /* bf16 [M,H] */
+} hb_pf_combine;
+
+/* Dense weight matrix of the 27B-style decode GEMV — stands in for hive::q27::GMat (engine/include/hive/q27/q27_kernels.h:17-36). */
+typedef enum hb_wfmt { HB_FMT_NVFP4 = 0, HB_FMT_LB3_G64 = 1, HB_FMT_LB2_G64 = 2 } hb_wfmt;
+typedef struct hb_qmat {
+  int fmt;            /* hb_wfmt */
+  int N, K;           /* out × in */
+  const uint8_t* w;   /* NVFP4: e2m1 [N,K/2].  LB2: codes [N,K/4] (4 per byte, low bits first).
+                         LB3: low-two-bit plane [N,K/4] followed by the high-bit plane [N,K/8] (8 per byte, low bit first). */
+  const void* s;      /* NVFP4: e4m3 [N,K/16].  LB*: fp16 [N,K/64] */
+  const void* zp;     /* LB*: fp16 zero-points [N,K/64]; value = (q - zp) * s.  NVFP4: NULL */
+  float g;            /* NVFP4 per-tensor scale (multiplies); LB*: ignored */
+} hb_qmat;
+
+/* ---- context (house style of the reference's C ABIs: engine/include/hive/qtts/qtts_capi.h:4-35) ---- */
+HB_API int hb_create(const hb_config* cfg, hb_ctx** out);
+HB_API void hb_destroy(hb_ctx* ctx);
+HB_API const char* hb_last_error(const hb_ctx* ctx);
+HB_API const char* hb_status_string(int status);
+HB_API int hb_sm_count(const hb_ctx* ctx);
+/* Reads (and clears) the device error word the kernels set when a bounded wait runs out.  Synchronises `stream`. */
+HB_API int hb_check_device(hb_ctx* ctx, void* stream);
+/* Number of kernels this library has launched on ctx since creation (the benchmark's launch count). */
+HB_API uint64_t hb_launch_count(const hb_ctx* ctx);
+
+/* ---- formats ---- */
+/* hive::glm::ExpertRecLayout::make — engine/include/hive/glm/glm_moe.h:15-21 */
+HB_API int hb_rec_layout_make(int H, int I, hb_rec_layout* out);
+/* hive::glm::nvfp4_dequant — engine/include/hive/glm/nvfp4.h:23, engine/src/glm/nvfp4.cu:65-74: out[n,k] = bf16(E2M1·(e4m3·g)) */
+HB_API int hb_nvfp4_dequant(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int N, int K, void* out_bf16, void* stream);
+/* hive::glm::nvfp4_gemv / hive::q27::k::gemv — engine/include/hive/glm/nvfp4.h:21, engine/src/glm/nvfp4.cu:17-86:
+ * y[m,n] = g·Σ_k x[m,k]·W[n,k], x bf16 [M,K] (row stride ldx), y fp32 [M,N] (row stride ldy), 1 ≤ M ≤ 16, K % 32 == 0. */
+HB_API int hb_nvfp4_gemv(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int N, int K, const void* x_bf16, int ldx, int M,
+                         float* y, int ldy, void* stream);
+/* hive::q27::k::requant_nvfp4's quantisation rule — engine/src/q27/q27_kernels.cu:2492-2542 — applied to an fp32 matrix:
+ * g_mul[0] = amax/(448·6); scale = e4m3(m·gs/6); code = e2m1(v·gs/scale).  amax_scratch: 4 device bytes. */
+HB_API int hb_nvfp4_quantize(hb_ctx* ctx, const float* w_f32, int N, int K, uint8_t* q, uint8_t* s, float* g_mul, float* amax_scratch,
+                             void* stream);
+/* hive::qwen a4_quant_kernel — engine/src/qwen/fn_moe_pf.cu:456-502: per-row dynamic NVFP4 activation quantisation */
+HB_API int hb_a4_quant(hb_ctx* ctx, const void* x_bf16, int ld, int n, int K, uint8_t* q, uint8_t* s, float* g, void* stream);
+
+/* ---- routing ---- */
+/* hive::qwen::router_softmax_topk — engine/include/hive/qwen/qwen_kernels.h:51-55, engine/src/qwen/qwen_kernels.cu:159-206.
+ * logits fp32 [M,ld] (columns 0..E-1), optionally rounded to bf16 first; ties → smaller id; E ≤ 1024, k ≤ 16. */
+HB_API int hb_route_softmax_topk(hb_ctx* ctx, const float* logits, int ld, int M, int E, int k, int renorm, int logits_bf16,
+                                 int32_t* ids, float* w, void* stream);
+/* hive::glm::router_topk — engine/include/hive/glm/glm_kernels.h:12-17, engine/src/glm/glm_kernels.cu:35-53 */
+HB_API int hb_route_sigmoid_topk(hb_ctx* ctx, const float* logits, const float* bias, int M, int E, int k, float scale, int32_t* ids,
+                                 float* w, void* stream);
+/* hive::qwen::build_moe_pairs — engine/include/hive/qwen/qwen_kernels.h:63-66 */
+HB_API int hb_build_moe_pairs(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int K, const uint8_t* const* rec_tab, int li, int E,
+                              hb_moe_pair* pairs, void* stream);
+/* hive::qwen::moe_combine — engine/include/hive/qwen/qwen_kernels.h:58-59 (lg NULL: the GLM form without gate) */
+HB_API int hb_moe_combine(hb_ctx* ctx, const float* routed, const void* shared_bf16, const float* lg, int ld, int col, int M, int H,
+                          void* out_bf16, void* stream);
+
+/* ---- routed-expert decode (1–16 tokens per expert: streaming split-K GEMV) ---- */
+HB_API int hb_moe_decode_supported(int H, int I);
+/* hive::glm::moe_decode_ws_bytes / hive::qwen::fn_moe_decode_ws_bytes — glm_moe.h:29, fn_moe.h:21 */
+HB_API size_t hb_moe_decode_ws_bytes(int n_pairs, int H, int I);
+/* hive::glm::moe_decode / hive::qwen::fn_moe_decode — engine/include/hive/glm/glm_moe.h:27-31, engine/include/hive/qwen/fn_moe.h:22-23:
+ * out[row] += Σ_pairs w·expert(x[row]) (fp32, accumulated; per-row sum in pair order).  limit > 0 clamps (GLM), 0 = plain SiLU. */
+HB_API int hb_moe_decode(hb_ctx* ctx, const hb_moe_pair* pairs, int n_pairs, const void* x_bf16, int H, int I, float limit,
+                         float* out, void* ws, void* stream);
+/* hive::qwen::fn_moe_decode_routed — engine/include/hive/qwen/fn_moe.h:25-31 (without the hybrid CPU/PCIe arguments):
+ * out[m] = bf16( bf16(Σ_k w[m,k]·expert_ids[m,k](x[m])) + bf16( bf16(sigmoid(bf16(lg[m·ld+col]))) · shared[m] ) ).
+ * Records come from rec_tab[li·E + id]; ids outside [0,E) and NULL records contribute nothing.  cmb->lg NULL = no gate. */
+HB_API int hb_moe_decode_routed(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int K, const uint8_t* const* rec_tab, int li, int E,
+                                const void* x_bf16, int H, int I, float limit, const hb_pf_combine* cmb, void* ws, void* stream);
+/* A whole decode MoE layer in one call: router (softmax when bias == NULL and sigmoid_scale == 0, else sigmoid+bias) → routed
+ * experts → the always-on shared expert given as one more NVFP4 record (weight 1, every row; NULL = none) → combine.
+ * Composition of the operators above in the order of engine/src/qwen/qwen_engine.cpp:818-878; ids_out / w_out [M,K] receive
+ * the routing.  gate_col < 0: no shared-expert gate.  ws ≥ hb_moe_decode_ws_bytes(M·(K+1), H, I). */
+HB_API int hb_moe_layer_decode(hb_ctx* ctx, const float* logits, int ld, int M, int E, int K, int renorm, int logits_bf16,
+                               const float* bias, float sigmoid_scale, const uint8_t* const* rec_tab, int li,
+                               const uint8_t* shared_rec, int gate_col, const void* x_bf16, int H, int I, float limit,
+                               int32_t* ids_out, float* w_out, void* out_bf16, void* ws, void* stream);
+
+/* ---- prefill helpers kept for callers that compose (engine/include/hive/glm/glm_moe.h:33-41) ---- */
+HB_API int hb_gather_rows(hb_ctx* ctx, const void* x_bf16, const int32_t* rows, int R, int H, void* out_bf16, void* stream);
+HB_API int hb_swiglu_rows(hb_ctx* ctx, const void* gu_bf16, int R, int I, float limit, void* y_bf16, void* stream);
+HB_API int hb_scatter_add_rows(hb_ctx* ctx, const void* e_bf16, const int32_t* rows, const float* w, int R, int H, float* out, void* stream);
+HB_API int hb_add_f32(hb_ctx* ctx, float* a, const float* b, size_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HIVE_B200_H */

@@ -331,8 +331,9 @@ void ho_nvfp4_quantize(const float* w, int N, int K, int search, uint8_t* q, uin
   float amaxf = 0.f;
   for (size_t i = 0; i < (size_t)N * K; ++i) amaxf = fmaxf(amaxf, fabsf(w[i]));
   const double amax = (double)amaxf;
-  *g_mul = amax > 0 ? (float)(amax / (448.0 * 6.0)) : 1.f;
-  const float g = amax > 0 ? (float)(448.0 * 6.0 / amax) : 1.f;
+  *g_mul = amaxf > 0.f ? amaxf / (448.f * 6.f) : 1.f;                 /* fp32 division, as the device kernel does */
+  /* search: np.float32(448*6/amax) (a double division rounded once); device rule: 448.f*6.f / amax in fp32 */
+  const float g = amaxf > 0.f ? (search ? (float)(448.0 * 6.0 / amax) : 448.f * 6.f / amaxf) : 1.f;
   for (int n = 0; n < N; ++n)
     for (int b = 0; b < K / 16; ++b) {
       const float* wb = w + (size_t)n * K + (size_t)b * 16;

@@ -7,8 +7,9 @@ import numpy as np
 import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
-if str(ROOT) not in sys.path:
-    sys.path.insert(0, str(ROOT))
+for _p in (str(ROOT), str(Path(__file__).resolve().parent)):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
 os.environ.setdefault("FAKE_NUMA_NODES", "1")
 
 GOLDEN = Path(__file__).resolve().parent / "golden"

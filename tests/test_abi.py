@@ -1,0 +1,76 @@
+"""CPU-side checks of the boundary: the shared library loads, exports every symbol the public header declares, lays records out
+exactly like the reference, and sizes workspaces sanely.  No compute call is made (no GPU here)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from eke_hive_b200 import _lib
+    return _lib
+
+
+def test_library_exports_every_declared_symbol(lib):
+    names = lib.declared_symbols()
+    assert len(names) >= 25 and len(set(names)) == len(names)
+    L = lib.load()
+    for n in names:
+        assert hasattr(L, n), n
+
+
+def test_pair_struct_matches_reference_abi(lib):
+    # hive::glm::MoePair {int row; const uint8_t* rec; float w;} on LP64: 24 bytes, rec at 8, w at 16
+    assert C.sizeof(lib.MoePair) == 24 and lib.MoePair.rec.offset == 8 and lib.MoePair.w.offset == 16
+
+
+@pytest.mark.parametrize("H,I", [(2048, 512), (4096, 1536), (7168, 2048), (128, 64)])
+def test_record_layout_matches_reference_and_oracle(lib, oracle, H, I):
+    L = lib.load()
+    r = lib.RecLayout()
+    assert L.hb_rec_layout_make(H, I, C.byref(r)) == 0
+    off = oracle.rec_layout(H, I)
+    got = [r.w1, r.s1, r.w3, r.s3, r.w2, r.s2, r.g, r.total]
+    assert got == [int(v) for v in off]
+    assert r.total % 4096 == 0 and r.total - r.g >= 12 and r.g == 3 * H * I * 9 // 16
+
+
+def test_layout_rejects_bad_shapes(lib):
+    L = lib.load()
+    r = lib.RecLayout()
+    assert L.hb_rec_layout_make(100, 64, C.byref(r)) < 0
+    assert L.hb_rec_layout_make(0, 64, C.byref(r)) < 0
+    assert L.hb_rec_layout_make(128, 64, None) < 0
+
+
+def test_workspace_and_support_queries(lib):
+    L = lib.load()
+    assert L.hb_moe_decode_supported(2048, 512) == 2      # streaming path
+    assert L.hb_moe_decode_supported(4096, 1536) == 2
+    assert L.hb_moe_decode_supported(128, 64) == 1        # generic kernels
+    assert L.hb_moe_decode_supported(7168, 2048) == 1
+    assert L.hb_moe_decode_supported(100, 64) == 0
+    a, b = L.hb_moe_decode_ws_bytes(176, 2048, 512), L.hb_moe_decode_ws_bytes(352, 2048, 512)
+    assert a % 256 == 0 and a >= 176 * (2048 + 512) * 2 and a < b < 2 * a + 4096
+
+
+def test_status_strings_and_null_context(lib):
+    L = lib.load()
+    assert L.hb_status_string(0) == b"ok" and b"unsupported" in L.hb_status_string(-2)
+    assert L.hb_sm_count(None) == 0 and L.hb_launch_count(None) == 0
+    assert L.hb_moe_decode(None, None, 1, None, 256, 256, 0.0, None, None, None) == -1     # null context: a code, not a crash
+
+
+def test_no_cpu_fallback_without_device(lib):
+    """On a machine without a GPU the context cannot be created: the product path fails loudly instead of computing on the host."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    L = lib.load()
+    h = C.c_void_p()
+    cfg = lib.Config(0, 0, 0)
+    assert L.hb_create(C.byref(cfg), C.byref(h)) == -4 and not h.value
+    import eke_hive_b200 as E
+    with pytest.raises(E.HbError):
+        E.Context()
