@@ -53,6 +53,7 @@ def test_a4_quant_bit_exact(E, oracle):
     x = oracle.bf16r(rng.normal(0, 1, (9, 512)).astype(np.float32))
     x[4] = 0
     x[7, 100] = 3.0e5
+    x = oracle.bf16r(x)
     q, s, g = E.a4_quant(bf16_tensor(x))
     q0, s0, g0 = oracle.a4_quant(x)
     assert np.array_equal(q.cpu().numpy(), q0) and np.array_equal(s.cpu().numpy(), s0)

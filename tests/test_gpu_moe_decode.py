@@ -106,6 +106,7 @@ def test_outlier_activations_stay_finite(E, oracle):
     recs = make_records(oracle, H, I, Ex, seed=5)
     x = oracle.bf16r(rng.normal(0, 1, (3, H)).astype(np.float32))
     x[0, 17] = 3.0e5; x[1, 900] = -3.0e5; x[2] *= 1e-6
+    x = oracle.bf16r(x)
     ids = np.array([[0, 1], [2, 1], [3, 0]], np.int32)
     w = np.full((3, 2), 0.5, np.float32)
     acc = oracle.moe_routed(H, I, ids, w, recs, x, 0.0, 0)
