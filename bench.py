@@ -1,0 +1,415 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized routed-expert decode path (Qwen3-Next-shaped MoE, NVFP4 weights, bf16 activations).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one decode step of B tokens through the 48 MoE layers (router → routed NVFP4 experts → NVFP4 shared expert →
+combine), each layer with its own weights, so a step streams ≈ 48 × U × 1.77 MB of distinct expert records (far more than the
+126 MB L2).  The metric is MoE-layer tokens/s = B · layers / step time, whole job.  Printed: ONE JSON line.
+
+  value        device-resident inputs, the 48 layers replayed from one CUDA graph, timed with CUDA events on the launching stream
+  e2e          the same step through the Python mirror of the C ABI with pinned HOST inputs and outputs: H2D of logits and
+               activations, the layers, D2H of the layer outputs, all inside the timed region
+  roofline     the dominant kernel (gate/up weight stream): algorithmic bytes per launch ÷ its mean duration from the library's
+               per-kernel event timing, against the measured HBM copy bandwidth of this pool
+  cpu_baseline the reference engine's own CPU code (oracle/_ref, make_mat + matmul_multi in its CPU daemon's order) on the
+               host cores, on a bounded sample (two layers' worth of experts), reported beside the GPU number
+  --impl reference   times that CPU path alone with the same metric / unit / config
+
+At N > 1 the experts of every layer are sharded over the ranks (expert parallel), each rank brings its own B tokens
+(weak scaling): all-gather of rows and routing → local experts → reduce-scatter of the fp32 routed sums → local combine.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CFG = dict(H=2048, I=512, E=512, K=10, L=48, batches=(1, 4, 8, 16), headline_batch=16, sigma=0.02, seed=2)
+WORKLOAD = "qwen3-next-shaped MoE decode: hidden 2048, 512 routed experts top-10 + 1 shared, intermediate 512, 48 layers, NVFP4 W4A16"
+
+
+def rec_bytes(H, I):
+    return 3 * H * I * 9 // 16 + 12
+
+
+def layer_algorithmic_bytes(H, I, E, K, B, U):
+    """SURVEY/BASELINE figure: U records (incl. the shared expert) + x + out + logits + ids/w."""
+    return U * rec_bytes(H, I) + B * H * 2 + B * H * 2 + B * (E + 1) * 4 + B * K * 8
+
+
+# ------------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clock and clock-event reasons through NVML (read-only) while `active` is set."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap", 0x80: "hw_power_brake",
+               0x2: "applications_clocks_setting", 0x10: "sync_boost", 0x100: "display_clock_setting"}
+
+    def __init__(self, uuid: str, index: int):
+        self.samples, self.reasons, self.active, self._stop = [], set(), False, False
+        self.max_mhz = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            try:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.t = threading.Thread(target=self._run, daemon=True)
+            self.t.start()
+        except Exception as e:  # NVML missing: the line says so instead of inventing numbers
+            self.nv = None
+            self.err = str(e)
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop:
+            if self.active:
+                try:
+                    self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                    for bit, name in self.REASONS.items():
+                        if r & bit:
+                            self.reasons.add(name)
+                except Exception:
+                    pass
+            time.sleep(0.005)
+
+    def result(self):
+        self._stop = True
+        if self.nv is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "error": getattr(self, "err", "nvml unavailable")}
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz, "samples": len(self.samples),
+                "reasons": sorted(self.reasons)}
+
+
+# ------------------------------------------------------------------------------------------------ CPU reference arm
+def cpu_reference(B: int, steps: int, warmup: int, budget_s: float | None, seed: int = 0):
+    """Times the reference's CPU expert path (oracle/_ref) on a bounded sample: two layers' worth of expert records
+    (2 × 513 × 1.77 MB ≈ 1.8 GB, beyond any L3), B tokens, routing from seeded N(0,1) logits.  Returns (tokens_per_s, info)."""
+    os.environ.setdefault("FAKE_NUMA_NODES", "1")
+    from oracle import oracle as O
+    if not O.have_ref():
+        O.build(ref=True)
+    if not O.have_ref():
+        raise RuntimeError("oracle/_ref/libhive_ref.so is not built and the reference tree is not present")
+    H, I, E, K = CFG["H"], CFG["I"], CFG["E"], CFG["K"]
+    n_layers = 2
+    rng = np.random.default_rng(seed)
+    pool = []
+    for _ in range(8):                                            # 8 distinct quantized experts, replicated into distinct memory
+        mats = [O.nvfp4_quantize(rng.normal(0, CFG["sigma"], sh).astype(np.float32), False) for sh in ((I, H), (I, H), (H, I))]
+        pool.append(O.pack_record(H, I, *mats))
+    R = O.ref()
+    threads = int(R.ref_pool_threads())
+    layers = []
+    import ctypes as C
+    off = O.rec_layout(H, I)
+    for li in range(n_layers):
+        recs = [pool[(li * 3 + e) % len(pool)] for e in range(E + 1)]
+        layers.append(R.ref_layer_create(H, I, E + 1, C.cast(O._rec_ptrs(recs), C.POINTER(C.c_void_p)), O._ptr(off, O._u64p)))
+    sets = []
+    for s in range(4):
+        logits = rng.normal(0, 1, (n_layers, B, E)).astype(np.float32)
+        x = O.bf16r(rng.normal(0, 1, (n_layers, B, H)).astype(np.float32))
+        routed = []
+        for li in range(n_layers):
+            ids, w = O.router_softmax_topk(logits[li], K, True, True, 1)
+            ids = np.concatenate([ids, np.full((B, 1), E, np.int32)], axis=1)       # the shared expert: one more record, weight 1
+            w = np.concatenate([w, np.ones((B, 1), np.float32)], axis=1)
+            routed.append((np.ascontiguousarray(ids), np.ascontiguousarray(w)))
+        sets.append((x, routed))
+    acc = np.zeros((B, H), np.float32)
+
+    def one_step(i):
+        x, routed = sets[i % len(sets)]
+        for li in range(n_layers):
+            ids, w = routed[li]
+            R.ref_layer_routed(layers[li], B, K + 1, O._ptr(ids, O._i32p), O._ptr(w, O._f32p), O._ptr(x[li], O._f32p), C.c_float(0.0), O._ptr(acc, O._f32p))
+
+    t0 = time.perf_counter()
+    one_step(0)
+    t1 = time.perf_counter() - t0
+    if budget_s is not None:
+        steps = int(min(max(budget_s / max(t1, 1e-6), 3), 400))
+        warmup = min(warmup, 2)
+    for i in range(warmup):
+        one_step(i)
+    t0 = time.perf_counter()
+    for i in range(steps):
+        one_step(warmup + i)
+    dt = time.perf_counter() - t0
+    for h in layers:
+        R.ref_layer_destroy(h)
+    ms = dt / steps * 1e3
+    value = B * n_layers / (dt / steps)
+    u = float(np.mean([len(np.unique(r[0])) for _, routed in sets for r in routed]))
+    info = {"value": value, "unit": "tokens/s", "cores": threads, "kind": "reference",
+            "sample": f"{n_layers} layers x {E}+1 experts ({n_layers * (E + 1) * rec_bytes(H, I) / 1e9:.2f} GB of records, 8 distinct quantized experts "
+                      f"replicated into distinct memory), B={B} tokens, {steps} timed passes after {warmup}; routed + shared experts via "
+                      f"make_mat/matmul_multi (router and combine left out: <1% of the time)",
+            "ms_per_layer": ms / n_layers, "weight_GBps": u * rec_bytes(H, I) / (ms / n_layers * 1e-3) / 1e9, "numa_nodes": int(R.ref_pool_nodes())}
+    return value, ms, steps, warmup, info
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    B = args.batch or CFG["headline_batch"]
+    value, ms, steps, warmup, info = cpu_reference(B, args.steps, args.warmup, None)
+    line = {"impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate over NVFP4 weights",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "batch_tokens": B, "step": "bounded sample: 2 of the 48 layers per step (see cpu_baseline.sample)"},
+            "cpu_baseline": info, "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+class Layers:
+    """All expert records of the model resident in HBM: [L, E_local + 1, record] (last = the shared expert), quantised on the device
+    from seeded fp32 ~N(0, sigma) with the library's quantiser."""
+
+    def __init__(self, E_mod, H, I, L, experts, sigma, seed, device):
+        import torch
+        self.lay = E_mod.ExpertRecLayout.make(H, I)
+        self.n = len(experts) + 1                                      # local routed experts + shared
+        self.buf = torch.empty((L, self.n, self.lay.total), dtype=torch.uint8, device=device)
+        lay = self.lay
+        gen = torch.Generator(device=device)
+        chunk = 64
+        for li in range(L):
+            for c0 in range(0, self.n, chunk):
+                c1 = min(self.n, c0 + chunk)
+                # seeded per (layer, global expert id): a rank's shard holds the same weights the single-GPU run has
+                ids = [(experts[j] if j < len(experts) else 10 ** 6) for j in range(c0, c1)]
+                w = torch.empty((c1 - c0, 3, H * I), dtype=torch.float32, device=device)
+                for j, gid in enumerate(ids):
+                    gen.manual_seed(seed * 1000003 + li * 4099 + gid)
+                    w[j].normal_(0.0, sigma, generator=gen)
+                for j in range(c1 - c0):
+                    rec = self.buf[li, c0 + j]
+                    g = rec[lay.g:lay.g + 12].view(torch.float32)
+                    for m, (ow, osc, shape) in enumerate(((lay.w1, lay.s1, (I, H)), (lay.w3, lay.s3, (I, H)), (lay.w2, lay.s2, (H, I)))):
+                        N_, K_ = shape
+                        E_mod.nvfp4_quantize(w[j, m].view(N_, K_), q=rec[ow:ow + N_ * K_ // 2], s=rec[osc:osc + N_ * K_ // 16], g=g[m:m + 1])
+                del w
+        torch.cuda.synchronize()
+
+    def ptr(self, li, j):
+        return self.buf[li, j].data_ptr()
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import eke_hive_b200 as E
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    H, I, Ex, K, L = CFG["H"], CFG["I"], CFG["E"], CFG["K"], args.layers or CFG["L"]
+    ctx = E.context()
+    sampler = ClockSampler(str(torch.cuda.get_device_properties(local).uuid), local)
+
+    if world > 1:
+        from eke_hive_b200.ep import ExpertParallelMoE
+        e_lo, e_hi = rank * Ex // world, (rank + 1) * Ex // world
+        experts = list(range(e_lo, e_hi))
+    else:
+        experts = list(range(Ex))
+    t_setup = time.perf_counter()
+    layers = Layers(E, H, I, L, experts, CFG["sigma"], CFG["seed"], dev)
+    n_loc = len(experts)
+    # per-layer device tables of record pointers (global expert id → record or 0) and the shared record
+    tab_host = np.zeros((L, Ex), np.int64)
+    for li in range(L):
+        for j, gid in enumerate(experts):
+            tab_host[li, gid] = layers.ptr(li, j)
+    tab = torch.from_numpy(tab_host.reshape(-1)).to(dev)
+    shared_ptr = [layers.ptr(li, n_loc) for li in range(L)]
+    setup_s = time.perf_counter() - t_setup
+
+    results = {}
+    batches = [args.batch] if args.batch else list(CFG["batches"])
+    head_B = args.batch or CFG["headline_batch"]
+    NSETS = 2
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(CFG["seed"] * 7919 + rank)
+    for B in batches:
+        logits = torch.randn((NSETS, L, B, Ex + 1), dtype=torch.float32, device=dev, generator=gen)     # column E: shared-expert gate logit
+        x = torch.randn((NSETS, L, B, H), dtype=torch.float32, device=dev, generator=gen).to(torch.bfloat16)
+        out = torch.empty((L, B, H), dtype=torch.bfloat16, device=dev)
+        ids = torch.empty((NSETS, L, B, K), dtype=torch.int32, device=dev)
+        wts = torch.empty((NSETS, L, B, K), dtype=torch.float32, device=dev)
+        if world > 1:
+            ep = ExpertParallelMoE(E, ctx, H, I, Ex, K, B, world, rank, dev)
+
+            def run_layers(s):
+                for li in range(L):
+                    ep.layer(logits[s, li], x[s, li], tab, li, shared_ptr[li], Ex, ids[s, li], wts[s, li], out[li])
+        else:
+            ws = torch.empty(E.moe_decode_ws_bytes(B * (K + 1), H, I), dtype=torch.uint8, device=dev)
+
+            def run_layers(s):
+                for li in range(L):
+                    E.moe_layer_decode(logits[s, li], x[s, li], tab, li, Ex, K, H, I, shared_rec=shared_ptr[li], gate_col=Ex, ids=ids[s, li],
+                                       w=wts[s, li], out=out[li], ws=ws, ctx=ctx)
+        # warm every kernel once outside capture, then one graph per input set
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graphs = []
+        with torch.cuda.stream(side):
+            run_layers(0)
+            side.synchronize()
+            n0 = ctx.launches
+            for s in range(NSETS):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    run_layers(s)
+                graphs.append(g)
+            launches_per_step = (ctx.launches - n0) // NSETS
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+
+        def timed(nsteps, fn):
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(nsteps):
+                fn(i)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            if world > 1:
+                t = torch.tensor([ms], dtype=torch.float64, device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            return ms
+
+        for i in range(args.warmup):
+            graphs[i % NSETS].replay()
+        sampler.active = B == head_B
+        ms = timed(args.steps, lambda i: graphs[i % NSETS].replay())
+        sampler.active = False
+        ctx.check_device()
+        ms_step = ms / args.steps
+        ids_h = ids.cpu().numpy()
+        U = np.array([[len(np.unique(ids_h[s, li])) + 1 for li in range(L)] for s in range(NSETS)], np.float64)   # + shared
+        if world > 1:
+            # records streamed by THIS rank: distinct local experts over the gathered batch + its shared copy
+            U = ep.local_records_touched(ids, NSETS, L)
+            t = torch.tensor([U.mean()], dtype=torch.float64, device=dev); dist.all_reduce(t); u_total = float(t.item())
+        else:
+            u_total = float(U.mean())
+        bytes_step = L * layer_algorithmic_bytes(H, I, Ex, K, B * world, u_total)
+        results[B] = {"batch": B, "ms_per_step": ms_step, "us_per_layer": ms_step * 1e3 / L, "tokens_per_s": B * world * L / (ms_step * 1e-3),
+                      "records_per_layer": u_total, "algorithmic_GB_per_step": bytes_step / 1e9, "achieved_GBps": bytes_step / (ms_step * 1e-3) / 1e9,
+                      "launches_per_step": launches_per_step}
+
+        if B == head_B:
+            # ---- end to end: pinned host inputs → H2D → layers → D2H of the outputs, every step
+            hl = [torch.randn((L, B, Ex + 1), dtype=torch.float32).pin_memory() for _ in range(NSETS)]
+            hx = [torch.randn((L, B, H), dtype=torch.float32).to(torch.bfloat16).pin_memory() for _ in range(NSETS)]
+            hout = torch.empty((L, B, H), dtype=torch.bfloat16).pin_memory()
+
+            def e2e_step(i):
+                s = i % NSETS
+                logits[s].copy_(hl[s], non_blocking=True)
+                x[s].copy_(hx[s], non_blocking=True)
+                graphs[s].replay()
+                hout.copy_(out, non_blocking=True)
+
+            for i in range(max(3, args.warmup)):
+                e2e_step(i)
+            sampler.active = True
+            ms_e = timed(args.steps, e2e_step) / args.steps
+            sampler.active = False
+            e2e = {"value": B * world * L / (ms_e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e,
+                   "h2d_bytes_per_step": hl[0].numel() * 4 + hx[0].numel() * 2, "d2h_bytes_per_step": hout.numel() * 2}
+            # ---- per-kernel durations (library event pairs, PDL off, no graph) for the roofline of the dominant kernel
+            prof = None
+            if world == 1:
+                ctx.profile(True)
+                nprof = max(1, min(args.steps, 8192 // (launches_per_step + 1)))
+                for i in range(nprof):
+                    run_layers(i % NSETS)
+                prof = ctx.profile_read()
+                ctx.profile(False)
+                prof = {k: {"launches": v[0], "total_ms": v[1], "mean_us": v[1] * 1e3 / max(v[0], 1)} for k, v in prof.items()}
+        del logits, x, out, ids, wts, graphs
+        torch.cuda.empty_cache()
+
+    head = results[head_B]
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_src = "measured copy bandwidth of this pool (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s (earlier measurement on this pool)"
+    roofline = None
+    if world == 1 and prof and "moe_gate_up" in prof:
+        U = head["records_per_layer"]
+        gu_bytes = U * (2 * H * I * 9 // 16) + head_B * H * 2                     # gate+up halves of U records + the activation rows
+        ach = gu_bytes / (prof["moe_gate_up"]["mean_us"] * 1e-6) / 1e9
+        roofline = {"bound": "hbm", "kernel": "moe_gate_up (moe_stream_kernel<8,1,false>)", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                    "peak_source": peak_src, "traffic": None, "algorithmic_bytes_per_launch": gu_bytes, "mean_us": prof["moe_gate_up"]["mean_us"]}
+    clocks = sampler.result()
+    line = {"metric": "moe_layer_tokens_per_s", "value": head["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 products of e2m1·e4m3 weights and bf16 activations, f32 accumulate",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "batch_tokens_per_gpu": head_B, "layers": L,
+                                            "l2": "inputs larger than L2: every step streams %.1f GB of distinct expert records" % head["algorithmic_GB_per_step"],
+                                            "parallelism": "single GPU" if world == 1 else f"expert-parallel ep{world}: experts sharded, all-gather rows+routing, reduce-scatter fp32 sums"},
+            "layer": {"achieved_GBps": head["achieved_GBps"], "frac_of_measured_hbm": head["achieved_GBps"] / world / peak, "us_per_layer": head["us_per_layer"],
+                      "records_per_layer": head["records_per_layer"]},
+            "per_batch": [results[b] for b in sorted(results)], "roofline": roofline, "e2e": e2e, "gpu_launches": head["launches_per_step"] * args.steps,
+            "clocks": clocks, "kernels": prof, "setup_s": setup_s}
+    if world == 1 and not args.no_cpu:
+        try:
+            _, _, _, _, info = cpu_reference(head_B, 0, 1, args.cpu_budget)
+            line["cpu_baseline"] = info
+        except Exception as ex:  # the reference library was never built on this machine
+            line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "reference", "sample": f"unavailable: {ex}"}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=0, help="run one batch size only (default: 1, 4, 8, 16; headline 16)")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than 48 (development only; the number is then not the benchmark's)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for the baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -39,6 +39,10 @@ class PfCombine(C.Structure):
     _fields_ = [("shared", C.c_void_p), ("lg", C.c_void_p), ("ld", C.c_int), ("col", C.c_int), ("out", C.c_void_p)]
 
 
+class KernelStat(C.Structure):
+    _fields_ = [("name", C.c_char * 40), ("launches", C.c_uint32), ("total_ms", C.c_float)]
+
+
 class QMat(C.Structure):
     _fields_ = [("fmt", C.c_int), ("N", C.c_int), ("K", C.c_int), ("w", C.c_void_p), ("s", C.c_void_p), ("zp", C.c_void_p), ("g", C.c_float)]
 
@@ -69,6 +73,8 @@ def load() -> C.CDLL:
         "hb_sm_count": (i, [vp]),
         "hb_check_device": (i, [vp, vp]),
         "hb_launch_count": (C.c_uint64, [vp]),
+        "hb_profile_enable": (i, [vp, i]),
+        "hb_profile_read": (i, [vp, C.POINTER(KernelStat), i, C.POINTER(i)]),
         "hb_rec_layout_make": (i, [i, i, C.POINTER(RecLayout)]),
         "hb_nvfp4_dequant": (i, [vp, vp, vp, f, i, i, vp, vp]),
         "hb_nvfp4_gemv": (i, [vp, vp, vp, f, i, i, vp, i, i, vp, i, vp]),

@@ -42,7 +42,49 @@ int hb_create(const hb_config* cfg, hb_ctx** out) {
 void hb_destroy(hb_ctx* ctx) {
   if (!ctx) return;
   if (ctx->dev_err) cudaFree(ctx->dev_err);
+  if (ctx->prof_ev) {
+    for (int i = 0; i < 2 * hb_ctx::kProfMax; ++i) cudaEventDestroy(ctx->prof_ev[i]);
+    delete[] ctx->prof_ev;
+    delete[] ctx->prof_name;
+  }
   delete ctx;
+}
+
+int hb_profile_enable(hb_ctx* ctx, int on) {
+  HB_CTX(ctx);
+  if (on && !ctx->prof_ev) {
+    ctx->prof_ev = new (std::nothrow) cudaEvent_t[2 * hb_ctx::kProfMax];
+    ctx->prof_name = new (std::nothrow) const char*[hb_ctx::kProfMax];
+    if (!ctx->prof_ev || !ctx->prof_name) return hb_fail(ctx, HB_ERR_CUDA, "profile: out of host memory");
+    for (int i = 0; i < 2 * hb_ctx::kProfMax; ++i) HB_CUDA(ctx, cudaEventCreate(&ctx->prof_ev[i]));
+  }
+  ctx->prof_on = on != 0;
+  ctx->prof_n = 0;
+  return HB_OK;
+}
+
+int hb_profile_read(hb_ctx* ctx, hb_kernel_stat* out, int max_out, int* n_out) {
+  HB_CTX(ctx); HB_PTR(ctx, out); HB_PTR(ctx, n_out);
+  *n_out = 0;
+  HB_CUDA(ctx, cudaDeviceSynchronize());
+  int n = 0;
+  for (int i = 0; i < ctx->prof_n; ++i) {
+    float ms = 0.f;
+    HB_CUDA(ctx, cudaEventElapsedTime(&ms, ctx->prof_ev[2 * i], ctx->prof_ev[2 * i + 1]));
+    int j = 0;
+    while (j < n && strncmp(out[j].name, ctx->prof_name[i], sizeof out[j].name - 1) != 0) ++j;
+    if (j == n) {
+      if (n >= max_out) continue;
+      memset(&out[n], 0, sizeof out[n]);
+      strncpy(out[n].name, ctx->prof_name[i], sizeof out[n].name - 1);
+      ++n;
+    }
+    out[j].launches++;
+    out[j].total_ms += ms;
+  }
+  ctx->prof_n = 0;
+  *n_out = n;
+  return HB_OK;
 }
 
 const char* hb_last_error(const hb_ctx* ctx) { return ctx ? ctx->err : "null context"; }

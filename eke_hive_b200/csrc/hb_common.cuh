@@ -21,6 +21,12 @@ struct hb_ctx {
   uint32_t* dev_err = nullptr;   // device error word: 0 = fine; kernels OR a site code into it when a bounded wait gives up
   unsigned long long launches = 0;
   char err[512] = {0};
+  // optional per-kernel timing (hb_profile_enable): a start/stop event pair around every launch, aggregated by hb_profile_read
+  bool prof_on = false;
+  int prof_n = 0;
+  static constexpr int kProfMax = 8192;
+  cudaEvent_t* prof_ev = nullptr;        // [2 * kProfMax], created on first enable
+  const char** prof_name = nullptr;      // [kProfMax]
 };
 
 inline int hb_fail(hb_ctx* ctx, int code, const char* fmt, ...) {
@@ -44,28 +50,29 @@ inline int hb_fail(hb_ctx* ctx, int code, const char* fmt, ...) {
     if (!(cond)) return hb_fail((ctx), (code), __VA_ARGS__); \
   } while (0)
 
-// Returns HB_OK or records the launch error.  Every kernel launch of the library goes through this (it also counts launches).
-inline int hb_launched(hb_ctx* ctx, const char* what) {
+// Every kernel launch of the library goes through hb_launch: it counts the launch, converts a launch failure into a status
+// with a message, optionally asks for programmatic dependent launch (the kernel then calls griddep_wait() before touching its
+// inputs) and, when profiling is on, brackets the kernel with a CUDA event pair (PDL is then off so the pair times the kernel alone).
+template <typename... KArgs, typename... Args>
+inline int hb_launch(hb_ctx* ctx, const char* what, bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                     Args... args) {
+  const bool prof = ctx->prof_on && ctx->prof_n < hb_ctx::kProfMax;
+  if (prof) cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], st);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = (pdl && !ctx->prof_on && !(ctx->flags & HB_FLAG_NO_PDL)) ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (prof) { cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n + 1], st); ctx->prof_name[ctx->prof_n++] = what; }
   ctx->launches++;
-  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch %s: %s", what, cudaGetErrorString(e));
   return HB_OK;
 }
 
 inline size_t hb_align256(size_t b) { return (b + 255) / 256 * 256; }
 inline bool hb_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
-
-// Launch with the programmatic-dependent-launch attribute (the kernel calls griddep_wait() before touching its inputs).
-template <typename... KArgs, typename... Args>
-inline cudaError_t hb_launch_pdl(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
-}
 
 // ------------------------------------------------------------------------------------------------ device toolbox
 #ifdef __CUDACC__

@@ -596,7 +596,6 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
   const bool routed = src.ids != nullptr;
   const int P = routed ? src.M * src.K + (src.shared_rec ? src.M : 0) : src.n_pairs;
   if (P <= 0) return HB_OK;
-  const bool pdl = !(ctx->flags & HB_FLAG_NO_PDL);
   DecodeWs w = carve(ws, P, H, I);
   hb_rec_layout L;
   hb_rec_layout_make(H, I, &L);
@@ -604,9 +603,7 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
   GroupArgs ga{};
   ga.pairs = src.pairs; ga.n_pairs = src.n_pairs; ga.ids = src.ids; ga.w = src.w; ga.M = src.M; ga.K = src.K;
   ga.tab = src.tab; ga.li = src.li; ga.E = src.E; ga.shared_rec = src.shared_rec; ga.ws = w;
-  cudaError_t e = hb_launch_pdl(pdl, moe_group_kernel, dim3(1), dim3(kGroupThreads), group_smem(routed, P, src.E), st, ga);
-  if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_group: %s", cudaGetErrorString(e));
-  int r = hb_launched(ctx, "moe_group");
+  int r = hb_launch(ctx, "moe_group", true, moe_group_kernel, dim3(1), dim3(kGroupThreads), group_smem(routed, P, src.E), st, ga);
   if (r) return r;
 
   StreamArgs sa{};
@@ -630,34 +627,22 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
     sa.stages = s;
     int grid = ctx->sm_count * c;
     if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
-    e = hb_launch_pdl(pdl, kg.fn, dim3(grid), dim3(kg.threads), kg.smem(s), st, sa);
-    if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_gate_up: %s", cudaGetErrorString(e));
-    if ((r = hb_launched(ctx, "moe_gate_up"))) return r;
+    if ((r = hb_launch(ctx, "moe_gate_up", true, kg.fn, dim3(grid), dim3(kg.threads), kg.smem(s), st, sa))) return r;
     plan_stream(ctx, kd, &s, &c);
     sd.stages = s;
     grid = ctx->sm_count * c;
     if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
-    e = hb_launch_pdl(pdl, kd.fn, dim3(grid), dim3(kd.threads), kd.smem(s), st, sd);
-    if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_down: %s", cudaGetErrorString(e));
-    if ((r = hb_launched(ctx, "moe_down"))) return r;
+    if ((r = hb_launch(ctx, "moe_down", true, kd.fn, dim3(grid), dim3(kd.threads), kd.smem(s), st, sd))) return r;
   } else {
-    e = hb_launch_pdl(pdl, moe_generic_kernel<false>, dim3((I + 7) / 8, P), dim3(256), (size_t)H * 4, st, sa);
-    if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_gate_up_generic: %s", cudaGetErrorString(e));
-    if ((r = hb_launched(ctx, "moe_gate_up_generic"))) return r;
-    e = hb_launch_pdl(pdl, moe_generic_kernel<true>, dim3((H + 7) / 8, P), dim3(256), (size_t)I * 4, st, sd);
-    if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_down_generic: %s", cudaGetErrorString(e));
-    if ((r = hb_launched(ctx, "moe_down_generic"))) return r;
+    if ((r = hb_launch(ctx, "moe_gate_up_generic", true, moe_generic_kernel<false>, dim3((I + 7) / 8, P), dim3(256), (size_t)H * 4, st, sa))) return r;
+    if ((r = hb_launch(ctx, "moe_down_generic", true, moe_generic_kernel<true>, dim3((H + 7) / 8, P), dim3(256), (size_t)I * 4, st, sd))) return r;
   }
 
-  if (routed) {
-    e = hb_launch_pdl(pdl, moe_reduce_routed_kernel, dim3((unsigned)(((size_t)src.M * H / 2 + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16*)w.part,
-                      (const int*)w.pos_of, (const float*)w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared),
-                      red.lg, red.ld, red.col, reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32);
-    if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_reduce_routed: %s", cudaGetErrorString(e));
-    return hb_launched(ctx, "moe_reduce_routed");
-  }
-  e = hb_launch_pdl(pdl, moe_reduce_list_kernel, dim3((H / 2 + 255) / 256, P), dim3(256), 0, st, (const __nv_bfloat16*)w.part, (const int*)w.pos_of,
-                    (const int*)w.prow, (const float*)w.pw, P, H, red.out_accum);
-  if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_reduce_list: %s", cudaGetErrorString(e));
-  return hb_launched(ctx, "moe_reduce_list");
+  if (routed)
+    return hb_launch(ctx, "moe_reduce_routed", true, moe_reduce_routed_kernel, dim3((unsigned)(((size_t)src.M * H / 2 + 255) / 256)), dim3(256), 0, st,
+                     (const __nv_bfloat16*)w.part, (const int*)w.pos_of, (const float*)w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0,
+                     reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col, reinterpret_cast<__nv_bfloat16*>(red.out_bf16),
+                     red.out_f32);
+  return hb_launch(ctx, "moe_reduce_list", true, moe_reduce_list_kernel, dim3((H / 2 + 255) / 256, P), dim3(256), 0, st, (const __nv_bfloat16*)w.part,
+                   (const int*)w.pos_of, (const int*)w.prow, (const float*)w.pw, P, H, red.out_accum);
 }

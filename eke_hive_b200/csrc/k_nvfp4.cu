@@ -157,36 +157,35 @@ using namespace hb;
 
 int hbk_nvfp4_dequant(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int N, int K, void* out, cudaStream_t st) {
   const size_t nb = (size_t)N * K / 16;
-  const int blocks = (int)((nb + 255) / 256 < (size_t)ctx->sm_count * 16 ? (nb + 255) / 256 : (size_t)ctx->sm_count * 16);
-  nvfp4_dequant_kernel<<<blocks, 256, 0, st>>>(w, s, g, nb, reinterpret_cast<__nv_bfloat16*>(out));
-  return hb_launched(ctx, "nvfp4_dequant");
+  size_t blocks = (nb + 255) / 256, cap = (size_t)ctx->sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  return hb_launch(ctx, "nvfp4_dequant", false, nvfp4_dequant_kernel, dim3((unsigned)blocks), dim3(256), 0, st, w, s, g, nb,
+                   reinterpret_cast<__nv_bfloat16*>(out));
 }
 
 int hbk_nvfp4_gemv(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int N, int K, const void* x, int ldx, int M, float* y, int ldy,
                    cudaStream_t st) {
   const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
-  const int blocks = (N + 7) / 8;
-  if (M <= 1) nvfp4_gemv_kernel<1><<<blocks, 256, 0, st>>>(w, s, g, N, K, xb, ldx, M, y, ldy);
-  else if (M <= 2) nvfp4_gemv_kernel<2><<<blocks, 256, 0, st>>>(w, s, g, N, K, xb, ldx, M, y, ldy);
-  else if (M <= 4) nvfp4_gemv_kernel<4><<<blocks, 256, 0, st>>>(w, s, g, N, K, xb, ldx, M, y, ldy);
-  else if (M <= 8) nvfp4_gemv_kernel<8><<<blocks, 256, 0, st>>>(w, s, g, N, K, xb, ldx, M, y, ldy);
-  else nvfp4_gemv_kernel<16><<<blocks, 256, 0, st>>>(w, s, g, N, K, xb, ldx, M, y, ldy);
-  return hb_launched(ctx, "nvfp4_gemv");
+  const dim3 grid((N + 7) / 8), block(256);
+  auto fn = M <= 1 ? nvfp4_gemv_kernel<1> : M <= 2 ? nvfp4_gemv_kernel<2> : M <= 4 ? nvfp4_gemv_kernel<4> : M <= 8 ? nvfp4_gemv_kernel<8>
+                                                                                                                  : nvfp4_gemv_kernel<16>;
+  return hb_launch(ctx, "nvfp4_gemv", false, fn, grid, block, 0, st, w, s, g, N, K, xb, ldx, M, y, ldy);
 }
 
 int hbk_nvfp4_quantize(hb_ctx* ctx, const float* w, int N, int K, uint8_t* q, uint8_t* s, float* g_mul, float* amax, cudaStream_t st) {
   const size_t n = (size_t)N * K, nb = n / 16;
   cudaError_t e = cudaMemsetAsync(amax, 0, 4, st);
   if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "memset amax: %s", cudaGetErrorString(e));
-  const int blocks = (int)((n / 4 + 255) / 256 < (size_t)ctx->sm_count * 8 ? (n / 4 + 255) / 256 : (size_t)ctx->sm_count * 8);
-  amax_f32_kernel<<<blocks > 0 ? blocks : 1, 256, 0, st>>>(w, n, amax);
-  int r = hb_launched(ctx, "amax_f32");
+  size_t blocks = (n / 4 + 255) / 256, cap = (size_t)ctx->sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  int r = hb_launch(ctx, "amax_f32", false, amax_f32_kernel, dim3((unsigned)blocks), dim3(256), 0, st, w, n, amax);
   if (r) return r;
-  nvfp4_quant_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, st>>>(w, nb, amax, q, s, g_mul);
-  return hb_launched(ctx, "nvfp4_quant");
+  return hb_launch(ctx, "nvfp4_quant", false, nvfp4_quant_kernel, dim3((unsigned)((nb + 255) / 256)), dim3(256), 0, st, w, nb, (const float*)amax, q, s,
+                   g_mul);
 }
 
 int hbk_a4_quant(hb_ctx* ctx, const void* x, int ld, int n, int K, uint8_t* q, uint8_t* s, float* g, cudaStream_t st) {
-  a4_quant_kernel<<<(n + 7) / 8, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), ld, n, K, q, s, g);
-  return hb_launched(ctx, "a4_quant");
+  return hb_launch(ctx, "a4_quant", false, a4_quant_kernel, dim3((n + 7) / 8), dim3(256), 0, st, reinterpret_cast<const __nv_bfloat16*>(x), ld, n, K,
+                   q, s, g);
 }

@@ -173,47 +173,36 @@ static inline int grid_for(hb_ctx* ctx, size_t n, int per_block) {
 int hbk_route_softmax_topk(hb_ctx* ctx, const float* logits, int ld, int M, int E, int k, int renorm, int logits_bf16, int32_t* ids, float* w,
                            cudaStream_t st, bool pdl) {
   const int warps = 4;
-  cudaError_t e = hb_launch_pdl(pdl, router_softmax_kernel, dim3((M + warps - 1) / warps), dim3(warps * 32), (size_t)warps * E * 4, st, logits, ld, M,
-                                E, k, renorm, logits_bf16, ids, w);
-  if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch router_softmax: %s", cudaGetErrorString(e));
-  return hb_launched(ctx, "router_softmax");
+  return hb_launch(ctx, "router_softmax", pdl, router_softmax_kernel, dim3((M + warps - 1) / warps), dim3(warps * 32), (size_t)warps * E * 4, st,
+                   logits, ld, M, E, k, renorm, logits_bf16, ids, w);
 }
 int hbk_route_sigmoid_topk(hb_ctx* ctx, const float* logits, const float* bias, int M, int E, int k, float scale, int32_t* ids, float* w,
                            cudaStream_t st, bool pdl) {
   const int warps = 4;
-  cudaError_t e = hb_launch_pdl(pdl, router_sigmoid_kernel, dim3((M + warps - 1) / warps), dim3(warps * 32), (size_t)warps * 2 * E * 4, st, logits,
-                                bias, M, E, k, scale, ids, w);
-  if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch router_sigmoid: %s", cudaGetErrorString(e));
-  return hb_launched(ctx, "router_sigmoid");
+  return hb_launch(ctx, "router_sigmoid", pdl, router_sigmoid_kernel, dim3((M + warps - 1) / warps), dim3(warps * 32), (size_t)warps * 2 * E * 4, st,
+                   logits, bias, M, E, k, scale, ids, w);
 }
 int hbk_build_pairs(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int K, const uint8_t* const* tab, int li, int E, hb_moe_pair* pairs,
                     cudaStream_t st, bool pdl) {
-  cudaError_t e = hb_launch_pdl(pdl, build_pairs_kernel, dim3((M * K + 255) / 256), dim3(256), 0, st, ids, w, M, K, tab, li, E, pairs);
-  if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch build_pairs: %s", cudaGetErrorString(e));
-  return hb_launched(ctx, "build_pairs");
+  return hb_launch(ctx, "build_pairs", pdl, build_pairs_kernel, dim3((M * K + 255) / 256), dim3(256), 0, st, ids, w, M, K, tab, li, E, pairs);
 }
 int hbk_moe_combine(hb_ctx* ctx, const float* routed, const void* shared, const float* lg, int ld, int col, int M, int H, void* out, cudaStream_t st,
                     bool pdl) {
-  cudaError_t e = hb_launch_pdl(pdl, moe_combine_kernel, dim3((unsigned)(((size_t)M * H + 255) / 256)), dim3(256), 0, st, routed,
-                                reinterpret_cast<const __nv_bfloat16*>(shared), lg, ld, col, M, H, reinterpret_cast<__nv_bfloat16*>(out));
-  if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "launch moe_combine: %s", cudaGetErrorString(e));
-  return hb_launched(ctx, "moe_combine");
+  return hb_launch(ctx, "moe_combine", pdl, moe_combine_kernel, dim3((unsigned)(((size_t)M * H + 255) / 256)), dim3(256), 0, st, routed,
+                   reinterpret_cast<const __nv_bfloat16*>(shared), lg, ld, col, M, H, reinterpret_cast<__nv_bfloat16*>(out));
 }
 int hbk_gather_rows(hb_ctx* ctx, const void* x, const int32_t* rows, int R, int H, void* out, cudaStream_t st) {
-  gather_rows_kernel<<<grid_for(ctx, (size_t)R * (H / 8), 256), 256, 0, st>>>(reinterpret_cast<const uint4*>(x), rows, R, H / 8,
-                                                                             reinterpret_cast<uint4*>(out));
-  return hb_launched(ctx, "gather_rows");
+  return hb_launch(ctx, "gather_rows", false, gather_rows_kernel, dim3(grid_for(ctx, (size_t)R * (H / 8), 256)), dim3(256), 0, st,
+                   reinterpret_cast<const uint4*>(x), rows, R, H / 8, reinterpret_cast<uint4*>(out));
 }
 int hbk_swiglu_rows(hb_ctx* ctx, const void* gu, int R, int I, float limit, void* y, cudaStream_t st) {
-  swiglu_rows_kernel<<<grid_for(ctx, (size_t)R * I, 256), 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(gu), R, I, limit,
-                                                                        reinterpret_cast<__nv_bfloat16*>(y));
-  return hb_launched(ctx, "swiglu_rows");
+  return hb_launch(ctx, "swiglu_rows", false, swiglu_rows_kernel, dim3(grid_for(ctx, (size_t)R * I, 256)), dim3(256), 0, st,
+                   reinterpret_cast<const __nv_bfloat16*>(gu), R, I, limit, reinterpret_cast<__nv_bfloat16*>(y));
 }
 int hbk_scatter_add_rows(hb_ctx* ctx, const void* e, const int32_t* rows, const float* w, int R, int H, float* out, cudaStream_t st) {
-  scatter_add_rows_kernel<<<grid_for(ctx, (size_t)R * H, 256), 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(e), rows, w, R, H, out);
-  return hb_launched(ctx, "scatter_add_rows");
+  return hb_launch(ctx, "scatter_add_rows", false, scatter_add_rows_kernel, dim3(grid_for(ctx, (size_t)R * H, 256)), dim3(256), 0, st,
+                   reinterpret_cast<const __nv_bfloat16*>(e), rows, w, R, H, out);
 }
 int hbk_add_f32(hb_ctx* ctx, float* a, const float* b, size_t n, cudaStream_t st) {
-  add_f32_kernel<<<grid_for(ctx, n, 256), 256, 0, st>>>(a, b, n);
-  return hb_launched(ctx, "add_f32");
+  return hb_launch(ctx, "add_f32", false, add_f32_kernel, dim3(grid_for(ctx, n, 256)), dim3(256), 0, st, a, (const float*)b, n);
 }

@@ -66,6 +66,18 @@ class Context:
     def launches(self) -> int:
         return int(_L().hb_launch_count(self._h))
 
+    def profile(self, on: bool):
+        """Turns per-kernel event timing on or off (see hb_profile_enable)."""
+        self.check(_L().hb_profile_enable(self._h, int(on)))
+
+    def profile_read(self) -> dict[str, tuple[int, float]]:
+        """{kernel name: (launches, total ms)} since the last read; synchronises the device."""
+        from ._lib import KernelStat
+        arr = (KernelStat * 64)()
+        n = C.c_int(0)
+        self.check(_L().hb_profile_read(self._h, arr, 64, C.byref(n)))
+        return {arr[i].name.decode(): (int(arr[i].launches), float(arr[i].total_ms)) for i in range(n.value)}
+
     def check_device(self):
         self.check(_L().hb_check_device(self._h, _stream()))
 

@@ -88,6 +88,17 @@ HB_API int hb_sm_count(const hb_ctx* ctx);
 HB_API int hb_check_device(hb_ctx* ctx, void* stream);
 /* Number of kernels this library has launched on ctx since creation (the benchmark's launch count). */
 HB_API uint64_t hb_launch_count(const hb_ctx* ctx);
+/* Per-kernel device timing — the counterpart of the reference's HIVE_PROFILE event marks (engine/include/hive/glm/glm_experts.h:148-157).
+ * While enabled, every kernel launch is bracketed by a CUDA event pair (and programmatic dependent launch is off, so a pair times
+ * its kernel alone); hb_profile_read synchronises the device, sums the pairs by kernel name and clears the log (at most 8192
+ * launches are kept between reads).  Enabling it the first time creates the events; do not enable it during stream capture. */
+typedef struct hb_kernel_stat {
+  char name[40];
+  uint32_t launches;
+  float total_ms;
+} hb_kernel_stat;
+HB_API int hb_profile_enable(hb_ctx* ctx, int on);
+HB_API int hb_profile_read(hb_ctx* ctx, hb_kernel_stat* out, int max_out, int* n_out);
 
 /* ---- formats ---- */
 /* hive::glm::ExpertRecLayout::make — engine/include/hive/glm/glm_moe.h:15-21 */
