@@ -184,26 +184,27 @@ struct StreamCfg {
   static constexpr int RB = K / 2, RS = K / 16;            // bytes of one row: weights, scales
   static constexpr int TR = (DOWN ? 16 : 8) * WM;          // matrix rows per item (gate/up: TR gate rows + TR up rows)
   static constexpr int MAT = TR * (RB + RS);               // bytes of one matrix part of a stage
-  static constexpr int UP_OFF = MAT + 64;                  // the up part sits 64 B off a 128-B boundary: no bank overlap with gate
+  static constexpr int UP_OFF = MAT + 16;                  // the up part sits 16 B off a 128-B boundary: its rows use other banks than gate's
   static constexpr int STAGE = DOWN ? MAT : ((UP_OFF + MAT + 127) / 128 * 128);
   static constexpr int TX = DOWN ? MAT : 2 * MAT;          // bytes a full stage receives
-  static constexpr int RED = 2 * NW * 32 * 16;             // split-K exchange buffer, double buffered
-  static constexpr int HEAD = RED + 2 * kMaxStages * 8 + 64;
-  static size_t smem(int stages) { return (size_t)((HEAD + 127) / 128 * 128) + (size_t)stages * STAGE; }
+  static constexpr int SLOT = NW * 32 * 16;                // one split-K exchange slot: a float4 per consumer thread
+  static constexpr int BARS = 2 * kMaxStages * 8 + (kMaxStages + 1) * WM * 8;
+  __host__ __device__ static constexpr size_t head(int stages) { return (size_t)(((WK > 1 ? (stages + 1) * SLOT : 0) + BARS + 127) / 128 * 128); }
+  __host__ __device__ static constexpr size_t smem(int stages) { return head(stages) + (size_t)stages * STAGE; }
 };
 
-// Loads this warp's 256-column slice of ≤ 8 activation rows as the B fragments of 16 m16n8k16 tiles (f16).  Each row slice is
-// scaled by a power of two so its largest magnitude lands in [2^14, 2^15) before the bf16 → f16 conversion (no overflow, small
-// values keep their bits); inv[0], inv[1] return the inverse factors of the two tile columns this lane accumulates.
-__device__ __forceinline__ void load_b_frags(const __nv_bfloat16* src /* row of column g, or nullptr */, int t, uint32_t (&b)[32], float (&inv)[2]) {
+// Loads this warp's 256-column slice of ≤ 8 activation rows as the B fragments of 16 m16n8k16 tiles (f16): lane (g, t) holds
+// columns [64t, 64t+64) of activation row g of the group.  Each row slice is scaled by a power of two so its largest magnitude
+// lands in [2^14, 2^15) before the bf16 → f16 conversion (no overflow, small values keep their bits); inv[0], inv[1] return
+// the inverse factors of the two tile columns this lane accumulates.
+__device__ __forceinline__ void load_b_frags(const __nv_bfloat16* src /* slice of the row of column g, or nullptr */, int t, uint32_t (&b)[32],
+                                             float (&inv)[2]) {
   uint4 raw[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) raw[i] = make_uint4(0, 0, 0, 0);
   if (src) {
 #pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-      for (int v = 0; v < 4; ++v) raw[h * 4 + v] = __ldg(reinterpret_cast<const uint4*>(src + 32 * (t + 4 * h)) + v);
+    for (int v = 0; v < 8; ++v) raw[v] = __ldg(reinterpret_cast<const uint4*>(src + 64 * t) + v);
   }
   uint32_t am = 0;                                              // max |x| as bf16 bits (sign cleared): integer order = magnitude order
 #pragma unroll
@@ -233,53 +234,64 @@ __device__ __forceinline__ void load_b_frags(const __nv_bfloat16* src /* row of 
 }
 
 // One warp: 16 tile rows (this lane: rowA for the low half, rowB for the high half) × 256 columns against the B fragments.
-__device__ __forceinline__ void warp_slice_mma(const uint8_t* wa, const uint8_t* wb, const uint8_t* sa, const uint8_t* sb, int t,
+// wa / wb point at this lane's 32 weight bytes of the two rows (columns [64t, 64t+64) of the slice), sa / sb at its 4 scale bytes.
+// SWAP (down pass): lanes of odd g fetch their two 16-byte halves in the other order, so the two rows a quarter-warp reads
+// (one row pitch apart, a multiple of 128 B) fall on different banks.
+template <bool SWAP>
+__device__ __forceinline__ void warp_slice_mma(const uint8_t* wa, const uint8_t* wb, const uint8_t* sa, const uint8_t* sb, int g,
                                                const uint32_t (&b)[32], float (&acc)[4], uint64_t* empty_bar) {
-  uint4 qa[2], qb[2];
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    qa[h] = *reinterpret_cast<const uint4*>(wa + (t + 4 * h) * 16);
-    qb[h] = *reinterpret_cast<const uint4*>(wb + (t + 4 * h) * 16);
-  }
-  const uint4 sqa = *reinterpret_cast<const uint4*>(sa), sqb = *reinterpret_cast<const uint4*>(sb);
+  const int first = (SWAP && (g & 1)) ? 16 : 0;
+  uint4 qa0 = *reinterpret_cast<const uint4*>(wa + first), qa1 = *reinterpret_cast<const uint4*>(wa + (16 - first));
+  uint4 qb0 = *reinterpret_cast<const uint4*>(wb + first), qb1 = *reinterpret_cast<const uint4*>(wb + (16 - first));
+  const uint32_t s4a = *reinterpret_cast<const uint32_t*>(sa), s4b = *reinterpret_cast<const uint32_t*>(sb);
   // everything this warp needs from the stage is in registers: hand the stage back before the arithmetic
   __syncwarp();
   if ((threadIdx.x & 31) == 0) mbar_arrive(empty_bar);
+  if (SWAP && (g & 1)) { const uint4 ta = qa0; qa0 = qa1; qa1 = ta; const uint4 tb = qb0; qb0 = qb1; qb1 = tb; }
+  const uint32_t wqa[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
+  const uint32_t wqb[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
+  const uint32_t fa01 = cvt_e4m3x2_f16x2(s4a & 0xffffu), fa23 = cvt_e4m3x2_f16x2(s4a >> 16);
+  const uint32_t fb01 = cvt_e4m3x2_f16x2(s4b & 0xffffu), fb23 = cvt_e4m3x2_f16x2(s4b >> 16);
+  // each f16 block scale broadcast to both halves of a register
+  const uint32_t sca[4] = {__byte_perm(fa01, 0, 0x1010), __byte_perm(fa01, 0, 0x3232), __byte_perm(fa23, 0, 0x1010), __byte_perm(fa23, 0, 0x3232)};
+  const uint32_t scb[4] = {__byte_perm(fb01, 0, 0x1010), __byte_perm(fb01, 0, 0x3232), __byte_perm(fb23, 0, 0x1010), __byte_perm(fb23, 0, 0x3232)};
+  float c[4][4];                                        // four independent accumulator chains, summed at the end
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    // scale bytes 2c, 2c+1 of the slice's 16, c = t + 4h: half-word (t & 1) of word (t >> 1) + 2h
-    const uint32_t wsa = (t & 2) ? (h ? sqa.w : sqa.y) : (h ? sqa.z : sqa.x), wsb = (t & 2) ? (h ? sqb.w : sqb.y) : (h ? sqb.z : sqb.x);
-    const uint32_t fa = cvt_e4m3x2_f16x2((wsa >> (16 * (t & 1))) & 0xffffu), fb = cvt_e4m3x2_f16x2((wsb >> (16 * (t & 1))) & 0xffffu);
-    const uint32_t sa0 = __byte_perm(fa, 0, 0x1010), sa1 = __byte_perm(fa, 0, 0x3232);      // broadcast each f16 scale to both halves
-    const uint32_t sb0 = __byte_perm(fb, 0, 0x1010), sb1 = __byte_perm(fb, 0, 0x3232);
-    const uint32_t wqa[4] = {qa[h].x, qa[h].y, qa[h].z, qa[h].w}, wqb[4] = {qb[h].x, qb[h].y, qb[h].z, qb[h].w};
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {                       // word j = 8 columns = two tiles
-      uint32_t ha[4], hb_[4];
-      cvt_e2m1x8_f16x2(wqa[j], ha);
-      cvt_e2m1x8_f16x2(wqb[j], hb_);
-      const uint32_t sca = j < 2 ? sa0 : sa1, scb = j < 2 ? sb0 : sb1;
+    for (int j = 0; j < 4; ++j) c[i][j] = 0.f;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { ha[i] = hmul2_u32(ha[i], sca); hb_[i] = hmul2_u32(hb_[i], scb); }
-      const int m0 = h * 8 + j * 2;                     // tile index inside the slice
-      { const uint32_t afr[4] = {ha[0], hb_[0], ha[1], hb_[1]}; mma_f16_16816(acc, afr, b[m0 * 2], b[m0 * 2 + 1]); }
-      { const uint32_t afr[4] = {ha[2], hb_[2], ha[3], hb_[3]}; mma_f16_16816(acc, afr, b[m0 * 2 + 2], b[m0 * 2 + 3]); }
-    }
+  for (int j = 0; j < 8; ++j) {                         // word j = 8 columns = two tiles; its 16-column block is j >> 1
+    uint32_t ha[4], hb_[4];
+    cvt_e2m1x8_f16x2(wqa[j], ha);
+    cvt_e2m1x8_f16x2(wqb[j], hb_);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { ha[i] = hmul2_u32(ha[i], sca[j >> 1]); hb_[i] = hmul2_u32(hb_[i], scb[j >> 1]); }
+    { const uint32_t afr[4] = {ha[0], hb_[0], ha[1], hb_[1]}; mma_f16_16816(c[(2 * j) & 3], afr, b[4 * j], b[4 * j + 1]); }
+    { const uint32_t afr[4] = {ha[2], hb_[2], ha[3], hb_[3]}; mma_f16_16816(c[(2 * j + 1) & 3], afr, b[4 * j + 2], b[4 * j + 3]); }
   }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) acc[j] = (c[0][j] + c[1][j]) + (c[2][j] + c[3][j]);
 }
 
 template <int WK, int WM, bool DOWN>
 __global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK, WM, DOWN>::THREADS <= 512 ? 2 : 1) moe_stream_kernel(StreamArgs a) {
   using C = StreamCfg<WK, WM, DOWN>;
   extern __shared__ __align__(128) uint8_t smem[];
-  float4* red = reinterpret_cast<float4*>(smem);                                   // [2][NW][32]
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::RED);                     // [kMaxStages]
-  uint64_t* empty = full + kMaxStages;
-  uint8_t* ring = smem + (C::HEAD + 127) / 128 * 128;
+  const int S = a.stages, NSLOT = S + 1;
+  // split-K exchange: NSLOT slots of one float4 per consumer thread.  Slot reuse needs no CTA-wide barrier: a warp writes slot
+  // (n mod NSLOT) for its n-th item only after it got stage (n mod S) of that item, which the producer refilled only after every
+  // warp — the one that read the slot's previous contents included, in program order after that read — released the stage of
+  // item n - S; so NSLOT = S + 1 slots are never overwritten while still being read.
+  float4* red = reinterpret_cast<float4*>(smem);                                                // [NSLOT][NW][32]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (WK > 1 ? NSLOT * C::SLOT : 0));          // [kMaxStages]
+  uint64_t* empty = full + kMaxStages;                                                          // [kMaxStages]
+  uint64_t* redbar = empty + kMaxStages;                                                        // [NSLOT][WM]
+  uint8_t* ring = smem + C::head(S);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int S = a.stages;
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], C::NW); }
+    for (int s = 0; s < NSLOT * WM; ++s) mbar_init(&redbar[s], WK);
     mbar_fence_init();
   }
   __syncthreads();
@@ -290,21 +302,21 @@ __global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK
   const int N = DOWN ? a.H : a.I;
   const int tiles = N / C::TR;
   const long long total = (long long)n_groups * tiles;
-  const long long i_begin = total * blockIdx.x / gridDim.x, i_end = total * (blockIdx.x + 1) / gridDim.x;
+  const int i_begin = (int)(total * blockIdx.x / gridDim.x), i_end = (int)(total * (blockIdx.x + 1) / gridDim.x);
+  const int n_items = i_end - i_begin;
+  int gi = i_begin / tiles, tile = i_begin - gi * tiles;
   griddep_launch();
 
   if (warp == C::NW) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
-      long long it = 0;
-      bool ok = true;
-      for (long long item = i_begin; item < i_end && ok; ++item, ++it) {
-        const int s = (int)(it % S);
-        const uint32_t ph = (uint32_t)((it / S) & 1);
-        ok = mbar_wait(&empty[s], ph ^ 1u, a.err, 1u);
-        if (!ok) break;
-        const Group g = a.groups[item / tiles];
-        const int tile = (int)(item % tiles);
+      int s = 0, issued = 0;
+      uint32_t ph = 0;
+      Group g = {nullptr, 0, 0};
+      int cur = -1;
+      for (; issued < n_items; ++issued) {
+        if (!mbar_wait(&empty[s], ph ^ 1u, a.err, 1u)) break;
+        if (gi != cur) { g = a.groups[gi]; cur = gi; }
         uint8_t* st = ring + (size_t)s * C::STAGE;
         mbar_expect_tx(&full[s], C::TX);
         const size_t r0 = (size_t)tile * C::TR;
@@ -314,11 +326,11 @@ __global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK
           bulk_g2s(st + C::UP_OFF, g.rec + a.off_wb + r0 * C::RB, C::TR * C::RB, &full[s]);
           bulk_g2s(st + C::UP_OFF + C::TR * C::RB, g.rec + a.off_sb + r0 * C::RS, C::TR * C::RS, &full[s]);
         }
+        if (++tile == tiles) { tile = 0; ++gi; }
+        if (++s == S) { s = 0; ph ^= 1u; }
       }
       // copies still in flight land before the CTA leaves (immediate when the consumers took every stage)
-      const long long n_issued = it;
-      for (long long j = (n_issued > S ? n_issued - S : 0); j < n_issued; ++j)
-        mbar_wait(&full[j % S], (uint32_t)((j / S) & 1), a.err, 4u);
+      for (int j = issued > S ? issued - S : 0; j < issued; ++j) mbar_wait(&full[j % S], (uint32_t)((j / S) & 1), a.err, 4u);
     }
     return;
   }
@@ -330,18 +342,17 @@ __global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK
   int rowA, rowB, matoff = 0;
   if (DOWN) { rowA = 16 * mt + g; rowB = rowA + 8; }
   else { rowA = 8 * mt + (g >> 1); rowB = rowA + 4; matoff = (g & 1) ? C::UP_OFF : 0; }
-  const int wA = matoff + rowA * C::RB + ks * (kSlice / 2), wB = matoff + rowB * C::RB + ks * (kSlice / 2);
-  const int sA = matoff + C::TR * C::RB + rowA * C::RS + ks * (kSlice / 16), sB = matoff + C::TR * C::RB + rowB * C::RS + ks * (kSlice / 16);
+  const int wA = matoff + rowA * C::RB + ks * (kSlice / 2) + 32 * t, wB = matoff + rowB * C::RB + ks * (kSlice / 2) + 32 * t;
+  const int sA = matoff + C::TR * C::RB + rowA * C::RS + ks * (kSlice / 16) + 4 * t, sB = matoff + C::TR * C::RB + rowB * C::RS + ks * (kSlice / 16) + 4 * t;
 
   uint32_t bfr[32];
   float inv[2] = {1.f, 1.f};
   float gl[3] = {1.f, 1.f, 1.f};
-  long long cur_group = -1;
+  int cur_group = -1;
   Group grp = {nullptr, 0, 0};
-  long long it = 0;
-  for (long long item = i_begin; item < i_end; ++item, ++it) {
-    const long long gi = item / tiles;
-    const int tile = (int)(item % tiles);
+  int s = 0, slot = 0, epi = 0;
+  uint32_t ph = 0, rph = 0;
+  for (int it = 0; it < n_items; ++it) {
     if (gi != cur_group) {
       cur_group = gi;
       grp = a.groups[gi];
@@ -352,28 +363,32 @@ __global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK
       const float* gp = reinterpret_cast<const float*>(grp.rec + a.off_g);
       gl[0] = __ldg(gp); gl[1] = __ldg(gp + 1); gl[2] = __ldg(gp + 2);
     }
-    const int s = (int)(it % S);
-    const uint32_t ph = (uint32_t)((it / S) & 1);
     if (!mbar_wait(&full[s], ph, a.err, 2u)) break;
     const uint8_t* st = ring + (size_t)s * C::STAGE;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    warp_slice_mma(st + wA, st + wB, st + sA, st + sB, t, bfr, acc, &empty[s]);
+    float acc[4];
+    warp_slice_mma<DOWN>(st + wA, st + wB, st + sA, st + sB, g, bfr, acc, &empty[s]);
     acc[0] *= inv[0]; acc[1] *= inv[1]; acc[2] *= inv[0]; acc[3] *= inv[1];
-    float4* rb = red + (size_t)(it & 1) * C::NW * 32;
+    bool mine = true;
     if (WK > 1) {
-      rb[warp * 32 + lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-      named_bar_sync(1, C::NW * 32);
-    }
-    const int epi = (int)(it % WK);
-    if (ks == epi) {
-      if (WK > 1) {
-        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+      float4* rb = red + (size_t)slot * C::NW * 32;
+      mine = ks == epi;
+      if (!mine) {
+        rb[warp * 32 + lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&redbar[slot * WM + mt]);
+      } else {
+        if (lane == 0) mbar_arrive(&redbar[slot * WM + mt]);
+        if (!mbar_wait(&redbar[slot * WM + mt], rph, a.err, 8u)) break;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int k2 = 0; k2 < WK; ++k2) {                  // fixed order: deterministic
-          const float4 v = rb[(mt * WK + k2) * 32 + lane];
-          acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+        for (int k2 = 0; k2 < WK; ++k2) {                  // fixed order over the K slices: deterministic
+          const float4 v = k2 == ks ? make_float4(acc[0], acc[1], acc[2], acc[3]) : rb[(mt * WK + k2) * 32 + lane];
+          sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
         }
+        acc[0] = sum.x; acc[1] = sum.y; acc[2] = sum.z; acc[3] = sum.w;
       }
+    }
+    if (mine) {
       const int tok0 = 2 * t;
       if (DOWN) {
         const int n0 = tile * C::TR + 16 * mt + g;
@@ -399,6 +414,10 @@ __global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK
         }
       }
     }
+    if (++tile == tiles) { tile = 0; ++gi; }
+    if (++s == S) { s = 0; ph ^= 1u; }
+    if (++slot == NSLOT) { slot = 0; rph ^= 1u; }
+    if (++epi == WK) epi = 0;
   }
 }
 
