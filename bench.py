@@ -312,9 +312,12 @@ def run_ours(args):
         ids_h = ids.cpu().numpy()
         U = np.array([[len(np.unique(ids_h[s, li])) + 1 for li in range(L)] for s in range(NSETS)], np.float64)   # + shared
         if world > 1:
-            # records streamed by THIS rank: distinct local experts over the gathered batch + its shared copy
-            U = ep.local_records_touched(ids, NSETS, L)
-            t = torch.tensor([U.mean()], dtype=torch.float64, device=dev); dist.all_reduce(t); u_total = float(t.item())
+            # records streamed per layer, summed over ranks: each rank's distinct local experts over the gathered batch + its shared copy
+            ids_g = torch.empty((world,) + tuple(ids.shape), dtype=torch.int32, device=dev)
+            dist.all_gather_into_tensor(ids_g, ids.contiguous())
+            ids_g = ids_g.permute(1, 2, 0, 3, 4).reshape(NSETS * L, -1)
+            u_loc = ep.local_records_touched([ids_g[j] for j in range(ids_g.shape[0])])
+            t = torch.tensor([u_loc], dtype=torch.float64, device=dev); dist.all_reduce(t); u_total = float(t.item())
         else:
             u_total = float(U.mean())
         bytes_step = L * layer_algorithmic_bytes(H, I, Ex, K, B * world, u_total)

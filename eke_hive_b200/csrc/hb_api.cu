@@ -225,6 +225,19 @@ int hb_moe_decode_routed(hb_ctx* ctx, const int32_t* ids, const float* w, int M,
   return hbk_moe_decode_run(ctx, src, x, H, I, limit, red, ws, as_stream(stream));
 }
 
+int hb_moe_decode_routed_f32(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int K, const uint8_t* const* rec_tab, int li, int E,
+                             const void* x, int H, int I, float limit, float* out, void* ws, void* stream) {
+  HB_CTX(ctx);
+  if (M == 0) return HB_OK;
+  HB_PTR(ctx, ids); HB_PTR(ctx, w); HB_PTR(ctx, rec_tab); HB_PTR(ctx, x); HB_PTR(ctx, out);
+  HB_REQUIRE(ctx, M > 0 && K > 0 && E > 0 && E <= HB_MAX_EXPERTS && li >= 0, HB_ERR_INVALID, "moe_decode_routed_f32: M=%d K=%d E=%d li=%d", M, K, E, li);
+  int r = check_decode_shape(ctx, "moe_decode_routed_f32", M * K, H, I, x, ws);
+  if (r) return r;
+  hbk_pair_src src; src.ids = ids; src.w = w; src.M = M; src.K = K; src.tab = rec_tab; src.li = li; src.E = E;
+  hbk_reduce red; red.out_f32 = out;
+  return hbk_moe_decode_run(ctx, src, x, H, I, limit, red, ws, as_stream(stream));
+}
+
 int hb_moe_layer_decode(hb_ctx* ctx, const float* logits, int ld, int M, int E, int K, int renorm, int logits_bf16, const float* bias,
                         float sigmoid_scale, const uint8_t* const* rec_tab, int li, const uint8_t* shared_rec, int gate_col, const void* x,
                         int H, int I, float limit, int32_t* ids_out, float* w_out, void* out, void* ws, void* stream) {

@@ -187,6 +187,7 @@ struct StreamCfg {
   static constexpr int UP_OFF = MAT + 16;                  // the up part sits 16 B off a 128-B boundary: its rows use other banks than gate's
   static constexpr int STAGE = DOWN ? MAT : ((UP_OFF + MAT + 127) / 128 * 128);
   static constexpr int TX = DOWN ? MAT : 2 * MAT;          // bytes a full stage receives
+  static constexpr int CTAS_PER_SM = THREADS <= 320 ? 2 : 1;   // resident CTAs the register and shared-memory budgets are planned for
   static constexpr int SLOT = NW * 32 * 16;                // one split-K exchange slot: a float4 per consumer thread
   static constexpr int BARS = 2 * kMaxStages * 8 + (kMaxStages + 1) * WM * 8;
   __host__ __device__ static constexpr size_t head(int stages) { return (size_t)(((WK > 1 ? (stages + 1) * SLOT : 0) + BARS + 127) / 128 * 128); }
@@ -199,19 +200,18 @@ struct StreamCfg {
 // the inverse factors of the two tile columns this lane accumulates.
 __device__ __forceinline__ void load_b_frags(const __nv_bfloat16* src /* slice of the row of column g, or nullptr */, int t, uint32_t (&b)[32],
                                              float (&inv)[2]) {
-  uint4 raw[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) raw[i] = make_uint4(0, 0, 0, 0);
-  if (src) {
-#pragma unroll
-    for (int v = 0; v < 8; ++v) raw[v] = __ldg(reinterpret_cast<const uint4*>(src + 64 * t) + v);
-  }
+  // two passes over the lane's 128 bytes (the second hits L1/L2): max magnitude first, then scale + convert, so that at most
+  // the 32 result registers are live
+  const uint4* p = src ? reinterpret_cast<const uint4*>(src + 64 * t) : nullptr;
   uint32_t am = 0;                                              // max |x| as bf16 bits (sign cleared): integer order = magnitude order
+  if (p) {
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+    for (int i = 0; i < 8; ++i) {
+      const uint4 r = __ldg(p + i);
+      const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { am = max(am, w[j] & 0x7fffu); am = max(am, (w[j] >> 16) & 0x7fffu); }
+      for (int j = 0; j < 4; ++j) { am = max(am, w[j] & 0x7fffu); am = max(am, (w[j] >> 16) & 0x7fffu); }
+    }
   }
   am = max(am, __shfl_xor_sync(0xffffffffu, am, 1));
   am = max(am, __shfl_xor_sync(0xffffffffu, am, 2));
@@ -221,7 +221,8 @@ __device__ __forceinline__ void load_b_frags(const __nv_bfloat16* src /* slice o
   const float myinv = __int_as_float((uint32_t)(e - 14) << 23);                 // 2^((e - 127) - 14)
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+    const uint4 r = p ? __ldg(p + i) : make_uint4(0, 0, 0, 0);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float lo = __uint_as_float(w[j] << 16) * fac, hi = __uint_as_float(w[j] & 0xffff0000u) * fac;
@@ -235,47 +236,47 @@ __device__ __forceinline__ void load_b_frags(const __nv_bfloat16* src /* slice o
 
 // One warp: 16 tile rows (this lane: rowA for the low half, rowB for the high half) × 256 columns against the B fragments.
 // wa / wb point at this lane's 32 weight bytes of the two rows (columns [64t, 64t+64) of the slice), sa / sb at its 4 scale bytes.
-// SWAP (down pass): lanes of odd g fetch their two 16-byte halves in the other order, so the two rows a quarter-warp reads
-// (one row pitch apart, a multiple of 128 B) fall on different banks.
-template <bool SWAP>
-__device__ __forceinline__ void warp_slice_mma(const uint8_t* wa, const uint8_t* wb, const uint8_t* sa, const uint8_t* sb, int g,
+// The two 16-byte halves are fetched one after the other to keep few registers live; the stage is handed back to the producer
+// as soon as the second half is in registers.
+__device__ __forceinline__ void warp_slice_mma(const uint8_t* wa, const uint8_t* wb, const uint8_t* sa, const uint8_t* sb,
                                                const uint32_t (&b)[32], float (&acc)[4], uint64_t* empty_bar) {
-  const int first = (SWAP && (g & 1)) ? 16 : 0;
-  uint4 qa0 = *reinterpret_cast<const uint4*>(wa + first), qa1 = *reinterpret_cast<const uint4*>(wa + (16 - first));
-  uint4 qb0 = *reinterpret_cast<const uint4*>(wb + first), qb1 = *reinterpret_cast<const uint4*>(wb + (16 - first));
   const uint32_t s4a = *reinterpret_cast<const uint32_t*>(sa), s4b = *reinterpret_cast<const uint32_t*>(sb);
-  // everything this warp needs from the stage is in registers: hand the stage back before the arithmetic
-  __syncwarp();
-  if ((threadIdx.x & 31) == 0) mbar_arrive(empty_bar);
-  if (SWAP && (g & 1)) { const uint4 ta = qa0; qa0 = qa1; qa1 = ta; const uint4 tb = qb0; qb0 = qb1; qb1 = tb; }
-  const uint32_t wqa[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
-  const uint32_t wqb[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
-  const uint32_t fa01 = cvt_e4m3x2_f16x2(s4a & 0xffffu), fa23 = cvt_e4m3x2_f16x2(s4a >> 16);
-  const uint32_t fb01 = cvt_e4m3x2_f16x2(s4b & 0xffffu), fb23 = cvt_e4m3x2_f16x2(s4b >> 16);
-  // each f16 block scale broadcast to both halves of a register
-  const uint32_t sca[4] = {__byte_perm(fa01, 0, 0x1010), __byte_perm(fa01, 0, 0x3232), __byte_perm(fa23, 0, 0x1010), __byte_perm(fa23, 0, 0x3232)};
-  const uint32_t scb[4] = {__byte_perm(fb01, 0, 0x1010), __byte_perm(fb01, 0, 0x3232), __byte_perm(fb23, 0, 0x1010), __byte_perm(fb23, 0, 0x3232)};
-  float c[4][4];                                        // four independent accumulator chains, summed at the end
+  // four e4m3 block scales per row → f16 (exact)
+  const uint32_t fa[2] = {cvt_e4m3x2_f16x2(s4a & 0xffffu), cvt_e4m3x2_f16x2(s4a >> 16)};
+  const uint32_t fb[2] = {cvt_e4m3x2_f16x2(s4b & 0xffffu), cvt_e4m3x2_f16x2(s4b >> 16)};
+  float c[2][4];                                        // two independent accumulator chains, summed at the end
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < 2; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) c[i][j] = 0.f;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {                         // word j = 8 columns = two tiles; its 16-column block is j >> 1
-    uint32_t ha[4], hb_[4];
-    cvt_e2m1x8_f16x2(wqa[j], ha);
-    cvt_e2m1x8_f16x2(wqb[j], hb_);
+  for (int h = 0; h < 2; ++h) {
+    const uint4 qa = *reinterpret_cast<const uint4*>(wa + 16 * h), qb = *reinterpret_cast<const uint4*>(wb + 16 * h);
+    if (h == 1) {                                       // everything this warp needs from the stage is in registers
+      __syncwarp();
+      if ((threadIdx.x & 31) == 0) mbar_arrive(empty_bar);
+    }
+    const uint32_t wqa[4] = {qa.x, qa.y, qa.z, qa.w}, wqb[4] = {qb.x, qb.y, qb.z, qb.w};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { ha[i] = hmul2_u32(ha[i], sca[j >> 1]); hb_[i] = hmul2_u32(hb_[i], scb[j >> 1]); }
-    { const uint32_t afr[4] = {ha[0], hb_[0], ha[1], hb_[1]}; mma_f16_16816(c[(2 * j) & 3], afr, b[4 * j], b[4 * j + 1]); }
-    { const uint32_t afr[4] = {ha[2], hb_[2], ha[3], hb_[3]}; mma_f16_16816(c[(2 * j + 1) & 3], afr, b[4 * j + 2], b[4 * j + 3]); }
+    for (int jj = 0; jj < 4; ++jj) {                    // word j = 8 columns = two tiles; its 16-column block is j >> 1
+      const int j = 4 * h + jj;
+      // the block's f16 scale broadcast to both halves of a register
+      const uint32_t sca = __byte_perm(fa[h], 0, (jj >> 1) ? 0x3232 : 0x1010), scb = __byte_perm(fb[h], 0, (jj >> 1) ? 0x3232 : 0x1010);
+      uint32_t ha[4], hb_[4];
+      cvt_e2m1x8_f16x2(wqa[jj], ha);
+      cvt_e2m1x8_f16x2(wqb[jj], hb_);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { ha[i] = hmul2_u32(ha[i], sca); hb_[i] = hmul2_u32(hb_[i], scb); }
+      { const uint32_t afr[4] = {ha[0], hb_[0], ha[1], hb_[1]}; mma_f16_16816(c[0], afr, b[4 * j], b[4 * j + 1]); }
+      { const uint32_t afr[4] = {ha[2], hb_[2], ha[3], hb_[3]}; mma_f16_16816(c[1], afr, b[4 * j + 2], b[4 * j + 3]); }
+    }
   }
 #pragma unroll
-  for (int j = 0; j < 4; ++j) acc[j] = (c[0][j] + c[1][j]) + (c[2][j] + c[3][j]);
+  for (int j = 0; j < 4; ++j) acc[j] = c[0][j] + c[1][j];
 }
 
 template <int WK, int WM, bool DOWN>
-__global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK, WM, DOWN>::THREADS <= 512 ? 2 : 1) moe_stream_kernel(StreamArgs a) {
+__global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK, WM, DOWN>::CTAS_PER_SM) moe_stream_kernel(StreamArgs a) {
   using C = StreamCfg<WK, WM, DOWN>;
   extern __shared__ __align__(128) uint8_t smem[];
   const int S = a.stages, NSLOT = S + 1;
@@ -366,7 +367,7 @@ __global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK
     if (!mbar_wait(&full[s], ph, a.err, 2u)) break;
     const uint8_t* st = ring + (size_t)s * C::STAGE;
     float acc[4];
-    warp_slice_mma<DOWN>(st + wA, st + wB, st + sA, st + sB, g, bfr, acc, &empty[s]);
+    warp_slice_mma(st + wA, st + wB, st + sA, st + sB, bfr, acc, &empty[s]);
     acc[0] *= inv[0]; acc[1] *= inv[1]; acc[2] *= inv[0]; acc[3] *= inv[1];
     bool mine = true;
     if (WK > 1) {
@@ -573,7 +574,7 @@ bool pick_kernel(int K, StreamKernel* out) {
 void plan_stream(const hb_ctx* ctx, const StreamKernel& k, int* stages, int* ctas_per_sm) {
   const int budget = ctx->smem_optin;                       // per block opt-in limit (227 KB on sm_100)
   const int per_sm = 228 * 1024;
-  int cps = (k.threads <= 512) ? 2 : 1;
+  int cps = (k.threads <= 320) ? 2 : 1;
   for (;; --cps) {
     const int avail = (cps == 1 ? budget : per_sm / cps - 1024 - 1024);
     int s = kMaxStages;

@@ -15,7 +15,7 @@ from . import _lib
 from ._lib import Config, HbError, MoePair, PfCombine, RecLayout
 
 __all__ = ["Context", "context", "ExpertRecLayout", "nvfp4_dequant", "nvfp4_gemv", "nvfp4_quantize", "a4_quant", "router_softmax_topk",
-           "router_topk", "build_moe_pairs", "moe_combine", "moe_decode_ws_bytes", "moe_decode", "fn_moe_decode_routed", "moe_layer_decode",
+           "router_topk", "build_moe_pairs", "moe_combine", "moe_decode_ws_bytes", "moe_decode", "fn_moe_decode_routed", "moe_decode_routed_f32", "moe_layer_decode",
            "moe_decode_supported", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
 
 
@@ -248,6 +248,16 @@ def fn_moe_decode_routed(ids, w, rec_tab, li: int, E: int, x, H: int, I: int, sh
     ws = _ws(M * K, H, I, x.device, ws)
     cmb = PfCombine(_p(shared), _p(lg), 0 if lg is None else lg.stride(0), col, _p(out))
     ctx.check(_L().hb_moe_decode_routed(ctx.handle, _p(ids), _p(w), M, K, _p(rec_tab), li, E, _p(x), H, I, limit, C.byref(cmb), _p(ws), _stream()))
+    return out
+
+
+def moe_decode_routed_f32(ids, w, rec_tab, li: int, E: int, x, H: int, I: int, out=None, limit: float = 0.0, ws=None, ctx: Context | None = None):
+    """Routed sum alone: out fp32 [M, H] = Σ_k w·expert (overwritten); NULL table entries and invalid ids contribute nothing."""
+    ctx = ctx or context()
+    M, K = ids.shape
+    out = torch.empty((M, H), dtype=torch.float32, device=x.device) if out is None else out
+    ws = _ws(M * K, H, I, x.device, ws)
+    ctx.check(_L().hb_moe_decode_routed_f32(ctx.handle, _p(ids), _p(w), M, K, _p(rec_tab), li, E, _p(x), H, I, limit, _p(out), _p(ws), _stream()))
     return out
 
 

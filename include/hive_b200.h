@@ -144,6 +144,11 @@ HB_API int hb_moe_decode(hb_ctx* ctx, const hb_moe_pair* pairs, int n_pairs, con
  * Records come from rec_tab[li·E + id]; ids outside [0,E) and NULL records contribute nothing.  cmb->lg NULL = no gate. */
 HB_API int hb_moe_decode_routed(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int K, const uint8_t* const* rec_tab, int li, int E,
                                 const void* x_bf16, int H, int I, float limit, const hb_pf_combine* cmb, void* ws, void* stream);
+/* The routed sum alone, fp32, overwritten: out[m] = Σ_k w[m,k]·expert_ids[m,k](x[m]) in k order — the output contract of
+ * hive::qwen::fn_moe_prefill without its combine (engine/include/hive/qwen/fn_moe.h:46-61) on the decode kernels.  Used by the
+ * expert-parallel layer, where rec_tab holds NULL for experts that live on other GPUs (those pairs contribute nothing). */
+HB_API int hb_moe_decode_routed_f32(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int K, const uint8_t* const* rec_tab, int li, int E,
+                                    const void* x_bf16, int H, int I, float limit, float* out, void* ws, void* stream);
 /* A whole decode MoE layer in one call: router (softmax when bias == NULL and sigmoid_scale == 0, else sigmoid+bias) → routed
  * experts → the always-on shared expert given as one more NVFP4 record (weight 1, every row; NULL = none) → combine.
  * Composition of the operators above in the order of engine/src/qwen/qwen_engine.cpp:818-878; ids_out / w_out [M,K] receive
