@@ -112,7 +112,7 @@ int hb_check_device(hb_ctx* ctx, void* stream) {
   HB_CUDA(ctx, cudaStreamSynchronize(as_stream(stream)));
   if (v == 0) return HB_OK;
   HB_CUDA(ctx, cudaMemsetAsync(ctx->dev_err, 0, 4, as_stream(stream)));
-  return hb_fail(ctx, HB_ERR_DEVICE_FLAG, "device error word 0x%x (1 = producer wait, 2 = consumer wait, 4 = drain, 8 = split-K exchange wait)", v);
+  return hb_fail(ctx, HB_ERR_DEVICE_FLAG, "device error word 0x%x (1 = producer wait, 2 = consumer wait, 4 = drain, 8 = epilogue wait, 16 = exchange slot wait)", v);
 }
 
 int hb_rec_layout_make(int H, int I, hb_rec_layout* L) {

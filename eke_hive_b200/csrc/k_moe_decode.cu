@@ -12,45 +12,9 @@
 // HBM traffic per layer is the records touched plus O(pairs·(H+I)) bytes of activations; weights are read once per group.
 // Shapes the streaming path takes: H, I multiples of 256, at most 4096; anything else (H, I multiples of 32) runs on the
 // generic CUDA-core kernels at the end of this file.
-#include "hb_common.cuh"
-#include "hb_kernels.h"
+#include "moe_stream.cuh"
 
 namespace hb {
-
-constexpr int kGroupRows = 8;         // activation rows per group = columns of one m16n8k16 tile
-constexpr int kSlice = 256;           // K elements per consumer warp
-constexpr int kMaxStages = 8;
-constexpr int kGroupThreads = 1024;
-
-struct Group { const uint8_t* rec; int start; int n; };
-static_assert(sizeof(Group) == 16, "Group layout");
-
-struct DecodeWs {
-  int* hdr;               // [0] number of groups, [1] number of valid pairs
-  Group* groups;          // [n_pairs]
-  int* s_row;             // [n_pairs] activation row of each sorted position
-  int* pos_of;            // [n_pairs] sorted position of each original pair, -1 = skipped (invalid id / null record)
-  int* prow;              // [n_pairs] activation row of each original pair
-  float* pw;              // [n_pairs] routing weight of each original pair
-  __nv_bfloat16* y;       // [n_pairs, I]
-  __nv_bfloat16* part;    // [n_pairs, H]
-};
-
-__host__ __device__ inline size_t al256(size_t b) { return (b + 255) / 256 * 256; }
-
-static DecodeWs carve(void* ws, int n, int H, int I) {
-  uint8_t* p = reinterpret_cast<uint8_t*>(ws);
-  DecodeWs w;
-  w.hdr = reinterpret_cast<int*>(p); p += 256;
-  w.groups = reinterpret_cast<Group*>(p); p += al256((size_t)n * sizeof(Group));
-  w.s_row = reinterpret_cast<int*>(p); p += al256((size_t)n * 4);
-  w.pos_of = reinterpret_cast<int*>(p); p += al256((size_t)n * 4);
-  w.prow = reinterpret_cast<int*>(p); p += al256((size_t)n * 4);
-  w.pw = reinterpret_cast<float*>(p); p += al256((size_t)n * 4);
-  w.y = reinterpret_cast<__nv_bfloat16*>(p); p += al256((size_t)n * I * 2);
-  w.part = reinterpret_cast<__nv_bfloat16*>(p);
-  return w;
-}
 
 // ================================================================================================ grouping
 struct GroupArgs {
@@ -166,133 +130,25 @@ static size_t group_smem(bool routed, int P, int E) {
 }
 
 // ================================================================================================ streaming kernels
-struct StreamArgs {
-  const int* hdr; const Group* groups; const int* s_row;
-  const __nv_bfloat16* act; int act_ld;        // gate/up: x rows (indexed through s_row); down: y (indexed by sorted position)
-  __nv_bfloat16* outp;                         // gate/up: y [pos, I]; down: part [pos, H]
-  int H, I; float limit;
-  uint32_t off_wa, off_sa, off_wb, off_sb, off_g;   // record offsets: gate/up = w1,s1,w3,s3 ; down = w2,s2 (wb/sb unused)
-  int stages;
-  uint32_t* err;
-};
-
-template <int WK, int WM, bool DOWN>
-struct StreamCfg {
-  static constexpr int NW = WK * WM;                       // consumer warps
-  static constexpr int THREADS = (NW + 1) * 32;            // + one producer warp
-  static constexpr int K = WK * kSlice;
-  static constexpr int RB = K / 2, RS = K / 16;            // bytes of one row: weights, scales
-  static constexpr int TR = (DOWN ? 16 : 8) * WM;          // matrix rows per item (gate/up: TR gate rows + TR up rows)
-  static constexpr int MAT = TR * (RB + RS);               // bytes of one matrix part of a stage
-  static constexpr int UP_OFF = MAT + 16;                  // the up part sits 16 B off a 128-B boundary: its rows use other banks than gate's
-  static constexpr int STAGE = DOWN ? MAT : ((UP_OFF + MAT + 127) / 128 * 128);
-  static constexpr int TX = DOWN ? MAT : 2 * MAT;          // bytes a full stage receives
-  static constexpr int CTAS_PER_SM = THREADS <= 320 ? 2 : 1;   // resident CTAs the register and shared-memory budgets are planned for
-  static constexpr int SLOT = NW * 32 * 16;                // one split-K exchange slot: a float4 per consumer thread
-  static constexpr int BARS = 2 * kMaxStages * 8 + (kMaxStages + 1) * WM * 8;
-  __host__ __device__ static constexpr size_t head(int stages) { return (size_t)(((WK > 1 ? (stages + 1) * SLOT : 0) + BARS + 127) / 128 * 128); }
-  __host__ __device__ static constexpr size_t smem(int stages) { return head(stages) + (size_t)stages * STAGE; }
-};
-
-// Loads this warp's 256-column slice of ≤ 8 activation rows as the B fragments of 16 m16n8k16 tiles (f16): lane (g, t) holds
-// columns [64t, 64t+64) of activation row g of the group.  Each row slice is scaled by a power of two so its largest magnitude
-// lands in [2^14, 2^15) before the bf16 → f16 conversion (no overflow, small values keep their bits); inv[0], inv[1] return
-// the inverse factors of the two tile columns this lane accumulates.
-__device__ __forceinline__ void load_b_frags(const __nv_bfloat16* src /* slice of the row of column g, or nullptr */, int t, uint32_t (&b)[32],
-                                             float (&inv)[2]) {
-  // two passes over the lane's 128 bytes (the second hits L1/L2): max magnitude first, then scale + convert, so that at most
-  // the 32 result registers are live
-  const uint4* p = src ? reinterpret_cast<const uint4*>(src + 64 * t) : nullptr;
-  uint32_t am = 0;                                              // max |x| as bf16 bits (sign cleared): integer order = magnitude order
-  if (p) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint4 r = __ldg(p + i);
-      const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) { am = max(am, w[j] & 0x7fffu); am = max(am, (w[j] >> 16) & 0x7fffu); }
-    }
-  }
-  am = max(am, __shfl_xor_sync(0xffffffffu, am, 1));
-  am = max(am, __shfl_xor_sync(0xffffffffu, am, 2));
-  int e = (int)(am >> 7);                                       // biased exponent of the largest magnitude
-  e = min(max(e, 27), 254);                                     // tiny rows: keep the factor finite
-  const float fac = __int_as_float((uint32_t)(127 + 14 + 127 - e) << 23);       // 2^(14 - (e - 127))
-  const float myinv = __int_as_float((uint32_t)(e - 14) << 23);                 // 2^((e - 127) - 14)
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const uint4 r = p ? __ldg(p + i) : make_uint4(0, 0, 0, 0);
-    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float lo = __uint_as_float(w[j] << 16) * fac, hi = __uint_as_float(w[j] & 0xffff0000u) * fac;
-      const __half2 hh = __floats2half2_rn(lo, hi);
-      b[i * 4 + j] = *reinterpret_cast<const uint32_t*>(&hh);
-    }
-  }
-  inv[0] = __shfl_sync(0xffffffffu, myinv, (2 * t) * 4);
-  inv[1] = __shfl_sync(0xffffffffu, myinv, (2 * t + 1) * 4);
-}
-
-// One warp: 16 tile rows (this lane: rowA for the low half, rowB for the high half) × 256 columns against the B fragments.
-// wa / wb point at this lane's 32 weight bytes of the two rows (columns [64t, 64t+64) of the slice), sa / sb at its 4 scale bytes.
-// The two 16-byte halves are fetched one after the other to keep few registers live; the stage is handed back to the producer
-// as soon as the second half is in registers.
-__device__ __forceinline__ void warp_slice_mma(const uint8_t* wa, const uint8_t* wb, const uint8_t* sa, const uint8_t* sb,
-                                               const uint32_t (&b)[32], float (&acc)[4], uint64_t* empty_bar) {
-  const uint32_t s4a = *reinterpret_cast<const uint32_t*>(sa), s4b = *reinterpret_cast<const uint32_t*>(sb);
-  // four e4m3 block scales per row → f16 (exact)
-  const uint32_t fa[2] = {cvt_e4m3x2_f16x2(s4a & 0xffffu), cvt_e4m3x2_f16x2(s4a >> 16)};
-  const uint32_t fb[2] = {cvt_e4m3x2_f16x2(s4b & 0xffffu), cvt_e4m3x2_f16x2(s4b >> 16)};
-  float c[2][4];                                        // two independent accumulator chains, summed at the end
-#pragma unroll
-  for (int i = 0; i < 2; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) c[i][j] = 0.f;
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const uint4 qa = *reinterpret_cast<const uint4*>(wa + 16 * h), qb = *reinterpret_cast<const uint4*>(wb + 16 * h);
-    if (h == 1) {                                       // everything this warp needs from the stage is in registers
-      __syncwarp();
-      if ((threadIdx.x & 31) == 0) mbar_arrive(empty_bar);
-    }
-    const uint32_t wqa[4] = {qa.x, qa.y, qa.z, qa.w}, wqb[4] = {qb.x, qb.y, qb.z, qb.w};
-#pragma unroll
-    for (int jj = 0; jj < 4; ++jj) {                    // word j = 8 columns = two tiles; its 16-column block is j >> 1
-      const int j = 4 * h + jj;
-      // the block's f16 scale broadcast to both halves of a register
-      const uint32_t sca = __byte_perm(fa[h], 0, (jj >> 1) ? 0x3232 : 0x1010), scb = __byte_perm(fb[h], 0, (jj >> 1) ? 0x3232 : 0x1010);
-      uint32_t ha[4], hb_[4];
-      cvt_e2m1x8_f16x2(wqa[jj], ha);
-      cvt_e2m1x8_f16x2(wqb[jj], hb_);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) { ha[i] = hmul2_u32(ha[i], sca); hb_[i] = hmul2_u32(hb_[i], scb); }
-      { const uint32_t afr[4] = {ha[0], hb_[0], ha[1], hb_[1]}; mma_f16_16816(c[0], afr, b[4 * j], b[4 * j + 1]); }
-      { const uint32_t afr[4] = {ha[2], hb_[2], ha[3], hb_[3]}; mma_f16_16816(c[1], afr, b[4 * j + 2], b[4 * j + 3]); }
-    }
-  }
-#pragma unroll
-  for (int j = 0; j < 4; ++j) acc[j] = c[0][j] + c[1][j];
-}
-
 template <int WK, int WM, bool DOWN>
 __global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK, WM, DOWN>::CTAS_PER_SM) moe_stream_kernel(StreamArgs a) {
   using C = StreamCfg<WK, WM, DOWN>;
   extern __shared__ __align__(128) uint8_t smem[];
   const int S = a.stages, NSLOT = S + 1;
-  // split-K exchange: NSLOT slots of one float4 per consumer thread.  Slot reuse needs no CTA-wide barrier: a warp writes slot
-  // (n mod NSLOT) for its n-th item only after it got stage (n mod S) of that item, which the producer refilled only after every
-  // warp — the one that read the slot's previous contents included, in program order after that read — released the stage of
-  // item n - S; so NSLOT = S + 1 slots are never overwritten while still being read.
+  // split-K exchange: NSLOT slots of one float4 per consumer thread.  Consumer warps drop their partial sums into the item's slot
+  // and go on to the next item; a dedicated epilogue warp waits for the slot (redbar), adds the K slices in fixed order, applies
+  // the epilogue and hands the slot back (redfree).  No consumer ever waits for another consumer.
   float4* red = reinterpret_cast<float4*>(smem);                                                // [NSLOT][NW][32]
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + (WK > 1 ? NSLOT * C::SLOT : 0));          // [kMaxStages]
   uint64_t* empty = full + kMaxStages;                                                          // [kMaxStages]
   uint64_t* redbar = empty + kMaxStages;                                                        // [NSLOT][WM]
+  uint64_t* redfree = redbar + (kMaxStages + 1) * WM;                                           // [NSLOT]
   uint8_t* ring = smem + C::head(S);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], C::NW); }
     for (int s = 0; s < NSLOT * WM; ++s) mbar_init(&redbar[s], WK);
+    for (int s = 0; s < NSLOT; ++s) mbar_init(&redfree[s], 1);
     mbar_fence_init();
   }
   __syncthreads();
@@ -336,10 +192,75 @@ __global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK
     return;
   }
 
+  const int g = lane >> 2, t = lane & 3;
+  const int tok0 = 2 * t;
+  // epilogue of one 16-row tile held in fragment layout: acc[c] = (row g + 8·(c>>1), activation row tok0 + (c&1))
+  auto epilogue = [&](const float (&acc)[4], const Group& grp, const float (&gl)[3], int mt, int tile_) {
+    if (DOWN) {
+      const int n0 = tile_ * C::TR + 16 * mt + g;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int tok = tok0 + (c & 1), n = n0 + (c >> 1) * 8;
+        if (tok < grp.n) a.outp[(size_t)(grp.start + tok) * a.H + n] = __float2bfloat16(acc[c] * gl[2]);
+      }
+    } else {
+      float oth[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) oth[c] = __shfl_xor_sync(0xffffffffu, acc[c], 4);
+      const bool odd = g & 1;
+      const int i = tile_ * C::TR + 8 * mt + (g >> 1) + (odd ? 4 : 0);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float gv = odd ? oth[2 + c] : acc[c], uv = odd ? acc[2 + c] : oth[c];
+        gv = bf16r(gv * gl[0]); uv = bf16r(uv * gl[1]);
+        if (a.limit > 0.f) { uv = fminf(fmaxf(uv, -a.limit), a.limit); gv = fminf(gv, a.limit); }
+        const float yv = gv / (1.f + __expf(-gv)) * uv;
+        const int tok = tok0 + c;
+        if (tok < grp.n) a.outp[(size_t)(grp.start + tok) * a.I + i] = __float2bfloat16(yv);
+      }
+    }
+  };
+
+  if (warp == C::NW + 1) {
+    // ---------------------------------------------------------------- epilogue warp (split-K kernels only)
+    if (WK == 1) return;
+    int cur_group = -1, slot = 0;
+    uint32_t rph = 0;
+    Group grp = {nullptr, 0, 0};
+    float gl[3] = {1.f, 1.f, 1.f};
+    for (int it = 0; it < n_items; ++it) {
+      if (gi != cur_group) {
+        cur_group = gi;
+        grp = a.groups[gi];
+        const float* gp = reinterpret_cast<const float*>(grp.rec + a.off_g);
+        gl[0] = __ldg(gp); gl[1] = __ldg(gp + 1); gl[2] = __ldg(gp + 2);
+      }
+      const float4* rb = red + (size_t)slot * C::NW * 32;
+      bool ok = true;
+#pragma unroll
+      for (int mt = 0; mt < WM; ++mt) {
+        ok = mbar_wait(&redbar[slot * WM + mt], rph, a.err, 8u);
+        if (!ok) break;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int k2 = 0; k2 < WK; ++k2) {                  // fixed order over the K slices: deterministic
+          const float4 v = rb[(mt * WK + k2) * 32 + lane];
+          acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+        }
+        epilogue(acc, grp, gl, mt, tile);
+      }
+      if (!ok) break;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&redfree[slot]);
+      if (++tile == tiles) { tile = 0; ++gi; }
+      if (++slot == NSLOT) { slot = 0; rph ^= 1u; }
+    }
+    return;
+  }
+
   // ------------------------------------------------------------------ consumers
   if (DOWN) griddep_wait();
   const int mt = warp / WK, ks = warp % WK;
-  const int g = lane >> 2, t = lane & 3;
   int rowA, rowB, matoff = 0;
   if (DOWN) { rowA = 16 * mt + g; rowB = rowA + 8; }
   else { rowA = 8 * mt + (g >> 1); rowB = rowA + 4; matoff = (g & 1) ? C::UP_OFF : 0; }
@@ -351,7 +272,7 @@ __global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK
   float gl[3] = {1.f, 1.f, 1.f};
   int cur_group = -1;
   Group grp = {nullptr, 0, 0};
-  int s = 0, slot = 0, epi = 0;
+  int s = 0, slot = 0;
   uint32_t ph = 0, rph = 0;
   for (int it = 0; it < n_items; ++it) {
     if (gi != cur_group) {
@@ -361,64 +282,27 @@ __global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK
       if (g < grp.n) src = DOWN ? a.act + (size_t)(grp.start + g) * a.act_ld + ks * kSlice
                                 : a.act + (size_t)a.s_row[grp.start + g] * a.act_ld + ks * kSlice;
       load_b_frags(src, t, bfr, inv);
-      const float* gp = reinterpret_cast<const float*>(grp.rec + a.off_g);
-      gl[0] = __ldg(gp); gl[1] = __ldg(gp + 1); gl[2] = __ldg(gp + 2);
+      if (WK == 1) {
+        const float* gp = reinterpret_cast<const float*>(grp.rec + a.off_g);
+        gl[0] = __ldg(gp); gl[1] = __ldg(gp + 1); gl[2] = __ldg(gp + 2);
+      }
     }
     if (!mbar_wait(&full[s], ph, a.err, 2u)) break;
     const uint8_t* st = ring + (size_t)s * C::STAGE;
     float acc[4];
     warp_slice_mma(st + wA, st + wB, st + sA, st + sB, bfr, acc, &empty[s]);
     acc[0] *= inv[0]; acc[1] *= inv[1]; acc[2] *= inv[0]; acc[3] *= inv[1];
-    bool mine = true;
     if (WK > 1) {
-      float4* rb = red + (size_t)slot * C::NW * 32;
-      mine = ks == epi;
-      if (!mine) {
-        rb[warp * 32 + lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&redbar[slot * WM + mt]);
-      } else {
-        if (lane == 0) mbar_arrive(&redbar[slot * WM + mt]);
-        if (!mbar_wait(&redbar[slot * WM + mt], rph, a.err, 8u)) break;
-        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int k2 = 0; k2 < WK; ++k2) {                  // fixed order over the K slices: deterministic
-          const float4 v = k2 == ks ? make_float4(acc[0], acc[1], acc[2], acc[3]) : rb[(mt * WK + k2) * 32 + lane];
-          sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-        }
-        acc[0] = sum.x; acc[1] = sum.y; acc[2] = sum.z; acc[3] = sum.w;
-      }
-    }
-    if (mine) {
-      const int tok0 = 2 * t;
-      if (DOWN) {
-        const int n0 = tile * C::TR + 16 * mt + g;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int tok = tok0 + (c & 1), n = n0 + (c >> 1) * 8;
-          if (tok < grp.n) a.outp[(size_t)(grp.start + tok) * a.H + n] = __float2bfloat16(acc[c] * gl[2]);
-        }
-      } else {
-        float oth[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) oth[c] = __shfl_xor_sync(0xffffffffu, acc[c], 4);
-        const bool odd = g & 1;
-        const int i = tile * C::TR + 8 * mt + (g >> 1) + (odd ? 4 : 0);
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          float gv = odd ? oth[2 + c] : acc[c], uv = odd ? acc[2 + c] : oth[c];
-          gv = bf16r(gv * gl[0]); uv = bf16r(uv * gl[1]);
-          if (a.limit > 0.f) { uv = fminf(fmaxf(uv, -a.limit), a.limit); gv = fminf(gv, a.limit); }
-          const float yv = gv / (1.f + __expf(-gv)) * uv;
-          const int tok = tok0 + c;
-          if (tok < grp.n) a.outp[(size_t)(grp.start + tok) * a.I + i] = __float2bfloat16(yv);
-        }
-      }
+      if (!mbar_wait(&redfree[slot], rph ^ 1u, a.err, 16u)) break;      // the slot's previous contents have been read
+      red[(size_t)slot * C::NW * 32 + warp * 32 + lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&redbar[slot * WM + mt]);
+    } else {
+      epilogue(acc, grp, gl, mt, tile);
     }
     if (++tile == tiles) { tile = 0; ++gi; }
     if (++s == S) { s = 0; ph ^= 1u; }
     if (++slot == NSLOT) { slot = 0; rph ^= 1u; }
-    if (++epi == WK) epi = 0;
   }
 }
 
