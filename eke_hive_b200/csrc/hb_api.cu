@@ -112,7 +112,7 @@ int hb_check_device(hb_ctx* ctx, void* stream) {
   HB_CUDA(ctx, cudaStreamSynchronize(as_stream(stream)));
   if (v == 0) return HB_OK;
   HB_CUDA(ctx, cudaMemsetAsync(ctx->dev_err, 0, 4, as_stream(stream)));
-  return hb_fail(ctx, HB_ERR_DEVICE_FLAG, "device error word 0x%x (1 = producer wait, 2 = consumer wait, 4 = drain, 8 = epilogue wait, 16 = exchange slot wait)", v);
+  return hb_fail(ctx, HB_ERR_DEVICE_FLAG, "device error word 0x%x (1 = producer wait, 2 = consumer wait, 4 = drain, 8 = epilogue wait, 16 = exchange slot wait, 32 = gate/up counter wait, 64 = down counter wait)", v);
 }
 
 int hb_rec_layout_make(int H, int I, hb_rec_layout* L) {
@@ -250,14 +250,11 @@ int hb_moe_layer_decode(hb_ctx* ctx, const float* logits, int ld, int M, int E, 
   int r = check_decode_shape(ctx, "moe_layer_decode", M * (K + 1), H, I, x, ws);
   if (r) return r;
   const bool sigmoid = bias != nullptr || sigmoid_scale != 0.f;
-  if (sigmoid) {
-    HB_REQUIRE(ctx, ld == E, HB_ERR_INVALID, "moe_layer_decode: the sigmoid router takes dense logits rows (ld == E)");
-    r = hbk_route_sigmoid_topk(ctx, logits, bias, M, E, K, sigmoid_scale != 0.f ? sigmoid_scale : 1.f, ids_out, w_out, as_stream(stream), pdl_on(ctx));
-  } else {
-    r = hbk_route_softmax_topk(ctx, logits, ld, M, E, K, renorm, logits_bf16, ids_out, w_out, as_stream(stream), pdl_on(ctx));
-  }
-  if (r) return r;
+  if (sigmoid) HB_REQUIRE(ctx, ld == E, HB_ERR_INVALID, "moe_layer_decode: the sigmoid router takes dense logits rows (ld == E)");
+  // routing runs inside the grouping kernel (one launch for route + sort)
   hbk_pair_src src; src.ids = ids_out; src.w = w_out; src.M = M; src.K = K; src.tab = rec_tab; src.li = li; src.E = E; src.shared_rec = shared_rec;
+  src.route = sigmoid ? 2 : 1; src.logits = logits; src.ld = ld; src.renorm = renorm; src.logits_bf16 = logits_bf16; src.bias = bias;
+  src.sig_scale = sigmoid_scale != 0.f ? sigmoid_scale : 1.f;
   hbk_reduce red; red.out_bf16 = out;
   if (gate_col >= 0 && shared_rec) { red.lg = logits; red.ld = ld; red.col = gate_col; }
   return hbk_moe_decode_run(ctx, src, x, H, I, limit, red, ws, as_stream(stream));

@@ -39,6 +39,10 @@ struct hbk_pair_src {
   const int32_t* ids = nullptr; const float* w = nullptr; int M = 0, K = 0;  // routed form
   const uint8_t* const* tab = nullptr; int li = 0, E = 0;
   const uint8_t* shared_rec = nullptr;
+  // routed form, optional: route inside the grouping kernel (ids / w are then outputs written before they are grouped)
+  int route = 0;                                                             // 0 = ids / w given, 1 = softmax, 2 = sigmoid + bias
+  const float* logits = nullptr; int ld = 0, renorm = 0, logits_bf16 = 0;
+  const float* bias = nullptr; float sig_scale = 1.f;
 };
 // What the last kernel does with the per-pair outputs.
 struct hbk_reduce {

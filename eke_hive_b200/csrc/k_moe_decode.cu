@@ -13,6 +13,7 @@
 // Shapes the streaming path takes: H, I multiples of 256, at most 4096; anything else (H, I multiples of 32) runs on the
 // generic CUDA-core kernels at the end of this file.
 #include "moe_stream.cuh"
+#include "router.cuh"
 
 namespace hb {
 
@@ -23,6 +24,9 @@ struct GroupArgs {
   const uint8_t* const* tab; int li, E;
   const uint8_t* shared_rec;
   DecodeWs ws;
+  // optional routing stage (routed form): logits → ids / w by one warp per row before the grouping
+  int route; const float* logits; int ld, renorm, logits_bf16; const float* bias; float sig_scale;
+  int32_t* ids_out; float* w_out;
 };
 
 // Exclusive scan of two int arrays of length n in shared memory, by the whole block (blockDim.x == kGroupThreads).
@@ -67,6 +71,17 @@ __global__ void __launch_bounds__(kGroupThreads) moe_group_kernel(GroupArgs a) {
   int* fill = ngr + NK;                                 // [NK]
   int* misc = fill + NK;                                // [64 + 2]
   const uint8_t** recs = reinterpret_cast<const uint8_t**>(gsm + ((size_t)(P + 3 * NK + 68) * 4 + 7) / 8 * 8);   // [P], list form only
+  if (a.route) {                                        // routed form with routing: recs is unused, the router scratch sits there
+    float* rsm = reinterpret_cast<float*>(recs);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int m = warp; m < a.M; m += nwarps) {
+      if (a.route == 1) route_softmax_row(a.logits + (size_t)m * a.ld, a.E, a.K, a.renorm, a.logits_bf16, rsm + (size_t)warp * a.E, lane,
+                                          a.ids_out + (size_t)m * a.K, a.w_out + (size_t)m * a.K);
+      else route_sigmoid_row(a.logits + (size_t)m * a.ld, a.bias, a.E, a.K, a.sig_scale, rsm + (size_t)warp * 2 * a.E, lane,
+                             a.ids_out + (size_t)m * a.K, a.w_out + (size_t)m * a.K);
+    }
+    __syncthreads();                                    // ids / w of every row are written (same CTA): the grouping below reads them
+  }
   for (int k = threadIdx.x; k < NK; k += blockDim.x) { cnt[k] = 0; fill[k] = 0; }
   for (int i = threadIdx.x; i < P; i += blockDim.x) {
     int row, kk = -1; float wv;
@@ -119,13 +134,15 @@ __global__ void __launch_bounds__(kGroupThreads) moe_group_kernel(GroupArgs a) {
     if (kk >= 0) { pos = cnt[kk] + atomicAdd(&fill[kk], 1); a.ws.s_row[pos] = a.ws.prow[i]; }
     a.ws.pos_of[i] = pos;
   }
-  if (threadIdx.x == 0) { a.ws.hdr[0] = misc[65]; a.ws.hdr[1] = misc[64]; }
+  for (int i = threadIdx.x; i < P; i += blockDim.x) a.ws.done[i] = 0;
+  if (threadIdx.x == 0) { a.ws.hdr[0] = misc[65]; a.ws.hdr[1] = misc[64]; a.ws.hdr[2] = 0; }
 }
 
-static size_t group_smem(bool routed, int P, int E) {
+static size_t group_smem(bool routed, int P, int E, int route = 0) {
   const int NK = routed ? E + 1 : P;
   size_t b = (size_t)P * 4 + (size_t)NK * 12 + 68 * 4;
   b = (b + 7) / 8 * 8;
+  if (route) return b + (size_t)(kGroupThreads / 32) * E * 4 * (route == 2 ? 2 : 1);
   return b + (routed ? 0 : (size_t)P * 8);
 }
 
@@ -308,41 +325,11 @@ __global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK
 
 // ================================================================================================ reduce / combine
 // Routed form: out[m] = Σ_k w[m,k]·part[pos] in k order; then either fp32 (overwritten) or the shared-expert combine → bf16.
-__global__ void moe_reduce_routed_kernel(const __nv_bfloat16* __restrict__ part, const int* __restrict__ pos_of, const float* __restrict__ pw, int M, int K,
-                                         int H, int shared_pairs, const __nv_bfloat16* __restrict__ shared, const float* __restrict__ lg, int ld, int col,
-                                         __nv_bfloat16* __restrict__ out_bf16, float* __restrict__ out_f32) {
+__global__ void moe_reduce_routed_kernel(ReduceArgs r) {
   griddep_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;      // one thread per (row, 2 columns)
-  if (i >= (size_t)M * H / 2) return;
-  const int m = (int)(i / (H / 2)), d = (int)(i % (H / 2)) * 2;
-  float a0 = 0.f, a1 = 0.f;
-  for (int k = 0; k < K; ++k) {
-    const int pos = pos_of[m * K + k];
-    if (pos < 0) continue;
-    const float wv = pw[m * K + k];
-    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(part + (size_t)pos * H + d);
-    a0 = __fadd_rn(a0, __fmul_rn(wv, __bfloat162float(v.x)));
-    a1 = __fadd_rn(a1, __fmul_rn(wv, __bfloat162float(v.y)));
-  }
-  if (out_f32) { out_f32[(size_t)m * H + d] = a0; out_f32[(size_t)m * H + d + 1] = a1; }
-  if (!out_bf16) return;
-  float s0 = 0.f, s1 = 0.f;
-  bool have = false;
-  if (shared_pairs) {
-    const int pos = pos_of[M * K + m];
-    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(part + (size_t)pos * H + d);
-    s0 = __bfloat162float(v.x); s1 = __bfloat162float(v.y); have = true;
-  } else if (shared) {
-    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(shared + (size_t)m * H + d);
-    s0 = __bfloat162float(v.x); s1 = __bfloat162float(v.y); have = true;
-  }
-  if (have && lg) {
-    const float gt = bf16r(sigmoid_portable(bf16r(lg[(size_t)m * ld + col])));
-    s0 = bf16r(__fmul_rn(gt, s0)); s1 = bf16r(__fmul_rn(gt, s1));
-  }
-  __nv_bfloat162 o;
-  o.x = __float2bfloat16(__fadd_rn(bf16r(a0), s0)); o.y = __float2bfloat16(__fadd_rn(bf16r(a1), s1));
-  *reinterpret_cast<__nv_bfloat162*>(out_bf16 + (size_t)m * H + d) = o;
+  if (i >= (size_t)r.M * r.H / 2) return;
+  reduce_routed_unit(r, i);
 }
 
 // List form: out[row] += w·part, pairs visited in list order.  One block column per pair that is the first of its row.
@@ -426,6 +413,7 @@ using namespace hb;
 namespace {
 
 constexpr int kWkList[] = {1, 2, 3, 4, 6, 8, 12, 16};
+constexpr size_t kRouteSmemMax = 160 * 1024;       // shared memory the route + group kernel may ask for
 constexpr int wm_for(int wk) { return wk >= 8 ? 1 : (wk >= 4 ? 2 : (wk == 3 ? 2 : (wk == 2 ? 4 : 8))); }
 
 using StreamFn = void (*)(StreamArgs);
@@ -476,7 +464,7 @@ bool hbk_moe_decode_fast(int H, int I) {
 
 size_t hbk_moe_decode_ws_bytes(int n, int H, int I) {
   if (n < 1) n = 1;
-  return 256 + al256((size_t)n * sizeof(Group)) + 4 * al256((size_t)n * 4) + al256((size_t)n * I * 2) + al256((size_t)n * H * 2);
+  return 256 + al256((size_t)n * sizeof(Group)) + 5 * al256((size_t)n * 4) + al256((size_t)n * I * 2) + al256((size_t)n * H * 2);
 }
 
 int hbk_moe_decode_setup(hb_ctx* ctx) {
@@ -490,8 +478,12 @@ int hbk_moe_decode_setup(hb_ctx* ctx) {
       HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(kk.fn), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kk.smem(s)));
     }
   }
+  {
+    const int rf = hbk_moe_fused_setup(ctx);
+    if (rf) return rf;
+  }
   HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_group_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)group_smem(false, HB_MAX_PAIRS, 0)));
+                                    (int)kRouteSmemMax));
   return HB_OK;
 }
 
@@ -507,7 +499,20 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
   GroupArgs ga{};
   ga.pairs = src.pairs; ga.n_pairs = src.n_pairs; ga.ids = src.ids; ga.w = src.w; ga.M = src.M; ga.K = src.K;
   ga.tab = src.tab; ga.li = src.li; ga.E = src.E; ga.shared_rec = src.shared_rec; ga.ws = w;
-  int r = hb_launch(ctx, "moe_group", true, moe_group_kernel, dim3(1), dim3(kGroupThreads), group_smem(routed, P, src.E), st, ga);
+  int route = src.route;
+  if (route && group_smem(true, P, src.E, route) > kRouteSmemMax) {
+    // the per-warp router scratch does not fit beside the grouping arrays (large E): route with the stand-alone kernel first
+    int rr = route == 1 ? hbk_route_softmax_topk(ctx, src.logits, src.ld, src.M, src.E, src.K, src.renorm, src.logits_bf16, const_cast<int32_t*>(src.ids),
+                                                 const_cast<float*>(src.w), st, true)
+                        : hbk_route_sigmoid_topk(ctx, src.logits, src.bias, src.M, src.E, src.K, src.sig_scale, const_cast<int32_t*>(src.ids),
+                                                 const_cast<float*>(src.w), st, true);
+    if (rr) return rr;
+    route = 0;
+  }
+  ga.route = route; ga.logits = src.logits; ga.ld = src.ld; ga.renorm = src.renorm; ga.logits_bf16 = src.logits_bf16; ga.bias = src.bias;
+  ga.sig_scale = src.sig_scale; ga.ids_out = const_cast<int32_t*>(src.ids); ga.w_out = const_cast<float*>(src.w);
+  int r = hb_launch(ctx, route ? "moe_route_group" : "moe_group", true, moe_group_kernel, dim3(1), dim3(kGroupThreads), group_smem(routed, P, src.E, route),
+                    st, ga);
   if (r) return r;
 
   StreamArgs sa{};
@@ -519,7 +524,15 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
   sd.act = w.y; sd.act_ld = I; sd.outp = w.part;
   sd.off_wa = (uint32_t)L.w2; sd.off_sa = (uint32_t)L.s2;
 
-  if (hbk_moe_decode_fast(H, I)) {
+  if (hbk_moe_fused_available(H, I) && !(ctx->flags & HB_FLAG_UNFUSED)) {
+    // one persistent kernel: gate/up → down → (routed form) reduce + combine
+    if (routed) {
+      ReduceArgs ra{w.part, w.pos_of, w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
+                    reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32};
+      return hbk_moe_fused_launch(ctx, w, x, H, I, limit, L, &ra, st);
+    }
+    if ((r = hbk_moe_fused_launch(ctx, w, x, H, I, limit, L, nullptr, st))) return r;
+  } else if (hbk_moe_decode_fast(H, I)) {
     // PDL chain: group → gate/up → down → reduce.  Each streaming kernel calls griddepcontrol.launch_dependents only after its own
     // griddepcontrol.wait returned (gate/up) or after reading the group list (down), so when the down kernel's producer starts,
     // the grouping kernel has completed and its list is visible; the down consumers wait for gate/up before reading y.
@@ -542,11 +555,11 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
     if ((r = hb_launch(ctx, "moe_down_generic", true, moe_generic_kernel<true>, dim3((H + 7) / 8, P), dim3(256), (size_t)I * 4, st, sd))) return r;
   }
 
-  if (routed)
-    return hb_launch(ctx, "moe_reduce_routed", true, moe_reduce_routed_kernel, dim3((unsigned)(((size_t)src.M * H / 2 + 255) / 256)), dim3(256), 0, st,
-                     (const __nv_bfloat16*)w.part, (const int*)w.pos_of, (const float*)w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0,
-                     reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col, reinterpret_cast<__nv_bfloat16*>(red.out_bf16),
-                     red.out_f32);
+  if (routed) {
+    ReduceArgs ra{w.part, w.pos_of, w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
+                  reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32};
+    return hb_launch(ctx, "moe_reduce_routed", true, moe_reduce_routed_kernel, dim3((unsigned)(((size_t)src.M * H / 2 + 255) / 256)), dim3(256), 0, st, ra);
+  }
   return hb_launch(ctx, "moe_reduce_list", true, moe_reduce_list_kernel, dim3((H / 2 + 255) / 256, P), dim3(256), 0, st, (const __nv_bfloat16*)w.part,
                    (const int*)w.pos_of, (const int*)w.prow, (const float*)w.pw, P, H, red.out_accum);
 }

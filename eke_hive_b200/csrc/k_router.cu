@@ -2,22 +2,11 @@
 // shared-expert combine, and the gather / SwiGLU / scatter-add helpers of the composed prefill path.
 #include "hb_common.cuh"
 #include "hb_kernels.h"
+#include "router.cuh"
 
 namespace hb {
 
-// (value, id) maximum with ties to the smaller id, over the warp (16,8,4,2,1 butterfly)
-__device__ __forceinline__ void warp_argmax(float& best, int& bid) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bid, o);
-    if (ob > best || (ob == best && oi < bid)) { best = ob; bid = oi; }
-  }
-}
-
-// One warp per row.  p lives in shared memory (E floats per warp).  The exp is the portable polynomial form, the row sum is
-// taken per lane (e = lane, lane+32, …) and then by butterfly, the k picks are summed in pick order — the CPU oracle does
-// the same operations in the same order, so ids and weights agree to the bit.
+// One warp per row (see router.cuh)
 __global__ void router_softmax_kernel(const float* __restrict__ logits, int ld, int M, int E, int k, int renorm, int logits_bf16,
                                       int32_t* __restrict__ ids, float* __restrict__ w) {
   extern __shared__ float sm_p[];
@@ -25,49 +14,9 @@ __global__ void router_softmax_kernel(const float* __restrict__ logits, int ld, 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m = blockIdx.x * (blockDim.x >> 5) + warp;
   if (m >= M) return;
-  float* p = sm_p + (size_t)warp * E;
-  const float* lr = logits + (size_t)m * ld;
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) {
-    const float v = logits_bf16 ? bf16r(lr[e]) : lr[e];
-    p[e] = v;
-    mx = fmaxf(mx, v);
-  }
-  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) {
-    const float v = exp_portable(__fsub_rn(p[e], mx));
-    p[e] = v;
-    sum = __fadd_rn(sum, v);
-  }
-  for (int o = 16; o > 0; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
-  const float inv = __fdiv_rn(1.f, sum);
-  __syncwarp();
-  float my_w = 0.f, tot = 0.f;
-  int my_id = 0;
-  for (int r = 0; r < k; ++r) {
-    float best = -1.f;
-    int bid = 0x7fffffff;
-    for (int e = lane; e < E; e += 32) {
-      const float v = p[e];
-      if (v >= 0.f && v > best) { best = v; bid = e; }      // ascending e per lane: the first (smaller) id keeps a tie
-    }
-    warp_argmax(best, bid);
-    const float sw = __fmul_rn(best, inv);
-    tot = __fadd_rn(tot, sw);
-    if (lane == r) { my_id = bid; my_w = sw; }
-    if (bid != 0x7fffffff && (bid & 31) == lane) p[bid] = -1.f;
-    __syncwarp();
-  }
-  if (lane < k) {
-    const float sc = renorm ? __fdiv_rn(1.f, tot) : 1.f;
-    ids[(size_t)m * k + lane] = my_id;
-    w[(size_t)m * k + lane] = __fmul_rn(my_w, sc);
-  }
+  route_softmax_row(logits + (size_t)m * ld, E, k, renorm, logits_bf16, sm_p + (size_t)warp * E, lane, ids + (size_t)m * k, w + (size_t)m * k);
 }
 
-// One warp per row: s = sigmoid(logit), pick k maxima of s + bias (first maximum = smaller id), w = s/(Σs + 1e-20)·scale with
-// Σ in pick order.
 __global__ void router_sigmoid_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int M, int E, int k, float scale,
                                       int32_t* __restrict__ ids, float* __restrict__ w) {
   extern __shared__ float sm_p[];
@@ -75,38 +24,7 @@ __global__ void router_sigmoid_kernel(const float* __restrict__ logits, const fl
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m = blockIdx.x * (blockDim.x >> 5) + warp;
   if (m >= M) return;
-  float* s = sm_p + (size_t)warp * 2 * E;
-  float* c = s + E;
-  const float* lr = logits + (size_t)m * E;
-  for (int e = lane; e < E; e += 32) {
-    const float v = sigmoid_portable(lr[e]);
-    s[e] = v;
-    c[e] = bias ? __fadd_rn(v, bias[e]) : v;
-  }
-  __syncwarp();
-  float my_s = 0.f, sum = 0.f;
-  int my_id = 0;
-  for (int j = 0; j < k; ++j) {
-    float best = -INFINITY;
-    int bid = 0x7fffffff;
-    for (int e = lane; e < E; e += 32) {
-      const float v = c[e];
-      if (v > best) { best = v; bid = e; }
-    }
-    warp_argmax(best, bid);
-    if (bid == 0x7fffffff) bid = 0;                           // every candidate already taken or NaN: keep a valid id
-    const float sv = s[bid];
-    sum = __fadd_rn(sum, sv);
-    if (lane == j) { my_id = bid; my_s = sv; }
-    __syncwarp();
-    if ((bid & 31) == lane) c[bid] = -INFINITY;
-    __syncwarp();
-  }
-  if (lane < k) {
-    const float inv = __fdiv_rn(1.f, __fadd_rn(sum, 1e-20f));
-    ids[(size_t)m * k + lane] = my_id;
-    w[(size_t)m * k + lane] = __fmul_rn(__fmul_rn(my_s, inv), scale);
-  }
+  route_sigmoid_row(logits + (size_t)m * E, bias, E, k, scale, sm_p + (size_t)warp * 2 * E, lane, ids + (size_t)m * k, w + (size_t)m * k);
 }
 
 __global__ void build_pairs_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w, int M, int K, const uint8_t* const* __restrict__ tab,

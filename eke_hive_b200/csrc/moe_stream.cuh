@@ -24,6 +24,7 @@ struct DecodeWs {
   float* pw;              // [n_pairs] routing weight of each original pair
   __nv_bfloat16* y;       // [n_pairs, I]
   __nv_bfloat16* part;    // [n_pairs, H]
+  int* done;              // [n_pairs] fused kernel: gate/up items finished per group (zeroed by the grouping kernel); hdr[2] counts down items
 };
 
 __host__ __device__ inline size_t al256(size_t b) { return (b + 255) / 256 * 256; }
@@ -38,7 +39,8 @@ inline DecodeWs carve(void* ws, int n, int H, int I) {
   w.prow = reinterpret_cast<int*>(p); p += al256((size_t)n * 4);
   w.pw = reinterpret_cast<float*>(p); p += al256((size_t)n * 4);
   w.y = reinterpret_cast<__nv_bfloat16*>(p); p += al256((size_t)n * I * 2);
-  w.part = reinterpret_cast<__nv_bfloat16*>(p);
+  w.part = reinterpret_cast<__nv_bfloat16*>(p); p += al256((size_t)n * H * 2);
+  w.done = reinterpret_cast<int*>(p);
   return w;
 }
 
@@ -74,6 +76,9 @@ struct StreamCfg {
 // columns [64t, 64t+64) of activation row g of the group.  Each row slice is scaled by a power of two so its largest magnitude
 // lands in [2^14, 2^15) before the bf16 → f16 conversion (no overflow, small values keep their bits); inv[0], inv[1] return
 // the inverse factors of the two tile columns this lane accumulates.
+// COHERENT: the rows were written earlier in the same kernel by other CTAs — read them through L2 (ld.global.cg), never the
+// non-coherent path.
+template <bool COHERENT = false>
 __device__ __forceinline__ void load_b_frags(const __nv_bfloat16* src /* slice of the row of column g, or nullptr */, int t, uint32_t (&b)[32],
                                              float (&inv)[2]) {
   // two passes over the lane's 128 bytes (the second hits L1/L2): max magnitude first, then scale + convert, so that at most
@@ -83,7 +88,7 @@ __device__ __forceinline__ void load_b_frags(const __nv_bfloat16* src /* slice o
   if (p) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const uint4 r = __ldg(p + i);
+      const uint4 r = COHERENT ? __ldcg(p + i) : __ldg(p + i);
       const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) { am = max(am, w[j] & 0x7fffu); am = max(am, (w[j] >> 16) & 0x7fffu); }
@@ -97,7 +102,7 @@ __device__ __forceinline__ void load_b_frags(const __nv_bfloat16* src /* slice o
   const float myinv = __int_as_float((uint32_t)(e - 14) << 23);                 // 2^((e - 127) - 14)
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const uint4 r = p ? __ldg(p + i) : make_uint4(0, 0, 0, 0);
+    const uint4 r = p ? (COHERENT ? __ldcg(p + i) : __ldg(p + i)) : make_uint4(0, 0, 0, 0);
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -151,4 +156,79 @@ __device__ __forceinline__ void warp_slice_mma(const uint8_t* wa, const uint8_t*
   for (int j = 0; j < 4; ++j) acc[j] = c[0][j] + c[1][j];
 }
 
+// Epilogue of one 16-row tile held in m16n8k16 accumulator layout: acc[c] = (tile row g + 8·(c>>1), activation row 2t + (c&1)).
+// Gate/up tiles alternate gate and up rows (even g = gate, odd g = up of the same output row): bf16 roundings, optional clamp,
+// SiLU·up → y.  Down tiles: bf16(v · g2) → part.  gl = the record's three global scales.
+template <bool DOWN>
+__device__ __forceinline__ void tile_epilogue(const float (&acc)[4], const Group& grp, const float (&gl)[3], int row0 /* first matrix row of the tile */,
+                                              int lane, int H, int I, float limit, __nv_bfloat16* outp) {
+  const int g = lane >> 2, tok0 = 2 * (lane & 3);
+  if (DOWN) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int tok = tok0 + (c & 1), n = row0 + g + (c >> 1) * 8;
+      if (tok < grp.n) outp[(size_t)(grp.start + tok) * H + n] = __float2bfloat16(acc[c] * gl[2]);
+    }
+  } else {
+    float oth[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) oth[c] = __shfl_xor_sync(0xffffffffu, acc[c], 4);
+    const bool odd = g & 1;
+    const int i = row0 + (g >> 1) + (odd ? 4 : 0);
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      float gv = odd ? oth[2 + c] : acc[c], uv = odd ? acc[2 + c] : oth[c];
+      gv = bf16r(gv * gl[0]); uv = bf16r(uv * gl[1]);
+      if (limit > 0.f) { uv = fminf(fmaxf(uv, -limit), limit); gv = fminf(gv, limit); }
+      const float yv = gv / (1.f + __expf(-gv)) * uv;
+      const int tok = tok0 + c;
+      if (tok < grp.n) outp[(size_t)(grp.start + tok) * I + i] = __float2bfloat16(yv);
+    }
+  }
+}
+
+// Routed reduce of two adjacent columns of one row: Σ_k w·part in k order, then either the fp32 sum or the shared-expert combine.
+struct ReduceArgs {
+  const __nv_bfloat16* part; const int* pos_of; const float* pw; int M, K, H, shared_pairs;
+  const __nv_bfloat16* shared; const float* lg; int ld, col;
+  __nv_bfloat16* out_bf16; float* out_f32;
+};
+__device__ __forceinline__ void reduce_routed_unit(const ReduceArgs& r, size_t i) {
+  const int m = (int)(i / (r.H / 2)), d = (int)(i % (r.H / 2)) * 2;
+  float a0 = 0.f, a1 = 0.f;
+  for (int k = 0; k < r.K; ++k) {
+    const int pos = r.pos_of[m * r.K + k];
+    if (pos < 0) continue;
+    const float wv = r.pw[m * r.K + k];
+    const uint32_t raw = __ldcg(reinterpret_cast<const unsigned int*>(r.part + (size_t)pos * r.H + d));
+    a0 = __fadd_rn(a0, __fmul_rn(wv, __uint_as_float(raw << 16)));
+    a1 = __fadd_rn(a1, __fmul_rn(wv, __uint_as_float(raw & 0xffff0000u)));
+  }
+  if (r.out_f32) { r.out_f32[(size_t)m * r.H + d] = a0; r.out_f32[(size_t)m * r.H + d + 1] = a1; }
+  if (!r.out_bf16) return;
+  float s0 = 0.f, s1 = 0.f;
+  bool have = false;
+  if (r.shared_pairs) {
+    const int pos = r.pos_of[r.M * r.K + m];
+    const uint32_t raw = __ldcg(reinterpret_cast<const unsigned int*>(r.part + (size_t)pos * r.H + d));
+    s0 = __uint_as_float(raw << 16); s1 = __uint_as_float(raw & 0xffff0000u); have = true;
+  } else if (r.shared) {
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(r.shared + (size_t)m * r.H + d);
+    s0 = __bfloat162float(v.x); s1 = __bfloat162float(v.y); have = true;
+  }
+  if (have && r.lg) {
+    const float gt = bf16r(sigmoid_portable(bf16r(r.lg[(size_t)m * r.ld + r.col])));
+    s0 = bf16r(__fmul_rn(gt, s0)); s1 = bf16r(__fmul_rn(gt, s1));
+  }
+  __nv_bfloat162 o;
+  o.x = __float2bfloat16(__fadd_rn(bf16r(a0), s0)); o.y = __float2bfloat16(__fadd_rn(bf16r(a1), s1));
+  *reinterpret_cast<__nv_bfloat162*>(r.out_bf16 + (size_t)m * r.H + d) = o;
+}
+
 }  // namespace hb
+
+// fused layer kernel (k_moe_fused.cu)
+bool hbk_moe_fused_available(int H, int I);
+int hbk_moe_fused_setup(hb_ctx* ctx);
+int hbk_moe_fused_launch(hb_ctx* ctx, const hb::DecodeWs& w, const void* x, int H, int I, float limit, const hb_rec_layout& L, const hb::ReduceArgs* red,
+                         cudaStream_t st);

@@ -67,6 +67,14 @@ def test_routed_fast_path_vs_oracle(E, oracle, H, I, Ex, K, M):
     out2 = E.fn_moe_decode_routed(torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), E.rec_table(drecs), 0, Ex, bf16_tensor(x), H, I,
                                   shared=bf16_tensor(shared), lg=torch.from_numpy(lg).cuda(), col=1)
     assert torch.equal(out, out2)
+    # the three-kernel form (HB_FLAG_UNFUSED) performs the same arithmetic in the same order: bit-identical to the fused kernel
+    ctx3 = E.Context(flags=2)
+    out3 = E.fn_moe_decode_routed(torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), E.rec_table(drecs), 0, Ex, bf16_tensor(x), H, I,
+                                  shared=bf16_tensor(shared), lg=torch.from_numpy(lg).cuda(), col=1, ctx=ctx3)
+    torch.cuda.synchronize()
+    ctx3.check_device()
+    assert torch.equal(out, out3)
+    ctx3.close()
 
 
 def test_pair_list_accumulates_in_pair_order(E, oracle):
