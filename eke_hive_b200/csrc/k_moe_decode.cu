@@ -524,7 +524,7 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
   sd.act = w.y; sd.act_ld = I; sd.outp = w.part;
   sd.off_wa = (uint32_t)L.w2; sd.off_sa = (uint32_t)L.s2;
 
-  if (hbk_moe_fused_available(H, I) && !(ctx->flags & HB_FLAG_UNFUSED)) {
+  if (hbk_moe_fused_available(H, I) && (ctx->flags & HB_FLAG_FUSED)) {
     // one persistent kernel: gate/up → down → (routed form) reduce + combine
     if (routed) {
       ReduceArgs ra{w.part, w.pos_of, w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,

@@ -32,7 +32,7 @@ __device__ __forceinline__ int ld_acquire(const int* p) {
 __device__ __forceinline__ bool wait_counter(const int* p, int target, uint32_t* err, uint32_t site) {
   for (uint32_t it = 0; it < (1u << 22); ++it) {
     if (ld_acquire(p) >= target) return true;
-    if (it > 16) __nanosleep(64);
+    if (it > 4096) __nanosleep(64);
   }
   if (err) atomicOr(err, site);
   return false;
@@ -91,9 +91,11 @@ __device__ __forceinline__ bool epilogue_stage(const FusedArgs& a, const SmemVie
   // fence, then add the run length to the group's counter (gate/up) or to the down total.
   auto publish = [&]() {
     if (pending == 0) return;
-    __threadfence();                                       // the run's outputs are visible device-wide before they are counted
-    __syncwarp();
-    if (lane == 0) atomicAdd(DOWN ? &a.hdr[2] : &a.done[cur], pending);
+    __syncwarp();                                          // every lane's stores of the run are ordered before lane 0's fence …
+    if (lane == 0) {
+      __threadfence();                                     // … which makes them visible device-wide before they are counted
+      atomicAdd(DOWN ? &a.hdr[2] : &a.done[cur], pending);
+    }
     pending = 0;
   };
   for (int it = 0; it < n_items; ++it) {
@@ -194,30 +196,46 @@ __global__ void __launch_bounds__(FusedCfg<WKA, WKB, NW>::THREADS, FusedCfg<WKA,
   griddep_wait();                                          // the grouping kernel's list and zeroed counters
   const int n_groups = a.hdr[0];
   const int tilesA = a.I / CA::TR, tilesB = a.H / CB::TR;
-  const long long totA = (long long)n_groups * tilesA, totB = (long long)n_groups * tilesB;
-  const int a0 = (int)(totA * blockIdx.x / gridDim.x), a1 = (int)(totA * (blockIdx.x + 1) / gridDim.x);
-  const int b0 = (int)(totB * blockIdx.x / gridDim.x), b1 = (int)(totB * (blockIdx.x + 1) / gridDim.x);
   griddep_launch();
+  // Work split, aligned to groups: with no more groups than CTAs, a team of T = ⌊CTAs / groups⌋ CTAs shares one group (each
+  // member a contiguous share of its gate/up tiles, then of its down tiles), so a CTA loads its activation fragments once per
+  // stage and only waits for its own team before the down stage; with more groups than CTAs every CTA takes whole groups.
+  const int G = (int)gridDim.x, cta = (int)blockIdx.x;
+  const int T = n_groups > 0 && n_groups <= G ? G / n_groups : 1;
+  const int g_first = cta / T, member = cta % T, g_stride = n_groups <= G ? n_groups : G;   // one pass when teams are used
+  const int ta0 = tilesA * member / T, ta1 = tilesA * (member + 1) / T;
+  const int tb0 = tilesB * member / T, tb1 = tilesB * (member + 1) / T;
   Cursor c;
 
-  if (warp == NW) {                                        // ---- producer: one lane keeps the ring full across both stages
+  if (warp == NW) {                                        // ---- producer: one lane keeps the ring full across stages and groups
     if (lane == 0) {
       int issued = 0;
-      if (producer_stage<CA, false>(a, v, c, a0, a1 - a0, tilesA, &issued)) producer_stage<CB, true>(a, v, c, b0, b1 - b0, tilesB, &issued);
+      bool ok = true;
+      for (int gi = g_first; gi < n_groups && ok; gi += g_stride) {
+        ok = producer_stage<CA, false>(a, v, c, gi * tilesA + ta0, ta1 - ta0, tilesA, &issued);
+        if (ok) ok = producer_stage<CB, true>(a, v, c, gi * tilesB + tb0, tb1 - tb0, tilesB, &issued);
+      }
       // copies still in flight land before the CTA leaves (immediate when the consumers took every stage)
       for (int j = issued > v.S ? issued - v.S : 0; j < issued; ++j) mbar_wait(&v.full[j % v.S], (uint32_t)((j / v.S) & 1), a.err, 4u);
     }
     return;
   }
   if (warp == NW + 1) {                                    // ---- epilogue warp
-    if (epilogue_stage<CA, false>(a, v, c, a0, a1 - a0, tilesA, lane)) epilogue_stage<CB, true>(a, v, c, b0, b1 - b0, tilesB, lane);
+    bool ok = true;
+    for (int gi = g_first; gi < n_groups && ok; gi += g_stride) {
+      ok = epilogue_stage<CA, false>(a, v, c, gi * tilesA + ta0, ta1 - ta0, tilesA, lane);
+      if (ok) ok = epilogue_stage<CB, true>(a, v, c, gi * tilesB + tb0, tb1 - tb0, tilesB, lane);
+    }
     return;
   }
   // ---- consumers
-  if (!consumer_stage<CA, false>(a, v, c, a0, a1 - a0, tilesA, warp, lane, tilesA)) return;
-  if (!consumer_stage<CB, true>(a, v, c, b0, b1 - b0, tilesB, warp, lane, tilesA)) return;
+  for (int gi = g_first; gi < n_groups; gi += g_stride) {
+    if (!consumer_stage<CA, false>(a, v, c, gi * tilesA + ta0, ta1 - ta0, tilesA, warp, lane, tilesA)) return;
+    if (!consumer_stage<CB, true>(a, v, c, gi * tilesB + tb0, tb1 - tb0, tilesB, warp, lane, tilesA)) return;
+  }
   if (!a.do_reduce) return;
   // ---- routed reduce + combine over this CTA's share of (row, column pair) units, once every down item is counted
+  const long long totB = (long long)n_groups * tilesB;
   const size_t units = (size_t)a.red.M * a.H / 2;
   const size_t per = (units + gridDim.x - 1) / gridDim.x;
   const size_t u0 = per * blockIdx.x, u1 = u0 + per < units ? u0 + per : units;

@@ -196,13 +196,22 @@ struct ReduceArgs {
 __device__ __forceinline__ void reduce_routed_unit(const ReduceArgs& r, size_t i) {
   const int m = (int)(i / (r.H / 2)), d = (int)(i % (r.H / 2)) * 2;
   float a0 = 0.f, a1 = 0.f;
-  for (int k = 0; k < r.K; ++k) {
-    const int pos = r.pos_of[m * r.K + k];
-    if (pos < 0) continue;
-    const float wv = r.pw[m * r.K + k];
-    const uint32_t raw = __ldcg(reinterpret_cast<const unsigned int*>(r.part + (size_t)pos * r.H + d));
-    a0 = __fadd_rn(a0, __fmul_rn(wv, __uint_as_float(raw << 16)));
-    a1 = __fadd_rn(a1, __fmul_rn(wv, __uint_as_float(raw & 0xffff0000u)));
+  // K ≤ 16: fetch every term first (independent loads in flight together), then add in k order
+  uint32_t raw[16]; float wv[16];
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    raw[k] = 0u; wv[k] = 0.f;
+    if (k < r.K) {
+      const int pos = r.pos_of[m * r.K + k];
+      if (pos >= 0) { wv[k] = r.pw[m * r.K + k]; raw[k] = __ldcg(reinterpret_cast<const unsigned int*>(r.part + (size_t)pos * r.H + d)); }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    if (k < r.K && r.pos_of[m * r.K + k] >= 0) {           // a skipped pair adds nothing (not even +0: keeps -0 sums as they are)
+      a0 = __fadd_rn(a0, __fmul_rn(wv[k], __uint_as_float(raw[k] << 16)));
+      a1 = __fadd_rn(a1, __fmul_rn(wv[k], __uint_as_float(raw[k] & 0xffff0000u)));
+    }
   }
   if (r.out_f32) { r.out_f32[(size_t)m * r.H + d] = a0; r.out_f32[(size_t)m * r.H + d + 1] = a1; }
   if (!r.out_bf16) return;

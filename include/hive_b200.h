@@ -44,7 +44,7 @@ typedef struct hb_config {
   int flags;        /* HB_FLAG_* */
 } hb_config;
 #define HB_FLAG_NO_PDL 1   /* launch every kernel fully serialised (no programmatic dependent launch) */
-#define HB_FLAG_UNFUSED 2  /* decode: run gate/up, down and reduce as three kernels instead of the fused persistent one */
+#define HB_FLAG_FUSED 2    /* decode: run gate/up, down and reduce as ONE persistent kernel (experimental; default: three kernels chained by PDL) */
 
 /* Expert record layout, byte-identical to hive::glm::ExpertRecLayout::make (engine/include/hive/glm/glm_moe.h:13-22):
  * [w1 gate e2m1 [I,H/2]][s1 e4m3 [I,H/16]][w3 up][s3][w2 down e2m1 [H,I/2]][s2 e4m3 [H,I/16]][g1 g3 g2 fp32], total 4096-aligned. */

@@ -67,7 +67,7 @@ def test_routed_fast_path_vs_oracle(E, oracle, H, I, Ex, K, M):
     out2 = E.fn_moe_decode_routed(torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), E.rec_table(drecs), 0, Ex, bf16_tensor(x), H, I,
                                   shared=bf16_tensor(shared), lg=torch.from_numpy(lg).cuda(), col=1)
     assert torch.equal(out, out2)
-    # the three-kernel form (HB_FLAG_UNFUSED) performs the same arithmetic in the same order: bit-identical to the fused kernel
+    # the single persistent kernel (HB_FLAG_FUSED) performs the same arithmetic in the same order: bit-identical to the three-kernel form
     ctx3 = E.Context(flags=2)
     out3 = E.fn_moe_decode_routed(torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), E.rec_table(drecs), 0, Ex, bf16_tensor(x), H, I,
                                   shared=bf16_tensor(shared), lg=torch.from_numpy(lg).cuda(), col=1, ctx=ctx3)
