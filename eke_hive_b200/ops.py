@@ -15,7 +15,7 @@ from . import _lib
 from ._lib import Config, HbError, MoePair, PfCombine, RecLayout
 
 __all__ = ["Context", "context", "ExpertRecLayout", "nvfp4_dequant", "nvfp4_gemv", "nvfp4_quantize", "a4_quant", "router_softmax_topk",
-           "router_topk", "build_moe_pairs", "moe_combine", "moe_decode_ws_bytes", "moe_decode", "fn_moe_decode_routed", "moe_decode_routed_f32", "moe_layer_decode",
+           "router_topk", "build_moe_pairs", "moe_combine", "moe_decode_ws_bytes", "moe_decode", "fn_moe_decode_routed", "fn_moe_decode_routed_static", "static_max_pairs", "moe_decode_routed_f32", "moe_layer_decode",
            "moe_decode_supported", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
 
 
@@ -249,6 +249,25 @@ def fn_moe_decode_routed(ids, w, rec_tab, li: int, E: int, x, H: int, I: int, sh
     cmb = PfCombine(_p(shared), _p(lg), 0 if lg is None else lg.stride(0), col, _p(out))
     ctx.check(_L().hb_moe_decode_routed(ctx.handle, _p(ids), _p(w), M, K, _p(rec_tab), li, E, _p(x), H, I, limit, C.byref(cmb), _p(ws), _stream()))
     return out
+
+
+def fn_moe_decode_routed_static(ids, w, rec_tab, li: int, E: int, x, H: int, I: int, shared=None, lg=None, col: int = 0, out=None, limit: float = 0.0,
+                                ctx: Context | None = None):
+    """fn_moe_decode_routed without a workspace argument, for hosts that may not allocate when they call: the scratch is the
+    library's built-in 4 MiB device array.  `out` must be given by the caller if the call itself has to be allocation-free
+    (this wrapper creates it with torch when it is None).  Raises HbError(-2) when M·K exceeds static_max_pairs(H, I).
+    Calls sharing a device must not overlap on the GPU."""
+    ctx = ctx or context()
+    M, K = ids.shape
+    out = torch.empty((M, H), dtype=torch.bfloat16, device=x.device) if out is None else out
+    cmb = PfCombine(_p(shared), _p(lg), 0 if lg is None else lg.stride(0), col, _p(out))
+    ctx.check(_L().hb_moe_decode_routed_static(ctx.handle, _p(ids), _p(w), M, K, _p(rec_tab), li, E, _p(x), H, I, limit, C.byref(cmb), _stream()))
+    return out
+
+
+def static_max_pairs(H: int, I: int) -> int:
+    """Largest M·K hb_moe_decode_routed_static accepts at this expert shape."""
+    return int(_L().hb_moe_decode_static_max_pairs(H, I))
 
 
 def moe_decode_routed_f32(ids, w, rec_tab, li: int, E: int, x, H: int, I: int, out=None, limit: float = 0.0, ws=None, ctx: Context | None = None):

@@ -145,6 +145,20 @@ HB_API int hb_moe_decode(hb_ctx* ctx, const hb_moe_pair* pairs, int n_pairs, con
  * Records come from rec_tab[li·E + id]; ids outside [0,E) and NULL records contribute nothing.  cmb->lg NULL = no gate. */
 HB_API int hb_moe_decode_routed(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int K, const uint8_t* const* rec_tab, int li, int E,
                                 const void* x_bf16, int H, int I, float limit, const hb_pf_combine* cmb, void* ws, void* stream);
+/* (No counterpart in the reference.)  hb_moe_decode_routed for callers that cannot allocate device memory when they call —
+ * an engine that spends its whole memory budget at start-up and forbids cudaMalloc afterwards, a decode loop that must not
+ * synchronise the device, a plugin host that keeps the allocator to itself.  Same arguments and result as
+ * hb_moe_decode_routed without `ws`: the scratch is a fixed 4 MiB array built into the library (each GPU that loads the
+ * library holds it until the process exits).  Limits and rules:
+ *   - a call whose scratch would exceed the array fails with HB_ERR_UNSUPPORTED and a message naming the limit;
+ *     hb_moe_decode_static_max_pairs(H, I) gives the largest M·K accepted at a shape (813 pairs at H 2048, I 512; 371 at H 4096, I 1536);
+ *   - the first call on a device looks up the array's device address (with that device current); make that first call before
+ *     any stream capture.  No call allocates or frees memory;
+ *   - every call on a device uses the same array and finds the previous call's contents in it (what must start at zero is
+ *     cleared by the kernels themselves); calls that overlap on the GPU race on it — keep them on one stream. */
+HB_API int hb_moe_decode_static_max_pairs(int H, int I);
+HB_API int hb_moe_decode_routed_static(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int K, const uint8_t* const* rec_tab, int li, int E,
+                                       const void* x_bf16, int H, int I, float limit, const hb_pf_combine* cmb, void* stream);
 /* The routed sum alone, fp32, overwritten: out[m] = Σ_k w[m,k]·expert_ids[m,k](x[m]) in k order — the output contract of
  * hive::qwen::fn_moe_prefill without its combine (engine/include/hive/qwen/fn_moe.h:46-61) on the decode kernels.  Used by the
  * expert-parallel layer, where rec_tab holds NULL for experts that live on other GPUs (those pairs contribute nothing). */
