@@ -92,6 +92,10 @@ def load() -> C.CDLL:
         "hb_moe_decode_routed_static": (i, [vp, vp, vp, i, i, vp, i, i, vp, i, i, f, C.POINTER(PfCombine), vp]),
         "hb_moe_decode_routed_f32": (i, [vp, vp, vp, i, i, vp, i, i, vp, i, i, f, vp, vp, vp]),
         "hb_moe_layer_decode": (i, [vp, vp, i, i, i, i, i, i, vp, f, vp, i, vp, i, vp, i, i, f, vp, vp, vp, vp, vp]),
+        "hb_dense_gemv_ws_bytes": (sz, [i, i, i, i]),
+        "hb_dense_gemv": (i, [vp, C.POINTER(QMat), vp, i, i, vp, vp, i, vp, vp]),
+        "hb_dense_gemv_gu": (i, [vp, C.POINTER(QMat), C.POINTER(QMat), vp, i, i, vp, i, vp, vp]),
+        "hb_lb_dequant": (i, [vp, C.POINTER(QMat), vp, vp]),
         "hb_gather_rows": (i, [vp, vp, vp, i, i, vp, vp]),
         "hb_swiglu_rows": (i, [vp, vp, i, i, f, vp, vp]),
         "hb_scatter_add_rows": (i, [vp, vp, vp, vp, i, i, vp, vp]),

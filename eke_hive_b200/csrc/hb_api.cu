@@ -33,7 +33,8 @@ int hb_create(const hb_config* cfg, hb_ctx** out) {
   c->sm_count = prop.multiProcessorCount;
   c->smem_optin = (int)prop.sharedMemPerBlockOptin;
   if (cudaMalloc(&c->dev_err, 256) != cudaSuccess || cudaMemset(c->dev_err, 0, 256) != cudaSuccess) { delete c; cudaGetLastError(); return HB_ERR_CUDA; }
-  const int r = hbk_moe_decode_setup(c);
+  int r = hbk_moe_decode_setup(c);
+  if (r == HB_OK) r = hbk_dense_setup(c);
   if (r != HB_OK) { cudaFree(c->dev_err); delete c; return r; }
   *out = c;
   return HB_OK;

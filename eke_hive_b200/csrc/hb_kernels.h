@@ -54,3 +54,6 @@ struct hbk_reduce {
 };
 int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int H, int I, float limit, const hbk_reduce& red, void* ws,
                        cudaStream_t st);
+
+// dense GEMV (k_dense.cu)
+int hbk_dense_setup(hb_ctx* ctx);

@@ -135,7 +135,7 @@ __device__ __forceinline__ void warp_slice_mma(const uint8_t* wa, const uint8_t*
     const uint4 qa = *reinterpret_cast<const uint4*>(wa + 16 * h), qb = *reinterpret_cast<const uint4*>(wb + 16 * h);
     if (h == 1) {                                       // everything this warp needs from the stage is in registers
       __syncwarp();
-      if ((threadIdx.x & 31) == 0) mbar_arrive(empty_bar);
+      if (empty_bar && (threadIdx.x & 31) == 0) mbar_arrive(empty_bar);
     }
     const uint32_t wqa[4] = {qa.x, qa.y, qa.z, qa.w}, wqb[4] = {qb.x, qb.y, qb.z, qb.w};
 #pragma unroll

@@ -16,7 +16,7 @@ from ._lib import Config, HbError, MoePair, PfCombine, RecLayout
 
 __all__ = ["Context", "context", "ExpertRecLayout", "nvfp4_dequant", "nvfp4_gemv", "nvfp4_quantize", "a4_quant", "router_softmax_topk",
            "router_topk", "build_moe_pairs", "moe_combine", "moe_decode_ws_bytes", "moe_decode", "fn_moe_decode_routed", "fn_moe_decode_routed_static", "static_max_pairs", "moe_decode_routed_f32", "moe_layer_decode",
-           "moe_decode_supported", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
+           "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
 
 
 def _L():
@@ -293,6 +293,52 @@ def moe_layer_decode(logits, x, rec_tab, li: int, E: int, K: int, H: int, I: int
     ctx.check(_L().hb_moe_layer_decode(ctx.handle, _p(logits), logits.stride(0), M, E, K, int(renorm), int(logits_bf16), _p(bias), sigmoid_scale,
                                        _p(rec_tab), li, _p(shared_rec), gate_col, _p(x), H, I, limit, _p(ids), _p(w), _p(out), _p(ws), _stream()))
     return ids, w, out
+
+
+# ---------------------------------------------------------------------------------------------------- dense GEMV (hb_qmat)
+FMT_NVFP4, FMT_LB3_G64, FMT_LB2_G64 = 0, 1, 2
+
+
+class GMat:
+    """hive::q27::GMat for the formats this library takes: device tensors of one [N, K] weight matrix.
+    NVFP4: w u8 [N, K/2], s u8 [N, K/16], g.  LB2/LB3: w u8 codes (LB3: low plane then high plane), s / zp fp16 [N, K/64]."""
+
+    def __init__(self, fmt: int, N: int, K: int, w, s, zp=None, g: float = 1.0):
+        from ._lib import QMat
+        self.fmt, self.N, self.K, self.w, self.s, self.zp, self.g = fmt, N, K, w, s, zp, g
+        self.c = QMat(fmt, N, K, _p(w), _p(s), _p(zp), g)
+
+
+def dense_gemv_ws_bytes(fmt: int, N: int, K: int, n_mats: int = 1) -> int:
+    return int(_L().hb_dense_gemv_ws_bytes(fmt, N, K, n_mats))
+
+
+def dense_gemv(W: GMat, x, out_dtype=torch.float32, y=None, ws=None, ctx: Context | None = None):
+    """hive::q27::k::gemv: y[m, n] = Σ_k x[m, k]·W[n, k]; y bf16 or fp32 [M, N]."""
+    ctx = ctx or context()
+    M = x.shape[0]
+    y = torch.empty((M, W.N), dtype=out_dtype, device=x.device) if y is None else y
+    ws = torch.empty(dense_gemv_ws_bytes(W.fmt, W.N, W.K, 1), dtype=torch.uint8, device=x.device) if ws is None else ws
+    yb, yf = (_p(y), None) if y.dtype == torch.bfloat16 else (None, _p(y))
+    ctx.check(_L().hb_dense_gemv(ctx.handle, C.byref(W.c), _p(x), x.stride(0), M, yb, yf, y.stride(0), _p(ws), _stream()))
+    return y
+
+
+def dense_gemv_gu(G: GMat, U: GMat, x, act=None, ws=None, ctx: Context | None = None):
+    """hive::q27::k::gemv_gu: act = bf16(bf16(silu(bf16 g)) · bf16 u), bf16 [M, N]."""
+    ctx = ctx or context()
+    M = x.shape[0]
+    act = torch.empty((M, G.N), dtype=torch.bfloat16, device=x.device) if act is None else act
+    ws = torch.empty(dense_gemv_ws_bytes(G.fmt, G.N, G.K, 2), dtype=torch.uint8, device=x.device) if ws is None else ws
+    ctx.check(_L().hb_dense_gemv_gu(ctx.handle, C.byref(G.c), C.byref(U.c), _p(x), x.stride(0), M, _p(act), act.stride(0), _p(ws), _stream()))
+    return act
+
+
+def lb_dequant(W: GMat, out=None, ctx: Context | None = None):
+    ctx = ctx or context()
+    out = torch.empty((W.N, W.K), dtype=torch.bfloat16, device=W.w.device) if out is None else out
+    ctx.check(_L().hb_lb_dequant(ctx.handle, C.byref(W.c), _p(out), _stream()))
+    return out
 
 
 # ---------------------------------------------------------------------------------------------------- prefill helpers

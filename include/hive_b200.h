@@ -173,6 +173,21 @@ HB_API int hb_moe_layer_decode(hb_ctx* ctx, const float* logits, int ld, int M, 
                                const uint8_t* shared_rec, int gate_col, const void* x_bf16, int H, int I, float limit,
                                int32_t* ids_out, float* w_out, void* out_bf16, void* ws, void* stream);
 
+/* ---- dense decode GEMV of the 27B-style MLP: NVFP4 and the 3-/2-bit group-64 formats (hb_qmat) ---- */
+HB_API size_t hb_dense_gemv_ws_bytes(int fmt, int N, int K, int n_mats /* 1 = gemv, 2 = gemv_gu */);
+/* hive::q27::k::gemv — engine/include/hive/q27/q27_kernels.h:48-50, engine/src/q27/q27_kernels.cu:2423-2449:
+ * y[m,n] = Σ_k x[m,k]·W[n,k], fp32 accumulation, written as bf16 (yb) or fp32 (yf): exactly one non-NULL.  x bf16 [M,K] (row
+ * stride ldx), M ≤ 16 (the reference takes ≤ 8; rows are processed 8 at a time with batch-independent arithmetic), K % 256 == 0. */
+HB_API int hb_dense_gemv(hb_ctx* ctx, const hb_qmat* W, const void* x_bf16, int ldx, int M, void* yb_bf16, float* yf, int ldy, void* ws,
+                         void* stream);
+/* hive::q27::k::gemv_gu — engine/include/hive/q27/q27_kernels.h:62-64, engine/src/q27/q27_kernels.cu:258-289:
+ * act[m,n] = bf16( bf16(silu(bf16 g)) · bf16 u ), g / u = rows n of the gate / up matrices (same K and format). */
+HB_API int hb_dense_gemv_gu(hb_ctx* ctx, const hb_qmat* gate, const hb_qmat* up, const void* x_bf16, int ldx, int M, void* act_bf16, int lda,
+                            void* ws, void* stream);
+/* Dequantise a 3-/2-bit group-64 matrix to bf16 [N,K]: out = bf16((q − zp)·s) — the format's definition (no reference counterpart:
+ * the reference ships no low-bit layout, only an error probe, tools/lowbit_probe.py:18-38). */
+HB_API int hb_lb_dequant(hb_ctx* ctx, const hb_qmat* W, void* out_bf16, void* stream);
+
 /* ---- prefill helpers kept for callers that compose (engine/include/hive/glm/glm_moe.h:33-41) ---- */
 HB_API int hb_gather_rows(hb_ctx* ctx, const void* x_bf16, const int32_t* rows, int R, int H, void* out_bf16, void* stream);
 HB_API int hb_swiglu_rows(hb_ctx* ctx, const void* gu_bf16, int R, int I, float limit, void* y_bf16, void* stream);
