@@ -2,10 +2,11 @@
 // (hb_qmat).  HBM-bound: every weight byte is read once, decoded in registers and fed to m16n8k16 tensor-core tiles whose 8
 // columns are the activation rows (fp32 accumulation).
 //
-//   prep     the activation rows become f16 B fragments in the order the tiles consume them (per-row power-of-two rescale so
-//            bf16 outliers cannot overflow f16), plus, for the low-bit formats, two sums per 64-column group (see below)
-//   stream   grid = (128-row tiles, K splits).  A CTA keeps the B fragments of its K range in shared memory; each of its 8
-//            warps owns 16 weight rows and streams them through a private 4-stage cp.async ring, 256 columns per stage
+//   stream   persistent CTAs, grid = (CTAs per K split, K splits).  A CTA first turns the activation columns of its K range into
+//            f16 B fragments in shared memory, in the order the tiles consume them; every (row, 256-column slice) gets its own
+//            power-of-two rescale so bf16 outliers cannot overflow f16, undone in fp32 when the slice is accumulated.  Then each
+//            of its 8 warps claims strips of 16 weight rows from the split's counter and streams them through a private cp.async
+//            ring, 256 columns per stage; the ring keeps running across strip boundaries
 //   reduce   fixed-order sum over the K splits, output conversion, or the fused SiLU·up activation of the gate/up pair
 //
 // Low-bit decode without shifts or subtractions per element: a 2-bit field left at bit 2j of an f16 mantissa under exponent
@@ -18,7 +19,7 @@ namespace hb {
 
 constexpr int kDSlice = 256;            // columns per pipeline stage
 constexpr int kDWarps = 8;              // consumer warps per CTA, 16 weight rows each
-constexpr int kDRows = kDWarps * 16;    // rows per CTA tile
+constexpr int kDCounterWord = 8;        // strip counters live in words [8, 64) of the context's 256-byte device status block
 __host__ __device__ constexpr int dense_stages(int fmt) { return fmt == HB_FMT_NVFP4 ? 3 : 4; }
 // K range of one CTA (slices of 256 columns whose B fragments sit in shared memory): sized for two CTAs per SM
 __host__ __device__ constexpr int dense_max_slices(int fmt) { return fmt == HB_FMT_LB3_G64 ? 4 : 8; }
@@ -39,115 +40,89 @@ __host__ __device__ constexpr int dense_stage_bytes(int fmt) {
   return 16 * (dense_fmt(fmt).pitch_w + dense_fmt(fmt).pitch_h + dense_fmt(fmt).bytes_s);
 }
 
-struct DenseWs {
-  uint32_t* xb;      // [slices][planes][1024] B fragments: index ((r >> 2) * 32 + lane) * 4 + (r & 3), r = register 0..31 of the slice
-  float2* sums;      // [slices][4 groups][8 rows] (S0, S1), low-bit formats
-  unsigned int* amax; // [8] max |x| of each row as bf16 bits, then [8..] the strip counters of the K splits
-  float* part;       // [mats][K splits][8][N] fp32 partial sums
-};
-inline DenseWs dense_carve(void* ws, int slices, int planes, int mats, int ksplit, int N) {
-  uint8_t* p = reinterpret_cast<uint8_t*>(ws);
-  DenseWs w;
-  w.xb = reinterpret_cast<uint32_t*>(p); p += al256((size_t)slices * planes * 4096);
-  w.sums = reinterpret_cast<float2*>(p); p += al256((size_t)slices * 256);
-  w.amax = reinterpret_cast<unsigned int*>(p); p += 256;
-  w.part = reinterpret_cast<float*>(p);
-  (void)mats; (void)ksplit; (void)N;
-  return w;
-}
+// Workspace = fp32 partial sums [mats][K splits][8][N].
+//
+// Fragment order.  Register r (0..31) of lane (tok = lane >> 2, t = lane & 3) of a slice sits at uint32 index
+// ((r >> 2) * 32 + lane) * 4 + (r & 3) of the slice's plane; its halves hold, with gq = r >> 3 and pr = r & 7:
+//   NVFP4          columns 64t + 2r, 64t + 2r + 1
+//   2-bit plane    columns 64gq + 16t + pr and + 8, times 4^-j, j = pr < 5 ? pr : pr - 5   (the lane's 32-bit word of the group)
+//   1-bit plane    columns 64gq + 32(t >> 1) + 8(t & 1) + pr and + 16, times 4 / 2^pr      (lanes 0,1 share word 0, lanes 2,3 word 1)
 
-// ------------------------------------------------------------------------------------------------ prep
-// max |x| of each row as bf16 bits (integer order = magnitude order), over a grid of (row, column chunk) blocks; also zeroes
-// the strip counters of the stream kernel.  amax must be zero on entry (the reduce kernel of the previous pass leaves it so;
-// the first pass clears it with a memset).
-__global__ void dense_amax_kernel(const __nv_bfloat16* __restrict__ x, int ldx, int M, int K, unsigned int* __restrict__ amax, int* __restrict__ counters,
-                                  int n_counters) {
-  griddep_wait();
-  const int m = blockIdx.x;
-  if (blockIdx.x == 0 && blockIdx.y == 0) for (int i = threadIdx.x; i < n_counters; i += blockDim.x) counters[i] = 0;
-  if (m >= M) return;
+// B fragments, slice factor and group sums of row `tok`, slice `cs` (of the CTA's range) from the 8 columns [8·lane, 8·lane+8)
+// this lane holds in v.  One warp per (slice, row).
+template <int FMT>
+__device__ __forceinline__ void dense_build_row_slice(uint4 v, int cs, int tok, int lane, uint4* xb_s, float2* sums_s, float* inv_s) {
+  constexpr int PL = dense_fmt(FMT).planes;
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
   unsigned int am = 0;
-  const uint4* row = reinterpret_cast<const uint4*>(x + (size_t)m * ldx);
-  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < K / 8; i += gridDim.y * blockDim.x) {
-    const uint4 v = __ldg(row + i);
-    const unsigned int w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { am = max(am, w[j] & 0x7fffu); am = max(am, (w[j] >> 16) & 0x7fffu); }
-  }
+  for (int j = 0; j < 4; ++j) { am = max(am, w[j] & 0x7fffu); am = max(am, (w[j] >> 16) & 0x7fffu); }
+#pragma unroll
   for (int o = 16; o > 0; o >>= 1) am = max(am, __shfl_xor_sync(0xffffffffu, am, o));
-  if ((threadIdx.x & 31) == 0 && am) atomicMax(&amax[m], am);
-}
-// rescale factor of a row from its max magnitude: the max lands in [2^12, 2^13), so 4·x (high-bit plane) stays inside f16
-__device__ __forceinline__ float dense_fac(unsigned int am) {
-  int e = (int)(am >> 7);
-  e = min(max(e, 27), 254);
-  return __int_as_float((uint32_t)(127 + 12 + 127 - e) << 23);
-}
-__device__ __forceinline__ float dense_inv(unsigned int am) {
-  int e = (int)(am >> 7);
-  e = min(max(e, 27), 254);
-  return __int_as_float((uint32_t)(e - 12) << 23);
-}
-
-// element (within the slice) and position factor of half `hi` (0 / 1) of B register r of lane (tok, t), plane p
-__device__ __forceinline__ void dense_b_elem(int fmt, int p, int r, int t, int hi, int* elem, float* scale) {
-  if (fmt == HB_FMT_NVFP4) { *elem = 64 * t + 2 * r + hi; *scale = 1.f; return; }
-  const int gq = r >> 3, i = (r >> 1) & 3, h = r & 1, pr = 2 * i + h;      // group of the slice, tile of the group, pair of the lane's word
-  if (p == 0) {                                              // 2-bit plane: the lane's word = columns [16t, 16t+16) of the group
-    *elem = 64 * gq + 16 * t + pr + 8 * hi;
-    const int j = pr < 5 ? pr : pr - 5;
-    *scale = 1.f / (float)(1 << (2 * j));
-  } else {                                                   // 1-bit plane: lanes 0,1 share word 0, lanes 2,3 word 1; odd lanes take its upper bytes
-    *elem = 64 * gq + 32 * (t >> 1) + 8 * (t & 1) + pr + 16 * hi;
-    *scale = 4.f / (float)(1 << pr);
+  const int e = min(max((int)(am >> 7), 27), 254);                       // bf16 exponent field of the largest magnitude
+  const float f = __int_as_float((uint32_t)(127 + 12 + 127 - e) << 23);  // the maximum lands in [2^12, 2^13): 4·x (high-bit plane) stays inside f16
+  if (lane == 0) inv_s[cs * 8 + tok] = __int_as_float((uint32_t)(e - 12) << 23);
+  float xv[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { xv[2 * j] = __int_as_float(w[j] << 16) * f; xv[2 * j + 1] = __int_as_float(w[j] & 0xffff0000u) * f; }
+  if (FMT == HB_FMT_NVFP4) {
+    uint4 o;
+    __half2 h;
+    h = __floats2half2_rn(xv[0], xv[1]); o.x = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2half2_rn(xv[2], xv[3]); o.y = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2half2_rn(xv[4], xv[5]); o.z = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2half2_rn(xv[6], xv[7]); o.w = *reinterpret_cast<uint32_t*>(&h);
+    xb_s[(size_t)cs * 256 + (lane & 7) * 32 + tok * 4 + (lane >> 3)] = o;
+    return;
   }
-}
-
-// one block per slice: B fragments (both planes) and the group sums
-__global__ void __launch_bounds__(256) dense_prep_kernel(int fmt, const __nv_bfloat16* __restrict__ x, int ldx, int M, const unsigned int* __restrict__ amax,
-                                                         uint32_t* __restrict__ xb, float2* __restrict__ sums) {
-  griddep_wait();
-  const int sl = blockIdx.x, planes = dense_fmt(fmt).planes;
-  for (int p = 0; p < planes; ++p)
-    for (int idx = threadIdx.x; idx < 1024; idx += blockDim.x) {
-      const int r = idx >> 5, lane = idx & 31, tok = lane >> 2, t = lane & 3;
-      float v[2] = {0.f, 0.f};
-      int e0, e1; float sc0, sc1;
-      dense_b_elem(fmt, p, r, t, 0, &e0, &sc0);
-      dense_b_elem(fmt, p, r, t, 1, &e1, &sc1);
-      if (tok < M) {
-        const float f = dense_fac(amax[tok]);
-        v[0] = __bfloat162float(x[(size_t)tok * ldx + (size_t)sl * kDSlice + e0]) * f * sc0;
-        v[1] = __bfloat162float(x[(size_t)tok * ldx + (size_t)sl * kDSlice + e1]) * f * sc1;
-      }
-      const __half2 hh = __floats2half2_rn(v[0], v[1]);
-      xb[((size_t)sl * planes + p) * 1024 + ((r >> 2) * 32 + lane) * 4 + (r & 3)] = *reinterpret_cast<const uint32_t*>(&hh);
+  const int gq = lane >> 3, l7 = lane & 7;
+  float s0 = 0.f, s1 = 0.f;
+  {                                                                      // 2-bit plane: partner lane ^1 holds the other half of each register
+    float sv[8];
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      const int j = p < 5 ? p : p - 5;
+      sv[p] = __half2float(__float2half_rn(xv[p] * (1.f / (float)(1 << (2 * j)))));
+      s0 += __half2float(__float2half_rn(xv[p]));
+      s1 += sv[p];
     }
-  if (fmt == HB_FMT_NVFP4) return;
-  if (threadIdx.x < 32) {                                    // (group, row): S0 = Σ x (rescaled, as f16), S1 = 1024·Σ x' — serial, fixed order
-    const int gq = threadIdx.x >> 3, tok = threadIdx.x & 7;
-    float s0 = 0.f, s1 = 0.f;
-    if (tok < M) {
-      const float f = dense_fac(amax[tok]);
-      for (int k = 0; k < 64; ++k) {
-        const float xn = __bfloat162float(x[(size_t)tok * ldx + (size_t)sl * kDSlice + 64 * gq + k]) * f;
-        s0 += __half2float(__float2half_rn(xn));
-        const int pr = k & 7, j = pr < 5 ? pr : pr - 5;      // the factors dense_b_elem gives column k of a group
-        s1 += __half2float(__float2half_rn(xn / (float)(1 << (2 * j))));
-        if (planes > 1) s1 += __half2float(__float2half_rn(xn * 4.f / (float)(1 << pr)));
-      }
+    const int hi = lane & 1, t = l7 >> 1;
+    uint32_t o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float got = __shfl_xor_sync(0xffffffffu, hi ? sv[q] : sv[4 + q], 1);
+      const __half2 h = hi ? __floats2half2_rn(got, sv[4 + q]) : __floats2half2_rn(sv[q], got);
+      o[q] = *reinterpret_cast<const uint32_t*>(&h);
     }
-    sums[(size_t)sl * 32 + gq * 8 + tok] = make_float2(s0, 1024.f * s1);
+    xb_s[(size_t)cs * PL * 256 + (2 * gq + hi) * 32 + tok * 4 + t] = make_uint4(o[0], o[1], o[2], o[3]);
   }
+  if (FMT == HB_FMT_LB3_G64) {                                           // 1-bit plane: partner lane ^2
+    float hv[8];
+#pragma unroll
+    for (int p = 0; p < 8; ++p) { hv[p] = __half2float(__float2half_rn(xv[p] * (4.f / (float)(1 << p)))); s1 += hv[p]; }
+    const int hi = (l7 >> 1) & 1, t = 2 * (l7 >> 2) + (l7 & 1);
+    uint32_t o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float got = __shfl_xor_sync(0xffffffffu, hi ? hv[q] : hv[4 + q], 2);
+      const __half2 h = hi ? __floats2half2_rn(got, hv[4 + q]) : __floats2half2_rn(hv[q], got);
+      o[q] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    xb_s[(size_t)cs * PL * 256 + 256 + (2 * gq + hi) * 32 + tok * 4 + t] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  // the tile of a 64-column group sums (1024 + q·4^j)·x' (+ (1024 + b·2^j)·x''): S0 = Σ x removes the zero-point, S1 = 1024·Σ x' the offset
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) { s0 += __shfl_xor_sync(0xffffffffu, s0, o); s1 += __shfl_xor_sync(0xffffffffu, s1, o); }
+  if (l7 == 0) sums_s[(size_t)cs * 32 + gq * 8 + tok] = make_float2(s0, 1024.f * s1);
 }
 
 // ------------------------------------------------------------------------------------------------ stream
 struct DenseMat { const uint8_t* w; const uint8_t* wh; const uint8_t* s; const uint8_t* zp; float g; };
 struct DenseArgs {
   DenseMat mat[2]; int n_mats;
-  int N, K, M, ksplit, slices;            // slices = K / 256
-  const uint32_t* xb; const float2* sums; const unsigned int* amax;
-  int* counters;                          // [ksplit] next unclaimed strip of each K split (zeroed by the amax kernel)
+  int N, K, M, ksplit, slices, ldx;       // slices = K / 256
+  const __nv_bfloat16* x;
+  int* counters;                          // [ksplit] next unclaimed strip of each K split; zero between launches (the last claim of a launch resets it)
   float* part;                            // [n_mats][ksplit][8][N]
 };
 
@@ -170,30 +145,23 @@ __global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseAr
   constexpr int STG = dense_stage_bytes(FMT), NST = dense_stages(FMT), MAXSL = dense_max_slices(FMT);
   extern __shared__ __align__(128) uint8_t dsm[];
   uint4* xb_s = reinterpret_cast<uint4*>(dsm);                                            // [MAXSL][planes][256] uint4
-  float4* sums_s = reinterpret_cast<float4*>(dsm + (size_t)MAXSL * F.planes * 4096);      // [MAXSL][4 groups][4] float4 = rows (2i, 2i+1)
-  int* claimed_s = reinterpret_cast<int*>(dsm + (size_t)MAXSL * F.planes * 4096 + (size_t)MAXSL * 256);   // [warps][8]
+  float2* sums_s = reinterpret_cast<float2*>(dsm + (size_t)MAXSL * F.planes * 4096);      // [MAXSL][4 groups][8 rows] (S0, S1)
+  float* inv_s = reinterpret_cast<float*>(dsm + (size_t)MAXSL * F.planes * 4096 + (size_t)MAXSL * 256);   // [MAXSL][8 rows] 1 / slice factor
+  int* claimed_s = reinterpret_cast<int*>(inv_s + MAXSL * 8);                             // [warps][8]
   uint8_t* rings = reinterpret_cast<uint8_t*>(claimed_s) + 256;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int ks = blockIdx.y;
   const int sl0 = (int)((long long)a.slices * ks / a.ksplit), sl1 = (int)((long long)a.slices * (ks + 1) / a.ksplit), nsl = sl1 - sl0;
-  griddep_wait();
-  {                                                                 // B fragments (and group sums) of this K range → shared memory
-    const uint4* src = reinterpret_cast<const uint4*>(a.xb) + (size_t)sl0 * F.planes * 256;
-    for (int i = threadIdx.x; i < nsl * F.planes * 256; i += blockDim.x) xb_s[i] = __ldg(src + i);
-    if (FMT != HB_FMT_NVFP4) {
-      const float4* ss = reinterpret_cast<const float4*>(a.sums) + (size_t)sl0 * 16;
-      for (int i = threadIdx.x; i < nsl * 16; i += blockDim.x) sums_s[i] = __ldg(ss + i);
-    }
-  }
-  __syncthreads();
-  griddep_launch();
   const int strips_per_mat = (a.N + 15) / 16, n_strips = strips_per_mat * a.n_mats;
   uint8_t* ring = rings + (size_t)warp * NST * STG;
   int* claimed = claimed_s + warp * 8;
   const int K = a.K;
+  // every warp of the split claims until it draws a number ≥ n_strips, so the launch makes exactly n_strips + (warps of the
+  // split) claims; the one that draws the last number puts the counter back to zero for the next launch
+  const int last_claim = n_strips + (int)gridDim.x * kDWarps - 1;
   auto claim = [&]() -> int {
     int v = 0;
-    if (lane == 0) v = atomicAdd(&a.counters[ks], 1);
+    if (lane == 0) { v = atomicAdd(&a.counters[ks], 1); if (v == last_claim) atomicExch(&a.counters[ks], 0); }
     return __shfl_sync(0xffffffffu, v, 0);
   };
   auto issue = [&](int strip, int sl, int stage) {                  // slice sl (absolute) of a strip → ring stage
@@ -232,8 +200,16 @@ __global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseAr
     }
     cp_async_commit();                                              // always commit: the group count stays in step with the slice count
   };
-  for (int i = 0; i < NST - 1; ++i) issue_next();
-  __syncwarp();
+  for (int i = 0; i < NST - 1; ++i) issue_next();                  // weights do not depend on the previous kernel: fetch before waiting for it
+  griddep_wait();
+  for (int it = warp; it < nsl * 8; it += kDWarps) {                // B fragments of this K range, one warp per (slice, row)
+    const int bs = it >> 3, tok = it & 7;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (tok < a.M) v = __ldcg(reinterpret_cast<const uint4*>(a.x + (size_t)tok * a.ldx + (size_t)(sl0 + bs) * kDSlice) + lane);
+    dense_build_row_slice<FMT>(v, bs, tok, lane, xb_s, sums_s, inv_s);
+  }
+  __syncthreads();
+  griddep_launch();
   int co = 0, cs = 0, cstage = 0;
   float total[4] = {0.f, 0.f, 0.f, 0.f};
   for (;;) {
@@ -244,6 +220,7 @@ __global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseAr
     __syncwarp();
     const uint8_t* st = ring + (size_t)cstage * STG;
     const uint4* xb_i = xb_s + (size_t)cs * F.planes * 256;
+    const float2 iv = *reinterpret_cast<const float2*>(inv_s + cs * 8 + 2 * t);           // undo the slice factor of rows 2t, 2t+1
     if (FMT == HB_FMT_NVFP4) {
       uint32_t b[32];
 #pragma unroll
@@ -252,11 +229,12 @@ __global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseAr
       warp_slice_mma(st + g * F.pitch_w + 32 * t, st + (g + 8) * F.pitch_w + 32 * t, st + 16 * F.pitch_w + g * 16 + 4 * t,
                      st + 16 * F.pitch_w + (g + 8) * 16 + 4 * t, b, acc, nullptr);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) total[c] += acc[c];
+      for (int c = 0; c < 4; ++c) total[c] = fmaf(acc[c], (c & 1) ? iv.y : iv.x, total[c]);
     } else {
       const uint8_t* sz = st + 16 * (F.pitch_w + F.pitch_h);
       const uint4 szA = *reinterpret_cast<const uint4*>(sz + g * 16), szB = *reinterpret_cast<const uint4*>(sz + (g + 8) * 16);
       const uint32_t szAw[4] = {szA.x, szA.y, szA.z, szA.w}, szBw[4] = {szB.x, szB.y, szB.z, szB.w};   // {s01, s23, zp01, zp23} as f16 pairs
+      float sub[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int gq = 0; gq < 4; ++gq) {
         float tmp[4] = {0.f, 0.f, 0.f, 0.f};
@@ -290,16 +268,18 @@ __global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseAr
           for (int m4 = 0; m4 < 4; ++m4) { const uint32_t afr[4] = {pA[2 * m4], pB[2 * m4], pA[2 * m4 + 1], pB[2 * m4 + 1]}; mma_f16_16816(tmp, afr, b[2 * m4], b[2 * m4 + 1]); }
         }
         // scale and zero-point in fp32: y += s·(tile − zp·S0 − S1)
-        const float4 su = sums_s[(size_t)cs * 16 + gq * 4 + t];     // (S0, S1) of rows 2t, 2t+1
+        const float4 su = *reinterpret_cast<const float4*>(sums_s + (size_t)cs * 32 + gq * 8 + 2 * t);   // (S0, S1) of rows 2t, 2t+1
         const __half2 sA2 = *reinterpret_cast<const __half2*>(&szAw[gq >> 1]), zA2 = *reinterpret_cast<const __half2*>(&szAw[2 + (gq >> 1)]);
         const __half2 sB2 = *reinterpret_cast<const __half2*>(&szBw[gq >> 1]), zB2 = *reinterpret_cast<const __half2*>(&szBw[2 + (gq >> 1)]);
         const float sA = (gq & 1) ? __high2float(sA2) : __low2float(sA2), zA = (gq & 1) ? __high2float(zA2) : __low2float(zA2);
         const float sB = (gq & 1) ? __high2float(sB2) : __low2float(sB2), zB = (gq & 1) ? __high2float(zB2) : __low2float(zB2);
-        total[0] = fmaf(sA, tmp[0] - fmaf(zA, su.x, su.y), total[0]);
-        total[1] = fmaf(sA, tmp[1] - fmaf(zA, su.z, su.w), total[1]);
-        total[2] = fmaf(sB, tmp[2] - fmaf(zB, su.x, su.y), total[2]);
-        total[3] = fmaf(sB, tmp[3] - fmaf(zB, su.z, su.w), total[3]);
+        sub[0] = fmaf(sA, tmp[0] - fmaf(zA, su.x, su.y), sub[0]);
+        sub[1] = fmaf(sA, tmp[1] - fmaf(zA, su.z, su.w), sub[1]);
+        sub[2] = fmaf(sB, tmp[2] - fmaf(zB, su.x, su.y), sub[2]);
+        sub[3] = fmaf(sB, tmp[3] - fmaf(zB, su.z, su.w), sub[3]);
       }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) total[c] = fmaf(sub[c], (c & 1) ? iv.y : iv.x, total[c]);
     }
     __syncwarp();
     if (++cstage == NST) cstage = 0;
@@ -310,7 +290,7 @@ __global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseAr
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int tok = 2 * t + (c & 1), n = n0 + g + (c >> 1) * 8;
-        if (tok < a.M && n < a.N) part[(size_t)tok * a.N + n] = total[c] * dense_inv(a.amax[tok]) * gsc;
+        if (tok < a.M && n < a.N) part[(size_t)tok * a.N + n] = total[c] * gsc;
         total[c] = 0.f;
       }
       cs = 0; ++co;
@@ -323,6 +303,7 @@ __global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseAr
 // mode 0: y fp32; 1: y bf16; 2: act = bf16( bf16(silu(bf16 g)) · bf16 u ) from the two matrices' sums
 __global__ void dense_reduce_kernel(const float* __restrict__ part, int n_mats, int ksplit, int M, int N, int mode, void* __restrict__ y, int ldy) {
   griddep_wait();
+  griddep_launch();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)M * N) return;
   const int m = (int)(i / N), n = (int)(i % N);
@@ -357,7 +338,7 @@ namespace {
 int dense_ksplit(int fmt, int K) { const int sl = K / kDSlice, mx = dense_max_slices(fmt); return (sl + mx - 1) / mx; }
 size_t dense_smem(int fmt) {
   const DenseFmt F = dense_fmt(fmt);
-  return (size_t)dense_max_slices(fmt) * F.planes * 4096 + (size_t)dense_max_slices(fmt) * 256 + 256 + (size_t)kDWarps * dense_stages(fmt) * dense_stage_bytes(fmt);
+  return (size_t)dense_max_slices(fmt) * F.planes * 4096 + (size_t)dense_max_slices(fmt) * 256 + (size_t)dense_max_slices(fmt) * 32 + 256 + (size_t)kDWarps * dense_stages(fmt) * dense_stage_bytes(fmt);
 }
 int check_mat(hb_ctx* ctx, const hb_qmat* W, const char* fn) {
   HB_REQUIRE(ctx, W && W->w && W->s, HB_ERR_INVALID, "%s: NULL matrix", fn);
@@ -375,21 +356,15 @@ DenseMat to_mat(const hb_qmat* W) {
   m.wh = W->fmt == HB_FMT_LB3_G64 ? W->w + (size_t)W->N * (W->K / 4) : nullptr;
   return m;
 }
-// one pass of ≤ 8 rows: prep → stream → reduce
+// one pass of ≤ 8 rows: stream → reduce
 int dense_pass(hb_ctx* ctx, const hb_qmat* A, const hb_qmat* B2, const void* x, int ldx, int M, int mode, void* y, int ldy, void* ws, cudaStream_t st) {
-  const int fmt = A->fmt, N = A->N, K = A->K, slices = K / kDSlice, planes = dense_fmt(fmt).planes, ksplit = dense_ksplit(fmt, K), mats = B2 ? 2 : 1;
-  DenseWs w = dense_carve(ws, slices, planes, mats, ksplit, N);
-  const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
-  int* counters = reinterpret_cast<int*>(w.amax + 8);
-  cudaError_t e = cudaMemsetAsync(w.amax, 0, 32, st);
-  if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "memset amax: %s", cudaGetErrorString(e));
-  int r = hb_launch(ctx, "dense_amax", false, dense_amax_kernel, dim3(8, 16), dim3(256), 0, st, xb, ldx, M, K, w.amax, counters, ksplit);
-  if (r) return r;
-  if ((r = hb_launch(ctx, "dense_prep", true, dense_prep_kernel, dim3(slices), dim3(256), 0, st, fmt, xb, ldx, M, (const unsigned int*)w.amax, w.xb, w.sums))) return r;
+  const int fmt = A->fmt, N = A->N, K = A->K, slices = K / kDSlice, ksplit = dense_ksplit(fmt, K), mats = B2 ? 2 : 1;
+  float* part = reinterpret_cast<float*>(ws);
   DenseArgs a{};
   a.mat[0] = to_mat(A); if (B2) a.mat[1] = to_mat(B2);
-  a.n_mats = mats; a.N = N; a.K = K; a.M = M; a.ksplit = ksplit; a.slices = slices;
-  a.xb = w.xb; a.sums = w.sums; a.amax = w.amax; a.counters = counters; a.part = w.part;
+  a.n_mats = mats; a.N = N; a.K = K; a.M = M; a.ksplit = ksplit; a.slices = slices; a.ldx = ldx;
+  a.x = reinterpret_cast<const __nv_bfloat16*>(x); a.counters = reinterpret_cast<int*>(ctx->dev_err) + kDCounterWord; a.part = part;
+  int r;
   int per_split = (2 * ctx->sm_count) / ksplit;                    // two CTAs per SM in all, shared out over the K splits
   const int strips = ((N + 15) / 16) * mats, max_useful = (strips + kDWarps - 1) / kDWarps;
   if (per_split < 1) per_split = 1;
@@ -398,7 +373,7 @@ int dense_pass(hb_ctx* ctx, const hb_qmat* A, const hb_qmat* B2, const void* x, 
   auto fn = fmt == HB_FMT_NVFP4 ? dense_stream_kernel<HB_FMT_NVFP4> : fmt == HB_FMT_LB2_G64 ? dense_stream_kernel<HB_FMT_LB2_G64> : dense_stream_kernel<HB_FMT_LB3_G64>;
   if ((r = hb_launch(ctx, fmt == HB_FMT_NVFP4 ? "dense_stream_nvfp4" : fmt == HB_FMT_LB2_G64 ? "dense_stream_lb2" : "dense_stream_lb3", true, fn, grid,
                      dim3(kDWarps * 32), dense_smem(fmt), st, a))) return r;
-  return hb_launch(ctx, "dense_reduce", true, dense_reduce_kernel, dim3((unsigned)(((size_t)M * N + 255) / 256)), dim3(256), 0, st, (const float*)w.part, mats,
+  return hb_launch(ctx, "dense_reduce", true, dense_reduce_kernel, dim3((unsigned)(((size_t)M * N + 255) / 256)), dim3(256), 0, st, (const float*)part, mats,
                    ksplit, M, N, mode, y, ldy);
 }
 }  // namespace
@@ -414,8 +389,7 @@ extern "C" {
 
 size_t hb_dense_gemv_ws_bytes(int fmt, int N, int K, int n_mats) {
   if (K <= 0 || N <= 0 || K % kDSlice || n_mats < 1 || n_mats > 2) return 0;
-  const int slices = K / kDSlice;
-  return al256((size_t)slices * dense_fmt(fmt).planes * 4096) + al256((size_t)slices * 256) + 256 + al256((size_t)n_mats * dense_ksplit(fmt, K) * 8 * N * 4);
+  return al256((size_t)n_mats * dense_ksplit(fmt, K) * 8 * N * 4);
 }
 
 int hb_dense_gemv(hb_ctx* ctx, const hb_qmat* W, const void* x, int ldx, int M, void* yb, float* yf, int ldy, void* ws, void* stream) {
@@ -423,6 +397,7 @@ int hb_dense_gemv(hb_ctx* ctx, const hb_qmat* W, const void* x, int ldx, int M, 
   int r = check_mat(ctx, W, "dense_gemv");
   if (r) return r;
   HB_REQUIRE(ctx, x && ((yb != nullptr) != (yf != nullptr)), HB_ERR_INVALID, "dense_gemv: x NULL, or not exactly one of yb / yf given");
+  HB_REQUIRE(ctx, hb_aligned(x, 16) && ldx % 8 == 0, HB_ERR_INVALID, "dense_gemv: x must be 16-byte aligned with ldx a multiple of 8");
   HB_REQUIRE(ctx, M >= 1 && M <= 16 && ldx >= W->K && ldy >= W->N, HB_ERR_UNSUPPORTED, "dense_gemv: M=%d (1..16) ldx=%d ldy=%d", M, ldx, ldy);
   HB_REQUIRE(ctx, ws && hb_aligned(ws, 256), HB_ERR_WORKSPACE, "dense_gemv: ws NULL or not 256-byte aligned");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -441,6 +416,7 @@ int hb_dense_gemv_gu(hb_ctx* ctx, const hb_qmat* G, const hb_qmat* U, const void
   if (!r) r = check_mat(ctx, U, "dense_gemv_gu");
   if (r) return r;
   HB_REQUIRE(ctx, G->fmt == U->fmt && G->N == U->N && G->K == U->K, HB_ERR_INVALID, "dense_gemv_gu: gate and up must share format and shape");
+  HB_REQUIRE(ctx, x && hb_aligned(x, 16) && ldx % 8 == 0, HB_ERR_INVALID, "dense_gemv_gu: x must be 16-byte aligned with ldx a multiple of 8");
   HB_REQUIRE(ctx, x && act && M >= 1 && M <= 16 && ldx >= G->K && lda >= G->N, HB_ERR_UNSUPPORTED, "dense_gemv_gu: M=%d (1..16) ldx=%d lda=%d", M, ldx, lda);
   HB_REQUIRE(ctx, ws && hb_aligned(ws, 256), HB_ERR_WORKSPACE, "dense_gemv_gu: ws NULL or not 256-byte aligned");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
