@@ -96,6 +96,11 @@ def load() -> C.CDLL:
         "hb_dense_gemv": (i, [vp, C.POINTER(QMat), vp, i, i, vp, vp, i, vp, vp]),
         "hb_dense_gemv_gu": (i, [vp, C.POINTER(QMat), C.POINTER(QMat), vp, i, i, vp, i, vp, vp]),
         "hb_lb_dequant": (i, [vp, C.POINTER(QMat), vp, vp]),
+        "hb_moe_prefill_supported": (i, [i, i]),
+        "hb_moe_prefill_ws_bytes": (sz, [i, i, i, i, i]),
+        "hb_moe_prefill": (i, [vp, vp, i, i, vp, vp, i, i, vp, i, i, f, vp, vp, i, vp, C.POINTER(PfCombine)]),
+        "hb_nvfp4_gemm_a4": (i, [vp, C.POINTER(QMat), vp, vp, vp, i, vp, i, vp]),
+        "hb_fp4_peak_probe": (i, [vp, i, C.POINTER(f)]),
         "hb_gather_rows": (i, [vp, vp, vp, i, i, vp, vp]),
         "hb_swiglu_rows": (i, [vp, vp, i, i, f, vp, vp]),
         "hb_scatter_add_rows": (i, [vp, vp, vp, vp, i, i, vp, vp]),

@@ -35,6 +35,7 @@ int hb_create(const hb_config* cfg, hb_ctx** out) {
   if (cudaMalloc(&c->dev_err, 256) != cudaSuccess || cudaMemset(c->dev_err, 0, 256) != cudaSuccess) { delete c; cudaGetLastError(); return HB_ERR_CUDA; }
   int r = hbk_moe_decode_setup(c);
   if (r == HB_OK) r = hbk_dense_setup(c);
+  if (r == HB_OK) r = hbk_moe_prefill_setup(c);
   if (r != HB_OK) { cudaFree(c->dev_err); delete c; return r; }
   *out = c;
   return HB_OK;

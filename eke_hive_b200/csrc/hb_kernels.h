@@ -57,3 +57,4 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
 
 // dense GEMV (k_dense.cu)
 int hbk_dense_setup(hb_ctx* ctx);
+int hbk_moe_prefill_setup(hb_ctx* ctx);

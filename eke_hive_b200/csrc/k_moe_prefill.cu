@@ -1,0 +1,551 @@
+// Routed-expert prefill (rows > 64): one grouped W4A4 GEMM pass over every expert that received rows, on the 5th-generation tensor
+// cores.  Mirrors hive::qwen::fn_moe_prefill with its NVFP4-activation switch on (engine/src/qwen/fn_moe_pf.cu:439-446, :858-941):
+//
+//   count / scan / fill   the (row, k) pairs sorted by expert (the order inside an expert is irrelevant: a pair's result depends only
+//                         on its own row) and a list of 128-pair tiles
+//   quantise x            per-row dynamic NVFP4 (hb_a4_quant's rule)
+//   gate|up GEMM          tile = 128 pairs × (128 gate + 128 up rows of I); block-scaled FP4 MMA, fp32 accumulators in tensor memory;
+//                         epilogue g = bf16(acc·gx·g1), u = bf16(acc·gx·g3), y = bf16(silu(g)·u)
+//   quantise y            per pair
+//   down GEMM             tile = 128 pairs × 256 rows of H; part[pair] = bf16(acc·(gy·g2))
+//   reduce                out[row] = Σ_k part·w in k order (or the fused shared-expert combine)
+//
+// GEMM kernel: persistent CTAs of 9 warps.  Warps 5-8 gather the operands: 16-byte cp.async copies written straight into the
+// 128-byte-swizzled K-major layout the MMA reads (pair rows come from anywhere in the activation buffer and expert records sit at
+// arbitrary addresses, so the gather is done by address, not by tensor map), and the e4m3 block scales as 4-byte copies into the
+// 32×16-byte chunks `tcgen05.cp` moves to tensor memory.  Warp 4 issues `tcgen05.cp` + `tcgen05.mma kind::mxf4nvf4` (block 16,
+// ue4m3 scales: both operands' block scales are applied by the tensor core) and commits to the stage's mbarrier.  Warps 0-3 read
+// the accumulators back with `tcgen05.ld` and run the epilogue.  Every wait is bounded; on a timeout the kernel records a site
+// code in the context's error word, drains its copies, frees its tensor memory and returns.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "hb_common.cuh"
+#include "hb_kernels.h"
+
+namespace hb {
+
+constexpr int PF_BM = 128;              // pairs per tile (MMA M)
+constexpr int PF_BN = 256;              // weight rows per tile (MMA N)
+constexpr int PF_BK = 256;              // k values per stage = one 128-byte swizzle row of e2m1 codes
+constexpr int PF_ST = 4;                // stages
+constexpr int PF_LAG = 2;               // loader threads publish a stage this many iterations after issuing it
+constexpr int PF_A_BYTES = PF_BM * 128, PF_B_BYTES = PF_BN * 128;
+constexpr int PF_SFA_BYTES = 4 * 512;   // 4 MMA k-steps × one 128-row chunk
+constexpr int PF_SFB_BYTES = 8 * 512;   // 4 k-steps × two 128-row chunks
+constexpr int PF_STAGE = PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + PF_SFB_BYTES;
+constexpr int PF_SMEM = PF_ST * PF_STAGE + 1024 + 256;
+constexpr int PF_THREADS = 9 * 32;
+constexpr int PF_TMEM_COLS = 512;
+constexpr int PF_SF_COL0 = 256;         // accumulator: columns [0, 256); scales of stage s: [256 + 48 s, 256 + 48 s + 48)
+static_assert(PF_STAGE % 1024 == 0, "stage buffers must keep the 1024-byte alignment of the swizzle atom");
+static_assert(PF_SMEM <= 227 * 1024, "shared memory");
+
+struct PfTile { int e, slot0, m; };
+
+enum { PF_PLAIN = 0, PF_GU = 1, PF_DOWN = 2 };
+
+struct PfGemmArgs {
+  // work list
+  const PfTile* tiles; const int* n_tiles;     // n_tiles == nullptr: one implicit tile list of ceil(M / 128) tiles over rows [0, M)
+  int M;                                       // PLAIN only
+  const int* perm; int K_top;                  // pair of a sorted slot; GU reads activation row perm[slot] / K_top
+  // A operand (quantised activations)
+  const uint8_t* aq; const uint8_t* as; const float* ag; int Kd;   // codes [rows, Kd/2], scales [rows, Kd/16], per-row global
+  // B operand
+  const uint8_t* const* tab; hb_rec_layout L;  // GU / DOWN: expert records
+  const uint8_t* bw; const uint8_t* bs; float bg;   // PLAIN: one matrix [N, Kd]
+  int N;                                       // output columns in all (I for GU, H for DOWN, N for PLAIN)
+  float limit;
+  void* out; int ldo;                          // GU: y bf16 [slots, I]; DOWN: part bf16 [pairs, H]; PLAIN: fp32 [M, ldo]
+  uint32_t* err;
+};
+
+// ---- tcgen05 wrappers -------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 rows × 16 bytes of shared memory → 4 columns of tensor memory, the same data in all four 32-lane quarters
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
+      "%23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+        "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+        "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void pf_cp16(uint32_t dst, const void* src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
+__device__ __forceinline__ void pf_cp4(uint32_t dst, const void* src) { asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory"); }
+__device__ __forceinline__ void pf_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N_>
+__device__ __forceinline__ void pf_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N_) : "memory"); }
+
+// Shared-memory matrix descriptor, K-major operand rows of 128 bytes under the 128-byte swizzle: 8-row groups 1024 bytes apart
+// (stride field), leading-dimension field 1 (not used by swizzled K-major operands), descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t pf_desc_sw128(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Descriptor of one 32-row × 16-byte scale chunk: no swizzle, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t pf_desc_sf(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | (1ull << 46);
+}
+// Instruction descriptor, kind::mxf4nvf4: A and B e2m1 (format 1, bits 7-9 and 10-12), both K-major, N / 8 at bit 17, ue4m3 scales
+// (bit 23 = 0), M / 16 at bit 24, K = 64 per instruction (bit 31 = 0).
+constexpr uint32_t PF_IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(PF_BN >> 3) << 17) | ((uint32_t)(PF_BM >> 4) << 24);
+
+// ---- the grouped GEMM ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ PfTile pf_tile(const PfGemmArgs& a, int ti) {
+  if (a.tiles) return a.tiles[ti];
+  PfTile t; t.e = 0; t.slot0 = ti * PF_BM; t.m = min(PF_BM, a.M - ti * PF_BM);
+  return t;
+}
+__device__ __forceinline__ uint4 pf_pack8(const float* v) {
+  const __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
+  const __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
+  return make_uint4(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1), *reinterpret_cast<const uint32_t*>(&p2),
+                    *reinterpret_cast<const uint32_t*>(&p3));
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(PfGemmArgs a) {
+  extern __shared__ uint8_t pf_raw[];
+  const uint32_t raw = smem_u32(pf_raw), base = (raw + 1023u) & ~1023u;     // swizzle atoms want 1024-byte alignment
+  uint8_t* sm = pf_raw + (base - raw);
+  uint64_t* full = reinterpret_cast<uint64_t*>(sm + PF_ST * PF_STAGE);       // [ST] operands of the stage have landed
+  uint64_t* empty = full + PF_ST;                                            // [ST] the MMAs that read the stage are done
+  uint64_t* acc_full = empty + PF_ST;                                        // the tile's accumulators are complete
+  uint64_t* acc_empty = acc_full + 1;                                        // the epilogue has read them
+  uint64_t* mma_done = acc_empty + 1;                                        // the issuing thread's last operation has retired
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mma_done + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PF_ST; ++s) { mbar_init(&full[s], 128); mbar_init(&empty[s], 1); }
+    mbar_init(acc_full, 1); mbar_init(acc_empty, 128); mbar_init(mma_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 4) { tmem_alloc(tmem_slot, PF_TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  griddep_wait();
+  griddep_launch();
+  const int n_tiles = a.tiles ? *a.n_tiles : (a.M + PF_BM - 1) / PF_BM;
+  constexpr int NW = MODE == PF_GU ? 128 : 256;                              // output columns per tile
+  const int n_nt = a.N / NW, nkb = a.Kd / PF_BK;
+  const long long work = (long long)n_tiles * n_nt;                          // tile-major: the CTAs of a wave share activation tiles and expert rows in L2
+  const size_t rowb = (size_t)a.Kd / 2, rows = (size_t)a.Kd / 16;
+
+  if (warp >= 5) {
+    // ------------------------------------------------------------------------------------------------ loaders: thread lt owns A row lt, B rows lt and lt + 128
+    const int lt = threadIdx.x - 160;
+    const uint32_t sw = (uint32_t)((lt >> 3) * 1024 + (lt & 7) * 128), x7 = (uint32_t)(lt & 7);
+    const uint32_t sfo = (uint32_t)((lt & 31) * 16 + (lt >> 5) * 4);
+    uint32_t it = 0;
+    bool ok = true;
+    for (long long w = blockIdx.x; w < work && ok; w += gridDim.x) {
+      const int ti = (int)(w / n_nt), nt = (int)(w - (long long)ti * n_nt);
+      const PfTile tl = pf_tile(a, ti);
+      const int slot = tl.slot0 + min(lt, tl.m - 1);                         // rows past the tile's end repeat its last row (never stored)
+      const size_t arow = MODE == PF_GU ? (size_t)(a.perm[slot] / a.K_top) : (size_t)slot;
+      const uint8_t* ap = a.aq + arow * rowb;
+      const uint8_t* asp = a.as + arow * rows;
+      const uint8_t *b0, *b1, *s0, *s1;
+      if (MODE == PF_PLAIN) {
+        b0 = a.bw + (size_t)(nt * 256 + lt) * rowb; b1 = b0 + 128 * rowb;
+        s0 = a.bs + (size_t)(nt * 256 + lt) * rows; s1 = s0 + 128 * rows;
+      } else {
+        const uint8_t* rec = a.tab[tl.e];
+        if (MODE == PF_GU) {
+          b0 = rec + a.L.w1 + (size_t)(nt * 128 + lt) * rowb; b1 = rec + a.L.w3 + (size_t)(nt * 128 + lt) * rowb;
+          s0 = rec + a.L.s1 + (size_t)(nt * 128 + lt) * rows; s1 = rec + a.L.s3 + (size_t)(nt * 128 + lt) * rows;
+        } else {
+          b0 = rec + a.L.w2 + (size_t)(nt * 256 + lt) * rowb; b1 = b0 + 128 * rowb;
+          s0 = rec + a.L.s2 + (size_t)(nt * 256 + lt) * rows; s1 = s0 + 128 * rows;
+        }
+      }
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const uint32_t stage = it % PF_ST;
+        if (!(ok = mbar_wait(&empty[stage], ((it / PF_ST) & 1) ^ 1, a.err, 0x100u))) break;
+        const uint32_t sb = base + stage * PF_STAGE;
+#pragma unroll
+        for (uint32_t c = 0; c < 8; ++c) {
+          const uint32_t o = sw + ((c ^ x7) << 4);
+          pf_cp16(sb + o, ap + (size_t)kb * 128 + c * 16);
+          pf_cp16(sb + PF_A_BYTES + o, b0 + (size_t)kb * 128 + c * 16);
+          pf_cp16(sb + PF_A_BYTES + 128 * 128 + o, b1 + (size_t)kb * 128 + c * 16);
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {                                   // the row's 16 scales of this stage: 4 per MMA k-step
+          pf_cp4(sb + PF_A_BYTES + PF_B_BYTES + j * 512 + sfo, asp + (size_t)kb * 16 + j * 4);
+          pf_cp4(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + (2 * j) * 512 + sfo, s0 + (size_t)kb * 16 + j * 4);
+          pf_cp4(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + (2 * j + 1) * 512 + sfo, s1 + (size_t)kb * 16 + j * 4);
+        }
+        pf_cp_commit();
+        if (it >= PF_LAG) {                                                  // the copies issued LAG iterations ago have landed: publish them
+          pf_cp_wait<PF_LAG>();
+          fence_proxy_async_smem();
+          mbar_arrive(&full[(it - PF_LAG) % PF_ST]);
+        }
+      }
+    }
+    pf_cp_wait<0>();
+    fence_proxy_async_smem();
+    for (uint32_t j = it >= PF_LAG ? it - PF_LAG : 0; j < it; ++j) mbar_arrive(&full[j % PF_ST]);
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------------------------------------ MMA issue: one thread
+    if (lane == 0) {
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (long long w = blockIdx.x; w < work && ok; w += gridDim.x, ++tcount) {
+        if (tcount > 0 && !(ok = mbar_wait(acc_empty, (tcount - 1) & 1, a.err, 0x200u))) break;
+        tc_fence_after();
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const uint32_t stage = it % PF_ST;
+          if (!(ok = mbar_wait(&full[stage], (it / PF_ST) & 1, a.err, 0x400u))) break;
+          tc_fence_after();
+          const uint32_t sb = base + stage * PF_STAGE, sfc = tmem + PF_SF_COL0 + stage * 48;
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {
+            tc_cp_sf(sfc + 4 * j, pf_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + j * 512));
+            tc_cp_sf(sfc + 16 + 8 * j, pf_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + (2 * j) * 512));
+            tc_cp_sf(sfc + 16 + 8 * j + 4, pf_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + (2 * j + 1) * 512));
+          }
+          const uint64_t ad = pf_desc_sw128(sb), bd = pf_desc_sw128(sb + PF_A_BYTES);
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j)                                   // 64 k values = 32 bytes further along the swizzled row
+            tc_mma_nvf4(tmem, ad + 2 * j, bd + 2 * j, PF_IDESC, sfc + 4 * j, sfc + 16 + 8 * j, (kb | (int)j) != 0 ? 1u : 0u);
+          tc_commit(&empty[stage]);
+        }
+        if (ok) tc_commit(acc_full);
+      }
+      tc_commit(mma_done);                                                   // nothing of this thread's is in flight when tensor memory is freed
+      mbar_wait(mma_done, 0, a.err, 0x800u);
+    }
+  } else {
+    // ------------------------------------------------------------------------------------------------ epilogue: warp q reads lanes [32q, 32q + 32)
+    const int m = warp * 32 + lane;
+    const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (long long w = blockIdx.x; w < work && ok; w += gridDim.x, ++tcount) {
+      const int ti = (int)(w / n_nt), nt = (int)(w - (long long)ti * n_nt);
+      const PfTile tl = pf_tile(a, ti);
+      const bool valid = m < tl.m;
+      const int slot = tl.slot0 + min(m, tl.m - 1);
+      float f0 = 0.f, f1 = 0.f, f2 = 0.f;
+      size_t orow = 0;
+      if (MODE == PF_PLAIN) { f0 = a.ag[slot] * a.bg; orow = (size_t)slot; }
+      else {
+        const float* g = reinterpret_cast<const float*>(a.tab[tl.e] + a.L.g);
+        if (MODE == PF_GU) { f0 = a.ag[a.perm[slot] / a.K_top]; f1 = g[0]; f2 = g[1]; orow = (size_t)slot; }
+        else { f0 = a.ag[slot] * g[2]; orow = (size_t)a.perm[slot]; }
+      }
+      if (!(ok = mbar_wait(acc_full, tcount & 1, a.err, 0x1000u))) break;
+      tc_fence_after();
+      if (MODE == PF_GU) {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + orow * a.ldo + (size_t)nt * 128;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t rg[32], ru[32];
+          tc_ld32(trow + 32 * c, rg);
+          tc_ld32(trow + 128 + 32 * c, ru);
+          tc_wait_ld();
+          float y[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float gv = bf16r(__uint_as_float(rg[i]) * f0 * f1), uv = bf16r(__uint_as_float(ru[i]) * f0 * f2);
+            if (a.limit > 0.f) { gv = fminf(gv, a.limit); uv = fminf(fmaxf(uv, -a.limit), a.limit); }
+            y[i] = gv / (1.f + __expf(-gv)) * uv;
+          }
+          if (valid) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(o + 32 * c + 8 * q) = pf_pack8(y + 8 * q);
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t r[32];
+          tc_ld32(trow + 32 * c, r);
+          tc_wait_ld();
+          if (MODE == PF_DOWN) {
+            float y[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) y[i] = __uint_as_float(r[i]) * f0;
+            if (valid) {
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + orow * a.ldo + (size_t)nt * 256 + 32 * c;
+#pragma unroll
+              for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(o + 8 * q) = pf_pack8(y + 8 * q);
+            }
+          } else if (valid) {
+            float* o = reinterpret_cast<float*>(a.out) + orow * a.ldo + (size_t)nt * 256 + 32 * c;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<float4*>(o + 4 * q) = make_float4(__uint_as_float(r[4 * q]) * f0, __uint_as_float(r[4 * q + 1]) * f0,
+                                                                  __uint_as_float(r[4 * q + 2]) * f0, __uint_as_float(r[4 * q + 3]) * f0);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(acc_empty);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) { tc_fence_after(); tmem_dealloc(tmem, PF_TMEM_COLS); }
+}
+
+// Tensor-pipe ceiling: the same MMA issued back to back on operands that sit in shared memory (arbitrary bytes), no loads, no epilogue.
+__global__ void __launch_bounds__(128, 1) pf_peak_kernel(int n_rounds, uint32_t* err) {
+  extern __shared__ uint8_t pf_raw[];
+  const uint32_t raw = smem_u32(pf_raw), base = (raw + 1023u) & ~1023u;
+  uint8_t* sm = pf_raw + (base - raw);
+  uint64_t* bar = reinterpret_cast<uint64_t*>(sm + PF_STAGE);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+  const int warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < PF_STAGE / 4; i += blockDim.x) {            // e2m1 codes: any bytes; scales: 0x38 = 1.0
+    uint32_t v = (uint32_t)i * 2654435761u + 0x9E3779B9u * (blockIdx.x + 1);
+    reinterpret_cast<uint32_t*>(sm)[i] = i * 4 < PF_A_BYTES + PF_B_BYTES ? v : 0x38383838u;
+  }
+  if (threadIdx.x == 0) { mbar_init(bar, 1); mbar_fence_init(); }
+  fence_proxy_async_smem();
+  if (warp == 0) { tmem_alloc(tmem_slot, PF_TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  if (threadIdx.x == 0) {
+    const uint32_t sfc = tmem + PF_SF_COL0;
+    for (uint32_t j = 0; j < 4; ++j) {
+      tc_cp_sf(sfc + 4 * j, pf_desc_sf(base + PF_A_BYTES + PF_B_BYTES + j * 512));
+      tc_cp_sf(sfc + 16 + 8 * j, pf_desc_sf(base + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + (2 * j) * 512));
+      tc_cp_sf(sfc + 16 + 8 * j + 4, pf_desc_sf(base + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + (2 * j + 1) * 512));
+    }
+    const uint64_t ad = pf_desc_sw128(base), bd = pf_desc_sw128(base + PF_A_BYTES);
+    for (int r = 0; r < n_rounds; ++r)
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j) tc_mma_nvf4(tmem, ad + 2 * j, bd + 2 * j, PF_IDESC, sfc + 4 * j, sfc + 16 + 8 * j, (r | (int)j) != 0 ? 1u : 0u);
+    tc_commit(bar);
+    mbar_wait(bar, 0, err, 0x2000u);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, PF_TMEM_COLS); }
+}
+
+// ---- sort by expert ----------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ bool pf_live(const int32_t* ids, int p, int E, const uint8_t* const* tab, int* e_out) {
+  const int e = ids[p];
+  *e_out = e;
+  return e >= 0 && e < E && tab[e] != nullptr;                               // ids outside [0, E) and absent records contribute nothing
+}
+__global__ void pf_count_kernel(const int32_t* __restrict__ ids, int P, int E, const uint8_t* const* __restrict__ tab, int* __restrict__ cnt) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  int e;
+  if (p < P && pf_live(ids, p, E, tab, &e)) atomicAdd(&cnt[e], 1);
+}
+// one block, E ≤ 1024: exclusive prefix sums of the pair counts (→ fill cursors) and of the tile counts (→ the tile list)
+__global__ void __launch_bounds__(1024) pf_scan_kernel(const int* __restrict__ cnt, int E, int* __restrict__ cursor, PfTile* __restrict__ tiles,
+                                                       int* __restrict__ n_tiles) {
+  __shared__ int wsum_c[32], wsum_t[32];
+  const int e = threadIdx.x, lane = e & 31, wp = e >> 5;
+  const int c = e < E ? cnt[e] : 0, t = (c + PF_BM - 1) / PF_BM;
+  int ic = c, itl = t;                                                       // inclusive scans inside the warp
+  for (int o = 1; o < 32; o <<= 1) {
+    const int uc = __shfl_up_sync(0xffffffffu, ic, o), ut = __shfl_up_sync(0xffffffffu, itl, o);
+    if (lane >= o) { ic += uc; itl += ut; }
+  }
+  if (lane == 31) { wsum_c[wp] = ic; wsum_t[wp] = itl; }
+  __syncthreads();
+  if (wp == 0) {
+    int vc = wsum_c[lane], vt = wsum_t[lane];
+    for (int o = 1; o < 32; o <<= 1) {
+      const int uc = __shfl_up_sync(0xffffffffu, vc, o), ut = __shfl_up_sync(0xffffffffu, vt, o);
+      if (lane >= o) { vc += uc; vt += ut; }
+    }
+    wsum_c[lane] = vc; wsum_t[lane] = vt;
+  }
+  __syncthreads();
+  const int off = ic - c + (wp ? wsum_c[wp - 1] : 0), toff = itl - t + (wp ? wsum_t[wp - 1] : 0);
+  if (e < E) {
+    cursor[e] = off;
+    for (int i = 0; i < t; ++i) { PfTile tl; tl.e = e; tl.slot0 = off + i * PF_BM; tl.m = min(PF_BM, c - i * PF_BM); tiles[toff + i] = tl; }
+  }
+  if (e == 1023) *n_tiles = wsum_t[31];
+}
+__global__ void pf_fill_kernel(const int32_t* __restrict__ ids, int P, int E, const uint8_t* const* __restrict__ tab, int* __restrict__ cursor,
+                               int* __restrict__ perm) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  int e;
+  if (p < P && pf_live(ids, p, E, tab, &e)) perm[atomicAdd(&cursor[e], 1)] = p;
+}
+
+// ---- reduce --------------------------------------------------------------------------------------------------------------------------
+// out[row] = Σ_k part[row·K + k]·w[row, k], fp32 in k order, overwritten — or the shared-expert combine on top of it:
+// out = bf16(bf16(Σ) + bf16(bf16(sigmoid(bf16 gate logit))·shared)); lg == NULL: no gate
+__global__ void pf_reduce_kernel(const __nv_bfloat16* __restrict__ part, const int32_t* __restrict__ ids, const float* __restrict__ w, int M, int K, int E,
+                                 const uint8_t* const* __restrict__ tab, int H, float* __restrict__ out, const __nv_bfloat16* __restrict__ shared,
+                                 const float* __restrict__ lg, int ld, int col, __nv_bfloat16* __restrict__ cout) {
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (i >= (size_t)M * H) return;
+  const int m = (int)(i / H), n = (int)(i % H);
+  float a0 = 0.f, a1 = 0.f;
+  for (int k = 0; k < K; ++k) {
+    const int p = m * K + k;
+    int e;
+    if (!pf_live(ids, p, E, tab, &e)) continue;
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(part + (size_t)p * H + n));
+    const float wv = w[p];
+    a0 += v.x * wv; a1 += v.y * wv;
+  }
+  if (!cout) { *reinterpret_cast<float2*>(out + i) = make_float2(a0, a1); return; }
+  float g = 1.f;
+  if (lg) g = bf16r(1.f / (1.f + expf(-bf16r(lg[(size_t)m * ld + col]))));
+  const float2 sh = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(shared + i));
+  *reinterpret_cast<__nv_bfloat162*>(cout + i) = __halves2bfloat162(__float2bfloat16(bf16r(a0) + bf16r(g * sh.x)), __float2bfloat16(bf16r(a1) + bf16r(g * sh.y)));
+}
+
+}  // namespace hb
+
+using namespace hb;
+
+namespace {
+struct PfWs { int* cnt; int* cursor; int* n_tiles; PfTile* tiles; int* perm; __nv_bfloat16* y; __nv_bfloat16* part; uint8_t *xq, *xs, *yq, *ys; float *xg, *yg; };
+size_t pf_carve(void* ws, int S, int K, int E, int H, int I, PfWs* w) {
+  size_t off = 0;
+  auto take = [&](size_t b) { void* r = ws ? static_cast<char*>(ws) + off : nullptr; off += hb_align256(b); return r; };
+  const size_t P = (size_t)S * K;
+  PfWs t;
+  t.cnt = (int*)take((size_t)E * 4); t.cursor = (int*)take((size_t)E * 4); t.n_tiles = (int*)take(4);
+  t.tiles = (PfTile*)take((P / PF_BM + E) * sizeof(PfTile)); t.perm = (int*)take(P * 4);
+  t.y = (__nv_bfloat16*)take(P * I * 2); t.part = (__nv_bfloat16*)take(P * H * 2);
+  t.xq = (uint8_t*)take((size_t)S * H / 2); t.xs = (uint8_t*)take((size_t)S * H / 16); t.xg = (float*)take((size_t)S * 4);
+  t.yq = (uint8_t*)take(P * I / 2); t.ys = (uint8_t*)take(P * I / 16); t.yg = (float*)take(P * 4);
+  if (w) *w = t;
+  return off;
+}
+template <int MODE>
+int pf_launch(hb_ctx* ctx, const char* name, const PfGemmArgs& a, cudaStream_t st) {
+  const int grid = ctx->max_ctas > 0 && ctx->max_ctas < ctx->sm_count ? ctx->max_ctas : ctx->sm_count;
+  return hb_launch(ctx, name, false, pf_gemm_kernel<MODE>, dim3(grid), dim3(PF_THREADS), (size_t)PF_SMEM, st, a);
+}
+}  // namespace
+
+int hbk_moe_prefill_setup(hb_ctx* ctx) {
+  HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(pf_gemm_kernel<PF_PLAIN>), cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
+  HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(pf_gemm_kernel<PF_GU>), cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
+  HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(pf_gemm_kernel<PF_DOWN>), cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
+  HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(pf_peak_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, PF_STAGE + 2048));
+  return HB_OK;
+}
+
+extern "C" {
+
+int hb_moe_prefill_supported(int H, int I) { return H > 0 && I > 0 && H % 256 == 0 && I % 256 == 0; }
+
+size_t hb_moe_prefill_ws_bytes(int S, int K, int E, int H, int I) {
+  if (S < 1 || K < 1 || E < 1 || !hb_moe_prefill_supported(H, I)) return 0;
+  return pf_carve(nullptr, S, K, E, H, I, nullptr);
+}
+
+int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, const int32_t* ids, const float* w, int M, int K, const void* x_bf16,
+                   int H, int I, float limit, float* out, void* ws, int S, void* stream, const hb_pf_combine* cmb) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (M <= 0) return HB_OK;
+  HB_REQUIRE(ctx, rec_tab && ids && w && x_bf16 && (out || cmb), HB_ERR_INVALID, "moe_prefill: NULL argument");
+  HB_REQUIRE(ctx, !cmb || (cmb->shared && cmb->out), HB_ERR_INVALID, "moe_prefill: combine without shared rows or output");
+  HB_REQUIRE(ctx, hb_moe_prefill_supported(H, I) && S >= 1 && K >= 1 && E >= 1 && E <= 1024 && li >= 0, HB_ERR_UNSUPPORTED,
+             "moe_prefill: H=%d I=%d (multiples of 256) E=%d (≤ 1024) K=%d S=%d", H, I, E, K, S);
+  HB_REQUIRE(ctx, (long long)S * K < (1ll << 30), HB_ERR_UNSUPPORTED, "moe_prefill: S·K too large");
+  HB_REQUIRE(ctx, ws && hb_aligned(ws, 256), HB_ERR_WORKSPACE, "moe_prefill: ws NULL or not 256-byte aligned");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  PfWs W;
+  pf_carve(ws, S, K, E, H, I, &W);
+  hb_rec_layout L;
+  hb_rec_layout_make(H, I, &L);
+  const uint8_t* const* lt = rec_tab + (size_t)li * E;
+  const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(x_bf16);
+  int r;
+  for (int s0 = 0; s0 < M; s0 += S) {
+    const int n = M - s0 < S ? M - s0 : S, P = n * K;
+    const int32_t* sid = ids + (size_t)s0 * K;
+    HB_CUDA(ctx, cudaMemsetAsync(W.cnt, 0, (size_t)E * 4, st));
+    if ((r = hb_launch(ctx, "pf_count", false, pf_count_kernel, dim3((P + 255) / 256), dim3(256), 0, st, sid, P, E, lt, W.cnt))) return r;
+    if ((r = hb_launch(ctx, "pf_scan", false, pf_scan_kernel, dim3(1), dim3(1024), 0, st, (const int*)W.cnt, E, W.cursor, W.tiles, W.n_tiles))) return r;
+    if ((r = hb_launch(ctx, "pf_fill", false, pf_fill_kernel, dim3((P + 255) / 256), dim3(256), 0, st, sid, P, E, lt, W.cursor, W.perm))) return r;
+    if ((r = hbk_a4_quant(ctx, x + (size_t)s0 * H, H, n, H, W.xq, W.xs, W.xg, st))) return r;
+    PfGemmArgs a{};
+    a.tiles = W.tiles; a.n_tiles = W.n_tiles; a.perm = W.perm; a.K_top = K; a.tab = lt; a.L = L; a.limit = limit; a.err = ctx->dev_err;
+    a.aq = W.xq; a.as = W.xs; a.ag = W.xg; a.Kd = H; a.N = I; a.out = W.y; a.ldo = I;
+    if ((r = pf_launch<PF_GU>(ctx, "pf_gemm_gu", a, st))) return r;
+    if ((r = hbk_a4_quant(ctx, W.y, I, P, I, W.yq, W.ys, W.yg, st))) return r;
+    a.aq = W.yq; a.as = W.ys; a.ag = W.yg; a.Kd = I; a.N = H; a.out = W.part; a.ldo = H;
+    if ((r = pf_launch<PF_DOWN>(ctx, "pf_gemm_down", a, st))) return r;
+    const size_t pairs2 = (size_t)n * H / 2;
+    const __nv_bfloat16* sh = cmb ? reinterpret_cast<const __nv_bfloat16*>(cmb->shared) + (size_t)s0 * H : nullptr;
+    if ((r = hb_launch(ctx, "pf_reduce", false, pf_reduce_kernel, dim3((unsigned)((pairs2 + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16*)W.part, sid,
+                       w + (size_t)s0 * K, n, K, E, lt, H, cmb ? (float*)nullptr : out + (size_t)s0 * H, sh,
+                       cmb && cmb->lg ? cmb->lg + (size_t)s0 * cmb->ld : (const float*)nullptr, cmb ? cmb->ld : 0, cmb ? cmb->col : 0,
+                       cmb ? reinterpret_cast<__nv_bfloat16*>(cmb->out) + (size_t)s0 * H : (__nv_bfloat16*)nullptr)))
+      return r;
+  }
+  return HB_OK;
+}
+
+int hb_nvfp4_gemm_a4(hb_ctx* ctx, const hb_qmat* W, const uint8_t* xq, const uint8_t* xs, const float* xg, int M, float* y, int ldy, void* stream) {
+  if (!ctx) return HB_ERR_INVALID;
+  HB_REQUIRE(ctx, W && W->w && W->s && xq && xs && xg && y, HB_ERR_INVALID, "nvfp4_gemm_a4: NULL argument");
+  HB_REQUIRE(ctx, W->fmt == HB_FMT_NVFP4 && W->N > 0 && W->N % 256 == 0 && W->K > 0 && W->K % 256 == 0 && M >= 1 && ldy >= W->N && ldy % 4 == 0,
+             HB_ERR_UNSUPPORTED, "nvfp4_gemm_a4: NVFP4 matrix with N and K multiples of 256 wanted (fmt %d N=%d K=%d M=%d ldy=%d)", W->fmt, W->N, W->K, M, ldy);
+  HB_REQUIRE(ctx, hb_aligned(W->w, 16) && hb_aligned(W->s, 16) && hb_aligned(xq, 16) && hb_aligned(xs, 16) && hb_aligned(y, 16), HB_ERR_INVALID,
+             "nvfp4_gemm_a4: operands must be 16-byte aligned");
+  PfGemmArgs a{};
+  a.M = M; a.aq = xq; a.as = xs; a.ag = xg; a.Kd = W->K; a.bw = W->w; a.bs = reinterpret_cast<const uint8_t*>(W->s); a.bg = W->g; a.N = W->N;
+  a.out = y; a.ldo = ldy; a.err = ctx->dev_err;
+  return pf_launch<PF_PLAIN>(ctx, "pf_gemm_plain", a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int hb_fp4_peak_probe(hb_ctx* ctx, int rounds, float* tflops) {
+  if (!ctx) return HB_ERR_INVALID;
+  HB_REQUIRE(ctx, rounds >= 1 && rounds <= (1 << 20) && tflops, HB_ERR_INVALID, "fp4_peak_probe: rounds 1..2^20");
+  cudaEvent_t e0, e1;
+  HB_CUDA(ctx, cudaEventCreate(&e0)); HB_CUDA(ctx, cudaEventCreate(&e1));
+  int r = hb_launch(ctx, "pf_peak", false, pf_peak_kernel, dim3(ctx->sm_count), dim3(128), (size_t)PF_STAGE + 2048, (cudaStream_t)0, 64, ctx->dev_err);   // warm-up
+  cudaEventRecord(e0, 0);
+  if (!r) r = hb_launch(ctx, "pf_peak", false, pf_peak_kernel, dim3(ctx->sm_count), dim3(128), (size_t)PF_STAGE + 2048, (cudaStream_t)0, rounds, ctx->dev_err);
+  cudaEventRecord(e1, 0);
+  const cudaError_t e = cudaEventSynchronize(e1);
+  float ms = 0.f;
+  cudaEventElapsedTime(&ms, e0, e1);
+  cudaEventDestroy(e0); cudaEventDestroy(e1);
+  if (r) return r;
+  if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "fp4_peak_probe: %s", cudaGetErrorString(e));
+  *tflops = (float)(2.0 * PF_BM * PF_BN * 64.0 * 4.0 * rounds * ctx->sm_count / (ms * 1e-3) / 1e12);
+  return HB_OK;
+}
+
+}  // extern "C"

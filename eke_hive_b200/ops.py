@@ -16,7 +16,7 @@ from ._lib import Config, HbError, MoePair, PfCombine, RecLayout
 
 __all__ = ["Context", "context", "ExpertRecLayout", "nvfp4_dequant", "nvfp4_gemv", "nvfp4_quantize", "a4_quant", "router_softmax_topk",
            "router_topk", "build_moe_pairs", "moe_combine", "moe_decode_ws_bytes", "moe_decode", "fn_moe_decode_routed", "fn_moe_decode_routed_static", "static_max_pairs", "moe_decode_routed_f32", "moe_layer_decode",
-           "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
+           "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "moe_prefill_supported", "moe_prefill_ws_bytes", "fn_moe_prefill", "nvfp4_gemm_a4", "fp4_peak_probe", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
 
 
 def _L():
@@ -339,6 +339,49 @@ def lb_dequant(W: GMat, out=None, ctx: Context | None = None):
     out = torch.empty((W.N, W.K), dtype=torch.bfloat16, device=W.w.device) if out is None else out
     ctx.check(_L().hb_lb_dequant(ctx.handle, C.byref(W.c), _p(out), _stream()))
     return out
+
+
+# ---------------------------------------------------------------------------------------------------- prefill (tcgen05 grouped GEMM)
+def moe_prefill_supported(H: int, I: int) -> bool:
+    return bool(_L().hb_moe_prefill_supported(H, I))
+
+
+def moe_prefill_ws_bytes(S: int, K: int, E: int, H: int, I: int) -> int:
+    return int(_L().hb_moe_prefill_ws_bytes(S, K, E, H, I))
+
+
+def fn_moe_prefill(rec_tab, li: int, E: int, ids, w, x, H: int, I: int, out=None, ws=None, S: int | None = None, limit: float = 0.0,
+                   shared=None, lg=None, col: int = 0, cout=None, ctx: Context | None = None):
+    """hive::qwen::fn_moe_prefill (NVFP4 activations): fp32 [M, H] routed sums, or with `shared` the fused combine → bf16 [M, H]."""
+    ctx = ctx or context()
+    M, K = ids.shape
+    S = M if S is None else S
+    ws = torch.empty(moe_prefill_ws_bytes(S, K, E, H, I), dtype=torch.uint8, device=x.device) if ws is None else ws
+    if shared is None:
+        out = torch.empty((M, H), dtype=torch.float32, device=x.device) if out is None else out
+        ctx.check(_L().hb_moe_prefill(ctx.handle, _p(rec_tab), li, E, _p(ids), _p(w), M, K, _p(x), H, I, limit, _p(out), _p(ws), S, _stream(), None))
+        return out
+    cout = torch.empty((M, H), dtype=torch.bfloat16, device=x.device) if cout is None else cout
+    cmb = PfCombine(_p(shared), _p(lg), 0 if lg is None else lg.stride(0), col, _p(cout))
+    ctx.check(_L().hb_moe_prefill(ctx.handle, _p(rec_tab), li, E, _p(ids), _p(w), M, K, _p(x), H, I, limit, None, _p(ws), S, _stream(), C.byref(cmb)))
+    return cout
+
+
+def nvfp4_gemm_a4(W: "GMat", xq, xs, xg, y=None, ctx: Context | None = None):
+    """Dense W4A4 GEMM: y fp32 [M, N] from activations quantised by a4_quant."""
+    ctx = ctx or context()
+    M = xq.shape[0]
+    y = torch.empty((M, W.N), dtype=torch.float32, device=xq.device) if y is None else y
+    ctx.check(_L().hb_nvfp4_gemm_a4(ctx.handle, C.byref(W.c), _p(xq), _p(xs), _p(xg), M, _p(y), y.stride(0), _stream()))
+    return y
+
+
+def fp4_peak_probe(rounds: int = 4096, ctx: Context | None = None) -> float:
+    """Dense FP4 TFLOP/s of the device's tensor pipe, measured with resident operands."""
+    ctx = ctx or context()
+    v = C.c_float(0.0)
+    ctx.check(_L().hb_fp4_peak_probe(ctx.handle, rounds, C.byref(v)))
+    return float(v.value)
 
 
 # ---------------------------------------------------------------------------------------------------- prefill helpers

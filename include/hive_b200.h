@@ -188,6 +188,29 @@ HB_API int hb_dense_gemv_gu(hb_ctx* ctx, const hb_qmat* gate, const hb_qmat* up,
  * the reference ships no low-bit layout, only an error probe, tools/lowbit_probe.py:18-38). */
 HB_API int hb_lb_dequant(hb_ctx* ctx, const hb_qmat* W, void* out_bf16, void* stream);
 
+/* ---- routed-expert prefill: grouped W4A4 GEMM on the tcgen05 tensor cores ---- */
+/* hive::qwen::fn_moe_prefill_supported — engine/include/hive/qwen/fn_moe.h:48.  Here: H and I multiples of 256. */
+HB_API int hb_moe_prefill_supported(int H, int I);
+/* hive::qwen::fn_moe_prefill_ws_bytes — engine/include/hive/qwen/fn_moe.h:56: scratch for sub-chunks of S rows. */
+HB_API size_t hb_moe_prefill_ws_bytes(int S, int K, int E, int H, int I);
+/* hive::qwen::fn_moe_prefill with NVFP4 activations (engine/include/hive/qwen/fn_moe.h:46-61, engine/src/qwen/fn_moe_pf.cu:439-446,
+ * :858-941): for every row m, out[m] = Σ_k bf16(expert_{ids[m,k]}(x[m]))·w[m,k] (fp32, k order, overwritten), or with cmb the
+ * fused combine → bf16 cmb->out and `out` may be NULL.  Inside an expert: x and y = bf16(silu(g)·u) are quantised per row to NVFP4
+ * (hb_a4_quant's rule), both GEMMs run as block-scaled FP4 MMAs with fp32 accumulation, g, u, y and the down result are
+ * rounded to bf16 where the decode kernels round them.  Records come from rec_tab[li·E + id]; ids outside [0,E) and NULL
+ * records contribute nothing.  Rows are processed in sub-chunks of S; ws ≥ hb_moe_prefill_ws_bytes(S, K, E, H, I).  E ≤ 1024.
+ * Block scales are read as unsigned e4m3 (the sign bit of a scale byte must be clear, as every NVFP4 writer leaves it). */
+HB_API int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, const int32_t* ids, const float* w, int M, int K,
+                          const void* x_bf16, int H, int I, float limit, float* out, void* ws, int S, void* stream, const hb_pf_combine* cmb);
+/* The same GEMM on one dense NVFP4 matrix: y[m,n] = xg[m]·W.g·Σ_k xq[m,k]·xs[m,k/16]·W[n,k], fp32 [M, ldy].  xq / xs / xg as written by
+ * hb_a4_quant.  N and K multiples of 256.  (No single counterpart in the reference; it is the building block hb_moe_prefill is
+ * tested through.) */
+HB_API int hb_nvfp4_gemm_a4(hb_ctx* ctx, const hb_qmat* W, const uint8_t* xq, const uint8_t* xs, const float* xg, int M, float* y, int ldy,
+                            void* stream);
+/* Measures the FP4 tensor-pipe ceiling of the device: every SM issues `rounds`×4 block-scaled 128×256×64 MMAs on operands held in
+ * shared memory (no loads, no epilogue); *tflops = dense FP4 TFLOP/s.  Synchronises the device.  (No reference counterpart.) */
+HB_API int hb_fp4_peak_probe(hb_ctx* ctx, int rounds, float* tflops);
+
 /* ---- prefill helpers kept for callers that compose (engine/include/hive/glm/glm_moe.h:33-41) ---- */
 HB_API int hb_gather_rows(hb_ctx* ctx, const void* x_bf16, const int32_t* rows, int R, int H, void* out_bf16, void* stream);
 HB_API int hb_swiglu_rows(hb_ctx* ctx, const void* gu_bf16, int R, int I, float limit, void* y_bf16, void* stream);

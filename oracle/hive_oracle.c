@@ -392,6 +392,52 @@ void ho_a4_quant(const float* x, int ld, int n, int K, uint8_t* q, uint8_t* s, f
   }
 }
 
+/* W4A4 GEMV of one quantised activation row (codes aq, scales as, global ag) against an NVFP4 matrix: what the block-scaled
+ * tensor-core GEMM of the prefill path computes (engine/src/qwen/fn_moe_pf.cu:439-446): per 16-value block the integer-valued
+ * dot product of the two code vectors (exact) times both block scales, summed in fp32 (double here: the hardware's summation
+ * order is not specified, so the oracle keeps the sum exact and rounds once). */
+static void gemv_a4(const uint8_t* wq, const uint8_t* wsc, int N, int K, const uint8_t* aq, const uint8_t* as, double* y) {
+  for (int n = 0; n < N; ++n) {
+    double acc = 0.0;
+    for (int b = 0; b < K / 16; ++b) {
+      float dot = 0.f;
+      for (int j = 0; j < 8; ++j) {
+        const uint8_t wb = wq[(size_t)n * (K / 2) + (size_t)b * 8 + j], ab = aq[(size_t)b * 8 + j];
+        dot += ho_e2m1_to_f32(wb & 15) * ho_e2m1_to_f32(ab & 15) + ho_e2m1_to_f32(wb >> 4) * ho_e2m1_to_f32(ab >> 4);
+      }
+      acc += (double)dot * (double)ho_e4m3_to_f32(wsc[(size_t)n * (K / 16) + b]) * (double)ho_e4m3_to_f32(as[b]);
+    }
+    y[n] = acc;
+  }
+}
+
+/* One expert on one row with NVFP4 activations: x → a4 quant → gate, up; g = bf16(acc·gx·g1), u = bf16(acc·gx·g3),
+ * y = bf16(silu(g)·u) → a4 quant → down; out = bf16(acc·(gy·g2)) (fn_moe_pf.cu:636-660, :903-908).  out is not multiplied by a
+ * routing weight: the prefill reduce does that. */
+void ho_expert_forward_a4(const uint8_t* rec, const uint64_t* off, int H, int I, const float* x, float limit, float* out) {
+  float g[3];
+  memcpy(g, rec + off[6], 12);
+  const int Kmax = H > I ? H : I;
+  uint8_t* q = (uint8_t*)malloc((size_t)Kmax / 2 + (size_t)Kmax / 16);
+  uint8_t* sc = q + Kmax / 2;
+  double* acc = (double*)malloc(sizeof(double) * (size_t)(2 * I > H ? 2 * I : H));
+  float* y = (float*)malloc(sizeof(float) * (size_t)I);
+  float gx;
+  ho_a4_quant(x, H, 1, H, q, sc, &gx);
+  gemv_a4(rec + off[0], rec + off[1], I, H, q, sc, acc);
+  gemv_a4(rec + off[2], rec + off[3], I, H, q, sc, acc + I);
+  for (int i = 0; i < I; ++i) {
+    float gv = ho_bf16r((float)acc[i] * gx * g[0]), uv = ho_bf16r((float)acc[I + i] * gx * g[1]);
+    if (limit > 0.f) { uv = fminf(fmaxf(uv, -limit), limit); gv = fminf(gv, limit); }
+    y[i] = ho_bf16r(gv / (1.f + expf(-gv)) * uv);
+  }
+  float gy;
+  ho_a4_quant(y, I, 1, I, q, sc, &gy);
+  gemv_a4(rec + off[4], rec + off[5], H, I, q, sc, acc);
+  for (int d = 0; d < H; ++d) out[d] = ho_bf16r((float)acc[d] * (gy * g[2]));
+  free(y); free(acc); free(q);
+}
+
 /* ------------------------------------------------------------------------------------------------ 3-/2-bit group-64 */
 size_t ho_lb_weight_bytes(int bits, int N, int K) { return bits == 2 ? (size_t)N * K / 4 : (size_t)N * K / 4 + (size_t)N * K / 8; }
 

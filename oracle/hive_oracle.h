@@ -75,6 +75,8 @@ void ho_moe_combine(const float* routed, const float* shared, const float* gate_
 void ho_nvfp4_quantize(const float* w, int N, int K, int search, uint8_t* q, uint8_t* s, float* g_mul);
 /* engine/src/qwen/fn_moe_pf.cu:456-502 (a4_quant_kernel): per-row dynamic NVFP4 activation quantization. x = bf16 values as fp32. */
 void ho_a4_quant(const float* x, int ld, int n, int K, uint8_t* q, uint8_t* s, float* g);
+/* one expert on one row with NVFP4 activations (the prefill path's W4A4 rounding points); out [H] = bf16 values, unweighted */
+void ho_expert_forward_a4(const uint8_t* rec, const uint64_t* off, int H, int I, const float* x, float limit, float* out);
 
 /* ---- 3-/2-bit group-64 dense matrices (layout defined by this project; no reference counterpart: parity unpinned) ----
  * bits = 2: w = [N, K/4] bytes, byte j of a row holds codes of columns 4j..4j+3, low bits first.

@@ -182,6 +182,15 @@ def expert_forward(rec: np.ndarray, H: int, I: int, a: np.ndarray, route_w: floa
     return out
 
 
+def expert_forward_a4(rec: np.ndarray, H: int, I: int, x: np.ndarray, limit: float = 0.0) -> np.ndarray:
+    """One expert on one activation row (fp32 holding bf16 values) with the prefill path's NVFP4 activations; unweighted bf16 values."""
+    off = rec_layout(H, I)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.zeros(H, np.float32)
+    _C.ho_expert_forward_a4(_ptr(rec, _u8p), _ptr(off, _u64p), H, I, _ptr(x, _f32p), C.c_float(limit), _ptr(out, _f32p))
+    return out
+
+
 def a4_quant(x: np.ndarray):
     x = np.ascontiguousarray(x, dtype=np.float32)
     n, K = x.shape

@@ -1,0 +1,117 @@
+"""GPU parity of the prefill path: the block-scaled FP4 GEMM against an fp64 evaluation of the same quantised operands, and
+hb_moe_prefill against the CPU oracle's W4A4 expert (activations quantised by the reference's a4 rule, fn_moe_pf.cu:456-502)."""
+import numpy as np
+import pytest
+import torch
+
+from util import random_records, upload
+
+pytestmark = pytest.mark.gpu
+
+E2M1 = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
+
+
+def _lut_e2m1(dev):
+    return torch.tensor(E2M1 + [-v for v in E2M1], dtype=torch.float64, device=dev)
+
+
+def _lut_e4m3(dev):
+    v = np.zeros(256)
+    for b in range(256):
+        e, m = (b >> 3) & 15, b & 7
+        mag = m * 2.0 ** -9 if e == 0 else (1 + m / 8) * 2.0 ** (e - 7)
+        v[b] = -mag if b & 0x80 else mag
+    return torch.tensor(v, dtype=torch.float64, device=dev)
+
+
+def dequant64(q, s):
+    """codes u8 [R, K/2] + e4m3 scales u8 [R, K/16] → fp64 [R, K] (no global)."""
+    dev = q.device
+    lo, hi = (q & 0xF).long(), (q >> 4).long()
+    codes = torch.stack([lo, hi], dim=-1).reshape(q.shape[0], -1)
+    vals = _lut_e2m1(dev)[codes]
+    sc = _lut_e4m3(dev)[s.long()].repeat_interleave(16, dim=1)
+    return vals * sc
+
+
+@pytest.fixture(scope="module")
+def E():
+    import eke_hive_b200 as E
+    return E
+
+
+def test_fp4_peak_probe_runs(E):
+    tf = E.fp4_peak_probe(512)
+    assert 100.0 < tf < 20000.0, tf
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 256), (100, 256, 512), (300, 512, 2048), (1024, 1024, 7168)])
+def test_gemm_a4_matches_fp64(E, M, N, K):
+    dev = torch.device("cuda")
+    g = torch.Generator(device="cpu").manual_seed(M * 7 + N + K)
+    x = (torch.randn((M, K), generator=g) * torch.exp(torch.randn((M, 1), generator=g))).to(torch.bfloat16).to(dev)
+    wq = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g).to(dev)
+    ws = torch.randint(0x20, 0x48, (N, K // 16), dtype=torch.uint8, generator=g).to(dev)
+    xq, xs, xg = E.a4_quant(x)
+    W = E.GMat(E.FMT_NVFP4, N, K, wq, ws, None, 0.0123)
+    y = E.nvfp4_gemm_a4(W, xq, xs, xg)
+    torch.cuda.synchronize()
+    E.context().check_device()
+    A, B = dequant64(xq, xs), dequant64(wq, ws)
+    ref = (A @ B.T) * xg.double()[:, None] * 0.0123
+    bound = (A.abs() @ B.abs().T) * xg.double()[:, None] * 0.0123
+    err = (y.double() - ref).abs()
+    assert torch.all(err <= 2e-6 * bound + 1e-30), float((err / (bound + 1e-30)).max())
+
+
+def _oracle_prefill(oracle, recs, H, I, ids, w, x_f32, limit=0.0):
+    """Σ_k w·bf16(expert(x)) per row with the W4A4 rounding points, on the CPU."""
+    M, K = ids.shape
+    out = np.zeros((M, H), dtype=np.float32)
+    for m in range(M):
+        for k in range(K):
+            e = int(ids[m, k])
+            if e < 0 or e >= len(recs) or recs[e] is None:
+                continue
+            out[m] += oracle.expert_forward_a4(recs[e], H, I, x_f32[m], limit) * np.float32(w[m, k])
+    return out
+
+
+@pytest.mark.parametrize("H,I,E_,K,M,S", [(256, 256, 4, 2, 70, 70), (512, 256, 8, 2, 300, 128), (2048, 512, 16, 4, 200, 200)])
+def test_moe_prefill_vs_oracle(E, oracle, H, I, E_, K, M, S):
+    dev = torch.device("cuda")
+    rng = np.random.default_rng(H + I + M)
+    recs = random_records(oracle, H, I, E_, H + M)
+    keep = upload(recs, dev)
+    tab = E.rec_table(keep)
+    ids = np.stack([rng.permutation(E_)[:K] for _ in range(M)]).astype(np.int32)
+    ids[3, 0] = -1
+    ids[5, 1] = E_ + 3
+    w = rng.random((M, K), dtype=np.float32)
+    x = torch.tensor(rng.standard_normal((M, H)).astype(np.float32)).to(torch.bfloat16)
+    out = E.fn_moe_prefill(tab, 0, E_, torch.tensor(ids, device=dev), torch.tensor(w, device=dev), x.to(dev), H, I, S=S)
+    torch.cuda.synchronize()
+    E.context().check_device()
+    ref = _oracle_prefill(oracle, recs, H, I, ids, w, x.float().numpy())
+    got = out.cpu().numpy()
+    rms = np.sqrt((ref.astype(np.float64) ** 2).mean(axis=1, keepdims=True)) + 1e-12
+    assert np.max(np.abs(got - ref) / rms) <= 2e-2          # tolerance of the expert-output gate: 2e-2 × row RMS
+
+
+def test_moe_prefill_combine_matches_separate(E, oracle):
+    dev = torch.device("cuda")
+    H, I, E_, K, M = 512, 256, 8, 2, 150
+    rng = np.random.default_rng(11)
+    recs = random_records(oracle, H, I, E_, 11)
+    keep = upload(recs, dev)
+    tab = E.rec_table(keep)
+    ids = torch.tensor(np.stack([rng.permutation(E_)[:K] for _ in range(M)]).astype(np.int32), device=dev)
+    w = torch.tensor(rng.random((M, K), dtype=np.float32), device=dev)
+    x = torch.tensor(rng.standard_normal((M, H)).astype(np.float32)).to(torch.bfloat16).to(dev)
+    shared = torch.tensor(rng.standard_normal((M, H)).astype(np.float32)).to(torch.bfloat16).to(dev)
+    lg = torch.tensor(rng.standard_normal((M, 3)).astype(np.float32), device=dev)
+    routed = E.fn_moe_prefill(tab, 0, E_, ids, w, x, H, I)
+    fused = E.fn_moe_prefill(tab, 0, E_, ids, w, x, H, I, shared=shared, lg=lg, col=1)
+    sep = E.moe_combine(routed, shared, lg, 1)
+    torch.cuda.synchronize()
+    assert torch.equal(fused.view(torch.int16), sep.view(torch.int16))
