@@ -3,20 +3,22 @@
 //
 //   count / scan / fill   the (row, k) pairs sorted by expert (the order inside an expert is irrelevant: a pair's result depends only
 //                         on its own row) and a list of 128-pair tiles
-//   quantise x            per-row dynamic NVFP4 (hb_a4_quant's rule)
+//   quantise x            per-row dynamic NVFP4 (hb_a4_quant's rule), then the quantised rows copied into expert order
 //   gate|up GEMM          tile = 128 pairs × (128 gate + 128 up rows of I); block-scaled FP4 MMA, fp32 accumulators in tensor memory;
 //                         epilogue g = bf16(acc·gx·g1), u = bf16(acc·gx·g3), y = bf16(silu(g)·u)
 //   quantise y            per pair
 //   down GEMM             tile = 128 pairs × 256 rows of H; part[pair] = bf16(acc·(gy·g2))
 //   reduce                out[row] = Σ_k part·w in k order (or the fused shared-expert combine)
 //
-// GEMM kernel: persistent CTAs of 9 warps.  Warps 5-8 gather the operands: 16-byte cp.async copies written straight into the
-// 128-byte-swizzled K-major layout the MMA reads (pair rows come from anywhere in the activation buffer and expert records sit at
-// arbitrary addresses, so the gather is done by address, not by tensor map), and the e4m3 block scales as 4-byte copies into the
-// 32×16-byte chunks `tcgen05.cp` moves to tensor memory.  Warp 4 issues `tcgen05.cp` + `tcgen05.mma kind::mxf4nvf4` (block 16,
-// ue4m3 scales: both operands' block scales are applied by the tensor core) and commits to the stage's mbarrier.  Warps 0-3 read
-// the accumulators back with `tcgen05.ld` and run the epilogue.  Every wait is bounded; on a timeout the kernel records a site
-// code in the context's error word, drains its copies, frees its tensor memory and returns.
+// GEMM kernel: persistent CTAs of 10 warps.  Warp 5 moves the e2m1 codes of both operands with TMA (`cp.async.bulk.tensor`, 128-byte
+// swizzle: the K-major layout the MMA reads).  The activation rows of a tile are contiguous because the quantised rows are first
+// copied into expert order; the weight matrices sit inside expert records at arbitrary addresses, so a small kernel stamps each
+// record's addresses into tensor maps on the device (`tensormap.replace`).  Warps 6-9 bring the e4m3 block scales as 4-byte
+// cp.async copies into the 32×16-byte chunks `tcgen05.cp` moves to tensor memory.  Warp 4 issues `tcgen05.cp` + `tcgen05.mma
+// kind::mxf4nvf4` (block 16, ue4m3 scales: both operands' block scales are applied by the tensor core) and commits to the stage's
+// mbarrier.  Warps 0-3 read the accumulators back with `tcgen05.ld` and run the epilogue.  Every wait is bounded; on a timeout
+// the kernel records a site code in the context's error word, drains its copies, frees its tensor memory and returns.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -35,7 +37,7 @@ constexpr int PF_SFA_BYTES = 4 * 512;   // 4 MMA k-steps × one 128-row chunk
 constexpr int PF_SFB_BYTES = 8 * 512;   // 4 k-steps × two 128-row chunks
 constexpr int PF_STAGE = PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + PF_SFB_BYTES;
 constexpr int PF_SMEM = PF_ST * PF_STAGE + 1024 + 256;
-constexpr int PF_THREADS = 9 * 32;
+constexpr int PF_THREADS = 10 * 32;
 constexpr int PF_TMEM_COLS = 512;
 constexpr int PF_SF_COL0 = 256;         // accumulator: columns [0, 256); scales of stage s: [256 + 48 s, 256 + 48 s + 48)
 static_assert(PF_STAGE % 1024 == 0, "stage buffers must keep the 1024-byte alignment of the swizzle atom");
@@ -49,12 +51,13 @@ struct PfGemmArgs {
   // work list
   const PfTile* tiles; const int* n_tiles;     // n_tiles == nullptr: one implicit tile list of ceil(M / 128) tiles over rows [0, M)
   int M;                                       // PLAIN only
-  const int* perm; int K_top;                  // pair of a sorted slot; GU reads activation row perm[slot] / K_top
-  // A operand (quantised activations)
-  const uint8_t* aq; const uint8_t* as; const float* ag; int Kd;   // codes [rows, Kd/2], scales [rows, Kd/16], per-row global
+  const int* perm;                             // pair of a sorted slot (DOWN scatters its rows by it)
+  // A operand (quantised activations, tile rows contiguous): codes come through the kernel's tensor-map parameter
+  const uint8_t* as; const float* ag; int Kd;  // scales [rows, Kd/16], per-row global
   // B operand
   const uint8_t* const* tab; hb_rec_layout L;  // GU / DOWN: expert records
-  const uint8_t* bw; const uint8_t* bs; float bg;   // PLAIN: one matrix [N, Kd]
+  const CUtensorMap* tmB;                      // GU / DOWN: [expert][3] tensor maps of w1, w3, w2 (written by pf_tmaps_kernel)
+  const uint8_t* bs; float bg;                 // PLAIN: scales and global of the one matrix [N, Kd] (codes: tensor-map parameter)
   int N;                                       // output columns in all (I for GU, H for DOWN, N for PLAIN)
   float limit;
   void* out; int ldo;                          // GU: y bf16 [slots, I]; DOWN: part bf16 [pairs, H]; PLAIN: fp32 [M, ldo]
@@ -103,6 +106,16 @@ __device__ __forceinline__ void pf_cp_commit() { asm volatile("cp.async.commit_g
 template <int N_>
 __device__ __forceinline__ void pf_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N_) : "memory"); }
 
+// 2-D tiled TMA load: box (128 bytes × 128 rows) at byte column c0, row c1 → shared memory, completion in bytes on `bar`
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int c0, int c1, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+// a tensor map another kernel modified in global memory: make the modification visible to this thread's TMA operations
+__device__ __forceinline__ void tmap_acquire(const void* tmap) {
+  asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(tmap) : "memory");
+}
+
 // Shared-memory matrix descriptor, K-major operand rows of 128 bytes under the 128-byte swizzle: 8-row groups 1024 bytes apart
 // (stride field), leading-dimension field 1 (not used by swizzled K-major operands), descriptor version 1, layout type 2.
 __device__ __forceinline__ uint64_t pf_desc_sw128(uint32_t saddr) {
@@ -130,7 +143,8 @@ __device__ __forceinline__ uint4 pf_pack8(const float* v) {
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(PfGemmArgs a) {
+__global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs a, const __grid_constant__ CUtensorMap tmA,
+                                                                const __grid_constant__ CUtensorMap tmB0) {
   extern __shared__ uint8_t pf_raw[];
   const uint32_t raw = smem_u32(pf_raw), base = (raw + 1023u) & ~1023u;     // swizzle atoms want 1024-byte alignment
   uint8_t* sm = pf_raw + (base - raw);
@@ -142,7 +156,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(PfGemmArgs a) {
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mma_done + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < PF_ST; ++s) { mbar_init(&full[s], 128); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < PF_ST; ++s) { mbar_init(&full[s], 128 + 1); mbar_init(&empty[s], 1); }   // 128 scale loaders + the TMA thread
     mbar_init(acc_full, 1); mbar_init(acc_empty, 128); mbar_init(mma_done, 1);
     mbar_fence_init();
   }
@@ -157,52 +171,59 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(PfGemmArgs a) {
   constexpr int NW = MODE == PF_GU ? 128 : 256;                              // output columns per tile
   const int n_nt = a.N / NW, nkb = a.Kd / PF_BK;
   const long long work = (long long)n_tiles * n_nt;                          // tile-major: the CTAs of a wave share activation tiles and expert rows in L2
-  const size_t rowb = (size_t)a.Kd / 2, rows = (size_t)a.Kd / 16;
+  const size_t rows = (size_t)a.Kd / 16;
 
-  if (warp >= 5) {
-    // ------------------------------------------------------------------------------------------------ loaders: thread lt owns A row lt, B rows lt and lt + 128
-    const int lt = threadIdx.x - 160;
-    const uint32_t sw = (uint32_t)((lt >> 3) * 1024 + (lt & 7) * 128), x7 = (uint32_t)(lt & 7);
+  if (warp == 5) {
+    // ------------------------------------------------------------------------------------------------ TMA: codes of both operands, one thread
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long w = blockIdx.x; w < work && ok; w += gridDim.x) {
+        const int ti = (int)(w / n_nt), nt = (int)(w - (long long)ti * n_nt);
+        const PfTile tl = pf_tile(a, ti);
+        const CUtensorMap *m0 = &tmB0, *m1 = &tmB0;
+        int r0 = nt * 256, r1 = nt * 256 + 128;                               // B rows of the tile's two 128-row boxes
+        if (MODE == PF_GU) { m0 = a.tmB + (size_t)tl.e * 3; m1 = m0 + 1; r0 = r1 = nt * 128; }
+        if (MODE == PF_DOWN) m0 = m1 = a.tmB + (size_t)tl.e * 3 + 2;
+        if (MODE != PF_PLAIN) { tmap_acquire(m0); if (m1 != m0) tmap_acquire(m1); }
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const uint32_t stage = it % PF_ST;
+          if (!(ok = mbar_wait(&empty[stage], ((it / PF_ST) & 1) ^ 1, a.err, 0x100u))) break;
+          const uint32_t sb = base + stage * PF_STAGE;
+          mbar_expect_tx(&full[stage], PF_A_BYTES + PF_B_BYTES);
+          tma_load_2d(sb, &tmA, kb * 128, tl.slot0, &full[stage]);
+          tma_load_2d(sb + PF_A_BYTES, m0, kb * 128, r0, &full[stage]);
+          tma_load_2d(sb + PF_A_BYTES + 128 * 128, m1, kb * 128, r1, &full[stage]);
+        }
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------------------------------------ scale loaders: thread lt owns A row lt, B rows lt and lt + 128
+    const int lt = threadIdx.x - 192;
     const uint32_t sfo = (uint32_t)((lt & 31) * 16 + (lt >> 5) * 4);
     uint32_t it = 0;
     bool ok = true;
     for (long long w = blockIdx.x; w < work && ok; w += gridDim.x) {
       const int ti = (int)(w / n_nt), nt = (int)(w - (long long)ti * n_nt);
       const PfTile tl = pf_tile(a, ti);
-      const int slot = tl.slot0 + min(lt, tl.m - 1);                         // rows past the tile's end repeat its last row (never stored)
-      const size_t arow = MODE == PF_GU ? (size_t)(a.perm[slot] / a.K_top) : (size_t)slot;
-      const uint8_t* ap = a.aq + arow * rowb;
-      const uint8_t* asp = a.as + arow * rows;
-      const uint8_t *b0, *b1, *s0, *s1;
-      if (MODE == PF_PLAIN) {
-        b0 = a.bw + (size_t)(nt * 256 + lt) * rowb; b1 = b0 + 128 * rowb;
-        s0 = a.bs + (size_t)(nt * 256 + lt) * rows; s1 = s0 + 128 * rows;
-      } else {
+      const size_t slot = (size_t)(tl.slot0 + min(lt, tl.m - 1));            // rows past the tile's end repeat its last row (never stored)
+      const uint8_t* asp = a.as + slot * rows;
+      const uint8_t *s0, *s1;
+      if (MODE == PF_PLAIN) { s0 = a.bs + (size_t)(nt * 256 + lt) * rows; s1 = s0 + 128 * rows; }
+      else {
         const uint8_t* rec = a.tab[tl.e];
-        if (MODE == PF_GU) {
-          b0 = rec + a.L.w1 + (size_t)(nt * 128 + lt) * rowb; b1 = rec + a.L.w3 + (size_t)(nt * 128 + lt) * rowb;
-          s0 = rec + a.L.s1 + (size_t)(nt * 128 + lt) * rows; s1 = rec + a.L.s3 + (size_t)(nt * 128 + lt) * rows;
-        } else {
-          b0 = rec + a.L.w2 + (size_t)(nt * 256 + lt) * rowb; b1 = b0 + 128 * rowb;
-          s0 = rec + a.L.s2 + (size_t)(nt * 256 + lt) * rows; s1 = s0 + 128 * rows;
-        }
+        if (MODE == PF_GU) { s0 = rec + a.L.s1 + (size_t)(nt * 128 + lt) * rows; s1 = rec + a.L.s3 + (size_t)(nt * 128 + lt) * rows; }
+        else { s0 = rec + a.L.s2 + (size_t)(nt * 256 + lt) * rows; s1 = s0 + 128 * rows; }
       }
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const uint32_t stage = it % PF_ST;
         if (!(ok = mbar_wait(&empty[stage], ((it / PF_ST) & 1) ^ 1, a.err, 0x100u))) break;
-        const uint32_t sb = base + stage * PF_STAGE;
-#pragma unroll
-        for (uint32_t c = 0; c < 8; ++c) {
-          const uint32_t o = sw + ((c ^ x7) << 4);
-          pf_cp16(sb + o, ap + (size_t)kb * 128 + c * 16);
-          pf_cp16(sb + PF_A_BYTES + o, b0 + (size_t)kb * 128 + c * 16);
-          pf_cp16(sb + PF_A_BYTES + 128 * 128 + o, b1 + (size_t)kb * 128 + c * 16);
-        }
+        const uint32_t sb = base + stage * PF_STAGE + PF_A_BYTES + PF_B_BYTES;
 #pragma unroll
         for (uint32_t j = 0; j < 4; ++j) {                                   // the row's 16 scales of this stage: 4 per MMA k-step
-          pf_cp4(sb + PF_A_BYTES + PF_B_BYTES + j * 512 + sfo, asp + (size_t)kb * 16 + j * 4);
-          pf_cp4(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + (2 * j) * 512 + sfo, s0 + (size_t)kb * 16 + j * 4);
-          pf_cp4(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + (2 * j + 1) * 512 + sfo, s1 + (size_t)kb * 16 + j * 4);
+          pf_cp4(sb + j * 512 + sfo, asp + (size_t)kb * 16 + j * 4);
+          pf_cp4(sb + PF_SFA_BYTES + (2 * j) * 512 + sfo, s0 + (size_t)kb * 16 + j * 4);
+          pf_cp4(sb + PF_SFA_BYTES + (2 * j + 1) * 512 + sfo, s1 + (size_t)kb * 16 + j * 4);
         }
         pf_cp_commit();
         if (it >= PF_LAG) {                                                  // the copies issued LAG iterations ago have landed: publish them
@@ -261,7 +282,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(PfGemmArgs a) {
       if (MODE == PF_PLAIN) { f0 = a.ag[slot] * a.bg; orow = (size_t)slot; }
       else {
         const float* g = reinterpret_cast<const float*>(a.tab[tl.e] + a.L.g);
-        if (MODE == PF_GU) { f0 = a.ag[a.perm[slot] / a.K_top]; f1 = g[0]; f2 = g[1]; orow = (size_t)slot; }
+        if (MODE == PF_GU) { f0 = a.ag[slot]; f1 = g[0]; f2 = g[1]; orow = (size_t)slot; }
         else { f0 = a.ag[slot] * g[2]; orow = (size_t)a.perm[slot]; }
       }
       if (!(ok = mbar_wait(acc_full, tcount & 1, a.err, 0x1000u))) break;
@@ -370,7 +391,7 @@ __global__ void pf_count_kernel(const int32_t* __restrict__ ids, int P, int E, c
 }
 // one block, E ≤ 1024: exclusive prefix sums of the pair counts (→ fill cursors) and of the tile counts (→ the tile list)
 __global__ void __launch_bounds__(1024) pf_scan_kernel(const int* __restrict__ cnt, int E, int* __restrict__ cursor, PfTile* __restrict__ tiles,
-                                                       int* __restrict__ n_tiles) {
+                                                       int* __restrict__ n_tiles, int* __restrict__ n_slots) {
   __shared__ int wsum_c[32], wsum_t[32];
   const int e = threadIdx.x, lane = e & 31, wp = e >> 5;
   const int c = e < E ? cnt[e] : 0, t = (c + PF_BM - 1) / PF_BM;
@@ -395,13 +416,48 @@ __global__ void __launch_bounds__(1024) pf_scan_kernel(const int* __restrict__ c
     cursor[e] = off;
     for (int i = 0; i < t; ++i) { PfTile tl; tl.e = e; tl.slot0 = off + i * PF_BM; tl.m = min(PF_BM, c - i * PF_BM); tiles[toff + i] = tl; }
   }
-  if (e == 1023) *n_tiles = wsum_t[31];
+  if (e == 1023) { *n_tiles = wsum_t[31]; *n_slots = wsum_c[31]; }
 }
 __global__ void pf_fill_kernel(const int32_t* __restrict__ ids, int P, int E, const uint8_t* const* __restrict__ tab, int* __restrict__ cursor,
                                int* __restrict__ perm) {
   const int p = blockIdx.x * blockDim.x + threadIdx.x;
   int e;
   if (p < P && pf_live(ids, p, E, tab, &e)) perm[atomicAdd(&cursor[e], 1)] = p;
+}
+
+// the quantised activation rows in expert order: slot s ← row perm[s] / K (codes, scales and the row's global)
+__global__ void pf_gather_q_kernel(const int* __restrict__ perm, const int* __restrict__ cnt_total, int K, int Hd, const uint8_t* __restrict__ xq,
+                                   const uint8_t* __restrict__ xs, const float* __restrict__ xg, uint8_t* __restrict__ q, uint8_t* __restrict__ sc,
+                                   float* __restrict__ g) {
+  const int n_slots = *cnt_total;
+  const int per_row = Hd / 32 + Hd / 256;                                    // 16-byte pieces of a row: codes then scales
+  for (int slot = blockIdx.x; slot < n_slots; slot += gridDim.x) {
+    const size_t row = (size_t)(perm[slot] / K);
+    for (int i = threadIdx.x; i < per_row; i += blockDim.x) {
+      if (i < Hd / 32) reinterpret_cast<uint4*>(q + (size_t)slot * (Hd / 2))[i] = __ldg(reinterpret_cast<const uint4*>(xq + row * (Hd / 2)) + i);
+      else reinterpret_cast<uint4*>(sc + (size_t)slot * (Hd / 16))[i - Hd / 32] = __ldg(reinterpret_cast<const uint4*>(xs + row * (Hd / 16)) + (i - Hd / 32));
+    }
+    if (threadIdx.x == 0) g[slot] = xg[row];
+  }
+}
+
+// Tensor maps of every resident expert's three matrices: the host encodes one map per matrix shape (on any valid address), this
+// kernel copies it and stamps in the address of the matrix inside the expert's record.
+struct PfMapPair { CUtensorMap gu, dn; };                                   // [I rows × H/2 bytes] for w1 / w3, [H rows × I/2 bytes] for w2
+__global__ void pf_tmaps_kernel(const __grid_constant__ PfMapPair tpl, const uint8_t* const* __restrict__ tab, int E, hb_rec_layout L,
+                                CUtensorMap* __restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= E * 3) return;
+  const int e = i / 3, mat = i - e * 3;
+  const uint8_t* rec = tab[e];
+  if (!rec) return;
+  const uint4* src = reinterpret_cast<const uint4*>(mat == 2 ? &tpl.dn : &tpl.gu);
+  uint4* dst = reinterpret_cast<uint4*>(out + i);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) dst[j] = src[j];
+  const uint64_t addr = reinterpret_cast<uint64_t>(rec + (mat == 0 ? L.w1 : mat == 1 ? L.w3 : L.w2));
+  asm volatile("tensormap.replace.tile.global_address.global.b1024.b64 [%0], %1;" ::"l"(dst), "l"(addr) : "memory");
+  asm volatile("fence.proxy.tensormap::generic.release.gpu;" ::: "memory");
 }
 
 // ---- reduce --------------------------------------------------------------------------------------------------------------------------
@@ -434,24 +490,53 @@ __global__ void pf_reduce_kernel(const __nv_bfloat16* __restrict__ part, const i
 using namespace hb;
 
 namespace {
-struct PfWs { int* cnt; int* cursor; int* n_tiles; PfTile* tiles; int* perm; __nv_bfloat16* y; __nv_bfloat16* part; uint8_t *xq, *xs, *yq, *ys; float *xg, *yg; };
+struct PfWs {
+  int* cnt; int* cursor; int* n_tiles; PfTile* tiles; int* perm; CUtensorMap* tmB; __nv_bfloat16* y; __nv_bfloat16* part;
+  uint8_t *xq, *xs, *yq, *ys, *xq_s, *xs_s; float *xg, *yg, *xg_s;
+};
 size_t pf_carve(void* ws, int S, int K, int E, int H, int I, PfWs* w) {
   size_t off = 0;
   auto take = [&](size_t b) { void* r = ws ? static_cast<char*>(ws) + off : nullptr; off += hb_align256(b); return r; };
   const size_t P = (size_t)S * K;
   PfWs t;
-  t.cnt = (int*)take((size_t)E * 4); t.cursor = (int*)take((size_t)E * 4); t.n_tiles = (int*)take(4);
+  t.cnt = (int*)take((size_t)(E + 1) * 4); t.cursor = (int*)take((size_t)E * 4); t.n_tiles = (int*)take(4);
   t.tiles = (PfTile*)take((P / PF_BM + E) * sizeof(PfTile)); t.perm = (int*)take(P * 4);
+  t.tmB = (CUtensorMap*)take((size_t)E * 3 * sizeof(CUtensorMap));
   t.y = (__nv_bfloat16*)take(P * I * 2); t.part = (__nv_bfloat16*)take(P * H * 2);
   t.xq = (uint8_t*)take((size_t)S * H / 2); t.xs = (uint8_t*)take((size_t)S * H / 16); t.xg = (float*)take((size_t)S * 4);
+  t.xq_s = (uint8_t*)take(P * H / 2); t.xs_s = (uint8_t*)take(P * H / 16); t.xg_s = (float*)take(P * 4);
   t.yq = (uint8_t*)take(P * I / 2); t.ys = (uint8_t*)take(P * I / 16); t.yg = (float*)take(P * 4);
   if (w) *w = t;
   return off;
 }
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link libcuda)
+typedef CUresult (*PfEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                               CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+PfEncodeFn pf_encode_fn() {
+  static PfEncodeFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = reinterpret_cast<PfEncodeFn>(p);
+  }
+  return fn;
+}
+// map of a byte matrix [n_rows][row_bytes] (e2m1 codes, two per byte), boxes of 128 bytes × 128 rows, 128-byte swizzle
+int pf_make_map(hb_ctx* ctx, CUtensorMap* m, const void* base, size_t row_bytes, size_t n_rows) {
+  PfEncodeFn fn = pf_encode_fn();
+  HB_REQUIRE(ctx, fn, HB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)n_rows}, strides[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {128, 128}, estr[2] = {1, 1};
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  HB_REQUIRE(ctx, r == CUDA_SUCCESS, HB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for %zu rows of %zu bytes at %p", (int)r, n_rows, row_bytes, base);
+  return HB_OK;
+}
 template <int MODE>
-int pf_launch(hb_ctx* ctx, const char* name, const PfGemmArgs& a, cudaStream_t st) {
+int pf_launch(hb_ctx* ctx, const char* name, const PfGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB0, cudaStream_t st) {
   const int grid = ctx->max_ctas > 0 && ctx->max_ctas < ctx->sm_count ? ctx->max_ctas : ctx->sm_count;
-  return hb_launch(ctx, name, false, pf_gemm_kernel<MODE>, dim3(grid), dim3(PF_THREADS), (size_t)PF_SMEM, st, a);
+  return hb_launch(ctx, name, false, pf_gemm_kernel<MODE>, dim3(grid), dim3(PF_THREADS), (size_t)PF_SMEM, st, a, tmA, tmB0);
 }
 }  // namespace
 
@@ -490,21 +575,31 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
   const uint8_t* const* lt = rec_tab + (size_t)li * E;
   const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(x_bf16);
   int r;
+  const size_t Pcap = (size_t)S * K;
+  CUtensorMap tm_x, tm_y;
+  PfMapPair tpl;
+  if ((r = pf_make_map(ctx, &tm_x, W.xq_s, (size_t)H / 2, Pcap))) return r;
+  if ((r = pf_make_map(ctx, &tm_y, W.yq, (size_t)I / 2, Pcap))) return r;
+  if ((r = pf_make_map(ctx, &tpl.gu, W.xq_s, (size_t)H / 2, (size_t)I))) return r;          // addresses are stamped per expert on the device
+  if ((r = pf_make_map(ctx, &tpl.dn, W.xq_s, (size_t)I / 2, (size_t)H))) return r;
+  if ((r = hb_launch(ctx, "pf_tmaps", false, pf_tmaps_kernel, dim3((E * 3 + 127) / 128), dim3(128), 0, st, tpl, lt, E, L, W.tmB))) return r;
   for (int s0 = 0; s0 < M; s0 += S) {
     const int n = M - s0 < S ? M - s0 : S, P = n * K;
     const int32_t* sid = ids + (size_t)s0 * K;
     HB_CUDA(ctx, cudaMemsetAsync(W.cnt, 0, (size_t)E * 4, st));
     if ((r = hb_launch(ctx, "pf_count", false, pf_count_kernel, dim3((P + 255) / 256), dim3(256), 0, st, sid, P, E, lt, W.cnt))) return r;
-    if ((r = hb_launch(ctx, "pf_scan", false, pf_scan_kernel, dim3(1), dim3(1024), 0, st, (const int*)W.cnt, E, W.cursor, W.tiles, W.n_tiles))) return r;
+    if ((r = hb_launch(ctx, "pf_scan", false, pf_scan_kernel, dim3(1), dim3(1024), 0, st, (const int*)W.cnt, E, W.cursor, W.tiles, W.n_tiles, W.cnt + E))) return r;
     if ((r = hb_launch(ctx, "pf_fill", false, pf_fill_kernel, dim3((P + 255) / 256), dim3(256), 0, st, sid, P, E, lt, W.cursor, W.perm))) return r;
     if ((r = hbk_a4_quant(ctx, x + (size_t)s0 * H, H, n, H, W.xq, W.xs, W.xg, st))) return r;
+    if ((r = hb_launch(ctx, "pf_gather_q", false, pf_gather_q_kernel, dim3(ctx->sm_count * 8), dim3(256), 0, st, (const int*)W.perm, (const int*)(W.cnt + E), K, H,
+                       (const uint8_t*)W.xq, (const uint8_t*)W.xs, (const float*)W.xg, W.xq_s, W.xs_s, W.xg_s))) return r;
     PfGemmArgs a{};
-    a.tiles = W.tiles; a.n_tiles = W.n_tiles; a.perm = W.perm; a.K_top = K; a.tab = lt; a.L = L; a.limit = limit; a.err = ctx->dev_err;
-    a.aq = W.xq; a.as = W.xs; a.ag = W.xg; a.Kd = H; a.N = I; a.out = W.y; a.ldo = I;
-    if ((r = pf_launch<PF_GU>(ctx, "pf_gemm_gu", a, st))) return r;
+    a.tiles = W.tiles; a.n_tiles = W.n_tiles; a.perm = W.perm; a.tab = lt; a.L = L; a.tmB = W.tmB; a.limit = limit; a.err = ctx->dev_err;
+    a.as = W.xs_s; a.ag = W.xg_s; a.Kd = H; a.N = I; a.out = W.y; a.ldo = I;
+    if ((r = pf_launch<PF_GU>(ctx, "pf_gemm_gu", a, tm_x, tm_x, st))) return r;
     if ((r = hbk_a4_quant(ctx, W.y, I, P, I, W.yq, W.ys, W.yg, st))) return r;
-    a.aq = W.yq; a.as = W.ys; a.ag = W.yg; a.Kd = I; a.N = H; a.out = W.part; a.ldo = H;
-    if ((r = pf_launch<PF_DOWN>(ctx, "pf_gemm_down", a, st))) return r;
+    a.as = W.ys; a.ag = W.yg; a.Kd = I; a.N = H; a.out = W.part; a.ldo = H;
+    if ((r = pf_launch<PF_DOWN>(ctx, "pf_gemm_down", a, tm_y, tm_y, st))) return r;
     const size_t pairs2 = (size_t)n * H / 2;
     const __nv_bfloat16* sh = cmb ? reinterpret_cast<const __nv_bfloat16*>(cmb->shared) + (size_t)s0 * H : nullptr;
     if ((r = hb_launch(ctx, "pf_reduce", false, pf_reduce_kernel, dim3((unsigned)((pairs2 + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16*)W.part, sid,
@@ -524,9 +619,13 @@ int hb_nvfp4_gemm_a4(hb_ctx* ctx, const hb_qmat* W, const uint8_t* xq, const uin
   HB_REQUIRE(ctx, hb_aligned(W->w, 16) && hb_aligned(W->s, 16) && hb_aligned(xq, 16) && hb_aligned(xs, 16) && hb_aligned(y, 16), HB_ERR_INVALID,
              "nvfp4_gemm_a4: operands must be 16-byte aligned");
   PfGemmArgs a{};
-  a.M = M; a.aq = xq; a.as = xs; a.ag = xg; a.Kd = W->K; a.bw = W->w; a.bs = reinterpret_cast<const uint8_t*>(W->s); a.bg = W->g; a.N = W->N;
+  a.M = M; a.as = xs; a.ag = xg; a.Kd = W->K; a.bs = reinterpret_cast<const uint8_t*>(W->s); a.bg = W->g; a.N = W->N;
   a.out = y; a.ldo = ldy; a.err = ctx->dev_err;
-  return pf_launch<PF_PLAIN>(ctx, "pf_gemm_plain", a, reinterpret_cast<cudaStream_t>(stream));
+  CUtensorMap tm_a, tm_b;
+  int r;
+  if ((r = pf_make_map(ctx, &tm_a, xq, (size_t)W->K / 2, (size_t)M))) return r;
+  if ((r = pf_make_map(ctx, &tm_b, W->w, (size_t)W->K / 2, (size_t)W->N))) return r;
+  return pf_launch<PF_PLAIN>(ctx, "pf_gemm_plain", a, tm_a, tm_b, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int hb_fp4_peak_probe(hb_ctx* ctx, int rounds, float* tflops) {
