@@ -13,8 +13,9 @@
 // GEMM kernel: persistent CTAs of 10 warps.  Warp 5 moves the e2m1 codes of both operands with TMA (`cp.async.bulk.tensor`, 128-byte
 // swizzle: the K-major layout the MMA reads).  The activation rows of a tile are contiguous because the quantised rows are first
 // copied into expert order; the weight matrices sit inside expert records at arbitrary addresses, so a small kernel stamps each
-// record's addresses into tensor maps on the device (`tensormap.replace`).  Warps 6-9 bring the e4m3 block scales as 4-byte
-// cp.async copies into the 32×16-byte chunks `tcgen05.cp` moves to tensor memory.  Warp 4 issues `tcgen05.cp` + `tcgen05.mma
+// record's addresses into tensor maps on the device (`tensormap.replace`).  The e4m3 block scales arrive by TMA too, row-major
+// (16 bytes per row and stage); warps 6-9 transpose them in place into the 32×16-byte chunks `tcgen05.cp` moves to tensor
+// memory.  Warp 4 issues `tcgen05.cp` + `tcgen05.mma
 // kind::mxf4nvf4` (block 16, ue4m3 scales: both operands' block scales are applied by the tensor core) and commits to the stage's
 // mbarrier.  Warps 0-3 read the accumulators back with `tcgen05.ld` and run the epilogue.  Every wait is bounded; on a timeout
 // the kernel records a site code in the context's error word, drains its copies, frees its tensor memory and returns.
@@ -31,10 +32,9 @@ constexpr int PF_BM = 128;              // pairs per tile (MMA M)
 constexpr int PF_BN = 256;              // weight rows per tile (MMA N)
 constexpr int PF_BK = 256;              // k values per stage = one 128-byte swizzle row of e2m1 codes
 constexpr int PF_ST = 4;                // stages
-constexpr int PF_LAG = 2;               // loader threads publish a stage this many iterations after issuing it
 constexpr int PF_A_BYTES = PF_BM * 128, PF_B_BYTES = PF_BN * 128;
 constexpr int PF_SFA_BYTES = 4 * 512;   // 4 MMA k-steps × one 128-row chunk
-constexpr int PF_SFB_BYTES = 8 * 512;   // 4 k-steps × two 128-row chunks
+constexpr int PF_SFB_BYTES = 8 * 512;   // two 128-row blocks × 4 k-steps
 constexpr int PF_STAGE = PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + PF_SFB_BYTES;
 constexpr int PF_SMEM = PF_ST * PF_STAGE + 1024 + 256;
 constexpr int PF_THREADS = 10 * 32;
@@ -53,11 +53,11 @@ struct PfGemmArgs {
   int M;                                       // PLAIN only
   const int* perm;                             // pair of a sorted slot (DOWN scatters its rows by it)
   // A operand (quantised activations, tile rows contiguous): codes come through the kernel's tensor-map parameter
-  const uint8_t* as; const float* ag; int Kd;  // scales [rows, Kd/16], per-row global
+  const float* ag; int Kd;                     // per-row global (codes and scales: tensor-map parameters)
   // B operand
   const uint8_t* const* tab; hb_rec_layout L;  // GU / DOWN: expert records
-  const CUtensorMap* tmB;                      // GU / DOWN: [expert][3] tensor maps of w1, w3, w2 (written by pf_tmaps_kernel)
-  const uint8_t* bs; float bg;                 // PLAIN: scales and global of the one matrix [N, Kd] (codes: tensor-map parameter)
+  const CUtensorMap* tmB;                      // GU / DOWN: [expert][6] tensor maps of w1, w3, w2, s1, s3, s2 (written by pf_tmaps_kernel)
+  float bg;                                    // PLAIN: global of the one matrix [N, Kd] (codes and scales: tensor-map parameters)
   int N;                                       // output columns in all (I for GU, H for DOWN, N for PLAIN)
   float limit;
   void* out; int ldo;                          // GU: y bf16 [slots, I]; DOWN: part bf16 [pairs, H]; PLAIN: fp32 [M, ldo]
@@ -106,7 +106,7 @@ __device__ __forceinline__ void pf_cp_commit() { asm volatile("cp.async.commit_g
 template <int N_>
 __device__ __forceinline__ void pf_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N_) : "memory"); }
 
-// 2-D tiled TMA load: box (128 bytes × 128 rows) at byte column c0, row c1 → shared memory, completion in bytes on `bar`
+// 2-D tiled TMA load of the map's box at byte column c0, row c1 → shared memory, completion in bytes on `bar`
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int c0, int c1, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                ::"r"(dst), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
@@ -144,7 +144,8 @@ __device__ __forceinline__ uint4 pf_pack8(const float* v) {
 
 template <int MODE>
 __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs a, const __grid_constant__ CUtensorMap tmA,
-                                                                const __grid_constant__ CUtensorMap tmB0) {
+                                                                const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmSA,
+                                                                const __grid_constant__ CUtensorMap tmSB0) {
   extern __shared__ uint8_t pf_raw[];
   const uint32_t raw = smem_u32(pf_raw), base = (raw + 1023u) & ~1023u;     // swizzle atoms want 1024-byte alignment
   uint8_t* sm = pf_raw + (base - raw);
@@ -153,11 +154,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
   uint64_t* acc_full = empty + PF_ST;                                        // the tile's accumulators are complete
   uint64_t* acc_empty = acc_full + 1;                                        // the epilogue has read them
   uint64_t* mma_done = acc_empty + 1;                                        // the issuing thread's last operation has retired
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mma_done + 1);
+  uint64_t* sf_full = mma_done + 1;                                          // [ST] the stage's row-major scales have landed
+  uint64_t* tr_bar = sf_full + PF_ST;                                        // the 128 transposing threads have read their rows
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tr_bar + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < PF_ST; ++s) { mbar_init(&full[s], 128 + 1); mbar_init(&empty[s], 1); }   // 128 scale loaders + the TMA thread
-    mbar_init(acc_full, 1); mbar_init(acc_empty, 128); mbar_init(mma_done, 1);
+    for (int s = 0; s < PF_ST; ++s) { mbar_init(&full[s], 128 + 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], 1); }   // full: 128 scale threads + the TMA thread
+    mbar_init(acc_full, 1); mbar_init(acc_empty, 128); mbar_init(mma_done, 1); mbar_init(tr_bar, 128);
     mbar_fence_init();
   }
   if (warp == 4) { tmem_alloc(tmem_slot, PF_TMEM_COLS); tmem_relinquish(); }
@@ -171,7 +174,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
   constexpr int NW = MODE == PF_GU ? 128 : 256;                              // output columns per tile
   const int n_nt = a.N / NW, nkb = a.Kd / PF_BK;
   const long long work = (long long)n_tiles * n_nt;                          // tile-major: the CTAs of a wave share activation tiles and expert rows in L2
-  const size_t rows = (size_t)a.Kd / 16;
 
   if (warp == 5) {
     // ------------------------------------------------------------------------------------------------ TMA: codes of both operands, one thread
@@ -181,15 +183,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
       for (long long w = blockIdx.x; w < work && ok; w += gridDim.x) {
         const int ti = (int)(w / n_nt), nt = (int)(w - (long long)ti * n_nt);
         const PfTile tl = pf_tile(a, ti);
-        const CUtensorMap *m0 = &tmB0, *m1 = &tmB0;
+        const CUtensorMap *m0 = &tmB0, *m1 = &tmB0, *q0 = &tmSB0, *q1 = &tmSB0;
         int r0 = nt * 256, r1 = nt * 256 + 128;                               // B rows of the tile's two 128-row boxes
-        if (MODE == PF_GU) { m0 = a.tmB + (size_t)tl.e * 3; m1 = m0 + 1; r0 = r1 = nt * 128; }
-        if (MODE == PF_DOWN) m0 = m1 = a.tmB + (size_t)tl.e * 3 + 2;
-        if (MODE != PF_PLAIN) { tmap_acquire(m0); if (m1 != m0) tmap_acquire(m1); }
+        if (MODE == PF_GU) { m0 = a.tmB + (size_t)tl.e * 6; m1 = m0 + 1; q0 = m0 + 3; q1 = m0 + 4; r0 = r1 = nt * 128; }
+        if (MODE == PF_DOWN) { m0 = m1 = a.tmB + (size_t)tl.e * 6 + 2; q0 = q1 = m0 + 3; }
+        if (MODE != PF_PLAIN) { tmap_acquire(m0); tmap_acquire(q0); if (m1 != m0) { tmap_acquire(m1); tmap_acquire(q1); } }
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const uint32_t stage = it % PF_ST;
           if (!(ok = mbar_wait(&empty[stage], ((it / PF_ST) & 1) ^ 1, a.err, 0x100u))) break;
-          const uint32_t sb = base + stage * PF_STAGE;
+          const uint32_t sb = base + stage * PF_STAGE, sf = sb + PF_A_BYTES + PF_B_BYTES;
+          mbar_expect_tx(&sf_full[stage], PF_SFA_BYTES + PF_SFB_BYTES);      // scales first: they still have to be transposed
+          tma_load_2d(sf, &tmSA, kb * 16, tl.slot0, &sf_full[stage]);
+          tma_load_2d(sf + PF_SFA_BYTES, q0, kb * 16, r0, &sf_full[stage]);
+          tma_load_2d(sf + PF_SFA_BYTES + 2048, q1, kb * 16, r1, &sf_full[stage]);
           mbar_expect_tx(&full[stage], PF_A_BYTES + PF_B_BYTES);
           tma_load_2d(sb, &tmA, kb * 128, tl.slot0, &full[stage]);
           tma_load_2d(sb + PF_A_BYTES, m0, kb * 128, r0, &full[stage]);
@@ -198,44 +204,30 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
       }
     }
   } else if (warp >= 6) {
-    // ------------------------------------------------------------------------------------------------ scale loaders: thread lt owns A row lt, B rows lt and lt + 128
+    // ------------------------------------------------------------------------------------------------ scale transposers: thread lt owns row lt of each 128-row block
+    // A block arrives row-major, 16 bytes per row = 4 MMA k-steps × 4 scales.  tcgen05.cp wants, per k-step, 32 rows × 16 bytes
+    // where row l holds the 4 scales of rows l, l + 32, l + 64, l + 96: a 4-byte-word transpose, done in place.
     const int lt = threadIdx.x - 192;
-    const uint32_t sfo = (uint32_t)((lt & 31) * 16 + (lt >> 5) * 4);
+    const uint32_t src = (uint32_t)lt * 16, dst = (uint32_t)((lt & 31) * 16 + (lt >> 5) * 4);
     uint32_t it = 0;
     bool ok = true;
     for (long long w = blockIdx.x; w < work && ok; w += gridDim.x) {
-      const int ti = (int)(w / n_nt), nt = (int)(w - (long long)ti * n_nt);
-      const PfTile tl = pf_tile(a, ti);
-      const size_t slot = (size_t)(tl.slot0 + min(lt, tl.m - 1));            // rows past the tile's end repeat its last row (never stored)
-      const uint8_t* asp = a.as + slot * rows;
-      const uint8_t *s0, *s1;
-      if (MODE == PF_PLAIN) { s0 = a.bs + (size_t)(nt * 256 + lt) * rows; s1 = s0 + 128 * rows; }
-      else {
-        const uint8_t* rec = a.tab[tl.e];
-        if (MODE == PF_GU) { s0 = rec + a.L.s1 + (size_t)(nt * 128 + lt) * rows; s1 = rec + a.L.s3 + (size_t)(nt * 128 + lt) * rows; }
-        else { s0 = rec + a.L.s2 + (size_t)(nt * 256 + lt) * rows; s1 = s0 + 128 * rows; }
-      }
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const uint32_t stage = it % PF_ST;
-        if (!(ok = mbar_wait(&empty[stage], ((it / PF_ST) & 1) ^ 1, a.err, 0x100u))) break;
-        const uint32_t sb = base + stage * PF_STAGE + PF_A_BYTES + PF_B_BYTES;
-#pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) {                                   // the row's 16 scales of this stage: 4 per MMA k-step
-          pf_cp4(sb + j * 512 + sfo, asp + (size_t)kb * 16 + j * 4);
-          pf_cp4(sb + PF_SFA_BYTES + (2 * j) * 512 + sfo, s0 + (size_t)kb * 16 + j * 4);
-          pf_cp4(sb + PF_SFA_BYTES + (2 * j + 1) * 512 + sfo, s1 + (size_t)kb * 16 + j * 4);
-        }
-        pf_cp_commit();
-        if (it >= PF_LAG) {                                                  // the copies issued LAG iterations ago have landed: publish them
-          pf_cp_wait<PF_LAG>();
-          fence_proxy_async_smem();
-          mbar_arrive(&full[(it - PF_LAG) % PF_ST]);
-        }
+        if (!(ok = mbar_wait(&sf_full[stage], (it / PF_ST) & 1, a.err, 0x4000u))) break;
+        uint8_t* sf = sm + stage * PF_STAGE + PF_A_BYTES + PF_B_BYTES;
+        const uint4 va = *reinterpret_cast<const uint4*>(sf + src), vb = *reinterpret_cast<const uint4*>(sf + 2048 + src),
+                    vc = *reinterpret_cast<const uint4*>(sf + 4096 + src);
+        mbar_arrive(tr_bar);                                                 // every row of the stage is in registers before any is overwritten
+        if (!(ok = mbar_wait(tr_bar, it & 1, a.err, 0x8000u))) break;
+        uint32_t* o = reinterpret_cast<uint32_t*>(sf + dst);
+        o[0] = va.x; o[128] = va.y; o[256] = va.z; o[384] = va.w;            // k-step j of a block sits 512 bytes after k-step j - 1
+        o[512] = vb.x; o[640] = vb.y; o[768] = vb.z; o[896] = vb.w;
+        o[1024] = vc.x; o[1152] = vc.y; o[1280] = vc.z; o[1408] = vc.w;
+        fence_proxy_async_smem();
+        mbar_arrive(&full[stage]);
       }
     }
-    pf_cp_wait<0>();
-    fence_proxy_async_smem();
-    for (uint32_t j = it >= PF_LAG ? it - PF_LAG : 0; j < it; ++j) mbar_arrive(&full[j % PF_ST]);
   } else if (warp == 4) {
     // ------------------------------------------------------------------------------------------------ MMA issue: one thread
     if (lane == 0) {
@@ -252,8 +244,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
 #pragma unroll
           for (uint32_t j = 0; j < 4; ++j) {
             tc_cp_sf(sfc + 4 * j, pf_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + j * 512));
-            tc_cp_sf(sfc + 16 + 8 * j, pf_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + (2 * j) * 512));
-            tc_cp_sf(sfc + 16 + 8 * j + 4, pf_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + (2 * j + 1) * 512));
+            tc_cp_sf(sfc + 16 + 8 * j, pf_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + j * 512));
+            tc_cp_sf(sfc + 16 + 8 * j + 4, pf_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + 2048 + j * 512));
           }
           const uint64_t ad = pf_desc_sw128(sb), bd = pf_desc_sw128(sb + PF_A_BYTES);
 #pragma unroll
@@ -443,19 +435,21 @@ __global__ void pf_gather_q_kernel(const int* __restrict__ perm, const int* __re
 
 // Tensor maps of every resident expert's three matrices: the host encodes one map per matrix shape (on any valid address), this
 // kernel copies it and stamps in the address of the matrix inside the expert's record.
-struct PfMapPair { CUtensorMap gu, dn; };                                   // [I rows × H/2 bytes] for w1 / w3, [H rows × I/2 bytes] for w2
-__global__ void pf_tmaps_kernel(const __grid_constant__ PfMapPair tpl, const uint8_t* const* __restrict__ tab, int E, hb_rec_layout L,
+struct PfMapSet { CUtensorMap gu, dn, gu_s, dn_s; };    // codes [I × H/2] (w1, w3), [H × I/2] (w2); scales [I × H/16] (s1, s3), [H × I/16] (s2)
+__global__ void pf_tmaps_kernel(const __grid_constant__ PfMapSet tpl, const uint8_t* const* __restrict__ tab, int E, hb_rec_layout L,
                                 CUtensorMap* __restrict__ out) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= E * 3) return;
-  const int e = i / 3, mat = i - e * 3;
+  if (i >= E * 6) return;
+  const int e = i / 6, mat = i - e * 6;                                      // w1, w3, w2, s1, s3, s2
   const uint8_t* rec = tab[e];
   if (!rec) return;
-  const uint4* src = reinterpret_cast<const uint4*>(mat == 2 ? &tpl.dn : &tpl.gu);
+  const CUtensorMap* t = mat < 2 ? &tpl.gu : mat == 2 ? &tpl.dn : mat < 5 ? &tpl.gu_s : &tpl.dn_s;
+  const uint64_t offs[6] = {L.w1, L.w3, L.w2, L.s1, L.s3, L.s2};
+  const uint4* src = reinterpret_cast<const uint4*>(t);
   uint4* dst = reinterpret_cast<uint4*>(out + i);
 #pragma unroll
   for (int j = 0; j < 8; ++j) dst[j] = src[j];
-  const uint64_t addr = reinterpret_cast<uint64_t>(rec + (mat == 0 ? L.w1 : mat == 1 ? L.w3 : L.w2));
+  const uint64_t addr = reinterpret_cast<uint64_t>(rec + offs[mat]);
   asm volatile("tensormap.replace.tile.global_address.global.b1024.b64 [%0], %1;" ::"l"(dst), "l"(addr) : "memory");
   asm volatile("fence.proxy.tensormap::generic.release.gpu;" ::: "memory");
 }
@@ -501,7 +495,7 @@ size_t pf_carve(void* ws, int S, int K, int E, int H, int I, PfWs* w) {
   PfWs t;
   t.cnt = (int*)take((size_t)(E + 1) * 4); t.cursor = (int*)take((size_t)E * 4); t.n_tiles = (int*)take(4);
   t.tiles = (PfTile*)take((P / PF_BM + E) * sizeof(PfTile)); t.perm = (int*)take(P * 4);
-  t.tmB = (CUtensorMap*)take((size_t)E * 3 * sizeof(CUtensorMap));
+  t.tmB = (CUtensorMap*)take((size_t)E * 6 * sizeof(CUtensorMap));
   t.y = (__nv_bfloat16*)take(P * I * 2); t.part = (__nv_bfloat16*)take(P * H * 2);
   t.xq = (uint8_t*)take((size_t)S * H / 2); t.xs = (uint8_t*)take((size_t)S * H / 16); t.xg = (float*)take((size_t)S * 4);
   t.xq_s = (uint8_t*)take(P * H / 2); t.xs_s = (uint8_t*)take(P * H / 16); t.xg_s = (float*)take(P * 4);
@@ -522,21 +516,23 @@ PfEncodeFn pf_encode_fn() {
   }
   return fn;
 }
-// map of a byte matrix [n_rows][row_bytes] (e2m1 codes, two per byte), boxes of 128 bytes × 128 rows, 128-byte swizzle
-int pf_make_map(hb_ctx* ctx, CUtensorMap* m, const void* base, size_t row_bytes, size_t n_rows) {
+// map of a byte matrix [n_rows][row_bytes] with boxes of 128 rows: e2m1 codes (two per byte) in boxes 128 bytes wide under the
+// 128-byte swizzle, or e4m3 block scales in boxes 16 bytes wide, unswizzled
+int pf_make_map(hb_ctx* ctx, CUtensorMap* m, const void* base, size_t row_bytes, size_t n_rows, bool scales = false) {
   PfEncodeFn fn = pf_encode_fn();
   HB_REQUIRE(ctx, fn, HB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)n_rows}, strides[1] = {(cuuint64_t)row_bytes};
-  const cuuint32_t box[2] = {128, 128}, estr[2] = {1, 1};
+  const cuuint32_t box[2] = {scales ? 16u : 128u, 128}, estr[2] = {1, 1};
   const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        scales ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   HB_REQUIRE(ctx, r == CUDA_SUCCESS, HB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for %zu rows of %zu bytes at %p", (int)r, n_rows, row_bytes, base);
   return HB_OK;
 }
 template <int MODE>
-int pf_launch(hb_ctx* ctx, const char* name, const PfGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB0, cudaStream_t st) {
+int pf_launch(hb_ctx* ctx, const char* name, const PfGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap& tmSA,
+              const CUtensorMap& tmSB0, cudaStream_t st) {
   const int grid = ctx->max_ctas > 0 && ctx->max_ctas < ctx->sm_count ? ctx->max_ctas : ctx->sm_count;
-  return hb_launch(ctx, name, false, pf_gemm_kernel<MODE>, dim3(grid), dim3(PF_THREADS), (size_t)PF_SMEM, st, a, tmA, tmB0);
+  return hb_launch(ctx, name, false, pf_gemm_kernel<MODE>, dim3(grid), dim3(PF_THREADS), (size_t)PF_SMEM, st, a, tmA, tmB0, tmSA, tmSB0);
 }
 }  // namespace
 
@@ -576,13 +572,17 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
   const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(x_bf16);
   int r;
   const size_t Pcap = (size_t)S * K;
-  CUtensorMap tm_x, tm_y;
-  PfMapPair tpl;
+  CUtensorMap tm_x, tm_y, tm_xs, tm_ys;
+  PfMapSet tpl;
   if ((r = pf_make_map(ctx, &tm_x, W.xq_s, (size_t)H / 2, Pcap))) return r;
   if ((r = pf_make_map(ctx, &tm_y, W.yq, (size_t)I / 2, Pcap))) return r;
+  if ((r = pf_make_map(ctx, &tm_xs, W.xs_s, (size_t)H / 16, Pcap, true))) return r;
+  if ((r = pf_make_map(ctx, &tm_ys, W.ys, (size_t)I / 16, Pcap, true))) return r;
   if ((r = pf_make_map(ctx, &tpl.gu, W.xq_s, (size_t)H / 2, (size_t)I))) return r;          // addresses are stamped per expert on the device
   if ((r = pf_make_map(ctx, &tpl.dn, W.xq_s, (size_t)I / 2, (size_t)H))) return r;
-  if ((r = hb_launch(ctx, "pf_tmaps", false, pf_tmaps_kernel, dim3((E * 3 + 127) / 128), dim3(128), 0, st, tpl, lt, E, L, W.tmB))) return r;
+  if ((r = pf_make_map(ctx, &tpl.gu_s, W.xq_s, (size_t)H / 16, (size_t)I, true))) return r;
+  if ((r = pf_make_map(ctx, &tpl.dn_s, W.xq_s, (size_t)I / 16, (size_t)H, true))) return r;
+  if ((r = hb_launch(ctx, "pf_tmaps", false, pf_tmaps_kernel, dim3((E * 6 + 127) / 128), dim3(128), 0, st, tpl, lt, E, L, W.tmB))) return r;
   for (int s0 = 0; s0 < M; s0 += S) {
     const int n = M - s0 < S ? M - s0 : S, P = n * K;
     const int32_t* sid = ids + (size_t)s0 * K;
@@ -595,11 +595,11 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
                        (const uint8_t*)W.xq, (const uint8_t*)W.xs, (const float*)W.xg, W.xq_s, W.xs_s, W.xg_s))) return r;
     PfGemmArgs a{};
     a.tiles = W.tiles; a.n_tiles = W.n_tiles; a.perm = W.perm; a.tab = lt; a.L = L; a.tmB = W.tmB; a.limit = limit; a.err = ctx->dev_err;
-    a.as = W.xs_s; a.ag = W.xg_s; a.Kd = H; a.N = I; a.out = W.y; a.ldo = I;
-    if ((r = pf_launch<PF_GU>(ctx, "pf_gemm_gu", a, tm_x, tm_x, st))) return r;
+    a.ag = W.xg_s; a.Kd = H; a.N = I; a.out = W.y; a.ldo = I;
+    if ((r = pf_launch<PF_GU>(ctx, "pf_gemm_gu", a, tm_x, tm_x, tm_xs, tm_xs, st))) return r;
     if ((r = hbk_a4_quant(ctx, W.y, I, P, I, W.yq, W.ys, W.yg, st))) return r;
-    a.as = W.ys; a.ag = W.yg; a.Kd = I; a.N = H; a.out = W.part; a.ldo = H;
-    if ((r = pf_launch<PF_DOWN>(ctx, "pf_gemm_down", a, tm_y, tm_y, st))) return r;
+    a.ag = W.yg; a.Kd = I; a.N = H; a.out = W.part; a.ldo = H;
+    if ((r = pf_launch<PF_DOWN>(ctx, "pf_gemm_down", a, tm_y, tm_y, tm_ys, tm_ys, st))) return r;
     const size_t pairs2 = (size_t)n * H / 2;
     const __nv_bfloat16* sh = cmb ? reinterpret_cast<const __nv_bfloat16*>(cmb->shared) + (size_t)s0 * H : nullptr;
     if ((r = hb_launch(ctx, "pf_reduce", false, pf_reduce_kernel, dim3((unsigned)((pairs2 + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16*)W.part, sid,
@@ -619,13 +619,15 @@ int hb_nvfp4_gemm_a4(hb_ctx* ctx, const hb_qmat* W, const uint8_t* xq, const uin
   HB_REQUIRE(ctx, hb_aligned(W->w, 16) && hb_aligned(W->s, 16) && hb_aligned(xq, 16) && hb_aligned(xs, 16) && hb_aligned(y, 16), HB_ERR_INVALID,
              "nvfp4_gemm_a4: operands must be 16-byte aligned");
   PfGemmArgs a{};
-  a.M = M; a.as = xs; a.ag = xg; a.Kd = W->K; a.bs = reinterpret_cast<const uint8_t*>(W->s); a.bg = W->g; a.N = W->N;
+  a.M = M; a.ag = xg; a.Kd = W->K; a.bg = W->g; a.N = W->N;
   a.out = y; a.ldo = ldy; a.err = ctx->dev_err;
-  CUtensorMap tm_a, tm_b;
+  CUtensorMap tm_a, tm_b, tm_as, tm_bs;
   int r;
   if ((r = pf_make_map(ctx, &tm_a, xq, (size_t)W->K / 2, (size_t)M))) return r;
   if ((r = pf_make_map(ctx, &tm_b, W->w, (size_t)W->K / 2, (size_t)W->N))) return r;
-  return pf_launch<PF_PLAIN>(ctx, "pf_gemm_plain", a, tm_a, tm_b, reinterpret_cast<cudaStream_t>(stream));
+  if ((r = pf_make_map(ctx, &tm_as, xs, (size_t)W->K / 16, (size_t)M, true))) return r;
+  if ((r = pf_make_map(ctx, &tm_bs, W->s, (size_t)W->K / 16, (size_t)W->N, true))) return r;
+  return pf_launch<PF_PLAIN>(ctx, "pf_gemm_plain", a, tm_a, tm_b, tm_as, tm_bs, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int hb_fp4_peak_probe(hb_ctx* ctx, int rounds, float* tflops) {
