@@ -217,10 +217,17 @@ def run_ours(args):
 
     import eke_hive_b200 as E
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    t_start = time.perf_counter()
+
+    def trace(msg):
+        """Progress lines on stderr when BENCH_TRACE is set (stdout stays one JSON line)."""
+        if os.environ.get("BENCH_TRACE"):
+            print(f"[bench r{rank} +{time.perf_counter() - t_start:6.1f}s] {msg}", file=sys.stderr, flush=True)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        trace("process group up")
     H, I, Ex, K, L = CFG["H"], CFG["I"], CFG["E"], CFG["K"], args.layers or CFG["L"]
     ctx = E.context()
     sampler = ClockSampler(str(torch.cuda.get_device_properties(local).uuid), local)
@@ -242,6 +249,7 @@ def run_ours(args):
     tab = torch.from_numpy(tab_host.reshape(-1)).to(dev)
     shared_ptr = [layers.ptr(li, n_loc) for li in range(L)]
     setup_s = time.perf_counter() - t_setup
+    trace(f"weights ready in {setup_s:.1f}s")
 
     results = {}
     batches = [args.batch] if args.batch else list(CFG["batches"])
@@ -275,6 +283,7 @@ def run_ours(args):
         with torch.cuda.stream(side):
             run_layers(0)
             side.synchronize()
+            trace(f"B={B}: eager pass done")
             n0 = ctx.launches
             for s in range(NSETS):
                 g = torch.cuda.CUDAGraph()
@@ -284,6 +293,7 @@ def run_ours(args):
             launches_per_step = (ctx.launches - n0) // NSETS
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        trace(f"B={B}: graphs captured")
 
         def timed(nsteps, fn):
             if world > 1:
@@ -309,6 +319,7 @@ def run_ours(args):
         sampler.active = False
         ctx.check_device()
         ms_step = ms / args.steps
+        trace(f"B={B}: timed {ms_step:.3f} ms/step")
         ids_h = ids.cpu().numpy()
         U = np.array([[len(np.unique(ids_h[s, li])) + 1 for li in range(L)] for s in range(NSETS)], np.float64)   # + shared
         if world > 1:
@@ -355,7 +366,7 @@ def run_ours(args):
                 prof = ctx.profile_read()
                 ctx.profile(False)
                 prof = {k: {"launches": v[0], "total_ms": v[1], "mean_us": v[1] * 1e3 / max(v[0], 1)} for k, v in prof.items()}
-        del logits, x, out, ids, wts, graphs
+        del logits, x, out, ids, wts, graphs, g
         torch.cuda.empty_cache()
 
     head = results[head_B]
@@ -390,10 +401,22 @@ def run_ours(args):
         except Exception as ex:  # the reference library was never built on this machine
             line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "reference", "sample": f"unavailable: {ex}"}
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
+        # Tearing down an NCCL communicator waits for every CUDA graph that captured its collectives to be destroyed, and a graph
+        # that is still referenced somewhere makes that wait endless.  Release what this function holds, and do not let the
+        # teardown outlive a short grace period: the result is printed, the process may simply exit.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        g = graphs = ep = run_layers = e2e_step = None
+        import gc
+        gc.collect()
+        threading.Timer(20.0, lambda: os._exit(0)).start()
+        try:
+            dist.destroy_process_group()
+        finally:
+            sys.stdout.flush()
+            os._exit(0)
 
 
 def main():
