@@ -2,6 +2,8 @@
 """Benchmark of the quantized routed-expert decode path (Qwen3-Next-shaped MoE, NVFP4 weights, bf16 activations).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --workload prefill [--tokens T]      one DeepSeek-shaped prefill MoE layer (tcgen05 FP4 grouped GEMM), FP4 roofline
+    python bench.py --workload dense                     the dense 27B-style MLP GEMVs (NVFP4, 3-bit, 2-bit), HBM roofline
 
 One "step" is one decode step of B tokens through the 48 MoE layers (router → routed NVFP4 experts → NVFP4 shared expert →
 combine), each layer with its own weights, so a step streams ≈ 48 × U × 1.77 MB of distinct expert records (far more than the
@@ -419,6 +421,132 @@ def run_ours(args):
             os._exit(0)
 
 
+# ------------------------------------------------------------------------------------------------ side workloads (one GPU)
+def _timed(torch, fn, n):
+    fn(); torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record(); torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / n
+
+
+def run_prefill(args):
+    """BASELINE config 4 (DeepSeek-shaped prefill) on one GPU: one MoE layer, H 7168, I 2048, 256 routed experts (6.3 GB resident),
+    top-8, T tokens, NVFP4 weights and NVFP4 activations; plus a dense W4A4 GEMM and the measured FP4 tensor-pipe ceiling."""
+    import torch
+    import eke_hive_b200 as E
+    dev = torch.device("cuda", 0)
+    ctx = E.context()
+    H, I, Ex, K, T = 7168, 2048, 256, 8, args.tokens
+    peak = E.fp4_peak_probe(8192)
+    rb = E.ExpertRecLayout.make(H, I)
+    blob = torch.randint(0, 256, (Ex, rb.total), dtype=torch.uint8, device=dev)          # e2m1 codes: any bytes
+    for off, n in ((rb.s1, I * H // 16), (rb.s3, I * H // 16), (rb.s2, H * I // 16)):    # e4m3 scales 2^-2 .. 2: finite, positive
+        blob[:, off:off + n] = torch.randint(0x28, 0x48, (Ex, n), dtype=torch.uint8, device=dev)
+    blob[:, rb.g:rb.g + 12] = torch.from_numpy(np.array([0.003, 0.003, 0.004], np.float32).view(np.uint8)).to(dev)
+    tab = torch.tensor([blob[e].data_ptr() for e in range(Ex)], dtype=torch.int64, device=dev)
+    g = torch.Generator(device=dev); g.manual_seed(4)
+    sets = []
+    for _ in range(2):
+        logits = torch.randn((T, Ex), device=dev, generator=g)
+        w, ids = torch.topk(torch.softmax(logits, -1), K)
+        sets.append((ids.to(torch.int32).contiguous(), w.contiguous(), torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)))
+    ws = torch.empty(E.moe_prefill_ws_bytes(T, K, Ex, H, I), dtype=torch.uint8, device=dev)
+    out = torch.empty((T, H), dtype=torch.float32, device=dev)
+    it = [0]
+
+    def layer():
+        ids, w, x = sets[it[0] % 2]; it[0] += 1
+        E.fn_moe_prefill(tab, 0, Ex, ids, w, x, H, I, out=out, ws=ws, S=T, ctx=ctx)
+    for _ in range(max(args.warmup, 3)):
+        layer()
+    ms = _timed(torch, layer, args.steps)
+    ctx.profile(True); layer(); layer(); prof = ctx.profile_read(); ctx.profile(False)
+    ctx.check_device()
+    prof = {k: {"launches": v[0], "mean_us": v[1] * 1e3 / max(v[0], 1)} for k, v in prof.items()}
+    flops = 2.0 * T * K * 3 * H * I
+    gemm_us = prof["pf_gemm_gu"]["mean_us"] + prof["pf_gemm_down"]["mean_us"]
+    M, N, Kd = 16384, 8192, 8192
+    xq, xs, xg = E.a4_quant(torch.randn((M, Kd), device=dev, generator=g).to(torch.bfloat16))
+    W = E.GMat(E.FMT_NVFP4, N, Kd, torch.randint(0, 256, (N, Kd // 2), dtype=torch.uint8, device=dev),
+               torch.randint(0x28, 0x48, (N, Kd // 16), dtype=torch.uint8, device=dev), None, 0.01)
+    y = torch.empty((M, N), dtype=torch.float32, device=dev)
+    dms = _timed(torch, lambda: E.nvfp4_gemm_a4(W, xq, xs, xg, y=y, ctx=ctx), args.steps)
+    line = {"metric": "moe_prefill_layer_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "ms_per_layer": ms,
+            "dtype": "e2m1 x e2m1 with ue4m3 block scales, f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"deepseek-shaped MoE prefill layer: hidden 7168, 256 routed experts top-8, intermediate 2048, T={T}, NVFP4 W4A4",
+                       "l2": "6.3 GB of expert records per layer (larger than L2)"},
+            "layer_TFLOPs": flops / (ms * 1e-3) / 1e12,
+            "roofline": {"bound": "tensor", "kernel": "pf_gemm_kernel (gate/up + down)", "achieved": flops / (gemm_us * 1e-6) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                         "frac": flops / (gemm_us * 1e-6) / 1e12 / peak, "peak_source": "hb_fp4_peak_probe on this GPU (dense FP4, resident operands)", "traffic": None},
+            "dense_gemm_a4": {"M": M, "N": N, "K": Kd, "ms": dms, "TFLOPs": 2.0 * M * N * Kd / (dms * 1e-3) / 1e12,
+                              "frac_of_measured_fp4_peak": 2.0 * M * N * Kd / (dms * 1e-3) / 1e12 / peak},
+            "kernels": prof}
+    print(json.dumps(line), flush=True)
+
+
+def run_dense(args):
+    """BASELINE config 5 (dense 27B-style MLP decode): one FFN layer = fused gate/up GEMV + down GEMV, hidden 5120, FFN 17408, M rows,
+    for the NVFP4, 3-bit and 2-bit group-64 formats; 12 distinct layers' matrices cycled so L2 cannot serve repeats."""
+    import torch
+    import eke_hive_b200 as E
+    dev = torch.device("cuda", 0)
+    ctx = E.context()
+    H, I, n = 5120, 17408, 12
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+
+    def mk(fmt, N, K):
+        mats = []
+        for _ in range(n):
+            if fmt == E.FMT_NVFP4:
+                mats.append(E.GMat(fmt, N, K, torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev),
+                                   torch.randint(0x28, 0x48, (N, K // 16), dtype=torch.uint8, device=dev), None, 0.003))
+            else:
+                nb = N * K // 4 + (N * K // 8 if fmt == E.FMT_LB3_G64 else 0)
+                mats.append(E.GMat(fmt, N, K, torch.randint(0, 256, (nb,), dtype=torch.uint8, device=dev),
+                                   (torch.rand((N, K // 64), device=dev) * 0.01 + 0.005).to(torch.float16), (torch.rand((N, K // 64), device=dev) * 3).to(torch.float16)))
+        return mats
+    res = []
+    for fmt, name, bpe in ((E.FMT_NVFP4, "nvfp4", 0.5625), (E.FMT_LB3_G64, "lb3_g64", 0.4375), (E.FMT_LB2_G64, "lb2_g64", 0.3125)):
+        gs, us, ds = mk(fmt, I, H), mk(fmt, I, H), mk(fmt, H, I)
+        for M in (1, 8):
+            x = torch.randn((M, H), device=dev).to(torch.bfloat16)
+            ws = torch.empty(max(E.dense_gemv_ws_bytes(fmt, I, H, 2), E.dense_gemv_ws_bytes(fmt, H, I, 1)), dtype=torch.uint8, device=dev)
+            act = torch.empty((M, I), dtype=torch.bfloat16, device=dev); y = torch.empty((M, H), dtype=torch.bfloat16, device=dev)
+
+            def layer(i):
+                E.dense_gemv_gu(gs[i % n], us[i % n], x, act=act, ws=ws, ctx=ctx); E.dense_gemv(ds[i % n], act, y=y, ws=ws, ctx=ctx)
+            for i in range(4):
+                layer(i)
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for i in range(n):
+                    layer(i)
+            us_layer = _timed(torch, gr.replay, max(args.steps // 4, 5)) * 1e3 / n
+            by = 3 * H * I * bpe + M * (2 * H + I) * 2
+            res.append({"fmt": name, "M": M, "us_per_ffn_layer": us_layer, "algorithmic_MB": by / 1e6, "achieved_GBps": by / us_layer / 1e3,
+                        "frac_of_measured_hbm": by / us_layer / 1e3 / peak})
+            del gr
+        del gs, us, ds
+        torch.cuda.empty_cache()
+    ctx.check_device()
+    head = res[0]
+    print(json.dumps({"metric": "dense_ffn_layer_GBps", "value": head["achieved_GBps"], "unit": "GB/s", "n_gpus": 1, "data": "synthetic",
+                      "config": {"workload": "dense 27B-style MLP decode: hidden 5120, FFN 17408, gate/up + down GEMV, M in {1, 8}",
+                                 "l2": "12 layers' matrices cycled (1.2-1.8 GB, larger than L2)"},
+                      "roofline": {"bound": "hbm", "kernel": "dense_stream_kernel", "achieved": head["achieved_GBps"], "peak": peak, "unit": "GB/s",
+                                   "frac": head["frac_of_measured_hbm"], "traffic": None},
+                      "per_case": res}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -427,11 +555,19 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=0, help="run one batch size only (default: 1, 4, 8, 16; headline 16)")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than 48 (development only; the number is then not the benchmark's)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "dense"],
+                    help="decode = the benchmark proper (BASELINE config 2); prefill = one config-4 MoE layer on the FP4 tensor cores; "
+                         "dense = the config-5 MLP GEMVs (one GPU each; their own JSON line)")
+    ap.add_argument("--tokens", type=int, default=8192, help="--workload prefill: tokens per layer call")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for the baseline leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.impl == "reference":
+    if args.workload == "prefill":
+        run_prefill(args)
+    elif args.workload == "dense":
+        run_dense(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

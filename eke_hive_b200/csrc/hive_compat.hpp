@@ -96,6 +96,20 @@ inline void fn_moe_decode_routed(const glm::ExpertRecLayout&, const int32_t* ids
   hb_pf_combine c{shared, lg, ld, col, out};
   b200::check(hb_moe_decode_routed(b200::ctx(), ids, w, M, K, rec_tab, li, E, x, H, I, 0.f, &c, ws, st));
 }
+// Prefill (engine/include/hive/qwen/fn_moe.h:46-61).  This library's grouped GEMM is the NVFP4-activation form (the reference's
+// fn_moe_prefill_set_a4(true)); fn_moe_prefill_a4() therefore reports true and the setter refuses false.
+inline bool fn_moe_prefill_supported(int H, int I) { return hb_moe_prefill_supported(H, I) > 0; }
+inline bool fn_moe_prefill_a4() { return true; }
+inline void fn_moe_prefill_set_a4(bool on) {
+  if (!on) throw b200::Error(HB_ERR_UNSUPPORTED, "fn_moe_prefill: only the NVFP4-activation (W4A4) grouped GEMM is built; use the decode operators for bf16 activations");
+}
+inline size_t fn_moe_prefill_ws_bytes(int S, int K, int E, int H, int I) { return hb_moe_prefill_ws_bytes(S, K, E, H, I); }
+inline void fn_moe_prefill(const glm::ExpertRecLayout&, const uint8_t* const* tab, int li, int E, const int32_t* ids, const float* w, int M, int K,
+                           const __nv_bfloat16* x, int H, int I, float* out, void* ws, int S, cudaStream_t st, const FnPfCombine* cmb = nullptr) {
+  hb_pf_combine c{};
+  if (cmb) c = hb_pf_combine{cmb->shared, cmb->lg, cmb->ld, cmb->col, cmb->out};
+  b200::check(hb_moe_prefill(b200::ctx(), tab, li, E, ids, w, M, K, x, H, I, 0.f, out, ws, S, st, cmb ? &c : nullptr));
+}
 inline void router_softmax_topk(const float* logits, int ld, int M, int E, int k, bool renorm, int32_t* ids, float* w, int32_t* ids_host, float* w_host,
                                 cudaStream_t st) {
   b200::check(hb_route_softmax_topk(b200::ctx(), logits, ld, M, E, k, renorm ? 1 : 0, 1, ids, w, st));
@@ -113,3 +127,19 @@ inline void build_moe_pairs(const int32_t* ids, const float* w, int M, int K, co
   b200::check(hb_build_moe_pairs(b200::ctx(), ids, w, M, K, rec_tab, li, E, reinterpret_cast<hb_moe_pair*>(pairs), st));
 }
 }  // namespace hive::qwen
+
+// Dense decode GEMV of the 27B-style MLP (engine/include/hive/q27/q27_kernels.h:17-64).  GMat here carries the formats this library
+// streams: NVFP4 as in the reference, plus the 3-/2-bit group-64 layouts hb_qmat defines.  The workspace the reference keeps
+// inside its kernels is explicit: ws ≥ hb_dense_gemv_ws_bytes(fmt, N, K, 1 or 2).
+namespace hive::q27 {
+struct GMat { hb_qmat m; };
+namespace k {
+inline size_t gemv_ws_bytes(const GMat& W, int n_mats = 1) { return hb_dense_gemv_ws_bytes(W.m.fmt, W.m.N, W.m.K, n_mats); }
+inline void gemv(const GMat& W, const __nv_bfloat16* x, int ldx, int M, __nv_bfloat16* yb, float* yf, int ldy, void* ws, cudaStream_t st) {
+  b200::check(hb_dense_gemv(b200::ctx(), &W.m, x, ldx, M, yb, yf, ldy, ws, st));
+}
+inline void gemv_gu(const GMat& G, const GMat& U, const __nv_bfloat16* x, int ldx, int M, __nv_bfloat16* act, int lda, void* ws, cudaStream_t st) {
+  b200::check(hb_dense_gemv_gu(b200::ctx(), &G.m, &U.m, x, ldx, M, act, lda, ws, st));
+}
+}  // namespace k
+}  // namespace hive::q27
