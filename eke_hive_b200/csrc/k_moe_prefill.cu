@@ -37,7 +37,7 @@ constexpr int PF_SFA_BYTES = 4 * 512;   // 4 MMA k-steps × one 128-row chunk
 constexpr int PF_SFB_BYTES = 8 * 512;   // two 128-row blocks × 4 k-steps
 constexpr int PF_STAGE = PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + PF_SFB_BYTES;
 constexpr int PF_SMEM = PF_ST * PF_STAGE + 1024 + 256;
-constexpr int PF_THREADS = 10 * 32;
+constexpr int PF_THREADS = 14 * 32;     // warps 0-3 and 10-13 epilogue, 4 MMA issue, 5 TMA, 6-9 scale transposition
 constexpr int PF_TMEM_COLS = 512;
 constexpr int PF_SF_COL0 = 256;         // accumulator: columns [0, 256); scales of stage s: [256 + 48 s, 256 + 48 s + 48)
 static_assert(PF_STAGE % 1024 == 0, "stage buffers must keep the 1024-byte alignment of the swizzle atom");
@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < PF_ST; ++s) { mbar_init(&full[s], 128 + 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], 1); }   // full: 128 scale threads + the TMA thread
-    mbar_init(acc_full, 1); mbar_init(acc_empty, 128); mbar_init(mma_done, 1); mbar_init(tr_bar, 128);
+    mbar_init(acc_full, 1); mbar_init(acc_empty, 256); mbar_init(mma_done, 1); mbar_init(tr_bar, 128);
     mbar_fence_init();
   }
   if (warp == 4) { tmem_alloc(tmem_slot, PF_TMEM_COLS); tmem_relinquish(); }
@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
         }
       }
     }
-  } else if (warp >= 6) {
+  } else if (warp >= 6 && warp < 10) {
     // ------------------------------------------------------------------------------------------------ scale transposers: thread lt owns row lt of each 128-row block
     // A block arrives row-major, 16 bytes per row = 4 MMA k-steps × 4 scales.  tcgen05.cp wants, per k-step, 32 rows × 16 bytes
     // where row l holds the 4 scales of rows l, l + 32, l + 64, l + 96: a 4-byte-word transpose, done in place.
@@ -258,10 +258,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
       tc_commit(mma_done);                                                   // nothing of this thread's is in flight when tensor memory is freed
       mbar_wait(mma_done, 0, a.err, 0x800u);
     }
-  } else {
-    // ------------------------------------------------------------------------------------------------ epilogue: warp q reads lanes [32q, 32q + 32)
-    const int m = warp * 32 + lane;
-    const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
+  } else if (warp < 4 || warp >= 10) {
+    // ------------------------------------------------------------------------------------------------ epilogue: a warp reads the 32 lanes of its quarter (warp index mod 4);
+    // warps 0-3 take the first half of the tile's columns, warps 10-13 the second
+    const int qtr = warp & 3, half = warp >= 10 ? 1 : 0;
+    const int m = qtr * 32 + lane;
+    const uint32_t trow = tmem + ((uint32_t)(qtr * 32) << 16);
     uint32_t tcount = 0;
     bool ok = true;
     for (long long w = blockIdx.x; w < work && ok; w += gridDim.x, ++tcount) {
@@ -282,7 +284,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
       if (MODE == PF_GU) {
         __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + orow * a.ldo + (size_t)nt * 128;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 2 * half; c < 2 * half + 2; ++c) {
           uint32_t rg[32], ru[32];
           tc_ld32(trow + 32 * c, rg);
           tc_ld32(trow + 128 + 32 * c, ru);
@@ -301,7 +303,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
         }
       } else {
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 4 * half; c < 4 * half + 4; ++c) {
           uint32_t r[32];
           tc_ld32(trow + 32 * c, r);
           tc_wait_ld();
@@ -460,23 +462,36 @@ __global__ void pf_tmaps_kernel(const __grid_constant__ PfMapSet tpl, const uint
 __global__ void pf_reduce_kernel(const __nv_bfloat16* __restrict__ part, const int32_t* __restrict__ ids, const float* __restrict__ w, int M, int K, int E,
                                  const uint8_t* const* __restrict__ tab, int H, float* __restrict__ out, const __nv_bfloat16* __restrict__ shared,
                                  const float* __restrict__ lg, int ld, int col, __nv_bfloat16* __restrict__ cout) {
-  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;      // 8 columns of one row per thread (H is a multiple of 256)
   if (i >= (size_t)M * H) return;
   const int m = (int)(i / H), n = (int)(i % H);
-  float a0 = 0.f, a1 = 0.f;
+  float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   for (int k = 0; k < K; ++k) {
     const int p = m * K + k;
     int e;
     if (!pf_live(ids, p, E, tab, &e)) continue;
-    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(part + (size_t)p * H + n));
+    const uint4 v = __ldcs(reinterpret_cast<const uint4*>(part + (size_t)p * H + n));
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
     const float wv = w[p];
-    a0 += v.x * wv; a1 += v.y * wv;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { a[2 * j] += __uint_as_float(u[j] << 16) * wv; a[2 * j + 1] += __uint_as_float(u[j] & 0xffff0000u) * wv; }
   }
-  if (!cout) { *reinterpret_cast<float2*>(out + i) = make_float2(a0, a1); return; }
+  if (!cout) {
+    *reinterpret_cast<float4*>(out + i) = make_float4(a[0], a[1], a[2], a[3]);
+    *reinterpret_cast<float4*>(out + i + 4) = make_float4(a[4], a[5], a[6], a[7]);
+    return;
+  }
   float g = 1.f;
   if (lg) g = bf16r(1.f / (1.f + expf(-bf16r(lg[(size_t)m * ld + col]))));
-  const float2 sh = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(shared + i));
-  *reinterpret_cast<__nv_bfloat162*>(cout + i) = __halves2bfloat162(__float2bfloat16(bf16r(a0) + bf16r(g * sh.x)), __float2bfloat16(bf16r(a1) + bf16r(g * sh.y)));
+  const uint4 sv = *reinterpret_cast<const uint4*>(shared + i);
+  const uint32_t su[4] = {sv.x, sv.y, sv.z, sv.w};
+  float r[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    r[2 * j] = bf16r(a[2 * j]) + bf16r(g * __uint_as_float(su[j] << 16));
+    r[2 * j + 1] = bf16r(a[2 * j + 1]) + bf16r(g * __uint_as_float(su[j] & 0xffff0000u));
+  }
+  *reinterpret_cast<uint4*>(cout + i) = pf_pack8(r);
 }
 
 }  // namespace hb
@@ -563,6 +578,8 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
              "moe_prefill: H=%d I=%d (multiples of 256) E=%d (≤ 1024) K=%d S=%d", H, I, E, K, S);
   HB_REQUIRE(ctx, (long long)S * K < (1ll << 30), HB_ERR_UNSUPPORTED, "moe_prefill: S·K too large");
   HB_REQUIRE(ctx, ws && hb_aligned(ws, 256), HB_ERR_WORKSPACE, "moe_prefill: ws NULL or not 256-byte aligned");
+  HB_REQUIRE(ctx, hb_aligned(x_bf16, 16) && hb_aligned(out, 16) && (!cmb || (hb_aligned(cmb->shared, 16) && hb_aligned(cmb->out, 16))), HB_ERR_INVALID,
+             "moe_prefill: x, out, shared rows and combined output must be 16-byte aligned");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   PfWs W;
   pf_carve(ws, S, K, E, H, I, &W);
@@ -600,7 +617,7 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
     if ((r = hbk_a4_quant(ctx, W.y, I, P, I, W.yq, W.ys, W.yg, st))) return r;
     a.ag = W.yg; a.Kd = I; a.N = H; a.out = W.part; a.ldo = H;
     if ((r = pf_launch<PF_DOWN>(ctx, "pf_gemm_down", a, tm_y, tm_y, tm_ys, tm_ys, st))) return r;
-    const size_t pairs2 = (size_t)n * H / 2;
+    const size_t pairs2 = (size_t)n * H / 8;
     const __nv_bfloat16* sh = cmb ? reinterpret_cast<const __nv_bfloat16*>(cmb->shared) + (size_t)s0 * H : nullptr;
     if ((r = hb_launch(ctx, "pf_reduce", false, pf_reduce_kernel, dim3((unsigned)((pairs2 + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16*)W.part, sid,
                        w + (size_t)s0 * K, n, K, E, lt, H, cmb ? (float*)nullptr : out + (size_t)s0 * H, sh,

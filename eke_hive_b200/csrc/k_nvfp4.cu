@@ -127,18 +127,33 @@ __global__ void a4_quant_kernel(const __nv_bfloat16* __restrict__ x, int ld, int
   if (row >= n) return;
   const __nv_bfloat16* xr = x + (size_t)row * ld;
   const int nb = K / 16;
+  const bool vec = (reinterpret_cast<uintptr_t>(xr) & 15) == 0;              // 16-byte loads when the row allows them
+  auto load16 = [&](int b, float* v) {
+    if (vec) {
+      const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(xr + b * 16)), u1 = __ldg(reinterpret_cast<const uint4*>(xr + b * 16) + 1);
+      const uint32_t w[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { v[2 * j] = __uint_as_float(w[j] << 16); v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u); }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = __bfloat162float(xr[b * 16 + j]);
+    }
+  };
   float a = 0.f;
   for (int b = lane; b < nb; b += 32) {
+    float v[16];
+    load16(b, v);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) a = fmaxf(a, fabsf(__bfloat162float(xr[b * 16 + j])));
+    for (int j = 0; j < 16; ++j) a = fmaxf(a, fabsf(v[j]));
   }
   for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
   const float gx = a > 0.f ? __fdiv_rn(a, 6.f * 448.f) : 1.f, inv = __fdiv_rn(1.f, gx);
   if (lane == 0) g[row] = gx;
   for (int b = lane; b < nb; b += 32) {
     float v[16], ab = 0.f;
+    load16(b, v);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) { v[j] = __bfloat162float(xr[b * 16 + j]); ab = fmaxf(ab, fabsf(v[j])); }
+    for (int j = 0; j < 16; ++j) ab = fmaxf(ab, fabsf(v[j]));
     const __nv_fp8_storage_t se = __nv_cvt_float_to_fp8(__fmul_rn(__fdiv_rn(ab, 6.f), inv), __NV_SATFINITE, __NV_E4M3);
     const float sv = e4m3_to_f32(se);
     const float f = sv > 0.f ? __fdiv_rn(inv, sv) : 0.f;
