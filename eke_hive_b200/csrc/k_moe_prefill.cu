@@ -31,15 +31,18 @@ namespace hb {
 constexpr int PF_BM = 128;              // pairs per tile (MMA M)
 constexpr int PF_BN = 256;              // weight rows per tile (MMA N)
 constexpr int PF_BK = 256;              // k values per stage = one 128-byte swizzle row of e2m1 codes
-constexpr int PF_ST = 4;                // stages
+constexpr int PF_ST = 3;                // stages
 constexpr int PF_A_BYTES = PF_BM * 128, PF_B_BYTES = PF_BN * 128;
 constexpr int PF_SFA_BYTES = 4 * 512;   // 4 MMA k-steps × one 128-row chunk
 constexpr int PF_SFB_BYTES = 8 * 512;   // two 128-row blocks × 4 k-steps
 constexpr int PF_STAGE = PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + PF_SFB_BYTES;
-constexpr int PF_SMEM = PF_ST * PF_STAGE + 1024 + 256;
+constexpr int PF_STG_PITCH = 144;        // epilogue staging: 32 rows × 128 bytes per warp, rows padded to 144 bytes (conflict-free 16-byte accesses)
+constexpr int PF_STG_BYTES = 32 * PF_STG_PITCH;
+constexpr int PF_SMEM = PF_ST * PF_STAGE + 1024 + 512 + 8 * PF_STG_BYTES;
 constexpr int PF_THREADS = 14 * 32;     // warps 0-3 and 10-13 epilogue, 4 MMA issue, 5 TMA, 6-9 scale transposition
 constexpr int PF_TMEM_COLS = 512;
 constexpr int PF_SF_COL0 = 256;         // accumulator: columns [0, 256); scales of stage s: [256 + 48 s, 256 + 48 s + 48)
+static_assert(PF_SF_COL0 + 48 * PF_ST <= PF_TMEM_COLS, "tensor memory");
 static_assert(PF_STAGE % 1024 == 0, "stage buffers must keep the 1024-byte alignment of the swizzle atom");
 static_assert(PF_SMEM <= 227 * 1024, "shared memory");
 
@@ -140,6 +143,21 @@ __device__ __forceinline__ uint4 pf_pack8(const float* v) {
   const __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
   return make_uint4(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1), *reinterpret_cast<const uint32_t*>(&p2),
                     *reinterpret_cast<const uint32_t*>(&p3));
+}
+
+// Epilogue staging → global: the warp's 32 rows × 128 bytes leave as 8 stores of 4 rows × 128 contiguous bytes (a thread owns a row
+// when it reads tensor memory, which would make every store instruction touch 32 different rows).  gptr: this lane's row in
+// global memory (nullptr = row past the tile's end), already offset to the first of the 128 bytes.
+__device__ __forceinline__ void pf_epi_flush(const uint8_t* stg, uint8_t* gptr, int lane) {
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3);
+    uint8_t* p = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(gptr), r));
+    const uint4 v = *reinterpret_cast<const uint4*>(stg + r * PF_STG_PITCH + (lane & 7) * 16);
+    if (p) *reinterpret_cast<uint4*>(p + (lane & 7) * 16) = v;
+  }
+  __syncwarp();
 }
 
 template <int MODE>
@@ -264,6 +282,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
     const int qtr = warp & 3, half = warp >= 10 ? 1 : 0;
     const int m = qtr * 32 + lane;
     const uint32_t trow = tmem + ((uint32_t)(qtr * 32) << 16);
+    uint8_t* stg = sm + PF_ST * PF_STAGE + 512 + (size_t)(half * 4 + qtr) * PF_STG_BYTES;
     uint32_t tcount = 0;
     bool ok = true;
     for (long long w = blockIdx.x; w < work && ok; w += gridDim.x, ++tcount) {
@@ -281,14 +300,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
       }
       if (!(ok = mbar_wait(acc_full, tcount & 1, a.err, 0x1000u))) break;
       tc_fence_after();
+      uint8_t* mine = stg + lane * PF_STG_PITCH;
       if (MODE == PF_GU) {
-        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + orow * a.ldo + (size_t)nt * 128;
+        uint8_t* gp = valid ? reinterpret_cast<uint8_t*>(reinterpret_cast<__nv_bfloat16*>(a.out) + orow * a.ldo + (size_t)nt * 128 + 64 * half) : nullptr;
 #pragma unroll 1
-        for (int c = 2 * half; c < 2 * half + 2; ++c) {
+        for (int c2 = 0; c2 < 2; ++c2) {
+          const int c = 2 * half + c2;
           uint32_t rg[32], ru[32];
           tc_ld32(trow + 32 * c, rg);
           tc_ld32(trow + 128 + 32 * c, ru);
           tc_wait_ld();
+          if (c2 == 1) { tc_fence_before(); mbar_arrive(acc_empty); }       // the accumulators are read: the next tile may start
           float y[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -296,37 +318,43 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
             if (a.limit > 0.f) { gv = fminf(gv, a.limit); uv = fminf(fmaxf(uv, -a.limit), a.limit); }
             y[i] = gv / (1.f + __expf(-gv)) * uv;
           }
-          if (valid) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(o + 32 * c + 8 * q) = pf_pack8(y + 8 * q);
+          for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(mine + c2 * 64 + q * 16) = pf_pack8(y + 8 * q);
+        }
+        pf_epi_flush(stg, gp, lane);
+      } else if (MODE == PF_DOWN) {
+#pragma unroll 1
+        for (int p2 = 0; p2 < 2; ++p2) {
+          uint8_t* gp = valid ? reinterpret_cast<uint8_t*>(reinterpret_cast<__nv_bfloat16*>(a.out) + orow * a.ldo + (size_t)nt * 256 + 128 * half + 64 * p2) : nullptr;
+#pragma unroll 1
+          for (int c2 = 0; c2 < 2; ++c2) {
+            uint32_t r[32];
+            tc_ld32(trow + 128 * half + 64 * p2 + 32 * c2, r);
+            tc_wait_ld();
+            if (p2 == 1 && c2 == 1) { tc_fence_before(); mbar_arrive(acc_empty); }
+            float y[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) y[i] = __uint_as_float(r[i]) * f0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(mine + c2 * 64 + q * 16) = pf_pack8(y + 8 * q);
           }
+          pf_epi_flush(stg, gp, lane);
         }
       } else {
 #pragma unroll 1
         for (int c = 4 * half; c < 4 * half + 4; ++c) {
+          uint8_t* gp = valid ? reinterpret_cast<uint8_t*>(reinterpret_cast<float*>(a.out) + orow * a.ldo + (size_t)nt * 256 + 32 * c) : nullptr;
           uint32_t r[32];
           tc_ld32(trow + 32 * c, r);
           tc_wait_ld();
-          if (MODE == PF_DOWN) {
-            float y[32];
+          if (c == 4 * half + 3) { tc_fence_before(); mbar_arrive(acc_empty); }
 #pragma unroll
-            for (int i = 0; i < 32; ++i) y[i] = __uint_as_float(r[i]) * f0;
-            if (valid) {
-              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + orow * a.ldo + (size_t)nt * 256 + 32 * c;
-#pragma unroll
-              for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(o + 8 * q) = pf_pack8(y + 8 * q);
-            }
-          } else if (valid) {
-            float* o = reinterpret_cast<float*>(a.out) + orow * a.ldo + (size_t)nt * 256 + 32 * c;
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-              *reinterpret_cast<float4*>(o + 4 * q) = make_float4(__uint_as_float(r[4 * q]) * f0, __uint_as_float(r[4 * q + 1]) * f0,
-                                                                  __uint_as_float(r[4 * q + 2]) * f0, __uint_as_float(r[4 * q + 3]) * f0);
-          }
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<float4*>(mine + q * 16) = make_float4(__uint_as_float(r[4 * q]) * f0, __uint_as_float(r[4 * q + 1]) * f0,
+                                                                    __uint_as_float(r[4 * q + 2]) * f0, __uint_as_float(r[4 * q + 3]) * f0);
+          pf_epi_flush(stg, gp, lane);
         }
       }
-      tc_fence_before();
-      mbar_arrive(acc_empty);
     }
   }
   tc_fence_before();
