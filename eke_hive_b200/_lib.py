@@ -91,6 +91,7 @@ def load() -> C.CDLL:
         "hb_moe_decode_static_max_pairs": (i, [i, i]),
         "hb_moe_decode_routed_static": (i, [vp, vp, vp, i, i, vp, i, i, vp, i, i, f, C.POINTER(PfCombine), vp]),
         "hb_moe_decode_routed_f32": (i, [vp, vp, vp, i, i, vp, i, i, vp, i, i, f, vp, vp, vp]),
+        "hb_moe_decode_ep_local": (i, [vp, vp, vp, i, i, i, vp, i, i, vp, i, i, i, f, vp, i, i, vp, vp, vp, vp]),
         "hb_moe_layer_decode": (i, [vp, vp, i, i, i, i, i, i, vp, f, vp, i, vp, i, vp, i, i, f, vp, vp, vp, vp, vp]),
         "hb_dense_gemv_ws_bytes": (sz, [i, i, i, i]),
         "hb_dense_gemv": (i, [vp, C.POINTER(QMat), vp, i, i, vp, vp, i, vp, vp]),

@@ -240,6 +240,24 @@ int hb_moe_decode_routed_f32(hb_ctx* ctx, const int32_t* ids, const float* w, in
   return hbk_moe_decode_run(ctx, src, x, H, I, limit, red, ws, as_stream(stream));
 }
 
+int hb_moe_decode_ep_local(hb_ctx* ctx, const int32_t* ids, const float* w, int ld_ids, int M, int K, const uint8_t* const* rec_tab, int li, int E,
+                           const void* x, int ldx, int H, int I, float limit, const uint8_t* shared_rec, int sh_row0, int sh_rows, float* routed_out,
+                           void* shared_out, void* ws, void* stream) {
+  HB_CTX(ctx);
+  if (M == 0) return HB_OK;
+  HB_PTR(ctx, ids); HB_PTR(ctx, w); HB_PTR(ctx, rec_tab); HB_PTR(ctx, x); HB_PTR(ctx, routed_out);
+  HB_REQUIRE(ctx, M > 0 && K > 0 && E > 0 && E <= HB_MAX_EXPERTS && li >= 0 && ld_ids >= K && ldx >= H && ldx % 8 == 0, HB_ERR_INVALID,
+             "moe_decode_ep_local: M=%d K=%d E=%d li=%d ld_ids=%d ldx=%d (ldx a multiple of 8)", M, K, E, li, ld_ids, ldx);
+  HB_REQUIRE(ctx, !shared_rec || (shared_out && sh_row0 >= 0 && sh_rows >= 0 && sh_row0 + sh_rows <= M), HB_ERR_INVALID,
+             "moe_decode_ep_local: shared expert rows [%d, %d) outside the %d rows, or no output for them", sh_row0, sh_row0 + sh_rows, M);
+  int r = check_decode_shape(ctx, "moe_decode_ep_local", M * (K + (shared_rec ? 1 : 0)), H, I, x, ws);
+  if (r) return r;
+  hbk_pair_src src; src.ids = ids; src.w = w; src.M = M; src.K = K; src.tab = rec_tab; src.li = li; src.E = E;
+  src.ld_ids = ld_ids; src.x_ld = ldx; src.shared_rec = shared_rec; src.sh_row0 = sh_row0; src.sh_rows = shared_rec ? sh_rows : 0;
+  hbk_reduce red; red.out_f32 = routed_out; red.shared_out = shared_rec ? shared_out : nullptr;
+  return hbk_moe_decode_run(ctx, src, x, H, I, limit, red, ws, as_stream(stream));
+}
+
 int hb_moe_layer_decode(hb_ctx* ctx, const float* logits, int ld, int M, int E, int K, int renorm, int logits_bf16, const float* bias,
                         float sigmoid_scale, const uint8_t* const* rec_tab, int li, const uint8_t* shared_rec, int gate_col, const void* x,
                         int H, int I, float limit, int32_t* ids_out, float* w_out, void* out, void* ws, void* stream) {

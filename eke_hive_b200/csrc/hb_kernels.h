@@ -39,6 +39,9 @@ struct hbk_pair_src {
   const int32_t* ids = nullptr; const float* w = nullptr; int M = 0, K = 0;  // routed form
   const uint8_t* const* tab = nullptr; int li = 0, E = 0;
   const uint8_t* shared_rec = nullptr;
+  int ld_ids = 0;                                                            // row pitch of ids / w in elements (0 = K)
+  int x_ld = 0;                                                              // row pitch of x in elements (0 = H; other values: streaming path only)
+  int sh_row0 = 0, sh_rows = -1;                                             // rows that get the shared expert's pair (-1 = all M)
   // routed form, optional: route inside the grouping kernel (ids / w are then outputs written before they are grouped)
   int route = 0;                                                             // 0 = ids / w given, 1 = softmax, 2 = sigmoid + bias
   const float* logits = nullptr; int ld = 0, renorm = 0, logits_bf16 = 0;
@@ -51,6 +54,7 @@ struct hbk_reduce {
   const float* lg = nullptr; int ld = 0, col = 0;
   void* out_bf16 = nullptr;                   // routed form with combine
   float* out_f32 = nullptr;                   // routed form without combine: overwritten with Σ_k w·expert
+  void* shared_out = nullptr;                 // with out_f32 and a shared record: the shared expert's rows bf16 [sh_rows, H], written apart
 };
 int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int H, int I, float limit, const hbk_reduce& red, void* ws,
                        cudaStream_t st);

@@ -23,6 +23,7 @@ struct GroupArgs {
   const int32_t* ids; const float* w; int M, K;          // routed form
   const uint8_t* const* tab; int li, E;
   const uint8_t* shared_rec;
+  int ld_ids, sh_row0, sh_rows;                          // pitch of ids / w rows; rows [sh_row0, sh_row0 + sh_rows) get the shared pair
   DecodeWs ws;
   // optional routing stage (routed form): logits → ids / w by one warp per row before the grouping
   int route; const float* logits; int ld, renorm, logits_bf16; const float* bias; float sig_scale;
@@ -87,10 +88,12 @@ __global__ void __launch_bounds__(kGroupThreads) moe_group_kernel(GroupArgs a) {
     int row, kk = -1; float wv;
     if (routed) {
       if (i < a.M * a.K) {
-        const int e = a.ids[i];
-        row = i / a.K; wv = a.w[i];
+        row = i / a.K;
+        const size_t src = (size_t)row * a.ld_ids + (i - row * a.K);
+        const int e = a.ids[src];
+        wv = a.w[src];
         if (e >= 0 && e < a.E && a.tab[(size_t)a.li * a.E + e] != nullptr) kk = e;
-      } else { row = i - a.M * a.K; wv = 1.f; kk = a.E; }
+      } else { row = i - a.M * a.K; wv = 1.f; kk = row >= a.sh_row0 && row < a.sh_row0 + a.sh_rows ? a.E : -1; }
     } else {
       const hb_moe_pair p = a.pairs[i];
       row = p.row; wv = p.w; recs[i] = p.rec;
@@ -499,6 +502,9 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
   GroupArgs ga{};
   ga.pairs = src.pairs; ga.n_pairs = src.n_pairs; ga.ids = src.ids; ga.w = src.w; ga.M = src.M; ga.K = src.K;
   ga.tab = src.tab; ga.li = src.li; ga.E = src.E; ga.shared_rec = src.shared_rec; ga.ws = w;
+  ga.ld_ids = src.ld_ids ? src.ld_ids : src.K; ga.sh_row0 = src.sh_row0; ga.sh_rows = src.sh_rows < 0 ? src.M : src.sh_rows;
+  const int x_ld = src.x_ld ? src.x_ld : H;
+  if (src.route && ga.ld_ids != src.K) return hb_fail(ctx, HB_ERR_INVALID, "moe_decode: in-kernel routing writes dense ids / w rows");
   int route = src.route;
   if (route && group_smem(true, P, src.E, route) > kRouteSmemMax) {
     // the per-warp router scratch does not fit beside the grouping arrays (large E): route with the stand-alone kernel first
@@ -519,16 +525,17 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
   sa.hdr = w.hdr; sa.groups = w.groups; sa.s_row = w.s_row; sa.H = H; sa.I = I; sa.limit = limit; sa.err = ctx->dev_err;
   sa.off_g = (uint32_t)L.g;
   StreamArgs sd = sa;
-  sa.act = reinterpret_cast<const __nv_bfloat16*>(x); sa.act_ld = H; sa.outp = w.y;
+  sa.act = reinterpret_cast<const __nv_bfloat16*>(x); sa.act_ld = x_ld; sa.outp = w.y;
   sa.off_wa = (uint32_t)L.w1; sa.off_sa = (uint32_t)L.s1; sa.off_wb = (uint32_t)L.w3; sa.off_sb = (uint32_t)L.s3;
   sd.act = w.y; sd.act_ld = I; sd.outp = w.part;
   sd.off_wa = (uint32_t)L.w2; sd.off_sa = (uint32_t)L.s2;
 
-  if (hbk_moe_fused_available(H, I) && (ctx->flags & HB_FLAG_FUSED)) {
+  if (x_ld != H && !hbk_moe_decode_fast(H, I)) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "moe_decode: strided activation rows need a shape of the streaming path");
+  if (hbk_moe_fused_available(H, I) && (ctx->flags & HB_FLAG_FUSED) && x_ld == H) {
     // one persistent kernel: gate/up → down → (routed form) reduce + combine
     if (routed) {
       ReduceArgs ra{w.part, w.pos_of, w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
-                    reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32};
+                    reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), ga.sh_row0, ga.sh_rows};
       return hbk_moe_fused_launch(ctx, w, x, H, I, limit, L, &ra, st);
     }
     if ((r = hbk_moe_fused_launch(ctx, w, x, H, I, limit, L, nullptr, st))) return r;
@@ -557,7 +564,7 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
 
   if (routed) {
     ReduceArgs ra{w.part, w.pos_of, w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
-                  reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32};
+                  reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), ga.sh_row0, ga.sh_rows};
     return hb_launch(ctx, "moe_reduce_routed", true, moe_reduce_routed_kernel, dim3((unsigned)(((size_t)src.M * H / 2 + 255) / 256)), dim3(256), 0, st, ra);
   }
   return hb_launch(ctx, "moe_reduce_list", true, moe_reduce_list_kernel, dim3((H / 2 + 255) / 256, P), dim3(256), 0, st, (const __nv_bfloat16*)w.part,

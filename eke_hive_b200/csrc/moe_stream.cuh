@@ -192,6 +192,7 @@ struct ReduceArgs {
   const __nv_bfloat16* part; const int* pos_of; const float* pw; int M, K, H, shared_pairs;
   const __nv_bfloat16* shared; const float* lg; int ld, col;
   __nv_bfloat16* out_bf16; float* out_f32;
+  __nv_bfloat16* shared_out = nullptr; int sh_row0 = 0, sh_rows = 0;   // fp32 form: the shared expert's output rows, written apart
 };
 __device__ __forceinline__ void reduce_routed_unit(const ReduceArgs& r, size_t i) {
   const int m = (int)(i / (r.H / 2)), d = (int)(i % (r.H / 2)) * 2;
@@ -214,6 +215,11 @@ __device__ __forceinline__ void reduce_routed_unit(const ReduceArgs& r, size_t i
     }
   }
   if (r.out_f32) { r.out_f32[(size_t)m * r.H + d] = a0; r.out_f32[(size_t)m * r.H + d + 1] = a1; }
+  if (r.shared_out && m >= r.sh_row0 && m < r.sh_row0 + r.sh_rows) {
+    const int pos = r.pos_of[r.M * r.K + m];
+    *reinterpret_cast<unsigned int*>(r.shared_out + (size_t)(m - r.sh_row0) * r.H + d) =
+        pos >= 0 ? __ldcg(reinterpret_cast<const unsigned int*>(r.part + (size_t)pos * r.H + d)) : 0u;
+  }
   if (!r.out_bf16) return;
   float s0 = 0.f, s1 = 0.f;
   bool have = false;

@@ -3,15 +3,15 @@
 The reference engine has no multi-GPU code; this is the sharded form of its MoE layer.  Rank r of G owns the routed experts
 [r·E/G, (r+1)·E/G) of every layer; the router and the shared expert are replicated; every rank brings its own B rows.
 
-    route (local rows) → ONE all-gather of [row | ids | w] records → local experts over all G·B rows (pairs whose expert
-    lives elsewhere are skipped through NULL table entries) → reduce-scatter of the fp32 routed sums → shared expert and
-    combine on the local rows.
+    route (local rows) → ONE all-gather of [row | ids | w] records → ONE operator pass: local experts over all G·B rows, read in
+    place from the gathered buffer (pairs whose expert lives elsewhere are skipped through NULL table entries), plus the shared
+    expert on the local rows → reduce-scatter of the fp32 routed sums → combine on the local rows.
 
 Remote data always lands in local memory through the collective before a kernel reads it; no kernel touches a peer's memory.
 The fp32 routed sum of a row is then a sum over ranks of per-rank sums in k order, which differs from the single-GPU k order
 only by fp32 reassociation; routing indices are unaffected.
 
-`ops` is the operator module (eke_hive_b200 itself on GPUs).  The CPU tests pass a stand-in with the same four functions, so the
+`ops` is the operator module (eke_hive_b200 itself on GPUs).  The CPU tests pass a stand-in with the same three functions, so the
 exchange logic runs under the gloo backend without a GPU.
 """
 from __future__ import annotations
@@ -37,50 +37,42 @@ class ExpertParallelMoE:
         self.ops, self.ctx, self.H, self.I, self.E, self.K, self.B = ops, ctx, H, I, E, K, B
         self.world, self.rank, self.dev, self.group = world, rank, device, group
         self.renorm, self.logits_bf16, self.limit = renorm, logits_bf16, limit
-        self.rec_bytes = H * 2 + K * 8                                    # one row's record: bf16 row | int32 ids | fp32 weights
-        self.send = torch.empty((B, self.rec_bytes), dtype=torch.uint8, device=device)
-        self.recv = torch.empty((world * B, self.rec_bytes), dtype=torch.uint8, device=device)
-        self.x_all = torch.empty((world * B, H), dtype=torch.bfloat16, device=device)
-        self.ids_all = torch.empty((world * B, K), dtype=torch.int32, device=device)
-        self.w_all = torch.empty((world * B, K), dtype=torch.float32, device=device)
+        # one row's exchange record: bf16 row | int32 ids | fp32 weights, padded to 16 bytes so every field of every gathered
+        # row stays aligned for the kernels that read the gathered buffer in place
+        self.rec_bytes = (H * 2 + K * 8 + 15) // 16 * 16
+        self.send = torch.zeros((B, self.rec_bytes), dtype=torch.uint8, device=device)
+        self.recv = torch.zeros((world * B, self.rec_bytes), dtype=torch.uint8, device=device)
+        # strided views of the gathered buffer: no unpacking copies
+        self.x_all = self.recv[:, :H * 2].view(torch.bfloat16)
+        self.ids_all = self.recv[:, H * 2:H * 2 + K * 4].view(torch.int32)
+        self.w_all = self.recv[:, H * 2 + K * 4:H * 2 + K * 8].view(torch.float32)
         self.part = torch.empty((world * B, H), dtype=torch.float32, device=device)
         self.routed = torch.empty((B, H), dtype=torch.float32, device=device)
-        self.shared_f32 = torch.empty((B, H), dtype=torch.float32, device=device)
-        self.one_id = torch.zeros((B, 1), dtype=torch.int32, device=device)
-        self.one_w = torch.ones((B, 1), dtype=torch.float32, device=device)
-        self.shared_tab = torch.zeros(1, dtype=torch.int64, device=device)
+        self.shared = torch.zeros((B, H), dtype=torch.bfloat16, device=device)
         self.reduce_scatter = dist.get_backend(group) != "gloo"            # gloo has no reduce-scatter: all-reduce and slice there
-        ws_bytes = getattr(ops, "moe_decode_ws_bytes", lambda n, h, i: 256)(world * B * K, H, I)
+        ws_bytes = getattr(ops, "moe_decode_ws_bytes", lambda n, h, i: 256)(world * B * (K + 1), H, I)
         self.ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
 
     def layer(self, logits, x, tab, li: int, shared_ptr: int, gate_col: int, ids_out, w_out, out):
         """logits fp32 [B, ≥E(+1)], x bf16 [B, H] local rows; tab: device table [L·E] of local record pointers (0 = elsewhere);
         shared_ptr: this layer's shared-expert record (0 = none).  Writes ids_out / w_out [B, K] and out bf16 [B, H]."""
-        ops, B, H, K, G = self.ops, self.B, self.H, self.K, self.world
+        ops, B, H, K = self.ops, self.B, self.H, self.K
         ops.router_softmax_topk(logits, K, self.renorm, self.logits_bf16, E=self.E, ids=ids_out, w=w_out, ctx=self.ctx)
-        # pack [row | ids | w] per row, one all-gather, unpack into dense arrays
-        self.send[:, :H * 2].copy_(x.view(torch.uint8).view(B, H * 2))
-        self.send[:, H * 2:H * 2 + K * 4].copy_(ids_out.view(torch.uint8).view(B, K * 4))
-        self.send[:, H * 2 + K * 4:].copy_(w_out.view(torch.uint8).view(B, K * 4))
+        # pack [row | ids | w] per row (one kernel), one all-gather
+        torch.cat([x.view(torch.uint8).view(B, H * 2), ids_out.view(torch.uint8).view(B, K * 4), w_out.view(torch.uint8).view(B, K * 4)], dim=1,
+                  out=self.send[:, :H * 2 + K * 8])
         dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
-        self.x_all.view(torch.uint8).view(G * B, H * 2).copy_(self.recv[:, :H * 2])
-        self.ids_all.view(torch.uint8).view(G * B, K * 4).copy_(self.recv[:, H * 2:H * 2 + K * 4])
-        self.w_all.view(torch.uint8).view(G * B, K * 4).copy_(self.recv[:, H * 2 + K * 4:])
-        # local experts over every rank's rows
-        ops.moe_decode_routed_f32(self.ids_all, self.w_all, tab, li, self.E, self.x_all, H, self.I, out=self.part, limit=self.limit, ws=self.ws,
-                                  ctx=self.ctx)
+        # local experts over every rank's rows, read in place from the gathered buffer, and the (replicated) shared expert on the
+        # local rows in the same pass
+        ops.moe_decode_ep_local(self.ids_all, self.w_all, tab, li, self.E, self.x_all, H, self.I, self.part, shared_ptr=shared_ptr,
+                                sh_row0=self.rank * B, sh_rows=B, shared_out=self.shared, limit=self.limit, ws=self.ws, ctx=self.ctx)
         if self.reduce_scatter:
             dist.reduce_scatter_tensor(self.routed, self.part, op=dist.ReduceOp.SUM, group=self.group)
         else:
             dist.all_reduce(self.part, op=dist.ReduceOp.SUM, group=self.group)
             self.routed.copy_(self.part[self.rank * B:(self.rank + 1) * B])
-        # shared expert (replicated) on the local rows, then the combine
         if shared_ptr:
-            self.shared_tab.fill_(shared_ptr)
-            ops.moe_decode_routed_f32(self.one_id, self.one_w, self.shared_tab, 0, 1, x, H, self.I, out=self.shared_f32, limit=self.limit,
-                                      ws=self.ws, ctx=self.ctx)
-            shared = self.shared_f32.to(torch.bfloat16)                     # exact: the values are bf16 already
-            ops.moe_combine(self.routed, shared, logits if gate_col >= 0 else None, gate_col if gate_col >= 0 else 0, out=out, ctx=self.ctx)
+            ops.moe_combine(self.routed, self.shared, logits if gate_col >= 0 else None, gate_col if gate_col >= 0 else 0, out=out, ctx=self.ctx)
         else:
             ops.moe_combine(self.routed, torch.zeros_like(out), None, 0, out=out, ctx=self.ctx)
         return out

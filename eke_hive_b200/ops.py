@@ -16,7 +16,7 @@ from ._lib import Config, HbError, MoePair, PfCombine, RecLayout
 
 __all__ = ["Context", "context", "ExpertRecLayout", "nvfp4_dequant", "nvfp4_gemv", "nvfp4_quantize", "a4_quant", "router_softmax_topk",
            "router_topk", "build_moe_pairs", "moe_combine", "moe_decode_ws_bytes", "moe_decode", "fn_moe_decode_routed", "fn_moe_decode_routed_static", "static_max_pairs", "moe_decode_routed_f32", "moe_layer_decode",
-           "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "moe_prefill_supported", "moe_prefill_ws_bytes", "fn_moe_prefill", "nvfp4_gemm_a4", "fp4_peak_probe", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
+           "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "moe_decode_ep_local", "moe_prefill_supported", "moe_prefill_ws_bytes", "fn_moe_prefill", "nvfp4_gemm_a4", "fp4_peak_probe", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
 
 
 def _L():
@@ -339,6 +339,19 @@ def lb_dequant(W: GMat, out=None, ctx: Context | None = None):
     out = torch.empty((W.N, W.K), dtype=torch.bfloat16, device=W.w.device) if out is None else out
     ctx.check(_L().hb_lb_dequant(ctx.handle, C.byref(W.c), _p(out), _stream()))
     return out
+
+
+def moe_decode_ep_local(ids, w, rec_tab, li: int, E: int, x, H: int, I: int, routed_out, shared_ptr: int = 0, sh_row0: int = 0, sh_rows: int = 0,
+                        shared_out=None, limit: float = 0.0, ws=None, ctx: Context | None = None):
+    """One rank's share of an expert-parallel decode layer (hb_moe_decode_ep_local).  ids int32 / w fp32 [M, K] and x bf16 [M, H] may be
+    strided row views (e.g. columns of a gathered exchange buffer); routed_out fp32 [M, H]; shared_out bf16 [sh_rows, H]."""
+    ctx = ctx or context()
+    M, K = ids.shape
+    assert ids.stride(1) == 1 and w.stride(1) == 1 and x.stride(1) == 1 and ids.stride(0) == w.stride(0)
+    ws = _ws(M * (K + 1), H, I, x.device, ws)
+    ctx.check(_L().hb_moe_decode_ep_local(ctx.handle, _p(ids), _p(w), ids.stride(0), M, K, _p(rec_tab), li, E, _p(x), x.stride(0), H, I, limit,
+                                          shared_ptr or None, sh_row0, sh_rows, _p(routed_out), _p(shared_out), _p(ws), _stream()))
+    return routed_out
 
 
 # ---------------------------------------------------------------------------------------------------- prefill (tcgen05 grouped GEMM)

@@ -164,6 +164,15 @@ HB_API int hb_moe_decode_routed_static(hb_ctx* ctx, const int32_t* ids, const fl
  * expert-parallel layer, where rec_tab holds NULL for experts that live on other GPUs (those pairs contribute nothing). */
 HB_API int hb_moe_decode_routed_f32(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int K, const uint8_t* const* rec_tab, int li, int E,
                                     const void* x_bf16, int H, int I, float limit, float* out, void* ws, void* stream);
+/* (No counterpart in the reference, which is single-GPU.)  One rank's share of an expert-parallel decode layer, in one pass:
+ * routed_out[m] = Σ_k w[m,k]·expert_ids[m,k](x[m]) over the experts whose records this rank holds (NULL table entries = experts
+ * held elsewhere, skipped), fp32 [M,H] overwritten — to be summed over ranks — and, when shared_rec is given, the always-on
+ * shared expert on rows [sh_row0, sh_row0 + sh_rows) (this rank's own rows) → shared_out bf16 [sh_rows, H].  ids / w / x may be
+ * strided views into a gathered exchange buffer: row m of ids / w starts at element m·ld_ids, row m of x at element m·ldx
+ * (ldx a multiple of 8, x 16-byte aligned).  ws ≥ hb_moe_decode_ws_bytes(M·(K+1), H, I). */
+HB_API int hb_moe_decode_ep_local(hb_ctx* ctx, const int32_t* ids, const float* w, int ld_ids, int M, int K, const uint8_t* const* rec_tab, int li,
+                                  int E, const void* x_bf16, int ldx, int H, int I, float limit, const uint8_t* shared_rec, int sh_row0, int sh_rows,
+                                  float* routed_out, void* shared_out_bf16, void* ws, void* stream);
 /* A whole decode MoE layer in one call: router (softmax when bias == NULL and sigmoid_scale == 0, else sigmoid+bias) → routed
  * experts → the always-on shared expert given as one more NVFP4 record (weight 1, every row; NULL = none) → combine.
  * Composition of the operators above in the order of engine/src/qwen/qwen_engine.cpp:818-878; ids_out / w_out [M,K] receive

@@ -17,7 +17,7 @@ H, I, E, K, B = 128, 64, 8, 3, 4
 
 
 class OracleOps:
-    """The four operators ExpertParallelMoE calls, computed by the CPU oracle on CPU tensors.  Records are numpy arrays kept in
+    """The three operators ExpertParallelMoE calls, computed by the CPU oracle on CPU tensors.  Records are numpy arrays kept in
     a registry; the 'pointer table' holds registry keys."""
 
     def __init__(self, O, registry):
@@ -28,11 +28,17 @@ class OracleOps:
         ids.copy_(torch.from_numpy(i)); w.copy_(torch.from_numpy(ww))
         return ids, w
 
-    def moe_decode_routed_f32(self, ids, w, tab, li, E, x, H_, I_, out=None, limit=0.0, ws=None, ctx=None):
+    def moe_decode_ep_local(self, ids, w, tab, li, E, x, H_, I_, routed_out, shared_ptr=0, sh_row0=0, sh_rows=0, shared_out=None, limit=0.0,
+                            ws=None, ctx=None):
         recs = [self.reg.get(int(p)) for p in tab[li * E:(li + 1) * E]]
-        acc = self.O.moe_routed(H_, I_, ids.numpy(), w.numpy(), recs, x.float().numpy(), limit, 0)
-        out.copy_(torch.from_numpy(acc))
-        return out
+        xs = np.ascontiguousarray(x.float().numpy())
+        acc = self.O.moe_routed(H_, I_, np.ascontiguousarray(ids.numpy()), np.ascontiguousarray(w.numpy()), recs, xs, limit, 0)
+        routed_out.copy_(torch.from_numpy(acc))
+        if shared_ptr:
+            rec = self.reg[int(shared_ptr)]
+            sh = np.stack([self.O.expert_forward(rec, H_, I_, xs[sh_row0 + m], 1.0, limit, 0) for m in range(sh_rows)])
+            shared_out.copy_(torch.from_numpy(sh).to(torch.bfloat16))
+        return routed_out
 
     def moe_combine(self, routed, shared, lg, col, out=None, ctx=None):
         bits = self.O.moe_combine(routed.numpy(), shared.float().numpy(), None if lg is None else lg.numpy(), col, True)

@@ -200,3 +200,38 @@ def test_decode_argument_errors(E):
     # an all-null pair list is a no-op, not an error
     E.moe_decode(pairs, x, 256, 256, 0.0, out)
     assert float(out.abs().sum()) == 0.0
+
+
+def test_ep_local_matches_separate_operators(E, oracle):
+    """hb_moe_decode_ep_local on strided views of a packed exchange buffer (with NULL table entries for experts held elsewhere)
+    equals the routed fp32 operator on contiguous copies bit for bit, and its shared-expert rows equal a separate pass."""
+    import torch
+    H, I, Ex, K, G, B = 2048, 512, 16, 4, 2, 8
+    M = G * B
+    rng = np.random.default_rng(5)
+    recs = random_records(oracle, H, I, Ex + 1, 31)
+    drecs = upload(recs)
+    local = [drecs[e] if e < Ex // 2 else None for e in range(Ex)]              # rank 0 of 2 holds the first half
+    tab = E.rec_table(local)
+    rec_bytes = (H * 2 + K * 8 + 15) // 16 * 16
+    buf = torch.zeros((M, rec_bytes), dtype=torch.uint8, device="cuda")
+    x = bf16_tensor(rng.standard_normal((M, H)).astype(np.float32))
+    ids = torch.from_numpy(np.stack([rng.permutation(Ex)[:K] for _ in range(M)]).astype(np.int32)).cuda()
+    w = torch.from_numpy(rng.random((M, K), dtype=np.float32)).cuda()
+    buf[:, :H * 2] = x.view(torch.uint8).view(M, H * 2)
+    buf[:, H * 2:H * 2 + K * 4] = ids.view(torch.uint8).view(M, K * 4)
+    buf[:, H * 2 + K * 4:H * 2 + K * 8] = w.view(torch.uint8).view(M, K * 4)
+    xv, iv, wv = buf[:, :H * 2].view(torch.bfloat16), buf[:, H * 2:H * 2 + K * 4].view(torch.int32), buf[:, H * 2 + K * 4:H * 2 + K * 8].view(torch.float32)
+    routed = torch.empty((M, H), dtype=torch.float32, device="cuda")
+    shared = torch.empty((B, H), dtype=torch.bfloat16, device="cuda")
+    E.moe_decode_ep_local(iv, wv, tab, 0, Ex, xv, H, I, routed, shared_ptr=drecs[Ex].data_ptr(), sh_row0=B, sh_rows=B, shared_out=shared)
+    ref = torch.empty_like(routed)
+    E.moe_decode_routed_f32(ids, w, tab, 0, Ex, x, H, I, out=ref)
+    one_tab = E.rec_table([drecs[Ex]])
+    sh_ref = torch.empty((B, H), dtype=torch.float32, device="cuda")
+    E.moe_decode_routed_f32(torch.zeros((B, 1), dtype=torch.int32, device="cuda"), torch.ones((B, 1), dtype=torch.float32, device="cuda"), one_tab, 0, 1,
+                            x[B:2 * B].contiguous(), H, I, out=sh_ref)
+    torch.cuda.synchronize()
+    E.context().check_device()
+    assert torch.equal(routed, ref)
+    assert torch.equal(shared.float(), sh_ref)
