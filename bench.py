@@ -439,7 +439,7 @@ def run_prefill(args):
     import eke_hive_b200 as E
     dev = torch.device("cuda", 0)
     ctx = E.context()
-    H, I, Ex, K, T = 7168, 2048, 256, 8, args.tokens
+    H, I, Ex, K, T = 7168, 2048, args.experts, 8, args.tokens
     peak = E.fp4_peak_probe(8192)
     rb = E.ExpertRecLayout.make(H, I)
     blob = torch.randint(0, 256, (Ex, rb.total), dtype=torch.uint8, device=dev)          # e2m1 codes: any bytes
@@ -476,8 +476,8 @@ def run_prefill(args):
     dms = _timed(torch, lambda: E.nvfp4_gemm_a4(W, xq, xs, xg, y=y, ctx=ctx), args.steps)
     line = {"metric": "moe_prefill_layer_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "ms_per_layer": ms,
             "dtype": "e2m1 x e2m1 with ue4m3 block scales, f32 accumulate", "data": "synthetic",
-            "config": {"workload": f"deepseek-shaped MoE prefill layer: hidden 7168, 256 routed experts top-8, intermediate 2048, T={T}, NVFP4 W4A4",
-                       "l2": "6.3 GB of expert records per layer (larger than L2)"},
+            "config": {"workload": f"deepseek-shaped MoE prefill layer: hidden 7168, {Ex} routed experts top-8, intermediate 2048, T={T}, NVFP4 W4A4",
+                       "l2": f"{Ex * rb.total / 1e9:.1f} GB of expert records per layer (larger than L2)"},
             "layer_TFLOPs": flops / (ms * 1e-3) / 1e12,
             "roofline": {"bound": "tensor", "kernel": "pf_gemm_kernel (gate/up + down)", "achieved": flops / (gemm_us * 1e-6) / 1e12, "peak": peak, "unit": "TFLOP/s",
                          "frac": flops / (gemm_us * 1e-6) / 1e12 / peak, "peak_source": "hb_fp4_peak_probe on this GPU (dense FP4, resident operands)", "traffic": None},
@@ -559,6 +559,7 @@ def main():
                     help="decode = the benchmark proper (BASELINE config 2); prefill = one config-4 MoE layer on the FP4 tensor cores; "
                          "dense = the config-5 MLP GEMVs (one GPU each; their own JSON line)")
     ap.add_argument("--tokens", type=int, default=8192, help="--workload prefill: tokens per layer call")
+    ap.add_argument("--experts", type=int, default=256, help="--workload prefill: routed experts resident (fewer = a smaller case for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for the baseline leg")
     args = ap.parse_args()

@@ -4,9 +4,9 @@
 //
 //   stream   persistent CTAs, grid = (CTAs per K split, K splits).  A CTA first turns the activation columns of its K range into
 //            f16 B fragments in shared memory, in the order the tiles consume them; every (row, 256-column slice) gets its own
-//            power-of-two rescale so bf16 outliers cannot overflow f16, undone in fp32 when the slice is accumulated.  Then each
-//            of its 8 warps claims strips of 16 weight rows from the split's counter and streams them through a private cp.async
-//            ring, 256 columns per stage; the ring keeps running across strip boundaries
+//            power-of-two rescale so bf16 outliers cannot overflow f16, undone in fp32 when the slice is accumulated.  The CTA
+//            then walks strips of 16 weight rows (b, b + CTAs, ...): warp w streams the strip's slice w through its own cp.async
+//            ring, which keeps running across strips, and the 8 partial tiles are summed in warp order in shared memory
 //   reduce   fixed-order sum over the K splits, output conversion, or the fused SiLU·up activation of the gate/up pair
 //
 // Low-bit decode without shifts or subtractions per element: a 2-bit field left at bit 2j of an f16 mantissa under exponent
@@ -19,10 +19,9 @@ namespace hb {
 
 constexpr int kDSlice = 256;            // columns per pipeline stage
 constexpr int kDWarps = 8;              // consumer warps per CTA, 16 weight rows each
-constexpr int kDCounterWord = 8;        // strip counters live in words [8, 64) of the context's 256-byte device status block
 __host__ __device__ constexpr int dense_stages(int fmt) { return fmt == HB_FMT_NVFP4 ? 3 : 4; }
 // K range of one CTA (slices of 256 columns whose B fragments sit in shared memory): sized for two CTAs per SM
-__host__ __device__ constexpr int dense_max_slices(int fmt) { return fmt == HB_FMT_LB3_G64 ? 4 : 8; }
+__host__ __device__ constexpr int dense_max_slices(int) { return kDWarps; }     // one slice per warp
 
 struct DenseFmt {
   int planes;         // B-fragment planes (LB3 has two)
@@ -122,7 +121,6 @@ struct DenseArgs {
   DenseMat mat[2]; int n_mats;
   int N, K, M, ksplit, slices, ldx;       // slices = K / 256
   const __nv_bfloat16* x;
-  int* counters;                          // [ksplit] next unclaimed strip of each K split; zero between launches (the last claim of a launch resets it)
   float* part;                            // [n_mats][ksplit][8][N]
 };
 
@@ -136,9 +134,11 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N_>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N_) : "memory"); }
 
-// Persistent CTAs: blockIdx.y = K split (the CTA keeps that range's B fragments in shared memory for its whole life),
-// blockIdx.x = one of the CTAs sharing the split.  Work unit of a warp = a strip of 16 weight rows of one matrix over the
-// split's columns, claimed from the split's counter; the warp's cp.async ring runs on across strip boundaries.
+// Persistent CTAs: blockIdx.y = K split (the CTA keeps that range's B fragments in shared memory for its whole life), blockIdx.x = one
+// of the CTAs sharing the split.  Work unit of a CTA = a strip of 16 weight rows of one matrix over the split's columns; CTA b takes
+// strips b, b + gridDim.x, ...  Warp w streams slice w of every strip through its own cp.async ring (so the CTA's requests cover
+// 8 consecutive slices of the same 16 rows: long contiguous runs per row), and the warps' partial tiles meet in shared memory
+// in warp order once per strip.
 template <int FMT>
 __global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseArgs a) {
   constexpr DenseFmt F = dense_fmt(FMT);
@@ -147,26 +147,20 @@ __global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseAr
   uint4* xb_s = reinterpret_cast<uint4*>(dsm);                                            // [MAXSL][planes][256] uint4
   float2* sums_s = reinterpret_cast<float2*>(dsm + (size_t)MAXSL * F.planes * 4096);      // [MAXSL][4 groups][8 rows] (S0, S1)
   float* inv_s = reinterpret_cast<float*>(dsm + (size_t)MAXSL * F.planes * 4096 + (size_t)MAXSL * 256);   // [MAXSL][8 rows] 1 / slice factor
-  int* claimed_s = reinterpret_cast<int*>(inv_s + MAXSL * 8);                             // [warps][8]
-  uint8_t* rings = reinterpret_cast<uint8_t*>(claimed_s) + 256;
+  float4* red_s = reinterpret_cast<float4*>(inv_s + MAXSL * 8);                           // [2][warps][32 lanes] partial tiles
+  uint8_t* rings = reinterpret_cast<uint8_t*>(red_s + 2 * kDWarps * 32);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int ks = blockIdx.y;
   const int sl0 = (int)((long long)a.slices * ks / a.ksplit), sl1 = (int)((long long)a.slices * (ks + 1) / a.ksplit), nsl = sl1 - sl0;
   const int strips_per_mat = (a.N + 15) / 16, n_strips = strips_per_mat * a.n_mats;
   uint8_t* ring = rings + (size_t)warp * NST * STG;
-  int* claimed = claimed_s + warp * 8;
   const int K = a.K;
-  // every warp of the split claims until it draws a number ≥ n_strips, so the launch makes exactly n_strips + (warps of the
-  // split) claims; the one that draws the last number puts the counter back to zero for the next launch
-  const int last_claim = n_strips + (int)gridDim.x * kDWarps - 1;
-  auto claim = [&]() -> int {
-    int v = 0;
-    if (lane == 0) { v = atomicAdd(&a.counters[ks], 1); if (v == last_claim) atomicExch(&a.counters[ks], 0); }
-    return __shfl_sync(0xffffffffu, v, 0);
-  };
+  const bool active = warp < nsl;                                   // this warp's slice of the split: sl0 + warp
   auto issue = [&](int strip, int sl, int stage) {                  // slice sl (absolute) of a strip → ring stage
-    const DenseMat& W = a.mat[strip >= strips_per_mat ? 1 : 0];
-    const int n0 = (strip >= strips_per_mat ? strip - strips_per_mat : strip) * 16;
+    const bool m1 = strip >= strips_per_mat;                        // (selects, not an index: a dynamic index would copy the parameter to local memory)
+    DenseMat W;
+    W.w = m1 ? a.mat[1].w : a.mat[0].w; W.wh = m1 ? a.mat[1].wh : a.mat[0].wh; W.s = m1 ? a.mat[1].s : a.mat[0].s; W.zp = m1 ? a.mat[1].zp : a.mat[0].zp;
+    const int n0 = (m1 ? strip - strips_per_mat : strip) * 16;
     uint8_t* st = ring + (size_t)stage * STG;
     if (FMT == HB_FMT_NVFP4) {
 #pragma unroll
@@ -189,16 +183,12 @@ __global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseAr
       cp_async8(st + 16 * (F.pitch_w + F.pitch_h) + row * 16 + which * 8, (which ? W.zp : W.s) + ((size_t)n * (K / 64) + (size_t)sl * 4) * 2);
     }
   };
-  // issue cursor: ordinal of the strip being fetched (io), its slice (is); compute cursor (co, cs) follows NST-1 slices behind
-  int io = 0, is = 0, istage = 0, istrip = claim();
-  if (lane == 0) claimed[0] = istrip;
+  int istrip = blockIdx.x, istage = 0;                             // issue cursor, NST-1 strips ahead of the compute cursor
   auto issue_next = [&]() {
-    if (istrip < n_strips) {
-      issue(istrip, sl0 + is, istage);
-      if (++is == nsl) { is = 0; ++io; istrip = claim(); if (lane == 0) claimed[io & 7] = istrip; }
-      if (++istage == NST) istage = 0;
-    }
-    cp_async_commit();                                              // always commit: the group count stays in step with the slice count
+    if (active && istrip < n_strips) issue(istrip, sl0 + warp, istage);
+    istrip += gridDim.x;
+    if (++istage == NST) istage = 0;
+    cp_async_commit();                                              // always commit: the group count stays in step with the strip count
   };
   for (int i = 0; i < NST - 1; ++i) issue_next();                  // weights do not depend on the previous kernel: fetch before waiting for it
   griddep_wait();
@@ -210,24 +200,26 @@ __global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseAr
   }
   __syncthreads();
   griddep_launch();
-  int co = 0, cs = 0, cstage = 0;
-  float total[4] = {0.f, 0.f, 0.f, 0.f};
-  for (;;) {
-    const int strip = claimed[co & 7];
-    if (strip >= n_strips) break;
+  const int cs = active ? warp : 0;                                 // slice index inside the CTA's range
+  const uint4* xb_i = xb_s + (size_t)cs * F.planes * 256;
+  const float2 iv = *reinterpret_cast<const float2*>(inv_s + cs * 8 + 2 * t);             // undo the slice factor of rows 2t, 2t+1
+  uint32_t bq[32];
+  if constexpr (FMT == HB_FMT_NVFP4) {                                        // the warp's slice never changes: its B fragments stay in registers
+#pragma unroll
+    for (int q = 0; q < 8; ++q) { const uint4 v = xb_i[q * 32 + lane]; bq[4 * q] = v.x; bq[4 * q + 1] = v.y; bq[4 * q + 2] = v.z; bq[4 * q + 3] = v.w; }
+  }
+  int cstage = 0, par = 0;
+  for (int strip = blockIdx.x; strip < n_strips; strip += gridDim.x, par ^= 1) {
     issue_next();
     cp_async_wait<NST - 1>();
     __syncwarp();
+    float total[4] = {0.f, 0.f, 0.f, 0.f};
+    if (active) {
     const uint8_t* st = ring + (size_t)cstage * STG;
-    const uint4* xb_i = xb_s + (size_t)cs * F.planes * 256;
-    const float2 iv = *reinterpret_cast<const float2*>(inv_s + cs * 8 + 2 * t);           // undo the slice factor of rows 2t, 2t+1
-    if (FMT == HB_FMT_NVFP4) {
-      uint32_t b[32];
-#pragma unroll
-      for (int q = 0; q < 8; ++q) { const uint4 v = xb_i[q * 32 + lane]; b[4 * q] = v.x; b[4 * q + 1] = v.y; b[4 * q + 2] = v.z; b[4 * q + 3] = v.w; }
+    if constexpr (FMT == HB_FMT_NVFP4) {
       float acc[4];
       warp_slice_mma(st + g * F.pitch_w + 32 * t, st + (g + 8) * F.pitch_w + 32 * t, st + 16 * F.pitch_w + g * 16 + 4 * t,
-                     st + 16 * F.pitch_w + (g + 8) * 16 + 4 * t, b, acc, nullptr);
+                     st + 16 * F.pitch_w + (g + 8) * 16 + 4 * t, bq, acc, nullptr);
 #pragma unroll
       for (int c = 0; c < 4; ++c) total[c] = fmaf(acc[c], (c & 1) ? iv.y : iv.x, total[c]);
     } else {
@@ -281,19 +273,20 @@ __global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseAr
 #pragma unroll
       for (int c = 0; c < 4; ++c) total[c] = fmaf(sub[c], (c & 1) ? iv.y : iv.x, total[c]);
     }
+    }
     __syncwarp();
     if (++cstage == NST) cstage = 0;
-    if (++cs == nsl) {                                              // strip finished: its partial sums of this K split → [mat][ks][row 0..7][N]
+    // the warps' partial tiles → one tile, summed in warp order, → [mat][ks][row 0..7][N]
+    red_s[(par * kDWarps + warp) * 32 + lane] = make_float4(total[0], total[1], total[2], total[3]);
+    __syncthreads();
+    if (threadIdx.x < 128) {
+      const int ln = threadIdx.x >> 2, c = threadIdx.x & 3, tg = ln >> 2, tt = ln & 3;   // element c of lane ln's fragment
+      float v = 0.f;
+      for (int w2 = 0; w2 < nsl; ++w2) v += reinterpret_cast<const float*>(red_s + (par * kDWarps + w2) * 32 + ln)[c];
       const int mat_i = strip >= strips_per_mat ? 1 : 0, n0 = (mat_i ? strip - strips_per_mat : strip) * 16;
-      float* part = a.part + ((size_t)mat_i * a.ksplit + ks) * 8 * a.N;
-      const float gsc = FMT == HB_FMT_NVFP4 ? a.mat[mat_i].g : 1.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int tok = 2 * t + (c & 1), n = n0 + g + (c >> 1) * 8;
-        if (tok < a.M && n < a.N) part[(size_t)tok * a.N + n] = total[c] * gsc;
-        total[c] = 0.f;
-      }
-      cs = 0; ++co;
+      const int tok = 2 * tt + (c & 1), n = n0 + tg + (c >> 1) * 8;
+      const float gsc = FMT == HB_FMT_NVFP4 ? (mat_i ? a.mat[1].g : a.mat[0].g) : 1.f;
+      if (tok < a.M && n < a.N) a.part[(((size_t)mat_i * a.ksplit + ks) * 8 + tok) * a.N + n] = v * gsc;
     }
   }
   cp_async_wait<0>();
@@ -338,13 +331,12 @@ namespace {
 int dense_ksplit(int fmt, int K) { const int sl = K / kDSlice, mx = dense_max_slices(fmt); return (sl + mx - 1) / mx; }
 size_t dense_smem(int fmt) {
   const DenseFmt F = dense_fmt(fmt);
-  return (size_t)dense_max_slices(fmt) * F.planes * 4096 + (size_t)dense_max_slices(fmt) * 256 + (size_t)dense_max_slices(fmt) * 32 + 256 + (size_t)kDWarps * dense_stages(fmt) * dense_stage_bytes(fmt);
+  return (size_t)dense_max_slices(fmt) * F.planes * 4096 + (size_t)dense_max_slices(fmt) * 256 + (size_t)dense_max_slices(fmt) * 32 + 2 * kDWarps * 32 * 16 + (size_t)kDWarps * dense_stages(fmt) * dense_stage_bytes(fmt);
 }
 int check_mat(hb_ctx* ctx, const hb_qmat* W, const char* fn) {
   HB_REQUIRE(ctx, W && W->w && W->s, HB_ERR_INVALID, "%s: NULL matrix", fn);
   HB_REQUIRE(ctx, W->fmt == HB_FMT_NVFP4 || W->fmt == HB_FMT_LB3_G64 || W->fmt == HB_FMT_LB2_G64, HB_ERR_INVALID, "%s: unknown format %d", fn, W->fmt);
   HB_REQUIRE(ctx, W->N > 0 && W->K > 0 && W->K % kDSlice == 0, HB_ERR_UNSUPPORTED, "%s: N=%d K=%d (K must be a multiple of %d)", fn, W->N, W->K, kDSlice);
-  HB_REQUIRE(ctx, W->K / kDSlice <= 56 * dense_max_slices(W->fmt), HB_ERR_UNSUPPORTED, "%s: K=%d beyond the %d K splits the workspace header holds", fn, W->K, 56);
   HB_REQUIRE(ctx, W->fmt == HB_FMT_NVFP4 || W->zp, HB_ERR_INVALID, "%s: low-bit matrix without zero-points", fn);
   HB_REQUIRE(ctx, hb_aligned(W->w, 16) && hb_aligned(W->s, 16) && (W->fmt == HB_FMT_NVFP4 || hb_aligned(W->zp, 8)), HB_ERR_INVALID,
              "%s: weight / scale pointers must be 16-byte aligned", fn);
@@ -363,10 +355,10 @@ int dense_pass(hb_ctx* ctx, const hb_qmat* A, const hb_qmat* B2, const void* x, 
   DenseArgs a{};
   a.mat[0] = to_mat(A); if (B2) a.mat[1] = to_mat(B2);
   a.n_mats = mats; a.N = N; a.K = K; a.M = M; a.ksplit = ksplit; a.slices = slices; a.ldx = ldx;
-  a.x = reinterpret_cast<const __nv_bfloat16*>(x); a.counters = reinterpret_cast<int*>(ctx->dev_err) + kDCounterWord; a.part = part;
+  a.x = reinterpret_cast<const __nv_bfloat16*>(x); a.part = part;
   int r;
   int per_split = (2 * ctx->sm_count) / ksplit;                    // two CTAs per SM in all, shared out over the K splits
-  const int strips = ((N + 15) / 16) * mats, max_useful = (strips + kDWarps - 1) / kDWarps;
+  const int strips = ((N + 15) / 16) * mats, max_useful = strips;
   if (per_split < 1) per_split = 1;
   if (per_split > max_useful) per_split = max_useful;
   const dim3 grid(per_split, ksplit, 1);
