@@ -39,6 +39,11 @@ class PfCombine(C.Structure):
     _fields_ = [("shared", C.c_void_p), ("lg", C.c_void_p), ("ld", C.c_int), ("col", C.c_int), ("out", C.c_void_p)]
 
 
+class Plan(C.Structure):
+    _fields_ = [("regime", C.c_int), ("pairs", C.c_int), ("distinct_experts", C.c_int), ("max_rows", C.c_int), ("decode_groups", C.c_int),
+                ("prefill_tiles", C.c_int), ("tile_fill", C.c_double), ("ws_bytes", C.c_size_t)]
+
+
 class KernelStat(C.Structure):
     _fields_ = [("name", C.c_char * 40), ("launches", C.c_uint32), ("total_ms", C.c_float)]
 
@@ -102,6 +107,7 @@ def load() -> C.CDLL:
         "hb_moe_prefill": (i, [vp, vp, i, i, vp, vp, i, i, vp, i, i, f, vp, vp, i, vp, C.POINTER(PfCombine)]),
         "hb_nvfp4_gemm_a4": (i, [vp, C.POINTER(QMat), vp, vp, vp, i, vp, i, vp]),
         "hb_fp4_peak_probe": (i, [vp, i, C.POINTER(f)]),
+        "hb_dispatch_plan": (i, [vp, i, i, i, i, i, vp, C.POINTER(Plan)]),
         "hb_gather_rows": (i, [vp, vp, vp, i, i, vp, vp]),
         "hb_swiglu_rows": (i, [vp, vp, i, i, f, vp, vp]),
         "hb_scatter_add_rows": (i, [vp, vp, vp, vp, i, i, vp, vp]),

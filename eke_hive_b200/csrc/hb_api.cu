@@ -309,4 +309,33 @@ int hb_add_f32(hb_ctx* ctx, float* a, const float* b, size_t n, void* stream) {
   return hbk_add_f32(ctx, a, b, n, as_stream(stream));
 }
 
+
+// Rows ≤ 64 go to the decode operators, more to the grouped GEMM — the reference engine's own switch
+// (engine/src/qwen/qwen_engine.cpp:825, :873) — provided the shape is one the grouped GEMM takes.
+int hb_dispatch_plan(const int32_t* ids, int M, int K, int E, int H, int I, int* counts, hb_plan* plan) {
+  if (!ids || !plan || M < 0 || K < 1 || E < 1 || E > HB_MAX_EXPERTS) return HB_ERR_INVALID;
+  int local[HB_MAX_EXPERTS];
+  int* c = counts ? counts : local;
+  for (int e = 0; e < E; ++e) c[e] = 0;
+  hb_plan p = {};
+  for (long long i = 0; i < (long long)M * K; ++i) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) { ++c[e]; ++p.pairs; }
+  }
+  for (int e = 0; e < E; ++e) {
+    if (!c[e]) continue;
+    ++p.distinct_experts;
+    if (c[e] > p.max_rows) p.max_rows = c[e];
+    p.decode_groups += (c[e] + 7) / 8;
+    p.prefill_tiles += (c[e] + 127) / 128;
+  }
+  p.tile_fill = p.prefill_tiles ? (double)p.pairs / (128.0 * p.prefill_tiles) : 0.0;
+  const bool pf_ok = hb_moe_prefill_supported(H, I) > 0;
+  p.regime = (M > 64 && pf_ok) ? 1 : 0;
+  if (p.regime == 1) p.ws_bytes = hb_moe_prefill_ws_bytes(M, K, E, H, I);
+  else p.ws_bytes = ((long long)M * K <= HB_MAX_PAIRS && hb_moe_decode_supported(H, I) > 0) ? hb_moe_decode_ws_bytes(M * K, H, I) : 0;
+  *plan = p;
+  return HB_OK;
+}
+
 }  // extern "C"

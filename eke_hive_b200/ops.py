@@ -16,7 +16,7 @@ from ._lib import Config, HbError, MoePair, PfCombine, RecLayout
 
 __all__ = ["Context", "context", "ExpertRecLayout", "nvfp4_dequant", "nvfp4_gemv", "nvfp4_quantize", "a4_quant", "router_softmax_topk",
            "router_topk", "build_moe_pairs", "moe_combine", "moe_decode_ws_bytes", "moe_decode", "fn_moe_decode_routed", "fn_moe_decode_routed_static", "static_max_pairs", "moe_decode_routed_f32", "moe_layer_decode",
-           "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "moe_decode_ep_local", "moe_prefill_supported", "moe_prefill_ws_bytes", "fn_moe_prefill", "nvfp4_gemm_a4", "fp4_peak_probe", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
+           "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "dispatch_plan", "moe_decode_ep_local", "moe_prefill_supported", "moe_prefill_ws_bytes", "fn_moe_prefill", "nvfp4_gemm_a4", "fp4_peak_probe", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
 
 
 def _L():
@@ -352,6 +352,21 @@ def moe_decode_ep_local(ids, w, rec_tab, li: int, E: int, x, H: int, I: int, rou
     ctx.check(_L().hb_moe_decode_ep_local(ctx.handle, _p(ids), _p(w), ids.stride(0), M, K, _p(rec_tab), li, E, _p(x), x.stride(0), H, I, limit,
                                           shared_ptr or None, sh_row0, sh_rows, _p(routed_out), _p(shared_out), _p(ws), _stream()))
     return routed_out
+
+
+def dispatch_plan(ids_host: np.ndarray, E: int, H: int, I: int):
+    """hb_dispatch_plan on host routing ids [M, K]: dict of the plan fields plus `counts` (pairs per expert)."""
+    from ._lib import Plan
+    ids_host = np.ascontiguousarray(ids_host, dtype=np.int32)
+    M, K = ids_host.shape
+    counts = np.zeros(E, np.int32)
+    p = Plan()
+    st = _L().hb_dispatch_plan(ids_host.ctypes.data, M, K, E, H, I, counts.ctypes.data, C.byref(p))
+    if st != 0:
+        raise HbError(st, "dispatch_plan: bad arguments")
+    d = {n: getattr(p, n) for n, _ in Plan._fields_}
+    d["counts"] = counts
+    return d
 
 
 # ---------------------------------------------------------------------------------------------------- prefill (tcgen05 grouped GEMM)

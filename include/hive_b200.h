@@ -220,6 +220,24 @@ HB_API int hb_nvfp4_gemm_a4(hb_ctx* ctx, const hb_qmat* W, const uint8_t* xq, co
  * shared memory (no loads, no epilogue); *tflops = dense FP4 TFLOP/s.  Synchronises the device.  (No reference counterpart.) */
 HB_API int hb_fp4_peak_probe(hb_ctx* ctx, int rounds, float* tflops);
 
+/* ---- regime choice ---- */
+/* What a caller needs to know before it runs a layer on M rows: how the (row, k) pairs fall on the experts and which operator
+ * family takes them.  Host-side restatement of the classification the reference spreads over GlmExperts::decode_layer
+ * (engine/src/glm/glm_experts.cpp:565-653: pairs grouped per expert, at most 8 rows per GEMV group as in
+ * engine/include/hive/decode_handshake.h:26) and fn_moe_prefill's count / scan / tile rule (engine/src/qwen/fn_moe_pf.cu:39-75, :898).
+ * ids: HOST int32 [M,K]; ids outside [0,E) are skipped.  counts (optional, [E]) receives the pairs per expert. */
+typedef struct hb_plan {
+  int regime;            /* 0 = decode operators (weight-streaming GEMV groups), 1 = prefill operator (grouped tensor-core GEMM) */
+  int pairs;             /* valid (row, k) pairs */
+  int distinct_experts;  /* experts with at least one pair: the records a decode call streams */
+  int max_rows;          /* most pairs on one expert */
+  int decode_groups;     /* Σ ceil(count / 8): work groups of the decode kernels */
+  int prefill_tiles;     /* Σ ceil(count / 128): tiles of the grouped GEMM */
+  double tile_fill;      /* pairs / (128 · prefill_tiles): how full the GEMM tiles would be */
+  size_t ws_bytes;       /* workspace the chosen operator needs (0 when the shape is unsupported by it) */
+} hb_plan;
+HB_API int hb_dispatch_plan(const int32_t* ids_host, int M, int K, int E, int H, int I, int* counts, hb_plan* plan);
+
 /* ---- prefill helpers kept for callers that compose (engine/include/hive/glm/glm_moe.h:33-41) ---- */
 HB_API int hb_gather_rows(hb_ctx* ctx, const void* x_bf16, const int32_t* rows, int R, int H, void* out_bf16, void* stream);
 HB_API int hb_swiglu_rows(hb_ctx* ctx, const void* gu_bf16, int R, int I, float limit, void* y_bf16, void* stream);

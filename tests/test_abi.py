@@ -74,3 +74,26 @@ def test_no_cpu_fallback_without_device(lib):
     import eke_hive_b200 as E
     with pytest.raises(E.HbError):
         E.Context()
+
+
+def test_dispatch_plan_host_logic(lib):
+    """hb_dispatch_plan is pure host code: counts, group / tile numbers and the rows ≤ 64 → decode, more → grouped GEMM switch."""
+    L = lib
+    lib = L.load()
+    rng = np.random.default_rng(3)
+    for M, K, E, H, I in ((16, 10, 512, 2048, 512), (8192, 8, 256, 7168, 2048), (100, 4, 16, 2048 + 32, 512), (64, 8, 160, 4096, 1536)):
+        ids = np.stack([rng.permutation(E)[:K] for _ in range(M)]).astype(np.int32)
+        ids[0, 0] = -1
+        ids[M - 1, K - 1] = E + 5
+        counts = np.zeros(E, np.int32)
+        p = L.Plan()
+        assert lib.hb_dispatch_plan(ids.ctypes.data, M, K, E, H, I, counts.ctypes.data, C.byref(p)) == 0
+        ref = np.bincount(ids[(ids >= 0) & (ids < E)], minlength=E)
+        assert np.array_equal(counts, ref)
+        assert p.pairs == int(ref.sum()) and p.distinct_experts == int((ref > 0).sum()) and p.max_rows == int(ref.max())
+        assert p.decode_groups == int(((ref + 7) // 8).sum()) and p.prefill_tiles == int(((ref + 127) // 128).sum())
+        want = 1 if (M > 64 and H % 256 == 0 and I % 256 == 0) else 0
+        assert p.regime == want
+        assert abs(p.tile_fill - ref.sum() / (128.0 * p.prefill_tiles)) < 1e-12
+        if want == 1:
+            assert p.ws_bytes == lib.hb_moe_prefill_ws_bytes(M, K, E, H, I) > 0
