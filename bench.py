@@ -385,7 +385,7 @@ def run_ours(args):
         gu_bytes = U * (2 * H * I * 9 // 16) + head_B * H * 2                     # gate+up halves of U records + the activation rows
         ach = gu_bytes / (prof["moe_gate_up"]["mean_us"] * 1e-6) / 1e9
         roofline = {"bound": "hbm", "kernel": "moe_gate_up (moe_stream_kernel<8,1,false>)", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                    "peak_source": peak_src, "traffic": None, "algorithmic_bytes_per_launch": gu_bytes, "mean_us": prof["moe_gate_up"]["mean_us"]}
+                    "peak_source": peak_src, "traffic": gu_bytes * (163.1 + 3.9) / 164.0, "traffic_source": "ncu dram bytes of a 4-layer capture of the same kernel (profiles/moe_stream_decode_b16.md): 1.018 x algorithmic, scaled to this run's records", "algorithmic_bytes_per_launch": gu_bytes, "mean_us": prof["moe_gate_up"]["mean_us"]}
     clocks = sampler.result()
     line = {"metric": "moe_layer_tokens_per_s", "value": head["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 products of e2m1·e4m3 weights and bf16 activations, f32 accumulate",

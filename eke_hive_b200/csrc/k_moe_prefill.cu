@@ -609,6 +609,24 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
   HB_REQUIRE(ctx, hb_aligned(x_bf16, 16) && hb_aligned(out, 16) && (!cmb || (hb_aligned(cmb->shared, 16) && hb_aligned(cmb->out, 16))), HB_ERR_INVALID,
              "moe_prefill: x, out, shared rows and combined output must be 16-byte aligned");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (ctx->flags & HB_FLAG_PREFILL_A16) {
+    // bf16 activations: the decode operators over sub-chunks of rows (their scratch fits inside this operator's workspace)
+    int rows = HB_MAX_PAIRS / K < S ? HB_MAX_PAIRS / K : S;
+    HB_REQUIRE(ctx, rows >= 1 && hb_moe_decode_supported(H, I) > 0, HB_ERR_UNSUPPORTED, "moe_prefill (bf16 activations): K=%d H=%d I=%d", K, H, I);
+    while (rows > 1 && hbk_moe_decode_ws_bytes(rows * K, H, I) > hb_moe_prefill_ws_bytes(S, K, E, H, I)) rows /= 2;
+    for (int m0 = 0; m0 < M; m0 += rows) {
+      const int n = M - m0 < rows ? M - m0 : rows;
+      hbk_pair_src src; src.ids = ids + (size_t)m0 * K; src.w = w + (size_t)m0 * K; src.M = n; src.K = K; src.tab = rec_tab; src.li = li; src.E = E;
+      hbk_reduce red;
+      if (cmb) {
+        red.shared = reinterpret_cast<const __nv_bfloat16*>(cmb->shared) + (size_t)m0 * H; red.lg = cmb->lg ? cmb->lg + (size_t)m0 * cmb->ld : nullptr;
+        red.ld = cmb->ld; red.col = cmb->col; red.out_bf16 = reinterpret_cast<__nv_bfloat16*>(cmb->out) + (size_t)m0 * H;
+      } else red.out_f32 = out + (size_t)m0 * H;
+      const int r2 = hbk_moe_decode_run(ctx, src, reinterpret_cast<const __nv_bfloat16*>(x_bf16) + (size_t)m0 * H, H, I, limit, red, ws, st);
+      if (r2) return r2;
+    }
+    return HB_OK;
+  }
   PfWs W;
   pf_carve(ws, S, K, E, H, I, &W);
   hb_rec_layout L;

@@ -45,6 +45,8 @@ typedef struct hb_config {
 } hb_config;
 #define HB_FLAG_NO_PDL 1   /* launch every kernel fully serialised (no programmatic dependent launch) */
 #define HB_FLAG_FUSED 2    /* decode: run gate/up, down and reduce as ONE persistent kernel (experimental; default: three kernels chained by PDL) */
+#define HB_FLAG_PREFILL_A16 4u /* hb_moe_prefill keeps bf16 activations (W4A16, the reference's default prefill arithmetic): rows run through
+                                  the decode kernels in sub-chunks — exact, but the expert records are streamed once per sub-chunk */
 
 /* Expert record layout, byte-identical to hive::glm::ExpertRecLayout::make (engine/include/hive/glm/glm_moe.h:13-22):
  * [w1 gate e2m1 [I,H/2]][s1 e4m3 [I,H/16]][w3 up][s3][w2 down e2m1 [H,I/2]][s2 e4m3 [H,I/16]][g1 g3 g2 fp32], total 4096-aligned. */
@@ -208,7 +210,9 @@ HB_API size_t hb_moe_prefill_ws_bytes(int S, int K, int E, int H, int I);
  * (hb_a4_quant's rule), both GEMMs run as block-scaled FP4 MMAs with fp32 accumulation, g, u, y and the down result are
  * rounded to bf16 where the decode kernels round them.  Records come from rec_tab[li·E + id]; ids outside [0,E) and NULL
  * records contribute nothing.  Rows are processed in sub-chunks of S; ws ≥ hb_moe_prefill_ws_bytes(S, K, E, H, I).  E ≤ 1024.
- * Block scales are read as unsigned e4m3 (the sign bit of a scale byte must be clear, as every NVFP4 writer leaves it). */
+ * Block scales are read as unsigned e4m3 (the sign bit of a scale byte must be clear, as every NVFP4 writer leaves it).
+ * With HB_FLAG_PREFILL_A16 in the context's flags the activations stay bf16 (W4A16: the decode operators' arithmetic and rounding
+ * points, bit-identical to hb_moe_decode_routed(_f32) on the same rows), at decode-kernel speed. */
 HB_API int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, const int32_t* ids, const float* w, int M, int K,
                           const void* x_bf16, int H, int I, float limit, float* out, void* ws, int S, void* stream, const hb_pf_combine* cmb);
 /* The same GEMM on one dense NVFP4 matrix: y[m,n] = xg[m]·W.g·Σ_k xq[m,k]·xs[m,k/16]·W[n,k], fp32 [M, ldy].  xq / xs / xg as written by

@@ -115,3 +115,28 @@ def test_moe_prefill_combine_matches_separate(E, oracle):
     sep = E.moe_combine(routed, shared, lg, 1)
     torch.cuda.synchronize()
     assert torch.equal(fused.view(torch.int16), sep.view(torch.int16))
+
+
+def test_moe_prefill_bf16_activations_equals_decode_operator(E, oracle):
+    """HB_FLAG_PREFILL_A16: hb_moe_prefill with bf16 activations is the decode arithmetic on sub-chunks of rows — bit-identical to
+    hb_moe_decode_routed_f32 on the same rows, and within the expert-output gate of the W4A16 oracle."""
+    dev = torch.device("cuda")
+    H, I, E_, K, M = 512, 256, 8, 2, 150
+    rng = np.random.default_rng(21)
+    recs = random_records(oracle, H, I, E_, 21)
+    keep = upload(recs, dev)
+    tab = E.rec_table(keep)
+    ids_np = np.stack([rng.permutation(E_)[:K] for _ in range(M)]).astype(np.int32)
+    w_np = rng.random((M, K), dtype=np.float32)
+    ids, w = torch.tensor(ids_np, device=dev), torch.tensor(w_np, device=dev)
+    x = torch.tensor(rng.standard_normal((M, H)).astype(np.float32)).to(torch.bfloat16).to(dev)
+    ctx16 = E.Context(flags=4)
+    out = E.fn_moe_prefill(tab, 0, E_, ids, w, x, H, I, S=64, ctx=ctx16)
+    ref = E.moe_decode_routed_f32(ids, w, tab, 0, E_, x, H, I)
+    torch.cuda.synchronize()
+    ctx16.check_device()
+    assert torch.equal(out, ref)
+    xs = x.float().cpu().numpy()
+    orc = oracle.moe_routed(H, I, ids_np, w_np, recs, xs, 0.0, 0)
+    rms = np.sqrt((orc.astype(np.float64) ** 2).mean(axis=1, keepdims=True)) + 1e-12
+    assert np.max(np.abs(out.cpu().numpy() - orc) / rms) <= 2e-2
