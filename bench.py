@@ -7,7 +7,7 @@
 
 One "step" is one decode step of B tokens through the 48 MoE layers (router → routed NVFP4 experts → NVFP4 shared expert →
 combine), each layer with its own weights, so a step streams ≈ 48 × U × 1.77 MB of distinct expert records (far more than the
-126 MB L2).  The metric is MoE-layer tokens/s = B · layers / step time, whole job.  Printed: ONE JSON line (see DESIGN.md).
+126 MB L2).  The metric is MoE-layer tokens/s = B · layers / step time, whole job.  Printed: ONE JSON line.
 
   value        device-resident inputs, the 48 layers replayed from one CUDA graph, timed with CUDA events on the launching stream
   e2e          the same step through the Python mirror of the C ABI with pinned HOST inputs and outputs: H2D of logits and
@@ -45,7 +45,7 @@ def rec_bytes(H, I):
 
 
 def layer_algorithmic_bytes(H, I, E, K, B, U):
-    """SURVEY/BASELINE figure: U records (incl. the shared expert) + x + out + logits + ids/w."""
+    """Algorithmic bytes of one decode layer: U records (incl. the shared expert) + x + out + logits + ids/w."""
     return U * rec_bytes(H, I) + B * H * 2 + B * H * 2 + B * (E + 1) * 4 + B * K * 8
 
 
