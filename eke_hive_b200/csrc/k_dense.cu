@@ -18,7 +18,8 @@
 namespace hb {
 
 constexpr int kDSlice = 256;            // columns per pipeline stage
-constexpr int kDWarps = 8;              // consumer warps per CTA, 16 weight rows each
+constexpr int kDWarps = 8;              // streaming warps per CTA (one slice of K each); a ninth warp sums their partial tiles
+constexpr int kDSlots = 4;              // ring of partial-tile slots between the streaming warps and the summing warp
 __host__ __device__ constexpr int dense_stages(int fmt) { return fmt == HB_FMT_NVFP4 ? 3 : 4; }
 // K range of one CTA (slices of 256 columns whose B fragments sit in shared memory): sized for two CTAs per SM
 __host__ __device__ constexpr int dense_max_slices(int) { return kDWarps; }     // one slice per warp
@@ -119,6 +120,7 @@ __device__ __forceinline__ void dense_build_row_slice(uint4 v, int cs, int tok, 
 struct DenseMat { const uint8_t* w; const uint8_t* wh; const uint8_t* s; const uint8_t* zp; float g; };
 struct DenseArgs {
   DenseMat mat[2]; int n_mats;
+  uint32_t* err;                          // the context's error word (bounded waits)
   int N, K, M, ksplit, slices, ldx;       // slices = K / 256
   const __nv_bfloat16* x;
   float* part;                            // [n_mats][ksplit][8][N]
@@ -140,15 +142,17 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // 8 consecutive slices of the same 16 rows: long contiguous runs per row), and the warps' partial tiles meet in shared memory
 // in warp order once per strip.
 template <int FMT>
-__global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseArgs a) {
+__global__ void __launch_bounds__((kDWarps + 1) * 32, 2) dense_stream_kernel(DenseArgs a) {
   constexpr DenseFmt F = dense_fmt(FMT);
   constexpr int STG = dense_stage_bytes(FMT), NST = dense_stages(FMT), MAXSL = dense_max_slices(FMT);
   extern __shared__ __align__(128) uint8_t dsm[];
   uint4* xb_s = reinterpret_cast<uint4*>(dsm);                                            // [MAXSL][planes][256] uint4
   float2* sums_s = reinterpret_cast<float2*>(dsm + (size_t)MAXSL * F.planes * 4096);      // [MAXSL][4 groups][8 rows] (S0, S1)
   float* inv_s = reinterpret_cast<float*>(dsm + (size_t)MAXSL * F.planes * 4096 + (size_t)MAXSL * 256);   // [MAXSL][8 rows] 1 / slice factor
-  float4* red_s = reinterpret_cast<float4*>(inv_s + MAXSL * 8);                           // [2][warps][32 lanes] partial tiles
-  uint8_t* rings = reinterpret_cast<uint8_t*>(red_s + 2 * kDWarps * 32);
+  float4* red_s = reinterpret_cast<float4*>(inv_s + MAXSL * 8);                           // [kDSlots][warps][32 lanes] partial tiles
+  uint64_t* redbar = reinterpret_cast<uint64_t*>(red_s + kDSlots * kDWarps * 32);         // [kDSlots] the slot's partial tiles are written
+  uint64_t* redfree = redbar + kDSlots;                                                   // [kDSlots] the slot has been summed and may be reused
+  uint8_t* rings = reinterpret_cast<uint8_t*>(redfree + kDSlots);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int ks = blockIdx.y;
   const int sl0 = (int)((long long)a.slices * ks / a.ksplit), sl1 = (int)((long long)a.slices * (ks + 1) / a.ksplit), nsl = sl1 - sl0;
@@ -190,9 +194,13 @@ __global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseAr
     if (++istage == NST) istage = 0;
     cp_async_commit();                                              // always commit: the group count stays in step with the strip count
   };
-  for (int i = 0; i < NST - 1; ++i) issue_next();                  // weights do not depend on the previous kernel: fetch before waiting for it
+  if (threadIdx.x == 0) {
+    for (int q = 0; q < kDSlots; ++q) { mbar_init(&redbar[q], (uint32_t)nsl); mbar_init(&redfree[q], 1); }
+    mbar_fence_init();
+  }
+  if (warp < kDWarps) for (int i = 0; i < NST - 1; ++i) issue_next();   // weights do not depend on the previous kernel: fetch before waiting for it
   griddep_wait();
-  for (int it = warp; it < nsl * 8; it += kDWarps) {                // B fragments of this K range, one warp per (slice, row)
+  for (int it = warp; it < nsl * 8; it += kDWarps + 1) {                // B fragments of this K range, one warp per (slice, row)
     const int bs = it >> 3, tok = it & 7;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (tok < a.M) v = __ldcg(reinterpret_cast<const uint4*>(a.x + (size_t)tok * a.ldx + (size_t)(sl0 + bs) * kDSlice) + lane);
@@ -208,13 +216,36 @@ __global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseAr
 #pragma unroll
     for (int q = 0; q < 8; ++q) { const uint4 v = xb_i[q * 32 + lane]; bq[4 * q] = v.x; bq[4 * q + 1] = v.y; bq[4 * q + 2] = v.z; bq[4 * q + 3] = v.w; }
   }
-  int cstage = 0, par = 0;
-  for (int strip = blockIdx.x; strip < n_strips; strip += gridDim.x, par ^= 1) {
+  if (warp == kDWarps) {
+    // ------------------------------------------------------------------------------------------------ summing warp
+    // waits for a slot's partial tiles, adds them in warp order (fixed: deterministic), writes [mat][ks][row 0..7][N], frees the slot
+    int slot = 0; uint32_t rph = 0;
+    for (int strip = blockIdx.x; strip < n_strips; strip += gridDim.x) {
+      if (!mbar_wait(&redbar[slot], rph, a.err, 0x10000u)) break;
+      const int mat_i = strip >= strips_per_mat ? 1 : 0, n0 = (mat_i ? strip - strips_per_mat : strip) * 16;
+      const float gsc = FMT == HB_FMT_NVFP4 ? (mat_i ? a.mat[1].g : a.mat[0].g) : 1.f;
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int w2 = 0; w2 < nsl; ++w2) { const float4 p = red_s[(slot * kDWarps + w2) * 32 + lane]; v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w; }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&redfree[slot]);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int tok = 2 * t + (c & 1), n = n0 + g + (c >> 1) * 8;
+        if (tok < a.M && n < a.N) a.part[(((size_t)mat_i * a.ksplit + ks) * 8 + tok) * a.N + n] = v[c] * gsc;
+      }
+      if (++slot == kDSlots) { slot = 0; rph ^= 1u; }
+    }
+    return;
+  }
+  if (!active) { cp_async_wait<0>(); return; }
+  int cstage = 0, slot = 0;
+  uint32_t rph = 0;
+  for (int strip = blockIdx.x; strip < n_strips; strip += gridDim.x) {
     issue_next();
     cp_async_wait<NST - 1>();
     __syncwarp();
     float total[4] = {0.f, 0.f, 0.f, 0.f};
-    if (active) {
+    {
     const uint8_t* st = ring + (size_t)cstage * STG;
     if constexpr (FMT == HB_FMT_NVFP4) {
       float acc[4];
@@ -276,18 +307,12 @@ __global__ void __launch_bounds__((kDWarps) * 32, 2) dense_stream_kernel(DenseAr
     }
     __syncwarp();
     if (++cstage == NST) cstage = 0;
-    // the warps' partial tiles → one tile, summed in warp order, → [mat][ks][row 0..7][N]
-    red_s[(par * kDWarps + warp) * 32 + lane] = make_float4(total[0], total[1], total[2], total[3]);
-    __syncthreads();
-    if (threadIdx.x < 128) {
-      const int ln = threadIdx.x >> 2, c = threadIdx.x & 3, tg = ln >> 2, tt = ln & 3;   // element c of lane ln's fragment
-      float v = 0.f;
-      for (int w2 = 0; w2 < nsl; ++w2) v += reinterpret_cast<const float*>(red_s + (par * kDWarps + w2) * 32 + ln)[c];
-      const int mat_i = strip >= strips_per_mat ? 1 : 0, n0 = (mat_i ? strip - strips_per_mat : strip) * 16;
-      const int tok = 2 * tt + (c & 1), n = n0 + tg + (c >> 1) * 8;
-      const float gsc = FMT == HB_FMT_NVFP4 ? (mat_i ? a.mat[1].g : a.mat[0].g) : 1.f;
-      if (tok < a.M && n < a.N) a.part[(((size_t)mat_i * a.ksplit + ks) * 8 + tok) * a.N + n] = v * gsc;
-    }
+    // hand the partial tile to the summing warp through the slot ring; no streaming warp waits for another one
+    if (!mbar_wait(&redfree[slot], rph ^ 1u, a.err, 0x20000u)) break;   // the slot's previous contents have been summed
+    red_s[(slot * kDWarps + warp) * 32 + lane] = make_float4(total[0], total[1], total[2], total[3]);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&redbar[slot]);
+    if (++slot == kDSlots) { slot = 0; rph ^= 1u; }
   }
   cp_async_wait<0>();
 }
@@ -331,7 +356,7 @@ namespace {
 int dense_ksplit(int fmt, int K) { const int sl = K / kDSlice, mx = dense_max_slices(fmt); return (sl + mx - 1) / mx; }
 size_t dense_smem(int fmt) {
   const DenseFmt F = dense_fmt(fmt);
-  return (size_t)dense_max_slices(fmt) * F.planes * 4096 + (size_t)dense_max_slices(fmt) * 256 + (size_t)dense_max_slices(fmt) * 32 + 2 * kDWarps * 32 * 16 + (size_t)kDWarps * dense_stages(fmt) * dense_stage_bytes(fmt);
+  return (size_t)dense_max_slices(fmt) * F.planes * 4096 + (size_t)dense_max_slices(fmt) * 256 + (size_t)dense_max_slices(fmt) * 32 + kDSlots * kDWarps * 32 * 16 + 2 * kDSlots * 8 + (size_t)kDWarps * dense_stages(fmt) * dense_stage_bytes(fmt);
 }
 int check_mat(hb_ctx* ctx, const hb_qmat* W, const char* fn) {
   HB_REQUIRE(ctx, W && W->w && W->s, HB_ERR_INVALID, "%s: NULL matrix", fn);
@@ -355,7 +380,7 @@ int dense_pass(hb_ctx* ctx, const hb_qmat* A, const hb_qmat* B2, const void* x, 
   DenseArgs a{};
   a.mat[0] = to_mat(A); if (B2) a.mat[1] = to_mat(B2);
   a.n_mats = mats; a.N = N; a.K = K; a.M = M; a.ksplit = ksplit; a.slices = slices; a.ldx = ldx;
-  a.x = reinterpret_cast<const __nv_bfloat16*>(x); a.part = part;
+  a.x = reinterpret_cast<const __nv_bfloat16*>(x); a.part = part; a.err = ctx->dev_err;
   int r;
   int per_split = (2 * ctx->sm_count) / ksplit;                    // two CTAs per SM in all, shared out over the K splits
   const int strips = ((N + 15) / 16) * mats, max_useful = strips;
@@ -364,7 +389,7 @@ int dense_pass(hb_ctx* ctx, const hb_qmat* A, const hb_qmat* B2, const void* x, 
   const dim3 grid(per_split, ksplit, 1);
   auto fn = fmt == HB_FMT_NVFP4 ? dense_stream_kernel<HB_FMT_NVFP4> : fmt == HB_FMT_LB2_G64 ? dense_stream_kernel<HB_FMT_LB2_G64> : dense_stream_kernel<HB_FMT_LB3_G64>;
   if ((r = hb_launch(ctx, fmt == HB_FMT_NVFP4 ? "dense_stream_nvfp4" : fmt == HB_FMT_LB2_G64 ? "dense_stream_lb2" : "dense_stream_lb3", true, fn, grid,
-                     dim3(kDWarps * 32), dense_smem(fmt), st, a))) return r;
+                     dim3((kDWarps + 1) * 32), dense_smem(fmt), st, a))) return r;
   return hb_launch(ctx, "dense_reduce", true, dense_reduce_kernel, dim3((unsigned)(((size_t)M * N + 255) / 256)), dim3(256), 0, st, (const float*)part, mats,
                    ksplit, M, N, mode, y, ldy);
 }
