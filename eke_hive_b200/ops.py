@@ -7,6 +7,7 @@ Every call is asynchronous on the current torch CUDA stream and raises HbError o
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import numpy as np
 import torch
@@ -97,9 +98,10 @@ _CTX: dict[int, Context] = {}
 
 
 def context(device: int | None = None) -> Context:
+    """The process-wide default context of a device.  HIVE_B200_FLAGS (an integer, default 0) gives its hb_config flags."""
     d = torch.cuda.current_device() if device is None else device
     if d not in _CTX:
-        _CTX[d] = Context(d)
+        _CTX[d] = Context(d, flags=int(os.environ.get("HIVE_B200_FLAGS", "0")))
     return _CTX[d]
 
 
