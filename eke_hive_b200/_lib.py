@@ -97,6 +97,14 @@ def load() -> C.CDLL:
         "hb_moe_decode_routed_static": (i, [vp, vp, vp, i, i, vp, i, i, vp, i, i, f, C.POINTER(PfCombine), vp]),
         "hb_moe_decode_routed_f32": (i, [vp, vp, vp, i, i, vp, i, i, vp, i, i, f, vp, vp, vp]),
         "hb_moe_decode_ep_local": (i, [vp, vp, vp, i, i, i, vp, i, i, vp, i, i, i, f, vp, i, i, vp, vp, vp, vp]),
+        "hb_ep_rec_bytes": (sz, [i, i]),
+        "hb_ep_enable_peer": (i, [vp, i]),
+        "hb_ep_create": (i, [vp, i, i, i, i, i, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
+        "hb_ep_destroy": (None, [vp]),
+        "hb_ep_push_rows": (i, [vp, vp, i, vp, vp, vp]),
+        "hb_ep_wait_rows": (i, [vp, vp]),
+        "hb_ep_push_partials": (i, [vp, vp, vp]),
+        "hb_ep_combine": (i, [vp, vp, vp, i, i, vp, vp]),
         "hb_moe_layer_decode": (i, [vp, vp, i, i, i, i, i, i, vp, f, vp, i, vp, i, vp, i, i, f, vp, vp, vp, vp, vp]),
         "hb_dense_gemv_ws_bytes": (sz, [i, i, i, i]),
         "hb_dense_gemv": (i, [vp, C.POINTER(QMat), vp, i, i, vp, vp, i, vp, vp]),

@@ -7,7 +7,11 @@ The reference engine has no multi-GPU code; this is the sharded form of its MoE 
     place from the gathered buffer (pairs whose expert lives elsewhere are skipped through NULL table entries), plus the shared
     expert on the local rows → reduce-scatter of the fp32 routed sums → combine on the local rows.
 
-Remote data always lands in local memory through the collective before a kernel reads it; no kernel touches a peer's memory.
+Two transports.  "nccl": all-gather and reduce-scatter of torch.distributed; remote data lands in local memory through the
+collective before a kernel reads it.  "peer" (HIVE_B200_EP=peer or transport="peer"): the library's own kernels write the rows and the
+partial sums straight into the other GPUs' exchange buffers over NVLink (plain peer stores, buffers mapped through CUDA IPC) and
+announce them with step-number flags — no collective launch on the layer's critical path, and the cross-rank sum is added in
+rank order by the combine kernel.  Reads of exchanged data are always local.
 The fp32 routed sum of a row is then a sum over ranks of per-rank sums in k order, which differs from the single-GPU k order
 only by fp32 reassociation; routing indices are unaffected.
 
@@ -15,6 +19,9 @@ only by fp32 reassociation; routing indices are unaffected.
 exchange logic runs under the gloo backend without a GPU.
 """
 from __future__ import annotations
+
+import os
+import sys
 
 import torch
 import torch.distributed as dist
@@ -33,7 +40,7 @@ def local_table(E: int, world: int, rank: int, ptr_of) -> list[int]:
 
 class ExpertParallelMoE:
     def __init__(self, ops, ctx, H: int, I: int, E: int, K: int, B: int, world: int, rank: int, device, group=None, renorm=True,
-                 logits_bf16=True, limit=0.0):
+                 logits_bf16=True, limit=0.0, transport: str | None = None):
         self.ops, self.ctx, self.H, self.I, self.E, self.K, self.B = ops, ctx, H, I, E, K, B
         self.world, self.rank, self.dev, self.group = world, rank, device, group
         self.renorm, self.logits_bf16, self.limit = renorm, logits_bf16, limit
@@ -50,14 +57,64 @@ class ExpertParallelMoE:
         self.routed = torch.empty((B, H), dtype=torch.float32, device=device)
         self.shared = torch.zeros((B, H), dtype=torch.bfloat16, device=device)
         self.reduce_scatter = dist.get_backend(group) != "gloo"            # gloo has no reduce-scatter: all-reduce and slice there
+        want_peer = (transport or os.environ.get("HIVE_B200_EP", "nccl")) == "peer" and self.reduce_scatter and hasattr(ops, "PeerExchange")
+        self.peer = self._setup_peer() if want_peer else None
+        self.transport = "peer" if self.peer is not None else "nccl"
         ws_bytes = getattr(ops, "moe_decode_ws_bytes", lambda n, h, i: 256)(world * B * (K + 1), H, I)
         self.ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
+
+    def _setup_peer(self):
+        """Maps every rank's exchange memory into this process (CUDA IPC) and builds the hb_ep object.  All ranks agree on the
+        outcome: if any rank fails, every rank falls back to the NCCL transport."""
+        ops, G, B, H, K = self.ops, self.world, self.B, self.H, self.K
+        peer, err = None, ""
+        try:
+            from torch.multiprocessing.reductions import reduce_tensor
+            off, total, rec = ops.PeerExchange.layout(G, B, H, K)
+            assert rec == self.rec_bytes
+            mine = torch.zeros(total, dtype=torch.uint8, device=self.dev)
+            torch.cuda.synchronize(self.dev)
+            fn, args = reduce_tensor(mine)
+            gathered = [None] * G
+            dist.all_gather_object(gathered, args, group=self.group)
+            bufs = [mine if r == self.rank else fn(*gathered[r]) for r in range(G)]
+            peer = ops.PeerExchange(bufs, self.rank, G, B, H, K, ctx=self.ctx)
+            # the gathered rows are read in place from this rank's own buffer
+            view = mine[off["recv"]:off["recv"] + G * B * rec].view(G * B, rec)
+            self.recv = view
+            self.x_all = view[:, :H * 2].view(torch.bfloat16)
+            self.ids_all = view[:, H * 2:H * 2 + K * 4].view(torch.int32)
+            self.w_all = view[:, H * 2 + K * 4:H * 2 + K * 8].view(torch.float32)
+        except Exception as e:  # noqa: BLE001 - any failure means "use the collective library"
+            err = f"{type(e).__name__}: {e}"
+            peer = None
+        ok = torch.tensor([1 if peer is not None else 0], dtype=torch.int32, device=self.dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) == 0:
+            if err and self.rank == 0:
+                print(f"[ep] peer-memory transport unavailable ({err}); using NCCL collectives", file=sys.stderr, flush=True)
+            if peer is not None:                                           # another rank failed: drop the views into the exchange memory
+                self.recv = torch.zeros((G * B, self.rec_bytes), dtype=torch.uint8, device=self.dev)
+                self.x_all = self.recv[:, :H * 2].view(torch.bfloat16)
+                self.ids_all = self.recv[:, H * 2:H * 2 + K * 4].view(torch.int32)
+                self.w_all = self.recv[:, H * 2 + K * 4:H * 2 + K * 8].view(torch.float32)
+            return None
+        dist.barrier(group=self.group)                                     # nobody pushes before everybody has mapped and zeroed
+        return peer
 
     def layer(self, logits, x, tab, li: int, shared_ptr: int, gate_col: int, ids_out, w_out, out):
         """logits fp32 [B, ≥E(+1)], x bf16 [B, H] local rows; tab: device table [L·E] of local record pointers (0 = elsewhere);
         shared_ptr: this layer's shared-expert record (0 = none).  Writes ids_out / w_out [B, K] and out bf16 [B, H]."""
         ops, B, H, K = self.ops, self.B, self.H, self.K
         ops.router_softmax_topk(logits, K, self.renorm, self.logits_bf16, E=self.E, ids=ids_out, w=w_out, ctx=self.ctx)
+        if self.peer is not None:
+            self.peer.push_rows(x, ids_out, w_out)
+            self.peer.wait_rows()
+            ops.moe_decode_ep_local(self.ids_all, self.w_all, tab, li, self.E, self.x_all, H, self.I, self.part, shared_ptr=shared_ptr,
+                                    sh_row0=self.rank * B, sh_rows=B, shared_out=self.shared, limit=self.limit, ws=self.ws, ctx=self.ctx)
+            self.peer.push_partials(self.part)
+            self.peer.combine(self.shared if shared_ptr else None, logits if (shared_ptr and gate_col >= 0) else None, max(gate_col, 0), out)
+            return out
         # pack [row | ids | w] per row (one kernel), one all-gather
         torch.cat([x.view(torch.uint8).view(B, H * 2), ids_out.view(torch.uint8).view(B, K * 4), w_out.view(torch.uint8).view(B, K * 4)], dim=1,
                   out=self.send[:, :H * 2 + K * 8])

@@ -17,7 +17,7 @@ from ._lib import Config, HbError, MoePair, PfCombine, RecLayout
 
 __all__ = ["Context", "context", "ExpertRecLayout", "nvfp4_dequant", "nvfp4_gemv", "nvfp4_quantize", "a4_quant", "router_softmax_topk",
            "router_topk", "build_moe_pairs", "moe_combine", "moe_decode_ws_bytes", "moe_decode", "fn_moe_decode_routed", "fn_moe_decode_routed_static", "static_max_pairs", "moe_decode_routed_f32", "moe_layer_decode",
-           "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "dispatch_plan", "moe_decode_ep_local", "moe_prefill_supported", "moe_prefill_ws_bytes", "fn_moe_prefill", "nvfp4_gemm_a4", "fp4_peak_probe", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
+           "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "dispatch_plan", "PeerExchange", "moe_decode_ep_local", "moe_prefill_supported", "moe_prefill_ws_bytes", "fn_moe_prefill", "nvfp4_gemm_a4", "fp4_peak_probe", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
 
 
 def _L():
@@ -369,6 +369,54 @@ def dispatch_plan(ids_host: np.ndarray, E: int, H: int, I: int):
     d = {n: getattr(p, n) for n, _ in Plan._fields_}
     d["counts"] = counts
     return d
+
+
+class PeerExchange:
+    """hb_ep: the expert-parallel exchanges over NVLink peer memory.  `bufs[p]` is a uint8 device tensor holding rank p's exchange
+    memory (this rank's own allocation for p == rank, the peers' mapped into this process), laid out by `layout(...)`."""
+
+    @staticmethod
+    def layout(world: int, B: int, H: int, K: int):
+        """(offsets dict, total bytes) of one rank's exchange memory: gather buffer, gather flags, partial buffer, partial flags."""
+        rec = int(_L().hb_ep_rec_bytes(H, K))
+        off, o = {}, 0
+        for name, size in (("recv", world * B * rec), ("ag_flag", 256), ("rs", world * B * H * 4), ("rs_flag", 256)):
+            off[name] = o
+            o += (size + 255) // 256 * 256
+        return off, o, rec
+
+    def __init__(self, bufs, rank: int, world: int, B: int, H: int, K: int, ctx: Context | None = None):
+        self.ctx = ctx or context()
+        self.bufs = bufs                                               # keeps the mappings alive
+        off, total, self.rec_bytes = self.layout(world, B, H, K)
+        for p, b in enumerate(bufs):
+            assert b.numel() >= total and b.dtype == torch.uint8
+            if b.device.index != self.ctx.device:
+                self.ctx.check(_L().hb_ep_enable_peer(self.ctx.handle, b.device.index))
+        arr = lambda name: (C.c_void_p * world)(*[b.data_ptr() + off[name] for b in bufs])
+        self._h = C.c_void_p()
+        self.ctx.check(_L().hb_ep_create(self.ctx.handle, rank, world, B, H, K, arr("recv"), arr("ag_flag"), arr("rs"), arr("rs_flag"), C.byref(self._h)))
+        self.off = off
+
+    def push_rows(self, x, ids, w):
+        self.ctx.check(_L().hb_ep_push_rows(self._h, _p(x), x.stride(0), _p(ids), _p(w), _stream()))
+
+    def wait_rows(self):
+        self.ctx.check(_L().hb_ep_wait_rows(self._h, _stream()))
+
+    def push_partials(self, part):
+        self.ctx.check(_L().hb_ep_push_partials(self._h, _p(part), _stream()))
+
+    def combine(self, shared, lg, col: int, out):
+        self.ctx.check(_L().hb_ep_combine(self._h, _p(shared), _p(lg), 0 if lg is None else lg.stride(0), col, _p(out), _stream()))
+
+    def __del__(self):
+        try:
+            if self._h:
+                _L().hb_ep_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
 
 
 # ---------------------------------------------------------------------------------------------------- prefill (tcgen05 grouped GEMM)

@@ -175,6 +175,33 @@ HB_API int hb_moe_decode_routed_f32(hb_ctx* ctx, const int32_t* ids, const float
 HB_API int hb_moe_decode_ep_local(hb_ctx* ctx, const int32_t* ids, const float* w, int ld_ids, int M, int K, const uint8_t* const* rec_tab, int li,
                                   int E, const void* x_bf16, int ldx, int H, int I, float limit, const uint8_t* shared_rec, int sh_row0, int sh_rows,
                                   float* routed_out, void* shared_out_bf16, void* ws, void* stream);
+/* (No counterpart in the reference.)  The two exchanges of an expert-parallel decode layer done by this library's own kernels over
+ * NVLink peer memory instead of a collective library: rows are pushed into every rank's gather buffer, partial sums into the
+ * owning rank's partial buffer, each followed by a step-number flag the receiver polls (bounded; a wait that gives up sets the
+ * context's error word — hb_check_device reports it — and later waits return at once).
+ *   hb_ep_rec_bytes(H, K)            bytes of one exchanged row record [bf16 row | int32 ids | fp32 weights], padded to 16
+ *   hb_ep_enable_peer(ctx, dev)      lets the context's device address memory of device `dev`
+ *   hb_ep_create(...)                recv[p], ag_flag[p], rs[p], rs_flag[p] for p < world: addresses, valid on THIS device, of rank p's
+ *                                    gather buffer [world·B·rec_bytes], gather flags [world] u32, partial buffer [world·B·H] f32
+ *                                    and partial flags [world] u32 (the caller allocates its own, zero-filled, and maps its
+ *                                    peers' through CUDA IPC or any other way); entry `rank` is the caller's own
+ *   hb_ep_push_rows                  pack this rank's B rows and push them to every rank
+ *   hb_ep_wait_rows                  returns (on the stream) when every rank's rows of this step are in the own gather buffer; then
+ *                                    hb_moe_decode_ep_local reads them in place
+ *   hb_ep_push_partials              part fp32 [world·B, H] (hb_moe_decode_ep_local's routed_out): rows of rank p → rank p
+ *   hb_ep_combine                    waits for every rank's partials of the own rows, adds them in rank order, applies the
+ *                                    shared-expert combine (hb_moe_combine's arithmetic) → out bf16 [B,H]; ends the step
+ * All ranks must issue the same sequence of steps.  Calls of one hb_ep must not overlap. */
+typedef struct hb_ep hb_ep;
+HB_API size_t hb_ep_rec_bytes(int H, int K);
+HB_API int hb_ep_enable_peer(hb_ctx* ctx, int peer_device);
+HB_API int hb_ep_create(hb_ctx* ctx, int rank, int world, int B, int H, int K, void* const* recv, void* const* ag_flag, void* const* rs,
+                        void* const* rs_flag, hb_ep** out);
+HB_API void hb_ep_destroy(hb_ep* ep);
+HB_API int hb_ep_push_rows(hb_ep* ep, const void* x_bf16, int ldx, const int32_t* ids, const float* w, void* stream);
+HB_API int hb_ep_wait_rows(hb_ep* ep, void* stream);
+HB_API int hb_ep_push_partials(hb_ep* ep, const float* part, void* stream);
+HB_API int hb_ep_combine(hb_ep* ep, const void* shared_bf16, const float* lg, int ld, int col, void* out_bf16, void* stream);
 /* A whole decode MoE layer in one call: router (softmax when bias == NULL and sigmoid_scale == 0, else sigmoid+bias) → routed
  * experts → the always-on shared expert given as one more NVFP4 record (weight 1, every row; NULL = none) → combine.
  * Composition of the operators above in the order of engine/src/qwen/qwen_engine.cpp:818-878; ids_out / w_out [M,K] receive

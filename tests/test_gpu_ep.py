@@ -1,0 +1,92 @@
+"""Expert parallelism on real GPUs (needs ≥ 2): two ranks, one GPU each, over NCCL.  Both transports of ExpertParallelMoE — the
+collective library and the library's own peer-memory exchange — must reproduce the single-GPU layer on each rank's rows:
+routing bit-exact, outputs equal up to the fp32 reassociation of the cross-rank sum; at two ranks the two transports add the
+same two numbers and must agree bit for bit.  Ranks leave only after a barrier, with nothing in flight."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+H, I, E_, K, B, L = 2048, 512, 16, 4, 8, 3
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    sys.path.insert(0, str(ROOT)); sys.path.insert(0, str(ROOT / "tests"))
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import eke_hive_b200 as E
+        from eke_hive_b200.ep import ExpertParallelMoE, expert_range
+        from oracle import oracle as O
+        from util import random_records, upload
+        ctx = E.context()
+        recs = random_records(O, H, I, L * (E_ + 1), seed=77)              # every rank builds the same experts; last of each layer = shared
+        drecs = upload(recs, dev)
+        lo, hi = expert_range(E_, world, rank)
+        full = E.rec_table([drecs[li * (E_ + 1) + e] for li in range(L) for e in range(E_)])
+        local = E.rec_table([drecs[li * (E_ + 1) + e] if lo <= e < hi else None for li in range(L) for e in range(E_)] + [drecs[0]])[:L * E_]
+        rng = np.random.default_rng(5)                                      # the same stream on every rank: the global batch
+        x_all = torch.from_numpy(O.bf16r(rng.normal(0, 1, (L, world * B, H)).astype(np.float32))).to(torch.bfloat16)
+        lg_all = torch.from_numpy(rng.normal(0, 1, (L, world * B, E_ + 1)).astype(np.float32))
+        x = x_all[:, rank * B:(rank + 1) * B].contiguous().to(dev); lg = lg_all[:, rank * B:(rank + 1) * B].contiguous().to(dev)
+        outs = {}
+        for transport in ("nccl", "peer"):
+            ep = ExpertParallelMoE(E, ctx, H, I, E_, K, B, world, rank, dev, transport=transport)
+            ids = torch.empty((L, B, K), dtype=torch.int32, device=dev); w = torch.empty((L, B, K), dtype=torch.float32, device=dev)
+            out = torch.empty((L, B, H), dtype=torch.bfloat16, device=dev)
+            for rep in range(2):                                            # twice: the exchange buffers and step counters are reused
+                for li in range(L):
+                    ep.layer(lg[li], x[li], local, li, drecs[li * (E_ + 1) + E_].data_ptr(), E_, ids[li], w[li], out[li])
+            torch.cuda.synchronize()
+            ctx.check_device()
+            outs[transport] = (ep.transport, ids.clone(), out.clone())
+            dist.barrier()
+        # single-GPU layer on this rank's rows, all experts resident
+        rid = torch.empty((L, B, K), dtype=torch.int32, device=dev); rout = torch.empty((L, B, H), dtype=torch.bfloat16, device=dev)
+        for li in range(L):
+            i2, w2, o2 = E.moe_layer_decode(lg[li], x[li], full, li, E_, K, H, I, shared_rec=drecs[li * (E_ + 1) + E_], gate_col=E_)
+            rid[li] = i2; rout[li] = o2
+        torch.cuda.synchronize()
+        ref = rout.float()
+        rms = ref.pow(2).mean(dim=-1, keepdim=True).sqrt() + 1e-30
+        res = {"rank": rank}
+        for t, (used, ids, out) in outs.items():
+            res[t] = (used, bool(torch.equal(ids, rid)), float(((out.float() - ref).abs() / rms).max()))
+        res["same"] = bool(torch.equal(outs["nccl"][2].view(torch.int16), outs["peer"][2].view(torch.int16)))
+        q.put(res)
+        dist.barrier()
+        torch.cuda.synchronize()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_both_transports_match_single_gpu():
+    import torch.multiprocessing as mp
+    world = 2
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for r in res:
+        for t in ("nccl", "peer"):
+            used, ok_ids, err = r[t]
+            assert used == t, f"rank {r['rank']}: asked for {t}, ran {used}"
+            assert ok_ids, f"rank {r['rank']} {t}: routing differs"
+            assert err <= 8e-3, f"rank {r['rank']} {t}: error {err} x RMS"       # one bf16 ulp of the output after fp32 reassociation
+        assert r["same"], f"rank {r['rank']}: the two transports differ at two ranks"

@@ -235,3 +235,27 @@ def test_ep_local_matches_separate_operators(E, oracle):
     E.context().check_device()
     assert torch.equal(routed, ref)
     assert torch.equal(shared.float(), sh_ref)
+
+
+def test_glm_shaped_layer_with_zipf_bias(E, oracle):
+    """The GLM-style configuration at its full shape: hidden 4096, intermediate 1536, 160 routed experts, top-8 + shared expert,
+    8 tokens, sigmoid router with a Zipf(1.1) log-weight bias over a seeded permutation of the experts, SwiGLU clamp 10."""
+    import torch
+    H, I, Ex, K, M = 4096, 1536, 160, 8, 8
+    rng = np.random.default_rng(160)
+    recs = random_records(oracle, H, I, Ex + 1, seed=160)
+    x = oracle.bf16r(rng.normal(0, 1, (M, H)).astype(np.float32))
+    lg = rng.normal(0, 1, (M, Ex)).astype(np.float32)
+    zipf = 1.0 / np.arange(1, Ex + 1) ** 1.1
+    bias = np.log(zipf / zipf.sum())[rng.permutation(Ex)].astype(np.float32)
+    drecs = upload(recs)
+    tab = E.rec_table(drecs[:Ex])
+    ids, w, out = E.moe_layer_decode(torch.from_numpy(lg).cuda(), bf16_tensor(x), tab, 0, Ex, K, H, I, shared_rec=drecs[Ex], gate_col=-1,
+                                     bias=torch.from_numpy(bias).cuda(), sigmoid_scale=2.5, limit=10.0)
+    rids, rw, rout = oracle.moe_layer(H, I, lg, x, recs[:Ex], K, shared_rec=recs[Ex], router="sigmoid", bias=bias, scale=2.5, limit=10.0)
+    assert np.array_equal(ids.cpu().numpy(), rids)
+    assert w.cpu().numpy().tobytes() == rw.tobytes()
+    assert rel_rms_err(out.float().cpu().numpy(), oracle.bf16_to_f32(rout)) <= TOL
+    hot = np.bincount(rids.ravel(), minlength=Ex)
+    assert hot.max() >= 4                                            # the bias does skew the routing: some expert takes several of the 8 rows
+    E.context().check_device()

@@ -77,7 +77,8 @@ def _oracle_prefill(oracle, recs, H, I, ids, w, x_f32, limit=0.0):
     return out
 
 
-@pytest.mark.parametrize("H,I,E_,K,M,S", [(256, 256, 4, 2, 70, 70), (512, 256, 8, 2, 300, 128), (2048, 512, 16, 4, 200, 200)])
+@pytest.mark.parametrize("H,I,E_,K,M,S", [(256, 256, 4, 2, 70, 70), (512, 256, 8, 2, 300, 128), (2048, 512, 16, 4, 200, 200),
+                                            (7168, 2048, 3, 2, 40, 40)])          # last: the DeepSeek-shaped expert at full size
 def test_moe_prefill_vs_oracle(E, oracle, H, I, E_, K, M, S):
     dev = torch.device("cuda")
     rng = np.random.default_rng(H + I + M)
