@@ -368,6 +368,9 @@ def run_ours(args):
                 prof = ctx.profile_read()
                 ctx.profile(False)
                 prof = {k: {"launches": v[0], "total_ms": v[1], "mean_us": v[1] * 1e3 / max(v[0], 1)} for k, v in prof.items()}
+        if world > 1:
+            torch.cuda.synchronize()
+            ep.close()
         del logits, x, out, ids, wts, graphs, g
         torch.cuda.empty_cache()
 

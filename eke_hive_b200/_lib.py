@@ -98,7 +98,9 @@ def load() -> C.CDLL:
         "hb_moe_decode_routed_f32": (i, [vp, vp, vp, i, i, vp, i, i, vp, i, i, f, vp, vp, vp]),
         "hb_moe_decode_ep_local": (i, [vp, vp, vp, i, i, i, vp, i, i, vp, i, i, i, f, vp, i, i, vp, vp, vp, vp]),
         "hb_ep_rec_bytes": (sz, [i, i]),
-        "hb_ep_enable_peer": (i, [vp, i]),
+        "hb_ep_export": (i, [vp, vp, vp, C.POINTER(sz)]),
+        "hb_ep_import": (i, [vp, vp, sz, C.POINTER(vp), C.POINTER(vp)]),
+        "hb_ep_close": (i, [vp, vp]),
         "hb_ep_create": (i, [vp, i, i, i, i, i, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
         "hb_ep_destroy": (None, [vp]),
         "hb_ep_push_rows": (i, [vp, vp, i, vp, vp, vp]),

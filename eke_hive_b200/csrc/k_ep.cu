@@ -15,8 +15,11 @@
 // Every wait is bounded; a wait that gives up sets the context's error word, and once that word is set all later waits return at
 // once, so a lost peer ends the step in seconds instead of hanging the GPU.  No kernel here is ever launched twice on one GPU
 // to wait for itself: the kernel a wait depends on runs on another GPU.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include <cstring>
 
 #include "hb_common.cuh"
 #include "hb_kernels.h"
@@ -140,15 +143,48 @@ extern "C" {
 
 size_t hb_ep_rec_bytes(int H, int K) { return H > 0 && K > 0 ? ((size_t)H * 2 + (size_t)K * 8 + 15) / 16 * 16 : 0; }
 
-int hb_ep_enable_peer(hb_ctx* ctx, int peer_device) {
+// Sharing exchange memory between the ranks' processes.  The importing side opens the handle with ITS OWN device current and lazy
+// peer access, which is the documented way to make another device's allocation addressable from this device's kernels
+// (opening it under the exporting device's context and enabling peer access afterwards left the range unmapped for this device).
+int hb_ep_export(hb_ctx* ctx, const void* ptr, void* handle64, size_t* offset) {
   if (!ctx) return HB_ERR_INVALID;
-  if (peer_device == ctx->device) return HB_OK;
-  int can = 0;
-  HB_CUDA(ctx, cudaDeviceCanAccessPeer(&can, ctx->device, peer_device));
-  HB_REQUIRE(ctx, can, HB_ERR_UNSUPPORTED, "ep: device %d cannot access device %d", ctx->device, peer_device);
-  const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
-  if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); return HB_OK; }
-  HB_CUDA(ctx, e);
+  HB_REQUIRE(ctx, ptr && handle64 && offset, HB_ERR_INVALID, "ep_export: NULL argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t h;
+  HB_CUDA(ctx, cudaIpcGetMemHandle(&h, const_cast<void*>(ptr)));
+  typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+  static RangeFn range = nullptr;
+  if (!range) {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &f, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) range = reinterpret_cast<RangeFn>(f);
+  }
+  HB_REQUIRE(ctx, range, HB_ERR_CUDA, "ep_export: cuMemGetAddressRange is not available from this driver");
+  CUdeviceptr base = 0; size_t size = 0;
+  HB_REQUIRE(ctx, range(&base, &size, reinterpret_cast<CUdeviceptr>(ptr)) == CUDA_SUCCESS, HB_ERR_CUDA, "ep_export: cuMemGetAddressRange failed");
+  memcpy(handle64, &h, 64);
+  *offset = reinterpret_cast<uintptr_t>(ptr) - static_cast<uintptr_t>(base);      // the handle names the whole allocation
+  return HB_OK;
+}
+
+int hb_ep_import(hb_ctx* ctx, const void* handle64, size_t offset, void** ptr, void** base_out) {
+  if (!ctx) return HB_ERR_INVALID;
+  HB_REQUIRE(ctx, handle64 && ptr && base_out, HB_ERR_INVALID, "ep_import: NULL argument");
+  int cur = -1;
+  HB_CUDA(ctx, cudaGetDevice(&cur));
+  HB_REQUIRE(ctx, cur == ctx->device, HB_ERR_INVALID, "ep_import: the context's device %d must be current (current: %d)", ctx->device, cur);
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* base = nullptr;
+  HB_CUDA(ctx, cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+  *base_out = base;
+  *ptr = static_cast<uint8_t*>(base) + offset;
+  return HB_OK;
+}
+
+int hb_ep_close(hb_ctx* ctx, void* base) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (base) HB_CUDA(ctx, cudaIpcCloseMemHandle(base));
   return HB_OK;
 }
 

@@ -69,16 +69,16 @@ class ExpertParallelMoE:
         ops, G, B, H, K = self.ops, self.world, self.B, self.H, self.K
         peer, err = None, ""
         try:
-            from torch.multiprocessing.reductions import reduce_tensor
             off, total, rec = ops.PeerExchange.layout(G, B, H, K)
             assert rec == self.rec_bytes
             mine = torch.zeros(total, dtype=torch.uint8, device=self.dev)
             torch.cuda.synchronize(self.dev)
-            fn, args = reduce_tensor(mine)
-            gathered = [None] * G
-            dist.all_gather_object(gathered, args, group=self.group)
-            bufs = [mine if r == self.rank else fn(*gathered[r]) for r in range(G)]
-            peer = ops.PeerExchange(bufs, self.rank, G, B, H, K, ctx=self.ctx)
+
+            def exchange(obj):
+                got = [None] * G
+                dist.all_gather_object(got, obj, group=self.group)
+                return got
+            peer = ops.PeerExchange(mine, exchange, self.rank, G, B, H, K, ctx=self.ctx)
             # the gathered rows are read in place from this rank's own buffer
             view = mine[off["recv"]:off["recv"] + G * B * rec].view(G * B, rec)
             self.recv = view
@@ -133,6 +133,13 @@ class ExpertParallelMoE:
         else:
             ops.moe_combine(self.routed, torch.zeros_like(out), None, 0, out=out, ctx=self.ctx)
         return out
+
+    def close(self):
+        """Drops the mappings of the peers' exchange memory (peer transport).  Every rank calls it, with no exchange in flight."""
+        if self.peer is not None:
+            dist.barrier(group=self.group)
+            self.peer.close()
+            self.peer = None
 
     def local_records_touched(self, ids_all_sets) -> float:
         """Mean number of distinct local expert records (plus the shared copy) one layer call streams, from gathered ids."""

@@ -372,12 +372,13 @@ def dispatch_plan(ids_host: np.ndarray, E: int, H: int, I: int):
 
 
 class PeerExchange:
-    """hb_ep: the expert-parallel exchanges over NVLink peer memory.  `bufs[p]` is a uint8 device tensor holding rank p's exchange
-    memory (this rank's own allocation for p == rank, the peers' mapped into this process), laid out by `layout(...)`."""
+    """hb_ep: the expert-parallel exchanges over NVLink peer memory.  `mine` is this rank's exchange memory (a zero-filled uint8
+    device tensor of `layout(...)` bytes); `exchange(obj)` must return the list of every rank's `obj` (e.g. an all_gather_object):
+    it carries the CUDA IPC handles, which every rank opens with its own device current."""
 
     @staticmethod
     def layout(world: int, B: int, H: int, K: int):
-        """(offsets dict, total bytes) of one rank's exchange memory: gather buffer, gather flags, partial buffer, partial flags."""
+        """(offsets dict, total bytes, record bytes) of one rank's exchange memory: gather buffer, gather flags, partial buffer, partial flags."""
         rec = int(_L().hb_ep_rec_bytes(H, K))
         off, o = {}, 0
         for name, size in (("recv", world * B * rec), ("ag_flag", 256), ("rs", world * B * H * 4), ("rs_flag", 256)):
@@ -385,17 +386,31 @@ class PeerExchange:
             o += (size + 255) // 256 * 256
         return off, o, rec
 
-    def __init__(self, bufs, rank: int, world: int, B: int, H: int, K: int, ctx: Context | None = None):
+    def __init__(self, mine, exchange, rank: int, world: int, B: int, H: int, K: int, ctx: Context | None = None):
         self.ctx = ctx or context()
-        self.bufs = bufs                                               # keeps the mappings alive
+        self.mine = mine                                               # keeps the exported memory alive
+        self._h = None
+        self._bases = []
         off, total, self.rec_bytes = self.layout(world, B, H, K)
-        for p, b in enumerate(bufs):
-            assert b.numel() >= total and b.dtype == torch.uint8
-            if b.device.index != self.ctx.device:
-                self.ctx.check(_L().hb_ep_enable_peer(self.ctx.handle, b.device.index))
-        arr = lambda name: (C.c_void_p * world)(*[b.data_ptr() + off[name] for b in bufs])
-        self._h = C.c_void_p()
-        self.ctx.check(_L().hb_ep_create(self.ctx.handle, rank, world, B, H, K, arr("recv"), arr("ag_flag"), arr("rs"), arr("rs_flag"), C.byref(self._h)))
+        assert mine.numel() >= total and mine.dtype == torch.uint8 and mine.device.index == self.ctx.device
+        handle = (C.c_ubyte * 64)()
+        offset = C.c_size_t(0)
+        self.ctx.check(_L().hb_ep_export(self.ctx.handle, mine.data_ptr(), handle, C.byref(offset)))
+        everyone = exchange((bytes(handle), int(offset.value)))
+        ptrs = []
+        for p in range(world):
+            if p == rank:
+                ptrs.append(mine.data_ptr())
+                continue
+            hb, ob = everyone[p]
+            ptr, base = C.c_void_p(), C.c_void_p()
+            self.ctx.check(_L().hb_ep_import(self.ctx.handle, (C.c_ubyte * 64).from_buffer_copy(hb), ob, C.byref(ptr), C.byref(base)))
+            self._bases.append(base)
+            ptrs.append(ptr.value)
+        arr = lambda name: (C.c_void_p * world)(*[q + off[name] for q in ptrs])
+        h = C.c_void_p()
+        self.ctx.check(_L().hb_ep_create(self.ctx.handle, rank, world, B, H, K, arr("recv"), arr("ag_flag"), arr("rs"), arr("rs_flag"), C.byref(h)))
+        self._h = h
         self.off = off
 
     def push_rows(self, x, ids, w):
@@ -410,11 +425,18 @@ class PeerExchange:
     def combine(self, shared, lg, col: int, out):
         self.ctx.check(_L().hb_ep_combine(self._h, _p(shared), _p(lg), 0 if lg is None else lg.stride(0), col, _p(out), _stream()))
 
+    def close(self):
+        """Unmaps the peers' memory.  Call it on every rank, after a barrier, when no exchange is in flight."""
+        if self._h:
+            _L().hb_ep_destroy(self._h)
+            self._h = None
+        for b in self._bases:
+            _L().hb_ep_close(self.ctx.handle, b)
+        self._bases = []
+
     def __del__(self):
         try:
-            if self._h:
-                _L().hb_ep_destroy(self._h)
-                self._h = None
+            self.close()
         except Exception:
             pass
 

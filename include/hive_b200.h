@@ -180,7 +180,9 @@ HB_API int hb_moe_decode_ep_local(hb_ctx* ctx, const int32_t* ids, const float* 
  * owning rank's partial buffer, each followed by a step-number flag the receiver polls (bounded; a wait that gives up sets the
  * context's error word — hb_check_device reports it — and later waits return at once).
  *   hb_ep_rec_bytes(H, K)            bytes of one exchanged row record [bf16 row | int32 ids | fp32 weights], padded to 16
- *   hb_ep_enable_peer(ctx, dev)      lets the context's device address memory of device `dev`
+ *   hb_ep_export / import / close    share a device buffer between the ranks' processes (CUDA IPC): export gives a 64-byte handle and
+ *                                    the buffer's offset inside its allocation; import (with the context's device current) maps it for
+ *                                    this device's kernels and returns the buffer's address plus the base to close later
  *   hb_ep_create(...)                recv[p], ag_flag[p], rs[p], rs_flag[p] for p < world: addresses, valid on THIS device, of rank p's
  *                                    gather buffer [world·B·rec_bytes], gather flags [world] u32, partial buffer [world·B·H] f32
  *                                    and partial flags [world] u32 (the caller allocates its own, zero-filled, and maps its
@@ -194,7 +196,9 @@ HB_API int hb_moe_decode_ep_local(hb_ctx* ctx, const int32_t* ids, const float* 
  * All ranks must issue the same sequence of steps.  Calls of one hb_ep must not overlap. */
 typedef struct hb_ep hb_ep;
 HB_API size_t hb_ep_rec_bytes(int H, int K);
-HB_API int hb_ep_enable_peer(hb_ctx* ctx, int peer_device);
+HB_API int hb_ep_export(hb_ctx* ctx, const void* ptr, void* handle64, size_t* offset);
+HB_API int hb_ep_import(hb_ctx* ctx, const void* handle64, size_t offset, void** ptr, void** base);
+HB_API int hb_ep_close(hb_ctx* ctx, void* base);
 HB_API int hb_ep_create(hb_ctx* ctx, int rank, int world, int B, int H, int K, void* const* recv, void* const* ag_flag, void* const* rs,
                         void* const* rs_flag, hb_ep** out);
 HB_API void hb_ep_destroy(hb_ep* ep);

@@ -49,6 +49,7 @@ def _worker(rank, world, port, q):
             torch.cuda.synchronize()
             ctx.check_device()
             outs[transport] = (ep.transport, ids.clone(), out.clone())
+            ep.close()
             dist.barrier()
         # single-GPU layer on this rank's rows, all experts resident
         rid = torch.empty((L, B, K), dtype=torch.int32, device=dev); rout = torch.empty((L, B, H), dtype=torch.bfloat16, device=dev)
@@ -65,8 +66,12 @@ def _worker(rank, world, port, q):
         q.put(res)
         dist.barrier()
         torch.cuda.synchronize()
-    finally:
         dist.destroy_process_group()
+    except Exception:  # noqa: BLE001 - report and leave at once: the other rank must not be left waiting in a collective
+        import traceback
+        q.put({"rank": rank, "error": traceback.format_exc()})
+        q.close(); q.join_thread()
+        os._exit(1)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
@@ -79,10 +84,18 @@ def test_expert_parallel_both_transports_match_single_gpu():
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=300) for _ in range(world)]
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    res = []
+    try:
+        for _ in range(world):
+            res.append(q.get(timeout=240))
+            assert "error" not in res[-1], res[-1]["error"]
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:                                                     # never leave a rank behind (exact processes started here)
+            if p.is_alive():
+                p.kill()
     for r in res:
         for t in ("nccl", "peer"):
             used, ok_ids, err = r[t]
