@@ -104,6 +104,8 @@ def load() -> C.CDLL:
         "hb_ep_create": (i, [vp, i, i, i, i, i, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
         "hb_ep_destroy": (None, [vp]),
         "hb_ep_push_rows": (i, [vp, vp, i, vp, vp, vp]),
+        "hb_ep_route_push": (i, [vp, vp, i, i, i, i, vp, i, vp, vp, vp]),
+        "hb_ep_layer_local": (i, [vp, vp, i, i, i, f, vp, vp, vp, vp]),
         "hb_ep_wait_rows": (i, [vp, vp]),
         "hb_ep_push_partials": (i, [vp, vp, vp]),
         "hb_ep_combine": (i, [vp, vp, vp, i, i, vp, vp]),

@@ -33,6 +33,9 @@ constexpr int HB_MAX_EXPERTS = 1024;
 bool hbk_moe_decode_fast(int H, int I);                 // shapes the streaming tensor-core path takes
 size_t hbk_moe_decode_ws_bytes(int n_pairs, int H, int I);
 int hbk_moe_decode_setup(hb_ctx* ctx);                  // one-time kernel attributes (dynamic shared memory)
+// Expert-parallel exchange hooks of a decode pass (k_ep.cu): wait for the gathered rows before grouping, push the routed sums to the
+// owning ranks instead of storing them.
+struct hbk_ep_push { float* rs[8]; uint32_t* flag[8]; int B, rank, world; const uint32_t* step; unsigned int* done; };
 // Source of the pairs: either an explicit list, or router output (+ optionally the shared expert as M extra pairs of weight 1).
 struct hbk_pair_src {
   const hb_moe_pair* pairs = nullptr; int n_pairs = 0;                       // list form
@@ -42,6 +45,7 @@ struct hbk_pair_src {
   int ld_ids = 0;                                                            // row pitch of ids / w in elements (0 = K)
   int x_ld = 0;                                                              // row pitch of x in elements (0 = H; other values: streaming path only)
   int sh_row0 = 0, sh_rows = -1;                                             // rows that get the shared expert's pair (-1 = all M)
+  const uint32_t* wait_flags = nullptr; int wait_n = 0; const uint32_t* wait_step = nullptr;   // grouping first waits until wait_flags[0..n) ≥ *wait_step + 1
   // routed form, optional: route inside the grouping kernel (ids / w are then outputs written before they are grouped)
   int route = 0;                                                             // 0 = ids / w given, 1 = softmax, 2 = sigmoid + bias
   const float* logits = nullptr; int ld = 0, renorm = 0, logits_bf16 = 0;
@@ -55,6 +59,7 @@ struct hbk_reduce {
   void* out_bf16 = nullptr;                   // routed form with combine
   float* out_f32 = nullptr;                   // routed form without combine: overwritten with Σ_k w·expert
   void* shared_out = nullptr;                 // with out_f32 and a shared record: the shared expert's rows bf16 [sh_rows, H], written apart
+  const hbk_ep_push* ep = nullptr;            // routed sums go to the owning ranks' partial buffers (row m belongs to rank m / B) instead of out_f32
 };
 int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int H, int I, float limit, const hbk_reduce& red, void* ws,
                        cudaStream_t st);

@@ -21,8 +21,10 @@
 
 #include <cstring>
 
+#include "ep.cuh"
 #include "hb_common.cuh"
 #include "hb_kernels.h"
+#include "router.cuh"
 
 namespace hb {
 
@@ -33,23 +35,6 @@ struct EpPeers {
   float* rs[kEpMaxRanks];            // peer p's partial buffer [G, B, H]
   uint32_t* rs_flag[kEpMaxRanks];    // peer p's partial flags [G]
 };
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-// flag ≥ step (wrap-safe), polled at most ~2^24 times with back-off (seconds); false = gave up
-__device__ __forceinline__ bool ep_wait_flag(const uint32_t* flag, uint32_t step, uint32_t* err, uint32_t site) {
-  for (uint32_t it = 0; it < (1u << 24); ++it) {
-    if ((int32_t)(ld_acquire_sys(flag) - step) >= 0) return true;
-    if (it > 32) __nanosleep(it < 4096 ? 64 : 256);
-    if ((it & 1023) == 1023 && *reinterpret_cast<volatile uint32_t*>(err)) return false;      // somebody already gave up
-  }
-  atomicOr(err, site);
-  return false;
-}
 
 // grid = G (one CTA per destination rank)
 __global__ void __launch_bounds__(512) ep_push_rows_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const int32_t* __restrict__ ids,
@@ -66,6 +51,41 @@ __global__ void __launch_bounds__(512) ep_push_rows_kernel(const __nv_bfloat16* 
   for (int i = threadIdx.x; i < B * 2 * K; i += blockDim.x) {               // ids then weights, 4 bytes each
     const int r = i / (2 * K), c = i - r * 2 * K;
     const uint32_t v = c < K ? (uint32_t)ids[(size_t)r * K + c] : __float_as_uint(w[(size_t)r * K + c - K]);
+    reinterpret_cast<uint32_t*>(dst + (size_t)r * rec_bytes + (size_t)H * 2)[c] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) st_release_sys(peers.ag_flag[pi] + rank, step);
+}
+
+// Router and push in one launch: every CTA (one per destination rank) routes all B rows itself — the routing is a deterministic
+// function of the logits, so the G copies agree — and sends rows, ids and weights to its rank.  CTA 0 also stores ids / w for
+// the caller.  Dynamic shared memory: (warps·E + 2·B·K) words.
+__global__ void __launch_bounds__(512) ep_route_push_kernel(const float* __restrict__ logits, int ld, int E, int K, int renorm, int logits_bf16,
+                                                            const __nv_bfloat16* __restrict__ x, int ldx, int32_t* __restrict__ ids_out,
+                                                            float* __restrict__ w_out, int B, int H, int rec_bytes, EpPeers peers, int rank,
+                                                            const uint32_t* __restrict__ step_ctr) {
+  extern __shared__ float ep_sm[];
+  griddep_wait();                                                          // the previous step's combine has advanced the step counter
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  int32_t* ids_s = reinterpret_cast<int32_t*>(ep_sm + (size_t)nw * E);
+  float* w_s = reinterpret_cast<float*>(ids_s + B * K);
+  for (int m = warp; m < B; m += nw)
+    route_softmax_row(logits + (size_t)m * ld, E, K, renorm, logits_bf16, ep_sm + (size_t)warp * E, lane, ids_s + m * K, w_s + m * K);
+  __syncthreads();
+  const int pi = blockIdx.x;
+  if (pi == 0)
+    for (int i = threadIdx.x; i < B * K; i += blockDim.x) { ids_out[i] = ids_s[i]; w_out[i] = w_s[i]; }
+  const uint32_t step = *step_ctr + 1u;
+  uint8_t* dst = peers.recv[pi] + (size_t)rank * B * rec_bytes;
+  const int xc = H / 8;
+  for (int i = threadIdx.x; i < B * xc; i += blockDim.x) {
+    const int r = i / xc, c = i - r * xc;
+    reinterpret_cast<uint4*>(dst + (size_t)r * rec_bytes)[c] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)r * ldx) + c);
+  }
+  for (int i = threadIdx.x; i < B * 2 * K; i += blockDim.x) {
+    const int r = i / (2 * K), c = i - r * 2 * K;
+    const uint32_t v = c < K ? (uint32_t)ids_s[r * K + c] : __float_as_uint(w_s[r * K + c - K]);
     reinterpret_cast<uint32_t*>(dst + (size_t)r * rec_bytes + (size_t)H * 2)[c] = v;
   }
   __threadfence_system();
@@ -105,6 +125,7 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const float* __restrict
                                                          __nv_bfloat16* __restrict__ out, uint32_t* __restrict__ step_ctr, unsigned int* __restrict__ done,
                                                          uint32_t* err) {
   __shared__ int ok_s;
+  griddep_wait();
   const uint32_t step = *step_ctr + 1u;
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();
@@ -223,6 +244,39 @@ int hb_ep_push_rows(hb_ep* e, const void* x_bf16, int ldx, const int32_t* ids, c
                    (const uint32_t*)e->step_ctr);
 }
 
+int hb_ep_route_push(hb_ep* e, const float* logits, int ld, int E, int renorm, int logits_bf16, const void* x_bf16, int ldx, int32_t* ids_out,
+                     float* w_out, void* stream) {
+  if (!e) return HB_ERR_INVALID;
+  hb_ctx* ctx = e->ctx;
+  HB_REQUIRE(ctx, logits && x_bf16 && ids_out && w_out && ldx >= e->H && ldx % 8 == 0 && hb_aligned(x_bf16, 16), HB_ERR_INVALID, "ep_route_push: bad arguments");
+  HB_REQUIRE(ctx, E >= 1 && ld >= E && e->K <= 16 && e->K <= E, HB_ERR_INVALID, "ep_route_push: E=%d ld=%d K=%d", E, ld, e->K);
+  const size_t smem = ((size_t)16 * E + 2 * (size_t)e->B * e->K) * 4;
+  HB_REQUIRE(ctx, smem <= 48 * 1024, HB_ERR_UNSUPPORTED, "ep_route_push: E=%d too large for the fused router (route with hb_route_softmax_topk, then hb_ep_push_rows)", E);
+  return hb_launch(ctx, "ep_route_push", true, ep_route_push_kernel, dim3(e->world), dim3(512), smem, reinterpret_cast<cudaStream_t>(stream), logits, ld, E,
+                   e->K, renorm, logits_bf16, reinterpret_cast<const __nv_bfloat16*>(x_bf16), ldx, ids_out, w_out, e->B, e->H, e->rec_bytes, e->peers, e->rank,
+                   (const uint32_t*)e->step_ctr);
+}
+
+int hb_ep_layer_local(hb_ep* e, const uint8_t* const* rec_tab, int li, int E, int I, float limit, const uint8_t* shared_rec, void* shared_out_bf16, void* ws,
+                      void* stream) {
+  if (!e) return HB_ERR_INVALID;
+  hb_ctx* ctx = e->ctx;
+  const int M = e->world * e->B;
+  HB_REQUIRE(ctx, rec_tab && ws && hb_aligned(ws, 256) && E >= 1 && E <= HB_MAX_EXPERTS && li >= 0 && (!shared_rec || shared_out_bf16), HB_ERR_INVALID,
+             "ep_layer_local: bad arguments");
+  HB_REQUIRE(ctx, hbk_moe_decode_fast(e->H, I) && M * (e->K + 1) <= HB_MAX_PAIRS, HB_ERR_UNSUPPORTED, "ep_layer_local: H=%d I=%d, %d pairs", e->H, I, M * (e->K + 1));
+  hbk_pair_src src;
+  src.ids = reinterpret_cast<const int32_t*>(e->recv + (size_t)e->H * 2); src.w = reinterpret_cast<const float*>(e->recv + (size_t)e->H * 2 + (size_t)e->K * 4);
+  src.ld_ids = e->rec_bytes / 4; src.M = M; src.K = e->K; src.tab = rec_tab; src.li = li; src.E = E; src.x_ld = e->rec_bytes / 2;
+  src.shared_rec = shared_rec; src.sh_row0 = e->rank * e->B; src.sh_rows = shared_rec ? e->B : 0;
+  src.wait_flags = e->ag_flag; src.wait_n = e->world; src.wait_step = e->step_ctr;
+  hbk_ep_push push{};
+  for (int p = 0; p < e->world; ++p) { push.rs[p] = e->peers.rs[p]; push.flag[p] = e->peers.rs_flag[p]; }
+  push.B = e->B; push.rank = e->rank; push.world = e->world; push.step = e->step_ctr; push.done = e->done + kEpMaxRanks + 1;
+  hbk_reduce red; red.ep = &push; red.shared_out = shared_rec ? shared_out_bf16 : nullptr;
+  return hbk_moe_decode_run(ctx, src, e->recv, e->H, I, limit, red, ws, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int hb_ep_wait_rows(hb_ep* e, void* stream) {
   if (!e) return HB_ERR_INVALID;
   return hb_launch(e->ctx, "ep_wait_rows", false, ep_wait_kernel, dim3(1), dim3(32), 0, reinterpret_cast<cudaStream_t>(stream), (const uint32_t*)e->ag_flag,
@@ -244,7 +298,7 @@ int hb_ep_combine(hb_ep* e, const void* shared_bf16, const float* lg, int ld, in
   hb_ctx* ctx = e->ctx;
   HB_REQUIRE(ctx, out_bf16 && (!lg || shared_bf16), HB_ERR_INVALID, "ep_combine: no output, or a gate without shared rows");
   const size_t n = (size_t)e->B * e->H;
-  return hb_launch(ctx, "ep_combine", false, ep_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+  return hb_launch(ctx, "ep_combine", true, ep_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
                    (const float*)e->rs, (const uint32_t*)e->rs_flag, e->world, e->B, e->H, reinterpret_cast<const __nv_bfloat16*>(shared_bf16), lg, ld, col,
                    reinterpret_cast<__nv_bfloat16*>(out_bf16), e->step_ctr, e->done + kEpMaxRanks, ctx->dev_err);
 }

@@ -12,6 +12,7 @@
 // HBM traffic per layer is the records touched plus O(pairs·(H+I)) bytes of activations; weights are read once per group.
 // Shapes the streaming path takes: H, I multiples of 256, at most 4096; anything else (H, I multiples of 32) runs on the
 // generic CUDA-core kernels at the end of this file.
+#include "ep.cuh"
 #include "moe_stream.cuh"
 #include "router.cuh"
 
@@ -24,6 +25,7 @@ struct GroupArgs {
   const uint8_t* const* tab; int li, E;
   const uint8_t* shared_rec;
   int ld_ids, sh_row0, sh_rows;                          // pitch of ids / w rows; rows [sh_row0, sh_row0 + sh_rows) get the shared pair
+  const uint32_t* wait_flags; int wait_n; const uint32_t* wait_step; uint32_t* wait_err;   // expert parallel: the gathered rows' flags
   DecodeWs ws;
   // optional routing stage (routed form): logits → ids / w by one warp per row before the grouping
   int route; const float* logits; int ld, renorm, logits_bf16; const float* bias; float sig_scale;
@@ -63,6 +65,11 @@ __device__ void block_scan2(int* a, int* b, int n, int* tot_a, int* tot_b, int* 
 __global__ void __launch_bounds__(kGroupThreads) moe_group_kernel(GroupArgs a) {
   extern __shared__ __align__(16) uint8_t gsm[];
   griddep_wait();
+  if (a.wait_flags) {                                   // the rows, ids and weights this pass reads are pushed by the other ranks
+    if ((int)threadIdx.x < a.wait_n && !*reinterpret_cast<volatile uint32_t*>(a.wait_err))
+      ep_wait_flag(a.wait_flags + threadIdx.x, *a.wait_step + 1u, a.wait_err, 0x40000u);
+    __syncthreads();
+  }
   const bool routed = a.ids != nullptr;
   const int P = routed ? a.M * a.K + (a.shared_rec ? a.M : 0) : a.n_pairs;
   const int NK = routed ? a.E + 1 : P;                  // key space: expert id (E = the shared expert) or leader pair index
@@ -331,8 +338,18 @@ __global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK
 __global__ void moe_reduce_routed_kernel(ReduceArgs r) {
   griddep_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;      // one thread per (row, 2 columns)
-  if (i >= (size_t)r.M * r.H / 2) return;
-  reduce_routed_unit(r, i);
+  if (i < (size_t)r.M * r.H / 2) reduce_routed_unit(r, i);
+  if (r.ep.world > 0) {
+    // expert parallel: the sums were stored into the owning ranks' memory; when the last block is through, tell every rank
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(r.ep.done, 1u) == gridDim.x - 1) {
+      *r.ep.done = 0;
+      __threadfence_system();
+      const uint32_t step = *r.ep.step + 1u;
+      for (int p = 0; p < r.ep.world; ++p) st_release_sys(r.ep.flag[p] + r.ep.rank, step);
+    }
+  }
 }
 
 // List form: out[row] += w·part, pairs visited in list order.  One block column per pair that is the first of its row.
@@ -503,6 +520,7 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
   ga.pairs = src.pairs; ga.n_pairs = src.n_pairs; ga.ids = src.ids; ga.w = src.w; ga.M = src.M; ga.K = src.K;
   ga.tab = src.tab; ga.li = src.li; ga.E = src.E; ga.shared_rec = src.shared_rec; ga.ws = w;
   ga.ld_ids = src.ld_ids ? src.ld_ids : src.K; ga.sh_row0 = src.sh_row0; ga.sh_rows = src.sh_rows < 0 ? src.M : src.sh_rows;
+  ga.wait_flags = src.wait_flags; ga.wait_n = src.wait_n; ga.wait_step = src.wait_step; ga.wait_err = ctx->dev_err;
   const int x_ld = src.x_ld ? src.x_ld : H;
   if (src.route && ga.ld_ids != src.K) return hb_fail(ctx, HB_ERR_INVALID, "moe_decode: in-kernel routing writes dense ids / w rows");
   int route = src.route;
@@ -531,11 +549,12 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
   sd.off_wa = (uint32_t)L.w2; sd.off_sa = (uint32_t)L.s2;
 
   if (x_ld != H && !hbk_moe_decode_fast(H, I)) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "moe_decode: strided activation rows need a shape of the streaming path");
-  if (hbk_moe_fused_available(H, I) && (ctx->flags & HB_FLAG_FUSED) && x_ld == H) {
+  if (hbk_moe_fused_available(H, I) && (ctx->flags & HB_FLAG_FUSED) && x_ld == H && !red.ep) {
     // one persistent kernel: gate/up → down → (routed form) reduce + combine
     if (routed) {
       ReduceArgs ra{w.part, w.pos_of, w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
-                    reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), ga.sh_row0, ga.sh_rows};
+                    reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), ga.sh_row0, ga.sh_rows,
+                  red.ep ? *red.ep : hbk_ep_push{}};
       return hbk_moe_fused_launch(ctx, w, x, H, I, limit, L, &ra, st);
     }
     if ((r = hbk_moe_fused_launch(ctx, w, x, H, I, limit, L, nullptr, st))) return r;
@@ -564,7 +583,8 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
 
   if (routed) {
     ReduceArgs ra{w.part, w.pos_of, w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
-                  reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), ga.sh_row0, ga.sh_rows};
+                  reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), ga.sh_row0, ga.sh_rows,
+                  red.ep ? *red.ep : hbk_ep_push{}};
     return hb_launch(ctx, "moe_reduce_routed", true, moe_reduce_routed_kernel, dim3((unsigned)(((size_t)src.M * H / 2 + 255) / 256)), dim3(256), 0, st, ra);
   }
   return hb_launch(ctx, "moe_reduce_list", true, moe_reduce_list_kernel, dim3((H / 2 + 255) / 256, P), dim3(256), 0, st, (const __nv_bfloat16*)w.part,

@@ -193,6 +193,7 @@ struct ReduceArgs {
   const __nv_bfloat16* shared; const float* lg; int ld, col;
   __nv_bfloat16* out_bf16; float* out_f32;
   __nv_bfloat16* shared_out = nullptr; int sh_row0 = 0, sh_rows = 0;   // fp32 form: the shared expert's output rows, written apart
+  hbk_ep_push ep = {};                            // ep.world > 0: the routed sums go to the owning ranks' partial buffers
 };
 __device__ __forceinline__ void reduce_routed_unit(const ReduceArgs& r, size_t i) {
   const int m = (int)(i / (r.H / 2)), d = (int)(i % (r.H / 2)) * 2;
@@ -214,7 +215,10 @@ __device__ __forceinline__ void reduce_routed_unit(const ReduceArgs& r, size_t i
       a1 = __fadd_rn(a1, __fmul_rn(wv[k], __uint_as_float(raw[k] & 0xffff0000u)));
     }
   }
-  if (r.out_f32) { r.out_f32[(size_t)m * r.H + d] = a0; r.out_f32[(size_t)m * r.H + d + 1] = a1; }
+  if (r.ep.world > 0) {                            // row m belongs to rank m / B: slot `rank` of that rank's partial buffer
+    const int pr = m / r.ep.B;
+    *reinterpret_cast<float2*>(r.ep.rs[pr] + ((size_t)r.ep.rank * r.ep.B + (m - pr * r.ep.B)) * r.H + d) = make_float2(a0, a1);
+  } else if (r.out_f32) { r.out_f32[(size_t)m * r.H + d] = a0; r.out_f32[(size_t)m * r.H + d + 1] = a1; }
   if (r.shared_out && m >= r.sh_row0 && m < r.sh_row0 + r.sh_rows) {
     const int pos = r.pos_of[r.M * r.K + m];
     *reinterpret_cast<unsigned int*>(r.shared_out + (size_t)(m - r.sh_row0) * r.H + d) =

@@ -106,15 +106,13 @@ class ExpertParallelMoE:
         """logits fp32 [B, ≥E(+1)], x bf16 [B, H] local rows; tab: device table [L·E] of local record pointers (0 = elsewhere);
         shared_ptr: this layer's shared-expert record (0 = none).  Writes ids_out / w_out [B, K] and out bf16 [B, H]."""
         ops, B, H, K = self.ops, self.B, self.H, self.K
-        ops.router_softmax_topk(logits, K, self.renorm, self.logits_bf16, E=self.E, ids=ids_out, w=w_out, ctx=self.ctx)
         if self.peer is not None:
-            self.peer.push_rows(x, ids_out, w_out)
-            self.peer.wait_rows()
-            ops.moe_decode_ep_local(self.ids_all, self.w_all, tab, li, self.E, self.x_all, H, self.I, self.part, shared_ptr=shared_ptr,
-                                    sh_row0=self.rank * B, sh_rows=B, shared_out=self.shared, limit=self.limit, ws=self.ws, ctx=self.ctx)
-            self.peer.push_partials(self.part)
+            # three calls, six kernels: [route + push rows] → [wait + group] → gate/up → down → [reduce + push sums] → [wait + combine]
+            self.peer.route_push(logits, x, ids_out, w_out, self.E, self.renorm, self.logits_bf16)
+            self.peer.layer_local(tab, li, self.E, self.I, shared_ptr, self.shared, self.ws, self.limit)
             self.peer.combine(self.shared if shared_ptr else None, logits if (shared_ptr and gate_col >= 0) else None, max(gate_col, 0), out)
             return out
+        ops.router_softmax_topk(logits, K, self.renorm, self.logits_bf16, E=self.E, ids=ids_out, w=w_out, ctx=self.ctx)
         # pack [row | ids | w] per row (one kernel), one all-gather
         torch.cat([x.view(torch.uint8).view(B, H * 2), ids_out.view(torch.uint8).view(B, K * 4), w_out.view(torch.uint8).view(B, K * 4)], dim=1,
                   out=self.send[:, :H * 2 + K * 8])

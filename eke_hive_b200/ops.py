@@ -413,6 +413,13 @@ class PeerExchange:
         self._h = h
         self.off = off
 
+    def route_push(self, logits, x, ids_out, w_out, E: int, renorm: bool = True, logits_bf16: bool = True):
+        self.ctx.check(_L().hb_ep_route_push(self._h, _p(logits), logits.stride(0), E, int(renorm), int(logits_bf16), _p(x), x.stride(0), _p(ids_out),
+                                             _p(w_out), _stream()))
+
+    def layer_local(self, rec_tab, li: int, E: int, I: int, shared_ptr: int, shared_out, ws, limit: float = 0.0):
+        self.ctx.check(_L().hb_ep_layer_local(self._h, _p(rec_tab), li, E, I, limit, shared_ptr or None, _p(shared_out), _p(ws), _stream()))
+
     def push_rows(self, x, ids, w):
         self.ctx.check(_L().hb_ep_push_rows(self._h, _p(x), x.stride(0), _p(ids), _p(w), _stream()))
 

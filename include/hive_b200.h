@@ -193,6 +193,10 @@ HB_API int hb_moe_decode_ep_local(hb_ctx* ctx, const int32_t* ids, const float* 
  *   hb_ep_push_partials              part fp32 [world·B, H] (hb_moe_decode_ep_local's routed_out): rows of rank p → rank p
  *   hb_ep_combine                    waits for every rank's partials of the own rows, adds them in rank order, applies the
  *                                    shared-expert combine (hb_moe_combine's arithmetic) → out bf16 [B,H]; ends the step
+ *   hb_ep_route_push                 softmax router (hb_route_softmax_topk's arithmetic; ids / w also returned) + hb_ep_push_rows in one launch
+ *   hb_ep_layer_local                hb_ep_wait_rows + hb_moe_decode_ep_local on the gathered rows + hb_ep_push_partials as ONE chain of four
+ *                                    kernels: the grouping kernel does the wait, the reduce kernel stores straight into the owners' buffers
+ * A layer is then three calls: hb_ep_route_push, hb_ep_layer_local, hb_ep_combine.
  * All ranks must issue the same sequence of steps.  Calls of one hb_ep must not overlap. */
 typedef struct hb_ep hb_ep;
 HB_API size_t hb_ep_rec_bytes(int H, int K);
@@ -203,6 +207,10 @@ HB_API int hb_ep_create(hb_ctx* ctx, int rank, int world, int B, int H, int K, v
                         void* const* rs_flag, hb_ep** out);
 HB_API void hb_ep_destroy(hb_ep* ep);
 HB_API int hb_ep_push_rows(hb_ep* ep, const void* x_bf16, int ldx, const int32_t* ids, const float* w, void* stream);
+HB_API int hb_ep_route_push(hb_ep* ep, const float* logits, int ld, int E, int renorm, int logits_bf16, const void* x_bf16, int ldx,
+                            int32_t* ids_out, float* w_out, void* stream);
+HB_API int hb_ep_layer_local(hb_ep* ep, const uint8_t* const* rec_tab, int li, int E, int I, float limit, const uint8_t* shared_rec,
+                             void* shared_out_bf16, void* ws, void* stream);
 HB_API int hb_ep_wait_rows(hb_ep* ep, void* stream);
 HB_API int hb_ep_push_partials(hb_ep* ep, const float* part, void* stream);
 HB_API int hb_ep_combine(hb_ep* ep, const void* shared_bf16, const float* lg, int ld, int col, void* out_bf16, void* stream);
