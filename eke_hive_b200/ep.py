@@ -8,7 +8,7 @@ The reference engine has no multi-GPU code; this is the sharded form of its MoE 
     expert on the local rows → reduce-scatter of the fp32 routed sums → combine on the local rows.
 
 Two transports.  "nccl": all-gather and reduce-scatter of torch.distributed; remote data lands in local memory through the
-collective before a kernel reads it.  "peer" (HIVE_B200_EP=peer or transport="peer"): the library's own kernels write the rows and the
+collective before a kernel reads it.  "peer" (default on GPUs; HIVE_B200_EP=nccl selects the other): the library's own kernels write the rows and the
 partial sums straight into the other GPUs' exchange buffers over NVLink (plain peer stores, buffers mapped through CUDA IPC) and
 announce them with step-number flags — no collective launch on the layer's critical path, and the cross-rank sum is added in
 rank order by the combine kernel.  Reads of exchanged data are always local.
@@ -57,7 +57,7 @@ class ExpertParallelMoE:
         self.routed = torch.empty((B, H), dtype=torch.float32, device=device)
         self.shared = torch.zeros((B, H), dtype=torch.bfloat16, device=device)
         self.reduce_scatter = dist.get_backend(group) != "gloo"            # gloo has no reduce-scatter: all-reduce and slice there
-        want_peer = (transport or os.environ.get("HIVE_B200_EP", "nccl")) == "peer" and self.reduce_scatter and hasattr(ops, "PeerExchange")
+        want_peer = (transport or os.environ.get("HIVE_B200_EP", "peer")) == "peer" and self.reduce_scatter and hasattr(ops, "PeerExchange")
         self.peer = self._setup_peer() if want_peer else None
         self.transport = "peer" if self.peer is not None else "nccl"
         ws_bytes = getattr(ops, "moe_decode_ws_bytes", lambda n, h, i: 256)(world * B * (K + 1), H, I)
