@@ -438,58 +438,88 @@ def _timed(torch, fn, n):
 
 
 def run_prefill(args):
-    """BASELINE config 4 (DeepSeek-shaped prefill) on one GPU: one MoE layer, H 7168, I 2048, 256 routed experts (6.3 GB resident),
-    top-8, T tokens, NVFP4 weights and NVFP4 activations; plus a dense W4A4 GEMM and the measured FP4 tensor-pipe ceiling."""
+    """BASELINE config 4 (DeepSeek-shaped prefill): one MoE layer, H 7168, I 2048, 256 routed experts (6.3 GB), top-8, T tokens, NVFP4
+    weights and NVFP4 activations; plus a dense W4A4 GEMM and the measured FP4 tensor-pipe ceiling.  Under torchrun (N > 1) the
+    experts are sharded over the ranks and every rank brings T / N tokens (strong scaling on the same total problem)."""
     import torch
+    import torch.distributed as dist
     import eke_hive_b200 as E
-    dev = torch.device("cuda", 0)
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     ctx = E.context()
     H, I, Ex, K, T = 7168, 2048, args.experts, 8, args.tokens
+    assert Ex % world == 0 and T % world == 0
     peak = E.fp4_peak_probe(8192)
     rb = E.ExpertRecLayout.make(H, I)
-    blob = torch.randint(0, 256, (Ex, rb.total), dtype=torch.uint8, device=dev)          # e2m1 codes: any bytes
+    e_lo, e_hi = rank * Ex // world, (rank + 1) * Ex // world
+    n_loc = e_hi - e_lo
+    blob = torch.randint(0, 256, (n_loc, rb.total), dtype=torch.uint8, device=dev)       # e2m1 codes: any bytes
     for off, n in ((rb.s1, I * H // 16), (rb.s3, I * H // 16), (rb.s2, H * I // 16)):    # e4m3 scales 2^-2 .. 2: finite, positive
-        blob[:, off:off + n] = torch.randint(0x28, 0x48, (Ex, n), dtype=torch.uint8, device=dev)
+        blob[:, off:off + n] = torch.randint(0x28, 0x48, (n_loc, n), dtype=torch.uint8, device=dev)
     blob[:, rb.g:rb.g + 12] = torch.from_numpy(np.array([0.003, 0.003, 0.004], np.float32).view(np.uint8)).to(dev)
-    tab = torch.tensor([blob[e].data_ptr() for e in range(Ex)], dtype=torch.int64, device=dev)
-    g = torch.Generator(device=dev); g.manual_seed(4)
+    tab = torch.tensor([blob[e - e_lo].data_ptr() if e_lo <= e < e_hi else 0 for e in range(Ex)], dtype=torch.int64, device=dev)
+    g = torch.Generator(device=dev); g.manual_seed(4 + rank)
+    Tl = T // world
     sets = []
     for _ in range(2):
-        logits = torch.randn((T, Ex), device=dev, generator=g)
+        logits = torch.randn((Tl, Ex), device=dev, generator=g)
         w, ids = torch.topk(torch.softmax(logits, -1), K)
-        sets.append((ids.to(torch.int32).contiguous(), w.contiguous(), torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)))
-    ws = torch.empty(E.moe_prefill_ws_bytes(T, K, Ex, H, I), dtype=torch.uint8, device=dev)
-    out = torch.empty((T, H), dtype=torch.float32, device=dev)
+        sets.append((ids.to(torch.int32).contiguous(), w.contiguous(), torch.randn((Tl, H), device=dev, generator=g).to(torch.bfloat16)))
     it = [0]
+    if world == 1:
+        ws = torch.empty(E.moe_prefill_ws_bytes(T, K, Ex, H, I), dtype=torch.uint8, device=dev)
+        out = torch.empty((T, H), dtype=torch.float32, device=dev)
 
-    def layer():
-        ids, w, x = sets[it[0] % 2]; it[0] += 1
-        E.fn_moe_prefill(tab, 0, Ex, ids, w, x, H, I, out=out, ws=ws, S=T, ctx=ctx)
+        def layer():
+            ids, w, x = sets[it[0] % 2]; it[0] += 1
+            E.fn_moe_prefill(tab, 0, Ex, ids, w, x, H, I, out=out, ws=ws, S=T, ctx=ctx)
+    else:
+        from eke_hive_b200.ep import ExpertParallelPrefill
+        epp = ExpertParallelPrefill(E, ctx, H, I, Ex, K, Tl, world, rank, dev)
+
+        def layer():
+            ids, w, x = sets[it[0] % 2]; it[0] += 1
+            epp.layer(ids, w, x, tab, 0)
     for _ in range(max(args.warmup, 3)):
         layer()
+    if world > 1:
+        dist.barrier()
     ms = _timed(torch, layer, args.steps)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
     ctx.profile(True); layer(); layer(); prof = ctx.profile_read(); ctx.profile(False)
     ctx.check_device()
     prof = {k: {"launches": v[0], "mean_us": v[1] * 1e3 / max(v[0], 1)} for k, v in prof.items()}
     flops = 2.0 * T * K * 3 * H * I
     gemm_us = prof["pf_gemm_gu"]["mean_us"] + prof["pf_gemm_down"]["mean_us"]
-    M, N, Kd = 16384, 8192, 8192
-    xq, xs, xg = E.a4_quant(torch.randn((M, Kd), device=dev, generator=g).to(torch.bfloat16))
-    W = E.GMat(E.FMT_NVFP4, N, Kd, torch.randint(0, 256, (N, Kd // 2), dtype=torch.uint8, device=dev),
-               torch.randint(0x28, 0x48, (N, Kd // 16), dtype=torch.uint8, device=dev), None, 0.01)
-    y = torch.empty((M, N), dtype=torch.float32, device=dev)
-    dms = _timed(torch, lambda: E.nvfp4_gemm_a4(W, xq, xs, xg, y=y, ctx=ctx), args.steps)
-    line = {"metric": "moe_prefill_layer_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "ms_per_layer": ms,
-            "dtype": "e2m1 x e2m1 with ue4m3 block scales, f32 accumulate", "data": "synthetic",
+    line = {"metric": "moe_prefill_layer_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "ms_per_layer": ms,
+            "dtype": "e2m1 x e2m1 with ue4m3 block scales, f32 accumulate", "data": "synthetic", "scaling": "strong",
             "config": {"workload": f"deepseek-shaped MoE prefill layer: hidden 7168, {Ex} routed experts top-8, intermediate 2048, T={T}, NVFP4 W4A4",
-                       "l2": f"{Ex * rb.total / 1e9:.1f} GB of expert records per layer (larger than L2)"},
+                       "l2": f"{Ex * rb.total / 1e9:.1f} GB of expert records per layer (larger than L2)",
+                       "parallelism": "single GPU" if world == 1 else f"expert-parallel ep{world}: all-gather of rows and routing, local experts over all rows, reduce-scatter of fp32 sums (NCCL)"},
             "layer_TFLOPs": flops / (ms * 1e-3) / 1e12,
-            "roofline": {"bound": "tensor", "kernel": "pf_gemm_kernel (gate/up + down)", "achieved": flops / (gemm_us * 1e-6) / 1e12, "peak": peak, "unit": "TFLOP/s",
-                         "frac": flops / (gemm_us * 1e-6) / 1e12 / peak, "peak_source": "hb_fp4_peak_probe on this GPU (dense FP4, resident operands)", "traffic": None},
-            "dense_gemm_a4": {"M": M, "N": N, "K": Kd, "ms": dms, "TFLOPs": 2.0 * M * N * Kd / (dms * 1e-3) / 1e12,
-                              "frac_of_measured_fp4_peak": 2.0 * M * N * Kd / (dms * 1e-3) / 1e12 / peak},
+            "roofline": {"bound": "tensor", "kernel": "pf_gemm_kernel (gate/up + down), this rank's share", "achieved": flops / world / (gemm_us * 1e-6) / 1e12, "peak": peak,
+                         "unit": "TFLOP/s", "frac": flops / world / (gemm_us * 1e-6) / 1e12 / peak,
+                         "peak_source": "hb_fp4_peak_probe on this GPU (dense FP4, resident operands)", "traffic": None},
             "kernels": prof}
-    print(json.dumps(line), flush=True)
+    if world == 1:
+        M, N, Kd = 16384, 8192, 8192
+        xq, xs, xg = E.a4_quant(torch.randn((M, Kd), device=dev, generator=g).to(torch.bfloat16))
+        W = E.GMat(E.FMT_NVFP4, N, Kd, torch.randint(0, 256, (N, Kd // 2), dtype=torch.uint8, device=dev),
+                   torch.randint(0x28, 0x48, (N, Kd // 16), dtype=torch.uint8, device=dev), None, 0.01)
+        y = torch.empty((M, N), dtype=torch.float32, device=dev)
+        dms = _timed(torch, lambda: E.nvfp4_gemm_a4(W, xq, xs, xg, y=y, ctx=ctx), args.steps)
+        line["dense_gemm_a4"] = {"M": M, "N": N, "K": Kd, "ms": dms, "TFLOPs": 2.0 * M * N * Kd / (dms * 1e-3) / 1e12,
+                                 "frac_of_measured_fp4_peak": 2.0 * M * N * Kd / (dms * 1e-3) / 1e12 / peak}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+        dist.destroy_process_group()
 
 
 def run_dense(args):

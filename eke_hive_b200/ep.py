@@ -147,3 +147,49 @@ class ExpertParallelMoE:
             v = ids[(ids >= lo) & (ids < hi)]
             n.append(int(torch.unique(v).numel()) + 1)
         return float(sum(n)) / max(len(n), 1)
+
+
+class ExpertParallelPrefill:
+    """Expert-parallel prefill of one MoE layer: every rank holds T_local rows and the experts [r·E/G, (r+1)·E/G).
+
+        all-gather of rows, ids and weights → the grouped-GEMM operator (fn_moe_prefill) over ALL G·T_local rows with the local
+        experts only (NULL table entries: pairs of experts held elsewhere contribute nothing) → reduce-scatter of the fp32
+        routed sums → combine on the local rows.
+
+    Each rank therefore runs 1/G of the pairs; the exchange moves whole rows (bf16 in, fp32 sums out) rather than the exact
+    (row, expert) pairs of an all-to-all dispatch, which keeps the operator pass and its tile list unchanged.  The routed sum
+    of a row is a sum over ranks of per-rank sums in k order: fp32 reassociation only, routing unaffected."""
+
+    def __init__(self, ops, ctx, H: int, I: int, E: int, K: int, T_local: int, world: int, rank: int, device, group=None, limit: float = 0.0):
+        self.ops, self.ctx, self.H, self.I, self.E, self.K, self.T = ops, ctx, H, I, E, K, T_local
+        self.world, self.rank, self.group, self.limit = world, rank, group, limit
+        G = world
+        self.x_all = torch.empty((G * T_local, H), dtype=torch.bfloat16, device=device)
+        self.ids_all = torch.empty((G * T_local, K), dtype=torch.int32, device=device)
+        self.w_all = torch.empty((G * T_local, K), dtype=torch.float32, device=device)
+        self.part = torch.empty((G * T_local, H), dtype=torch.float32, device=device)
+        self.routed = torch.empty((T_local, H), dtype=torch.float32, device=device)
+        self.reduce_scatter = dist.get_backend(group) != "gloo"
+        ws_bytes = getattr(ops, "moe_prefill_ws_bytes", lambda s, k, e, h, i: 256)(G * T_local, K, E, H, I)
+        self.ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
+
+    def layer(self, ids, w, x, tab, li: int, shared=None, lg=None, col: int = 0, out=None):
+        """ids int32 / w fp32 [T_local, K], x bf16 [T_local, H]: this rank's rows; tab: device table [L·E] of local record pointers.
+        Returns fp32 routed sums [T_local, H], or with `shared` (bf16 [T_local, H]) the combined bf16 rows written to `out`."""
+        ops, G, T = self.ops, self.world, self.T
+        dist.all_gather_into_tensor(self.x_all, x.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(self.ids_all, ids.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(self.w_all, w.contiguous(), group=self.group)
+        ops.fn_moe_prefill(tab, li, self.E, self.ids_all, self.w_all, self.x_all, self.H, self.I, out=self.part, ws=self.ws, S=G * T, limit=self.limit,
+                           ctx=self.ctx)
+        if self.reduce_scatter:
+            dist.reduce_scatter_tensor(self.routed, self.part, op=dist.ReduceOp.SUM, group=self.group)
+        else:
+            dist.all_reduce(self.part, op=dist.ReduceOp.SUM, group=self.group)
+            self.routed.copy_(self.part[self.rank * T:(self.rank + 1) * T])
+        if shared is None:
+            return self.routed
+        out = torch.empty((T, self.H), dtype=torch.bfloat16, device=x.device) if out is None else out
+        ops.moe_combine(self.routed, shared, lg, col, out=out, ctx=self.ctx)
+        return out
+

@@ -40,6 +40,18 @@ class OracleOps:
             shared_out.copy_(torch.from_numpy(sh).to(torch.bfloat16))
         return routed_out
 
+    def fn_moe_prefill(self, tab, li, E, ids, w, x, H_, I_, out=None, ws=None, S=None, limit=0.0, ctx=None):
+        recs = [self.reg.get(int(p)) for p in tab[li * E:(li + 1) * E]]
+        xs, idn, wn = x.float().numpy(), ids.numpy(), w.numpy()
+        acc = np.zeros((xs.shape[0], H_), np.float32)
+        for m in range(xs.shape[0]):
+            for k in range(idn.shape[1]):
+                e = int(idn[m, k])
+                if 0 <= e < E and recs[e] is not None:
+                    acc[m] += self.O.expert_forward_a4(recs[e], H_, I_, xs[m], limit) * np.float32(wn[m, k])
+        out.copy_(torch.from_numpy(acc))
+        return out
+
     def moe_combine(self, routed, shared, lg, col, out=None, ctx=None):
         bits = self.O.moe_combine(routed.numpy(), shared.float().numpy(), None if lg is None else lg.numpy(), col, True)
         out.copy_(torch.from_numpy(self.O.bf16_to_f32(bits)).to(torch.bfloat16))
@@ -78,7 +90,13 @@ def _worker(rank, world, port, q):
         ok_ids = bool(np.array_equal(ids.numpy(), rids)) and ids.numpy().tobytes() == rids.tobytes()
         err = float(np.max(np.abs(got - ref)) / (np.sqrt(np.mean(ref ** 2)) + 1e-30))
         touched = layer.local_records_touched([layer.ids_all])
-        q.put((rank, ok_ids, err, touched))
+        # prefill form: the same rows through the grouped-GEMM operator's stand-in (NVFP4 activations), sharded vs unsharded
+        pf = ep_mod.ExpertParallelPrefill(OracleOps(O, registry), None, H, I, E, K, B, world, rank, torch.device("cpu"))
+        got_pf = pf.layer(ids, w, x, tab, 0).numpy().copy()
+        full = torch.tensor([1000 + e for e in range(E)], dtype=torch.int64)
+        ref_pf = OracleOps(O, registry).fn_moe_prefill(full, 0, E, ids, w, x, H, I, out=torch.empty((B, H), dtype=torch.float32)).numpy()
+        err_pf = float(np.max(np.abs(got_pf - ref_pf)) / (np.sqrt(np.mean(ref_pf ** 2)) + 1e-30))
+        q.put((rank, ok_ids, err, touched, err_pf))
     finally:
         dist.destroy_process_group()
 
@@ -95,7 +113,8 @@ def test_expert_parallel_two_ranks_match_unsharded_oracle():
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    for rank, ok_ids, err, touched in res:
+    for rank, ok_ids, err, touched, err_pf in res:
+        assert err_pf <= 1e-5, f"rank {rank}: sharded prefill differs from unsharded by {err_pf} x RMS"      # fp32 reassociation of the cross-rank sum
         assert ok_ids, f"rank {rank}: routing differs"
         assert err <= 8e-3, f"rank {rank}: error {err} x RMS"            # bf16 output ulp after fp32 reassociation
         assert 1 <= touched <= E // world + 1
