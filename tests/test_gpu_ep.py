@@ -63,6 +63,20 @@ def _worker(rank, world, port, q):
         for t, (used, ids, out) in outs.items():
             res[t] = (used, bool(torch.equal(ids, rid)), float(((out.float() - ref).abs() / rms).max()))
         res["same"] = bool(torch.equal(outs["nccl"][2].view(torch.int16), outs["peer"][2].view(torch.int16)))
+        # prefill form: T rows per rank through the grouped GEMM, sharded against unsharded (all experts resident)
+        from eke_hive_b200.ep import ExpertParallelPrefill
+        T = 96
+        g = torch.Generator(device=dev); g.manual_seed(100 + rank)
+        xp = torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)
+        wp, ip = torch.topk(torch.softmax(torch.randn((T, E_), device=dev, generator=g), -1), K)
+        ip = ip.to(torch.int32).contiguous(); wp = wp.contiguous()
+        pf = ExpertParallelPrefill(E, ctx, H, I, E_, K, T, world, rank, dev)
+        got = pf.layer(ip, wp, xp, local, 1).clone()
+        refp = E.fn_moe_prefill(full, 1, E_, ip, wp, xp, H, I)
+        torch.cuda.synchronize()
+        ctx.check_device()
+        prms = refp.pow(2).mean(dim=-1, keepdim=True).sqrt() + 1e-30
+        res["prefill"] = float(((got - refp).abs() / prms).max())
         q.put(res)
         dist.barrier()
         torch.cuda.synchronize()
@@ -103,3 +117,4 @@ def test_expert_parallel_both_transports_match_single_gpu():
             assert ok_ids, f"rank {r['rank']} {t}: routing differs"
             assert err <= 8e-3, f"rank {r['rank']} {t}: error {err} x RMS"       # one bf16 ulp of the output after fp32 reassociation
         assert r["same"], f"rank {r['rank']}: the two transports differ at two ranks"
+        assert r["prefill"] <= 1e-5, f"rank {r['rank']}: sharded prefill differs by {r['prefill']} x RMS"     # fp32 reassociation only
