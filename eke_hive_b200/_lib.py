@@ -120,6 +120,7 @@ def load() -> C.CDLL:
         "hb_nvfp4_gemm_a4": (i, [vp, C.POINTER(QMat), vp, vp, vp, i, vp, i, vp]),
         "hb_fp4_peak_probe": (i, [vp, i, C.POINTER(f)]),
         "hb_dispatch_plan": (i, [vp, i, i, i, i, i, vp, C.POINTER(Plan)]),
+        "hb_expert_dequant": (i, [vp, vp, i, i, vp, vp, vp]),
         "hb_gather_rows": (i, [vp, vp, vp, i, i, vp, vp]),
         "hb_swiglu_rows": (i, [vp, vp, i, i, f, vp, vp]),
         "hb_scatter_add_rows": (i, [vp, vp, vp, vp, i, i, vp, vp]),

@@ -280,6 +280,19 @@ int hb_moe_layer_decode(hb_ctx* ctx, const float* logits, int ld, int M, int E, 
   return hbk_moe_decode_run(ctx, src, x, H, I, limit, red, ws, as_stream(stream));
 }
 
+int hb_expert_dequant(hb_ctx* ctx, const uint8_t* rec, int H, int I, void* gu_bf16, void* d_bf16, void* stream) {
+  HB_CTX(ctx);
+  HB_PTR(ctx, rec); HB_PTR(ctx, gu_bf16); HB_PTR(ctx, d_bf16);
+  hb_rec_layout L;
+  HB_REQUIRE(ctx, hb_rec_layout_make(H, I, &L) == HB_OK && hb_aligned(rec, 16) && hb_aligned(gu_bf16, 16) && hb_aligned(d_bf16, 16), HB_ERR_INVALID,
+             "expert_dequant: H=%d I=%d, or misaligned pointers", H, I);
+  const float* g = reinterpret_cast<const float*>(rec + L.g);
+  __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(gu_bf16);
+  int r = hbk_nvfp4_dequant(ctx, rec + L.w1, rec + L.s1, 0.f, I, H, gu, as_stream(stream), g);
+  if (!r) r = hbk_nvfp4_dequant(ctx, rec + L.w3, rec + L.s3, 0.f, I, H, gu + (size_t)I * H, as_stream(stream), g + 1);
+  if (!r) r = hbk_nvfp4_dequant(ctx, rec + L.w2, rec + L.s2, 0.f, H, I, d_bf16, as_stream(stream), g + 2);
+  return r;
+}
 int hb_gather_rows(hb_ctx* ctx, const void* x, const int32_t* rows, int R, int H, void* out, void* stream) {
   HB_CTX(ctx);
   if (R == 0) return HB_OK;

@@ -8,7 +8,7 @@
 
 #include "../../include/hive_b200.h"
 
-int hbk_nvfp4_dequant(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int N, int K, void* out, cudaStream_t st);
+int hbk_nvfp4_dequant(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int N, int K, void* out, cudaStream_t st, const float* g_dev = nullptr);
 int hbk_nvfp4_gemv(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int N, int K, const void* x, int ldx, int M, float* y, int ldy,
                    cudaStream_t st);
 int hbk_nvfp4_quantize(hb_ctx* ctx, const float* w, int N, int K, uint8_t* q, uint8_t* s, float* g_mul, float* amax, cudaStream_t st);

@@ -61,6 +61,9 @@ inline void nvfp4_gemv(const Nvfp4Mat& W, const __nv_bfloat16* x, int ldx, int M
 inline void nvfp4_dequant(const Nvfp4Mat& W, __nv_bfloat16* out, cudaStream_t st) {
   b200::check(hb_nvfp4_dequant(b200::ctx(), W.w, W.s, W.g, W.N, W.K, out, st));
 }
+inline void expert_dequant(const ExpertRecLayout&, const uint8_t* rec, int H, int I, __nv_bfloat16* gu, __nv_bfloat16* d, cudaStream_t st) {
+  b200::check(hb_expert_dequant(b200::ctx(), rec, H, I, gu, d, st));
+}
 inline void swiglu_rows(const __nv_bfloat16* gu_out, int R, int I, float limit, __nv_bfloat16* y, cudaStream_t st) {
   b200::check(hb_swiglu_rows(b200::ctx(), gu_out, R, I, limit, y, st));
 }

@@ -10,8 +10,9 @@
 namespace hb {
 
 // ---- dequant: out[n, k] = bf16( E2M1[nib] * (e4m3(s[n, k/16]) * g) ) — the reference's expression order, so bit-exact
-__global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ W, const uint8_t* __restrict__ S, float g, size_t n_blocks16,
-                                     __nv_bfloat16* __restrict__ out) {
+__global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ W, const uint8_t* __restrict__ S, float g, const float* __restrict__ g_dev,
+                                     size_t n_blocks16, __nv_bfloat16* __restrict__ out) {
+  if (g_dev) g = __ldg(g_dev);                          // the global sits on the device (inside an expert record)
   // one thread per 16-column block: 8 weight bytes in, 32 bytes out
   for (size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x; b < n_blocks16; b += (size_t)gridDim.x * blockDim.x) {
     const float s = __fmul_rn(e4m3_to_f32(S[b]), g);
@@ -170,11 +171,11 @@ __global__ void a4_quant_kernel(const __nv_bfloat16* __restrict__ x, int ld, int
 
 using namespace hb;
 
-int hbk_nvfp4_dequant(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int N, int K, void* out, cudaStream_t st) {
+int hbk_nvfp4_dequant(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int N, int K, void* out, cudaStream_t st, const float* g_dev) {
   const size_t nb = (size_t)N * K / 16;
   size_t blocks = (nb + 255) / 256, cap = (size_t)ctx->sm_count * 16;
   if (blocks > cap) blocks = cap;
-  return hb_launch(ctx, "nvfp4_dequant", false, nvfp4_dequant_kernel, dim3((unsigned)blocks), dim3(256), 0, st, w, s, g, nb,
+  return hb_launch(ctx, "nvfp4_dequant", false, nvfp4_dequant_kernel, dim3((unsigned)blocks), dim3(256), 0, st, w, s, g, g_dev, nb,
                    reinterpret_cast<__nv_bfloat16*>(out));
 }
 

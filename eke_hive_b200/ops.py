@@ -17,7 +17,7 @@ from ._lib import Config, HbError, MoePair, PfCombine, RecLayout
 
 __all__ = ["Context", "context", "ExpertRecLayout", "nvfp4_dequant", "nvfp4_gemv", "nvfp4_quantize", "a4_quant", "router_softmax_topk",
            "router_topk", "build_moe_pairs", "moe_combine", "moe_decode_ws_bytes", "moe_decode", "fn_moe_decode_routed", "fn_moe_decode_routed_static", "static_max_pairs", "moe_decode_routed_f32", "moe_layer_decode",
-           "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "dispatch_plan", "PeerExchange", "moe_decode_ep_local", "moe_prefill_supported", "moe_prefill_ws_bytes", "fn_moe_prefill", "nvfp4_gemm_a4", "fp4_peak_probe", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
+           "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "dispatch_plan", "PeerExchange", "moe_decode_ep_local", "moe_prefill_supported", "moe_prefill_ws_bytes", "fn_moe_prefill", "nvfp4_gemm_a4", "fp4_peak_probe", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "expert_dequant", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
 
 
 def _L():
@@ -492,6 +492,15 @@ def fp4_peak_probe(rounds: int = 4096, ctx: Context | None = None) -> float:
 
 
 # ---------------------------------------------------------------------------------------------------- prefill helpers
+def expert_dequant(rec, H: int, I: int, gu=None, d=None, ctx: Context | None = None):
+    """hive::glm::expert_dequant: one record → bf16 gu [2I, H] (gate rows then up rows), d [H, I]."""
+    ctx = ctx or context()
+    gu = torch.empty((2 * I, H), dtype=torch.bfloat16, device=rec.device) if gu is None else gu
+    d = torch.empty((H, I), dtype=torch.bfloat16, device=rec.device) if d is None else d
+    ctx.check(_L().hb_expert_dequant(ctx.handle, _p(rec), H, I, _p(gu), _p(d), _stream()))
+    return gu, d
+
+
 def gather_rows(x, rows, out=None, ctx: Context | None = None):
     ctx = ctx or context()
     R, H = rows.shape[0], x.shape[1]

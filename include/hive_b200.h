@@ -282,6 +282,10 @@ typedef struct hb_plan {
 HB_API int hb_dispatch_plan(const int32_t* ids_host, int M, int K, int E, int H, int I, int* counts, hb_plan* plan);
 
 /* ---- prefill helpers kept for callers that compose (engine/include/hive/glm/glm_moe.h:33-41) ---- */
+/* hive::glm::expert_dequant — engine/include/hive/glm/glm_moe.h:32-33: one expert record → bf16 gu [2I, H] (gate rows then up rows) and
+ * d [H, I].  The record's globals are read on the device: unlike the reference (engine/src/glm/glm_moe.cu:608-616) the call does not
+ * synchronise the stream. */
+HB_API int hb_expert_dequant(hb_ctx* ctx, const uint8_t* rec, int H, int I, void* gu_bf16, void* d_bf16, void* stream);
 HB_API int hb_gather_rows(hb_ctx* ctx, const void* x_bf16, const int32_t* rows, int R, int H, void* out_bf16, void* stream);
 HB_API int hb_swiglu_rows(hb_ctx* ctx, const void* gu_bf16, int R, int I, float limit, void* y_bf16, void* stream);
 HB_API int hb_scatter_add_rows(hb_ctx* ctx, const void* e_bf16, const int32_t* rows, const float* w, int R, int H, float* out, void* stream);

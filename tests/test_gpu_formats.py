@@ -98,3 +98,20 @@ def test_argument_errors_are_codes_not_aborts(E):
     assert ei.value.status == -2
     with pytest.raises(E.HbError):
         E.ExpertRecLayout.make(100, 64)
+
+
+def test_expert_dequant_bit_exact(E, oracle):
+    """hive::glm::expert_dequant: the three matrices of a record, values bit-exact against the oracle's dequantiser."""
+    import torch
+    from util import random_records
+    H, I = 256, 128
+    rec = random_records(oracle, H, I, 1, 5)[0]
+    off = oracle.rec_layout(H, I)
+    gu, d = E.expert_dequant(torch.from_numpy(rec).cuda(), H, I)
+    g = rec[int(off[6]):int(off[6]) + 12].view(np.float32)
+    for name, got, (a, b), gi, (N, K) in (("w1", gu[:I], (0, 1), 0, (I, H)), ("w3", gu[I:], (2, 3), 1, (I, H)), ("w2", d, (4, 5), 2, (H, I))):
+        q = rec[int(off[a]):int(off[a]) + N * K // 2].reshape(N, K // 2)
+        s = rec[int(off[b]):int(off[b]) + N * K // 16].reshape(N, K // 16)
+        ref = oracle.nvfp4_dequant_bf16(q, s, float(g[gi]))
+        assert np.array_equal(bf16_bits_of(got), ref), name
+
