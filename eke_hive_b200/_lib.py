@@ -119,6 +119,8 @@ def load() -> C.CDLL:
         "hb_moe_prefill": (i, [vp, vp, i, i, vp, vp, i, i, vp, i, i, f, vp, vp, i, vp, C.POINTER(PfCombine)]),
         "hb_nvfp4_gemm_a4": (i, [vp, C.POINTER(QMat), vp, vp, vp, i, vp, i, vp]),
         "hb_fp4_peak_probe": (i, [vp, i, C.POINTER(f)]),
+        "hb_moe_layer_ws_bytes": (sz, [i, i, i, i, i]),
+        "hb_moe_layer": (i, [vp, vp, i, i, i, i, i, i, vp, f, vp, i, vp, i, vp, i, i, f, vp, vp, vp, vp, vp]),
         "hb_dispatch_plan": (i, [vp, i, i, i, i, i, vp, C.POINTER(Plan)]),
         "hb_expert_dequant": (i, [vp, vp, i, i, vp, vp, vp]),
         "hb_gather_rows": (i, [vp, vp, vp, i, i, vp, vp]),

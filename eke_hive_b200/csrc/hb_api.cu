@@ -280,6 +280,72 @@ int hb_moe_layer_decode(hb_ctx* ctx, const float* logits, int ld, int M, int E, 
   return hbk_moe_decode_run(ctx, src, x, H, I, limit, red, ws, as_stream(stream));
 }
 
+// ---- a whole MoE layer for any number of rows: the dispatcher ----
+namespace {
+constexpr int kDecodeRows = 64;          // rows ≤ 64: decode operators; more: grouped GEMM (engine/src/qwen/qwen_engine.cpp:825, :873)
+struct LayerWs { void* op; const uint8_t** tab1; int32_t* ids1; float* w1; float* sh32; void* sh16; };
+size_t layer_carve(void* ws, int M, int K, int E, int H, int I, LayerWs* w) {
+  size_t off = 0;
+  auto take = [&](size_t b) { void* r = ws ? static_cast<char*>(ws) + off : nullptr; off += hb_align256(b); return r; };
+  LayerWs t;
+  const bool pf = M > kDecodeRows && hb_moe_prefill_supported(H, I) > 0;
+  const int rows = M < kDecodeRows ? M : kDecodeRows;
+  t.op = take(pf ? hb_moe_prefill_ws_bytes(M, K, E, H, I) : hb_moe_decode_ws_bytes(rows * (K + 1), H, I));
+  t.tab1 = (const uint8_t**)take(256); t.ids1 = (int32_t*)take(pf ? (size_t)M * 4 : 0); t.w1 = (float*)take(pf ? (size_t)M * 4 : 0);
+  t.sh32 = (float*)take(pf ? (size_t)M * H * 4 : 0); t.sh16 = take(pf ? (size_t)M * H * 2 : 0);
+  if (w) *w = t;
+  return off;
+}
+}  // namespace
+
+size_t hb_moe_layer_ws_bytes(int M, int K, int E, int H, int I) {
+  if (M < 1 || K < 1 || E < 1 || hb_moe_decode_supported(H, I) <= 0) return 0;
+  return layer_carve(nullptr, M, K, E, H, I, nullptr);
+}
+
+int hb_moe_layer(hb_ctx* ctx, const float* logits, int ld, int M, int E, int K, int renorm, int logits_bf16, const float* bias, float sigmoid_scale,
+                 const uint8_t* const* rec_tab, int li, const uint8_t* shared_rec, int gate_col, const void* x, int H, int I, float limit,
+                 int32_t* ids_out, float* w_out, void* out, void* ws, void* stream) {
+  HB_CTX(ctx);
+  if (M == 0) return HB_OK;
+  HB_PTR(ctx, logits); HB_PTR(ctx, rec_tab); HB_PTR(ctx, x); HB_PTR(ctx, ids_out); HB_PTR(ctx, w_out); HB_PTR(ctx, out);
+  HB_REQUIRE(ctx, M > 0 && K >= 1 && K <= 16 && E > 0 && E <= HB_MAX_EXPERTS && K <= E && ld >= E && li >= 0 && gate_col < ld, HB_ERR_INVALID,
+             "moe_layer: M=%d K=%d E=%d ld=%d li=%d gate_col=%d", M, K, E, ld, li, gate_col);
+  HB_REQUIRE(ctx, ws && hb_aligned(ws, 256), HB_ERR_WORKSPACE, "moe_layer: ws NULL or not 256-byte aligned");
+  LayerWs W;
+  layer_carve(ws, M, K, E, H, I, &W);
+  const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(out);
+  if (M <= kDecodeRows || hb_moe_prefill_supported(H, I) <= 0) {
+    // decode operators, 64 rows at a time (one pass when M ≤ 64): per-row results do not depend on the batch
+    for (int m0 = 0; m0 < M; m0 += kDecodeRows) {
+      const int n = M - m0 < kDecodeRows ? M - m0 : kDecodeRows;
+      const int r = hb_moe_layer_decode(ctx, logits + (size_t)m0 * ld, ld, n, E, K, renorm, logits_bf16, bias, sigmoid_scale, rec_tab, li, shared_rec, gate_col,
+                                        xb + (size_t)m0 * H, H, I, limit, ids_out + (size_t)m0 * K, w_out + (size_t)m0 * K, ob + (size_t)m0 * H, W.op, stream);
+      if (r) return r;
+    }
+    return HB_OK;
+  }
+  // grouped GEMM: route → shared expert as a one-expert routing over all rows → routed experts with the fused combine
+  const bool sigmoid = bias != nullptr || sigmoid_scale != 0.f;
+  if (sigmoid) HB_REQUIRE(ctx, ld == E, HB_ERR_INVALID, "moe_layer: the sigmoid router takes dense logits rows (ld == E)");
+  cudaStream_t st = as_stream(stream);
+  int r = sigmoid ? hbk_route_sigmoid_topk(ctx, logits, bias, M, E, K, sigmoid_scale != 0.f ? sigmoid_scale : 1.f, ids_out, w_out, st, false)
+                  : hbk_route_softmax_topk(ctx, logits, ld, M, E, K, renorm, logits_bf16, ids_out, w_out, st, false);
+  if (r) return r;
+  hb_pf_combine cmb = {};
+  if (shared_rec) {
+    if ((r = hbk_layer_prep(ctx, W.tab1, W.ids1, W.w1, M, shared_rec, st))) return r;
+    if ((r = hb_moe_prefill(ctx, W.tab1, 0, 1, W.ids1, W.w1, M, 1, x, H, I, limit, W.sh32, W.op, M, stream, nullptr))) return r;
+    if ((r = hbk_f32_to_bf16(ctx, W.sh32, W.sh16, (size_t)M * H, st))) return r;      // exact: the values are bf16 already
+    cmb.shared = W.sh16; cmb.lg = gate_col >= 0 ? logits : nullptr; cmb.ld = ld; cmb.col = gate_col >= 0 ? gate_col : 0; cmb.out = out;
+    return hb_moe_prefill(ctx, rec_tab, li, E, ids_out, w_out, M, K, x, H, I, limit, nullptr, W.op, M, stream, &cmb);
+  }
+  // no shared expert: out = bf16(routed sum)
+  if ((r = hb_moe_prefill(ctx, rec_tab, li, E, ids_out, w_out, M, K, x, H, I, limit, W.sh32, W.op, M, stream, nullptr))) return r;
+  return hbk_f32_to_bf16(ctx, W.sh32, out, (size_t)M * H, st);
+}
+
 int hb_expert_dequant(hb_ctx* ctx, const uint8_t* rec, int H, int I, void* gu_bf16, void* d_bf16, void* stream) {
   HB_CTX(ctx);
   HB_PTR(ctx, rec); HB_PTR(ctx, gu_bf16); HB_PTR(ctx, d_bf16);

@@ -22,6 +22,8 @@ int hbk_build_pairs(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int 
                     cudaStream_t st, bool pdl);
 int hbk_moe_combine(hb_ctx* ctx, const float* routed, const void* shared, const float* lg, int ld, int col, int M, int H, void* out, cudaStream_t st,
                     bool pdl);
+int hbk_layer_prep(hb_ctx* ctx, const uint8_t** tab1, int32_t* ids1, float* w1, int M, const uint8_t* shared_rec, cudaStream_t st);
+int hbk_f32_to_bf16(hb_ctx* ctx, const float* in, void* out, size_t n, cudaStream_t st);
 int hbk_gather_rows(hb_ctx* ctx, const void* x, const int32_t* rows, int R, int H, void* out, cudaStream_t st);
 int hbk_swiglu_rows(hb_ctx* ctx, const void* gu, int R, int I, float limit, void* y, cudaStream_t st);
 int hbk_scatter_add_rows(hb_ctx* ctx, const void* e, const int32_t* rows, const float* w, int R, int H, float* out, cudaStream_t st);

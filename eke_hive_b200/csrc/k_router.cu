@@ -109,6 +109,21 @@ int hbk_moe_combine(hb_ctx* ctx, const float* routed, const void* shared, const 
   return hb_launch(ctx, "moe_combine", pdl, moe_combine_kernel, dim3((unsigned)(((size_t)M * H + 255) / 256)), dim3(256), 0, st, routed,
                    reinterpret_cast<const __nv_bfloat16*>(shared), lg, ld, col, M, H, reinterpret_cast<__nv_bfloat16*>(out));
 }
+__global__ void layer_prep_kernel(const uint8_t** tab1, int32_t* ids1, float* w1, int M, const uint8_t* shared_rec) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i == 0) tab1[0] = shared_rec;
+  if (i < M) { ids1[i] = 0; w1[i] = 1.f; }
+}
+__global__ void f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = __float2bfloat16(in[i]);
+}
+// the always-on shared expert as a one-expert routing: table {shared_rec}, ids 0, weights 1
+int hbk_layer_prep(hb_ctx* ctx, const uint8_t** tab1, int32_t* ids1, float* w1, int M, const uint8_t* shared_rec, cudaStream_t st) {
+  return hb_launch(ctx, "layer_prep", false, layer_prep_kernel, dim3((M + 255) / 256), dim3(256), 0, st, tab1, ids1, w1, M, shared_rec);
+}
+int hbk_f32_to_bf16(hb_ctx* ctx, const float* in, void* out, size_t n, cudaStream_t st) {
+  return hb_launch(ctx, "f32_to_bf16", false, f32_to_bf16_kernel, dim3(grid_for(ctx, n, 256)), dim3(256), 0, st, in, reinterpret_cast<__nv_bfloat16*>(out), n);
+}
 int hbk_gather_rows(hb_ctx* ctx, const void* x, const int32_t* rows, int R, int H, void* out, cudaStream_t st) {
   return hb_launch(ctx, "gather_rows", false, gather_rows_kernel, dim3(grid_for(ctx, (size_t)R * (H / 8), 256)), dim3(256), 0, st,
                    reinterpret_cast<const uint4*>(x), rows, R, H / 8, reinterpret_cast<uint4*>(out));

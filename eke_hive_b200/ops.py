@@ -17,7 +17,7 @@ from ._lib import Config, HbError, MoePair, PfCombine, RecLayout
 
 __all__ = ["Context", "context", "ExpertRecLayout", "nvfp4_dequant", "nvfp4_gemv", "nvfp4_quantize", "a4_quant", "router_softmax_topk",
            "router_topk", "build_moe_pairs", "moe_combine", "moe_decode_ws_bytes", "moe_decode", "fn_moe_decode_routed", "fn_moe_decode_routed_static", "static_max_pairs", "moe_decode_routed_f32", "moe_layer_decode",
-           "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "dispatch_plan", "PeerExchange", "moe_decode_ep_local", "moe_prefill_supported", "moe_prefill_ws_bytes", "fn_moe_prefill", "nvfp4_gemm_a4", "fp4_peak_probe", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "expert_dequant", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
+           "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "dispatch_plan", "moe_layer", "moe_layer_ws_bytes", "PeerExchange", "moe_decode_ep_local", "moe_prefill_supported", "moe_prefill_ws_bytes", "fn_moe_prefill", "nvfp4_gemm_a4", "fp4_peak_probe", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "expert_dequant", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
 
 
 def _L():
@@ -294,6 +294,26 @@ def moe_layer_decode(logits, x, rec_tab, li: int, E: int, K: int, H: int, I: int
     ws = _ws(M * (K + 1), H, I, x.device, ws)
     ctx.check(_L().hb_moe_layer_decode(ctx.handle, _p(logits), logits.stride(0), M, E, K, int(renorm), int(logits_bf16), _p(bias), sigmoid_scale,
                                        _p(rec_tab), li, _p(shared_rec), gate_col, _p(x), H, I, limit, _p(ids), _p(w), _p(out), _p(ws), _stream()))
+    return ids, w, out
+
+
+def moe_layer_ws_bytes(M: int, K: int, E: int, H: int, I: int) -> int:
+    return int(_L().hb_moe_layer_ws_bytes(M, K, E, H, I))
+
+
+def moe_layer(logits, x, rec_tab, li: int, E: int, K: int, H: int, I: int, shared_rec=None, gate_col: int = -1, renorm: bool = True,
+              logits_bf16: bool = True, bias=None, sigmoid_scale: float = 0.0, limit: float = 0.0, ids=None, w=None, out=None, ws=None,
+              ctx: Context | None = None):
+    """hb_moe_layer: the whole layer for any number of rows — decode operators up to 64 rows, the grouped tensor-core GEMM beyond.
+    Returns (ids, w, out bf16 [M, H])."""
+    ctx = ctx or context()
+    M = x.shape[0]
+    ids = torch.empty((M, K), dtype=torch.int32, device=x.device) if ids is None else ids
+    w = torch.empty((M, K), dtype=torch.float32, device=x.device) if w is None else w
+    out = torch.empty((M, H), dtype=torch.bfloat16, device=x.device) if out is None else out
+    ws = torch.empty(moe_layer_ws_bytes(M, K, E, H, I), dtype=torch.uint8, device=x.device) if ws is None else ws
+    ctx.check(_L().hb_moe_layer(ctx.handle, _p(logits), logits.stride(0), M, E, K, int(renorm), int(logits_bf16), _p(bias), sigmoid_scale,
+                                _p(rec_tab), li, _p(shared_rec), gate_col, _p(x), H, I, limit, _p(ids), _p(w), _p(out), _p(ws), _stream()))
     return ids, w, out
 
 

@@ -263,6 +263,17 @@ HB_API int hb_nvfp4_gemm_a4(hb_ctx* ctx, const hb_qmat* W, const uint8_t* xq, co
  * shared memory (no loads, no epilogue); *tflops = dense FP4 TFLOP/s.  Synchronises the device.  (No reference counterpart.) */
 HB_API int hb_fp4_peak_probe(hb_ctx* ctx, int rounds, float* tflops);
 
+/* ---- a whole MoE layer for any number of rows (the expert-dispatch scheduler) ---- */
+/* router → routed experts → always-on shared expert (one more NVFP4 record, NULL = none) → combine, like hb_moe_layer_decode, for
+ * any M: M ≤ 64 rows run on the decode operators (bf16 activations), more rows on the grouped tensor-core GEMM (hb_moe_prefill:
+ * NVFP4 activations unless the context has HB_FLAG_PREFILL_A16) when the shape allows it (H, I multiples of 256), else on the
+ * decode operators 64 rows at a time — the reference engine's own switch (engine/src/qwen/qwen_engine.cpp:825, :873).
+ * ws ≥ hb_moe_layer_ws_bytes(M, K, E, H, I). */
+HB_API size_t hb_moe_layer_ws_bytes(int M, int K, int E, int H, int I);
+HB_API int hb_moe_layer(hb_ctx* ctx, const float* logits, int ld, int M, int E, int K, int renorm, int logits_bf16, const float* bias,
+                        float sigmoid_scale, const uint8_t* const* rec_tab, int li, const uint8_t* shared_rec, int gate_col,
+                        const void* x_bf16, int H, int I, float limit, int32_t* ids_out, float* w_out, void* out_bf16, void* ws, void* stream);
+
 /* ---- regime choice ---- */
 /* What a caller needs to know before it runs a layer on M rows: how the (row, k) pairs fall on the experts and which operator
  * family takes them.  Host-side restatement of the classification the reference spreads over GlmExperts::decode_layer

@@ -141,3 +141,54 @@ def test_moe_prefill_bf16_activations_equals_decode_operator(E, oracle):
     orc = oracle.moe_routed(H, I, ids_np, w_np, recs, xs, 0.0, 0)
     rms = np.sqrt((orc.astype(np.float64) ** 2).mean(axis=1, keepdims=True)) + 1e-12
     assert np.max(np.abs(out.cpu().numpy() - orc) / rms) <= 2e-2
+
+
+def test_moe_layer_dispatches_by_row_count(E, oracle):
+    """hb_moe_layer: ≤ 64 rows are the decode layer bit for bit; more rows equal router → shared expert through the grouped GEMM →
+    routed experts with the fused combine, composed by hand from the same operators."""
+    dev = torch.device("cuda")
+    H, I, E_, K = 512, 256, 8, 2
+    rng = np.random.default_rng(31)
+    recs = random_records(oracle, H, I, E_ + 1, 31)
+    keep = upload(recs, dev)
+    tab = E.rec_table(keep[:E_])
+    for M in (20, 150):
+        x = torch.tensor(rng.standard_normal((M, H)).astype(np.float32)).to(torch.bfloat16).to(dev)
+        lg = torch.tensor(rng.standard_normal((M, E_ + 1)).astype(np.float32), device=dev)
+        ids, w, out = E.moe_layer(lg, x, tab, 0, E_, K, H, I, shared_rec=keep[E_], gate_col=E_)
+        if M <= 64:
+            ids2, w2, out2 = E.moe_layer_decode(lg, x, tab, 0, E_, K, H, I, shared_rec=keep[E_], gate_col=E_)
+        else:
+            ids2, w2 = E.router_softmax_topk(lg, K, True, True, E=E_)
+            sh = E.fn_moe_prefill(E.rec_table([keep[E_]]), 0, 1, torch.zeros((M, 1), dtype=torch.int32, device=dev),
+                                  torch.ones((M, 1), dtype=torch.float32, device=dev), x, H, I)
+            out2 = E.fn_moe_prefill(tab, 0, E_, ids2, w2, x, H, I, shared=sh.to(torch.bfloat16), lg=lg, col=E_)
+        torch.cuda.synchronize()
+        E.context().check_device()
+        assert torch.equal(ids, ids2) and torch.equal(w, w2), M
+        assert torch.equal(out.view(torch.int16), out2.view(torch.int16)), M
+
+
+def test_moe_prefill_degenerate_inputs(E, oracle):
+    """Nothing to do is not an error: zero rows, and rows whose every id is invalid or points at an absent record (output zeros)."""
+    dev = torch.device("cuda")
+    H, I, E_, K, M = 256, 256, 4, 2, 9
+    recs = random_records(oracle, H, I, E_, 3)
+    keep = upload(recs, dev)
+    tab = E.rec_table([keep[0], None, keep[2], None])
+    x = torch.randn((M, H), device=dev).to(torch.bfloat16)
+    ids = torch.tensor([[1, 3]] * M, dtype=torch.int32, device=dev)
+    ids[0, 0] = -7; ids[1, 1] = 99
+    w = torch.ones((M, K), dtype=torch.float32, device=dev)
+    out = torch.full((M, H), 5.0, dtype=torch.float32, device=dev)
+    E.fn_moe_prefill(tab, 0, E_, ids, w, x, H, I, out=out)
+    torch.cuda.synchronize()
+    E.context().check_device()
+    assert float(out.abs().max()) == 0.0
+    ctx = E.context()
+    ws = torch.empty(E.moe_prefill_ws_bytes(8, K, E_, H, I), dtype=torch.uint8, device=dev)
+    import ctypes as C
+    from eke_hive_b200 import _lib
+    assert _lib.load().hb_moe_prefill(ctx.handle, tab.data_ptr(), 0, E_, ids.data_ptr(), w.data_ptr(), 0, K, x.data_ptr(), H, I, 0.0, out.data_ptr(),
+                                      ws.data_ptr(), 8, None, None) == 0
+
