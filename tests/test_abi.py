@@ -97,3 +97,37 @@ def test_dispatch_plan_host_logic(lib):
         assert abs(p.tile_fill - ref.sum() / (128.0 * p.prefill_tiles)) < 1e-12
         if want == 1:
             assert p.ws_bytes == lib.hb_moe_prefill_ws_bytes(M, K, E, H, I) > 0
+
+
+def test_cxx_drop_in_header_compiles_and_links(tmp_path):
+    """The C++ surface with the reference's namespaces and signatures (csrc/hive_compat.hpp) compiles as host C++ against the public
+    header and links against the shared library — a maintainer's call sites keep compiling.  Nothing is run (no GPU here)."""
+    import shutil
+    import subprocess
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    cxx = shutil.which("g++", path="/usr/bin") or shutil.which("g++")
+    if cxx is None or not Path("/usr/local/cuda/include/cuda_runtime.h").exists():
+        pytest.skip("no host C++ compiler or CUDA headers")
+    src = tmp_path / "callsites.cpp"
+    src.write_text(r'''
+#include "hive_compat.hpp"
+// the reference's own call shapes (glm_experts.cpp:630, qwen_engine.cpp:842-878, fn_moe.h, q27_kernels.h)
+void decode_site(const hive::glm::ExpertRecLayout& L, const hive::glm::MoePair* pairs, int n, const __nv_bfloat16* x, float* out, void* ws, cudaStream_t st) {
+  hive::glm::moe_decode(L, pairs, n, x, 4096, 1536, 10.f, out, ws, st);
+}
+void routed_site(const hive::glm::ExpertRecLayout& L, const int32_t* ids, const float* w, const uint8_t* const* tab, const __nv_bfloat16* x,
+                 const __nv_bfloat16* shared, const float* lg, __nv_bfloat16* out, void* ws, cudaStream_t st) {
+  hive::qwen::fn_moe_decode_routed(L, ids, w, 16, 10, tab, 3, 512, x, 2048, 512, shared, lg, 513, 512, out, ws, st);
+  hive::qwen::FnPfCombine c{shared, lg, 513, 512, out};
+  hive::qwen::fn_moe_prefill(L, tab, 3, 512, ids, w, 8192, 10, x, 2048, 512, nullptr, ws, 8192, st, &c);
+}
+size_t sizes() { return hive::glm::moe_decode_ws_bytes(176, 2048, 512) + hive::qwen::fn_moe_prefill_ws_bytes(8192, 8, 256, 7168, 2048); }
+int main() { return sizes() > 0 ? 0 : 1; }
+''')
+    exe = tmp_path / "callsites"
+    cmd = [cxx, "-std=c++17", "-I", str(root / "include"), "-I", str(root / "eke_hive_b200" / "csrc"), "-I", "/usr/local/cuda/include", str(src),
+           "-L", str(root / "eke_hive_b200"), "-lhive_b200", "-L", "/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath," + str(root / "eke_hive_b200"),
+           "-o", str(exe)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
