@@ -39,7 +39,7 @@ constexpr int PF_STAGE = PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + PF_SFB_BYTES;
 constexpr int PF_STG_PITCH = 144;        // epilogue staging: 32 rows × 128 bytes per warp, rows padded to 144 bytes (conflict-free 16-byte accesses)
 constexpr int PF_STG_BYTES = 32 * PF_STG_PITCH;
 constexpr int PF_SMEM = PF_ST * PF_STAGE + 1024 + 512 + 8 * PF_STG_BYTES;
-constexpr int PF_THREADS = 14 * 32;     // warps 0-3 and 10-13 epilogue, 4 MMA issue, 5 TMA, 6-9 scale transposition
+constexpr int PF_THREADS = 15 * 32;     // warps 0-3 and 10-13 epilogue, 4 MMA issue, 5 TMA, 6-9 scale transposition, 14 scale copies into tensor memory
 constexpr int PF_TMEM_COLS = 512;
 constexpr int PF_SF_COL0 = 256;         // accumulator: columns [0, 256); scales of stage s: [256 + 48 s, 256 + 48 s + 48)
 static_assert(PF_SF_COL0 + 48 * PF_ST <= PF_TMEM_COLS, "tensor memory");
@@ -174,10 +174,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
   uint64_t* mma_done = acc_empty + 1;                                        // the issuing thread's last operation has retired
   uint64_t* sf_full = mma_done + 1;                                          // [ST] the stage's row-major scales have landed
   uint64_t* tr_bar = sf_full + PF_ST;                                        // the 128 transposing threads have read their rows
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tr_bar + 1);
+  uint64_t* sf_tm = tr_bar + 1;                                              // [ST] the stage's scales are in tensor memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_tm + PF_ST);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < PF_ST; ++s) { mbar_init(&full[s], 128 + 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], 1); }   // full: 128 scale threads + the TMA thread
+    for (int s = 0; s < PF_ST; ++s) { mbar_init(&full[s], 128 + 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], 1); mbar_init(&sf_tm[s], 1); }   // full: 128 scale threads + the TMA thread
     mbar_init(acc_full, 1); mbar_init(acc_empty, 256); mbar_init(mma_done, 1); mbar_init(tr_bar, 128);
     mbar_fence_init();
   }
@@ -259,12 +260,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
           if (!(ok = mbar_wait(&full[stage], (it / PF_ST) & 1, a.err, 0x400u))) break;
           tc_fence_after();
           const uint32_t sb = base + stage * PF_STAGE, sfc = tmem + PF_SF_COL0 + stage * 48;
-#pragma unroll
-          for (uint32_t j = 0; j < 4; ++j) {
-            tc_cp_sf(sfc + 4 * j, pf_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + j * 512));
-            tc_cp_sf(sfc + 16 + 8 * j, pf_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + j * 512));
-            tc_cp_sf(sfc + 16 + 8 * j + 4, pf_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + 2048 + j * 512));
-          }
+          if (!(ok = mbar_wait(&sf_tm[stage], (it / PF_ST) & 1, a.err, 0x100000u))) break;     // the copy warp has put the scales into tensor memory
+          tc_fence_after();
           const uint64_t ad = pf_desc_sw128(sb), bd = pf_desc_sw128(sb + PF_A_BYTES);
 #pragma unroll
           for (uint32_t j = 0; j < 4; ++j)                                   // 64 k values = 32 bytes further along the swizzled row
@@ -276,7 +273,28 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
       tc_commit(mma_done);                                                   // nothing of this thread's is in flight when tensor memory is freed
       mbar_wait(mma_done, 0, a.err, 0x800u);
     }
-  } else if (warp < 4 || warp >= 10) {
+  } else if (warp == 14) {
+    // ------------------------------------------------------------------------------------------------ scale copies: one thread, ahead of the MMA thread
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long w = blockIdx.x; w < work && ok; w += gridDim.x) {
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const uint32_t stage = it % PF_ST;
+          if (!(ok = mbar_wait(&full[stage], (it / PF_ST) & 1, a.err, 0x200000u))) break;
+          tc_fence_after();
+          const uint32_t sb = base + stage * PF_STAGE, sfc = tmem + PF_SF_COL0 + stage * 48;
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {
+            tc_cp_sf(sfc + 4 * j, pf_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + j * 512));
+            tc_cp_sf(sfc + 16 + 8 * j, pf_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + j * 512));
+            tc_cp_sf(sfc + 16 + 8 * j + 4, pf_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + 2048 + j * 512));
+          }
+          tc_commit(&sf_tm[stage]);
+        }
+      }
+    }
+  } else if (warp < 4 || (warp >= 10 && warp < 14)) {
     // ------------------------------------------------------------------------------------------------ epilogue: a warp reads the 32 lanes of its quarter (warp index mod 4);
     // warps 0-3 take the first half of the tile's columns, warps 10-13 the second
     const int qtr = warp & 3, half = warp >= 10 ? 1 : 0;
