@@ -56,11 +56,11 @@ struct PfGemmArgs {
   int M;                                       // PLAIN only
   const int* perm;                             // pair of a sorted slot (DOWN scatters its rows by it)
   // A operand (quantised activations, tile rows contiguous): codes come through the kernel's tensor-map parameter
-  const float* ag; int Kd;                     // per-row global (codes and scales: tensor-map parameters)
+  const uint8_t* as; const float* ag; int Kd;  // scales [rows, Kd/16] and per-row global (codes: tensor-map parameter)
   // B operand
   const uint8_t* const* tab; hb_rec_layout L;  // GU / DOWN: expert records
   const CUtensorMap* tmB;                      // GU / DOWN: [expert][6] tensor maps of w1, w3, w2, s1, s3, s2 (written by pf_tmaps_kernel)
-  float bg;                                    // PLAIN: global of the one matrix [N, Kd] (codes and scales: tensor-map parameters)
+  const uint8_t* bs; float bg;                 // PLAIN: scales and global of the one matrix [N, Kd] (codes: tensor-map parameter)
   int N;                                       // output columns in all (I for GU, H for DOWN, N for PLAIN)
   float limit;
   void* out; int ldo;                          // GU: y bf16 [slots, I]; DOWN: part bf16 [pairs, H]; PLAIN: fp32 [M, ldo]
@@ -162,8 +162,7 @@ __device__ __forceinline__ void pf_epi_flush(const uint8_t* stg, uint8_t* gptr, 
 
 template <int MODE>
 __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs a, const __grid_constant__ CUtensorMap tmA,
-                                                                const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmSA,
-                                                                const __grid_constant__ CUtensorMap tmSB0) {
+                                                                const __grid_constant__ CUtensorMap tmB0) {
   extern __shared__ uint8_t pf_raw[];
   const uint32_t raw = smem_u32(pf_raw), base = (raw + 1023u) & ~1023u;     // swizzle atoms want 1024-byte alignment
   uint8_t* sm = pf_raw + (base - raw);
@@ -172,14 +171,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
   uint64_t* acc_full = empty + PF_ST;                                        // the tile's accumulators are complete
   uint64_t* acc_empty = acc_full + 1;                                        // the epilogue has read them
   uint64_t* mma_done = acc_empty + 1;                                        // the issuing thread's last operation has retired
-  uint64_t* sf_full = mma_done + 1;                                          // [ST] the stage's row-major scales have landed
-  uint64_t* tr_bar = sf_full + PF_ST;                                        // the 128 transposing threads have read their rows
-  uint64_t* sf_tm = tr_bar + 1;                                              // [ST] the stage's scales are in tensor memory
+  uint64_t* sf_tm = mma_done + 1;                                              // [ST] the stage's scales are in tensor memory
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_tm + PF_ST);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < PF_ST; ++s) { mbar_init(&full[s], 128 + 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], 1); mbar_init(&sf_tm[s], 1); }   // full: 128 scale threads + the TMA thread
-    mbar_init(acc_full, 1); mbar_init(acc_empty, 256); mbar_init(mma_done, 1); mbar_init(tr_bar, 128);
+    for (int s = 0; s < PF_ST; ++s) { mbar_init(&full[s], 128 + 1); mbar_init(&empty[s], 1); mbar_init(&sf_tm[s], 1); }   // full: 128 scale threads + the TMA thread
+    mbar_init(acc_full, 1); mbar_init(acc_empty, 256); mbar_init(mma_done, 1);
     mbar_fence_init();
   }
   if (warp == 4) { tmem_alloc(tmem_slot, PF_TMEM_COLS); tmem_relinquish(); }
@@ -202,19 +199,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
       for (long long w = blockIdx.x; w < work && ok; w += gridDim.x) {
         const int ti = (int)(w / n_nt), nt = (int)(w - (long long)ti * n_nt);
         const PfTile tl = pf_tile(a, ti);
-        const CUtensorMap *m0 = &tmB0, *m1 = &tmB0, *q0 = &tmSB0, *q1 = &tmSB0;
+        const CUtensorMap *m0 = &tmB0, *m1 = &tmB0;
         int r0 = nt * 256, r1 = nt * 256 + 128;                               // B rows of the tile's two 128-row boxes
-        if (MODE == PF_GU) { m0 = a.tmB + (size_t)tl.e * 6; m1 = m0 + 1; q0 = m0 + 3; q1 = m0 + 4; r0 = r1 = nt * 128; }
-        if (MODE == PF_DOWN) { m0 = m1 = a.tmB + (size_t)tl.e * 6 + 2; q0 = q1 = m0 + 3; }
-        if (MODE != PF_PLAIN) { tmap_acquire(m0); tmap_acquire(q0); if (m1 != m0) { tmap_acquire(m1); tmap_acquire(q1); } }
+        if (MODE == PF_GU) { m0 = a.tmB + (size_t)tl.e * 6; m1 = m0 + 1; r0 = r1 = nt * 128; }
+        if (MODE == PF_DOWN) m0 = m1 = a.tmB + (size_t)tl.e * 6 + 2;
+        if (MODE != PF_PLAIN) { tmap_acquire(m0); if (m1 != m0) tmap_acquire(m1); }
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const uint32_t stage = it % PF_ST;
           if (!(ok = mbar_wait(&empty[stage], ((it / PF_ST) & 1) ^ 1, a.err, 0x100u))) break;
-          const uint32_t sb = base + stage * PF_STAGE, sf = sb + PF_A_BYTES + PF_B_BYTES;
-          mbar_expect_tx(&sf_full[stage], PF_SFA_BYTES + PF_SFB_BYTES);      // scales first: they still have to be transposed
-          tma_load_2d(sf, &tmSA, kb * 16, tl.slot0, &sf_full[stage]);
-          tma_load_2d(sf + PF_SFA_BYTES, q0, kb * 16, r0, &sf_full[stage]);
-          tma_load_2d(sf + PF_SFA_BYTES + 2048, q1, kb * 16, r1, &sf_full[stage]);
+          const uint32_t sb = base + stage * PF_STAGE;
           mbar_expect_tx(&full[stage], PF_A_BYTES + PF_B_BYTES);
           tma_load_2d(sb, &tmA, kb * 128, tl.slot0, &full[stage]);
           tma_load_2d(sb + PF_A_BYTES, m0, kb * 128, r0, &full[stage]);
@@ -223,28 +216,46 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
       }
     }
   } else if (warp >= 6 && warp < 10) {
-    // ------------------------------------------------------------------------------------------------ scale transposers: thread lt owns row lt of each 128-row block
-    // A block arrives row-major, 16 bytes per row = 4 MMA k-steps × 4 scales.  tcgen05.cp wants, per k-step, 32 rows × 16 bytes
-    // where row l holds the 4 scales of rows l, l + 32, l + 64, l + 96: a 4-byte-word transpose, done in place.
+    // ------------------------------------------------------------------------------------------------ scale loaders: thread lt owns row lt of each 128-row block
+    // A row's 16 scale bytes of a stage = 4 MMA k-steps × 4 scales.  tcgen05.cp wants, per k-step, 32 rows × 16 bytes where row l holds
+    // the 4 scales of rows l, l + 32, l + 64, l + 96: each thread loads its three rows (A block, two B blocks) two stages ahead
+    // into registers and stores them as 4-byte words into the transposed places.
     const int lt = threadIdx.x - 192;
-    const uint32_t src = (uint32_t)lt * 16, dst = (uint32_t)((lt & 31) * 16 + (lt >> 5) * 4);
+    const uint32_t dst = (uint32_t)((lt & 31) * 16 + (lt >> 5) * 4);
+    const size_t rows = (size_t)a.Kd / 16;
     uint32_t it = 0;
     bool ok = true;
     for (long long w = blockIdx.x; w < work && ok; w += gridDim.x) {
+      const int ti = (int)(w / n_nt), nt = (int)(w - (long long)ti * n_nt);
+      const PfTile tl = pf_tile(a, ti);
+      const uint8_t* pa = a.as + (size_t)(tl.slot0 + min(lt, tl.m - 1)) * rows;   // rows past the tile's end repeat its last row (never stored)
+      const uint8_t *pb, *pc;
+      if (MODE == PF_PLAIN) { pb = a.bs + (size_t)(nt * 256 + lt) * rows; pc = pb + 128 * rows; }
+      else {
+        const uint8_t* rec = a.tab[tl.e];
+        if (MODE == PF_GU) { pb = rec + a.L.s1 + (size_t)(nt * 128 + lt) * rows; pc = rec + a.L.s3 + (size_t)(nt * 128 + lt) * rows; }
+        else { pb = rec + a.L.s2 + (size_t)(nt * 256 + lt) * rows; pc = pb + 128 * rows; }
+      }
+      auto ld3 = [&](int kb, uint4& x0, uint4& x1, uint4& x2) {
+        if (kb < nkb) {
+          x0 = __ldg(reinterpret_cast<const uint4*>(pa) + kb); x1 = __ldg(reinterpret_cast<const uint4*>(pb) + kb); x2 = __ldg(reinterpret_cast<const uint4*>(pc) + kb);
+        }
+      };
+      uint4 va = make_uint4(0, 0, 0, 0), vb = va, vc = va, na = va, nb = va, nc = va;
+      ld3(0, va, vb, vc);
+      ld3(1, na, nb, nc);
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const uint32_t stage = it % PF_ST;
-        if (!(ok = mbar_wait(&sf_full[stage], (it / PF_ST) & 1, a.err, 0x4000u))) break;
-        uint8_t* sf = sm + stage * PF_STAGE + PF_A_BYTES + PF_B_BYTES;
-        const uint4 va = *reinterpret_cast<const uint4*>(sf + src), vb = *reinterpret_cast<const uint4*>(sf + 2048 + src),
-                    vc = *reinterpret_cast<const uint4*>(sf + 4096 + src);
-        mbar_arrive(tr_bar);                                                 // every row of the stage is in registers before any is overwritten
-        if (!(ok = mbar_wait(tr_bar, it & 1, a.err, 0x8000u))) break;
-        uint32_t* o = reinterpret_cast<uint32_t*>(sf + dst);
+        uint4 fa = make_uint4(0, 0, 0, 0), fb = fa, fc = fa;
+        ld3(kb + 2, fa, fb, fc);                                             // two stages ahead: the latency of these loads is never waited for
+        if (!(ok = mbar_wait(&empty[stage], ((it / PF_ST) & 1) ^ 1, a.err, 0x4000u))) break;
+        uint32_t* o = reinterpret_cast<uint32_t*>(sm + stage * PF_STAGE + PF_A_BYTES + PF_B_BYTES + dst);
         o[0] = va.x; o[128] = va.y; o[256] = va.z; o[384] = va.w;            // k-step j of a block sits 512 bytes after k-step j - 1
         o[512] = vb.x; o[640] = vb.y; o[768] = vb.z; o[896] = vb.w;
         o[1024] = vc.x; o[1152] = vc.y; o[1280] = vc.z; o[1408] = vc.w;
         fence_proxy_async_smem();
         mbar_arrive(&full[stage]);
+        va = na; vb = nb; vc = nc; na = fa; nb = fb; nc = fc;
       }
     }
   } else if (warp == 4) {
@@ -590,10 +601,9 @@ int pf_make_map(hb_ctx* ctx, CUtensorMap* m, const void* base, size_t row_bytes,
   return HB_OK;
 }
 template <int MODE>
-int pf_launch(hb_ctx* ctx, const char* name, const PfGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB0, const CUtensorMap& tmSA,
-              const CUtensorMap& tmSB0, cudaStream_t st) {
+int pf_launch(hb_ctx* ctx, const char* name, const PfGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB0, cudaStream_t st) {
   const int grid = ctx->max_ctas > 0 && ctx->max_ctas < ctx->sm_count ? ctx->max_ctas : ctx->sm_count;
-  return hb_launch(ctx, name, false, pf_gemm_kernel<MODE>, dim3(grid), dim3(PF_THREADS), (size_t)PF_SMEM, st, a, tmA, tmB0, tmSA, tmSB0);
+  return hb_launch(ctx, name, false, pf_gemm_kernel<MODE>, dim3(grid), dim3(PF_THREADS), (size_t)PF_SMEM, st, a, tmA, tmB0);
 }
 }  // namespace
 
@@ -653,12 +663,10 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
   const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(x_bf16);
   int r;
   const size_t Pcap = (size_t)S * K;
-  CUtensorMap tm_x, tm_y, tm_xs, tm_ys;
+  CUtensorMap tm_x, tm_y;
   PfMapSet tpl;
   if ((r = pf_make_map(ctx, &tm_x, W.xq_s, (size_t)H / 2, Pcap))) return r;
   if ((r = pf_make_map(ctx, &tm_y, W.yq, (size_t)I / 2, Pcap))) return r;
-  if ((r = pf_make_map(ctx, &tm_xs, W.xs_s, (size_t)H / 16, Pcap, true))) return r;
-  if ((r = pf_make_map(ctx, &tm_ys, W.ys, (size_t)I / 16, Pcap, true))) return r;
   if ((r = pf_make_map(ctx, &tpl.gu, W.xq_s, (size_t)H / 2, (size_t)I))) return r;          // addresses are stamped per expert on the device
   if ((r = pf_make_map(ctx, &tpl.dn, W.xq_s, (size_t)I / 2, (size_t)H))) return r;
   if ((r = pf_make_map(ctx, &tpl.gu_s, W.xq_s, (size_t)H / 16, (size_t)I, true))) return r;
@@ -676,11 +684,11 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
                        (const uint8_t*)W.xq, (const uint8_t*)W.xs, (const float*)W.xg, W.xq_s, W.xs_s, W.xg_s))) return r;
     PfGemmArgs a{};
     a.tiles = W.tiles; a.n_tiles = W.n_tiles; a.perm = W.perm; a.tab = lt; a.L = L; a.tmB = W.tmB; a.limit = limit; a.err = ctx->dev_err;
-    a.ag = W.xg_s; a.Kd = H; a.N = I; a.out = W.y; a.ldo = I;
-    if ((r = pf_launch<PF_GU>(ctx, "pf_gemm_gu", a, tm_x, tm_x, tm_xs, tm_xs, st))) return r;
+    a.as = W.xs_s; a.ag = W.xg_s; a.Kd = H; a.N = I; a.out = W.y; a.ldo = I;
+    if ((r = pf_launch<PF_GU>(ctx, "pf_gemm_gu", a, tm_x, tm_x, st))) return r;
     if ((r = hbk_a4_quant(ctx, W.y, I, P, I, W.yq, W.ys, W.yg, st))) return r;
-    a.ag = W.yg; a.Kd = I; a.N = H; a.out = W.part; a.ldo = H;
-    if ((r = pf_launch<PF_DOWN>(ctx, "pf_gemm_down", a, tm_y, tm_y, tm_ys, tm_ys, st))) return r;
+    a.as = W.ys; a.ag = W.yg; a.Kd = I; a.N = H; a.out = W.part; a.ldo = H;
+    if ((r = pf_launch<PF_DOWN>(ctx, "pf_gemm_down", a, tm_y, tm_y, st))) return r;
     const size_t pairs2 = (size_t)n * H / 8;
     const __nv_bfloat16* sh = cmb ? reinterpret_cast<const __nv_bfloat16*>(cmb->shared) + (size_t)s0 * H : nullptr;
     if ((r = hb_launch(ctx, "pf_reduce", false, pf_reduce_kernel, dim3((unsigned)((pairs2 + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16*)W.part, sid,
@@ -700,15 +708,13 @@ int hb_nvfp4_gemm_a4(hb_ctx* ctx, const hb_qmat* W, const uint8_t* xq, const uin
   HB_REQUIRE(ctx, hb_aligned(W->w, 16) && hb_aligned(W->s, 16) && hb_aligned(xq, 16) && hb_aligned(xs, 16) && hb_aligned(y, 16), HB_ERR_INVALID,
              "nvfp4_gemm_a4: operands must be 16-byte aligned");
   PfGemmArgs a{};
-  a.M = M; a.ag = xg; a.Kd = W->K; a.bg = W->g; a.N = W->N;
+  a.M = M; a.as = xs; a.ag = xg; a.Kd = W->K; a.bs = reinterpret_cast<const uint8_t*>(W->s); a.bg = W->g; a.N = W->N;
   a.out = y; a.ldo = ldy; a.err = ctx->dev_err;
-  CUtensorMap tm_a, tm_b, tm_as, tm_bs;
+  CUtensorMap tm_a, tm_b;
   int r;
   if ((r = pf_make_map(ctx, &tm_a, xq, (size_t)W->K / 2, (size_t)M))) return r;
   if ((r = pf_make_map(ctx, &tm_b, W->w, (size_t)W->K / 2, (size_t)W->N))) return r;
-  if ((r = pf_make_map(ctx, &tm_as, xs, (size_t)W->K / 16, (size_t)M, true))) return r;
-  if ((r = pf_make_map(ctx, &tm_bs, W->s, (size_t)W->K / 16, (size_t)W->N, true))) return r;
-  return pf_launch<PF_PLAIN>(ctx, "pf_gemm_plain", a, tm_a, tm_b, tm_as, tm_bs, reinterpret_cast<cudaStream_t>(stream));
+  return pf_launch<PF_PLAIN>(ctx, "pf_gemm_plain", a, tm_a, tm_b, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int hb_fp4_peak_probe(hb_ctx* ctx, int rounds, float* tflops) {
