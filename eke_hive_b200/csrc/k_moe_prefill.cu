@@ -225,29 +225,39 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
     const size_t rows = (size_t)a.Kd / 16;
     uint32_t it = 0;
     bool ok = true;
-    for (long long w = blockIdx.x; w < work && ok; w += gridDim.x) {
+    struct Rows { const uint8_t *pa, *pb, *pc; };
+    auto rows_of = [&](long long w) {                                       // this thread's three scale rows of work item w
+      Rows r = {nullptr, nullptr, nullptr};
+      if (w >= work) return r;
       const int ti = (int)(w / n_nt), nt = (int)(w - (long long)ti * n_nt);
       const PfTile tl = pf_tile(a, ti);
-      const uint8_t* pa = a.as + (size_t)(tl.slot0 + min(lt, tl.m - 1)) * rows;   // rows past the tile's end repeat its last row (never stored)
-      const uint8_t *pb, *pc;
-      if (MODE == PF_PLAIN) { pb = a.bs + (size_t)(nt * 256 + lt) * rows; pc = pb + 128 * rows; }
+      r.pa = a.as + (size_t)(tl.slot0 + min(lt, tl.m - 1)) * rows;          // rows past the tile's end repeat its last row (never stored)
+      if (MODE == PF_PLAIN) { r.pb = a.bs + (size_t)(nt * 256 + lt) * rows; r.pc = r.pb + 128 * rows; }
       else {
         const uint8_t* rec = a.tab[tl.e];
-        if (MODE == PF_GU) { pb = rec + a.L.s1 + (size_t)(nt * 128 + lt) * rows; pc = rec + a.L.s3 + (size_t)(nt * 128 + lt) * rows; }
-        else { pb = rec + a.L.s2 + (size_t)(nt * 256 + lt) * rows; pc = pb + 128 * rows; }
+        if (MODE == PF_GU) { r.pb = rec + a.L.s1 + (size_t)(nt * 128 + lt) * rows; r.pc = rec + a.L.s3 + (size_t)(nt * 128 + lt) * rows; }
+        else { r.pb = rec + a.L.s2 + (size_t)(nt * 256 + lt) * rows; r.pc = r.pb + 128 * rows; }
       }
-      auto ld3 = [&](int kb, uint4& x0, uint4& x1, uint4& x2) {
-        if (kb < nkb) {
-          x0 = __ldg(reinterpret_cast<const uint4*>(pa) + kb); x1 = __ldg(reinterpret_cast<const uint4*>(pb) + kb); x2 = __ldg(reinterpret_cast<const uint4*>(pc) + kb);
-        }
-      };
-      uint4 va = make_uint4(0, 0, 0, 0), vb = va, vc = va, na = va, nb = va, nc = va;
-      ld3(0, va, vb, vc);
-      ld3(1, na, nb, nc);
+      return r;
+    };
+    // the loads run two stages ahead of the stores, across work items: a cursor of their own
+    long long pw = blockIdx.x;
+    int pkb = 0;
+    Rows pr = rows_of(pw);
+    auto fetch = [&](uint4& x0, uint4& x1, uint4& x2) {
+      if (pr.pa) {
+        x0 = __ldg(reinterpret_cast<const uint4*>(pr.pa) + pkb); x1 = __ldg(reinterpret_cast<const uint4*>(pr.pb) + pkb); x2 = __ldg(reinterpret_cast<const uint4*>(pr.pc) + pkb);
+      }
+      if (++pkb == nkb) { pkb = 0; pw += gridDim.x; pr = rows_of(pw); }
+    };
+    uint4 va = make_uint4(0, 0, 0, 0), vb = va, vc = va, na = va, nb = va, nc = va;
+    fetch(va, vb, vc);
+    fetch(na, nb, nc);
+    for (long long w = blockIdx.x; w < work && ok; w += gridDim.x) {
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const uint32_t stage = it % PF_ST;
         uint4 fa = make_uint4(0, 0, 0, 0), fb = fa, fc = fa;
-        ld3(kb + 2, fa, fb, fc);                                             // two stages ahead: the latency of these loads is never waited for
+        fetch(fa, fb, fc);                                                   // the latency of these loads is never waited for
         if (!(ok = mbar_wait(&empty[stage], ((it / PF_ST) & 1) ^ 1, a.err, 0x4000u))) break;
         uint32_t* o = reinterpret_cast<uint32_t*>(sm + stage * PF_STAGE + PF_A_BYTES + PF_B_BYTES + dst);
         o[0] = va.x; o[128] = va.y; o[256] = va.z; o[384] = va.w;            // k-step j of a block sits 512 bytes after k-step j - 1
