@@ -505,6 +505,19 @@ def run_prefill(args):
                          "unit": "TFLOP/s", "frac": flops / world / (gemm_us * 1e-6) / 1e12 / peak,
                          "peak_source": "hb_fp4_peak_probe on this GPU (dense FP4, resident operands)", "traffic": None},
             "kernels": prof}
+    # the same two GEMMs against HBM: at ~256 rows per expert every weight byte serves 256 rows, so even at the FP4 peak the expert
+    # records would have to stream at 2·256 / (9/16) flop per byte — more than HBM gives.  Both views are reported.
+    hbm = {}
+    try:
+        hbm = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+    hbm_peak = float(hbm.get("hbm_gbs", 6650.0))
+    wbytes = n_loc * (3 * H * I * 9 // 16) + (T * K // world) * ((H + I) * 9 // 16) + (T * K // world) * (I + H) * 2      # records + quantised rows + y, part
+    line["roofline_hbm"] = {"bound": "hbm", "kernel": "pf_gemm_kernel (gate/up + down), this rank's share", "achieved": wbytes / (gemm_us * 1e-6) / 1e9,
+                            "peak": hbm_peak, "unit": "GB/s", "frac": wbytes / (gemm_us * 1e-6) / 1e9 / hbm_peak,
+                            "note": "expert records read once + quantised activation rows + bf16 outputs; min time at peak %.2f ms vs %.2f ms at the FP4 peak"
+                                    % (wbytes / hbm_peak / 1e6, flops / world / peak / 1e9)}
     if world == 1:
         M, N, Kd = 16384, 8192, 8192
         xq, xs, xg = E.a4_quant(torch.randn((M, Kd), device=dev, generator=g).to(torch.bfloat16))
