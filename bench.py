@@ -263,7 +263,7 @@ def run_ours(args):
     for B in batches:
         logits = torch.randn((NSETS, L, B, Ex + 1), dtype=torch.float32, device=dev, generator=gen)     # column E: shared-expert gate logit
         x = torch.randn((NSETS, L, B, H), dtype=torch.float32, device=dev, generator=gen).to(torch.bfloat16)
-        out = torch.empty((L, B, H), dtype=torch.bfloat16, device=dev)
+        out = torch.empty((NSETS, L, B, H), dtype=torch.bfloat16, device=dev)         # one output buffer per input set (the copies of a step overlap the next step)
         ids = torch.empty((NSETS, L, B, K), dtype=torch.int32, device=dev)
         wts = torch.empty((NSETS, L, B, K), dtype=torch.float32, device=dev)
         if world > 1:
@@ -272,14 +272,14 @@ def run_ours(args):
 
             def run_layers(s):
                 for li in range(L):
-                    ep.layer(logits[s, li], x[s, li], tab, li, shared_ptr[li], Ex, ids[s, li], wts[s, li], out[li])
+                    ep.layer(logits[s, li], x[s, li], tab, li, shared_ptr[li], Ex, ids[s, li], wts[s, li], out[s, li])
         else:
             ws = torch.empty(E.moe_decode_ws_bytes(B * (K + 1), H, I), dtype=torch.uint8, device=dev)
 
             def run_layers(s):
                 for li in range(L):
                     E.moe_layer_decode(logits[s, li], x[s, li], tab, li, Ex, K, H, I, shared_rec=shared_ptr[li], gate_col=Ex, ids=ids[s, li],
-                                       w=wts[s, li], out=out[li], ws=ws, ctx=ctx)
+                                       w=wts[s, li], out=out[s, li], ws=ws, ctx=ctx)
         # warm every kernel once outside capture, then one graph per input set
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -299,7 +299,7 @@ def run_ours(args):
         torch.cuda.synchronize()
         trace(f"B={B}: graphs captured")
 
-        def timed(nsteps, fn):
+        def timed(nsteps, fn, finish=None):
             if world > 1:
                 dist.barrier()
             torch.cuda.synchronize()
@@ -307,6 +307,8 @@ def run_ours(args):
             e0.record()
             for i in range(nsteps):
                 fn(i)
+            if finish:
+                finish()
             e1.record()
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1)
@@ -344,22 +346,48 @@ def run_ours(args):
             # ---- end to end: pinned host inputs → H2D → layers → D2H of the outputs, every step
             hl = [torch.randn((L, B, Ex + 1), dtype=torch.float32).pin_memory() for _ in range(NSETS)]
             hx = [torch.randn((L, B, H), dtype=torch.float32).to(torch.bfloat16).pin_memory() for _ in range(NSETS)]
-            hout = torch.empty((L, B, H), dtype=torch.bfloat16).pin_memory()
+            hout = [torch.empty((L, B, H), dtype=torch.bfloat16).pin_memory() for _ in range(NSETS)]
+            # Every step copies its inputs from pinned host memory and its outputs back, inside the timed region.  The copies run on a
+            # second stream so that step i+1's upload and step i's download overlap step i's / i+1's compute (two input sets, two
+            # output buffers); events order upload → compute → download per set, and the timed region ends only when the last
+            # download has finished.
+            main, cps = torch.cuda.current_stream(), torch.cuda.Stream()
+            up = [torch.cuda.Event() for _ in range(NSETS)]; comp = [torch.cuda.Event() for _ in range(NSETS)]; down = [torch.cuda.Event() for _ in range(NSETS)]
+
+            def upload(s):
+                with torch.cuda.stream(cps):
+                    cps.wait_event(comp[s])                          # the previous compute on this set has read its inputs
+                    logits[s].copy_(hl[s], non_blocking=True)
+                    x[s].copy_(hx[s], non_blocking=True)
+                    up[s].record(cps)
 
             def e2e_step(i):
                 s = i % NSETS
-                logits[s].copy_(hl[s], non_blocking=True)
-                x[s].copy_(hx[s], non_blocking=True)
+                main.wait_event(up[s])                               # this step's inputs are on the device
+                main.wait_event(down[s])                             # the previous results of this set have left its output buffer
                 graphs[s].replay()
-                hout.copy_(out, non_blocking=True)
+                comp[s].record(main)
+                upload((i + 1) % NSETS)                              # next step's inputs, while this step computes
+                with torch.cuda.stream(cps):
+                    cps.wait_event(comp[s])
+                    hout[s].copy_(out[s], non_blocking=True)
+                    down[s].record(cps)
 
+            def e2e_finish():
+                main.wait_stream(cps)
+
+            for s0 in range(NSETS):
+                comp[s0].record(main); down[s0].record(main)
+            upload(0)
             for i in range(max(3, args.warmup)):
                 e2e_step(i)
+            torch.cuda.synchronize()
             sampler.active = True
-            ms_e = timed(args.steps, e2e_step) / args.steps
+            ms_e = timed(args.steps, e2e_step, e2e_finish) / args.steps
             sampler.active = False
             e2e = {"value": B * world * L / (ms_e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e,
-                   "h2d_bytes_per_step": hl[0].numel() * 4 + hx[0].numel() * 2, "d2h_bytes_per_step": hout.numel() * 2}
+                   "h2d_bytes_per_step": hl[0].numel() * 4 + hx[0].numel() * 2, "d2h_bytes_per_step": hout[0].numel() * 2,
+                   "overlap": "copies on a second stream: step i+1's upload and step i's download overlap compute; all inside the timed region"}
             # ---- per-kernel durations (library event pairs, PDL off, no graph) for the roofline of the dominant kernel
             prof = None
             if world == 1:
