@@ -4,6 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --workload prefill [--tokens T]      one DeepSeek-shaped prefill MoE layer (tcgen05 FP4 grouped GEMM), FP4 roofline
     python bench.py --workload dense                     the dense 27B-style MLP GEMVs (NVFP4, 3-bit, 2-bit), HBM roofline
+    python bench.py --workload records                   expert records assembled on the device from checkpoint-form tensors (compressed scales)
 
 One "step" is one decode step of B tokens through the 48 MoE layers (router → routed NVFP4 experts → NVFP4 shared expert →
 combine), each layer with its own weights, so a step streams ≈ 48 × U × 1.77 MB of distinct expert records (far more than the
@@ -623,6 +624,79 @@ def run_dense(args):
                       "per_case": res}), flush=True)
 
 
+def run_records(args):
+    """The step in front of the path: n experts (Qwen3-Next shape, hidden 2048, FFN 512) assembled into records on the device from
+    checkpoint-form tensors whose block scales are stored compressed; one hb_record_pack_batch call per step."""
+    import torch
+    import eke_hive_b200 as E
+    dev = torch.device("cuda", 0)
+    ctx = E.context()
+    H, I, n, distinct = 2048, 512, 256, 8
+
+    def synth(rng, R, C):
+        """e4m3 codes around one level with a 2 % tail of outliers, compressed as a checkpoint stores them (base = row minimum, entries
+        more than 15 above it as exception words)"""
+        s = np.minimum(40 + rng.integers(0, 12, (R, C)) + np.where(rng.integers(0, 50, (R, C)) == 0, rng.integers(0, 70, (R, C)), 0), 0x7E).astype(np.uint8)
+        base = s.min(axis=1)
+        d = s.astype(np.int32) - base[:, None]
+        flat = np.flatnonzero(d.reshape(-1) > 15)
+        exc = ((s.reshape(-1)[flat].astype(np.uint32) << 24) | flat.astype(np.uint32)).astype(np.uint32)
+        d[d > 15] = 0
+        nib = d.reshape(R // 16, 16 * C).astype(np.uint8)
+        fixed = np.zeros((R // 16, 16 + 8 * C), dtype=np.uint8)
+        fixed[:, :16] = base.reshape(R // 16, 16)
+        fixed[:, 16:] = nib[:, 0::2] | (nib[:, 1::2] << 4)
+        return fixed, exc
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    rng = np.random.default_rng(0)
+    L = E.ExpertRecLayout(H, I)
+    host, src_bytes = [], 0
+    for _ in range(distinct):                                  # a few distinct compressed scale tensors, every expert its own copy on the device
+        pr = []
+        for rows, K in ((I, H), (I, H), (H, I)):
+            fx, ex = synth(rng, rows, K // 16)
+            pr.append((fx, ex.view(np.int32)))
+        host.append(pr)
+    experts = []
+    for r in range(n):
+        projs = []
+        for j, (rows, K) in enumerate(((I, H), (I, H), (H, I))):
+            fx, ex = host[r % distinct][j]
+            projs.append({"weight": torch.randint(0, 256, (rows, K // 2), dtype=torch.uint8, device=dev), "csf_fixed": torch.from_numpy(fx).to(dev),
+                          "csf_exc": torch.from_numpy(ex).to(dev), "global": 1e-4})
+            src_bytes += rows * K // 2 + fx.size + ex.size * 4
+        experts.append(projs)
+    recs = torch.zeros((n, int(L.total)), dtype=torch.uint8, device=dev)
+    jobs = E.record_jobs(experts, recs)
+    status = torch.empty((n, 3, 2), dtype=torch.int32, device=dev)
+    ws = torch.empty(E.record_pack_ws_bytes(H, I, n), dtype=torch.uint8, device=dev)
+    ms = _timed(torch, lambda: E.record_pack_batch(jobs, n, H, I, status=status, ws=ws, ctx=ctx), max(args.steps, 10))
+    ctx.check_device()
+    assert int(status.abs().sum()) == 0
+    by = src_bytes + n * (int(L.g) + 12)                        # sources read once, records written once
+    # CPU arm: the same assembly by the oracle port on one host thread, as many experts as fit in 3 s
+    from oracle import oracle as O
+    t0 = time.perf_counter(); m = 0
+    while time.perf_counter() - t0 < 3.0:
+        pr = host[m % distinct]
+        projs = [{"weight": np.zeros((rows, K // 2), np.uint8), "csf_fixed": pr[j][0], "csf_exc": pr[j][1].view(np.uint32), "global": 1e-4}
+                 for j, (rows, K) in enumerate(((I, H), (I, H), (H, I)))]
+        code, _ = O.record_pack(H, I, projs); assert code == 0
+        m += 1
+    cpu_rps = m / (time.perf_counter() - t0)
+    print(json.dumps({"metric": "record_pack_records_per_s", "value": n / ms * 1e3, "unit": "records/s", "n_gpus": 1, "ms_per_step": ms, "data": "synthetic",
+                      "config": {"workload": f"{n} experts, hidden {H}, FFN {I}, NVFP4 with compressed block scales → records; one batch call per step",
+                                 "l2": f"{by / 1e6:.0f} MB read + written per step (larger than L2)"},
+                      "roofline": {"bound": "hbm", "kernel": "record_copy_kernel + csf_*", "achieved": by / ms / 1e6, "peak": peak, "unit": "GB/s",
+                                   "frac": by / ms / 1e6 / peak, "traffic": None},
+                      "cpu_baseline": {"value": cpu_rps, "unit": "records/s", "cores": 1, "kind": "port", "sample": f"{m} experts in 3 s"}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -631,9 +705,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=0, help="run one batch size only (default: 1, 4, 8, 16; headline 16)")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than 48 (development only; the number is then not the benchmark's)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "dense"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "dense", "records"],
                     help="decode = the benchmark proper (BASELINE config 2); prefill = one config-4 MoE layer on the FP4 tensor cores; "
-                         "dense = the config-5 MLP GEMVs (one GPU each; their own JSON line)")
+                         "dense = the config-5 MLP GEMVs; records = record assembly in front of the path (one GPU each; their own JSON line)")
     ap.add_argument("--tokens", type=int, default=8192, help="--workload prefill: tokens per layer call")
     ap.add_argument("--experts", type=int, default=256, help="--workload prefill: routed experts resident (fewer = a smaller case for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -644,6 +718,8 @@ def main():
         run_prefill(args)
     elif args.workload == "dense":
         run_dense(args)
+    elif args.workload == "records":
+        run_records(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -44,6 +44,15 @@ class Plan(C.Structure):
                 ("prefill_tiles", C.c_int), ("tile_fill", C.c_double), ("ws_bytes", C.c_size_t)]
 
 
+class ProjSrc(C.Structure):
+    _fields_ = [("weight", C.c_void_p), ("scale", C.c_void_p), ("csf_fixed", C.c_void_p), ("csf_exc", C.c_void_p), ("csf_fixed_rows", C.c_int64),
+                ("csf_fixed_cols", C.c_int64), ("n_exc", C.c_uint64), ("global_", C.c_float)]
+
+
+class RecordJob(C.Structure):
+    _fields_ = [("src", ProjSrc * 3), ("rec", C.c_void_p)]
+
+
 class KernelStat(C.Structure):
     _fields_ = [("name", C.c_char * 40), ("launches", C.c_uint32), ("total_ms", C.c_float)]
 
@@ -123,6 +132,11 @@ def load() -> C.CDLL:
         "hb_moe_layer": (i, [vp, vp, i, i, i, i, i, i, vp, f, vp, i, vp, i, vp, i, i, f, vp, vp, vp, vp, vp]),
         "hb_dispatch_plan": (i, [vp, i, i, i, i, i, vp, C.POINTER(Plan)]),
         "hb_expert_dequant": (i, [vp, vp, i, i, vp, vp, vp]),
+        "hb_csf_ws_bytes": (sz, [i, i]),
+        "hb_csf_decode": (i, [vp, C.c_int64, C.c_int64, vp, C.c_uint64, i, i, vp, vp, vp, sz, vp]),
+        "hb_record_pack_ws_bytes": (sz, [i, i, i]),
+        "hb_record_pack_batch": (i, [vp, vp, i, i, i, vp, vp, sz, vp]),
+        "hb_record_pack": (i, [vp, C.POINTER(ProjSrc), i, i, vp, vp, vp, sz, vp]),
         "hb_gather_rows": (i, [vp, vp, vp, i, i, vp, vp]),
         "hb_swiglu_rows": (i, [vp, vp, i, i, f, vp, vp]),
         "hb_scatter_add_rows": (i, [vp, vp, vp, vp, i, i, vp, vp]),

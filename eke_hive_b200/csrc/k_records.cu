@@ -1,0 +1,275 @@
+// Expert-record assembly on the device: the step in front of the routed-expert path.  A checkpoint stores an expert as three NVFP4
+// projections (packed e2m1 bytes, e4m3 block scales, one fp32 global each); the kernels read one contiguous record per expert.
+// hb_record_pack builds that record in HBM from device-resident tensors, and decodes block scales that the checkpoint stores
+// compressed ("CSF": per 16 rows, 16 base code bytes + 4-bit deltas, plus a list of exception words) straight into the record —
+// the work of hive::glm::GlmExperts::load_all (engine/src/glm/glm_experts.cpp:216-287) and hive::ckq::csf_decode
+// (engine/src/ckpt_quant.cpp:34-73), which the reference runs on host threads.
+//
+// All of it is byte work bound by HBM: the expansion reads 8·C + 16 bytes and writes 16·C bytes per group of 16 rows, one thread
+// per 8 consecutive scales (one 4-byte load of deltas, one 8-byte store).  The data-dependent invariants the reference checks
+// sequentially are evaluated in parallel and reduced so that the reported violation is the one the sequential decoder meets first:
+// the lowest exception ordinal with its first failing check, else the lowest invalid scale index.  A repeated exception index is
+// resolved like the sequential loop (the last word wins) through a per-scale table of the highest claiming ordinal.
+//
+// A record is 1-2 MB, microseconds of HBM time, so the unit of work is a BATCH of records: the caller hands over a device array of
+// jobs (three projections and a destination each) and every kernel runs once per batch with the job index in blockIdx.y — eight
+// launches however many records, instead of host threads walking the tensors one by one.
+#include <algorithm>
+
+#include "hb_common.cuh"
+
+namespace hb {
+
+struct CsfArgs {
+  const uint8_t* fixed; long long fixed_cols;
+  const uint32_t* exc; uint32_t n_exc;
+  uint32_t C, total;             // columns of the scale matrix, R·C; total == 0: nothing to decode (plain scales, or refused by shape)
+  uint8_t* out;
+  uint32_t* winner;              // [total]: highest exception ordinal + 1 that names the entry (0 = none)
+  uint32_t* keys;                // [0] lowest (exception ordinal · 4 + failing check), [1] lowest invalid scale index; ~0 = none
+  int32_t* status;               // [2]: HB_CSF_* code, position
+  // plain copies of the same job (record assembly): weight bytes, and the scale bytes when they are stored uncompressed
+  const uint8_t* copy_src[2]; uint8_t* copy_dst[2]; unsigned long long copy_n[2];
+};
+
+__device__ __forceinline__ uint32_t csf_delta(const CsfArgs& a, uint32_t i) {
+  const uint32_t per_group = 16u * a.C, g = i / per_group, n = i - g * per_group;
+  return (a.fixed[(size_t)g * a.fixed_cols + 16 + (n >> 1)] >> ((n & 1) * 4)) & 15u;
+}
+
+// code = base[row] + delta; codes above 0x7E are written as 0xFF (not a scale unless an exception replaces them)
+__global__ void __launch_bounds__(256) csf_expand_kernel(const CsfArgs* __restrict__ jobs) {
+  const CsfArgs a = jobs[blockIdx.y];
+  const uint32_t per_group = 16u * a.C, units = a.total / 8;
+  for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < units; t += gridDim.x * blockDim.x) {
+    const uint32_t i = t * 8, g = i / per_group, n = i - g * per_group;
+    const uint8_t* grp = a.fixed + (size_t)g * a.fixed_cols;
+    const uint32_t d8 = *reinterpret_cast<const uint32_t*>(grp + 16 + (n >> 1));      // 8 deltas; 4-byte aligned: the group pitch and n/2 are multiples of 4
+    uint32_t r = n / a.C, c = n - r * a.C, base = grp[r];
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t code = base + ((d8 >> (4 * j)) & 15u);
+      w[j >> 2] |= (code > 0x7Eu ? 0xFFu : code) << (8 * (j & 3));
+      if (++c == a.C && j < 7) { c = 0; ++r; base = grp[r]; }                         // n + 8 ≤ 16·C: r stays below 16 while j < 7
+    }
+    *reinterpret_cast<uint2*>(a.out + i) = make_uint2(w[0], w[1]);
+  }
+}
+
+// per exception: the checks of the sequential decoder in its order (index range, stored delta is 0, value is a finite non-negative
+// e4m3 code), and a claim on the entry
+__global__ void __launch_bounds__(256) csf_claim_kernel(const CsfArgs* __restrict__ jobs) {
+  const CsfArgs a = jobs[blockIdx.y];
+  if (a.total == 0) return;
+  for (uint32_t k = blockIdx.x * blockDim.x + threadIdx.x; k < a.n_exc; k += gridDim.x * blockDim.x) {
+    const uint32_t w = a.exc[k], i = w & 0xFFFFFFu, v = w >> 24;
+    int bad = -1;
+    if (i >= a.total) bad = 0;
+    else {
+      if (csf_delta(a, i) != 0u) bad = 1;
+      else if (v > 0x7Eu) bad = 2;
+      atomicMax(&a.winner[i], k + 1u);
+    }
+    if (bad >= 0) atomicMin(&a.keys[0], k * 4u + (uint32_t)bad);
+  }
+}
+
+__global__ void __launch_bounds__(256) csf_apply_kernel(const CsfArgs* __restrict__ jobs) {
+  const CsfArgs a = jobs[blockIdx.y];
+  if (a.total == 0) return;
+  for (uint32_t k = blockIdx.x * blockDim.x + threadIdx.x; k < a.n_exc; k += gridDim.x * blockDim.x) {
+    const uint32_t w = a.exc[k], i = w & 0xFFFFFFu;
+    if (i < a.total && a.winner[i] == k + 1u) a.out[i] = (uint8_t)(w >> 24);
+  }
+}
+
+// every decoded byte must be ≤ 0x7E: 8 bytes per thread, a byte fails when its top bit is set or its low seven bits are all ones
+__global__ void __launch_bounds__(256) csf_check_kernel(const CsfArgs* __restrict__ jobs) {
+  const CsfArgs a = jobs[blockIdx.y];
+  const uint32_t units = a.total / 8;
+  uint32_t first = 0xFFFFFFFFu;
+  for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < units; t += gridDim.x * blockDim.x) {
+    const uint2 x = *reinterpret_cast<const uint2*>(a.out + (size_t)t * 8);
+    const uint32_t b0 = (x.x | ((x.x & 0x7F7F7F7Fu) + 0x01010101u)) & 0x80808080u;
+    const uint32_t b1 = (x.y | ((x.y & 0x7F7F7F7Fu) + 0x01010101u)) & 0x80808080u;
+    if (b0) first = min(first, t * 8 + (uint32_t)(__ffs((int)b0) - 1) / 8);
+    else if (b1) first = min(first, t * 8 + 4 + (uint32_t)(__ffs((int)b1) - 1) / 8);
+  }
+  if (first != 0xFFFFFFFFu) atomicMin(&a.keys[1], first);
+}
+
+// one thread per job: the verdict.  A job refused by shape keeps the status the preparation wrote.
+__global__ void csf_finish_kernel(const CsfArgs* __restrict__ jobs, int n_jobs) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n_jobs) return;
+  const CsfArgs a = jobs[j];
+  if (a.total == 0) return;
+  const uint32_t ke = a.keys[0], kc = a.keys[1];
+  int32_t code = HB_CSF_OK, where = 0;
+  if (ke != 0xFFFFFFFFu) { code = HB_CSF_EXC_INDEX + (int32_t)(ke & 3u); where = (int32_t)(ke >> 2); }
+  else if (kc != 0xFFFFFFFFu) { code = HB_CSF_CODE; where = (int32_t)kc; }
+  a.status[0] = code; a.status[1] = where;
+}
+
+// weights (and uncompressed scales) into the record: 16 bytes per thread where both sides allow it
+__global__ void __launch_bounds__(256) record_copy_kernel(const CsfArgs* __restrict__ jobs) {
+  const CsfArgs a = jobs[blockIdx.y];
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+#pragma unroll
+  for (int p = 0; p < 2; ++p) {
+    const uint8_t* s = a.copy_src[p];
+    uint8_t* d = a.copy_dst[p];
+    const size_t n = a.copy_n[p];
+    if (n == 0) continue;
+    if (((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d) | n) & 15) == 0) {
+      for (size_t i = tid; i < n / 16; i += nth) reinterpret_cast<uint4*>(d)[i] = __ldg(reinterpret_cast<const uint4*>(s) + i);
+    } else {
+      for (size_t i = tid; i < n; i += nth) d[i] = s[i];
+    }
+  }
+}
+
+struct RecordPrep {
+  const hb_record_job* jobs; int n;
+  int H, I;
+  hb_rec_layout L;
+  CsfArgs* out;                  // [3n]
+  uint32_t* keys;                // [3n][2]
+  uint32_t* winner;              // [3n][H·I/16]
+  int32_t* status;               // [n][3][2]
+};
+
+// one thread per (record, projection): the job descriptor the other kernels read, the shape rules of the format, the record's global
+__global__ void record_prep_kernel(RecordPrep p) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= 3 * p.n) return;
+  const int r = t / 3, j = t - 3 * r;
+  const hb_record_job job = p.jobs[r];
+  const hb_proj_src s = job.src[j];
+  const uint64_t w_off = j == 0 ? p.L.w1 : j == 1 ? p.L.w3 : p.L.w2, s_off = j == 0 ? p.L.s1 : j == 1 ? p.L.s3 : p.L.s2;
+  const int rows = j == 2 ? p.H : p.I, cols = j == 2 ? p.I : p.H, C = cols / 16;
+  const unsigned long long nw = (unsigned long long)rows * cols / 2, ns = nw / 8;
+  CsfArgs a;
+  a.fixed = s.csf_fixed; a.fixed_cols = s.csf_fixed_cols; a.exc = s.csf_exc; a.n_exc = (uint32_t)s.n_exc; a.C = (uint32_t)C; a.total = 0;
+  a.out = job.rec + s_off;
+  a.winner = p.winner + (size_t)t * (size_t)(rows * C);
+  a.keys = p.keys + 2 * t;
+  a.status = p.status + 2 * t;
+  const bool dst_ok = job.rec && !(reinterpret_cast<uintptr_t>(job.rec) & 15);
+  a.copy_src[0] = s.weight; a.copy_dst[0] = job.rec + w_off; a.copy_n[0] = s.weight && dst_ok ? nw : 0;
+  a.copy_src[1] = s.scale; a.copy_dst[1] = job.rec + s_off; a.copy_n[1] = s.scale && dst_ok ? ns : 0;
+  int32_t code = HB_CSF_OK;
+  if (!s.weight || (!s.scale && !s.csf_fixed) || !job.rec || (reinterpret_cast<uintptr_t>(job.rec) & 15)) code = HB_CSF_MISSING;
+  else if (!s.scale) {
+    if (s.csf_fixed_rows != rows / 16 || s.csf_fixed_cols != 16 + 8 * (long long)C) code = HB_CSF_SHAPE;
+    else if (s.n_exc >= (1ull << 30) || (s.n_exc && !s.csf_exc) || (reinterpret_cast<uintptr_t>(s.csf_fixed) & 3) || (reinterpret_cast<uintptr_t>(s.csf_exc) & 3))
+      code = HB_CSF_MISSING;
+    else a.total = (uint32_t)(rows * C);
+  }
+  a.keys[0] = 0xFFFFFFFFu; a.keys[1] = 0xFFFFFFFFu;
+  a.status[0] = code; a.status[1] = 0;
+  p.out[t] = a;
+  if (dst_ok) reinterpret_cast<float*>(job.rec + p.L.g)[j] = s.global;
+}
+
+static size_t csf_ws_bytes(long long total, long long jobs) {
+  return hb_align256((size_t)jobs * sizeof(CsfArgs)) + hb_align256((size_t)jobs * 8) + hb_align256((size_t)jobs * (size_t)total * 4);
+}
+
+struct CsfWs { CsfArgs* jobs; uint32_t* keys; uint32_t* winner; size_t winner_bytes; };
+static CsfWs csf_carve(void* ws, long long total, long long jobs) {
+  uint8_t* p = static_cast<uint8_t*>(ws);
+  CsfWs w;
+  w.jobs = reinterpret_cast<CsfArgs*>(p); p += hb_align256((size_t)jobs * sizeof(CsfArgs));
+  w.keys = reinterpret_cast<uint32_t*>(p); p += hb_align256((size_t)jobs * 8);
+  w.winner = reinterpret_cast<uint32_t*>(p); w.winner_bytes = (size_t)jobs * (size_t)total * 4;
+  return w;
+}
+
+// expansion, exceptions, validation and verdict of n_jobs prepared jobs (the winner tables are zeroed here)
+static int csf_launch(hb_ctx* ctx, const CsfWs& w, int n_jobs, long long total, bool copies, cudaStream_t st) {
+  HB_CUDA(ctx, cudaMemsetAsync(w.winner, 0, w.winner_bytes, st));
+  const unsigned bx = (unsigned)std::max<long long>(1, std::min<long long>((total / 8 + 255) / 256, std::max(1, ctx->sm_count * 8 / n_jobs)));
+  const dim3 grid(bx, (unsigned)n_jobs), blk(256);
+  int r;
+  if (copies && (r = hb_launch(ctx, "record_copy", false, record_copy_kernel, dim3(std::max(bx, 16u), (unsigned)n_jobs), blk, 0, st,
+                               static_cast<const CsfArgs*>(w.jobs)))) return r;
+  if ((r = hb_launch(ctx, "csf_expand", false, csf_expand_kernel, grid, blk, 0, st, static_cast<const CsfArgs*>(w.jobs)))) return r;
+  if ((r = hb_launch(ctx, "csf_claim", false, csf_claim_kernel, grid, blk, 0, st, static_cast<const CsfArgs*>(w.jobs)))) return r;
+  if ((r = hb_launch(ctx, "csf_apply", false, csf_apply_kernel, grid, blk, 0, st, static_cast<const CsfArgs*>(w.jobs)))) return r;
+  if ((r = hb_launch(ctx, "csf_check", false, csf_check_kernel, grid, blk, 0, st, static_cast<const CsfArgs*>(w.jobs)))) return r;
+  return hb_launch(ctx, "csf_finish", false, csf_finish_kernel, dim3((unsigned)(n_jobs + 127) / 128), dim3(128), 0, st,
+                   static_cast<const CsfArgs*>(w.jobs), n_jobs);
+}
+
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" {
+
+size_t hb_csf_ws_bytes(int R, int C) { return R > 0 && C > 0 ? csf_ws_bytes((long long)R * C, 1) : 0; }
+
+int hb_csf_decode(hb_ctx* ctx, const uint8_t* fixed, int64_t fixed_rows, int64_t fixed_cols, const uint32_t* exc, uint64_t n_exc, int R, int C,
+                  uint8_t* out, int32_t* status, void* ws, size_t ws_bytes, void* stream) {
+  if (!ctx) return HB_ERR_INVALID;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // shape rules of the format: refused before any launch
+  HB_REQUIRE(ctx, R > 0 && C > 0 && R % 16 == 0, HB_ERR_INVALID, "CSF: rows not a multiple of 16 (R=%d C=%d)", R, C);
+  HB_REQUIRE(ctx, fixed_rows == R / 16 && fixed_cols == 16 + 8 * (long long)C, HB_ERR_INVALID, "CSF: fixed shape [%lld, %lld] for scales [%d, %d]",
+             (long long)fixed_rows, (long long)fixed_cols, R, C);
+  const long long total = (long long)R * C;
+  HB_REQUIRE(ctx, total <= (1ll << 24), HB_ERR_INVALID, "CSF: more scales than a 24-bit index addresses");
+  HB_REQUIRE(ctx, n_exc < (1ull << 30), HB_ERR_UNSUPPORTED, "CSF: %llu exception words (limit 2^30)", (unsigned long long)n_exc);
+  HB_REQUIRE(ctx, fixed && out && status && (n_exc == 0 || exc), HB_ERR_INVALID, "CSF: NULL tensor");
+  HB_REQUIRE(ctx, hb_aligned(fixed, 4) && hb_aligned(exc, 4) && hb_aligned(out, 8) && hb_aligned(status, 4), HB_ERR_INVALID,
+             "CSF: fixed / exceptions / status 4-byte, out 8-byte aligned");
+  HB_REQUIRE(ctx, ws && hb_aligned(ws, 256) && ws_bytes >= csf_ws_bytes(total, 1), HB_ERR_WORKSPACE, "CSF: workspace of %zu bytes, 256-byte aligned",
+             csf_ws_bytes(total, 1));
+  const CsfWs w = csf_carve(ws, total, 1);
+  CsfArgs a = {};
+  a.fixed = fixed; a.fixed_cols = fixed_cols; a.exc = exc; a.n_exc = (uint32_t)n_exc; a.C = (uint32_t)C; a.total = (uint32_t)total; a.out = out;
+  a.winner = w.winner; a.keys = w.keys; a.status = status;
+  HB_CUDA(ctx, cudaMemcpyAsync(w.jobs, &a, sizeof a, cudaMemcpyHostToDevice, st));      // pageable source: staged before the call returns
+  HB_CUDA(ctx, cudaMemsetAsync(w.keys, 0xFF, 8, st));
+  return csf_launch(ctx, w, 1, total, false, st);
+}
+
+size_t hb_record_pack_ws_bytes(int H, int I, int n) {
+  return H > 0 && I > 0 && n > 0 ? hb_align256((size_t)n * sizeof(hb_record_job)) + csf_ws_bytes((long long)H * I / 16, 3ll * n) : 0;
+}
+
+int hb_record_pack_batch(hb_ctx* ctx, const hb_record_job* jobs, int n, int H, int I, int32_t* status, void* ws, size_t ws_bytes, void* stream) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (n == 0) return HB_OK;
+  HB_REQUIRE(ctx, jobs && status && n > 0, HB_ERR_INVALID, "record_pack: NULL argument or negative count");
+  hb_rec_layout L;
+  HB_REQUIRE(ctx, hb_rec_layout_make(H, I, &L) == HB_OK && H % 16 == 0 && I % 16 == 0, HB_ERR_UNSUPPORTED, "record_pack: H=%d I=%d", H, I);
+  const long long total = (long long)H * I / 16;
+  HB_REQUIRE(ctx, total <= (1ll << 24), HB_ERR_UNSUPPORTED, "record_pack: more scales per projection than a 24-bit index addresses");
+  HB_REQUIRE(ctx, hb_aligned(jobs, 8) && hb_aligned(status, 4), HB_ERR_INVALID, "record_pack: jobs 8-byte, status 4-byte aligned");
+  HB_REQUIRE(ctx, ws && hb_aligned(ws, 256) && ws_bytes >= hb_record_pack_ws_bytes(H, I, n), HB_ERR_WORKSPACE,
+             "record_pack: workspace of %zu bytes, 256-byte aligned", hb_record_pack_ws_bytes(H, I, n));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const CsfWs w = csf_carve(static_cast<uint8_t*>(ws) + hb_align256((size_t)n * sizeof(hb_record_job)), total, 3ll * n);
+  RecordPrep p;
+  p.jobs = jobs; p.n = n; p.H = H; p.I = I; p.L = L; p.out = w.jobs; p.keys = w.keys; p.winner = w.winner; p.status = status;
+  int r = hb_launch(ctx, "record_prep", false, record_prep_kernel, dim3((unsigned)(3 * n + 127) / 128), dim3(128), 0, st, p);
+  if (r) return r;
+  return csf_launch(ctx, w, 3 * n, total, true, st);
+}
+
+int hb_record_pack(hb_ctx* ctx, const hb_proj_src* src, int H, int I, uint8_t* rec, int32_t* status, void* ws, size_t ws_bytes, void* stream) {
+  if (!ctx) return HB_ERR_INVALID;
+  HB_REQUIRE(ctx, src && rec && status, HB_ERR_INVALID, "record_pack: NULL argument");
+  HB_REQUIRE(ctx, ws && hb_aligned(ws, 256) && ws_bytes >= hb_record_pack_ws_bytes(H, I, 1), HB_ERR_WORKSPACE,
+             "record_pack: workspace of %zu bytes, 256-byte aligned", hb_record_pack_ws_bytes(H, I, 1));
+  hb_record_job job;
+  for (int j = 0; j < 3; ++j) job.src[j] = src[j];
+  job.rec = rec;
+  HB_CUDA(ctx, cudaMemcpyAsync(ws, &job, sizeof job, cudaMemcpyHostToDevice, reinterpret_cast<cudaStream_t>(stream)));   // pageable: staged before return
+  return hb_record_pack_batch(ctx, static_cast<const hb_record_job*>(ws), 1, H, I, status, ws, ws_bytes, stream);
+}
+
+}  // extern "C"

@@ -17,7 +17,7 @@ from ._lib import Config, HbError, MoePair, PfCombine, RecLayout
 
 __all__ = ["Context", "context", "ExpertRecLayout", "nvfp4_dequant", "nvfp4_gemv", "nvfp4_quantize", "a4_quant", "router_softmax_topk",
            "router_topk", "build_moe_pairs", "moe_combine", "moe_decode_ws_bytes", "moe_decode", "fn_moe_decode_routed", "fn_moe_decode_routed_static", "static_max_pairs", "moe_decode_routed_f32", "moe_layer_decode",
-           "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "dispatch_plan", "moe_layer", "moe_layer_ws_bytes", "PeerExchange", "moe_decode_ep_local", "moe_prefill_supported", "moe_prefill_ws_bytes", "fn_moe_prefill", "nvfp4_gemm_a4", "fp4_peak_probe", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "expert_dequant", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
+           "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "dispatch_plan", "moe_layer", "moe_layer_ws_bytes", "PeerExchange", "moe_decode_ep_local", "moe_prefill_supported", "moe_prefill_ws_bytes", "fn_moe_prefill", "nvfp4_gemm_a4", "fp4_peak_probe", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "expert_dequant", "csf_decode", "record_pack", "record_pack_ws_bytes", "record_jobs", "record_pack_batch", "CSF_OK", "CSF_EXC_INDEX", "CSF_EXC_DELTA", "CSF_EXC_VALUE", "CSF_CODE", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
 
 
 def _L():
@@ -519,6 +519,80 @@ def expert_dequant(rec, H: int, I: int, gu=None, d=None, ctx: Context | None = N
     d = torch.empty((H, I), dtype=torch.bfloat16, device=rec.device) if d is None else d
     ctx.check(_L().hb_expert_dequant(ctx.handle, _p(rec), H, I, _p(gu), _p(d), _stream()))
     return gu, d
+
+
+CSF_OK, CSF_EXC_INDEX, CSF_EXC_DELTA, CSF_EXC_VALUE, CSF_CODE = 0, 4, 5, 6, 7
+
+
+def csf_decode(fixed, exc, R: int, Cc: int, out=None, status=None, ws=None, fixed_shape=None, ctx: Context | None = None):
+    """hive::ckq::csf_decode on the device: compressed NVFP4 block scales (fixed u8 [R/16, 16 + 8C], exc u32-as-int32 [n]) → u8 [R, C].
+    Returns (out, status int32[2] on the device: {CSF_* code, position}); raises HiveError for shapes the format rules out."""
+    ctx = ctx or context()
+    dev = fixed.device
+    fr, fc = fixed_shape if fixed_shape is not None else tuple(fixed.shape)
+    out = torch.empty((max(R, 0), max(Cc, 0)), dtype=torch.uint8, device=dev) if out is None else out
+    status = torch.full((2,), -1, dtype=torch.int32, device=dev) if status is None else status
+    nws = _L().hb_csf_ws_bytes(R, Cc)
+    ws = torch.empty(max(nws, 256), dtype=torch.uint8, device=dev) if ws is None else ws
+    n = 0 if exc is None else exc.numel()
+    ctx.check(_L().hb_csf_decode(ctx.handle, _p(fixed), fr, fc, _p(exc) if n else None, n, R, Cc, _p(out), _p(status), _p(ws), ws.numel(), _stream()))
+    return out, status
+
+
+def record_pack_ws_bytes(H: int, I: int, n: int = 1) -> int:
+    return _L().hb_record_pack_ws_bytes(H, I, n)
+
+
+def _fill_proj(dst, p):
+    dst.weight = _p(p["weight"])
+    dst.global_ = float(p["global"])
+    if p.get("scale") is not None:
+        dst.scale = _p(p["scale"])
+    else:
+        f, e = p["csf_fixed"], p["csf_exc"]
+        dst.csf_fixed = _p(f)
+        dst.csf_fixed_rows, dst.csf_fixed_cols = (f.shape if f.dim() == 2 else (-1, -1))
+        dst.n_exc = e.numel()
+        dst.csf_exc = _p(e) if e.numel() else None
+
+
+def record_pack(projs, H: int, I: int, rec=None, status=None, ws=None, ctx: Context | None = None):
+    """GlmExperts::load_all for one expert on the device.  projs = (gate, up, down), each a dict with 'weight' u8 [rows, K/2], 'global'
+    float and either 'scale' u8 [rows, K/16] or the compressed pair 'csf_fixed' u8 [rows/16, 16 + K/2] + 'csf_exc' (32-bit words).
+    Returns (rec u8 [layout.total], status int32 [3, 2] on the device)."""
+    ctx = ctx or context()
+    dev = projs[0]["weight"].device
+    rec = torch.zeros(int(ExpertRecLayout(H, I).total), dtype=torch.uint8, device=dev) if rec is None else rec
+    status = torch.full((3, 2), -1, dtype=torch.int32, device=dev) if status is None else status
+    ws = torch.empty(max(record_pack_ws_bytes(H, I), 256), dtype=torch.uint8, device=dev) if ws is None else ws
+    src = (_lib.ProjSrc * 3)()
+    for j, p in enumerate(projs):
+        _fill_proj(src[j], p)
+    ctx.check(_L().hb_record_pack(ctx.handle, src, H, I, _p(rec), _p(status), _p(ws), ws.numel(), _stream()))
+    return rec, status
+
+
+def record_jobs(experts, recs):
+    """Device array of hb_record_job for experts = [(gate, up, down) dicts as in record_pack], recs = u8 [n, layout.total] (or a list
+    of record tensors).  Keep the returned tensor and the sources alive until the packing has run."""
+    n = len(experts)
+    jobs = (_lib.RecordJob * n)()
+    for r, projs in enumerate(experts):
+        for j, p in enumerate(projs):
+            _fill_proj(jobs[r].src[j], p)
+        jobs[r].rec = _p(recs[r])
+    host = torch.frombuffer(bytearray(bytes(jobs)), dtype=torch.uint8)
+    return host.to(recs[0].device)
+
+
+def record_pack_batch(jobs, n: int, H: int, I: int, status=None, ws=None, ctx: Context | None = None):
+    """hb_record_pack_batch: jobs = device tensor from record_jobs.  Returns status int32 [n, 3, 2] on the device."""
+    ctx = ctx or context()
+    dev = jobs.device
+    status = torch.full((n, 3, 2), -1, dtype=torch.int32, device=dev) if status is None else status
+    ws = torch.empty(max(record_pack_ws_bytes(H, I, n), 256), dtype=torch.uint8, device=dev) if ws is None else ws
+    ctx.check(_L().hb_record_pack_batch(ctx.handle, _p(jobs), n, H, I, _p(status), _p(ws), ws.numel(), _stream()))
+    return status
 
 
 def gather_rows(x, rows, out=None, ctx: Context | None = None):

@@ -292,6 +292,48 @@ typedef struct hb_plan {
 } hb_plan;
 HB_API int hb_dispatch_plan(const int32_t* ids_host, int M, int K, int E, int H, int I, int* counts, hb_plan* plan);
 
+/* ---- record assembly: the step in front of the path (engine/src/glm/glm_experts.cpp:216-287, engine/include/hive/ckpt_quant.h:5-37) ----
+ * hive::ckq::csf_decode on the device.  The e4m3 block-scale matrix [R, C] (C = K / 16) of a projection, stored compressed as
+ * fixed u8 [R / 16, 16 + 8·C] (per 16 rows: 16 base code bytes, then 16·C 4-bit deltas row-major, even position = low nibble;
+ * code = base + delta) and exception words u32 [n_exc] (code << 24 | flat index r·C + c; the stored delta there is 0), is expanded
+ * into out [R, C].  A shape the format rules out (R % 16, the fixed shape, more than 2^24 scales) is refused on the host with
+ * HB_ERR_INVALID, like the reference's `false`.  The data-dependent invariants are checked on the device; status (device int32[2])
+ * receives {HB_CSF_* code, position} of the violation the reference's sequential decoder meets first (position = exception
+ * ordinal for the exception checks, flat scale index for HB_CSF_CODE), {0, 0} when the tensor is sound.  out is unspecified
+ * unless status[0] == 0.  All pointers are device-accessible; the call enqueues on `stream` and does not synchronise. */
+enum { HB_CSF_OK = 0, HB_CSF_SHAPE = 2 /* record assembly only: the fixed tensor's shape does not fit the projection */, HB_CSF_EXC_INDEX = 4,
+       HB_CSF_EXC_DELTA = 5, HB_CSF_EXC_VALUE = 6, HB_CSF_CODE = 7, HB_CSF_MISSING = 8 /* record assembly only: a NULL or misaligned tensor */ };
+HB_API size_t hb_csf_ws_bytes(int R, int C);
+HB_API int hb_csf_decode(hb_ctx* ctx, const uint8_t* fixed, int64_t fixed_rows, int64_t fixed_cols, const uint32_t* exc, uint64_t n_exc, int R, int C,
+                         uint8_t* out, int32_t* status, void* ws, size_t ws_bytes, void* stream);
+/* One projection of an expert as the checkpoint holds it: packed e2m1 bytes [rows, K/2], the fp32 global (`weight_scale_2`), and
+ * either plain e4m3 scales [rows, K/16] or, with scale == NULL, the compressed pair. */
+typedef struct hb_proj_src {
+  const uint8_t* weight;
+  const uint8_t* scale;
+  const uint8_t* csf_fixed;
+  const uint32_t* csf_exc;
+  int64_t csf_fixed_rows, csf_fixed_cols;
+  uint64_t n_exc;
+  float global;
+} hb_proj_src;
+/* One expert: its three projections (gate, up, down) and where its record goes (16-byte aligned, hb_rec_layout(H, I).total bytes). */
+typedef struct hb_record_job {
+  hb_proj_src src[3];
+  uint8_t* rec;
+} hb_record_job;
+/* GlmExperts::load_all on the device, for a batch of n experts in one go: jobs = DEVICE-accessible array [n]; every kernel of the
+ * call runs once for the whole batch (job index in the grid), so a batch costs nine launches however many records it holds.
+ * Weights are copied, scales copied or CSF-decoded straight into each record, the three globals written as g1 g3 g2; the bytes
+ * after the globals up to `total` are left as they are.  status = device int32 [n][3][2]: one {HB_CSF_* code, position} per
+ * projection ({0, 0} = sound; HB_CSF_SHAPE / HB_CSF_MISSING for what the reference's loader refuses by shape or dtype; a refused
+ * projection's scales are not written).  The reference aborts the load on the first violation; here the caller reads status
+ * once per batch and decides.  Sources 16-byte aligned copy with 16-byte accesses, others byte by byte.
+ * hb_record_pack is the same for one expert with the descriptor in host memory. */
+HB_API size_t hb_record_pack_ws_bytes(int H, int I, int n);
+HB_API int hb_record_pack_batch(hb_ctx* ctx, const hb_record_job* jobs, int n, int H, int I, int32_t* status, void* ws, size_t ws_bytes, void* stream);
+HB_API int hb_record_pack(hb_ctx* ctx, const hb_proj_src* src, int H, int I, uint8_t* rec, int32_t* status, void* ws, size_t ws_bytes, void* stream);
+
 /* ---- prefill helpers kept for callers that compose (engine/include/hive/glm/glm_moe.h:33-41) ---- */
 /* hive::glm::expert_dequant — engine/include/hive/glm/glm_moe.h:32-33: one expert record → bf16 gu [2I, H] (gate rows then up rows) and
  * d [H, I].  The record's globals are read on the device: unlike the reference (engine/src/glm/glm_moe.cu:608-616) the call does not

@@ -503,3 +503,56 @@ void ho_dense_act(const float* g, const float* u, int n, float* act) {
     act[i] = ho_bf16r(ho_bf16r(gv / (1.f + expf(-gv))) * uv);
   }
 }
+
+/* ================================================================================================ record assembly
+ * Compressed block scales, engine/src/ckpt_quant.cpp:34-73.  Position n of a group = 16 rows x C columns row-major; delta n sits in
+ * body[n / 2], low nibble when n is even. */
+static int csf_delta(const uint8_t* grp, size_t n) { return (grp[16 + (n >> 1)] >> ((n & 1) * 4)) & 15; }
+
+int ho_csf_decode(const uint8_t* fixed, int64_t fixed_rows, int64_t fixed_cols, const uint32_t* exc, size_t n_exc, int R, int C, uint8_t* out,
+                  int64_t* where) {
+  if (where) *where = 0;
+  if (R <= 0 || C <= 0 || R % 16 != 0) return HO_CSF_ROWS;
+  if (fixed_rows != R / 16 || fixed_cols != 16 + 8 * (int64_t)C) return HO_CSF_SHAPE;
+  const int64_t total = (int64_t)R * C, per_group = 16 * (int64_t)C;
+  if (total > ((int64_t)1 << 24)) return HO_CSF_TOO_MANY;
+  for (int64_t i = 0; i < total; ++i) {                   /* flat index i = group * 16C + position inside the group */
+    const uint8_t* grp = fixed + (size_t)(i / per_group) * (size_t)fixed_cols;
+    const int64_t n = i % per_group;
+    const int code = grp[n / C] + csf_delta(grp, (size_t)n);
+    out[i] = code > 0x7E ? 0xFF : (uint8_t)code;         /* 0xFF = not a scale unless an exception replaces it */
+  }
+  for (size_t k = 0; k < n_exc; ++k) {
+    const int64_t i = exc[k] & 0xFFFFFF;
+    const unsigned v = exc[k] >> 24;
+    if (where) *where = (int64_t)k;
+    if (i >= total) return HO_CSF_EXC_INDEX;
+    if (csf_delta(fixed + (size_t)(i / per_group) * (size_t)fixed_cols, (size_t)(i % per_group)) != 0) return HO_CSF_EXC_DELTA;
+    if (v > 0x7E) return HO_CSF_EXC_VALUE;
+    out[i] = (uint8_t)v;                                  /* a later exception for the same index wins */
+  }
+  for (int64_t i = 0; i < total; ++i)
+    if (out[i] > 0x7E) { if (where) *where = i; return HO_CSF_CODE; }
+  if (where) *where = 0;
+  return HO_CSF_OK;
+}
+
+int ho_record_pack(const uint64_t* off, int H, int I, const uint8_t* const weight[3], const uint8_t* const scale[3],
+                   const uint8_t* const csf_fixed[3], const uint32_t* const csf_exc[3], const size_t n_exc[3], const float global[3],
+                   uint8_t* rec) {
+  const uint64_t w_off[3] = {off[0], off[2], off[4]}, s_off[3] = {off[1], off[3], off[5]};
+  const int rows[3] = {I, I, H}, cols[3] = {H, H, I};
+  for (int j = 0; j < 3; ++j) {
+    const size_t nw = (size_t)rows[j] * cols[j] / 2, ns = (size_t)rows[j] * cols[j] / 16;
+    memcpy(rec + w_off[j], weight[j], nw);
+    if (scale[j]) memcpy(rec + s_off[j], scale[j], ns);
+    else {
+      const int C = cols[j] / 16;
+      const int r = ho_csf_decode(csf_fixed[j], rows[j] / 16, 16 + 8 * (int64_t)C, csf_exc[j], n_exc[j], rows[j], C, rec + s_off[j], NULL);
+      if (r) return 10 * (j + 1) + r;
+    }
+    memcpy(rec + off[6] + 4 * j, &global[j], 4);
+  }
+  return 0;
+}
+

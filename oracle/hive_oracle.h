@@ -90,6 +90,23 @@ void ho_lb_gemv(const uint8_t* q, const uint16_t* s, const uint16_t* zp, int bit
 /* engine/src/q27/q27_kernels.cu:258-289 (gemv_gu): act[i] = bf16( bf16(silu(bf16 g)) · bf16 u ), silu through libm expf */
 void ho_dense_act(const float* g, const float* u, int n, float* act);
 
+/* ---- record assembly: compressed NVFP4 block scales ("CSF") ----
+ * engine/include/hive/ckpt_quant.h:5-17 (format), engine/src/ckpt_quant.cpp:34-73 (csf_decode).  The e4m3 scale matrix [R, C] is
+ * stored per group of 16 rows as 16 base code bytes + 16*C 4-bit deltas (row-major inside the group, even position = low nibble),
+ * code = base + delta; each exception word (code << 24 | flat index) replaces one entry whose stored delta must be 0.
+ * Returns 0 and fills out [R, C], or the number of the first violated invariant in the reference's order of checks
+ * (HO_CSF_*; *where = exception ordinal for the exception checks, flat scale index for HO_CSF_CODE). */
+enum { HO_CSF_OK = 0, HO_CSF_ROWS = 1, HO_CSF_SHAPE = 2, HO_CSF_TOO_MANY = 3, HO_CSF_EXC_INDEX = 4, HO_CSF_EXC_DELTA = 5, HO_CSF_EXC_VALUE = 6,
+       HO_CSF_CODE = 7 };
+int ho_csf_decode(const uint8_t* fixed, int64_t fixed_rows, int64_t fixed_cols, const uint32_t* exc, size_t n_exc, int R, int C, uint8_t* out,
+                  int64_t* where);
+/* engine/src/glm/glm_experts.cpp:216-287 (GlmExperts::load_all, one record): weights copied, scales copied or CSF-decoded straight
+ * into the record, the three globals written as g1 g3 g2.  proj order: gate, up, down.  scale[j] == NULL selects the CSF pair.
+ * Returns 0 or 10*(j+1) + HO_CSF_* of the first failing projection. */
+int ho_record_pack(const uint64_t* off, int H, int I, const uint8_t* const weight[3], const uint8_t* const scale[3],
+                   const uint8_t* const csf_fixed[3], const uint32_t* const csf_exc[3], const size_t n_exc[3], const float global[3],
+                   uint8_t* rec);
+
 #ifdef __cplusplus
 }
 #endif

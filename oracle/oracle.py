@@ -79,6 +79,8 @@ def ref():
         R.ref_layer_create.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p), _u64p]
         R.ref_layer_destroy.argtypes = [C.c_void_p]
         R.ref_layer_routed.argtypes = [C.c_void_p, C.c_int, C.c_int, _i32p, _f32p, _f32p, C.c_float, _f32p]
+        R.ref_csf_decode.restype = C.c_int
+        R.ref_csf_decode.argtypes = [_u8p, C.c_int64, C.c_int64, C.POINTER(C.c_uint32), C.c_size_t, C.c_int, C.c_int, _u8p, C.c_char_p, C.c_int]
         _REF = R
     return _REF
 
@@ -320,3 +322,67 @@ def dense_act(g: np.ndarray, u: np.ndarray) -> np.ndarray:
     out = np.zeros_like(g)
     _C.ho_dense_act(_ptr(g.reshape(-1), _f32p), _ptr(u.reshape(-1), _f32p), g.size, _ptr(out.reshape(-1), _f32p))
     return out
+
+
+# ---------------------------------------------------------------------------------------------------- record assembly (compressed block scales)
+CSF_OK, CSF_ROWS, CSF_SHAPE, CSF_TOO_MANY, CSF_EXC_INDEX, CSF_EXC_DELTA, CSF_EXC_VALUE, CSF_CODE = range(8)
+_u32p = C.POINTER(C.c_uint32)
+
+
+def csf_encode(scales: np.ndarray):
+    """Test-side encoder written from the format description (engine/include/hive/ckpt_quant.h:5-17): base = the row's smallest code,
+    entries more than 15 above it become exceptions with delta 0.  scales u8 [R, C], R % 16 == 0 → (fixed u8 [R/16, 16 + 8C], exc u32 [n])."""
+    s = np.ascontiguousarray(scales, dtype=np.uint8)
+    R, Cc = s.shape
+    base = s.min(axis=1)
+    d = s.astype(np.int32) - base[:, None]
+    flat = np.flatnonzero(d.reshape(-1) > 15)
+    exc = ((s.reshape(-1)[flat].astype(np.uint32) << 24) | flat.astype(np.uint32)).astype(np.uint32)
+    d[d > 15] = 0
+    nib = d.reshape(R // 16, 16 * Cc).astype(np.uint8)             # position n inside the group = r * C + c
+    fixed = np.zeros((R // 16, 16 + 8 * Cc), dtype=np.uint8)
+    fixed[:, :16] = base.reshape(R // 16, 16)
+    fixed[:, 16:] = nib[:, 0::2] | (nib[:, 1::2] << 4)
+    return fixed, exc
+
+
+def csf_decode(fixed: np.ndarray, exc: np.ndarray, R: int, Cc: int, fixed_shape=None, use_ref: bool = False):
+    """→ (status, where, scales u8 [R, C]).  use_ref: the compiled reference decoder (status 0 / -1 only, where = its message)."""
+    fixed = np.ascontiguousarray(fixed, dtype=np.uint8); exc = np.ascontiguousarray(exc, dtype=np.uint32)
+    fr, fc = fixed_shape if fixed_shape is not None else fixed.shape
+    out = np.zeros((max(R, 0), max(Cc, 0)), dtype=np.uint8)
+    ex = exc if exc.size else np.zeros(1, np.uint32)
+    if use_ref:
+        msg = C.create_string_buffer(256)
+        ok = ref().ref_csf_decode(_ptr(fixed, _u8p), fr, fc, _ptr(ex, _u32p), exc.size, R, Cc, _ptr(out, _u8p), msg, 256)
+        return (0 if ok else -1), msg.value.decode(), out
+    where = C.c_int64(0)
+    _C.ho_csf_decode.restype = C.c_int
+    _C.ho_csf_decode.argtypes = [_u8p, C.c_int64, C.c_int64, _u32p, C.c_size_t, C.c_int, C.c_int, _u8p, C.POINTER(C.c_int64)]
+    st = _C.ho_csf_decode(_ptr(fixed, _u8p), fr, fc, _ptr(ex, _u32p), exc.size, R, Cc, _ptr(out, _u8p), C.byref(where))
+    return st, int(where.value), out
+
+
+def record_pack(H: int, I: int, projs) -> tuple[int, np.ndarray]:
+    """projs = three dicts (gate, up, down) with 'weight' u8 [rows, K/2], 'global' float and either 'scale' u8 [rows, K/16] or
+    'csf_fixed' + 'csf_exc'.  → (status, record bytes)."""
+    off = rec_layout(H, I)
+    rec = np.zeros(int(off[7]), dtype=np.uint8)
+    keep = []
+    def arr(a, dt):
+        a = np.ascontiguousarray(a, dtype=dt); keep.append(a); return a
+    W = (C.c_void_p * 3)(); S = (C.c_void_p * 3)(); F = (C.c_void_p * 3)(); X = (C.c_void_p * 3)(); N = (C.c_size_t * 3)(); G = (C.c_float * 3)()
+    for j, p in enumerate(projs):
+        W[j] = arr(p["weight"], np.uint8).ctypes.data
+        S[j] = arr(p["scale"], np.uint8).ctypes.data if p.get("scale") is not None else None
+        if p.get("scale") is None:
+            F[j] = arr(p["csf_fixed"], np.uint8).ctypes.data
+            e = arr(p["csf_exc"], np.uint32)
+            N[j] = e.size
+            X[j] = (e if e.size else arr(np.zeros(1), np.uint32)).ctypes.data
+        G[j] = float(p["global"])
+    _C.ho_record_pack.restype = C.c_int
+    _C.ho_record_pack.argtypes = [_u64p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, _u8p]
+    st = _C.ho_record_pack(_ptr(off, _u64p), H, I, W, S, F, X, N, G, _ptr(rec, _u8p))
+    return st, rec
+

@@ -11,6 +11,7 @@
 //   engine/include/hive/cpu/cpu_backend.h:23-108    Pool, make_mat, matmul_multi, bf16r
 //   engine/src/qwen/cpu/qwen_cpu_simd.h:17-41,153-165  portable exp / sigmoid / silu, silu_mul
 //   engine/src/qwen/cpu/qwen_cpu_engine.cpp:655-783 order of operations of the CPU MoE layer (followed by ref_moe_layer_*)
+//   engine/include/hive/ckpt_quant.h:35-37          csf_decode (compressed NVFP4 block scales of a checkpoint projection)
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -18,6 +19,9 @@
 #include <algorithm>
 #include <vector>
 
+#include <string>
+
+#include "hive/ckpt_quant.h"
 #include "hive/common.h"
 #include "hive/cpu/cpu_backend.h"
 #include "hive/expert_cpu.h"
@@ -169,4 +173,13 @@ void ref_layer_routed(void* p, int M, int K, const int32_t* ids, const float* wt
     }
 }
 
-}  // extern "C"
+// 1 = decoded, 0 = refused (the reference's message is copied into err, NUL-terminated, when err_len > 0)
+int ref_csf_decode(const uint8_t* fixed, int64_t fixed_rows, int64_t fixed_cols, const uint32_t* exc, size_t n_exc, int R, int C, uint8_t* out,
+                   char* err, int err_len) {
+  std::string e;
+  const bool ok = hive::ckq::csf_decode(fixed, fixed_rows, fixed_cols, exc, n_exc, R, C, out, &e);
+  if (err && err_len > 0) { std::strncpy(err, e.c_str(), (size_t)err_len - 1); err[err_len - 1] = 0; }
+  return ok ? 1 : 0;
+}
+
+}

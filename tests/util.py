@@ -52,3 +52,30 @@ def rel_rms_err(got, ref):
     got = np.asarray(got, np.float64); ref = np.asarray(ref, np.float64)
     rms = np.sqrt(np.mean(ref ** 2, axis=-1)) + 1e-30
     return float(np.max(np.max(np.abs(got - ref), axis=-1) / rms))
+
+
+# ---- compressed block scales: inputs of the record-assembly tests and of tests/golden/make_csf_golden.py
+CSF_SHAPES = [(640, 160), (2560, 40), (16, 1), (32, 3)]
+
+
+def csf_scale_matrix(rng, R, C):
+    """codes around one level per matrix with a 2 % tail of outliers, all ≤ 0x7E (the distribution the reference's test draws)"""
+    s = 40 + rng.integers(0, 12, (R, C)) + np.where(rng.integers(0, 50, (R, C)) == 0, rng.integers(0, 70, (R, C)), 0)
+    return np.minimum(s, 0x7E).astype(np.uint8)
+
+
+def csf_damaged(fx, ex, R, C):
+    """the reference test's negative controls: name → (fixed, exceptions, fixed_shape)"""
+    out = {}
+    out["index"] = (fx, np.append(ex, np.uint32((60 << 24) | (R * C))), fx.shape)
+    if ex.size:
+        i = int(ex[0] & 0xFFFFFF); n = (i // C % 16) * C + i % C
+        f2 = fx.copy(); f2[i // C // 16, 16 + (n >> 1)] |= 1 << ((n & 1) * 4)
+        out["delta"] = (f2, ex, fx.shape)
+        e2 = ex.copy(); e2[0] = (0x7F << 24) | (e2[0] & 0xFFFFFF)
+        out["value"] = (fx, e2, fx.shape)
+    if not np.any((ex & 0xFFFFFF) == 0):
+        f2 = fx.copy(); f2[0, 0] = 0x7E; f2[0, 16] |= 0x0F
+        out["code"] = (f2, ex, fx.shape)
+    out["shape"] = (fx, ex, (fx.shape[0], fx.shape[1] + 1))
+    return out
