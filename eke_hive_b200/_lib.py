@@ -133,7 +133,7 @@ def load() -> C.CDLL:
         "hb_dispatch_plan": (i, [vp, i, i, i, i, i, vp, C.POINTER(Plan)]),
         "hb_expert_dequant": (i, [vp, vp, i, i, vp, vp, vp]),
         "hb_csf_ws_bytes": (sz, [i, i]),
-        "hb_csf_decode": (i, [vp, C.c_int64, C.c_int64, vp, C.c_uint64, i, i, vp, vp, vp, sz, vp]),
+        "hb_csf_decode": (i, [vp, vp, C.c_int64, C.c_int64, vp, C.c_uint64, i, i, vp, vp, vp, sz, vp]),
         "hb_record_pack_ws_bytes": (sz, [i, i, i]),
         "hb_record_pack_batch": (i, [vp, vp, i, i, i, vp, vp, sz, vp]),
         "hb_record_pack": (i, [vp, C.POINTER(ProjSrc), i, i, vp, vp, vp, sz, vp]),

@@ -12,8 +12,8 @@
 // resolved like the sequential loop (the last word wins) through a per-scale table of the highest claiming ordinal.
 //
 // A record is 1-2 MB, microseconds of HBM time, so the unit of work is a BATCH of records: the caller hands over a device array of
-// jobs (three projections and a destination each) and every kernel runs once per batch with the job index in blockIdx.y — eight
-// launches however many records, instead of host threads walking the tensors one by one.
+// jobs (three projections and a destination each) and every kernel runs once per batch with the job index in blockIdx.y — a handful
+// of launches however many records, instead of host threads walking the tensors one by one.
 #include <algorithm>
 
 #include "hb_common.cuh"
@@ -37,32 +37,31 @@ __device__ __forceinline__ uint32_t csf_delta(const CsfArgs& a, uint32_t i) {
   return (a.fixed[(size_t)g * a.fixed_cols + 16 + (n >> 1)] >> ((n & 1) * 4)) & 15u;
 }
 
-// code = base[row] + delta; codes above 0x7E are written as 0xFF (not a scale unless an exception replaces them)
-__global__ void __launch_bounds__(256) csf_expand_kernel(const CsfArgs* __restrict__ jobs) {
-  const CsfArgs a = jobs[blockIdx.y];
-  const uint32_t per_group = 16u * a.C, units = a.total / 8;
-  for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < units; t += gridDim.x * blockDim.x) {
-    const uint32_t i = t * 8, g = i / per_group, n = i - g * per_group;
+// code = base[row] + delta; codes above 0x7E are written as 0xFF (not a scale unless an exception replaces them).  16 scales per
+// thread and step: one 8-byte load of deltas, one 16-byte store (a unit never straddles a group: 16·C is a multiple of 16).
+__device__ __forceinline__ void csf_expand(const CsfArgs& a, uint32_t bid, uint32_t nblk) {
+  const uint32_t per_group = 16u * a.C, units = a.total / 16;
+  for (uint32_t t = bid * blockDim.x + threadIdx.x; t < units; t += nblk * blockDim.x) {
+    const uint32_t i = t * 16, g = i / per_group, n = i - g * per_group;
     const uint8_t* grp = a.fixed + (size_t)g * a.fixed_cols;
-    const uint32_t d8 = *reinterpret_cast<const uint32_t*>(grp + 16 + (n >> 1));      // 8 deltas; 4-byte aligned: the group pitch and n/2 are multiples of 4
+    const uint2 d = *reinterpret_cast<const uint2*>(grp + 16 + (n >> 1));             // 8-byte aligned: the group pitch and n/2 are multiples of 8
     uint32_t r = n / a.C, c = n - r * a.C, base = grp[r];
-    uint32_t w[2] = {0u, 0u};
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const uint32_t code = base + ((d8 >> (4 * j)) & 15u);
+    for (int j = 0; j < 16; ++j) {
+      const uint32_t code = base + (((j < 8 ? d.x : d.y) >> (4 * (j & 7))) & 15u);
       w[j >> 2] |= (code > 0x7Eu ? 0xFFu : code) << (8 * (j & 3));
-      if (++c == a.C && j < 7) { c = 0; ++r; base = grp[r]; }                         // n + 8 ≤ 16·C: r stays below 16 while j < 7
+      if (++c == a.C && j < 15) { c = 0; ++r; base = grp[r]; }                        // n + 16 ≤ 16·C: r stays below 16 while j < 15
     }
-    *reinterpret_cast<uint2*>(a.out + i) = make_uint2(w[0], w[1]);
+    *reinterpret_cast<uint4*>(a.out + i) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
 // per exception: the checks of the sequential decoder in its order (index range, stored delta is 0, value is a finite non-negative
 // e4m3 code), and a claim on the entry
-__global__ void __launch_bounds__(256) csf_claim_kernel(const CsfArgs* __restrict__ jobs) {
-  const CsfArgs a = jobs[blockIdx.y];
+__device__ __forceinline__ void csf_claim(const CsfArgs& a, uint32_t bid, uint32_t nblk) {
   if (a.total == 0) return;
-  for (uint32_t k = blockIdx.x * blockDim.x + threadIdx.x; k < a.n_exc; k += gridDim.x * blockDim.x) {
+  for (uint32_t k = bid * blockDim.x + threadIdx.x; k < a.n_exc; k += nblk * blockDim.x) {
     const uint32_t w = a.exc[k], i = w & 0xFFFFFFu, v = w >> 24;
     int bad = -1;
     if (i >= a.total) bad = 0;
@@ -75,6 +74,40 @@ __global__ void __launch_bounds__(256) csf_claim_kernel(const CsfArgs* __restric
   }
 }
 
+// weights (and uncompressed scales) into the record: 16 bytes per thread where both sides allow it
+__device__ __forceinline__ void record_copy(const CsfArgs& a, uint32_t bid, uint32_t nblk) {
+  const size_t tid = (size_t)bid * blockDim.x + threadIdx.x, nth = (size_t)nblk * blockDim.x;
+#pragma unroll
+  for (int p = 0; p < 2; ++p) {
+    const uint8_t* s = a.copy_src[p];
+    uint8_t* d = a.copy_dst[p];
+    const size_t n = a.copy_n[p];
+    if (n == 0) continue;
+    if (((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d) | n) & 15) == 0) {
+      const uint4* s4 = reinterpret_cast<const uint4*>(s);
+      uint4* d4 = reinterpret_cast<uint4*>(d);
+      size_t i = tid;
+      for (; i + 3 * nth < n / 16; i += 4 * nth) {                                    // four loads in flight per thread
+        const uint4 v0 = __ldg(s4 + i), v1 = __ldg(s4 + i + nth), v2 = __ldg(s4 + i + 2 * nth), v3 = __ldg(s4 + i + 3 * nth);
+        d4[i] = v0; d4[i + nth] = v1; d4[i + 2 * nth] = v2; d4[i + 3 * nth] = v3;
+      }
+      for (; i < n / 16; i += nth) d4[i] = __ldg(s4 + i);
+    } else {
+      for (size_t i = tid; i < n; i += nth) d[i] = s[i];
+    }
+  }
+}
+
+// The three independent parts of a job in ONE launch, so that the latency-bound expansion and the scattered claims run under the
+// bandwidth-bound copies: blockIdx.x selects the part (copy | expand | claim), blockIdx.y the job.
+__global__ void __launch_bounds__(256) record_main_kernel(const CsfArgs* __restrict__ jobs, uint32_t cb, uint32_t eb, uint32_t kb) {
+  const CsfArgs a = jobs[blockIdx.y];
+  const uint32_t b = blockIdx.x;
+  if (b < cb) record_copy(a, b, cb);
+  else if (b < cb + eb) csf_expand(a, b - cb, eb);
+  else csf_claim(a, b - cb - eb, kb);
+}
+
 __global__ void __launch_bounds__(256) csf_apply_kernel(const CsfArgs* __restrict__ jobs) {
   const CsfArgs a = jobs[blockIdx.y];
   if (a.total == 0) return;
@@ -84,17 +117,19 @@ __global__ void __launch_bounds__(256) csf_apply_kernel(const CsfArgs* __restric
   }
 }
 
-// every decoded byte must be ≤ 0x7E: 8 bytes per thread, a byte fails when its top bit is set or its low seven bits are all ones
+// every decoded byte must be ≤ 0x7E: 16 bytes per thread, a byte fails when its top bit is set or its low seven bits are all ones
 __global__ void __launch_bounds__(256) csf_check_kernel(const CsfArgs* __restrict__ jobs) {
   const CsfArgs a = jobs[blockIdx.y];
-  const uint32_t units = a.total / 8;
+  const uint32_t units = a.total / 16;
   uint32_t first = 0xFFFFFFFFu;
   for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < units; t += gridDim.x * blockDim.x) {
-    const uint2 x = *reinterpret_cast<const uint2*>(a.out + (size_t)t * 8);
-    const uint32_t b0 = (x.x | ((x.x & 0x7F7F7F7Fu) + 0x01010101u)) & 0x80808080u;
-    const uint32_t b1 = (x.y | ((x.y & 0x7F7F7F7Fu) + 0x01010101u)) & 0x80808080u;
-    if (b0) first = min(first, t * 8 + (uint32_t)(__ffs((int)b0) - 1) / 8);
-    else if (b1) first = min(first, t * 8 + 4 + (uint32_t)(__ffs((int)b1) - 1) / 8);
+    const uint4 x = *reinterpret_cast<const uint4*>(a.out + (size_t)t * 16);
+    const uint32_t v[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int q = 3; q >= 0; --q) {
+      const uint32_t bad = (v[q] | ((v[q] & 0x7F7F7F7Fu) + 0x01010101u)) & 0x80808080u;
+      if (bad) first = min(first, t * 16 + 4 * q + (uint32_t)(__ffs((int)bad) - 1) / 8);
+    }
   }
   if (first != 0xFFFFFFFFu) atomicMin(&a.keys[1], first);
 }
@@ -110,24 +145,6 @@ __global__ void csf_finish_kernel(const CsfArgs* __restrict__ jobs, int n_jobs) 
   if (ke != 0xFFFFFFFFu) { code = HB_CSF_EXC_INDEX + (int32_t)(ke & 3u); where = (int32_t)(ke >> 2); }
   else if (kc != 0xFFFFFFFFu) { code = HB_CSF_CODE; where = (int32_t)kc; }
   a.status[0] = code; a.status[1] = where;
-}
-
-// weights (and uncompressed scales) into the record: 16 bytes per thread where both sides allow it
-__global__ void __launch_bounds__(256) record_copy_kernel(const CsfArgs* __restrict__ jobs) {
-  const CsfArgs a = jobs[blockIdx.y];
-  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
-#pragma unroll
-  for (int p = 0; p < 2; ++p) {
-    const uint8_t* s = a.copy_src[p];
-    uint8_t* d = a.copy_dst[p];
-    const size_t n = a.copy_n[p];
-    if (n == 0) continue;
-    if (((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d) | n) & 15) == 0) {
-      for (size_t i = tid; i < n / 16; i += nth) reinterpret_cast<uint4*>(d)[i] = __ldg(reinterpret_cast<const uint4*>(s) + i);
-    } else {
-      for (size_t i = tid; i < n; i += nth) d[i] = s[i];
-    }
-  }
 }
 
 struct RecordPrep {
@@ -163,7 +180,7 @@ __global__ void record_prep_kernel(RecordPrep p) {
   if (!s.weight || (!s.scale && !s.csf_fixed) || !job.rec || (reinterpret_cast<uintptr_t>(job.rec) & 15)) code = HB_CSF_MISSING;
   else if (!s.scale) {
     if (s.csf_fixed_rows != rows / 16 || s.csf_fixed_cols != 16 + 8 * (long long)C) code = HB_CSF_SHAPE;
-    else if (s.n_exc >= (1ull << 30) || (s.n_exc && !s.csf_exc) || (reinterpret_cast<uintptr_t>(s.csf_fixed) & 3) || (reinterpret_cast<uintptr_t>(s.csf_exc) & 3))
+    else if (s.n_exc >= (1ull << 30) || (s.n_exc && !s.csf_exc) || (reinterpret_cast<uintptr_t>(s.csf_fixed) & 7) || (reinterpret_cast<uintptr_t>(s.csf_exc) & 3))
       code = HB_CSF_MISSING;
     else a.total = (uint32_t)(rows * C);
   }
@@ -190,15 +207,17 @@ static CsfWs csf_carve(void* ws, long long total, long long jobs) {
 // expansion, exceptions, validation and verdict of n_jobs prepared jobs (the winner tables are zeroed here)
 static int csf_launch(hb_ctx* ctx, const CsfWs& w, int n_jobs, long long total, bool copies, cudaStream_t st) {
   HB_CUDA(ctx, cudaMemsetAsync(w.winner, 0, w.winner_bytes, st));
-  const unsigned bx = (unsigned)std::max<long long>(1, std::min<long long>((total / 8 + 255) / 256, std::max(1, ctx->sm_count * 8 / n_jobs)));
-  const dim3 grid(bx, (unsigned)n_jobs), blk(256);
+  // blocks per job: enough that the whole grid fills the device a few times over, no more than the job has work for
+  const unsigned per = (unsigned)std::max(1, ctx->sm_count * 8 / n_jobs);
+  const unsigned eb = (unsigned)std::max<long long>(1, std::min<long long>((total / 16 + 255) / 256, per));
+  const unsigned cb = copies ? std::max(2 * eb, 8u) : 0u, kb = eb;
+  const dim3 blk(256);
+  const CsfArgs* jobs = w.jobs;
   int r;
-  if (copies && (r = hb_launch(ctx, "record_copy", false, record_copy_kernel, dim3(std::max(bx, 16u), (unsigned)n_jobs), blk, 0, st,
-                               static_cast<const CsfArgs*>(w.jobs)))) return r;
-  if ((r = hb_launch(ctx, "csf_expand", false, csf_expand_kernel, grid, blk, 0, st, static_cast<const CsfArgs*>(w.jobs)))) return r;
-  if ((r = hb_launch(ctx, "csf_claim", false, csf_claim_kernel, grid, blk, 0, st, static_cast<const CsfArgs*>(w.jobs)))) return r;
-  if ((r = hb_launch(ctx, "csf_apply", false, csf_apply_kernel, grid, blk, 0, st, static_cast<const CsfArgs*>(w.jobs)))) return r;
-  if ((r = hb_launch(ctx, "csf_check", false, csf_check_kernel, grid, blk, 0, st, static_cast<const CsfArgs*>(w.jobs)))) return r;
+  if ((r = hb_launch(ctx, copies ? "record_main" : "csf_main", false, record_main_kernel, dim3(cb + eb + kb, (unsigned)n_jobs), blk, 0, st, jobs, cb, eb, kb)))
+    return r;
+  if ((r = hb_launch(ctx, "csf_apply", false, csf_apply_kernel, dim3(eb, (unsigned)n_jobs), blk, 0, st, jobs))) return r;
+  if ((r = hb_launch(ctx, "csf_check", false, csf_check_kernel, dim3(eb, (unsigned)n_jobs), blk, 0, st, jobs))) return r;
   return hb_launch(ctx, "csf_finish", false, csf_finish_kernel, dim3((unsigned)(n_jobs + 127) / 128), dim3(128), 0, st,
                    static_cast<const CsfArgs*>(w.jobs), n_jobs);
 }
@@ -223,8 +242,8 @@ int hb_csf_decode(hb_ctx* ctx, const uint8_t* fixed, int64_t fixed_rows, int64_t
   HB_REQUIRE(ctx, total <= (1ll << 24), HB_ERR_INVALID, "CSF: more scales than a 24-bit index addresses");
   HB_REQUIRE(ctx, n_exc < (1ull << 30), HB_ERR_UNSUPPORTED, "CSF: %llu exception words (limit 2^30)", (unsigned long long)n_exc);
   HB_REQUIRE(ctx, fixed && out && status && (n_exc == 0 || exc), HB_ERR_INVALID, "CSF: NULL tensor");
-  HB_REQUIRE(ctx, hb_aligned(fixed, 4) && hb_aligned(exc, 4) && hb_aligned(out, 8) && hb_aligned(status, 4), HB_ERR_INVALID,
-             "CSF: fixed / exceptions / status 4-byte, out 8-byte aligned");
+  HB_REQUIRE(ctx, hb_aligned(fixed, 8) && hb_aligned(exc, 4) && hb_aligned(out, 16) && hb_aligned(status, 4), HB_ERR_INVALID,
+             "CSF: fixed 8-byte, exceptions / status 4-byte, out 16-byte aligned");
   HB_REQUIRE(ctx, ws && hb_aligned(ws, 256) && ws_bytes >= csf_ws_bytes(total, 1), HB_ERR_WORKSPACE, "CSF: workspace of %zu bytes, 256-byte aligned",
              csf_ws_bytes(total, 1));
   const CsfWs w = csf_carve(ws, total, 1);

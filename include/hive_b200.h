@@ -300,7 +300,8 @@ HB_API int hb_dispatch_plan(const int32_t* ids_host, int M, int K, int E, int H,
  * HB_ERR_INVALID, like the reference's `false`.  The data-dependent invariants are checked on the device; status (device int32[2])
  * receives {HB_CSF_* code, position} of the violation the reference's sequential decoder meets first (position = exception
  * ordinal for the exception checks, flat scale index for HB_CSF_CODE), {0, 0} when the tensor is sound.  out is unspecified
- * unless status[0] == 0.  All pointers are device-accessible; the call enqueues on `stream` and does not synchronise. */
+ * unless status[0] == 0.  All pointers are device-accessible (fixed 8-byte, exc 4-byte, out 16-byte aligned); the call enqueues on
+ * `stream` and does not synchronise. */
 enum { HB_CSF_OK = 0, HB_CSF_SHAPE = 2 /* record assembly only: the fixed tensor's shape does not fit the projection */, HB_CSF_EXC_INDEX = 4,
        HB_CSF_EXC_DELTA = 5, HB_CSF_EXC_VALUE = 6, HB_CSF_CODE = 7, HB_CSF_MISSING = 8 /* record assembly only: a NULL or misaligned tensor */ };
 HB_API size_t hb_csf_ws_bytes(int R, int C);
@@ -323,11 +324,11 @@ typedef struct hb_record_job {
   uint8_t* rec;
 } hb_record_job;
 /* GlmExperts::load_all on the device, for a batch of n experts in one go: jobs = DEVICE-accessible array [n]; every kernel of the
- * call runs once for the whole batch (job index in the grid), so a batch costs nine launches however many records it holds.
+ * call runs once for the whole batch (job index in the grid), so a batch costs five launches and one memset however many records it holds.
  * Weights are copied, scales copied or CSF-decoded straight into each record, the three globals written as g1 g3 g2; the bytes
  * after the globals up to `total` are left as they are.  status = device int32 [n][3][2]: one {HB_CSF_* code, position} per
- * projection ({0, 0} = sound; HB_CSF_SHAPE / HB_CSF_MISSING for what the reference's loader refuses by shape or dtype; a refused
- * projection's scales are not written).  The reference aborts the load on the first violation; here the caller reads status
+ * projection ({0, 0} = sound; HB_CSF_SHAPE / HB_CSF_MISSING for what the reference's loader refuses by shape or dtype; the scales
+ * of a projection whose status is not 0 are unspecified).  The reference aborts the load on the first violation; here the caller reads status
  * once per batch and decides.  Sources 16-byte aligned copy with 16-byte accesses, others byte by byte.
  * hb_record_pack is the same for one expert with the descriptor in host memory. */
 HB_API size_t hb_record_pack_ws_bytes(int H, int I, int n);
