@@ -131,3 +131,26 @@ int main() { return sizes() > 0 ? 0 : 1; }
            "-o", str(exe)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     assert r.returncode == 0, r.stderr[-3000:]
+
+
+def test_python_signatures_have_the_headers_argument_counts(lib):
+    """every prototype of include/hive_b200.h that the ctypes mirror binds is bound with the same number of arguments (a missing
+    argtype shifts every later argument: a host crash, not an error code)"""
+    import re
+    from pathlib import Path
+    text = (Path(__file__).resolve().parent.parent / "include" / "hive_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
+    protos = dict()
+    for m in re.finditer(r"HB_API\s+[\w\s\*]+?\b(hb_\w+)\s*\(([^;]*?)\)\s*;", text, flags=re.S):
+        args = m.group(2).strip()
+        protos[m.group(1)] = 0 if args in ("", "void") else args.count(",") + 1
+    assert len(protos) > 40
+    bound = 0
+    dll = lib.load()
+    for name, n in protos.items():
+        fn = getattr(dll, name)
+        if fn.argtypes is None:
+            continue
+        bound += 1
+        assert len(fn.argtypes) == n, f"{name}: header has {n} arguments, the Python mirror binds {len(fn.argtypes)}"
+    assert bound > 40
