@@ -8,8 +8,10 @@
 // All of it is byte work bound by HBM: the expansion reads 8·C + 16 bytes and writes 16·C bytes per group of 16 rows, one thread
 // per 8 consecutive scales (one 4-byte load of deltas, one 8-byte store).  The data-dependent invariants the reference checks
 // sequentially are evaluated in parallel and reduced so that the reported violation is the one the sequential decoder meets first:
-// the lowest exception ordinal with its first failing check, else the lowest invalid scale index.  A repeated exception index is
-// resolved like the sequential loop (the last word wins) through a per-scale table of the highest claiming ordinal.
+// the lowest exception ordinal with its first failing check, else the lowest invalid scale index.  Exceptions are applied in
+// parallel; a repeated exception index with different values (no sound encoder writes one) is noticed afterwards — some word
+// does not find its value in place — and that tensor's words are then re-applied in order by one thread, so the last word wins
+// as in the sequential loop.
 //
 // A record is 1-2 MB, microseconds of HBM time, so the unit of work is a BATCH of records: the caller hands over a device array of
 // jobs (three projections and a destination each) and every kernel runs once per batch with the job index in blockIdx.y — a handful
@@ -25,7 +27,6 @@ struct CsfArgs {
   const uint32_t* exc; uint32_t n_exc;
   uint32_t C, total;             // columns of the scale matrix, R·C; total == 0: nothing to decode (plain scales, or refused by shape)
   uint8_t* out;
-  uint32_t* winner;              // [total]: highest exception ordinal + 1 that names the entry (0 = none)
   uint32_t* keys;                // [0] lowest (exception ordinal · 4 + failing check), [1] lowest invalid scale index; ~0 = none
   int32_t* status;               // [2]: HB_CSF_* code, position
   // plain copies of the same job (record assembly): weight bytes, and the scale bytes when they are stored uncompressed
@@ -58,18 +59,15 @@ __device__ __forceinline__ void csf_expand(const CsfArgs& a, uint32_t bid, uint3
 }
 
 // per exception: the checks of the sequential decoder in its order (index range, stored delta is 0, value is a finite non-negative
-// e4m3 code), and a claim on the entry
-__device__ __forceinline__ void csf_claim(const CsfArgs& a, uint32_t bid, uint32_t nblk) {
+// e4m3 code)
+__device__ __forceinline__ void csf_exc_check(const CsfArgs& a, uint32_t bid, uint32_t nblk) {
   if (a.total == 0) return;
   for (uint32_t k = bid * blockDim.x + threadIdx.x; k < a.n_exc; k += nblk * blockDim.x) {
     const uint32_t w = a.exc[k], i = w & 0xFFFFFFu, v = w >> 24;
     int bad = -1;
     if (i >= a.total) bad = 0;
-    else {
-      if (csf_delta(a, i) != 0u) bad = 1;
-      else if (v > 0x7Eu) bad = 2;
-      atomicMax(&a.winner[i], k + 1u);
-    }
+    else if (csf_delta(a, i) != 0u) bad = 1;
+    else if (v > 0x7Eu) bad = 2;
     if (bad >= 0) atomicMin(&a.keys[0], k * 4u + (uint32_t)bad);
   }
 }
@@ -98,14 +96,14 @@ __device__ __forceinline__ void record_copy(const CsfArgs& a, uint32_t bid, uint
   }
 }
 
-// The three independent parts of a job in ONE launch, so that the latency-bound expansion and the scattered claims run under the
-// bandwidth-bound copies: blockIdx.x selects the part (copy | expand | claim), blockIdx.y the job.
+// The three independent parts of a job in ONE launch, so that the latency-bound expansion and the scattered exception checks run
+// under the bandwidth-bound copies: blockIdx.x selects the part (copy | expand | exception checks), blockIdx.y the job.
 __global__ void __launch_bounds__(256) record_main_kernel(const CsfArgs* __restrict__ jobs, uint32_t cb, uint32_t eb, uint32_t kb) {
   const CsfArgs a = jobs[blockIdx.y];
   const uint32_t b = blockIdx.x;
   if (b < cb) record_copy(a, b, cb);
   else if (b < cb + eb) csf_expand(a, b - cb, eb);
-  else csf_claim(a, b - cb - eb, kb);
+  else csf_exc_check(a, b - cb - eb, kb);
 }
 
 __global__ void __launch_bounds__(256) csf_apply_kernel(const CsfArgs* __restrict__ jobs) {
@@ -113,7 +111,25 @@ __global__ void __launch_bounds__(256) csf_apply_kernel(const CsfArgs* __restric
   if (a.total == 0) return;
   for (uint32_t k = blockIdx.x * blockDim.x + threadIdx.x; k < a.n_exc; k += gridDim.x * blockDim.x) {
     const uint32_t w = a.exc[k], i = w & 0xFFFFFFu;
-    if (i < a.total && a.winner[i] == k + 1u) a.out[i] = (uint8_t)(w >> 24);
+    if (i < a.total) a.out[i] = (uint8_t)(w >> 24);
+  }
+}
+
+// One block per job.  Every exception word must find its value in place; if one does not, two words named the same entry with
+// different values and the parallel writes raced: thread 0 re-applies the job's words in order (the last word wins).
+__global__ void __launch_bounds__(256) csf_settle_kernel(const CsfArgs* __restrict__ jobs) {
+  const CsfArgs a = jobs[blockIdx.x];
+  if (a.total == 0 || a.n_exc == 0) return;
+  int conflict = 0;
+  for (uint32_t k = threadIdx.x; k < a.n_exc; k += blockDim.x) {
+    const uint32_t w = a.exc[k], i = w & 0xFFFFFFu;
+    if (i < a.total && a.out[i] != (uint8_t)(w >> 24)) conflict = 1;
+  }
+  if (__syncthreads_or(conflict) && threadIdx.x == 0) {
+    for (uint32_t k = 0; k < a.n_exc; ++k) {
+      const uint32_t w = a.exc[k], i = w & 0xFFFFFFu;
+      if (i < a.total) a.out[i] = (uint8_t)(w >> 24);
+    }
   }
 }
 
@@ -153,7 +169,6 @@ struct RecordPrep {
   hb_rec_layout L;
   CsfArgs* out;                  // [3n]
   uint32_t* keys;                // [3n][2]
-  uint32_t* winner;              // [3n][H·I/16]
   int32_t* status;               // [n][3][2]
 };
 
@@ -170,7 +185,6 @@ __global__ void record_prep_kernel(RecordPrep p) {
   CsfArgs a;
   a.fixed = s.csf_fixed; a.fixed_cols = s.csf_fixed_cols; a.exc = s.csf_exc; a.n_exc = (uint32_t)s.n_exc; a.C = (uint32_t)C; a.total = 0;
   a.out = job.rec + s_off;
-  a.winner = p.winner + (size_t)t * (size_t)(rows * C);
   a.keys = p.keys + 2 * t;
   a.status = p.status + 2 * t;
   const bool dst_ok = job.rec && !(reinterpret_cast<uintptr_t>(job.rec) & 15);
@@ -190,23 +204,19 @@ __global__ void record_prep_kernel(RecordPrep p) {
   if (dst_ok) reinterpret_cast<float*>(job.rec + p.L.g)[j] = s.global;
 }
 
-static size_t csf_ws_bytes(long long total, long long jobs) {
-  return hb_align256((size_t)jobs * sizeof(CsfArgs)) + hb_align256((size_t)jobs * 8) + hb_align256((size_t)jobs * (size_t)total * 4);
-}
+static size_t csf_ws_bytes(long long jobs) { return hb_align256((size_t)jobs * sizeof(CsfArgs)) + hb_align256((size_t)jobs * 8); }
 
-struct CsfWs { CsfArgs* jobs; uint32_t* keys; uint32_t* winner; size_t winner_bytes; };
-static CsfWs csf_carve(void* ws, long long total, long long jobs) {
+struct CsfWs { CsfArgs* jobs; uint32_t* keys; };
+static CsfWs csf_carve(void* ws, long long jobs) {
   uint8_t* p = static_cast<uint8_t*>(ws);
   CsfWs w;
   w.jobs = reinterpret_cast<CsfArgs*>(p); p += hb_align256((size_t)jobs * sizeof(CsfArgs));
-  w.keys = reinterpret_cast<uint32_t*>(p); p += hb_align256((size_t)jobs * 8);
-  w.winner = reinterpret_cast<uint32_t*>(p); w.winner_bytes = (size_t)jobs * (size_t)total * 4;
+  w.keys = reinterpret_cast<uint32_t*>(p);
   return w;
 }
 
-// expansion, exceptions, validation and verdict of n_jobs prepared jobs (the winner tables are zeroed here)
+// expansion, exceptions, validation and verdict of n_jobs prepared jobs
 static int csf_launch(hb_ctx* ctx, const CsfWs& w, int n_jobs, long long total, bool copies, cudaStream_t st) {
-  HB_CUDA(ctx, cudaMemsetAsync(w.winner, 0, w.winner_bytes, st));
   // blocks per job: enough that the whole grid fills the device a few times over, no more than the job has work for
   const unsigned per = (unsigned)std::max(1, ctx->sm_count * 8 / n_jobs);
   const unsigned eb = (unsigned)std::max<long long>(1, std::min<long long>((total / 16 + 255) / 256, per));
@@ -217,6 +227,7 @@ static int csf_launch(hb_ctx* ctx, const CsfWs& w, int n_jobs, long long total, 
   if ((r = hb_launch(ctx, copies ? "record_main" : "csf_main", false, record_main_kernel, dim3(cb + eb + kb, (unsigned)n_jobs), blk, 0, st, jobs, cb, eb, kb)))
     return r;
   if ((r = hb_launch(ctx, "csf_apply", false, csf_apply_kernel, dim3(eb, (unsigned)n_jobs), blk, 0, st, jobs))) return r;
+  if ((r = hb_launch(ctx, "csf_settle", false, csf_settle_kernel, dim3((unsigned)n_jobs), blk, 0, st, jobs))) return r;
   if ((r = hb_launch(ctx, "csf_check", false, csf_check_kernel, dim3(eb, (unsigned)n_jobs), blk, 0, st, jobs))) return r;
   return hb_launch(ctx, "csf_finish", false, csf_finish_kernel, dim3((unsigned)(n_jobs + 127) / 128), dim3(128), 0, st,
                    static_cast<const CsfArgs*>(w.jobs), n_jobs);
@@ -228,7 +239,7 @@ using namespace hb;
 
 extern "C" {
 
-size_t hb_csf_ws_bytes(int R, int C) { return R > 0 && C > 0 ? csf_ws_bytes((long long)R * C, 1) : 0; }
+size_t hb_csf_ws_bytes(int R, int C) { return R > 0 && C > 0 ? csf_ws_bytes(1) : 0; }
 
 int hb_csf_decode(hb_ctx* ctx, const uint8_t* fixed, int64_t fixed_rows, int64_t fixed_cols, const uint32_t* exc, uint64_t n_exc, int R, int C,
                   uint8_t* out, int32_t* status, void* ws, size_t ws_bytes, void* stream) {
@@ -244,19 +255,19 @@ int hb_csf_decode(hb_ctx* ctx, const uint8_t* fixed, int64_t fixed_rows, int64_t
   HB_REQUIRE(ctx, fixed && out && status && (n_exc == 0 || exc), HB_ERR_INVALID, "CSF: NULL tensor");
   HB_REQUIRE(ctx, hb_aligned(fixed, 8) && hb_aligned(exc, 4) && hb_aligned(out, 16) && hb_aligned(status, 4), HB_ERR_INVALID,
              "CSF: fixed 8-byte, exceptions / status 4-byte, out 16-byte aligned");
-  HB_REQUIRE(ctx, ws && hb_aligned(ws, 256) && ws_bytes >= csf_ws_bytes(total, 1), HB_ERR_WORKSPACE, "CSF: workspace of %zu bytes, 256-byte aligned",
-             csf_ws_bytes(total, 1));
-  const CsfWs w = csf_carve(ws, total, 1);
+  HB_REQUIRE(ctx, ws && hb_aligned(ws, 256) && ws_bytes >= csf_ws_bytes(1), HB_ERR_WORKSPACE, "CSF: workspace of %zu bytes, 256-byte aligned",
+             csf_ws_bytes(1));
+  const CsfWs w = csf_carve(ws, 1);
   CsfArgs a = {};
   a.fixed = fixed; a.fixed_cols = fixed_cols; a.exc = exc; a.n_exc = (uint32_t)n_exc; a.C = (uint32_t)C; a.total = (uint32_t)total; a.out = out;
-  a.winner = w.winner; a.keys = w.keys; a.status = status;
+  a.keys = w.keys; a.status = status;
   HB_CUDA(ctx, cudaMemcpyAsync(w.jobs, &a, sizeof a, cudaMemcpyHostToDevice, st));      // pageable source: staged before the call returns
   HB_CUDA(ctx, cudaMemsetAsync(w.keys, 0xFF, 8, st));
   return csf_launch(ctx, w, 1, total, false, st);
 }
 
 size_t hb_record_pack_ws_bytes(int H, int I, int n) {
-  return H > 0 && I > 0 && n > 0 ? hb_align256((size_t)n * sizeof(hb_record_job)) + csf_ws_bytes((long long)H * I / 16, 3ll * n) : 0;
+  return H > 0 && I > 0 && n > 0 ? hb_align256((size_t)n * sizeof(hb_record_job)) + csf_ws_bytes(3ll * n) : 0;
 }
 
 int hb_record_pack_batch(hb_ctx* ctx, const hb_record_job* jobs, int n, int H, int I, int32_t* status, void* ws, size_t ws_bytes, void* stream) {
@@ -271,9 +282,9 @@ int hb_record_pack_batch(hb_ctx* ctx, const hb_record_job* jobs, int n, int H, i
   HB_REQUIRE(ctx, ws && hb_aligned(ws, 256) && ws_bytes >= hb_record_pack_ws_bytes(H, I, n), HB_ERR_WORKSPACE,
              "record_pack: workspace of %zu bytes, 256-byte aligned", hb_record_pack_ws_bytes(H, I, n));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const CsfWs w = csf_carve(static_cast<uint8_t*>(ws) + hb_align256((size_t)n * sizeof(hb_record_job)), total, 3ll * n);
+  const CsfWs w = csf_carve(static_cast<uint8_t*>(ws) + hb_align256((size_t)n * sizeof(hb_record_job)), 3ll * n);
   RecordPrep p;
-  p.jobs = jobs; p.n = n; p.H = H; p.I = I; p.L = L; p.out = w.jobs; p.keys = w.keys; p.winner = w.winner; p.status = status;
+  p.jobs = jobs; p.n = n; p.H = H; p.I = I; p.L = L; p.out = w.jobs; p.keys = w.keys; p.status = status;
   int r = hb_launch(ctx, "record_prep", false, record_prep_kernel, dim3((unsigned)(3 * n + 127) / 128), dim3(128), 0, st, p);
   if (r) return r;
   return csf_launch(ctx, w, 3 * n, total, true, st);
