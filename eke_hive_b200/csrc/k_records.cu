@@ -150,6 +150,52 @@ __global__ void __launch_bounds__(256) csf_check_kernel(const CsfArgs* __restric
   if (first != 0xFFFFFFFFu) atomicMin(&a.keys[1], first);
 }
 
+// Large batches: apply, settle, validation and verdict of one job by ONE block (the four steps are ordered only within a tensor),
+// one launch instead of four.
+__global__ void __launch_bounds__(512) csf_tail_kernel(const CsfArgs* __restrict__ jobs) {
+  const CsfArgs a = jobs[blockIdx.x];
+  if (a.total == 0) return;
+  __shared__ uint32_t first_s;
+  if (threadIdx.x == 0) first_s = 0xFFFFFFFFu;
+  int conflict = 0;
+  for (uint32_t k = threadIdx.x; k < a.n_exc; k += blockDim.x) {
+    const uint32_t w = a.exc[k], i = w & 0xFFFFFFu;
+    if (i < a.total) a.out[i] = (uint8_t)(w >> 24);
+  }
+  __syncthreads();
+  for (uint32_t k = threadIdx.x; k < a.n_exc; k += blockDim.x) {
+    const uint32_t w = a.exc[k], i = w & 0xFFFFFFu;
+    if (i < a.total && a.out[i] != (uint8_t)(w >> 24)) conflict = 1;
+  }
+  if (__syncthreads_or(conflict)) {
+    if (threadIdx.x == 0)
+      for (uint32_t k = 0; k < a.n_exc; ++k) {
+        const uint32_t w = a.exc[k], i = w & 0xFFFFFFu;
+        if (i < a.total) a.out[i] = (uint8_t)(w >> 24);
+      }
+    __syncthreads();
+  }
+  uint32_t first = 0xFFFFFFFFu;
+  for (uint32_t t = threadIdx.x; t < a.total / 16; t += blockDim.x) {
+    const uint4 x = *reinterpret_cast<const uint4*>(a.out + (size_t)t * 16);
+    const uint32_t v[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int q = 3; q >= 0; --q) {
+      const uint32_t bad = (v[q] | ((v[q] & 0x7F7F7F7Fu) + 0x01010101u)) & 0x80808080u;
+      if (bad) first = min(first, t * 16 + 4 * q + (uint32_t)(__ffs((int)bad) - 1) / 8);
+    }
+  }
+  if (first != 0xFFFFFFFFu) atomicMin(&first_s, first);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t ke = a.keys[0], kc = first_s;
+    int32_t code = HB_CSF_OK, where = 0;
+    if (ke != 0xFFFFFFFFu) { code = HB_CSF_EXC_INDEX + (int32_t)(ke & 3u); where = (int32_t)(ke >> 2); }
+    else if (kc != 0xFFFFFFFFu) { code = HB_CSF_CODE; where = (int32_t)kc; }
+    a.status[0] = code; a.status[1] = where;
+  }
+}
+
 // one thread per job: the verdict.  A job refused by shape keeps the status the preparation wrote.
 __global__ void csf_finish_kernel(const CsfArgs* __restrict__ jobs, int n_jobs) {
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
@@ -226,6 +272,8 @@ static int csf_launch(hb_ctx* ctx, const CsfWs& w, int n_jobs, long long total, 
   int r;
   if ((r = hb_launch(ctx, copies ? "record_main" : "csf_main", false, record_main_kernel, dim3(cb + eb + kb, (unsigned)n_jobs), blk, 0, st, jobs, cb, eb, kb)))
     return r;
+  if (n_jobs >= ctx->sm_count)                          // enough tensors to fill the device with one block each
+    return hb_launch(ctx, "csf_tail", false, csf_tail_kernel, dim3((unsigned)n_jobs), dim3(512), 0, st, jobs);
   if ((r = hb_launch(ctx, "csf_apply", false, csf_apply_kernel, dim3(eb, (unsigned)n_jobs), blk, 0, st, jobs))) return r;
   if ((r = hb_launch(ctx, "csf_settle", false, csf_settle_kernel, dim3((unsigned)n_jobs), blk, 0, st, jobs))) return r;
   if ((r = hb_launch(ctx, "csf_check", false, csf_check_kernel, dim3(eb, (unsigned)n_jobs), blk, 0, st, jobs))) return r;

@@ -324,7 +324,8 @@ typedef struct hb_record_job {
   uint8_t* rec;
 } hb_record_job;
 /* GlmExperts::load_all on the device, for a batch of n experts in one go: jobs = DEVICE-accessible array [n]; every kernel of the
- * call runs once for the whole batch (job index in the grid), so a batch costs six launches however many records it holds (the workspace is a few hundred bytes per record).
+ * call runs once for the whole batch (job index in the grid), so a batch costs three launches however many records it holds (six when it has fewer tensors than the device has SMs; the
+ * workspace is a few hundred bytes per record).
  * Weights are copied, scales copied or CSF-decoded straight into each record, the three globals written as g1 g3 g2; the bytes
  * after the globals up to `total` are left as they are.  status = device int32 [n][3][2]: one {HB_CSF_* code, position} per
  * projection ({0, 0} = sound; HB_CSF_SHAPE / HB_CSF_MISSING for what the reference's loader refuses by shape or dtype; the scales

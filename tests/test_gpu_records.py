@@ -104,11 +104,11 @@ def test_record_pack_matches_oracle_and_runs(E, oracle, H, I):
     assert st.tolist() == [[0, 0], [0, 0], [4, e2.size - 1]]
 
 
-def test_record_pack_batch_matches_oracle(E, oracle):
-    """a batch of experts in one call: compressed, plain and mixed projections, one expert damaged — every record equals the oracle's,
-    the damaged projection is reported in its own slot and nothing else is disturbed"""
+@pytest.mark.parametrize("H,I,n", [(512, 256, 7), (256, 128, 60)])     # 21 tensors: one kernel per phase; 180: one block per tensor
+def test_record_pack_batch_matches_oracle(E, oracle, H, I, n):
+    """a batch of experts in one call: compressed, plain and mixed projections, one expert damaged, one with a repeated exception
+    index — every record equals the oracle's, the damaged projection is reported in its own slot and nothing else is disturbed"""
     dev = torch.device("cuda")
-    H, I, n = 512, 256, 7
     rng = np.random.default_rng(99)
     L = E.ExpertRecLayout(H, I)
     used = int(L.g) + 12
@@ -124,6 +124,9 @@ def test_record_pack_batch_matches_oracle(E, oracle):
             if (r + j) % 3 == 0:
                 projs_np.append({"weight": q, "scale": s, "global": gl}); projs_dev.append({"weight": _dev(q), "scale": _dev(s), "global": gl})
             else:
+                if r == 2 and j == 2:                                   # entry 9 named twice with different values: the later word wins
+                    fx = fx.copy(); fx[0, 16 + 4] &= 0x0F
+                    ex = np.concatenate([ex, np.array([(0x31 << 24) | 9, (0x42 << 24) | 9], np.uint32)]).astype(np.uint32)
                 if r == 4 and j == 1:
                     ex = np.append(ex, np.uint32((0x7F << 24) | 3)).astype(np.uint32); fx = fx.copy(); fx[0, 17] &= 0x0F   # delta of entry 3 cleared, value NaN
                 projs_np.append({"weight": q, "csf_fixed": fx, "csf_exc": ex, "global": gl})
