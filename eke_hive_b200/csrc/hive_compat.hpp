@@ -131,6 +131,25 @@ inline void build_moe_pairs(const int32_t* ids, const float* w, int M, int K, co
 }
 }  // namespace hive::qwen
 
+// Loading (engine/include/hive/ckpt_quant.h:35-37, engine/src/glm/glm_experts.cpp:216-287).  The reference decodes compressed block
+// scales and assembles records on host threads; these run on the device over tensors already uploaded, so the signatures differ:
+// device pointers, a stream, and a device status word instead of `false` / an exception.
+namespace hive::ckq {
+inline size_t csf_decode_ws_bytes(int R, int C) { return hb_csf_ws_bytes(R, C); }
+// status: device int32[2] = {HB_CSF_* code, position}; shapes the format rules out throw like every other misuse
+inline void csf_decode(const uint8_t* fixed, int64_t fixed_rows, int64_t fixed_cols, const uint32_t* exc, size_t n_exc, int R, int C, uint8_t* out,
+                       int32_t* status, void* ws, size_t ws_bytes, cudaStream_t st) {
+  b200::check(hb_csf_decode(b200::ctx(), fixed, fixed_rows, fixed_cols, exc, n_exc, R, C, out, status, ws, ws_bytes, st));
+}
+}  // namespace hive::ckq
+namespace hive::glm {
+inline size_t records_pack_ws_bytes(int H, int I, int n) { return hb_record_pack_ws_bytes(H, I, n); }
+// jobs: device array [n]; status: device int32 [n][3][2]
+inline void records_pack(const hb_record_job* jobs, int n, int H, int I, int32_t* status, void* ws, size_t ws_bytes, cudaStream_t st) {
+  b200::check(hb_record_pack_batch(b200::ctx(), jobs, n, H, I, status, ws, ws_bytes, st));
+}
+}  // namespace hive::glm
+
 // Dense decode GEMV of the 27B-style MLP (engine/include/hive/q27/q27_kernels.h:17-64).  GMat here carries the formats this library
 // streams: NVFP4 as in the reference, plus the 3-/2-bit group-64 layouts hb_qmat defines.  The workspace the reference keeps
 // inside its kernels is explicit: ws ≥ hb_dense_gemv_ws_bytes(fmt, N, K, 1 or 2).
