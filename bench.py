@@ -693,7 +693,9 @@ def run_records(args):
                       "config": {"workload": f"{n} experts, hidden {H}, FFN {I}, NVFP4 with compressed block scales → records; one batch call per step",
                                  "l2": f"{by / 1e6:.0f} MB read + written per step (larger than L2)"},
                       "roofline": {"bound": "hbm", "kernel": "record_copy_kernel + csf_*", "achieved": by / ms / 1e6, "peak": peak, "unit": "GB/s",
-                                   "frac": by / ms / 1e6 / peak, "traffic": None},
+                                   "frac": by / ms / 1e6 / peak, "traffic": 908.8e6,
+                                   "traffic_from": "ncu dram__bytes_read + dram__bytes_write of record_main + csf_tail for this workload "
+                                                   "(profiles/record_pack_batch_256x2048x512.md)", "algorithmic_bytes": by},
                       "cpu_baseline": {"value": cpu_rps, "unit": "records/s", "cores": 1, "kind": "port", "sample": f"{m} experts in 3 s"}}), flush=True)
 
 
