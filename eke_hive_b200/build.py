@@ -52,7 +52,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:
         list(ex.map(compile_one, jobs))
     objs = [OBJ / (s.stem + ".o") for s in srcs]
-    if jobs or not OUT.exists():
+    if jobs or not OUT.exists() or OUT.stat().st_mtime < max(o.stat().st_mtime for o in objs):
         cmd = [NVCC, "-shared", "-o", str(OUT), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a", "-lcudart",
                "-ccbin", "/usr/bin/g++" if Path("/usr/bin/g++").exists() else "g++"]
         r = subprocess.run(cmd, capture_output=True, text=True)

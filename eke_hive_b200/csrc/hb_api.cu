@@ -44,6 +44,7 @@ int hb_create(const hb_config* cfg, hb_ctx** out) {
 void hb_destroy(hb_ctx* ctx) {
   if (!ctx) return;
   if (ctx->dev_err) cudaFree(ctx->dev_err);
+  if (ctx->dtc_maps) cudaFree(ctx->dtc_maps);
   if (ctx->prof_ev) {
     for (int i = 0; i < 2 * hb_ctx::kProfMax; ++i) cudaEventDestroy(ctx->prof_ev[i]);
     delete[] ctx->prof_ev;
@@ -188,9 +189,9 @@ int hb_moe_combine(hb_ctx* ctx, const float* routed, const void* shared, const f
   return hbk_moe_combine(ctx, routed, shared, lg, ld, col, M, H, out, as_stream(stream), pdl_on(ctx));
 }
 
-static int check_decode_shape(hb_ctx* ctx, const char* fn, int P, int H, int I, const void* x, const void* ws) {
+static int check_decode_shape(hb_ctx* ctx, const char* fn, long long P, int H, int I, const void* x, const void* ws) {
   HB_REQUIRE(ctx, H > 0 && I > 0 && H % 32 == 0 && I % 32 == 0, HB_ERR_UNSUPPORTED, "%s: H=%d I=%d must be multiples of 32", fn, H, I);
-  HB_REQUIRE(ctx, P <= HB_MAX_PAIRS, HB_ERR_UNSUPPORTED, "%s: %d pairs > %d", fn, P, HB_MAX_PAIRS);
+  HB_REQUIRE(ctx, P >= 1 && P <= HB_MAX_PAIRS, HB_ERR_UNSUPPORTED, "%s: %lld pairs outside 1..%d", fn, P, HB_MAX_PAIRS);
   HB_REQUIRE(ctx, ws != nullptr && hb_aligned(ws, 256), HB_ERR_WORKSPACE, "%s: ws NULL or not 256-byte aligned", fn);
   HB_REQUIRE(ctx, hb_aligned(x, 16), HB_ERR_INVALID, "%s: x must be 16-byte aligned", fn);
   return HB_OK;
@@ -220,7 +221,7 @@ int hb_moe_decode_routed(hb_ctx* ctx, const int32_t* ids, const float* w, int M,
   if (M == 0) return HB_OK;
   HB_PTR(ctx, ids); HB_PTR(ctx, w); HB_PTR(ctx, rec_tab); HB_PTR(ctx, x); HB_PTR(ctx, cmb); HB_PTR(ctx, cmb->out);
   HB_REQUIRE(ctx, M > 0 && K > 0 && E > 0 && E <= HB_MAX_EXPERTS && li >= 0, HB_ERR_INVALID, "moe_decode_routed: M=%d K=%d E=%d li=%d", M, K, E, li);
-  int r = check_decode_shape(ctx, "moe_decode_routed", M * K, H, I, x, ws);
+  int r = check_decode_shape(ctx, "moe_decode_routed", (long long)M * K, H, I, x, ws);
   if (r) return r;
   hbk_pair_src src; src.ids = ids; src.w = w; src.M = M; src.K = K; src.tab = rec_tab; src.li = li; src.E = E;
   hbk_reduce red; red.shared = cmb->shared; red.lg = cmb->lg; red.ld = cmb->ld; red.col = cmb->col; red.out_bf16 = cmb->out;
@@ -233,7 +234,7 @@ int hb_moe_decode_routed_f32(hb_ctx* ctx, const int32_t* ids, const float* w, in
   if (M == 0) return HB_OK;
   HB_PTR(ctx, ids); HB_PTR(ctx, w); HB_PTR(ctx, rec_tab); HB_PTR(ctx, x); HB_PTR(ctx, out);
   HB_REQUIRE(ctx, M > 0 && K > 0 && E > 0 && E <= HB_MAX_EXPERTS && li >= 0, HB_ERR_INVALID, "moe_decode_routed_f32: M=%d K=%d E=%d li=%d", M, K, E, li);
-  int r = check_decode_shape(ctx, "moe_decode_routed_f32", M * K, H, I, x, ws);
+  int r = check_decode_shape(ctx, "moe_decode_routed_f32", (long long)M * K, H, I, x, ws);
   if (r) return r;
   hbk_pair_src src; src.ids = ids; src.w = w; src.M = M; src.K = K; src.tab = rec_tab; src.li = li; src.E = E;
   hbk_reduce red; red.out_f32 = out;
@@ -250,7 +251,7 @@ int hb_moe_decode_ep_local(hb_ctx* ctx, const int32_t* ids, const float* w, int 
              "moe_decode_ep_local: M=%d K=%d E=%d li=%d ld_ids=%d ldx=%d (ldx a multiple of 8)", M, K, E, li, ld_ids, ldx);
   HB_REQUIRE(ctx, !shared_rec || (shared_out && sh_row0 >= 0 && sh_rows >= 0 && sh_row0 + sh_rows <= M), HB_ERR_INVALID,
              "moe_decode_ep_local: shared expert rows [%d, %d) outside the %d rows, or no output for them", sh_row0, sh_row0 + sh_rows, M);
-  int r = check_decode_shape(ctx, "moe_decode_ep_local", M * (K + (shared_rec ? 1 : 0)), H, I, x, ws);
+  int r = check_decode_shape(ctx, "moe_decode_ep_local", (long long)M * (K + (shared_rec ? 1 : 0)), H, I, x, ws);
   if (r) return r;
   hbk_pair_src src; src.ids = ids; src.w = w; src.M = M; src.K = K; src.tab = rec_tab; src.li = li; src.E = E;
   src.ld_ids = ld_ids; src.x_ld = ldx; src.shared_rec = shared_rec; src.sh_row0 = sh_row0; src.sh_rows = shared_rec ? sh_rows : 0;
@@ -267,7 +268,7 @@ int hb_moe_layer_decode(hb_ctx* ctx, const float* logits, int ld, int M, int E, 
   HB_REQUIRE(ctx, M > 0 && K >= 1 && K <= 16 && E > 0 && E <= HB_MAX_EXPERTS && K <= E && ld >= E && li >= 0, HB_ERR_INVALID,
              "moe_layer_decode: M=%d K=%d E=%d ld=%d li=%d", M, K, E, ld, li);
   HB_REQUIRE(ctx, gate_col < ld, HB_ERR_INVALID, "moe_layer_decode: gate_col=%d outside the logits row (ld=%d)", gate_col, ld);
-  int r = check_decode_shape(ctx, "moe_layer_decode", M * (K + 1), H, I, x, ws);
+  int r = check_decode_shape(ctx, "moe_layer_decode", (long long)M * (K + 1), H, I, x, ws);
   if (r) return r;
   const bool sigmoid = bias != nullptr || sigmoid_scale != 0.f;
   if (sigmoid) HB_REQUIRE(ctx, ld == E, HB_ERR_INVALID, "moe_layer_decode: the sigmoid router takes dense logits rows (ld == E)");

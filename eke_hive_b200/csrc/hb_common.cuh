@@ -20,6 +20,9 @@ struct hb_ctx {
   int smem_optin = 0;            // cudaDevAttrMaxSharedMemoryPerBlockOptin
   uint32_t* dev_err = nullptr;   // device error word: 0 = fine; kernels OR a site code into it when a bounded wait gives up
   unsigned long long launches = 0;
+  // tensor maps of the decode layer kernel (k_moe_dtc.cu): device array + the shape they were made for
+  void* dtc_maps = nullptr;
+  int dtc_H = 0, dtc_I = 0;
   char err[512] = {0};
   // optional per-kernel timing (hb_profile_enable): a start/stop event pair around every launch, aggregated by hb_profile_read
   bool prof_on = false;

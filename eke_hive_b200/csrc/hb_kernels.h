@@ -66,6 +66,13 @@ struct hbk_reduce {
 int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int H, int I, float limit, const hbk_reduce& red, void* ws,
                        cudaStream_t st);
 
+// decode layer on the block-scaled tensor cores (k_moe_dtc.cu): routed form only, H and I multiples of 256
+bool hbk_moe_dtc_supported(int H, int I);
+bool hbk_moe_dtc_fits(const hb_ctx* ctx, int n_pairs, int E, int H, int I);   // the launch's work lists fit the CTAs' tables
+size_t hbk_moe_dtc_ws_extra(int n_pairs, int H, int I);      // bytes it needs after the streaming path's workspace
+int hbk_moe_dtc_setup(hb_ctx* ctx);
+int hbk_moe_dtc_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int H, int I, float limit, const hbk_reduce& red, void* ws, cudaStream_t st);
+
 // dense GEMV (k_dense.cu)
 int hbk_dense_setup(hb_ctx* ctx);
 int hbk_moe_prefill_setup(hb_ctx* ctx);

@@ -484,7 +484,7 @@ bool hbk_moe_decode_fast(int H, int I) {
 
 size_t hbk_moe_decode_ws_bytes(int n, int H, int I) {
   if (n < 1) n = 1;
-  return 256 + al256((size_t)n * sizeof(Group)) + 5 * al256((size_t)n * 4) + al256((size_t)n * I * 2) + al256((size_t)n * H * 2);
+  return 256 + al256((size_t)n * sizeof(Group)) + 5 * al256((size_t)n * 4) + al256((size_t)n * I * 2) + al256((size_t)n * H * 2) + hbk_moe_dtc_ws_extra(n, H, I);
 }
 
 int hbk_moe_decode_setup(hb_ctx* ctx) {
@@ -499,7 +499,8 @@ int hbk_moe_decode_setup(hb_ctx* ctx) {
     }
   }
   {
-    const int rf = hbk_moe_fused_setup(ctx);
+    int rf = hbk_moe_fused_setup(ctx);
+    if (!rf) rf = hbk_moe_dtc_setup(ctx);
     if (rf) return rf;
   }
   HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_group_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -512,6 +513,11 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
   const bool routed = src.ids != nullptr;
   const int P = routed ? src.M * src.K + (src.shared_rec ? src.M : 0) : src.n_pairs;
   if (P <= 0) return HB_OK;
+  // routed form on a shape the tensor-memory layer kernel takes: two launches (prep, layer) instead of the streaming chain below
+  const bool want_tc = (ctx->flags & HB_FLAG_DECODE_TC) != 0;       // library default for now: the streaming chain
+  if (routed && want_tc && !red.ep && !src.wait_flags && hbk_moe_dtc_supported(H, I) && !(ctx->flags & (HB_FLAG_FUSED | HB_FLAG_DECODE_MMA_SYNC)) &&
+      hbk_moe_dtc_fits(ctx, P, src.E, H, I))
+    return hbk_moe_dtc_run(ctx, src, x, H, I, limit, red, ws, st);
   DecodeWs w = carve(ws, P, H, I);
   hb_rec_layout L;
   hb_rec_layout_make(H, I, &L);

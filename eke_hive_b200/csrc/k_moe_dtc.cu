@@ -1,0 +1,911 @@
+// Routed-expert decode on the block-scaled tensor cores: the NVFP4 records go from HBM through shared memory into
+// `tcgen05.mma kind::mxf4nvf4` untouched — no instruction ever handles a weight.
+//
+// The tensor core multiplies FP4 by FP4, the operators take bf16 activations (the reference's W4A16 arithmetic).  A bf16 row is
+// therefore written, exactly, as eight FP4 "digit planes": with the row's largest exponent E, every element is the integer
+// X = x / 2^(E-21) (|X| < 2^22; exact for elements down to 2^-15 of the row maximum, rounded to nearest below that — finer than
+// an fp32 accumulation resolves), and X = Σ_p d_p·8^(7-p) in balanced base 8, digits d_p ∈ {-4 … 4}, all of which e2m1 holds.
+// The eight planes are eight B-operand rows (block scales 1.0); the weights are the A operand with their own e4m3 block scales
+// applied by the tensor core; the accumulator columns of one activation row are recombined in fp32 by Horner's rule:
+//     Σ_k w_k·x_k = 2^(E-21) · Σ_p 8^(7-p) · D[·, p].
+// Every product is exact; sums are fp32.  Rounding points after the products are the reference's (g, u → bf16 after the global
+// scale, y → bf16, down → bf16, fp32 sum in k order).
+//
+// Two launches per layer:
+//   prep   one CTA per activation row: (optional) routing of the row, the row's digit planes; the last CTA to finish sorts the
+//          (row, expert) pairs into groups of ≤ 8 rows per expert and clears the hand-over flags
+//   layer  persistent CTAs, one per SM.  Work items: gate/up = (group, 64 rows of I: 64 gate rows + 64 up rows form one 128-row
+//          A tile), down = (group, 128 rows of H).  Items are dealt round-robin; a CTA's list interleaves the gate/up items of
+//          round r with the down items of the groups whose gate/up finished in round r-1, so no down item ever waits for a
+//          gate/up item that is not already done or in its last microseconds.  Per CTA: a TMA thread streams weight boxes
+//          (128 bytes × 64/128 rows, 128-byte swizzle) through tensor maps anchored below the records, a second thread brings the
+//          digit planes (pre-swizzled 1 KB atoms, plain bulk copies), four warps fetch the e4m3 scales two windows ahead and
+//          lay them out as the 32 × 16-byte chunks `tcgen05.cp` moves to tensor memory, one thread issues the MMAs
+//          (128 × N × 64, N = 16 … 64) into double-buffered accumulators, four warps run the epilogues: SwiGLU → y → (last
+//          finisher of a group) y's digit planes; down → bf16 partial rows → (last arriver of a row's 128-column block) the
+//          k-order sum and the shared-expert combine.
+// Every wait is bounded and reports through the context's error word.
+#include <cstdlib>
+
+#include "moe_stream.cuh"
+#include "router.cuh"
+#include "tc_common.cuh"
+
+namespace hb {
+
+constexpr int DT_ST = 8;                       // pipeline stages
+constexpr int DT_A = 16384;                    // weight tile of a stage: 128 rows × 128 bytes (256 k values)
+constexpr int DT_B = 8192;                     // digit planes of a stage: up to 64 rows × 128 bytes
+constexpr int DT_STAGE = DT_A + DT_B;
+constexpr int DT_RAWD = 3;                     // windows the scale fetch runs ahead of its use
+constexpr int DT_RAW = (DT_RAWD + 1) * 2048;   // ring of fetched scale rows: 128 rows × 16 bytes per window
+constexpr int DT_EX = 8 * 64 * 4;              // SwiGLU exchange: up values of 64 rows × 8 activation rows
+constexpr int DT_TBL = 256;                    // work-list entries a CTA can hold (16 bytes + 8 row indices + 8 row units each)
+constexpr int DT_SMEM = 1024 + DT_ST * DT_STAGE + DT_RAW + 2 * DT_EX + 512 + 1024 + DT_TBL * 64;
+constexpr int DT_THREADS = 16 * 32;            // warps 0-7 epilogues (two sets of four), then one warp each: MMA issue, weight TMA, digit copies,
+                                               // (one idle); warps 12-15 fetch the scales and store them into tensor memory
+constexpr int DT_W_MMA = 8, DT_W_TMA = 9, DT_W_DIG = 10, DT_W_SC0 = 12;   // warp 11 idles: the scale warps must be warps 0-3 modulo 4
+constexpr int DT_TMEM_COLS = 512;              // accumulators 2 × 64, weight scales 8 × 16, digit scales 4
+constexpr int DT_SFA_COL0 = 128, DT_SFB_COL = DT_SFA_COL0 + DT_ST * 16;
+constexpr int DT_VMAX = 32;                    // tensor-map variants per matrix kind (see DtcMeta)
+constexpr int DT_GU_ROWS = 64;                 // rows of I per gate/up item
+constexpr int DT_DN_ROWS = 128;                // rows of H per down item
+static_assert(DT_STAGE % 1024 == 0, "stage buffers keep the swizzle atom's alignment");
+static_assert(DT_SFB_COL + 4 <= DT_TMEM_COLS, "tensor memory");
+static_assert(DT_SMEM <= 227 * 1024, "shared memory");
+
+// Tensor maps for the weight boxes cannot be made per record ahead of time (the table may change between calls) and records sit
+// at arbitrary 4096-aligned addresses.  One map per matrix kind covers them all: a 2-D byte matrix [2^31 rows][pitch] whose base
+// lies 2^30 rows below the lowest record seen when the maps were made.  A matrix whose distance from that base is not a multiple
+// of the pitch uses variant v of the map, shifted by v·gcd(pitch, 4096) bytes (pitch / gcd variants cover every residue).
+struct DtcMeta { unsigned long long anchor[2]; };
+
+struct DtcWs {
+  uint8_t* xdig;        // [rows][H/256][8 planes][128 bytes], swizzled
+  uint8_t* ydig;        // [pairs][I/256][8][128]
+  float* xs;            // [rows] unit of a row's digits (a power of two)
+  float* ys;            // [pairs]
+  unsigned int* ready;  // [pairs] group g: y's digit planes are complete
+  unsigned int* fin;    // CTAs of the layer kernel whose partial rows are all written
+  uint16_t* g_row;      // [groups][8] activation rows of a group
+  float* g_unit;        // [groups][8] digit units of those rows
+};
+
+// Division of a 32-bit unsigned number by a divisor fixed for the whole launch: multiply-high and shift (exact for n < 2^31).
+struct DtDiv {
+  uint32_t d, m, l;
+  __host__ __device__ void set(uint32_t d_) {
+    d = d_; l = 0;
+    while ((1u << l) < d) ++l;
+    m = (uint32_t)(((1ull << 32) * ((1ull << l) - d)) / d + 1);
+  }
+  __device__ uint32_t div(uint32_t n) const { return (uint32_t)(((unsigned long long)__umulhi(n, m) + n) >> l); }
+};
+
+struct DtcArgs {
+  const int* hdr; const Group* groups; const int* s_row;
+  int H, I; float limit; int lag;
+  DtDiv dIT, dHT, dG;                                    // dividers by the items per group (gate/up, down) and by the grid size
+  hb_rec_layout L;
+  const CUtensorMap* maps; const DtcMeta* meta;          // maps[kind · DT_VMAX + variant], kind 0 = gate/up, 1 = down
+  int pitch[2], gstep[2], pshift[2];                     // pshift: log2(pitch) when the pitch divides 4096, else -1
+  DtcWs dw;
+  __nv_bfloat16* y; __nv_bfloat16* part;
+  unsigned int* done;
+  ReduceArgs red;
+  uint32_t* err;
+};
+
+// ---- digit planes ------------------------------------------------------------------------------------------------------------------
+// Eight consecutive bf16 values (v: four packed pairs) of a row whose largest biased exponent is eb → one 32-bit word per plane
+// (plane 0 = most significant digit), nibble j = element j as an e2m1 code.
+__device__ __forceinline__ void dt_digits8(const uint32_t (&v)[4], int eb, uint32_t (&plane)[8]) {
+#pragma unroll
+  for (int p = 0; p < 8; ++p) plane[p] = 0u;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t b = (v[j >> 1] >> (16 * (j & 1))) & 0xffffu;
+    const uint32_t ex = (b >> 7) & 0xffu;
+    const uint32_t mant = ex ? ((b & 0x7fu) | 0x80u) : (b & 0x7fu);
+    const int sh = (int)(ex ? ex : 1u) - eb + 14;                    // ≤ 14
+    uint32_t X;
+    if (sh >= 0) X = mant << sh;
+    else if (sh < -9) X = 0u;
+    else {                                                           // far below the row maximum: round to nearest even
+      const int s2 = -sh;
+      const uint32_t q = mant >> s2, rem = mant & ((1u << s2) - 1u), half = 1u << (s2 - 1);
+      X = q + ((rem > half || (rem == half && (q & 1u))) ? 1u : 0u);
+    }
+    const uint32_t Y = X + 0x924924u;                                // + 4 in every octal digit: digit t of Y is the balanced digit + 4
+    // e2m1 codes of t - 4 (positive element) or 4 - t (negative element), nibble t
+    const uint32_t tbl = (b & 0x8000u) ? 0xDCA02456u : 0x5420ACDEu;
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      const uint32_t t4 = ((Y >> (3 * (7 - p))) & 7u) << 2;
+      plane[p] |= ((tbl >> t4) & 0xfu) << (4 * j);
+    }
+  }
+}
+__device__ __forceinline__ int dt_row_exponent(uint32_t amax_bits) {   // biased exponent the digits are taken against
+  int eb = (int)(amax_bits >> 7) & 0xff;
+  return min(max(eb, 30), 254);                                       // tiny rows: keep the unit a normal float
+}
+__device__ __forceinline__ float dt_unit(int eb) { return __int_as_float((uint32_t)(eb - 21) << 23); }   // 2^(eb - 148)
+// where the word of plane p for elements [k0, k0 + 8) of row `r` goes (rows of K values)
+__device__ __forceinline__ size_t dt_dig_off(size_t r, int K, int k0, int p) {
+  const int kb = k0 >> 8, bo = ((k0 & 255) >> 3) << 2;
+  return ((r * (size_t)(K >> 8) + kb) * 8 + p) * 128 + (size_t)((((bo >> 4) ^ p) << 4) + (bo & 15));
+}
+
+// ---- the work list of a CTA -----------------------------------------------------------------------------------------------------------
+// Items: gate/up = (group g, rows [64 t, 64 t + 64) of I), down = (group g, rows [128 t, 128 t + 128) of H).  Gate/up item j of the
+// launch goes to CTA j mod grid in round j / grid; the down items of a group follow `lag` rounds after the round in which the
+// group's last gate/up item runs, dealt round-robin in their own numbering.  A CTA's list is: round 0's gate/up item, round 0's
+// down items, round 1's ….  Every CTA builds its list once, into shared memory, before its pipeline starts.
+struct DtEnt { const uint8_t* rec; int start; uint32_t info; };      // info: bit 0 kind, bits 1-4 rows of the group, bits 5-15 t, bits 16-31 g
+static_assert(sizeof(DtEnt) == 16, "DtEnt layout");
+__device__ __forceinline__ int ent_kind(const DtEnt& e) { return (int)(e.info & 1u); }
+__device__ __forceinline__ int ent_n(const DtEnt& e) { return (int)((e.info >> 1) & 15u); }
+__device__ __forceinline__ int ent_t(const DtEnt& e) { return (int)((e.info >> 5) & 0x7ffu); }
+__device__ __forceinline__ int ent_g(const DtEnt& e) { return (int)(e.info >> 16); }
+
+// One warp writes the CTA's list (info words only; records and row ranges are filled in afterwards by all threads).  Lane l takes
+// round r0 + l of each batch of 32 rounds; a prefix sum over the lanes places the rounds' items one after the other.
+// Down items are dealt so that every CTA streams about the same number of bytes: the gate/up items do not divide evenly over the
+// CTAs (rem "heavy" CTAs have one more than the others), so down item d goes, in this order of d, to
+//   d < D1           all CTAs in turn               (q_h passes: what a heavy CTA can take before it exceeds the mean)
+//   D1 ≤ d < D2      the light CTAs in turn         (the extra passes that bring them up to the mean)
+//   D2 ≤ d           all CTAs in turn               (what is left)
+__device__ int dt_build_list(DtEnt* tbl, int cap, int G, const DtDiv& dIT, const DtDiv& dHT, const DtDiv& dG, int sGU, int sDN, int c, int lag, int lane) {
+  const int nIT = (int)dIT.d, nHT = (int)dHT.d, grid = (int)dG.d;
+  const int nGU = G * nIT, nD = G * nHT, R = (int)dG.div(nGU + grid - 1), NR = R + lag;
+  const int gu_l = (int)dG.div(nGU), rem = nGU - gu_l * grid, L = grid - rem, gu_h = gu_l + (rem ? 1 : 0);
+  const int target = (int)dG.div((uint32_t)(nGU * sGU + nD * sDN));
+  const int q_h = max(0, (target - gu_h * sGU) / sDN), q_l = max(q_h, (target - gu_l * sGU) / sDN);
+  const int D1 = min(nD, q_h * grid), D2 = rem ? min(nD, D1 + (q_l - q_h) * L) : D1;
+  auto glo = [&](int q) { return q <= 0 ? 0 : min(G, (int)dIT.div((uint32_t)(q * grid))); };   // first group whose gate/up ends in round ≥ q
+  // this CTA's share of down items [lo, hi) inside one dealing region: first item and count
+  auto share = [&](int lo, int hi, int origin, int mod, int cc, int& first, int& cnt) {
+    first = hi; cnt = 0;
+    if (lo >= hi || cc < 0) return;
+    const int back = mod == grid ? (lo - origin) - (int)dG.div((uint32_t)(lo - origin)) * grid : (lo - origin) % mod;
+    first = lo + (cc >= back ? cc - back : cc - back + mod);
+    if (first < hi) cnt = mod == grid ? (int)dG.div((uint32_t)(hi - first + grid - 1)) : (hi - first + mod - 1) / mod;
+  };
+  int base = 0;
+  for (int r0 = 0; r0 < NR; r0 += 32) {
+    const int r = r0 + lane;
+    int has_gu = 0, j = 0, f[3] = {0, 0, 0}, n3[3] = {0, 0, 0};
+    if (r < NR) {
+      j = r * grid + c;
+      has_gu = j < nGU ? 1 : 0;
+      if (r >= lag) {
+        const int lo = glo(r - lag) * nHT, hi = glo(r - lag + 1) * nHT;
+        share(min(lo, D1), min(hi, D1), 0, grid, c, f[0], n3[0]);
+        share(min(max(lo, D1), D2), min(max(hi, D1), D2), D1, L, c - rem, f[1], n3[1]);
+        share(max(lo, D2), max(hi, D2), D2, grid, c, f[2], n3[2]);
+      }
+    }
+    const int cnt = has_gu + n3[0] + n3[1] + n3[2];
+    int inc = cnt;
+    for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += t; }
+    int off = base + inc - cnt;
+    base += __shfl_sync(0xffffffffu, inc, 31);
+    if (off + cnt <= cap) {
+      if (has_gu) { const int g = (int)dIT.div((uint32_t)j); tbl[off++].info = 0u | ((uint32_t)(j - g * nIT) << 5) | ((uint32_t)g << 16); }
+#pragma unroll
+      for (int sgm = 0; sgm < 3; ++sgm) {
+        const int mod = sgm == 1 ? L : grid;
+        for (int i = 0, d = f[sgm]; i < n3[sgm]; ++i, d += mod) { const int g = (int)dHT.div((uint32_t)d); tbl[off++].info = 1u | ((uint32_t)(d - g * nHT) << 5) | ((uint32_t)g << 16); }
+      }
+    }
+  }
+  return base;
+}
+
+// Optional in-kernel timing (compile with -DHB_DTC_TRACE): every role of every CTA sums the clocks it spends in each kind of wait.
+#ifdef HB_DTC_TRACE
+__device__ long long g_dt_trace[256 * 32];
+#define DT_TIMED(acc, stmt) do { const long long t_ = clock64(); stmt; acc += clock64() - t_; } while (0)
+#define DT_TRACE_PUT(slot, v) g_dt_trace[blockIdx.x * 32 + (slot)] = (v)
+__device__ long long g_dt_stage[2 * 128 * 8];
+#define DT_STAMP(it, col) do { if ((blockIdx.x == 0 || blockIdx.x == 77) && (it) < 128) g_dt_stage[((blockIdx.x ? 1 : 0) * 128 + (it)) * 8 + (col)] = clock64(); } while (0)
+#else
+#define DT_TIMED(acc, stmt) do { stmt; } while (0)
+#define DT_TRACE_PUT(slot, v) do { } while (0)
+#define DT_STAMP(it, col) do { } while (0)
+#endif
+
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ uint32_t ld_acquire_u32(const unsigned int* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_u32(unsigned int* p, uint32_t v) { asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+
+// ---- the layer kernel -------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcArgs a) {
+  extern __shared__ uint8_t dt_raw[];
+  const uint32_t raw = smem_u32(dt_raw), base = (raw + 1023u) & ~1023u;
+  uint8_t* sm = dt_raw + (base - raw);
+  uint8_t* rawsc = sm + DT_ST * DT_STAGE;                                       // fetched scale rows
+  float* ex_all = reinterpret_cast<float*>(rawsc + DT_RAW);                     // [2 sets][8][64]
+  uint8_t* sfb1 = reinterpret_cast<uint8_t*>(ex_all) + 2 * DT_EX;               // 32 × 16 bytes of 1.0 (e4m3 0x38)
+  uint64_t* full = reinterpret_cast<uint64_t*>(sfb1 + 512);                     // [ST] weights and digits of the stage are in shared memory, its scales in tensor memory
+  uint64_t* empty = full + DT_ST;                                               // [ST] the MMAs that read the stage are done
+  uint64_t* acc_full = empty + DT_ST;                                           // [2]
+  uint64_t* acc_empty = acc_full + 2;                                           // [2]
+  uint64_t* mma_done = acc_empty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mma_done + 1);
+  int* n_items_s = reinterpret_cast<int*>(tmem_slot + 1);
+  volatile int* flag_all = reinterpret_cast<volatile int*>(n_items_s + 1);      // [2 sets][16] epilogue hand-over words: [0] last finisher, [8..15] row maxima
+  float* rowsc = reinterpret_cast<float*>(const_cast<int*>(flag_all) + 32);     // [16 items in flight][8] units of the item's activation rows
+  DtEnt* tbl = reinterpret_cast<DtEnt*>(sfb1 + 512 + 1024);                     // [DT_TBL] this CTA's work list
+  uint16_t* tbl_row = reinterpret_cast<uint16_t*>(tbl + DT_TBL);                // [DT_TBL][8] activation rows of the item's group
+  float* tbl_unit = reinterpret_cast<float*>(tbl_row + DT_TBL * 8);             // [DT_TBL][8] digit units of those rows (gate/up items)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  [[maybe_unused]] const long long t_k0 = clock64();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < DT_ST; ++s) { mbar_init(&full[s], 128 + 2); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+    mbar_init(mma_done, 1);
+    mbar_fence_init();
+  }
+  if (threadIdx.x < 128) { reinterpret_cast<uint32_t*>(sfb1)[threadIdx.x] = 0x38383838u; fence_proxy_async_smem(); }
+  if (warp == DT_W_MMA) { tmem_alloc(tmem_slot, DT_TMEM_COLS); tmem_relinquish(); }
+  griddep_wait();                                                               // the prep kernel's lists, digit planes and cleared flags
+  griddep_launch();
+  [[maybe_unused]] const long long t_k1 = clock64();
+  const int nIT = a.I / DT_GU_ROWS, nHT = a.H / DT_DN_ROWS;
+  if (warp == 0) {
+    int n = dt_build_list(tbl, DT_TBL, a.hdr[0], a.dIT, a.dHT, a.dG, a.H >> 8, a.I >> 8, (int)blockIdx.x, a.lag & 255, lane);
+    if (n > DT_TBL) { if (lane == 0) atomicOr(a.err, 0x1000u); n = 0; }         // the launcher sizes the grid so that this does not happen
+    if (lane == 0) *n_items_s = n;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const int n_items = *n_items_s;
+  for (int j = threadIdx.x; j < n_items * kGroupRows; j += DT_THREADS) {       // records, row ranges, activation rows and their digit units
+    const int i = j >> 3, c = j & 7;
+    const uint32_t info = tbl[i].info;
+    const size_t gj = (size_t)(info >> 16) * kGroupRows + c;
+    tbl_row[j] = a.dw.g_row[gj]; tbl_unit[j] = a.dw.g_unit[gj];
+    if (c == 0) {
+      const Group g = a.groups[info >> 16];
+      tbl[i].rec = g.rec; tbl[i].start = g.start; tbl[i].info = info | ((uint32_t)g.n << 1);
+    }
+  }
+  __syncthreads();
+  [[maybe_unused]] const long long t_k2 = clock64();
+
+  if (warp == DT_W_TMA) {
+    // ------------------------------------------------------------------------------------------------ weight boxes: one thread
+    if (lane == 0) {
+      uint32_t it = 0, seen[2] = {0u, 0u};
+      bool ok = true;
+      [[maybe_unused]] long long tw = 0, t_begin = clock64();
+      const unsigned long long anchor[2] = {a.meta->anchor[0], a.meta->anchor[1]};
+      const int up_rows = (int)((a.L.w3 - a.L.w1) / (unsigned long long)a.pitch[0]);
+      for (int ii = 0; ii < n_items && ok; ++ii) {
+        const DtEnt e = tbl[ii];
+        const int k = ent_kind(e);
+        const unsigned long long addr = reinterpret_cast<unsigned long long>(e.rec) + (k ? a.L.w2 : a.L.w1), delta = addr - anchor[k];
+        unsigned long long row;
+        int v = 0;
+        if (a.pshift[k] >= 0) row = delta >> a.pshift[k];                          // the pitch divides 4096: every matrix is a whole number of rows above the anchor
+        else {
+          const unsigned long long rem = delta % (unsigned long long)a.pitch[k];
+          row = (delta - rem) / (unsigned long long)a.pitch[k];
+          v = (int)(rem / (unsigned long long)a.gstep[k]);
+          if (rem % (unsigned long long)a.gstep[k] || v >= DT_VMAX) { atomicOr(a.err, 0x400000u); break; }
+        }
+        if (addr < anchor[k] || row + (1ull << 24) >= (1ull << 31)) { atomicOr(a.err, 0x400000u); break; }
+        const CUtensorMap* map = a.maps + k * DT_VMAX + v;
+        if (!((seen[k] >> v) & 1u)) { tmap_acquire(map); seen[k] |= 1u << v; }
+        const int r0 = (int)row + ent_t(e) * (k ? DT_DN_ROWS : DT_GU_ROWS), r1 = r0 + up_rows;
+        const int nkb = (k ? a.I : a.H) >> 8;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const uint32_t stage = it % DT_ST;
+          DT_TIMED(tw, ok = mbar_wait(&empty[stage], ((it / DT_ST) & 1) ^ 1, a.err, 0x1u));
+          if (!ok) break;
+          DT_STAMP(it, 0);
+          const uint32_t sb = base + stage * DT_STAGE;
+          mbar_expect_tx(&full[stage], DT_A);
+          if (k) tma_load_2d(sb, map, kb * 128, r0, &full[stage]);
+          else { tma_load_2d(sb, map, kb * 128, r0, &full[stage]); tma_load_2d(sb + DT_A / 2, map, kb * 128, r1, &full[stage]); }
+          DT_STAMP(it, 1);
+        }
+      }
+      DT_TRACE_PUT(0, tw); DT_TRACE_PUT(1, clock64() - t_begin); DT_TRACE_PUT(2, (long long)it);
+    }
+  } else if (warp == DT_W_DIG) {
+    // ------------------------------------------------------------------------------------------------ digit planes: one thread
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      [[maybe_unused]] long long tw = 0, tr = 0;
+      for (int ii = 0; ii < n_items && ok; ++ii) {
+        const DtEnt e = tbl[ii];
+        const int k = ent_kind(e), n = ent_n(e), nkb = (k ? a.I : a.H) >> 8;
+        const uint8_t* src[kGroupRows];
+        float unit[kGroupRows];
+        if (k) {                                                                  // y's planes exist once the group's gate/up items are all through
+          [[maybe_unused]] const long long t_ = clock64();
+          uint32_t spins = 0;
+          while (!(a.lag & 256) && ld_acquire_u32(a.dw.ready + ent_g(e)) == 0u) {
+            if (++spins > (1u << 22)) { atomicOr(a.err, 0x20u); ok = false; break; }
+            __nanosleep(40);
+          }
+          fence_proxy_async_all();                                                // the planes were written with ordinary stores, the copies below read them through the async proxy
+#ifdef HB_DTC_TRACE
+          tr += clock64() - t_;
+#endif
+          if (!ok) break;
+          for (int c = 0; c < n; ++c) { src[c] = a.dw.ydig + (size_t)(e.start + c) * nkb * 1024; unit[c] = __ldcg(a.dw.ys + e.start + c); }
+        } else {
+          for (int c = 0; c < n; ++c) { src[c] = a.dw.xdig + (size_t)tbl_row[ii * 8 + c] * nkb * 1024; unit[c] = tbl_unit[ii * 8 + c]; }
+        }
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const uint32_t stage = it % DT_ST;
+          DT_TIMED(tw, ok = mbar_wait(&empty[stage], ((it / DT_ST) & 1) ^ 1, a.err, 0x2u));
+          if (!ok) break;
+          DT_STAMP(it, 3);
+          // the rows' units travel to the epilogue through shared memory, ordered by the barrier of the item's last stage behind them
+          // (a down item's units are loaded above and only needed here: the copies of its earlier stages do not wait for them)
+          if (kb == nkb - 1) for (int c = 0; c < n; ++c) rowsc[(ii & 15) * 8 + c] = unit[c];
+          uint8_t* sb = sm + stage * DT_STAGE + DT_A;
+          mbar_expect_tx(&full[stage], (uint32_t)n * 1024u);
+          for (int c = 0; c < n; ++c) bulk_g2s(sb + c * 1024, src[c] + (size_t)kb * 1024, 1024, &full[stage]);
+          DT_STAMP(it, 7);
+        }
+      }
+      DT_TRACE_PUT(3, tw); DT_TRACE_PUT(4, tr);
+    }
+  } else if (warp >= DT_W_SC0) {
+    // ------------------------------------------------------------------------------------------------ weight scales: thread r owns row r of each A tile
+    // A row's 16 scale bytes of a window = 4 k-steps × 4 scales.  In tensor memory the scales of a k-step take four columns; the
+    // tensor core reads, for the accumulator rows of lane quarter q, column q of those four: lane l there holds the 4 scales of row
+    // 32 q + l — which is this thread's own row.  Each thread copies its row's 16 bytes asynchronously DT_RAWD windows ahead (a
+    // cursor of its own over the same work list) and stores the four words with one tcgen05.st into its own lane.
+    const int r = threadIdx.x - DT_W_SC0 * 32, q = r >> 5;
+    const uint32_t sf_lane = tmem + ((uint32_t)(q * 32) << 16);
+    const uint8_t* prow = nullptr;
+    int pii = 0, pkb = 0, pnkb = 0;
+    uint32_t pw = 0;
+    auto prefetch = [&]() {
+      if (pkb == pnkb) {
+        prow = nullptr;
+        if (pii < n_items) {
+          const DtEnt e = tbl[pii++];
+          if (ent_kind(e)) { prow = e.rec + a.L.s2 + (size_t)(ent_t(e) * DT_DN_ROWS + r) * (a.I / 16); pnkb = a.I >> 8; }
+          else { prow = e.rec + (r < 64 ? a.L.s1 : a.L.s3) + (size_t)(ent_t(e) * DT_GU_ROWS + (r & 63)) * (a.H / 16); pnkb = a.H >> 8; }
+          pkb = 0;
+        }
+      }
+      if (prow) { pf_cp16(smem_u32(rawsc + (pw % (DT_RAWD + 1)) * 2048 + r * 16), prow + (size_t)pkb * 16); ++pkb; }
+      pf_cp_commit();
+      ++pw;
+    };
+#pragma unroll
+    for (int i = 0; i < DT_RAWD; ++i) prefetch();
+    uint32_t it = 0;
+    bool ok = true;
+    [[maybe_unused]] long long tw = 0, tg = 0;
+    for (int ii = 0; ii < n_items && ok; ++ii) {
+      const int nkb = (ent_kind(tbl[ii]) ? a.I : a.H) >> 8;
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        prefetch();
+        DT_TIMED(tg, pf_cp_wait<DT_RAWD>());                                       // this window's own 16 bytes have landed
+        const uint4 v = *reinterpret_cast<const uint4*>(rawsc + (it % (DT_RAWD + 1)) * 2048 + r * 16);
+        const uint32_t stage = it % DT_ST;
+        DT_TIMED(tw, ok = mbar_wait(&empty[stage], ((it / DT_ST) & 1) ^ 1, a.err, 0x4u));   // the MMAs that read this stage's scale columns are done
+        if (!ok) break;
+        tc_fence_after();
+        // the word of k-step j goes to column 4 j + q of this thread's own lane; the other columns of the quarter are never read
+        uint32_t w16[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) w16[i] = 0u;
+        const uint32_t vj[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+          for (int qq = 0; qq < 4; ++qq) if (qq == q) w16[4 * j + qq] = vj[j];
+        }
+        tc_st16(sf_lane + DT_SFA_COL0 + stage * 16, w16);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&full[stage]);
+        if (r == 0) DT_STAMP(it, 2);
+      }
+    }
+    pf_cp_wait<0>();
+    if (r == 0) { DT_TRACE_PUT(5, tw); DT_TRACE_PUT(6, tg); }
+  } else if (warp == DT_W_MMA) {
+    // ------------------------------------------------------------------------------------------------ MMA issue: one thread
+    if (lane == 0) {
+      tc_cp_sf(tmem + DT_SFB_COL, tc_desc_sf(smem_u32(sfb1)));                  // block scales of the digit planes: 1.0 everywhere
+      uint32_t it = 0;
+      bool ok = true;
+      [[maybe_unused]] long long tf = 0, te = 0, t_begin = clock64();
+      for (int ii = 0; ii < n_items && ok; ++ii) {
+        const DtEnt e = tbl[ii];
+        const uint32_t n_eff = (uint32_t)((ent_n(e) + 1) >> 1) * 16u, buf = (uint32_t)ii & 1u;
+        const uint32_t idesc = (1u << 7) | (1u << 10) | ((n_eff >> 3) << 17) | ((128u >> 4) << 24);
+        if (ii >= 2) DT_TIMED(te, ok = mbar_wait(&acc_empty[buf], ((ii >> 1) - 1) & 1, a.err, 0x8u));
+        if (!ok) break;
+        tc_fence_after();
+        const int nkb = (ent_kind(e) ? a.I : a.H) >> 8;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const uint32_t stage = it % DT_ST;
+          DT_TIMED(tf, ok = mbar_wait(&full[stage], (it / DT_ST) & 1, a.err, 0x10u));
+          if (!ok) break;
+          DT_STAMP(it, 5);
+          tc_fence_after();
+          const uint32_t sb = base + stage * DT_STAGE, sfc = tmem + DT_SFA_COL0 + stage * 16;
+          const uint64_t ad = tc_desc_sw128(sb), bd = tc_desc_sw128(sb + DT_A);
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j)
+            tc_mma_nvf4(tmem + buf * 64, ad + 2 * j, bd + 2 * j, idesc, sfc + 4 * j, tmem + DT_SFB_COL, (kb | (int)j) != 0 ? 1u : 0u);
+          tc_commit(&empty[stage]);
+          DT_STAMP(it, 6);
+        }
+        if (ok) tc_commit(&acc_full[buf]);
+      }
+      tc_commit(mma_done);                                                       // nothing of this thread's is in flight when tensor memory is freed
+      mbar_wait(mma_done, 0, a.err, 0x40u);
+      DT_TRACE_PUT(7, tf); DT_TRACE_PUT(8, te); DT_TRACE_PUT(9, clock64() - t_begin); DT_TRACE_PUT(10, (long long)n_items);
+    }
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------------------------------------ epilogues: two sets of four warps, set s takes the items whose
+    // accumulator buffer is s; warp q of a set reads tensor-memory lanes [32 q, 32 q + 32)
+    const int set = warp >> 2, tl = threadIdx.x & 127;                           // tl = row of the A tile
+    const int bar_id = 1 + set;
+    float* ex = ex_all + set * (DT_EX / 4);
+    volatile int* flag = flag_all + set * 16;
+    const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16) + set * 64;
+    bool ok = true;
+    [[maybe_unused]] long long ta = 0, tgu = 0, tdn = 0, tdig = 0;
+    for (int ii = set; ii < n_items && ok; ii += 2) {
+      const DtEnt e = tbl[ii];
+      const int n = ent_n(e), kind = ent_kind(e), t = ent_t(e), g = ent_g(e);
+      const float* gp = reinterpret_cast<const float*>(e.rec + a.L.g);
+      const float gsc = __ldg(gp + (kind ? 2 : (tl < 64 ? 0 : 1)));               // the record's global scale this thread applies
+      DT_TIMED(ta, ok = mbar_wait(&acc_full[set], (ii >> 1) & 1, a.err, 0x80u));
+      if (!ok) break;
+      const float* units = rowsc + (ii & 15) * 8;
+      [[maybe_unused]] const long long t_item = clock64();
+      tc_fence_after();
+      float val[kGroupRows];
+#pragma unroll
+      for (int c2 = 0; c2 < kGroupRows / 2; ++c2) {
+        val[2 * c2] = val[2 * c2 + 1] = 0.f;
+        if (2 * c2 < n) {
+          uint32_t rr[16];
+          tc_ld16(trow + 16 * c2, rr);
+          tc_wait_ld();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            float acc = __uint_as_float(rr[8 * h]);
+#pragma unroll
+            for (int p = 1; p < 8; ++p) acc = __fmaf_rn(acc, 8.f, __uint_as_float(rr[8 * h + p]));
+            val[2 * c2 + h] = acc;
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[set]);
+      if (kind == 0) {
+        // gate rows in lanes 0-63 (warps 0, 1 of the set), up rows in lanes 64-127 (warps 2, 3): up values cross through shared memory
+        float gu[kGroupRows];
+#pragma unroll
+        for (int c = 0; c < kGroupRows; ++c) {
+          gu[c] = 0.f;
+          if (c < n) gu[c] = bf16r(val[c] * units[c] * gsc);
+        }
+        if (tl >= 64) {
+#pragma unroll
+          for (int c = 0; c < kGroupRows; ++c) if (c < n) ex[c * 64 + (tl - 64)] = gu[c];
+        }
+        named_bar_sync(bar_id, 128);
+        if (tl < 64) {
+          const int i = t * DT_GU_ROWS + tl;
+#pragma unroll
+          for (int c = 0; c < kGroupRows; ++c) {
+            if (c < n) {
+              float gv = gu[c], uv = ex[c * 64 + tl];
+              if (a.limit > 0.f) { uv = fminf(fmaxf(uv, -a.limit), a.limit); gv = fminf(gv, a.limit); }
+              a.y[(size_t)(e.start + c) * a.I + i] = __float2bfloat16(gv / (1.f + __expf(-gv)) * uv);
+            }
+          }
+        }
+        named_bar_sync(bar_id, 128);
+        if (tl == 0) { __threadfence(); flag[0] = atomicAdd(a.done + g, 1u) == (unsigned)(nIT - 1) ? 1 : 0; }
+        named_bar_sync(bar_id, 128);
+        [[maybe_unused]] const long long t_dig = clock64();
+        if (flag[0]) {
+          // this CTA finished the group's last gate/up item: every y row of the group is complete — write its digit planes
+          __threadfence();
+          if (tl < kGroupRows) flag[8 + tl] = 0;
+          named_bar_sync(bar_id, 128);
+          // all (row, 8 values) units of the group at once: the first four of a thread stay in registers between the two passes
+          const int U = a.I / 8, total = n * U;
+          uint4 keep[4];
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            const int idx = tl + 128 * k4;
+            keep[k4] = make_uint4(0u, 0u, 0u, 0u);
+            if (idx < total) {
+              const int c = idx / U, u = idx - c * U;
+              keep[k4] = __ldcg(reinterpret_cast<const uint4*>(a.y + (size_t)(e.start + c) * a.I) + u);
+              const uint32_t w4[4] = {keep[k4].x, keep[k4].y, keep[k4].z, keep[k4].w};
+              uint32_t am = 0;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) am = max(am, max(w4[j] & 0x7fffu, (w4[j] >> 16) & 0x7fffu));
+              atomicMax(const_cast<int*>(flag) + 8 + c, (int)am);
+            }
+          }
+          for (int idx = tl + 512; idx < total; idx += 128) {
+            const int c = idx / U, u = idx - c * U;
+            const uint4 q4 = __ldcg(reinterpret_cast<const uint4*>(a.y + (size_t)(e.start + c) * a.I) + u);
+            const uint32_t w4[4] = {q4.x, q4.y, q4.z, q4.w};
+            uint32_t am = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) am = max(am, max(w4[j] & 0x7fffu, (w4[j] >> 16) & 0x7fffu));
+            atomicMax(const_cast<int*>(flag) + 8 + c, (int)am);
+          }
+          named_bar_sync(bar_id, 128);
+          if (tl < n) a.dw.ys[e.start + tl] = dt_unit(dt_row_exponent((uint32_t)flag[8 + tl]));
+          for (int idx = tl; idx < total; idx += 128) {
+            const int c = idx / U, u = idx - c * U, k4 = idx >> 7;
+            uint4 q4;
+            if (k4 == 0) q4 = keep[0]; else if (k4 == 1) q4 = keep[1]; else if (k4 == 2) q4 = keep[2]; else if (k4 == 3) q4 = keep[3];
+            else q4 = __ldcg(reinterpret_cast<const uint4*>(a.y + (size_t)(e.start + c) * a.I) + u);
+            const uint32_t v4[4] = {q4.x, q4.y, q4.z, q4.w};
+            uint32_t pl[8];
+            dt_digits8(v4, dt_row_exponent((uint32_t)flag[8 + c]), pl);
+#pragma unroll
+            for (int p = 0; p < 8; ++p) *reinterpret_cast<uint32_t*>(a.dw.ydig + dt_dig_off((size_t)(e.start + c), a.I, u * 8, p)) = pl[p];
+          }
+          fence_proxy_async_all();
+          named_bar_sync(bar_id, 128);
+          if (tl == 0) { __threadfence(); st_release_u32(a.dw.ready + g, 1u); }
+        }
+#ifdef HB_DTC_TRACE
+        tdig += clock64() - t_dig; tgu += clock64() - t_item;
+#endif
+      } else {
+        const int h = t * DT_DN_ROWS + tl;
+#pragma unroll
+        for (int c = 0; c < kGroupRows; ++c)
+          if (c < n) a.part[(size_t)(e.start + c) * a.H + h] = __float2bfloat16(val[c] * units[c] * gsc);
+#ifdef HB_DTC_TRACE
+        tdn += clock64() - t_item;
+#endif
+      }
+    }
+    if (tl == 0 && set == 0) { DT_TRACE_PUT(11, ta); DT_TRACE_PUT(12, tgu); DT_TRACE_PUT(13, tdn); DT_TRACE_PUT(14, tdig); }
+  }
+  tc_fence_before();
+  __syncthreads();
+  [[maybe_unused]] const long long t_k3 = clock64();
+  if (warp == DT_W_MMA) { tc_fence_after(); tmem_dealloc(tmem, DT_TMEM_COLS); }
+  // ---- every CTA's partial rows are written once all CTAs have come this far: then the k-order sums, one (row, 128 columns) block per
+  // group of 64 threads.  A group fetches its first block's positions and weights before it waits.
+  const int blocks = a.red.M * nHT, sub = threadIdx.x >> 6, l64 = threadIdx.x & 63, nsub = DT_THREADS / 64;
+  const int b0 = (int)blockIdx.x + sub * (int)gridDim.x;
+  int pre_pos[17];
+  float pre_w[16];
+  const bool pre = b0 < blocks && a.red.K <= 16;
+  if (pre) {
+    const int m = b0 / nHT;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) { pre_pos[k] = k < a.red.K ? a.red.pos_of[m * a.red.K + k] : -1; pre_w[k] = k < a.red.K ? a.red.pw[m * a.red.K + k] : 0.f; }
+    pre_pos[16] = a.red.shared_pairs ? a.red.pos_of[a.red.M * a.red.K + m] : -1;
+  }
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(a.dw.fin, 1u);
+    uint32_t spins = 0;
+    while (ld_acquire_u32(a.dw.fin) < gridDim.x) {
+      if (++spins > (1u << 22)) { atomicOr(a.err, 0x800u); break; }
+      __nanosleep(40);
+    }
+  }
+  __syncthreads();
+  [[maybe_unused]] const long long t_k4 = clock64();
+  for (int b = b0; b < blocks && !(a.lag & 512); b += nsub * (int)gridDim.x) {
+    const int m = b / nHT, ht = b - m * nHT;
+    const size_t unit = (size_t)m * (a.H / 2) + (size_t)ht * (DT_DN_ROWS / 2) + l64;
+    if (b == b0 && pre) reduce_routed_unit(a.red, unit, pre_pos, pre_w);
+    else reduce_routed_unit(a.red, unit);
+  }
+  if (threadIdx.x == 0) { DT_TRACE_PUT(20, t_k1 - t_k0); DT_TRACE_PUT(21, t_k2 - t_k1); DT_TRACE_PUT(22, t_k3 - t_k2); DT_TRACE_PUT(23, t_k4 - t_k3); DT_TRACE_PUT(24, clock64() - t_k4); }
+}
+
+// ---- the prep kernel --------------------------------------------------------------------------------------------------------------------
+struct DtPrepArgs {
+  int route; const float* logits; int ld, renorm, logits_bf16; const float* bias; float sig_scale;
+  int32_t* ids; float* w; int ld_ids;
+  int M, K, E; const uint8_t* const* tab; int li; const uint8_t* shared_rec; int sh_row0, sh_rows;
+  const __nv_bfloat16* x; int x_ld; int H, I;
+  DecodeWs ws; DtcWs dw;
+  unsigned int* arrive;          // context-owned counter (zero between calls)
+};
+
+constexpr int DT_PREP_THREADS = 256;
+
+__device__ void dt_block_scan2(int* a, int* b, int n, int* tot_a, int* tot_b, int* warp_tmp /* [2][32] */) {
+  const int nt = blockDim.x, per = (n + nt - 1) / nt;
+  const int i0 = min(n, (int)threadIdx.x * per), i1 = min(n, i0 + per);
+  int sa = 0, sb = 0;
+  for (int i = i0; i < i1; ++i) { sa += a[i]; sb += b[i]; }
+  int xa = sa, xb = sb;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = nt >> 5;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int ta = __shfl_up_sync(0xffffffffu, xa, o), tb = __shfl_up_sync(0xffffffffu, xb, o);
+    if (lane >= o) { xa += ta; xb += tb; }
+  }
+  if (lane == 31) { warp_tmp[warp] = xa; warp_tmp[32 + warp] = xb; }
+  __syncthreads();
+  if (warp == 0) {
+    int va = lane < nw ? warp_tmp[lane] : 0, vb = lane < nw ? warp_tmp[32 + lane] : 0;
+    const int ia = va, ib = vb;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int ta = __shfl_up_sync(0xffffffffu, va, o), tb = __shfl_up_sync(0xffffffffu, vb, o);
+      if (lane >= o) { va += ta; vb += tb; }
+    }
+    warp_tmp[lane] = va - ia; warp_tmp[32 + lane] = vb - ib;
+    if (lane == 31) { *tot_a = va; *tot_b = vb; }
+  }
+  __syncthreads();
+  int ba = warp_tmp[warp] + xa - sa, bb = warp_tmp[32 + warp] + xb - sb;
+  for (int i = i0; i < i1; ++i) { const int ca = a[i], cb = b[i]; a[i] = ba; b[i] = bb; ba += ca; bb += cb; }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(DT_PREP_THREADS) moe_dtc_prep_kernel(const DtPrepArgs a) {
+  extern __shared__ __align__(16) uint8_t psm[];
+  __shared__ int s_red[8];
+  __shared__ int s_last;
+  const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int32_t my_id = 0;
+  float my_w = 0.f;
+  if (a.route && warp == 0) {
+    // the row's routing reads only the logits: it runs before the previous kernel of the stream is waited for
+    int32_t* sid = reinterpret_cast<int32_t*>(psm);
+    float* sw = reinterpret_cast<float*>(psm) + 16;
+    float* scratch = reinterpret_cast<float*>(psm) + 32;
+    if (a.route == 1) route_softmax_row(a.logits + (size_t)m * a.ld, a.E, a.K, a.renorm, a.logits_bf16, scratch, lane, sid, sw);
+    else route_sigmoid_row(a.logits + (size_t)m * a.ld, a.bias, a.E, a.K, a.sig_scale, scratch, lane, sid, sw);
+    __syncwarp();
+    if (lane < a.K) { my_id = sid[lane]; my_w = sw[lane]; }
+  }
+  griddep_wait();
+  griddep_launch();
+  if (a.route && warp == 0 && lane < a.K) { a.ids[(size_t)m * a.K + lane] = my_id; a.w[(size_t)m * a.K + lane] = my_w; }
+  // digit planes of row m
+  {
+    const uint32_t* xr = reinterpret_cast<const uint32_t*>(a.x + (size_t)m * a.x_ld);
+    uint32_t am = 0;
+    for (int e2 = threadIdx.x; e2 < a.H / 2; e2 += blockDim.x) { const uint32_t w2 = __ldg(xr + e2); am = max(am, max(w2 & 0x7fffu, (w2 >> 16) & 0x7fffu)); }
+    for (int o = 16; o > 0; o >>= 1) am = max(am, __shfl_xor_sync(0xffffffffu, am, o));
+    if (lane == 0) s_red[warp] = (int)am;
+    __syncthreads();
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) am = max(am, (uint32_t)s_red[i]);
+    const int eb = dt_row_exponent(am);
+    if (threadIdx.x == 0) a.dw.xs[m] = dt_unit(eb);
+    for (int u = threadIdx.x; u < a.H / 8; u += blockDim.x) {
+      const uint4 q4 = __ldg(reinterpret_cast<const uint4*>(xr) + u);
+      const uint32_t v4[4] = {q4.x, q4.y, q4.z, q4.w};
+      uint32_t pl[8];
+      dt_digits8(v4, eb, pl);
+#pragma unroll
+      for (int p = 0; p < 8; ++p) *reinterpret_cast<uint32_t*>(a.dw.xdig + dt_dig_off((size_t)m, a.H, u * 8, p)) = pl[p];
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(a.arrive, 1u) == gridDim.x - 1 ? 1 : 0;
+  __syncthreads();
+  if (!s_last) return;
+  // ---- the last CTA: every row's ids and weights are written — sort the pairs by expert into groups of ≤ 8 rows
+  __threadfence();
+  if (threadIdx.x == 0) *a.arrive = 0u;
+  const int P = a.M * a.K + (a.shared_rec ? a.M : 0), NK = a.E + 1;
+  int* key = reinterpret_cast<int*>(psm);                  // [P]
+  int* cnt = key + P;                                      // [NK] → exclusive offsets
+  int* ngr = cnt + NK;                                     // [NK] → exclusive group bases
+  int* fill = ngr + NK;                                    // [NK]
+  int* misc = fill + NK;                                   // [66]
+  for (int k = threadIdx.x; k < NK; k += blockDim.x) { cnt[k] = 0; fill[k] = 0; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < P; i += blockDim.x) {
+    int row, kk = -1;
+    float wv;
+    if (i < a.M * a.K) {
+      row = i / a.K;
+      const size_t src = (size_t)row * a.ld_ids + (i - row * a.K);
+      const int e = __ldcg(a.ids + src);
+      wv = __ldcg(a.w + src);
+      if (e >= 0 && e < a.E && a.tab[(size_t)a.li * a.E + e] != nullptr) kk = e;
+    } else { row = i - a.M * a.K; wv = 1.f; kk = row >= a.sh_row0 && row < a.sh_row0 + a.sh_rows ? a.E : -1; }
+    key[i] = kk; a.ws.prow[i] = row; a.ws.pw[i] = wv;
+    if (kk >= 0) atomicAdd(&cnt[kk], 1);
+  }
+  __syncthreads();
+  for (int k = threadIdx.x; k < NK; k += blockDim.x) { ngr[k] = (cnt[k] + kGroupRows - 1) / kGroupRows; fill[k] = cnt[k]; }
+  __syncthreads();
+  dt_block_scan2(cnt, ngr, NK, &misc[64], &misc[65], misc);
+  for (int k = threadIdx.x; k < NK; k += blockDim.x) {
+    const int c = fill[k];
+    if (c == 0) continue;
+    const uint8_t* rec = k == a.E ? a.shared_rec : a.tab[(size_t)a.li * a.E + k];
+    for (int j = 0; j * kGroupRows < c; ++j) a.ws.groups[ngr[k] + j] = Group{rec, cnt[k] + j * kGroupRows, min(kGroupRows, c - j * kGroupRows)};
+  }
+  __syncthreads();
+  for (int k = threadIdx.x; k < NK; k += blockDim.x) fill[k] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < P; i += blockDim.x) {
+    const int kk = key[i];
+    int pos = -1;
+    if (kk >= 0) { pos = cnt[kk] + atomicAdd(&fill[kk], 1); a.ws.s_row[pos] = a.ws.prow[i]; }
+    a.ws.pos_of[i] = pos;
+  }
+  for (int i = threadIdx.x; i < P; i += blockDim.x) { a.ws.done[i] = 0; a.dw.ready[i] = 0u; }
+  __syncthreads();
+  // per group: its activation rows and their digit units, so the layer kernel fills its work table in one round of loads
+  for (int j = threadIdx.x; j < misc[65] * kGroupRows; j += blockDim.x) {
+    const Group g = a.ws.groups[j >> 3];
+    const int c = j & 7;
+    if (c < g.n) { const int row = a.ws.s_row[g.start + c]; a.dw.g_row[j] = (uint16_t)row; a.dw.g_unit[j] = __ldcg(a.dw.xs + row); }
+  }
+  if (threadIdx.x == 0) { a.ws.hdr[0] = misc[65]; a.ws.hdr[1] = misc[64]; a.ws.hdr[2] = 0; *a.dw.fin = 0u; }
+}
+
+// Stamps the anchored bases into the tensor-map variants of both matrix kinds (one block; runs when the maps are first needed).
+struct DtcMapTpl { CUtensorMap t[2]; };
+__global__ void moe_dtc_anchor_kernel(const __grid_constant__ DtcMapTpl tpl, const uint8_t* const* __restrict__ tab, int n_tab, const uint8_t* shared_rec,
+                                      int pitch0, int pitch1, int gstep0, int gstep1, CUtensorMap* __restrict__ maps, DtcMeta* __restrict__ meta) {
+  __shared__ unsigned long long s_min;
+  if (threadIdx.x == 0) s_min = shared_rec ? reinterpret_cast<unsigned long long>(shared_rec) : ~0ull;
+  __syncthreads();
+  unsigned long long mn = ~0ull;
+  for (int i = threadIdx.x; i < n_tab; i += blockDim.x) { const unsigned long long p = reinterpret_cast<unsigned long long>(tab[i]); if (p) mn = min(mn, p); }
+  atomicMin(&s_min, mn);
+  __syncthreads();
+  const unsigned long long lo = s_min == ~0ull ? (1ull << 40) : (s_min & ~4095ull);
+  const int pitch[2] = {pitch0, pitch1}, gstep[2] = {gstep0, gstep1};
+  for (int i = threadIdx.x; i < 2 * DT_VMAX; i += blockDim.x) {
+    const int k = i / DT_VMAX, v = i - k * DT_VMAX;
+    if (v >= pitch[k] / gstep[k]) continue;
+    unsigned long long anchor = lo - ((unsigned long long)pitch[k] << 30);
+    anchor &= ~4095ull;
+    if (v == 0) meta->anchor[k] = anchor;
+    const uint4* src = reinterpret_cast<const uint4*>(&tpl.t[k]);
+    uint4* dst = reinterpret_cast<uint4*>(maps + i);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dst[j] = src[j];
+    const unsigned long long addr = anchor + (unsigned long long)v * gstep[k];
+    asm volatile("tensormap.replace.tile.global_address.global.b1024.b64 [%0], %1;" ::"l"(dst), "l"(addr) : "memory");
+    asm volatile("fence.proxy.tensormap::generic.release.gpu;" ::: "memory");
+  }
+}
+
+}  // namespace hb
+
+using namespace hb;
+
+namespace {
+int gcd_int(int a, int b) { while (b) { const int t = a % b; a = b; b = t; } return a; }
+
+size_t dtc_carve(void* ws, size_t off, int n, int H, int I, DtcWs* w) {
+  auto take = [&](size_t b) { void* r = ws ? static_cast<char*>(ws) + off : nullptr; off += al256(b); return r; };
+  DtcWs t;
+  t.xdig = (uint8_t*)take((size_t)n * 4 * H); t.ydig = (uint8_t*)take((size_t)n * 4 * I);
+  t.xs = (float*)take((size_t)n * 4); t.ys = (float*)take((size_t)n * 4);
+  t.ready = (unsigned int*)take((size_t)n * 4); t.fin = (unsigned int*)take(4);
+  t.g_row = (uint16_t*)take((size_t)n * 8 * 2); t.g_unit = (float*)take((size_t)n * 8 * 4);
+  if (w) *w = t;
+  return off;
+}
+}  // namespace
+
+bool hbk_moe_dtc_supported(int H, int I) {
+  if (H <= 0 || I <= 0 || H % 256 || I % 256) return false;
+  const int p0 = H / 2, p1 = I / 2;
+  return p0 / gcd_int(p0, 4096) <= DT_VMAX && p1 / gcd_int(p1, 4096) <= DT_VMAX;
+}
+
+// whether every CTA's work list fits its table for any routing of P pairs over E experts (+ the shared expert)
+bool hbk_moe_dtc_fits(const hb_ctx* ctx, int P, int E, int H, int I) {
+  int grid = ctx->sm_count;
+  if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
+  const long long G = P < E + 1 + P / kGroupRows ? P : E + 1 + P / kGroupRows;          // groups: at most one partly filled group per expert
+  // a CTA takes at most its gate/up items plus down items up to the mean number of stages, plus one pass of what is left
+  const long long gu = (G * (I / DT_GU_ROWS) + grid - 1) / grid, stages = (G * (I / DT_GU_ROWS) * (H >> 8) + G * (H / DT_DN_ROWS) * (I >> 8)) / grid;
+  const long long items = gu + stages / (I >> 8) + (G * (H / DT_DN_ROWS) + grid - 1) / grid + 16;
+  return items <= DT_TBL;
+}
+
+size_t hbk_moe_dtc_ws_extra(int n, int H, int I) { return hbk_moe_dtc_supported(H, I) ? dtc_carve(nullptr, 0, n, H, I, nullptr) : 0; }
+
+int hbk_moe_dtc_setup(hb_ctx* ctx) {
+  HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_dtc_layer_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM));
+  HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_dtc_prep_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+  HB_CUDA(ctx, cudaMalloc(&ctx->dtc_maps, (size_t)2 * DT_VMAX * sizeof(CUtensorMap) + 256));
+  HB_CUDA(ctx, cudaMemset(ctx->dtc_maps, 0, (size_t)2 * DT_VMAX * sizeof(CUtensorMap) + 256));
+  return HB_OK;
+}
+
+// the tensor maps for (H, I), anchored below the records of `tab`: made on first use and whenever the shape changes
+static int dtc_maps_for(hb_ctx* ctx, const uint8_t* const* tab, int n_tab, const uint8_t* shared_rec, int H, int I, cudaStream_t st) {
+  if (ctx->dtc_H == H && ctx->dtc_I == I) return HB_OK;
+  TcEncodeFn fn = tc_encode_fn();
+  HB_REQUIRE(ctx, fn, HB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  DtcMapTpl tpl;
+  const int pitch[2] = {H / 2, I / 2};
+  const cuuint32_t rows[2] = {DT_GU_ROWS, DT_DN_ROWS};
+  for (int k = 0; k < 2; ++k) {
+    const cuuint64_t dims[2] = {(cuuint64_t)pitch[k], (cuuint64_t)1 << 31}, strides[1] = {(cuuint64_t)pitch[k]};
+    const cuuint32_t box[2] = {128u, rows[k]}, estr[2] = {1, 1};
+    const CUresult r = fn(&tpl.t[k], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, ctx->dtc_maps, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    HB_REQUIRE(ctx, r == CUDA_SUCCESS, HB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for pitch %d", (int)r, pitch[k]);
+  }
+  CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(ctx->dtc_maps);
+  DtcMeta* meta = reinterpret_cast<DtcMeta*>(maps + 2 * DT_VMAX);
+  const int r = hb_launch(ctx, "moe_dtc_anchor", false, moe_dtc_anchor_kernel, dim3(1), dim3(256), 0, st, tpl, tab, n_tab, shared_rec, pitch[0], pitch[1],
+                          gcd_int(pitch[0], 4096), gcd_int(pitch[1], 4096), maps, meta);
+  if (r) return r;
+  ctx->dtc_H = H; ctx->dtc_I = I;
+  return HB_OK;
+}
+
+#ifdef HB_DTC_TRACE
+extern "C" __attribute__((visibility("default"))) int hb_dtc_trace_read(long long* out, int n) {
+  return (int)cudaMemcpyFromSymbol(out, g_dt_trace, (size_t)n * 8);
+}
+extern "C" __attribute__((visibility("default"))) int hb_dtc_stage_read(long long* out, int n) {
+  return (int)cudaMemcpyFromSymbol(out, g_dt_stage, (size_t)n * 8);
+}
+#endif
+
+int hbk_moe_dtc_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int H, int I, float limit, const hbk_reduce& red, void* ws, cudaStream_t st) {
+  const int M = src.M, K = src.K, P = M * K + (src.shared_rec ? M : 0);
+  if (P <= 0) return HB_OK;
+  DecodeWs w = carve(ws, P, H, I);
+  DtcWs dw;
+  dtc_carve(ws, hbk_moe_decode_ws_bytes(P, H, I) - hbk_moe_dtc_ws_extra(P, H, I), P, H, I, &dw);
+  hb_rec_layout L;
+  hb_rec_layout_make(H, I, &L);
+  int r = dtc_maps_for(ctx, src.tab + (size_t)src.li * src.E, src.E, src.shared_rec, H, I, st);
+  if (r) return r;
+  const int sh_row0 = src.sh_row0, sh_rows = src.sh_rows < 0 ? M : src.sh_rows;
+  ReduceArgs ra{w.part, w.pos_of, w.pw, M, K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
+                reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), sh_row0, sh_rows, hbk_ep_push{}};
+  DtPrepArgs pa{};
+  pa.route = src.route; pa.logits = src.logits; pa.ld = src.ld; pa.renorm = src.renorm; pa.logits_bf16 = src.logits_bf16; pa.bias = src.bias;
+  pa.sig_scale = src.sig_scale; pa.ids = const_cast<int32_t*>(src.ids); pa.w = const_cast<float*>(src.w); pa.ld_ids = src.ld_ids ? src.ld_ids : K;
+  pa.M = M; pa.K = K; pa.E = src.E; pa.tab = src.tab; pa.li = src.li; pa.shared_rec = src.shared_rec; pa.sh_row0 = sh_row0; pa.sh_rows = src.shared_rec ? sh_rows : 0;
+  pa.x = reinterpret_cast<const __nv_bfloat16*>(x); pa.x_ld = src.x_ld ? src.x_ld : H; pa.H = H; pa.I = I; pa.ws = w; pa.dw = dw;
+  pa.arrive = ctx->dev_err + 16;
+  const size_t group_b = ((size_t)P + 3 * (size_t)(src.E + 1) + 66) * 4;
+  const size_t route_b = (32 + (size_t)(src.route == 2 ? 2 : 1) * src.E) * 4;
+  const size_t prep_smem = group_b > route_b ? group_b : route_b;
+  HB_REQUIRE(ctx, prep_smem <= 96 * 1024, HB_ERR_UNSUPPORTED, "moe_decode: %d pairs over %d experts need %zu bytes of sort scratch", P, src.E, prep_smem);
+  if ((r = hb_launch(ctx, src.route ? "moe_dtc_route_prep" : "moe_dtc_prep", true, moe_dtc_prep_kernel, dim3(M), dim3(DT_PREP_THREADS), prep_smem, st, pa))) return r;
+  DtcArgs a{};
+  a.hdr = w.hdr; a.groups = w.groups; a.s_row = w.s_row; a.H = H; a.I = I; a.limit = limit; a.L = L;
+  { const char* e = getenv("HB_DTC_LAG"); a.lag = e ? atoi(e) : 2; if (a.lag < 1) a.lag = 1; }
+  a.maps = reinterpret_cast<const CUtensorMap*>(ctx->dtc_maps); a.meta = reinterpret_cast<const DtcMeta*>(a.maps + 2 * DT_VMAX);
+  a.pitch[0] = H / 2; a.pitch[1] = I / 2; a.gstep[0] = gcd_int(H / 2, 4096); a.gstep[1] = gcd_int(I / 2, 4096);
+  for (int k = 0; k < 2; ++k) { a.pshift[k] = -1; for (int b = 7; b <= 12; ++b) if (a.pitch[k] == (1 << b)) a.pshift[k] = b; }
+  a.dw = dw; a.y = w.y; a.part = w.part; a.done = reinterpret_cast<unsigned int*>(w.done); a.red = ra; a.err = ctx->dev_err;
+  int grid = ctx->sm_count;
+  if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
+  a.dIT.set((uint32_t)(I / DT_GU_ROWS)); a.dHT.set((uint32_t)(H / DT_DN_ROWS)); a.dG.set((uint32_t)grid);
+  return hb_launch(ctx, "moe_dtc_layer", true, moe_dtc_layer_kernel, dim3(grid), dim3(DT_THREADS), (size_t)DT_SMEM, st, a);
+}

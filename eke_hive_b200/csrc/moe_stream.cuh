@@ -195,41 +195,44 @@ struct ReduceArgs {
   __nv_bfloat16* shared_out = nullptr; int sh_row0 = 0, sh_rows = 0;   // fp32 form: the shared expert's output rows, written apart
   hbk_ep_push ep = {};                            // ep.world > 0: the routed sums go to the owning ranks' partial buffers
 };
-__device__ __forceinline__ void reduce_routed_unit(const ReduceArgs& r, size_t i) {
+// pre_pos / pre_w: the row's K positions (-1 = skipped pair) and weights and, at [16], the position of its shared-expert pair, when the
+// caller has them in registers already (K ≤ 16); nullptr: read from the workspace.
+__device__ __forceinline__ void reduce_routed_unit(const ReduceArgs& r, size_t i, const int* pre_pos = nullptr, const float* pre_w = nullptr) {
   const int m = (int)(i / (r.H / 2)), d = (int)(i % (r.H / 2)) * 2;
   float a0 = 0.f, a1 = 0.f;
-  // K ≤ 16: fetch every term first (independent loads in flight together), then add in k order
-  uint32_t raw[16]; float wv[16];
+  // 16 terms at a time: fetch them first (independent loads in flight together), then add in k order
+  for (int k0 = 0; k0 < r.K; k0 += 16) {
+    uint32_t raw[16]; float wv[16]; int ps[16];
 #pragma unroll
-  for (int k = 0; k < 16; ++k) {
-    raw[k] = 0u; wv[k] = 0.f;
-    if (k < r.K) {
-      const int pos = r.pos_of[m * r.K + k];
-      if (pos >= 0) { wv[k] = r.pw[m * r.K + k]; raw[k] = __ldcg(reinterpret_cast<const unsigned int*>(r.part + (size_t)pos * r.H + d)); }
+    for (int k = 0; k < 16; ++k) {
+      raw[k] = 0u; wv[k] = 0.f; ps[k] = -1;
+      if (k0 + k < r.K) {
+        ps[k] = pre_pos ? pre_pos[k] : r.pos_of[m * r.K + k0 + k];
+        if (ps[k] >= 0) { wv[k] = pre_w ? pre_w[k] : r.pw[m * r.K + k0 + k]; raw[k] = __ldcg(reinterpret_cast<const unsigned int*>(r.part + (size_t)ps[k] * r.H + d)); }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      if (ps[k] >= 0) {                                    // a skipped pair adds nothing (not even +0: keeps -0 sums as they are)
+        a0 = __fadd_rn(a0, __fmul_rn(wv[k], __uint_as_float(raw[k] << 16)));
+        a1 = __fadd_rn(a1, __fmul_rn(wv[k], __uint_as_float(raw[k] & 0xffff0000u)));
+      }
     }
   }
-#pragma unroll
-  for (int k = 0; k < 16; ++k) {
-    if (k < r.K && r.pos_of[m * r.K + k] >= 0) {           // a skipped pair adds nothing (not even +0: keeps -0 sums as they are)
-      a0 = __fadd_rn(a0, __fmul_rn(wv[k], __uint_as_float(raw[k] << 16)));
-      a1 = __fadd_rn(a1, __fmul_rn(wv[k], __uint_as_float(raw[k] & 0xffff0000u)));
-    }
-  }
+  const int sh_pos = (r.shared_pairs || r.shared_out) ? (pre_pos ? pre_pos[16] : r.pos_of[r.M * r.K + m]) : -1;
   if (r.ep.world > 0) {                            // row m belongs to rank m / B: slot `rank` of that rank's partial buffer
     const int pr = m / r.ep.B;
     *reinterpret_cast<float2*>(r.ep.rs[pr] + ((size_t)r.ep.rank * r.ep.B + (m - pr * r.ep.B)) * r.H + d) = make_float2(a0, a1);
   } else if (r.out_f32) { r.out_f32[(size_t)m * r.H + d] = a0; r.out_f32[(size_t)m * r.H + d + 1] = a1; }
   if (r.shared_out && m >= r.sh_row0 && m < r.sh_row0 + r.sh_rows) {
-    const int pos = r.pos_of[r.M * r.K + m];
     *reinterpret_cast<unsigned int*>(r.shared_out + (size_t)(m - r.sh_row0) * r.H + d) =
-        pos >= 0 ? __ldcg(reinterpret_cast<const unsigned int*>(r.part + (size_t)pos * r.H + d)) : 0u;
+        sh_pos >= 0 ? __ldcg(reinterpret_cast<const unsigned int*>(r.part + (size_t)sh_pos * r.H + d)) : 0u;
   }
   if (!r.out_bf16) return;
   float s0 = 0.f, s1 = 0.f;
   bool have = false;
   if (r.shared_pairs) {
-    const int pos = r.pos_of[r.M * r.K + m];
-    const uint32_t raw = __ldcg(reinterpret_cast<const unsigned int*>(r.part + (size_t)pos * r.H + d));
+    const uint32_t raw = __ldcg(reinterpret_cast<const unsigned int*>(r.part + (size_t)sh_pos * r.H + d));
     s0 = __uint_as_float(raw << 16); s1 = __uint_as_float(raw & 0xffff0000u); have = true;
   } else if (r.shared) {
     const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(r.shared + (size_t)m * r.H + d);

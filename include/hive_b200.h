@@ -45,6 +45,9 @@ typedef struct hb_config {
 } hb_config;
 #define HB_FLAG_NO_PDL 1   /* launch every kernel fully serialised (no programmatic dependent launch) */
 #define HB_FLAG_FUSED 2    /* decode: run gate/up, down and reduce as ONE persistent kernel (experimental; default: three kernels chained by PDL) */
+#define HB_FLAG_DECODE_MMA_SYNC 8 /* decode: run the routed operators on the register-dequantisation (mma.sync) streaming kernels */
+#define HB_FLAG_DECODE_TC 16      /* decode: run the routed operators on the tensor-memory layer kernel (tcgen05 block-scaled FP4 over exact
+                                     digit planes of the bf16 activations).  Neither flag: the library picks (see hb_moe_decode_supported). */
 #define HB_FLAG_PREFILL_A16 4u /* hb_moe_prefill keeps bf16 activations (W4A16, the reference's default prefill arithmetic): rows run through
                                   the decode kernels in sub-chunks — exact, but the expert records are streamed once per sub-chunk */
 

@@ -30,9 +30,15 @@ def _ptr(a: np.ndarray, t):
 def build(ref: bool = True) -> None:
     """Compile the C restatement and, when the reference tree is present, the reference shim."""
     subprocess.run(["make", "-s", "-C", str(HERE), str(HERE / "libhive_oracle.so")], check=True)
-    if ref and Path(os.environ.get("HIVE_REF", "/root/reference")).is_dir():
-        subprocess.run(["make", "-s", "-C", str(HERE), "ref", f"REF={os.environ.get('HIVE_REF', '/root/reference')}"], check=True,
-                       stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    root = ref_root()
+    if ref and root is not None:
+        subprocess.run(["make", "-s", "-C", str(HERE), "ref", f"REF={root}"], check=True, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+
+
+def ref_root():
+    """Where the reference project's sources are: $HIVE_REF, else a checkout named `reference` beside this repository; None if absent."""
+    cand = os.environ.get("HIVE_REF") or str(HERE.parent.parent / "reference")
+    return cand if Path(cand, "engine", "src", "cpu").is_dir() else None
 
 
 def _load_c():

@@ -16,6 +16,14 @@ def E():
     return E
 
 
+@pytest.fixture(params=[8, 16], ids=["mma_sync", "tensor_memory"])
+def eng(request, E):
+    """A context pinned to one of the two decode engines of the routed operators (HB_FLAG_DECODE_MMA_SYNC, HB_FLAG_DECODE_TC)."""
+    c = E.Context(flags=request.param)
+    yield c
+    c.close()
+
+
 def _routing(rng, M, Ex, K):
     ids = np.stack([rng.permutation(Ex)[:K] for _ in range(M)]).astype(np.int32)
     w = rng.uniform(0.05, 0.5, (M, K)).astype(np.float32)
@@ -67,14 +75,28 @@ def test_routed_fast_path_vs_oracle(E, oracle, H, I, Ex, K, M):
     out2 = E.fn_moe_decode_routed(torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), E.rec_table(drecs), 0, Ex, bf16_tensor(x), H, I,
                                   shared=bf16_tensor(shared), lg=torch.from_numpy(lg).cuda(), col=1)
     assert torch.equal(out, out2)
-    # the single persistent kernel (HB_FLAG_FUSED) performs the same arithmetic in the same order: bit-identical to the three-kernel form
-    ctx3 = E.Context(flags=2)
-    out3 = E.fn_moe_decode_routed(torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), E.rec_table(drecs), 0, Ex, bf16_tensor(x), H, I,
-                                  shared=bf16_tensor(shared), lg=torch.from_numpy(lg).cuda(), col=1, ctx=ctx3)
+    # the register-dequantisation kernels forced (HB_FLAG_DECODE_MMA_SYNC = 8) and their single persistent kernel form
+    # (HB_FLAG_FUSED = 2), which performs the same arithmetic in the same order: bit-identical to the three-kernel form
+    outs = []
+    for flags in (8, 2, 16):
+        c = E.Context(flags=flags)
+        o = E.fn_moe_decode_routed(torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), E.rec_table(drecs), 0, Ex, bf16_tensor(x), H, I,
+                                   shared=bf16_tensor(shared), lg=torch.from_numpy(lg).cuda(), col=1, ctx=c)
+        torch.cuda.synchronize()
+        c.check_device()
+        outs.append(o)
+        c.close()
+    assert rel_rms_err(outs[0].float().cpu().numpy(), ref) <= TOL
+    assert torch.equal(outs[0], outs[1])
+    # the tensor-memory layer kernel (HB_FLAG_DECODE_TC = 16): same inputs, same tolerance, and bit-identical run to run
+    assert rel_rms_err(outs[2].float().cpu().numpy(), ref) <= TOL
+    c = E.Context(flags=16)
+    o2 = E.fn_moe_decode_routed(torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), E.rec_table(drecs), 0, Ex, bf16_tensor(x), H, I,
+                                shared=bf16_tensor(shared), lg=torch.from_numpy(lg).cuda(), col=1, ctx=c)
     torch.cuda.synchronize()
-    ctx3.check_device()
-    assert torch.equal(out, out3)
-    ctx3.close()
+    c.check_device()
+    assert torch.equal(outs[2], o2)
+    c.close()
 
 
 def test_pair_list_accumulates_in_pair_order(E, oracle):
@@ -128,7 +150,7 @@ def test_outlier_activations_stay_finite(E, oracle):
 
 
 @pytest.mark.parametrize("router", ["softmax", "sigmoid"])
-def test_whole_layer_with_shared_expert(E, oracle, router):
+def test_whole_layer_with_shared_expert(E, oracle, router, eng):
     """hb_moe_layer_decode against the oracle's layer (config-1 style: H 2048, I 512, 64 experts, top-8, NVFP4 shared expert)."""
     import torch
     H, I, Ex, K, M = 2048, 512, 64, 8, 4
@@ -140,18 +162,19 @@ def test_whole_layer_with_shared_expert(E, oracle, router):
     drecs = upload(recs)
     tab = E.rec_table(drecs[:Ex])
     if router == "softmax":
-        ids, w, out = E.moe_layer_decode(torch.from_numpy(logits).cuda(), bf16_tensor(x), tab, 0, Ex, K, H, I, shared_rec=drecs[Ex], gate_col=Ex)
+        ids, w, out = E.moe_layer_decode(torch.from_numpy(logits).cuda(), bf16_tensor(x), tab, 0, Ex, K, H, I, shared_rec=drecs[Ex], gate_col=Ex, ctx=eng)
         rids, rw, rout = oracle.moe_layer(H, I, logits, x, recs[:Ex], K, shared_rec=recs[Ex], gate_logits=logits, gate_col=Ex)
     else:
         bias = rng.normal(0, 0.2, Ex).astype(np.float32)
         lg = np.ascontiguousarray(logits[:, :Ex])
         ids, w, out = E.moe_layer_decode(torch.from_numpy(lg).cuda(), bf16_tensor(x), tab, 0, Ex, K, H, I, shared_rec=drecs[Ex], gate_col=-1,
-                                         bias=torch.from_numpy(bias).cuda(), sigmoid_scale=2.5, limit=10.0)
+                                         bias=torch.from_numpy(bias).cuda(), sigmoid_scale=2.5, limit=10.0, ctx=eng)
         rids, rw, rout = oracle.moe_layer(H, I, lg, x, recs[:Ex], K, shared_rec=recs[Ex], router="sigmoid", bias=bias, scale=2.5, limit=10.0)
     assert np.array_equal(ids.cpu().numpy(), rids)                   # routing indices bit-exact
     assert w.cpu().numpy().tobytes() == rw.tobytes()
     assert rel_rms_err(out.float().cpu().numpy(), oracle.bf16_to_f32(rout)) <= TOL
-    E.context().check_device()
+    torch.cuda.synchronize()
+    eng.check_device()
 
 
 def test_batch_invariance_and_weight_linearity(E, oracle):
@@ -202,7 +225,7 @@ def test_decode_argument_errors(E):
     assert float(out.abs().sum()) == 0.0
 
 
-def test_ep_local_matches_separate_operators(E, oracle):
+def test_ep_local_matches_separate_operators(E, oracle, eng):
     """hb_moe_decode_ep_local on strided views of a packed exchange buffer (with NULL table entries for experts held elsewhere)
     equals the routed fp32 operator on contiguous copies bit for bit, and its shared-expert rows equal a separate pass."""
     import torch
@@ -224,20 +247,20 @@ def test_ep_local_matches_separate_operators(E, oracle):
     xv, iv, wv = buf[:, :H * 2].view(torch.bfloat16), buf[:, H * 2:H * 2 + K * 4].view(torch.int32), buf[:, H * 2 + K * 4:H * 2 + K * 8].view(torch.float32)
     routed = torch.empty((M, H), dtype=torch.float32, device="cuda")
     shared = torch.empty((B, H), dtype=torch.bfloat16, device="cuda")
-    E.moe_decode_ep_local(iv, wv, tab, 0, Ex, xv, H, I, routed, shared_ptr=drecs[Ex].data_ptr(), sh_row0=B, sh_rows=B, shared_out=shared)
+    E.moe_decode_ep_local(iv, wv, tab, 0, Ex, xv, H, I, routed, shared_ptr=drecs[Ex].data_ptr(), sh_row0=B, sh_rows=B, shared_out=shared, ctx=eng)
     ref = torch.empty_like(routed)
-    E.moe_decode_routed_f32(ids, w, tab, 0, Ex, x, H, I, out=ref)
+    E.moe_decode_routed_f32(ids, w, tab, 0, Ex, x, H, I, out=ref, ctx=eng)
     one_tab = E.rec_table([drecs[Ex]])
     sh_ref = torch.empty((B, H), dtype=torch.float32, device="cuda")
     E.moe_decode_routed_f32(torch.zeros((B, 1), dtype=torch.int32, device="cuda"), torch.ones((B, 1), dtype=torch.float32, device="cuda"), one_tab, 0, 1,
-                            x[B:2 * B].contiguous(), H, I, out=sh_ref)
+                            x[B:2 * B].contiguous(), H, I, out=sh_ref, ctx=eng)
     torch.cuda.synchronize()
-    E.context().check_device()
+    eng.check_device()
     assert torch.equal(routed, ref)
     assert torch.equal(shared.float(), sh_ref)
 
 
-def test_glm_shaped_layer_with_zipf_bias(E, oracle):
+def test_glm_shaped_layer_with_zipf_bias(E, oracle, eng):
     """The GLM-style configuration at its full shape: hidden 4096, intermediate 1536, 160 routed experts, top-8 + shared expert,
     8 tokens, sigmoid router with a Zipf(1.1) log-weight bias over a seeded permutation of the experts, SwiGLU clamp 10."""
     import torch
@@ -251,11 +274,12 @@ def test_glm_shaped_layer_with_zipf_bias(E, oracle):
     drecs = upload(recs)
     tab = E.rec_table(drecs[:Ex])
     ids, w, out = E.moe_layer_decode(torch.from_numpy(lg).cuda(), bf16_tensor(x), tab, 0, Ex, K, H, I, shared_rec=drecs[Ex], gate_col=-1,
-                                     bias=torch.from_numpy(bias).cuda(), sigmoid_scale=2.5, limit=10.0)
+                                     bias=torch.from_numpy(bias).cuda(), sigmoid_scale=2.5, limit=10.0, ctx=eng)
     rids, rw, rout = oracle.moe_layer(H, I, lg, x, recs[:Ex], K, shared_rec=recs[Ex], router="sigmoid", bias=bias, scale=2.5, limit=10.0)
     assert np.array_equal(ids.cpu().numpy(), rids)
     assert w.cpu().numpy().tobytes() == rw.tobytes()
     assert rel_rms_err(out.float().cpu().numpy(), oracle.bf16_to_f32(rout)) <= TOL
     hot = np.bincount(rids.ravel(), minlength=Ex)
     assert hot.max() >= 4                                            # the bias does skew the routing: some expert takes several of the 8 rows
-    E.context().check_device()
+    torch.cuda.synchronize()
+    eng.check_device()

@@ -70,6 +70,32 @@ def test_quantizer_roundtrip(oracle, golden):
     assert np.linalg.norm(dq - w) <= np.linalg.norm(dq0 - w) * 1.001
 
 
+@pytest.mark.parametrize("tag", ["a", "b", "ties", "tails", "zero"])
+def test_quantizer_against_reference_tool(oracle, tag):
+    """The weight quantiser (factor search on) against outputs of the reference's own numpy quantiser
+    (tools/q27_reencode.py nvfp4(), fixtures made by tests/golden/make_quantizer_golden.py): codes and block scales bit for bit;
+    the per-tensor scale is stored there as the divisor 448*6/amax, here as its reciprocal."""
+    from conftest import GOLDEN
+    g = np.load(GOLDEN / "quantizer_golden.npz")
+    w = g[f"{tag}_w"]
+    q, s, g_mul = oracle.nvfp4_quantize(w, search=True)
+    assert np.array_equal(q, g[f"{tag}_q"])
+    assert np.array_equal(s, g[f"{tag}_s"])
+    g_div = float(g[f"{tag}_g_div"][0])
+    amax = float(np.max(np.abs(w)))
+    if amax > 0:
+        assert g_mul == np.float32(np.float32(amax) / np.float32(448.0 * 6.0))
+        assert abs(g_mul * g_div - 1.0) < 2.0 ** -22
+    else:
+        assert g_mul == 1.0 and g_div == 1.0
+    if tag == "ties":
+        # the fixture really exercises the tie rule: some value sits exactly between two e2m1 codes for the chosen scale
+        E2, E4 = oracle.e2m1_table(), oracle.e4m3_table()
+        y = np.abs(w.reshape(w.shape[0], -1, 16).astype(np.float64) * g_div) / E4[s][..., None].astype(np.float64)
+        mids = (E2[:7].astype(np.float64) + E2[1:8].astype(np.float64)) / 2
+        assert np.isin(y, mids).sum() > 100
+
+
 def test_expert_forward_golden(oracle, golden):
     recs, x = golden["layer_recs"], golden["layer_x"]
     H, I = x.shape[1], 64
