@@ -190,29 +190,63 @@ class Layers:
         self.lay = E_mod.ExpertRecLayout.make(H, I)
         self.n = len(experts) + 1                                      # local routed experts + shared
         self.buf = torch.empty((L, self.n, self.lay.total), dtype=torch.uint8, device=device)
-        lay = self.lay
-        gen = torch.Generator(device=device)
-        chunk = 64
         for li in range(L):
-            for c0 in range(0, self.n, chunk):
-                c1 = min(self.n, c0 + chunk)
+            for j in range(self.n):
                 # seeded per (layer, global expert id): a rank's shard holds the same weights the single-GPU run has
-                ids = [(experts[j] if j < len(experts) else 10 ** 6) for j in range(c0, c1)]
-                w = torch.empty((c1 - c0, 3, H * I), dtype=torch.float32, device=device)
-                for j, gid in enumerate(ids):
-                    gen.manual_seed(seed * 1000003 + li * 4099 + gid)
-                    w[j].normal_(0.0, sigma, generator=gen)
-                for j in range(c1 - c0):
-                    rec = self.buf[li, c0 + j]
-                    g = rec[lay.g:lay.g + 12].view(torch.float32)
-                    for m, (ow, osc, shape) in enumerate(((lay.w1, lay.s1, (I, H)), (lay.w3, lay.s3, (I, H)), (lay.w2, lay.s2, (H, I)))):
-                        N_, K_ = shape
-                        E_mod.nvfp4_quantize(w[j, m].view(N_, K_), q=rec[ow:ow + N_ * K_ // 2], s=rec[osc:osc + N_ * K_ // 16], g=g[m:m + 1])
-                del w
+                self.fill_record(E_mod, self.buf[li, j], H, I, li, experts[j] if j < len(experts) else self.SHARED_ID, sigma, seed)
         torch.cuda.synchronize()
+
+    SHARED_ID = 10 ** 6
+
+    @staticmethod
+    def fill_record(E_mod, rec, H, I, li, gid, sigma, seed):
+        """Writes the record of (layer li, global expert id gid) into `rec` (device uint8 of the record's size)."""
+        import torch
+        lay = E_mod.ExpertRecLayout.make(H, I)
+        gen = torch.Generator(device=rec.device)
+        gen.manual_seed(seed * 1000003 + li * 4099 + gid)
+        w = torch.empty((3, H * I), dtype=torch.float32, device=rec.device)
+        w.normal_(0.0, sigma, generator=gen)
+        g = rec[lay.g:lay.g + 12].view(torch.float32)
+        for m, (ow, osc, shape) in enumerate(((lay.w1, lay.s1, (I, H)), (lay.w3, lay.s3, (I, H)), (lay.w2, lay.s2, (H, I)))):
+            N_, K_ = shape
+            E_mod.nvfp4_quantize(w[m].view(N_, K_), q=rec[ow:ow + N_ * K_ // 2], s=rec[osc:osc + N_ * K_ // 16], g=g[m:m + 1])
 
     def ptr(self, li, j):
         return self.buf[li, j].data_ptr()
+
+
+def parity_check(E_mod, torch, H, I, Ex, K, L, B, logits, x, ids, out, n_rows=2):
+    """Rows 0 and B-1 of the first and the last layer of input set 0, after the timed runs: the routing the device produced against the
+    oracle's router, and the layer outputs against the oracle's layer on the same logits and activations, with the experts those rows
+    touch regenerated from their seeds.  Returns {ids_equal, max_err_x_rms, rows, layers}; the caller fails the run above 2e-2."""
+    from oracle import oracle as O
+    rows = sorted({0, B - 1})[:n_rows]
+    worst, ids_equal = 0.0, True
+    layers = sorted({0, L - 1})
+    for li in layers:
+        lg = logits[0, li][rows].float().cpu().numpy()
+        xr = x[0, li][rows].float().cpu().numpy()
+        rids, _ = O.router_softmax_topk(lg[:, :Ex], K, True, True, 0, E=Ex)
+        ids_equal = ids_equal and bool(np.array_equal(rids, ids[0, li][rows].cpu().numpy()))
+        lay = E_mod.ExpertRecLayout.make(H, I)
+        tab = [None] * Ex
+        scratch = torch.empty(lay.total, dtype=torch.uint8, device=x.device)
+        for gid in sorted(set(int(v) for v in rids.ravel())) + [Layers.SHARED_ID]:
+            scratch.zero_()
+            Layers.fill_record(E_mod, scratch, H, I, li, gid, CFG["sigma"], CFG["seed"])
+            rec = scratch.cpu().numpy().copy()
+            if gid == Layers.SHARED_ID:
+                shared = rec
+            else:
+                tab[gid] = rec
+        _, _, ref = O.moe_layer(H, I, lg, xr, tab, K, shared_rec=shared, gate_logits=lg, gate_col=Ex)
+        ref = O.bf16_to_f32(ref).astype(np.float64)
+        got = out[0, li][rows].float().cpu().numpy().astype(np.float64)
+        rms = np.sqrt(np.mean(ref ** 2, axis=-1)) + 1e-30
+        worst = max(worst, float(np.max(np.max(np.abs(got - ref), axis=-1) / rms)))
+    return {"ids_equal": ids_equal, "max_err_x_rms": worst, "rows": rows, "layers": layers, "bar": 2e-2,
+            "what": "device routing vs the oracle router; layer outputs vs the CPU oracle's layer on the same inputs, touched experts regenerated from their seeds"}
 
 
 def run_ours(args):
@@ -399,6 +433,17 @@ def run_ours(args):
                 prof = ctx.profile_read()
                 ctx.profile(False)
                 prof = {k: {"launches": v[0], "total_ms": v[1], "mean_us": v[1] * 1e3 / max(v[0], 1)} for k, v in prof.items()}
+        if B == head_B:
+            # ---- correctness of what was timed, outside every timed region: one more replay of set 0, then sampled rows against the CPU oracle
+            graphs[0].replay()
+            torch.cuda.synchronize()
+            ctx.check_device()
+            parity = parity_check(E, torch, H, I, Ex, K, L, B, logits, x, ids, out)
+            if world > 1:
+                t = torch.tensor([parity["max_err_x_rms"], 0.0 if parity["ids_equal"] else 1.0], dtype=torch.float64, device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                parity["max_err_x_rms"] = float(t[0].item()); parity["ids_equal"] = bool(t[1].item() == 0.0); parity["ranks_checked"] = world
+            parity["ok"] = bool(parity["ids_equal"] and parity["max_err_x_rms"] <= parity["bar"])
         if world > 1:
             torch.cuda.synchronize()
             ep.close()
@@ -429,7 +474,7 @@ def run_ours(args):
             "layer": {"achieved_GBps": head["achieved_GBps"], "frac_of_measured_hbm": head["achieved_GBps"] / world / peak, "us_per_layer": head["us_per_layer"],
                       "records_per_layer": head["records_per_layer"]},
             "per_batch": [results[b] for b in sorted(results)], "roofline": roofline, "e2e": e2e, "gpu_launches": head["launches_per_step"] * args.steps,
-            "clocks": clocks, "kernels": prof, "setup_s": setup_s}
+            "clocks": clocks, "kernels": prof, "setup_s": setup_s, "parity": parity}
     if world == 1 and not args.no_cpu:
         try:
             _, _, _, _, info = cpu_reference(head_B, 0, 1, args.cpu_budget)
@@ -438,6 +483,7 @@ def run_ours(args):
             line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "reference", "sample": f"unavailable: {ex}"}
     if rank == 0:
         print(json.dumps(line), flush=True)
+    rc = 0 if parity["ok"] else 3                                     # a run whose sampled rows miss the oracle fails
     if world > 1:
         # Tearing down an NCCL communicator waits for every CUDA graph that captured its collectives to be destroyed, and a graph
         # that is still referenced somewhere makes that wait endless.  Release what this function holds, and do not let the
@@ -447,12 +493,14 @@ def run_ours(args):
         g = graphs = ep = run_layers = e2e_step = None
         import gc
         gc.collect()
-        threading.Timer(20.0, lambda: os._exit(0)).start()
+        threading.Timer(20.0, lambda: os._exit(rc)).start()
         try:
             dist.destroy_process_group()
         finally:
             sys.stdout.flush()
-            os._exit(0)
+            os._exit(rc)
+    if rc:
+        sys.exit(rc)
 
 
 # ------------------------------------------------------------------------------------------------ side workloads (one GPU)
@@ -558,6 +606,7 @@ def run_prefill(args):
                                  "frac_of_measured_fp4_peak": 2.0 * M * N * Kd / (dms * 1e-3) / 1e12 / peak}
     if rank == 0:
         print(json.dumps(line), flush=True)
+    rc = 0 if parity["ok"] else 3                                     # a run whose sampled rows miss the oracle fails
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()

@@ -25,8 +25,6 @@
 //          finisher of a group) y's digit planes; down → bf16 partial rows → (last arriver of a row's 128-column block) the
 //          k-order sum and the shared-expert combine.
 // Every wait is bounded and reports through the context's error word.
-#include <cstdlib>
-
 #include "moe_stream.cuh"
 #include "router.cuh"
 #include "tc_common.cuh"
@@ -41,17 +39,19 @@ constexpr int DT_RAWD = 3;                     // windows the scale fetch runs a
 constexpr int DT_RAW = (DT_RAWD + 1) * 2048;   // ring of fetched scale rows: 128 rows × 16 bytes per window
 constexpr int DT_EX = 8 * 64 * 4;              // SwiGLU exchange: up values of 64 rows × 8 activation rows
 constexpr int DT_TBL = 256;                    // work-list entries a CTA can hold (16 bytes + 8 row indices + 8 row units each)
-constexpr int DT_SMEM = 1024 + DT_ST * DT_STAGE + DT_RAW + 2 * DT_EX + 512 + 1024 + DT_TBL * 64;
+constexpr int DT_SFBC = 16 * 8 * 32;              // block-scale codes of the down items in flight: [16 items][8 rows][≤ 32 slices]
+constexpr int DT_SMEM = 1024 + DT_ST * DT_STAGE + DT_RAW + 2 * DT_EX + DT_SFBC + 1024 + DT_TBL * 64;
 constexpr int DT_THREADS = 16 * 32;            // warps 0-7 epilogues (two sets of four), then one warp each: MMA issue, weight TMA, digit copies,
                                                // (one idle); warps 12-15 fetch the scales and store them into tensor memory
 constexpr int DT_W_MMA = 8, DT_W_TMA = 9, DT_W_DIG = 10, DT_W_SC0 = 12;   // warp 11 idles: the scale warps must be warps 0-3 modulo 4
-constexpr int DT_TMEM_COLS = 512;              // accumulators 2 × 64, weight scales 8 × 16, digit scales 4
-constexpr int DT_SFA_COL0 = 128, DT_SFB_COL = DT_SFA_COL0 + DT_ST * 16;
+constexpr int DT_TMEM_COLS = 512;              // accumulators 2 × 64, weight scales 8 × 16, digit-plane scales 8 × 16
+constexpr int DT_SFA_COL0 = 128;               // per stage 32 columns: 16 of weight scales, 16 of digit-plane scales (down items)
+constexpr int DT_SFB1_COL = DT_SFA_COL0 + DT_ST * 32;   // 16 columns of 1.0: the digit-plane scales of gate/up items
 constexpr int DT_VMAX = 32;                    // tensor-map variants per matrix kind (see DtcMeta)
 constexpr int DT_GU_ROWS = 64;                 // rows of I per gate/up item
 constexpr int DT_DN_ROWS = 128;                // rows of H per down item
 static_assert(DT_STAGE % 1024 == 0, "stage buffers keep the swizzle atom's alignment");
-static_assert(DT_SFB_COL + 4 <= DT_TMEM_COLS, "tensor memory");
+static_assert(DT_SFB1_COL + 16 <= DT_TMEM_COLS, "tensor memory");
 static_assert(DT_SMEM <= 227 * 1024, "shared memory");
 
 // Tensor maps for the weight boxes cannot be made per record ahead of time (the table may change between calls) and records sit
@@ -62,10 +62,9 @@ struct DtcMeta { unsigned long long anchor[2]; };
 
 struct DtcWs {
   uint8_t* xdig;        // [rows][H/256][8 planes][128 bytes], swizzled
-  uint8_t* ydig;        // [pairs][I/256][8][128]
+  uint8_t* ydig;        // [pairs][I/256][8][128]; the 64 values of a gate/up item are digitised against their own exponent
+  uint8_t* yexp;        // [pairs][I/64, padded to 8] that exponent (biased), per pair and 64-value slice; 0 = slice not written yet
   float* xs;            // [rows] unit of a row's digits (a power of two)
-  float* ys;            // [pairs]
-  unsigned int* ready;  // [pairs] group g: y's digit planes are complete
   unsigned int* fin;    // CTAs of the layer kernel whose partial rows are all written
   uint16_t* g_row;      // [groups][8] activation rows of a group
   float* g_unit;        // [groups][8] digit units of those rows
@@ -84,7 +83,7 @@ struct DtDiv {
 
 struct DtcArgs {
   const int* hdr; const Group* groups; const int* s_row;
-  int H, I; float limit; int lag;
+  int H, I; float limit;
   DtDiv dIT, dHT, dG;                                    // dividers by the items per group (gate/up, down) and by the grid size
   hb_rec_layout L;
   const CUtensorMap* maps; const DtcMeta* meta;          // maps[kind · DT_VMAX + variant], kind 0 = gate/up, 1 = down
@@ -97,34 +96,50 @@ struct DtcArgs {
 };
 
 // ---- digit planes ------------------------------------------------------------------------------------------------------------------
+// One bf16 value → its eight digits, nibble p = the e2m1 code of plane p.
+__device__ __forceinline__ uint32_t dt_digits1(uint32_t b, int eb) {
+  const uint32_t ex = (b >> 7) & 0xffu;
+  const uint32_t mant = ex ? ((b & 0x7fu) | 0x80u) : (b & 0x7fu);
+  const int sh = (int)(ex ? ex : 1u) - eb + 14;
+  uint32_t X;
+  if (sh >= 0) X = mant << sh;
+  else if (sh < -9) X = 0u;
+  else {
+    const int s2 = -sh;
+    const uint32_t q = mant >> s2, rem = mant & ((1u << s2) - 1u), half = 1u << (s2 - 1);
+    X = q + ((rem > half || (rem == half && (q & 1u))) ? 1u : 0u);
+  }
+  const uint32_t Y = X + 0x924924u;
+  const uint32_t tbl = (b & 0x8000u) ? 0xDCA02456u : 0x5420ACDEu;
+  uint32_t w = 0u;
+#pragma unroll
+  for (int p = 0; p < 8; ++p) w |= ((tbl >> (((Y >> (3 * (7 - p))) & 7u) << 2)) & 0xfu) << (4 * p);
+  return w;
+}
 // Eight consecutive bf16 values (v: four packed pairs) of a row whose largest biased exponent is eb → one 32-bit word per plane
 // (plane 0 = most significant digit), nibble j = element j as an e2m1 code.
 __device__ __forceinline__ void dt_digits8(const uint32_t (&v)[4], int eb, uint32_t (&plane)[8]) {
 #pragma unroll
   for (int p = 0; p < 8; ++p) plane[p] = 0u;
+  unsigned long long lo = ((unsigned long long)v[1] << 32) | v[0], hi = ((unsigned long long)v[3] << 32) | v[2];
+#pragma unroll 1
+  for (int j = 0; j < 8; ++j) {                                       // rolled: this runs once per thread and launch, its size is its cost
+    const uint32_t w = dt_digits1((uint32_t)lo & 0xffffu, eb);
+    lo = (lo >> 16) | (hi << 48); hi >>= 16;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const uint32_t b = (v[j >> 1] >> (16 * (j & 1))) & 0xffffu;
-    const uint32_t ex = (b >> 7) & 0xffu;
-    const uint32_t mant = ex ? ((b & 0x7fu) | 0x80u) : (b & 0x7fu);
-    const int sh = (int)(ex ? ex : 1u) - eb + 14;                    // ≤ 14
-    uint32_t X;
-    if (sh >= 0) X = mant << sh;
-    else if (sh < -9) X = 0u;
-    else {                                                           // far below the row maximum: round to nearest even
-      const int s2 = -sh;
-      const uint32_t q = mant >> s2, rem = mant & ((1u << s2) - 1u), half = 1u << (s2 - 1);
-      X = q + ((rem > half || (rem == half && (q & 1u))) ? 1u : 0u);
-    }
-    const uint32_t Y = X + 0x924924u;                                // + 4 in every octal digit: digit t of Y is the balanced digit + 4
-    // e2m1 codes of t - 4 (positive element) or 4 - t (negative element), nibble t
-    const uint32_t tbl = (b & 0x8000u) ? 0xDCA02456u : 0x5420ACDEu;
-#pragma unroll
-    for (int p = 0; p < 8; ++p) {
-      const uint32_t t4 = ((Y >> (3 * (7 - p))) & 7u) << 2;
-      plane[p] |= ((tbl >> t4) & 0xfu) << (4 * j);
-    }
+    for (int p = 0; p < 8; ++p) plane[p] |= ((w >> (4 * p)) & 0xfu) << (4 * j);
   }
+}
+// Eight consecutive lanes hold one such word each (lane l: the digits of element l); afterwards lane l holds plane l's word of the
+// eight elements (nibble e = element e): an 8 × 8 transpose of nibbles in three exchange steps.
+__device__ __forceinline__ uint32_t dt_transpose8(uint32_t x, int lane) {
+#pragma unroll
+  for (int s = 4; s >= 1; s >>= 1) {
+    const uint32_t m = s == 4 ? 0x0000ffffu : s == 2 ? 0x00ff00ffu : 0x0f0f0f0fu;     // nibbles whose index has bit s clear
+    const uint32_t y = __shfl_xor_sync(0xffffffffu, x, s);
+    x = (lane & s) ? ((x & ~m) | ((y & ~m) >> (4 * s))) : ((x & m) | ((y & m) << (4 * s)));
+  }
+  return x;
 }
 __device__ __forceinline__ int dt_row_exponent(uint32_t amax_bits) {   // biased exponent the digits are taken against
   int eb = (int)(amax_bits >> 7) & 0xff;
@@ -149,74 +164,64 @@ __device__ __forceinline__ int ent_n(const DtEnt& e) { return (int)((e.info >> 1
 __device__ __forceinline__ int ent_t(const DtEnt& e) { return (int)((e.info >> 5) & 0x7ffu); }
 __device__ __forceinline__ int ent_g(const DtEnt& e) { return (int)(e.info >> 16); }
 
-// One warp writes the CTA's list (info words only; records and row ranges are filled in afterwards by all threads).  Lane l takes
-// round r0 + l of each batch of 32 rounds; a prefix sum over the lanes places the rounds' items one after the other.
-// Down items are dealt so that every CTA streams about the same number of bytes: the gate/up items do not divide evenly over the
-// CTAs (rem "heavy" CTAs have one more than the others), so down item d goes, in this order of d, to
+// A CTA's list: first its gate/up items, then its down items.  Gate/up item j of the launch goes to CTA j mod grid, so the items of
+// one group run on different CTAs at the same time and the groups finish in the order of their numbers; down item d (numbered
+// group by group) is dealt so that every CTA streams about the same number of bytes — the gate/up items do not divide evenly over
+// the CTAs (rem "heavy" CTAs have one more than the others):
 //   d < D1           all CTAs in turn               (q_h passes: what a heavy CTA can take before it exceeds the mean)
 //   D1 ≤ d < D2      the light CTAs in turn         (the extra passes that bring them up to the mean)
 //   D2 ≤ d           all CTAs in turn               (what is left)
-__device__ int dt_build_list(DtEnt* tbl, int cap, int G, const DtDiv& dIT, const DtDiv& dHT, const DtDiv& dG, int sGU, int sDN, int c, int lag, int lane) {
-  const int nIT = (int)dIT.d, nHT = (int)dHT.d, grid = (int)dG.d;
-  const int nGU = G * nIT, nD = G * nHT, R = (int)dG.div(nGU + grid - 1), NR = R + lag;
-  const int gu_l = (int)dG.div(nGU), rem = nGU - gu_l * grid, L = grid - rem, gu_h = gu_l + (rem ? 1 : 0);
-  const int target = (int)dG.div((uint32_t)(nGU * sGU + nD * sDN));
-  const int q_h = max(0, (target - gu_h * sGU) / sDN), q_l = max(q_h, (target - gu_l * sGU) / sDN);
-  const int D1 = min(nD, q_h * grid), D2 = rem ? min(nD, D1 + (q_l - q_h) * L) : D1;
-  auto glo = [&](int q) { return q <= 0 ? 0 : min(G, (int)dIT.div((uint32_t)(q * grid))); };   // first group whose gate/up ends in round ≥ q
-  // this CTA's share of down items [lo, hi) inside one dealing region: first item and count
-  auto share = [&](int lo, int hi, int origin, int mod, int cc, int& first, int& cnt) {
-    first = hi; cnt = 0;
-    if (lo >= hi || cc < 0) return;
-    const int back = mod == grid ? (lo - origin) - (int)dG.div((uint32_t)(lo - origin)) * grid : (lo - origin) % mod;
-    first = lo + (cc >= back ? cc - back : cc - back + mod);
-    if (first < hi) cnt = mod == grid ? (int)dG.div((uint32_t)(hi - first + grid - 1)) : (hi - first + mod - 1) / mod;
-  };
-  int base = 0;
-  for (int r0 = 0; r0 < NR; r0 += 32) {
-    const int r = r0 + lane;
-    int has_gu = 0, j = 0, f[3] = {0, 0, 0}, n3[3] = {0, 0, 0};
-    if (r < NR) {
-      j = r * grid + c;
-      has_gu = j < nGU ? 1 : 0;
-      if (r >= lag) {
-        const int lo = glo(r - lag) * nHT, hi = glo(r - lag + 1) * nHT;
-        share(min(lo, D1), min(hi, D1), 0, grid, c, f[0], n3[0]);
-        share(min(max(lo, D1), D2), min(max(hi, D1), D2), D1, L, c - rem, f[1], n3[1]);
-        share(max(lo, D2), max(hi, D2), D2, grid, c, f[2], n3[2]);
-      }
-    }
-    const int cnt = has_gu + n3[0] + n3[1] + n3[2];
-    int inc = cnt;
-    for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += t; }
-    int off = base + inc - cnt;
-    base += __shfl_sync(0xffffffffu, inc, 31);
-    if (off + cnt <= cap) {
-      if (has_gu) { const int g = (int)dIT.div((uint32_t)j); tbl[off++].info = 0u | ((uint32_t)(j - g * nIT) << 5) | ((uint32_t)g << 16); }
-#pragma unroll
-      for (int sgm = 0; sgm < 3; ++sgm) {
-        const int mod = sgm == 1 ? L : grid;
-        for (int i = 0, d = f[sgm]; i < n3[sgm]; ++i, d += mod) { const int g = (int)dHT.div((uint32_t)d); tbl[off++].info = 1u | ((uint32_t)(d - g * nHT) << 5) | ((uint32_t)g << 16); }
-      }
-    }
+// Both parts of a CTA's list ascend in group number, so its down items meet y rows that were finished long before, except at the
+// very end of the list.  The list is four arithmetic progressions: entry x is computed directly.
+struct DtList {
+  int grid, nIT, nHT, L, cntGU, cnt1, cnt2, first2, first3, total, c;
+  DtDiv dIT, dHT;
+  __device__ void init(int G, const DtDiv& dIT_, const DtDiv& dHT_, const DtDiv& dG, int sGU, int sDN, int c_) {
+    dIT = dIT_; dHT = dHT_; nIT = (int)dIT.d; nHT = (int)dHT.d; grid = (int)dG.d; c = c_;
+    const int nGU = G * nIT, nD = G * nHT;
+    const int gu_l = (int)dG.div(nGU), rem = nGU - gu_l * grid, gu_h = gu_l + (rem ? 1 : 0);
+    L = grid - rem;
+    const int target = (int)dG.div((uint32_t)(nGU * sGU + nD * sDN));
+    const int q_h = max(0, (target - gu_h * sGU) / sDN), q_l = max(q_h, (target - gu_l * sGU) / sDN);
+    const int D1 = min(nD, q_h * grid), D2 = rem ? min(nD, D1 + (q_l - q_h) * L) : D1;
+    cntGU = c < nGU ? (int)dG.div((uint32_t)(nGU - 1 - c)) + 1 : 0;
+    cnt1 = c < D1 ? (int)dG.div((uint32_t)(D1 - 1 - c)) + 1 : 0;
+    first2 = D1 + (c - rem);
+    cnt2 = (c >= rem && first2 < D2) ? (D2 - 1 - first2) / L + 1 : 0;
+    first3 = D2 + c;
+    cnt3_ = first3 < nD ? (int)dG.div((uint32_t)(nD - 1 - first3)) + 1 : 0;
+    total = cntGU + cnt1 + cnt2 + cnt3_;
   }
-  return base;
-}
+  int cnt3_;
+  __device__ uint32_t info(int x) const {                 // kind | t << 5 | g << 16 of entry x
+    if (x < cntGU) { const int j = c + x * grid, g = (int)dIT.div((uint32_t)j); return 0u | ((uint32_t)(j - g * nIT) << 5) | ((uint32_t)g << 16); }
+    x -= cntGU;
+    int d;
+    if (x < cnt1) d = c + x * grid;
+    else if (x < cnt1 + cnt2) d = first2 + (x - cnt1) * L;
+    else d = first3 + (x - cnt1 - cnt2) * grid;
+    const int g = (int)dHT.div((uint32_t)d);
+    return 1u | ((uint32_t)(d - g * nHT) << 5) | ((uint32_t)g << 16);
+  }
+};
 
 // Optional in-kernel timing (compile with -DHB_DTC_TRACE): every role of every CTA sums the clocks it spends in each kind of wait.
 #ifdef HB_DTC_TRACE
 __device__ long long g_dt_trace[256 * 32];
 #define DT_TIMED(acc, stmt) do { const long long t_ = clock64(); stmt; acc += clock64() - t_; } while (0)
 #define DT_TRACE_PUT(slot, v) g_dt_trace[blockIdx.x * 32 + (slot)] = (v)
+__device__ __forceinline__ void g_dt_trace_prep_put(long long v) { g_dt_trace[200 * 32] = v; }
 __device__ long long g_dt_stage[2 * 128 * 8];
 #define DT_STAMP(it, col) do { if ((blockIdx.x == 0 || blockIdx.x == 77) && (it) < 128) g_dt_stage[((blockIdx.x ? 1 : 0) * 128 + (it)) * 8 + (col)] = clock64(); } while (0)
 #else
 #define DT_TIMED(acc, stmt) do { stmt; } while (0)
 #define DT_TRACE_PUT(slot, v) do { } while (0)
+__device__ __forceinline__ void g_dt_trace_prep_put(long long) {}
 #define DT_STAMP(it, col) do { } while (0)
 #endif
 
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 __device__ __forceinline__ uint32_t ld_acquire_u32(const unsigned int* p) {
   uint32_t v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -231,46 +236,39 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
   uint8_t* sm = dt_raw + (base - raw);
   uint8_t* rawsc = sm + DT_ST * DT_STAGE;                                       // fetched scale rows
   float* ex_all = reinterpret_cast<float*>(rawsc + DT_RAW);                     // [2 sets][8][64]
-  uint8_t* sfb1 = reinterpret_cast<uint8_t*>(ex_all) + 2 * DT_EX;               // 32 × 16 bytes of 1.0 (e4m3 0x38)
-  uint64_t* full = reinterpret_cast<uint64_t*>(sfb1 + 512);                     // [ST] weights and digits of the stage are in shared memory, its scales in tensor memory
+  uint8_t* sfbc = reinterpret_cast<uint8_t*>(ex_all) + 2 * DT_EX;               // [16][8][32] e4m3 codes 2^(slice exponent - row reference) of down items
+  uint64_t* full = reinterpret_cast<uint64_t*>(sfbc + DT_SFBC);                     // [ST] weights and digits of the stage are in shared memory, its scales in tensor memory
   uint64_t* empty = full + DT_ST;                                               // [ST] the MMAs that read the stage are done
-  uint64_t* acc_full = empty + DT_ST;                                           // [2]
+  uint64_t* bmeta = empty + DT_ST;                                              // [ST] the stage's digit-plane scale codes are in shared memory
+  uint64_t* acc_full = bmeta + DT_ST;                                           // [2]
   uint64_t* acc_empty = acc_full + 2;                                           // [2]
   uint64_t* mma_done = acc_empty + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mma_done + 1);
-  int* n_items_s = reinterpret_cast<int*>(tmem_slot + 1);
-  volatile int* flag_all = reinterpret_cast<volatile int*>(n_items_s + 1);      // [2 sets][16] epilogue hand-over words: [0] last finisher, [8..15] row maxima
-  float* rowsc = reinterpret_cast<float*>(const_cast<int*>(flag_all) + 32);     // [16 items in flight][8] units of the item's activation rows
-  DtEnt* tbl = reinterpret_cast<DtEnt*>(sfb1 + 512 + 1024);                     // [DT_TBL] this CTA's work list
+  volatile int* flag_all = reinterpret_cast<volatile int*>(tmem_slot + 1);      // [2 sets][24] epilogue hand-over words: [8..23] the two gate warps' row maxima
+  float* rowsc = reinterpret_cast<float*>(const_cast<int*>(flag_all) + 48);     // [16 items in flight][8] units of the item's activation rows
+  DtEnt* tbl = reinterpret_cast<DtEnt*>(sfbc + DT_SFBC + 1024);                     // [DT_TBL] this CTA's work list
   uint16_t* tbl_row = reinterpret_cast<uint16_t*>(tbl + DT_TBL);                // [DT_TBL][8] activation rows of the item's group
   float* tbl_unit = reinterpret_cast<float*>(tbl_row + DT_TBL * 8);             // [DT_TBL][8] digit units of those rows (gate/up items)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   [[maybe_unused]] const long long t_k0 = clock64();
   if (threadIdx.x == 0) {
-    for (int s = 0; s < DT_ST; ++s) { mbar_init(&full[s], 128 + 2); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < DT_ST; ++s) { mbar_init(&full[s], 128 + 2); mbar_init(&empty[s], 1); mbar_init(&bmeta[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
     mbar_init(mma_done, 1);
     mbar_fence_init();
   }
-  if (threadIdx.x < 128) { reinterpret_cast<uint32_t*>(sfb1)[threadIdx.x] = 0x38383838u; fence_proxy_async_smem(); }
   if (warp == DT_W_MMA) { tmem_alloc(tmem_slot, DT_TMEM_COLS); tmem_relinquish(); }
   griddep_wait();                                                               // the prep kernel's lists, digit planes and cleared flags
   griddep_launch();
   [[maybe_unused]] const long long t_k1 = clock64();
   const int nIT = a.I / DT_GU_ROWS, nHT = a.H / DT_DN_ROWS;
-  if (warp == 0) {
-    int n = dt_build_list(tbl, DT_TBL, a.hdr[0], a.dIT, a.dHT, a.dG, a.H >> 8, a.I >> 8, (int)blockIdx.x, a.lag & 255, lane);
-    if (n > DT_TBL) { if (lane == 0) atomicOr(a.err, 0x1000u); n = 0; }         // the launcher sizes the grid so that this does not happen
-    if (lane == 0) *n_items_s = n;
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  const int n_items = *n_items_s;
+  DtList lst;
+  lst.init(a.hdr[0], a.dIT, a.dHT, a.dG, a.H >> 8, a.I >> 8, (int)blockIdx.x);
+  int n_items = lst.total;
+  if (n_items > DT_TBL) { if (threadIdx.x == 0) atomicOr(a.err, 0x1000u); n_items = 0; }   // the launcher sizes the grid so that this does not happen
   for (int j = threadIdx.x; j < n_items * kGroupRows; j += DT_THREADS) {       // records, row ranges, activation rows and their digit units
     const int i = j >> 3, c = j & 7;
-    const uint32_t info = tbl[i].info;
+    const uint32_t info = lst.info(i);
     const size_t gj = (size_t)(info >> 16) * kGroupRows + c;
     tbl_row[j] = a.dw.g_row[gj]; tbl_unit[j] = a.dw.g_unit[gj];
     if (c == 0) {
@@ -278,7 +276,10 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
       tbl[i].rec = g.rec; tbl[i].start = g.start; tbl[i].info = info | ((uint32_t)g.n << 1);
     }
   }
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
   [[maybe_unused]] const long long t_k2 = clock64();
 
   if (warp == DT_W_TMA) {
@@ -322,48 +323,124 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
       DT_TRACE_PUT(0, tw); DT_TRACE_PUT(1, clock64() - t_begin); DT_TRACE_PUT(2, (long long)it);
     }
   } else if (warp == DT_W_DIG) {
-    // ------------------------------------------------------------------------------------------------ digit planes: one thread
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      [[maybe_unused]] long long tw = 0, tr = 0;
-      for (int ii = 0; ii < n_items && ok; ++ii) {
-        const DtEnt e = tbl[ii];
-        const int k = ent_kind(e), n = ent_n(e), nkb = (k ? a.I : a.H) >> 8;
-        const uint8_t* src[kGroupRows];
-        float unit[kGroupRows];
-        if (k) {                                                                  // y's planes exist once the group's gate/up items are all through
+    // ------------------------------------------------------------------------------------------------ digit planes: one warp.  Items are taken four at a time: the
+    // eight lanes of quad j serve item base + j (lane c of the quad: row c of the item's group), so what the four items need
+    // before their copies can start is fetched and worked out side by side, and the next four items' fetches are in flight
+    // while this four's copies are issued.
+    uint32_t it = 0;
+    bool ok = true;
+    [[maybe_unused]] long long tw = 0, tr = 0;
+    // the 64-value slices of a y row were digitised against their own exponents (I / 64 bytes per row, rows padded to 8 bytes)
+    uint2 pre[4] = {make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u)};
+    int pre_item = -1;
+    const int nw8 = (nIT + 7) >> 3, nw4 = (nIT + 3) >> 2, ql = lane & 7, quad = lane >> 3;
+    auto fetch_exps = [&](const DtEnt& e, int item) {
+      if (ql < ent_n(e)) {
+        const uint2* p8 = reinterpret_cast<const uint2*>(a.dw.yexp + (size_t)(e.start + ql) * (nw8 * 8));
+#pragma unroll
+        for (int w = 0; w < 4; ++w) pre[w] = w < nw8 ? __ldcg(p8 + w) : make_uint2(0u, 0u);
+      }
+      pre_item = item;
+    };
+    // a row is complete when none of its I / 64 exponent bytes is zero (the prep kernel clears them, a biased exponent is never 0)
+    auto row_complete = [&](int item) {
+      if (pre_item != item) return false;
+      const uint32_t wds[8] = {pre[0].x, pre[0].y, pre[1].x, pre[1].y, pre[2].x, pre[2].y, pre[3].x, pre[3].y};
+      bool all = true;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) if (w < nw4 && __vcmpeq4(wds[w], 0u)) all = false;
+      return all;
+    };
+    for (int base0 = 0; base0 < n_items && ok; base0 += 4) {
+      const int my = base0 + quad;
+      const bool valid = my < n_items;
+      const DtEnt e = tbl[valid ? my : base0];
+      const int k = ent_kind(e), n = ent_n(e), nkb = (k ? a.I : a.H) >> 8;
+      const bool act = valid && ql < n;
+      const uint8_t* src = nullptr;
+      bool ready = true;
+      // what an item's copies need: the source of the row's planes; its unit for the epilogue; for a down item the block-scale codes
+      // that bring the slices of a y row onto one reference, 8 binades under the row's largest exponent (e4m3 reaches 2^8 up and
+      // 2^-9 down from there)
+      auto meta = [&]() {
+        float unit;
+        if (k) {
+          src = a.dw.ydig + (size_t)(e.start + ql) * nkb * 1024;
+          // four exponents per word, handled bytewise: e4m3 code of 2^(ex - eref) = (ex - eref + 7) << 3 for the normal range
+          const uint32_t wds[8] = {pre[0].x, pre[0].y, pre[1].x, pre[1].y, pre[2].x, pre[2].y, pre[3].x, pre[3].y};
+          uint32_t m4 = 0u;
+#pragma unroll
+          for (int w = 0; w < 8; ++w) if (w < nw4) m4 = __vmaxu4(m4, wds[w]);
+          const int emax = (int)max(max(m4 & 0xffu, (m4 >> 8) & 0xffu), max((m4 >> 16) & 0xffu, m4 >> 24));
+          const int eref = max(emax, 30) - 8;
+          const uint32_t off4 = 0x01010101u * (uint32_t)(eref - 7);                // ex - off = ex - eref + 7
+          uint32_t* codes = reinterpret_cast<uint32_t*>(sfbc + (my & 15) * 256 + ql * 32);
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            if (w < nw4) {
+              const uint32_t t4 = __vsubus4(wds[w], off4);                        // max(ex - eref + 7, 0) per byte, ≤ 15
+              uint32_t c4 = t4 << 3;
+              if (__vcmpeq4(t4, 0u)) {                                            // a slice 2^15 or more under the row's largest: subnormal codes 2^-7 … 2^-9, or nothing
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                  const int d = (int)((wds[w] >> (8 * b)) & 0xffu) - eref;
+                  if (d < -6) c4 = (c4 & ~(0xffu << (8 * b))) | ((d >= -9 ? (uint32_t)(1 << (d + 9)) : 0u) << (8 * b));
+                }
+              }
+              codes[w] = c4;
+            }
+          }
+          unit = dt_unit(eref);
+        } else {
+          src = a.dw.xdig + (size_t)tbl_row[my * 8 + ql] * nkb * 1024;
+          unit = tbl_unit[my * 8 + ql];
+        }
+        rowsc[(my & 15) * 8 + ql] = unit;
+      };
+      if (act) {
+        if (k && !row_complete(my)) ready = false;
+        else meta();
+      }
+      // the next four items' exponents
+      if (my + 4 < n_items) { const DtEnt e4 = tbl[my + 4]; if (ent_kind(e4) && ready) fetch_exps(e4, my + 4); }
+      for (int j = 0; j < 4 && base0 + j < n_items && ok; ++j) {
+        // item base + j: wait for its y rows if they were not complete above
+        if (quad == j && act && !ready) {
           [[maybe_unused]] const long long t_ = clock64();
           uint32_t spins = 0;
-          while (!(a.lag & 256) && ld_acquire_u32(a.dw.ready + ent_g(e)) == 0u) {
+          for (;;) {
+            fetch_exps(e, my);
+            if (row_complete(my)) break;
             if (++spins > (1u << 22)) { atomicOr(a.err, 0x20u); ok = false; break; }
             __nanosleep(40);
           }
-          fence_proxy_async_all();                                                // the planes were written with ordinary stores, the copies below read them through the async proxy
+          if (ok) meta();
+          if (my + 4 < n_items) { const DtEnt e4 = tbl[my + 4]; if (ent_kind(e4)) fetch_exps(e4, my + 4); }
 #ifdef HB_DTC_TRACE
           tr += clock64() - t_;
 #endif
-          if (!ok) break;
-          for (int c = 0; c < n; ++c) { src[c] = a.dw.ydig + (size_t)(e.start + c) * nkb * 1024; unit[c] = __ldcg(a.dw.ys + e.start + c); }
-        } else {
-          for (int c = 0; c < n; ++c) { src[c] = a.dw.xdig + (size_t)tbl_row[ii * 8 + c] * nkb * 1024; unit[c] = tbl_unit[ii * 8 + c]; }
         }
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const int jk = __shfl_sync(0xffffffffu, k, 8 * j), jn = __shfl_sync(0xffffffffu, n, 8 * j), jnkb = __shfl_sync(0xffffffffu, nkb, 8 * j);
+        if (jk) fence_proxy_async_global();                                     // the planes were written with ordinary stores, the copies below read them through the async proxy
+        for (int kb = 0; kb < jnkb; ++kb, ++it) {
           const uint32_t stage = it % DT_ST;
-          DT_TIMED(tw, ok = mbar_wait(&empty[stage], ((it / DT_ST) & 1) ^ 1, a.err, 0x2u));
+          if (lane == 0) DT_TIMED(tw, ok = mbar_wait(&empty[stage], ((it / DT_ST) & 1) ^ 1, a.err, 0x2u));
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
           if (!ok) break;
-          DT_STAMP(it, 3);
-          // the rows' units travel to the epilogue through shared memory, ordered by the barrier of the item's last stage behind them
-          // (a down item's units are loaded above and only needed here: the copies of its earlier stages do not wait for them)
-          if (kb == nkb - 1) for (int c = 0; c < n; ++c) rowsc[(ii & 15) * 8 + c] = unit[c];
-          uint8_t* sb = sm + stage * DT_STAGE + DT_A;
-          mbar_expect_tx(&full[stage], (uint32_t)n * 1024u);
-          for (int c = 0; c < n; ++c) bulk_g2s(sb + c * 1024, src[c] + (size_t)kb * 1024, 1024, &full[stage]);
-          DT_STAMP(it, 7);
+          if (lane == 0) {
+            DT_STAMP(it, 3);
+            mbar_arrive(&bmeta[stage]);                                           // the scale warps may read this item's codes
+            mbar_expect_tx(&full[stage], (uint32_t)jn * 1024u);
+          }
+          __syncwarp();
+          if (quad == j && act) bulk_g2s(sm + stage * DT_STAGE + DT_A + ql * 1024, src + (size_t)kb * 1024, 1024, &full[stage]);
+          if (lane == 0) DT_STAMP(it, 7);
         }
       }
-      DT_TRACE_PUT(3, tw); DT_TRACE_PUT(4, tr);
     }
+    if (lane == 0) { DT_TRACE_PUT(3, tw); DT_TRACE_PUT(4, tr); }
   } else if (warp >= DT_W_SC0) {
     // ------------------------------------------------------------------------------------------------ weight scales: thread r owns row r of each A tile
     // A row's 16 scale bytes of a window = 4 k-steps × 4 scales.  In tensor memory the scales of a k-step take four columns; the
@@ -394,39 +471,61 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
     uint32_t it = 0;
     bool ok = true;
     [[maybe_unused]] long long tw = 0, tg = 0;
+    // the digit planes of gate/up items have block scales 1.0: four columns written once, read by all their MMAs
+    {
+      uint32_t one16[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) one16[i] = 0x38383838u;
+      tc_st16(sf_lane + DT_SFB1_COL, one16);
+    }
+    int pend = -1;                                                               // stage whose scales are stored but not yet announced
     for (int ii = 0; ii < n_items && ok; ++ii) {
-      const int nkb = (ent_kind(tbl[ii]) ? a.I : a.H) >> 8;
+      const int kind = ent_kind(tbl[ii]), nkb = (kind ? a.I : a.H) >> 8;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         prefetch();
         DT_TIMED(tg, pf_cp_wait<DT_RAWD>());                                       // this window's own 16 bytes have landed
         const uint4 v = *reinterpret_cast<const uint4*>(rawsc + (it % (DT_RAWD + 1)) * 2048 + r * 16);
         const uint32_t stage = it % DT_ST;
-        DT_TIMED(tw, ok = mbar_wait(&empty[stage], ((it / DT_ST) & 1) ^ 1, a.err, 0x4u));   // the MMAs that read this stage's scale columns are done
-        if (!ok) break;
-        tc_fence_after();
-        // the word of k-step j goes to column 4 j + q of this thread's own lane; the other columns of the quarter are never read
-        uint32_t w16[16];
+        // columns [0, 16) of the stage's 32: the weight scales — the word of k-step j goes to column 4 j + q of this thread's own lane
+        // (the other columns of the quarter are never read).  Columns [16, 32), down items only: the block scales of the digit
+        // planes — plane row 8 c + p sits in lane (8 c + p) mod 32, column (8 c + p) / 32 of the k-step's four columns, in every
+        // quarter; k-step j of window kb is the 64-value slice 4 kb + j of the y rows.
+        uint32_t w32[32];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) w16[i] = 0u;
+        for (int i = 0; i < 32; ++i) w32[i] = i < 16 ? 0u : 0x38383838u;
         const uint32_t vj[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
 #pragma unroll
-          for (int qq = 0; qq < 4; ++qq) if (qq == q) w16[4 * j + qq] = vj[j];
+          for (int qq = 0; qq < 4; ++qq) if (qq == q) w32[4 * j + qq] = vj[j];
         }
-        tc_st16(sf_lane + DT_SFA_COL0 + stage * 16, w16);
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(&full[stage]);
+        // the previous stage's stores have had this long to land: announce it before anything below can wait
+        if (pend >= 0) { tc_wait_st(); tc_fence_before(); mbar_arrive(&full[pend]); pend = -1; }
+        if (kind) {
+          if (!(ok = mbar_wait(&bmeta[stage], (it / DT_ST) & 1, a.err, 0x400u))) break;
+          const uint8_t* codes = sfbc + (ii & 15) * 256 + kb * 4;
+          const int l = r & 31;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            w32[16 + 4 * j] = 0x01010101u * codes[(l >> 3) * 32 + j];
+            w32[16 + 4 * j + 1] = 0x01010101u * codes[(4 + (l >> 3)) * 32 + j];
+          }
+        }
+        DT_TIMED(tw, ok = mbar_wait(&empty[stage], ((it / DT_ST) & 1) ^ 1, a.err, 0x4u));   // the MMAs that read this stage's scale columns are done
+        if (!ok) break;
+        tc_fence_after();
+        if (kind) tc_st32(sf_lane + DT_SFA_COL0 + stage * 32, w32);
+        else tc_st16(sf_lane + DT_SFA_COL0 + stage * 32, reinterpret_cast<const uint32_t(&)[16]>(w32));
+        pend = (int)stage;
         if (r == 0) DT_STAMP(it, 2);
       }
     }
+    if (pend >= 0 && ok) { tc_wait_st(); tc_fence_before(); mbar_arrive(&full[pend]); }
     pf_cp_wait<0>();
     if (r == 0) { DT_TRACE_PUT(5, tw); DT_TRACE_PUT(6, tg); }
   } else if (warp == DT_W_MMA) {
     // ------------------------------------------------------------------------------------------------ MMA issue: one thread
     if (lane == 0) {
-      tc_cp_sf(tmem + DT_SFB_COL, tc_desc_sf(smem_u32(sfb1)));                  // block scales of the digit planes: 1.0 everywhere
       uint32_t it = 0;
       bool ok = true;
       [[maybe_unused]] long long tf = 0, te = 0, t_begin = clock64();
@@ -444,11 +543,11 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
           if (!ok) break;
           DT_STAMP(it, 5);
           tc_fence_after();
-          const uint32_t sb = base + stage * DT_STAGE, sfc = tmem + DT_SFA_COL0 + stage * 16;
+          const uint32_t sb = base + stage * DT_STAGE, sfc = tmem + DT_SFA_COL0 + stage * 32, sfb = ent_kind(e) ? sfc + 16 : tmem + DT_SFB1_COL;
           const uint64_t ad = tc_desc_sw128(sb), bd = tc_desc_sw128(sb + DT_A);
 #pragma unroll
           for (uint32_t j = 0; j < 4; ++j)
-            tc_mma_nvf4(tmem + buf * 64, ad + 2 * j, bd + 2 * j, idesc, sfc + 4 * j, tmem + DT_SFB_COL, (kb | (int)j) != 0 ? 1u : 0u);
+            tc_mma_nvf4(tmem + buf * 64, ad + 2 * j, bd + 2 * j, idesc, sfc + 4 * j, sfb + 4 * j, (kb | (int)j) != 0 ? 1u : 0u);
           tc_commit(&empty[stage]);
           DT_STAMP(it, 6);
         }
@@ -464,7 +563,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
     const int set = warp >> 2, tl = threadIdx.x & 127;                           // tl = row of the A tile
     const int bar_id = 1 + set;
     float* ex = ex_all + set * (DT_EX / 4);
-    volatile int* flag = flag_all + set * 16;
+    volatile int* flag = flag_all + set * 24;
     const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16) + set * 64;
     bool ok = true;
     [[maybe_unused]] long long ta = 0, tgu = 0, tdn = 0, tdig = 0;
@@ -511,70 +610,43 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
         }
         named_bar_sync(bar_id, 128);
         if (tl < 64) {
-          const int i = t * DT_GU_ROWS + tl;
+          // y = bf16(silu(g)·u) of the item's 64 values per row; its digit planes are taken against the largest exponent among the 64
+          uint32_t yb[kGroupRows];
 #pragma unroll
           for (int c = 0; c < kGroupRows; ++c) {
+            yb[c] = 0u;
             if (c < n) {
               float gv = gu[c], uv = ex[c * 64 + tl];
               if (a.limit > 0.f) { uv = fminf(fmaxf(uv, -a.limit), a.limit); gv = fminf(gv, a.limit); }
-              a.y[(size_t)(e.start + c) * a.I + i] = __float2bfloat16(gv / (1.f + __expf(-gv)) * uv);
+              yb[c] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16(gv / (1.f + __expf(-gv)) * uv));
+              const uint32_t am = __reduce_max_sync(0xffffffffu, yb[c] & 0x7fffu);
+              if (lane == 0) flag[8 + (warp & 1) * 8 + c] = (int)am;
             }
           }
-        }
-        named_bar_sync(bar_id, 128);
-        if (tl == 0) { __threadfence(); flag[0] = atomicAdd(a.done + g, 1u) == (unsigned)(nIT - 1) ? 1 : 0; }
-        named_bar_sync(bar_id, 128);
-        [[maybe_unused]] const long long t_dig = clock64();
-        if (flag[0]) {
-          // this CTA finished the group's last gate/up item: every y row of the group is complete — write its digit planes
-          __threadfence();
-          if (tl < kGroupRows) flag[8 + tl] = 0;
-          named_bar_sync(bar_id, 128);
-          // all (row, 8 values) units of the group at once: the first four of a thread stay in registers between the two passes
-          const int U = a.I / 8, total = n * U;
-          uint4 keep[4];
+          named_bar_sync(3 + set, 64);
+          int ebs[kGroupRows];
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) {
-            const int idx = tl + 128 * k4;
-            keep[k4] = make_uint4(0u, 0u, 0u, 0u);
-            if (idx < total) {
-              const int c = idx / U, u = idx - c * U;
-              keep[k4] = __ldcg(reinterpret_cast<const uint4*>(a.y + (size_t)(e.start + c) * a.I) + u);
-              const uint32_t w4[4] = {keep[k4].x, keep[k4].y, keep[k4].z, keep[k4].w};
-              uint32_t am = 0;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) am = max(am, max(w4[j] & 0x7fffu, (w4[j] >> 16) & 0x7fffu));
-              atomicMax(const_cast<int*>(flag) + 8 + c, (int)am);
+          for (int c = 0; c < kGroupRows; ++c) {
+            ebs[c] = 0;
+            if (c < n) {
+              const int eb = dt_row_exponent((uint32_t)max(flag[8 + c], flag[16 + c]));
+              ebs[c] = eb;
+              const uint32_t pw = dt_transpose8(dt_digits1(yb[c], eb), lane);
+              *reinterpret_cast<uint32_t*>(a.dw.ydig + dt_dig_off((size_t)(e.start + c), a.I, t * DT_GU_ROWS + (tl & ~7), lane & 7)) = pw;
             }
           }
-          for (int idx = tl + 512; idx < total; idx += 128) {
-            const int c = idx / U, u = idx - c * U;
-            const uint4 q4 = __ldcg(reinterpret_cast<const uint4*>(a.y + (size_t)(e.start + c) * a.I) + u);
-            const uint32_t w4[4] = {q4.x, q4.y, q4.z, q4.w};
-            uint32_t am = 0;
+          named_bar_sync(3 + set, 64);
+          // the slice's exponents are also what tells the down items that its planes are written: they go out last, behind a fence
+          // (a slice whose exponent byte reads non-zero has all its planes in memory)
+          if (tl == 0) {
+            fence_proxy_async_all();
+            __threadfence();
 #pragma unroll
-            for (int j = 0; j < 4; ++j) am = max(am, max(w4[j] & 0x7fffu, (w4[j] >> 16) & 0x7fffu));
-            atomicMax(const_cast<int*>(flag) + 8 + c, (int)am);
+            for (int c = 0; c < kGroupRows; ++c) if (c < n) a.dw.yexp[(size_t)(e.start + c) * (((nIT + 7) >> 3) << 3) + t] = (uint8_t)ebs[c];
           }
-          named_bar_sync(bar_id, 128);
-          if (tl < n) a.dw.ys[e.start + tl] = dt_unit(dt_row_exponent((uint32_t)flag[8 + tl]));
-          for (int idx = tl; idx < total; idx += 128) {
-            const int c = idx / U, u = idx - c * U, k4 = idx >> 7;
-            uint4 q4;
-            if (k4 == 0) q4 = keep[0]; else if (k4 == 1) q4 = keep[1]; else if (k4 == 2) q4 = keep[2]; else if (k4 == 3) q4 = keep[3];
-            else q4 = __ldcg(reinterpret_cast<const uint4*>(a.y + (size_t)(e.start + c) * a.I) + u);
-            const uint32_t v4[4] = {q4.x, q4.y, q4.z, q4.w};
-            uint32_t pl[8];
-            dt_digits8(v4, dt_row_exponent((uint32_t)flag[8 + c]), pl);
-#pragma unroll
-            for (int p = 0; p < 8; ++p) *reinterpret_cast<uint32_t*>(a.dw.ydig + dt_dig_off((size_t)(e.start + c), a.I, u * 8, p)) = pl[p];
-          }
-          fence_proxy_async_all();
-          named_bar_sync(bar_id, 128);
-          if (tl == 0) { __threadfence(); st_release_u32(a.dw.ready + g, 1u); }
         }
 #ifdef HB_DTC_TRACE
-        tdig += clock64() - t_dig; tgu += clock64() - t_item;
+        tgu += clock64() - t_item;
 #endif
       } else {
         const int h = t * DT_DN_ROWS + tl;
@@ -593,18 +665,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
   [[maybe_unused]] const long long t_k3 = clock64();
   if (warp == DT_W_MMA) { tc_fence_after(); tmem_dealloc(tmem, DT_TMEM_COLS); }
   // ---- every CTA's partial rows are written once all CTAs have come this far: then the k-order sums, one (row, 128 columns) block per
-  // group of 64 threads.  A group fetches its first block's positions and weights before it waits.
-  const int blocks = a.red.M * nHT, sub = threadIdx.x >> 6, l64 = threadIdx.x & 63, nsub = DT_THREADS / 64;
-  const int b0 = (int)blockIdx.x + sub * (int)gridDim.x;
-  int pre_pos[17];
-  float pre_w[16];
-  const bool pre = b0 < blocks && a.red.K <= 16;
-  if (pre) {
-    const int m = b0 / nHT;
-#pragma unroll
-    for (int k = 0; k < 16; ++k) { pre_pos[k] = k < a.red.K ? a.red.pos_of[m * a.red.K + k] : -1; pre_w[k] = k < a.red.K ? a.red.pw[m * a.red.K + k] : 0.f; }
-    pre_pos[16] = a.red.shared_pairs ? a.red.pos_of[a.red.M * a.red.K + m] : -1;
-  }
+  // group of 64 threads
   if (threadIdx.x == 0) {
     __threadfence();
     atomicAdd(a.dw.fin, 1u);
@@ -616,11 +677,12 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
   }
   __syncthreads();
   [[maybe_unused]] const long long t_k4 = clock64();
-  for (int b = b0; b < blocks && !(a.lag & 512); b += nsub * (int)gridDim.x) {
-    const int m = b / nHT, ht = b - m * nHT;
-    const size_t unit = (size_t)m * (a.H / 2) + (size_t)ht * (DT_DN_ROWS / 2) + l64;
-    if (b == b0 && pre) reduce_routed_unit(a.red, unit, pre_pos, pre_w);
-    else reduce_routed_unit(a.red, unit);
+  {
+    const int blocks = a.red.M * nHT, sub = threadIdx.x >> 6, l64 = threadIdx.x & 63, nsub = DT_THREADS / 64;
+    for (int b = (int)blockIdx.x + sub * (int)gridDim.x; b < blocks; b += nsub * (int)gridDim.x) {
+      const int m = b / nHT, ht = b - m * nHT;
+      reduce_routed_unit(a.red, (size_t)m * (a.H / 2) + (size_t)ht * (DT_DN_ROWS / 2) + l64);
+    }
   }
   if (threadIdx.x == 0) { DT_TRACE_PUT(20, t_k1 - t_k0); DT_TRACE_PUT(21, t_k2 - t_k1); DT_TRACE_PUT(22, t_k3 - t_k2); DT_TRACE_PUT(23, t_k4 - t_k3); DT_TRACE_PUT(24, clock64() - t_k4); }
 }
@@ -635,7 +697,7 @@ struct DtPrepArgs {
   unsigned int* arrive;          // context-owned counter (zero between calls)
 };
 
-constexpr int DT_PREP_THREADS = 256;
+constexpr int DT_PREP_THREADS = 288;      // warps 0-7: the row's digit planes; warp 8: the row's routing
 
 __device__ void dt_block_scan2(int* a, int* b, int n, int* tot_a, int* tot_b, int* warp_tmp /* [2][32] */) {
   const int nt = blockDim.x, per = (n + nt - 1) / nt;
@@ -671,33 +733,33 @@ __global__ void __launch_bounds__(DT_PREP_THREADS) moe_dtc_prep_kernel(const DtP
   __shared__ int s_red[8];
   __shared__ int s_last;
   const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int32_t my_id = 0;
-  float my_w = 0.f;
-  if (a.route && warp == 0) {
+  [[maybe_unused]] const long long t_p0 = clock64();
+  [[maybe_unused]] long long t_p1 = 0, t_p2 = 0;
+  if (warp == 8) {
     // the row's routing reads only the logits: it runs before the previous kernel of the stream is waited for
-    int32_t* sid = reinterpret_cast<int32_t*>(psm);
-    float* sw = reinterpret_cast<float*>(psm) + 16;
-    float* scratch = reinterpret_cast<float*>(psm) + 32;
-    if (a.route == 1) route_softmax_row(a.logits + (size_t)m * a.ld, a.E, a.K, a.renorm, a.logits_bf16, scratch, lane, sid, sw);
-    else route_sigmoid_row(a.logits + (size_t)m * a.ld, a.bias, a.E, a.K, a.sig_scale, scratch, lane, sid, sw);
-    __syncwarp();
-    if (lane < a.K) { my_id = sid[lane]; my_w = sw[lane]; }
-  }
-  griddep_wait();
-  griddep_launch();
-  if (a.route && warp == 0 && lane < a.K) { a.ids[(size_t)m * a.K + lane] = my_id; a.w[(size_t)m * a.K + lane] = my_w; }
-  // digit planes of row m
-  {
+    int32_t my_id = 0;
+    float my_w = 0.f;
+    if (a.route == 1) route_softmax_row_small(a.logits + (size_t)m * a.ld, a.E, a.K, a.renorm, a.logits_bf16, reinterpret_cast<float*>(psm), lane, my_id, my_w);
+    else if (a.route == 2) route_sigmoid_row_small(a.logits + (size_t)m * a.ld, a.bias, a.E, a.K, a.sig_scale, reinterpret_cast<float*>(psm), lane, my_id, my_w);
+    if (lane == 0) DT_TRACE_PUT(25, clock64() - t_p0);
+    griddep_wait();
+    griddep_launch();
+    if (a.route && lane < a.K) { a.ids[(size_t)m * a.K + lane] = my_id; a.w[(size_t)m * a.K + lane] = my_w; }
+  } else {
+    // digit planes of row m
+    griddep_wait();
+    griddep_launch();
     const uint32_t* xr = reinterpret_cast<const uint32_t*>(a.x + (size_t)m * a.x_ld);
     uint32_t am = 0;
-    for (int e2 = threadIdx.x; e2 < a.H / 2; e2 += blockDim.x) { const uint32_t w2 = __ldg(xr + e2); am = max(am, max(w2 & 0x7fffu, (w2 >> 16) & 0x7fffu)); }
+    for (int e2 = threadIdx.x; e2 < a.H / 2; e2 += 256) { const uint32_t w2 = __ldg(xr + e2); am = max(am, max(w2 & 0x7fffu, (w2 >> 16) & 0x7fffu)); }
     for (int o = 16; o > 0; o >>= 1) am = max(am, __shfl_xor_sync(0xffffffffu, am, o));
     if (lane == 0) s_red[warp] = (int)am;
-    __syncthreads();
-    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) am = max(am, (uint32_t)s_red[i]);
+    named_bar_sync(1, 256);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) am = max(am, (uint32_t)s_red[i]);
     const int eb = dt_row_exponent(am);
     if (threadIdx.x == 0) a.dw.xs[m] = dt_unit(eb);
-    for (int u = threadIdx.x; u < a.H / 8; u += blockDim.x) {
+    for (int u = threadIdx.x; u < a.H / 8; u += 256) {
       const uint4 q4 = __ldg(reinterpret_cast<const uint4*>(xr) + u);
       const uint32_t v4[4] = {q4.x, q4.y, q4.z, q4.w};
       uint32_t pl[8];
@@ -706,10 +768,12 @@ __global__ void __launch_bounds__(DT_PREP_THREADS) moe_dtc_prep_kernel(const DtP
       for (int p = 0; p < 8; ++p) *reinterpret_cast<uint32_t*>(a.dw.xdig + dt_dig_off((size_t)m, a.H, u * 8, p)) = pl[p];
     }
   }
-  __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) s_last = atomicAdd(a.arrive, 1u) == gridDim.x - 1 ? 1 : 0;
+  t_p1 = clock64();
+  if (threadIdx.x == 0) { __threadfence(); s_last = atomicAdd(a.arrive, 1u) == gridDim.x - 1 ? 1 : 0; }
   __syncthreads();
+  t_p2 = clock64();
+  if (threadIdx.x == 0) { DT_TRACE_PUT(26, t_p1 - t_p0); DT_TRACE_PUT(27, t_p2 - t_p1); }
   if (!s_last) return;
   // ---- the last CTA: every row's ids and weights are written — sort the pairs by expert into groups of ≤ 8 rows
   __threadfence();
@@ -748,21 +812,28 @@ __global__ void __launch_bounds__(DT_PREP_THREADS) moe_dtc_prep_kernel(const DtP
   __syncthreads();
   for (int k = threadIdx.x; k < NK; k += blockDim.x) fill[k] = 0;
   __syncthreads();
+  // positions inside an expert's run: any order gives the same results (the columns of a tile are independent); the shared expert's
+  // rows keep their order.  Each position is also entered, with its row's digit unit, in the per-group arrays the layer kernel
+  // builds its work table from.
   for (int i = threadIdx.x; i < P; i += blockDim.x) {
     const int kk = key[i];
     int pos = -1;
-    if (kk >= 0) { pos = cnt[kk] + atomicAdd(&fill[kk], 1); a.ws.s_row[pos] = a.ws.prow[i]; }
+    if (kk >= 0) {
+      const int row = i < a.M * a.K ? i / a.K : i - a.M * a.K;
+      const int slot = kk == a.E ? row - a.sh_row0 : atomicAdd(&fill[kk], 1);
+      pos = cnt[kk] + slot;
+      a.ws.s_row[pos] = row;
+      const size_t gj = (size_t)(ngr[kk] + (slot >> 3)) * kGroupRows + (slot & 7);
+      a.dw.g_row[gj] = (uint16_t)row;
+      a.dw.g_unit[gj] = __ldcg(a.dw.xs + row);
+    }
     a.ws.pos_of[i] = pos;
-  }
-  for (int i = threadIdx.x; i < P; i += blockDim.x) { a.ws.done[i] = 0; a.dw.ready[i] = 0u; }
-  __syncthreads();
-  // per group: its activation rows and their digit units, so the layer kernel fills its work table in one round of loads
-  for (int j = threadIdx.x; j < misc[65] * kGroupRows; j += blockDim.x) {
-    const Group g = a.ws.groups[j >> 3];
-    const int c = j & 7;
-    if (c < g.n) { const int row = a.ws.s_row[g.start + c]; a.dw.g_row[j] = (uint16_t)row; a.dw.g_unit[j] = __ldcg(a.dw.xs + row); }
+    a.ws.done[i] = 0;
+    for (int w = 0; w < (((a.I / DT_GU_ROWS) + 7) >> 3) * 2; ++w) reinterpret_cast<uint32_t*>(a.dw.yexp)[(size_t)i * ((((a.I / DT_GU_ROWS) + 7) >> 3) * 2) + w] = 0u;
   }
   if (threadIdx.x == 0) { a.ws.hdr[0] = misc[65]; a.ws.hdr[1] = misc[64]; a.ws.hdr[2] = 0; *a.dw.fin = 0u; }
+  __syncthreads();
+  if (threadIdx.x == 0) g_dt_trace_prep_put(clock64() - t_p2);
 }
 
 // Stamps the anchored bases into the tensor-map variants of both matrix kinds (one block; runs when the maps are first needed).
@@ -805,8 +876,7 @@ size_t dtc_carve(void* ws, size_t off, int n, int H, int I, DtcWs* w) {
   auto take = [&](size_t b) { void* r = ws ? static_cast<char*>(ws) + off : nullptr; off += al256(b); return r; };
   DtcWs t;
   t.xdig = (uint8_t*)take((size_t)n * 4 * H); t.ydig = (uint8_t*)take((size_t)n * 4 * I);
-  t.xs = (float*)take((size_t)n * 4); t.ys = (float*)take((size_t)n * 4);
-  t.ready = (unsigned int*)take((size_t)n * 4); t.fin = (unsigned int*)take(4);
+  t.xs = (float*)take((size_t)n * 4); t.yexp = (uint8_t*)take((size_t)n * ((I / DT_GU_ROWS + 7) / 8 * 8)); t.fin = (unsigned int*)take(4);
   t.g_row = (uint16_t*)take((size_t)n * 8 * 2); t.g_unit = (float*)take((size_t)n * 8 * 4);
   if (w) *w = t;
   return off;
@@ -814,7 +884,7 @@ size_t dtc_carve(void* ws, size_t off, int n, int H, int I, DtcWs* w) {
 }  // namespace
 
 bool hbk_moe_dtc_supported(int H, int I) {
-  if (H <= 0 || I <= 0 || H % 256 || I % 256) return false;
+  if (H <= 0 || I <= 0 || H % 256 || I % 256 || I / DT_GU_ROWS > 32) return false;
   const int p0 = H / 2, p1 = I / 2;
   return p0 / gcd_int(p0, 4096) <= DT_VMAX && p1 / gcd_int(p1, 4096) <= DT_VMAX;
 }
@@ -893,13 +963,12 @@ int hbk_moe_dtc_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int H, 
   pa.x = reinterpret_cast<const __nv_bfloat16*>(x); pa.x_ld = src.x_ld ? src.x_ld : H; pa.H = H; pa.I = I; pa.ws = w; pa.dw = dw;
   pa.arrive = ctx->dev_err + 16;
   const size_t group_b = ((size_t)P + 3 * (size_t)(src.E + 1) + 66) * 4;
-  const size_t route_b = (32 + (size_t)(src.route == 2 ? 2 : 1) * src.E) * 4;
+  const size_t route_b = (size_t)(src.route == 2 ? 2 : 1) * src.E * 4;
   const size_t prep_smem = group_b > route_b ? group_b : route_b;
   HB_REQUIRE(ctx, prep_smem <= 96 * 1024, HB_ERR_UNSUPPORTED, "moe_decode: %d pairs over %d experts need %zu bytes of sort scratch", P, src.E, prep_smem);
   if ((r = hb_launch(ctx, src.route ? "moe_dtc_route_prep" : "moe_dtc_prep", true, moe_dtc_prep_kernel, dim3(M), dim3(DT_PREP_THREADS), prep_smem, st, pa))) return r;
   DtcArgs a{};
   a.hdr = w.hdr; a.groups = w.groups; a.s_row = w.s_row; a.H = H; a.I = I; a.limit = limit; a.L = L;
-  { const char* e = getenv("HB_DTC_LAG"); a.lag = e ? atoi(e) : 2; if (a.lag < 1) a.lag = 1; }
   a.maps = reinterpret_cast<const CUtensorMap*>(ctx->dtc_maps); a.meta = reinterpret_cast<const DtcMeta*>(a.maps + 2 * DT_VMAX);
   a.pitch[0] = H / 2; a.pitch[1] = I / 2; a.gstep[0] = gcd_int(H / 2, 4096); a.gstep[1] = gcd_int(I / 2, 4096);
   for (int k = 0; k < 2; ++k) { a.pshift[k] = -1; for (int b = 7; b <= 12; ++b) if (a.pitch[k] == (1 << b)) a.pshift[k] = b; }

@@ -195,31 +195,30 @@ struct ReduceArgs {
   __nv_bfloat16* shared_out = nullptr; int sh_row0 = 0, sh_rows = 0;   // fp32 form: the shared expert's output rows, written apart
   hbk_ep_push ep = {};                            // ep.world > 0: the routed sums go to the owning ranks' partial buffers
 };
-// pre_pos / pre_w: the row's K positions (-1 = skipped pair) and weights and, at [16], the position of its shared-expert pair, when the
-// caller has them in registers already (K ≤ 16); nullptr: read from the workspace.
-__device__ __forceinline__ void reduce_routed_unit(const ReduceArgs& r, size_t i, const int* pre_pos = nullptr, const float* pre_w = nullptr) {
+__device__ __forceinline__ void reduce_routed_unit(const ReduceArgs& r, size_t i) {
   const int m = (int)(i / (r.H / 2)), d = (int)(i % (r.H / 2)) * 2;
   float a0 = 0.f, a1 = 0.f;
-  // 16 terms at a time: fetch them first (independent loads in flight together), then add in k order
-  for (int k0 = 0; k0 < r.K; k0 += 16) {
-    uint32_t raw[16]; float wv[16]; int ps[16];
+  // four terms at a time: fetch them first (independent loads in flight together), then add in k order
+#pragma unroll 1
+  for (int k0 = 0; k0 < r.K; k0 += 4) {
+    uint32_t raw[4]; float wv[4]; int ps[4];
 #pragma unroll
-    for (int k = 0; k < 16; ++k) {
+    for (int k = 0; k < 4; ++k) {
       raw[k] = 0u; wv[k] = 0.f; ps[k] = -1;
       if (k0 + k < r.K) {
-        ps[k] = pre_pos ? pre_pos[k] : r.pos_of[m * r.K + k0 + k];
-        if (ps[k] >= 0) { wv[k] = pre_w ? pre_w[k] : r.pw[m * r.K + k0 + k]; raw[k] = __ldcg(reinterpret_cast<const unsigned int*>(r.part + (size_t)ps[k] * r.H + d)); }
+        ps[k] = r.pos_of[m * r.K + k0 + k];
+        if (ps[k] >= 0) { wv[k] = r.pw[m * r.K + k0 + k]; raw[k] = __ldcg(reinterpret_cast<const unsigned int*>(r.part + (size_t)ps[k] * r.H + d)); }
       }
     }
 #pragma unroll
-    for (int k = 0; k < 16; ++k) {
+    for (int k = 0; k < 4; ++k) {
       if (ps[k] >= 0) {                                    // a skipped pair adds nothing (not even +0: keeps -0 sums as they are)
         a0 = __fadd_rn(a0, __fmul_rn(wv[k], __uint_as_float(raw[k] << 16)));
         a1 = __fadd_rn(a1, __fmul_rn(wv[k], __uint_as_float(raw[k] & 0xffff0000u)));
       }
     }
   }
-  const int sh_pos = (r.shared_pairs || r.shared_out) ? (pre_pos ? pre_pos[16] : r.pos_of[r.M * r.K + m]) : -1;
+  const int sh_pos = (r.shared_pairs || r.shared_out) ? r.pos_of[r.M * r.K + m] : -1;
   if (r.ep.world > 0) {                            // row m belongs to rank m / B: slot `rank` of that rank's partial buffer
     const int pr = m / r.ep.B;
     *reinterpret_cast<float2*>(r.ep.rs[pr] + ((size_t)r.ep.rank * r.ep.B + (m - pr * r.ep.B)) * r.H + d) = make_float2(a0, a1);

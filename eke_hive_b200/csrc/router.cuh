@@ -96,4 +96,91 @@ __device__ __forceinline__ void route_sigmoid_row(const float* __restrict__ lr, 
   }
 }
 
+// ---- compact forms for kernels that route one row per launch: the candidates sit in shared memory, every loop is rolled (such a
+// kernel runs its code once, so code size is run time), the per-round maximum is two warp reductions (largest value, then the
+// smallest id that has it) and a lane rescans its candidates only after it has lost one.  Same operations on the same values in
+// the same order as the forms above: ids and weights are the same bits.
+__device__ __forceinline__ uint32_t f32_sort_key(float v) {          // monotone map float → uint32 (NaN excluded by the callers)
+  const uint32_t b = __float_as_uint(v);
+  return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
+}
+// lanes 0..k-1 return their pick.  p: E floats of shared memory owned by this warp.
+static __device__ __noinline__ void route_softmax_row_small(const float* __restrict__ lr, int E, int k, int renorm, int logits_bf16, float* p, int lane,
+                                                     int32_t& out_id, float& out_w) {
+  float mx = -INFINITY;
+#pragma unroll 2
+  for (int e = lane; e < E; e += 32) { const float v = logits_bf16 ? bf16r(lr[e]) : lr[e]; p[e] = v; mx = fmaxf(mx, v); }
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f, lb = -1.f;
+  int le = 0x7fffffff;
+#pragma unroll 2
+  for (int e = lane; e < E; e += 32) {
+    const float v = exp_portable(__fsub_rn(p[e], mx));
+    p[e] = v;
+    sum = __fadd_rn(sum, v);
+    if (v >= 0.f && v > lb) { lb = v; le = e; }                       // this lane's best candidate: the first of equal values
+  }
+  for (int o = 16; o > 0; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
+  const float inv = __fdiv_rn(1.f, sum);
+  float my_w = 0.f, tot = 0.f;
+  int my_id = 0;
+#pragma unroll 1
+  for (int r = 0; r < k; ++r) {
+    const uint32_t key = le != 0x7fffffff ? __float_as_uint(lb) + 1u : 0u;   // values are ≥ 0: their bits order like the values
+    const uint32_t m = __reduce_max_sync(0xffffffffu, key);
+    const int bid = (int)__reduce_min_sync(0xffffffffu, (key == m && m != 0u) ? (uint32_t)le : 0x7fffffffu);
+    const float best = m ? __uint_as_float(m - 1u) : -1.f;
+    const float sw = __fmul_rn(best, inv);
+    tot = __fadd_rn(tot, sw);
+    if (lane == r) { my_id = bid; my_w = sw; }
+    if (bid != 0x7fffffff && (bid & 31) == lane) {
+      p[bid] = -1.f;
+      lb = -1.f; le = 0x7fffffff;
+#pragma unroll 2
+      for (int e = lane; e < E; e += 32) { const float v = p[e]; if (v >= 0.f && v > lb) { lb = v; le = e; } }
+    }
+  }
+  const float sc = renorm ? __fdiv_rn(1.f, tot) : 1.f;
+  out_id = my_id;
+  out_w = __fmul_rn(my_w, sc);
+}
+// sc: 2·E floats of shared memory owned by this warp
+static __device__ __noinline__ void route_sigmoid_row_small(const float* __restrict__ lr, const float* __restrict__ bias, int E, int k, float scale, float* sc, int lane,
+                                                     int32_t& out_id, float& out_w) {
+  float* s = sc;
+  float* c = sc + E;
+  float lb = -INFINITY;
+  int le = 0x7fffffff;
+#pragma unroll 2
+  for (int e = lane; e < E; e += 32) {
+    const float v = sigmoid_portable(lr[e]);
+    s[e] = v;
+    const float cv = bias ? __fadd_rn(v, bias[e]) : v;
+    c[e] = cv;
+    if (cv > lb) { lb = cv; le = e; }
+  }
+  __syncwarp();
+  float my_s = 0.f, sum = 0.f;
+  int my_id = 0;
+#pragma unroll 1
+  for (int r = 0; r < k; ++r) {
+    const uint32_t key = le != 0x7fffffff ? f32_sort_key(lb) : 0u;
+    const uint32_t m = __reduce_max_sync(0xffffffffu, key);
+    int bid = (int)__reduce_min_sync(0xffffffffu, (key == m && m != 0u) ? (uint32_t)le : 0x7fffffffu);
+    if (bid == 0x7fffffff) bid = 0;                                   // every candidate already taken or NaN: keep a valid id
+    const float sv = s[bid];
+    sum = __fadd_rn(sum, sv);
+    if (lane == r) { my_id = bid; my_s = sv; }
+    if ((bid & 31) == lane) {
+      c[bid] = -INFINITY;
+      lb = -INFINITY; le = 0x7fffffff;
+#pragma unroll 2
+      for (int e = lane; e < E; e += 32) { const float v = c[e]; if (v > lb) { lb = v; le = e; } }
+    }
+  }
+  const float inv = __fdiv_rn(1.f, __fadd_rn(sum, 1e-20f));
+  out_id = my_id;
+  out_w = __fmul_rn(__fmul_rn(my_s, inv), scale);
+}
+
 }  // namespace hb
