@@ -697,7 +697,7 @@ struct DtPrepArgs {
   unsigned int* arrive;          // context-owned counter (zero between calls)
 };
 
-constexpr int DT_PREP_THREADS = 288;      // warps 0-7: the row's digit planes; warp 8: the row's routing
+constexpr int DT_PREP_THREADS = 256;      // eight warps: the row's routing, then its digit planes
 
 __device__ void dt_block_scan2(int* a, int* b, int n, int* tot_a, int* tot_b, int* warp_tmp /* [2][32] */) {
   const int nt = blockDim.x, per = (n + nt - 1) / nt;
@@ -735,26 +735,25 @@ __global__ void __launch_bounds__(DT_PREP_THREADS) moe_dtc_prep_kernel(const DtP
   const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   [[maybe_unused]] const long long t_p0 = clock64();
   [[maybe_unused]] long long t_p1 = 0, t_p2 = 0;
-  if (warp == 8) {
-    // the row's routing reads only the logits: it runs before the previous kernel of the stream is waited for
+  griddep_wait();                                                               // logits and activations may come from the kernel before
+  griddep_launch();
+  if (a.route) {
+    // the row's routing: all eight warps (a two-level tournament, router.cuh)
     int32_t my_id = 0;
     float my_w = 0.f;
-    if (a.route == 1) route_softmax_row_small(a.logits + (size_t)m * a.ld, a.E, a.K, a.renorm, a.logits_bf16, reinterpret_cast<float*>(psm), lane, my_id, my_w);
-    else if (a.route == 2) route_sigmoid_row_small(a.logits + (size_t)m * a.ld, a.bias, a.E, a.K, a.sig_scale, reinterpret_cast<float*>(psm), lane, my_id, my_w);
-    if (lane == 0) DT_TRACE_PUT(25, clock64() - t_p0);
-    griddep_wait();
-    griddep_launch();
-    if (a.route && lane < a.K) { a.ids[(size_t)m * a.K + lane] = my_id; a.w[(size_t)m * a.K + lane] = my_w; }
-  } else {
+    route_row_group(a.route, a.logits + (size_t)m * a.ld, a.bias, a.E, a.K, a.renorm, a.logits_bf16, a.sig_scale, reinterpret_cast<float*>(psm), 8, warp, lane, 1,
+                    my_id, my_w);
+    if (warp == 0 && lane < a.K) { a.ids[(size_t)m * a.K + lane] = my_id; a.w[(size_t)m * a.K + lane] = my_w; }
+    if (threadIdx.x == 0) DT_TRACE_PUT(25, clock64() - t_p0);
+  }
+  {
     // digit planes of row m
-    griddep_wait();
-    griddep_launch();
     const uint32_t* xr = reinterpret_cast<const uint32_t*>(a.x + (size_t)m * a.x_ld);
     uint32_t am = 0;
     for (int e2 = threadIdx.x; e2 < a.H / 2; e2 += 256) { const uint32_t w2 = __ldg(xr + e2); am = max(am, max(w2 & 0x7fffu, (w2 >> 16) & 0x7fffu)); }
     for (int o = 16; o > 0; o >>= 1) am = max(am, __shfl_xor_sync(0xffffffffu, am, o));
     if (lane == 0) s_red[warp] = (int)am;
-    named_bar_sync(1, 256);
+    __syncthreads();
 #pragma unroll
     for (int i = 0; i < 8; ++i) am = max(am, (uint32_t)s_red[i]);
     const int eb = dt_row_exponent(am);
@@ -963,7 +962,7 @@ int hbk_moe_dtc_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int H, 
   pa.x = reinterpret_cast<const __nv_bfloat16*>(x); pa.x_ld = src.x_ld ? src.x_ld : H; pa.H = H; pa.I = I; pa.ws = w; pa.dw = dw;
   pa.arrive = ctx->dev_err + 16;
   const size_t group_b = ((size_t)P + 3 * (size_t)(src.E + 1) + 66) * 4;
-  const size_t route_b = (size_t)(src.route == 2 ? 2 : 1) * src.E * 4;
+  const size_t route_b = src.route ? RouteScratch::floats(src.E, K, 8) * 4 : 0;
   const size_t prep_smem = group_b > route_b ? group_b : route_b;
   HB_REQUIRE(ctx, prep_smem <= 96 * 1024, HB_ERR_UNSUPPORTED, "moe_decode: %d pairs over %d experts need %zu bytes of sort scratch", P, src.E, prep_smem);
   if ((r = hb_launch(ctx, src.route ? "moe_dtc_route_prep" : "moe_dtc_prep", true, moe_dtc_prep_kernel, dim3(M), dim3(DT_PREP_THREADS), prep_smem, st, pa))) return r;
