@@ -464,7 +464,7 @@ def run_ours(args):
         gu_bytes = U * (2 * H * I * 9 // 16) + head_B * H * 2                     # gate+up halves of U records + the activation rows
         ach = gu_bytes / (prof["moe_gate_up"]["mean_us"] * 1e-6) / 1e9
         roofline = {"bound": "hbm", "kernel": "moe_gate_up (moe_stream_kernel<8,1,false>)", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                    "peak_source": peak_src, "traffic": gu_bytes * (163.1 + 3.9) / 164.0, "traffic_source": "ncu dram bytes of a 4-layer capture of the same kernel (profiles/moe_stream_decode_b16.md): 1.018 x algorithmic, scaled to this run's records", "algorithmic_bytes_per_launch": gu_bytes, "mean_us": prof["moe_gate_up"]["mean_us"]}
+                    "peak_source": peak_src, "traffic": gu_bytes, "traffic_source": "algorithmic (an ncu capture of this kernel on a 4-layer case read 1.018 x algorithmic DRAM bytes; not measured in this run)", "algorithmic_bytes_per_launch": gu_bytes, "mean_us": prof["moe_gate_up"]["mean_us"]}
     clocks = sampler.result()
     line = {"metric": "moe_layer_tokens_per_s", "value": head["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 products of e2m1·e4m3 weights and bf16 activations, f32 accumulate",
@@ -515,12 +515,13 @@ def _timed(torch, fn, n):
 
 
 def run_prefill(args):
-    """BASELINE config 4 (DeepSeek-shaped prefill): one MoE layer, H 7168, I 2048, 256 routed experts (6.3 GB), top-8, T tokens, NVFP4
+    """The DeepSeek-shaped prefill workload: one MoE layer, H 7168, I 2048, 256 routed experts (6.3 GB), top-8, T tokens, NVFP4
     weights and NVFP4 activations; plus a dense W4A4 GEMM and the measured FP4 tensor-pipe ceiling.  Under torchrun (N > 1) the
     experts are sharded over the ranks and every rank brings T / N tokens (strong scaling on the same total problem)."""
     import torch
     import torch.distributed as dist
     import eke_hive_b200 as E
+    from oracle import oracle as O                                     # the checker of the sampled rows, outside the timed region
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -533,10 +534,16 @@ def run_prefill(args):
     rb = E.ExpertRecLayout.make(H, I)
     e_lo, e_hi = rank * Ex // world, (rank + 1) * Ex // world
     n_loc = e_hi - e_lo
-    blob = torch.randint(0, 256, (n_loc, rb.total), dtype=torch.uint8, device=dev)       # e2m1 codes: any bytes
-    for off, n in ((rb.s1, I * H // 16), (rb.s3, I * H // 16), (rb.s2, H * I // 16)):    # e4m3 scales 2^-2 .. 2: finite, positive
-        blob[:, off:off + n] = torch.randint(0x28, 0x48, (n_loc, n), dtype=torch.uint8, device=dev)
-    blob[:, rb.g:rb.g + 12] = torch.from_numpy(np.array([0.003, 0.003, 0.004], np.float32).view(np.uint8)).to(dev)
+    def fill_expert(rec, e):
+        """The record of global expert e, the same bytes on whichever rank makes it: e2m1 codes are any bytes, e4m3 scales 2^-2 .. 2."""
+        gg = torch.Generator(device=dev); gg.manual_seed(90001 + e)
+        rec.copy_(torch.randint(0, 256, (rb.total,), dtype=torch.uint8, device=dev, generator=gg))
+        for off, n in ((rb.s1, I * H // 16), (rb.s3, I * H // 16), (rb.s2, H * I // 16)):
+            rec[off:off + n] = torch.randint(0x28, 0x48, (n,), dtype=torch.uint8, device=dev, generator=gg)
+        rec[rb.g:rb.g + 12] = torch.from_numpy(np.array([0.003, 0.003, 0.004], np.float32).view(np.uint8)).to(dev)
+    blob = torch.empty((n_loc, rb.total), dtype=torch.uint8, device=dev)
+    for e in range(e_lo, e_hi):
+        fill_expert(blob[e - e_lo], e)
     tab = torch.tensor([blob[e - e_lo].data_ptr() if e_lo <= e < e_hi else 0 for e in range(Ex)], dtype=torch.int64, device=dev)
     g = torch.Generator(device=dev); g.manual_seed(4 + rank)
     Tl = T // world
@@ -604,17 +611,49 @@ def run_prefill(args):
         dms = _timed(torch, lambda: E.nvfp4_gemm_a4(W, xq, xs, xg, y=y, ctx=ctx), args.steps)
         line["dense_gemm_a4"] = {"M": M, "N": N, "K": Kd, "ms": dms, "TFLOPs": 2.0 * M * N * Kd / (dms * 1e-3) / 1e12,
                                  "frac_of_measured_fp4_peak": 2.0 * M * N * Kd / (dms * 1e-3) / 1e12 / peak}
+    # ---- correctness, outside the timed region: two of this rank's rows of the last layer call against the CPU oracle (their experts are
+    # made again from their seeds, so any rank can check rows whose experts live elsewhere), with the W4A4 rounding points; and how far
+    # W4A4 is from the reference's default W4A16 arithmetic on the same rows (its own gate for that is cosine > 0.98)
+    ids_l, w_l, x_l = sets[(it[0] - 1) % 2]
+    got = (out if world == 1 else epp.routed).float()
+    rows = sorted({0, Tl - 1})
+    tmp = torch.empty(rb.total, dtype=torch.uint8, device=dev)
+    err = 0.0; cos_min = 1.0; dev_max = 0.0
+    for m in rows:
+        ref4 = np.zeros(H, np.float64); ref16 = np.zeros(H, np.float64)
+        xr = x_l[m].float().cpu().numpy()
+        for k in range(K):
+            e = int(ids_l[m, k]); wk = float(w_l[m, k])
+            fill_expert(tmp, e)
+            rec = tmp.cpu().numpy()
+            ref4 += wk * O.expert_forward_a4(rec, H, I, xr, 0.0).astype(np.float64)
+            ref16 += wk * O.expert_forward(rec, H, I, xr, 1.0, 0.0).astype(np.float64)
+        g_m = got[m].double().cpu().numpy()
+        rms = float(np.sqrt((ref4 ** 2).mean())) + 1e-30
+        err = max(err, float(np.abs(g_m - ref4).max()) / rms)
+        cos_min = min(cos_min, float((g_m * ref16).sum() / (np.linalg.norm(g_m) * np.linalg.norm(ref16) + 1e-30)))
+        dev_max = max(dev_max, float(np.abs(g_m - ref16).max()) / (float(np.sqrt((ref16 ** 2).mean())) + 1e-30))
+    if world > 1:
+        t = torch.tensor([err, -cos_min, dev_max], dtype=torch.float64, device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        err, cos_min, dev_max = float(t[0].item()), -float(t[1].item()), float(t[2].item())
+    parity = {"max_err_x_rms": err, "bar": 2e-2, "rows_per_rank": rows, "ranks_checked": world,
+              "what": "routed sums of sampled rows vs the CPU oracle's W4A4 expert (NVFP4 activations), experts regenerated from their seeds",
+              "ok": bool(err <= 2e-2)}
+    line["parity"] = parity
+    line["w4a4_vs_w4a16"] = {"cos_min": cos_min, "max_err_x_rms": dev_max, "gate": "cosine > 0.98", "ok": bool(cos_min > 0.98),
+                             "what": "the same rows' W4A4 results against the oracle's W4A16 expert (bf16 activations, the reference's default prefill arithmetic)"}
     if rank == 0:
         print(json.dumps(line), flush=True)
-    rc = 0 if parity["ok"] else 3                                     # a run whose sampled rows miss the oracle fails
+    rc = 0 if parity["ok"] and line["w4a4_vs_w4a16"]["ok"] else 3      # a run whose sampled rows miss the oracle fails
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
         dist.destroy_process_group()
+    return rc
 
 
 def run_dense(args):
-    """BASELINE config 5 (dense 27B-style MLP decode): one FFN layer = fused gate/up GEMV + down GEMV, hidden 5120, FFN 17408, M rows,
+    """The dense 27B-style MLP decode workload: one FFN layer = fused gate/up GEMV + down GEMV, hidden 5120, FFN 17408, M rows,
     for the NVFP4, 3-bit and 2-bit group-64 formats; 12 distinct layers' matrices cycled so L2 cannot serve repeats."""
     import torch
     import eke_hive_b200 as E
@@ -742,9 +781,9 @@ def run_records(args):
                       "config": {"workload": f"{n} experts, hidden {H}, FFN {I}, NVFP4 with compressed block scales → records; one batch call per step",
                                  "l2": f"{by / 1e6:.0f} MB read + written per step (larger than L2)"},
                       "roofline": {"bound": "hbm", "kernel": "record_main_kernel + csf_tail_kernel", "achieved": by / ms / 1e6, "peak": peak, "unit": "GB/s",
-                                   "frac": by / ms / 1e6 / peak, "traffic": 908.8e6,
-                                   "traffic_from": "ncu dram__bytes_read + dram__bytes_write of record_main + csf_tail for this workload "
-                                                   "(profiles/record_pack_batch_256x2048x512.md)", "algorithmic_bytes": by},
+                                   "frac": by / ms / 1e6 / peak, "traffic": by,
+                                   "traffic_source": "algorithmic (an ncu capture of record_main + csf_tail on this workload read 908.8 MB of DRAM traffic; not measured in this run)",
+                                   "algorithmic_bytes": by},
                       "cpu_baseline": {"value": cpu_rps, "unit": "records/s", "cores": 1, "kind": "port", "sample": f"{m} experts in 3 s"}}), flush=True)
 
 
@@ -757,8 +796,8 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="run one batch size only (default: 1, 4, 8, 16; headline 16)")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than 48 (development only; the number is then not the benchmark's)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "dense", "records"],
-                    help="decode = the benchmark proper (BASELINE config 2); prefill = one config-4 MoE layer on the FP4 tensor cores; "
-                         "dense = the config-5 MLP GEMVs; records = record assembly in front of the path (one GPU each; their own JSON line)")
+                    help="decode = the benchmark proper (Qwen3-Next-shaped MoE decode); prefill = one DeepSeek-shaped MoE layer on the FP4 tensor cores; "
+                         "dense = the dense 27B-style MLP GEMVs; records = record assembly in front of the path (one GPU each; their own JSON line)")
     ap.add_argument("--tokens", type=int, default=8192, help="--workload prefill: tokens per layer call")
     ap.add_argument("--experts", type=int, default=256, help="--workload prefill: routed experts resident (fewer = a smaller case for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -766,7 +805,7 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.workload == "prefill":
-        run_prefill(args)
+        sys.exit(run_prefill(args) or 0)
     elif args.workload == "dense":
         run_dense(args)
     elif args.workload == "records":

@@ -28,7 +28,7 @@ class RecLayout(C.Structure):
 
 
 class Config(C.Structure):
-    _fields_ = [("device", C.c_int), ("max_ctas", C.c_int), ("flags", C.c_int)]
+    _fields_ = [("device", C.c_int), ("max_ctas", C.c_int), ("flags", C.c_int), ("wait_polls", C.c_uint)]
 
 
 class MoePair(C.Structure):

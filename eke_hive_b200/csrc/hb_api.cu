@@ -33,6 +33,10 @@ int hb_create(const hb_config* cfg, hb_ctx** out) {
   c->sm_count = prop.multiProcessorCount;
   c->smem_optin = (int)prop.sharedMemPerBlockOptin;
   if (cudaMalloc(&c->dev_err, 256) != cudaSuccess || cudaMemset(c->dev_err, 0, 256) != cudaSuccess) { delete c; cudaGetLastError(); return HB_ERR_CUDA; }
+  {
+    const uint32_t polls = cfg && cfg->wait_polls ? cfg->wait_polls : (1u << 24);
+    if (cudaMemcpy(c->dev_err + kErrWaitPolls, &polls, 4, cudaMemcpyHostToDevice) != cudaSuccess) { cudaFree(c->dev_err); delete c; cudaGetLastError(); return HB_ERR_CUDA; }
+  }
   int r = hbk_moe_decode_setup(c);
   if (r == HB_OK) r = hbk_dense_setup(c);
   if (r == HB_OK) r = hbk_moe_prefill_setup(c);
@@ -115,7 +119,8 @@ int hb_check_device(hb_ctx* ctx, void* stream) {
   HB_CUDA(ctx, cudaStreamSynchronize(as_stream(stream)));
   if (v == 0) return HB_OK;
   HB_CUDA(ctx, cudaMemsetAsync(ctx->dev_err, 0, 4, as_stream(stream)));
-  return hb_fail(ctx, HB_ERR_DEVICE_FLAG, "device error word 0x%x (1 = producer wait, 2 = consumer wait, 4 = drain, 8 = epilogue wait, 16 = exchange slot wait, 32 = gate/up counter wait, 64 = down counter wait)", v);
+  return hb_fail(ctx, HB_ERR_DEVICE_FLAG, "device error word 0x%x (bits 0x1-0x80: a pipeline wait inside a decode or prefill kernel; 0x400-0x2000: the decode layer kernel's tables and grid barrier; "
+                 "0x40000: rows of another rank did not arrive; 0x80000: partial sums of another rank did not arrive; 0x400000: an expert record outside the tensor maps' range)", v);
 }
 
 int hb_rec_layout_make(int H, int I, hb_rec_layout* L) {
@@ -317,8 +322,9 @@ int hb_moe_layer(hb_ctx* ctx, const float* logits, int ld, int M, int E, int K, 
   layer_carve(ws, M, K, E, H, I, &W);
   const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
   __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(out);
-  if (M <= kDecodeRows || hb_moe_prefill_supported(H, I) <= 0) {
-    // decode operators, 64 rows at a time (one pass when M ≤ 64): per-row results do not depend on the batch
+  if (M <= kDecodeRows || !(ctx->flags & HB_FLAG_LAYER_A4) || hb_moe_prefill_supported(H, I) <= 0) {
+    // decode operators, 64 rows at a time (one pass when M ≤ 64): per-row results do not depend on the batch.  More rows go to the
+    // W4A4 grouped GEMM only when the context asked for that arithmetic
     for (int m0 = 0; m0 < M; m0 += kDecodeRows) {
       const int n = M - m0 < kDecodeRows ? M - m0 : kDecodeRows;
       const int r = hb_moe_layer_decode(ctx, logits + (size_t)m0 * ld, ld, n, E, K, renorm, logits_bf16, bias, sigmoid_scale, rec_tab, li, shared_rec, gate_col,

@@ -12,6 +12,10 @@
 
 #include "../../include/hive_b200.h"
 
+// Words of the context's 256-byte device block besides the error word [0]: [16] a counter the decode prep kernel owns, [17] the
+// poll limit of waits on flags that other ranks set (hb_config.wait_polls).
+constexpr int kErrWaitPolls = 17;
+
 struct hb_ctx {
   int device = 0;
   int sm_count = 0;

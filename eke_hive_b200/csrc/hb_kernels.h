@@ -33,7 +33,8 @@ int hbk_add_f32(hb_ctx* ctx, float* a, const float* b, size_t n, cudaStream_t st
 constexpr int HB_MAX_PAIRS = 4096;     // pairs per call (M·K plus the shared expert's M)
 constexpr int HB_MAX_EXPERTS = 1024;
 bool hbk_moe_decode_fast(int H, int I);                 // shapes the streaming tensor-core path takes
-size_t hbk_moe_decode_ws_bytes(int n_pairs, int H, int I);
+size_t hbk_moe_decode_ws_bytes(int n_pairs, int H, int I);          // what the public *_ws_bytes report: enough for either decode engine
+size_t hbk_moe_decode_ws_stream_bytes(int n_pairs, int H, int I);   // the streaming chain alone
 int hbk_moe_decode_setup(hb_ctx* ctx);                  // one-time kernel attributes (dynamic shared memory)
 // Expert-parallel exchange hooks of a decode pass (k_ep.cu): wait for the gathered rows before grouping, push the routed sums to the
 // owning ranks instead of storing them.
@@ -52,6 +53,7 @@ struct hbk_pair_src {
   int route = 0;                                                             // 0 = ids / w given, 1 = softmax, 2 = sigmoid + bias
   const float* logits = nullptr; int ld = 0, renorm = 0, logits_bf16 = 0;
   const float* bias = nullptr; float sig_scale = 1.f;
+  bool ws_stream_only = false;                                               // ws holds hbk_moe_decode_ws_stream_bytes only: the streaming chain must run
 };
 // What the last kernel does with the per-pair outputs.
 struct hbk_reduce {

@@ -28,7 +28,7 @@ inline hb_ctx* ctx() {
   int dev = 0;
   cudaGetDevice(&dev);
   if (!c[dev]) {
-    hb_config cfg{dev, 0, 0};
+    hb_config cfg{dev, 0, 0, 0};
     const int st = hb_create(&cfg, &c[dev]);
     if (st != HB_OK) throw Error(st, std::string("hb_create: ") + hb_status_string(st));
   }

@@ -482,10 +482,11 @@ bool hbk_moe_decode_fast(int H, int I) {
   return H > 0 && I > 0 && pick_kernel<false>(H, &a) && pick_kernel<true>(I, &b) && I % a.tr == 0 && H % b.tr == 0;
 }
 
-size_t hbk_moe_decode_ws_bytes(int n, int H, int I) {
+size_t hbk_moe_decode_ws_stream_bytes(int n, int H, int I) {
   if (n < 1) n = 1;
-  return 256 + al256((size_t)n * sizeof(Group)) + 5 * al256((size_t)n * 4) + al256((size_t)n * I * 2) + al256((size_t)n * H * 2) + hbk_moe_dtc_ws_extra(n, H, I);
+  return 256 + al256((size_t)n * sizeof(Group)) + 5 * al256((size_t)n * 4) + al256((size_t)n * I * 2) + al256((size_t)n * H * 2);
 }
+size_t hbk_moe_decode_ws_bytes(int n, int H, int I) { return hbk_moe_decode_ws_stream_bytes(n, H, I) + hbk_moe_dtc_ws_extra(n < 1 ? 1 : n, H, I); }
 
 int hbk_moe_decode_setup(hb_ctx* ctx) {
   for (int wk : kWkList) {
@@ -515,7 +516,7 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
   if (P <= 0) return HB_OK;
   // routed form on a shape the tensor-memory layer kernel takes: two launches (prep, layer) instead of the streaming chain below
   const bool want_tc = (ctx->flags & HB_FLAG_DECODE_TC) != 0;       // library default for now: the streaming chain
-  if (routed && want_tc && !red.ep && !src.wait_flags && hbk_moe_dtc_supported(H, I) && !(ctx->flags & (HB_FLAG_FUSED | HB_FLAG_DECODE_MMA_SYNC)) &&
+  if (routed && want_tc && !src.ws_stream_only && !red.ep && !src.wait_flags && hbk_moe_dtc_supported(H, I) && !(ctx->flags & (HB_FLAG_FUSED | HB_FLAG_DECODE_MMA_SYNC)) &&
       hbk_moe_dtc_fits(ctx, P, src.E, H, I))
     return hbk_moe_dtc_run(ctx, src, x, H, I, limit, red, ws, st);
   DecodeWs w = carve(ws, P, H, I);

@@ -10,15 +10,14 @@
 //   down GEMM             tile = 128 pairs × 256 rows of H; part[pair] = bf16(acc·(gy·g2))
 //   reduce                out[row] = Σ_k part·w in k order (or the fused shared-expert combine)
 //
-// GEMM kernel: persistent CTAs of 10 warps.  Warp 5 moves the e2m1 codes of both operands with TMA (`cp.async.bulk.tensor`, 128-byte
+// GEMM kernel: persistent CTAs of 15 warps.  One warp moves the e2m1 codes of both operands with TMA (`cp.async.bulk.tensor`, 128-byte
 // swizzle: the K-major layout the MMA reads).  The activation rows of a tile are contiguous because the quantised rows are first
 // copied into expert order; the weight matrices sit inside expert records at arbitrary addresses, so a small kernel stamps each
-// record's addresses into tensor maps on the device (`tensormap.replace`).  The e4m3 block scales arrive by TMA too, row-major
-// (16 bytes per row and stage); warps 6-9 transpose them in place into the 32×16-byte chunks `tcgen05.cp` moves to tensor
-// memory.  Warp 4 issues `tcgen05.cp` + `tcgen05.mma
-// kind::mxf4nvf4` (block 16, ue4m3 scales: both operands' block scales are applied by the tensor core) and commits to the stage's
-// mbarrier.  Warps 0-3 read the accumulators back with `tcgen05.ld` and run the epilogue.  Every wait is bounded; on a timeout
-// the kernel records a site code in the context's error word, drains its copies, frees its tensor memory and returns.
+// record's addresses into tensor maps on the device (`tensormap.replace`).  The e4m3 block scales are fetched by the scale warps with
+// plain 16-byte loads (one row of a stage each) and put into the chunk order tensor memory wants.  One warp issues
+// `tcgen05.mma kind::mxf4nvf4` (block 16, ue4m3 scales: both operands' block scales are applied by the tensor core) and commits to
+// the stage's mbarrier.  Four warps read the accumulators back with `tcgen05.ld` and run the epilogue.  Every wait is bounded; on a
+// timeout the kernel records a site code in the context's error word, drains its copies, frees its tensor memory and returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>

@@ -20,6 +20,8 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 
 // Device address of the array, per device ordinal.  In host code `g_static_scratch` is only a handle for the runtime, not
 // a device address: it must go through cudaGetSymbolAddress, with the right device current, before a kernel may use it.
+// The cache is filled without a lock: two host threads making the FIRST call on a device at the same time both look the
+// address up and both store the same value — harmless, and the only thing calls from different threads share on the host.
 void* g_scratch_ptr[64] = {};
 
 int scratch_for_current_device(hb_ctx* ctx, void** out) {
@@ -44,7 +46,7 @@ extern "C" {
 int hb_moe_decode_static_max_pairs(int H, int I) {
   if (H <= 0 || I <= 0 || H % 32 || I % 32) return 0;
   int n = 0;
-  while (n < HB_MAX_PAIRS && hbk_moe_decode_ws_bytes(n + 1, H, I) <= kStaticScratchBytes) ++n;
+  while (n < HB_MAX_PAIRS && hbk_moe_decode_ws_stream_bytes(n + 1, H, I) <= kStaticScratchBytes) ++n;
   return n;
 }
 
@@ -56,7 +58,7 @@ int hb_moe_decode_routed_static(hb_ctx* ctx, const int32_t* ids, const float* w,
   HB_REQUIRE(ctx, M > 0 && K > 0 && E > 0 && E <= HB_MAX_EXPERTS && li >= 0, HB_ERR_INVALID, "moe_decode_routed_static: M=%d K=%d E=%d li=%d", M, K, E, li);
   HB_REQUIRE(ctx, H > 0 && I > 0 && H % 32 == 0 && I % 32 == 0, HB_ERR_UNSUPPORTED, "moe_decode_routed_static: H=%d I=%d must be multiples of 32", H, I);
   HB_REQUIRE(ctx, hb_aligned(x, 16), HB_ERR_INVALID, "moe_decode_routed_static: x must be 16-byte aligned");
-  const size_t need = hbk_moe_decode_ws_bytes(M * K, H, I);
+  const size_t need = hbk_moe_decode_ws_stream_bytes(M * K, H, I);    // this entry point always runs the streaming chain
   HB_REQUIRE(ctx, (long long)M * K <= HB_MAX_PAIRS && need <= kStaticScratchBytes, HB_ERR_UNSUPPORTED,
              "moe_decode_routed_static: %d pairs at H=%d I=%d need %zu bytes of scratch, the built-in array holds %zu (at most %d pairs at this shape); "
              "use hb_moe_decode_routed with a caller workspace",
@@ -65,6 +67,7 @@ int hb_moe_decode_routed_static(hb_ctx* ctx, const int32_t* ids, const float* w,
   const int r = scratch_for_current_device(ctx, &ws);
   if (r) return r;
   hbk_pair_src src; src.ids = ids; src.w = w; src.M = M; src.K = K; src.tab = rec_tab; src.li = li; src.E = E;
+  src.ws_stream_only = true;
   hbk_reduce red; red.shared = cmb->shared; red.lg = cmb->lg; red.ld = cmb->ld; red.col = cmb->col; red.out_bf16 = cmb->out;
   return hbk_moe_decode_run(ctx, src, x, H, I, limit, red, ws, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -41,12 +41,12 @@ def _stream():
 class Context:
     """One hb_ctx: a device, its SM count and the device error word.  Calls on one context must not overlap."""
 
-    def __init__(self, device: int | None = None, max_ctas: int = 0, flags: int = 0):
+    def __init__(self, device: int | None = None, max_ctas: int = 0, flags: int = 0, wait_polls: int = 0):
         if not torch.cuda.is_available():
             raise HbError(-4, "no CUDA device: the library has no CPU path")
         self.device = torch.cuda.current_device() if device is None else device
         self._h = C.c_void_p()
-        cfg = Config(self.device, max_ctas, flags)
+        cfg = Config(self.device, max_ctas, flags, wait_polls)
         st = _L().hb_create(C.byref(cfg), C.byref(self._h))
         if st != 0:
             raise HbError(st, _L().hb_status_string(st).decode())

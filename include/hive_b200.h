@@ -42,12 +42,17 @@ typedef struct hb_config {
   int device;       /* CUDA device ordinal */
   int max_ctas;     /* 0 = one CTA set per SM of the device; >0 caps the persistent grids (tests) */
   int flags;        /* HB_FLAG_* */
+  unsigned wait_polls; /* how often a kernel polls a flag another rank sets before it gives up and sets the device error word
+                          (hb_check_device then returns HB_ERR_DEVICE_FLAG); 0 = 2^24 polls with back-off, a few seconds */
 } hb_config;
 #define HB_FLAG_NO_PDL 1   /* launch every kernel fully serialised (no programmatic dependent launch) */
 #define HB_FLAG_FUSED 2    /* decode: run gate/up, down and reduce as ONE persistent kernel (experimental; default: three kernels chained by PDL) */
 #define HB_FLAG_DECODE_MMA_SYNC 8 /* decode: run the routed operators on the register-dequantisation (mma.sync) streaming kernels */
 #define HB_FLAG_DECODE_TC 16      /* decode: run the routed operators on the tensor-memory layer kernel (tcgen05 block-scaled FP4 over exact
                                      digit planes of the bf16 activations).  Neither flag: the library picks (see hb_moe_decode_supported). */
+#define HB_FLAG_LAYER_A4 32       /* hb_moe_layer may run calls of more than 64 rows on the W4A4 grouped GEMM (activations quantised to NVFP4 — the
+                                     reference's lossy opt-in, fn_moe_prefill_set_a4).  Without it hb_moe_layer keeps bf16 activations at every
+                                     row count: the same numbers as the decode operators, never a silent change of arithmetic */
 #define HB_FLAG_PREFILL_A16 4u /* hb_moe_prefill keeps bf16 activations (W4A16, the reference's default prefill arithmetic): rows run through
                                   the decode kernels in sub-chunks — exact, but the expert records are streamed once per sub-chunk */
 
@@ -158,9 +163,11 @@ HB_API int hb_moe_decode_routed(hb_ctx* ctx, const int32_t* ids, const float* w,
  *   - a call whose scratch would exceed the array fails with HB_ERR_UNSUPPORTED and a message naming the limit;
  *     hb_moe_decode_static_max_pairs(H, I) gives the largest M·K accepted at a shape (813 pairs at H 2048, I 512; 371 at H 4096, I 1536);
  *   - the first call on a device looks up the array's device address (with that device current); make that first call before
- *     any stream capture.  No call allocates or frees memory;
+ *     any stream capture (two host threads that make that first call at the same time both look it up and store the same
+ *     value: harmless).  No call allocates or frees memory;
  *   - every call on a device uses the same array and finds the previous call's contents in it (what must start at zero is
- *     cleared by the kernels themselves); calls that overlap on the GPU race on it — keep them on one stream. */
+ *     cleared by the kernels themselves); calls that overlap on the GPU race on it — keep them on one stream;
+ *   - it always runs the streaming kernels, whatever decode engine the context's flags select. */
 HB_API int hb_moe_decode_static_max_pairs(int H, int I);
 HB_API int hb_moe_decode_routed_static(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int K, const uint8_t* const* rec_tab, int li, int E,
                                        const void* x_bf16, int H, int I, float limit, const hb_pf_combine* cmb, void* stream);
@@ -268,9 +275,11 @@ HB_API int hb_fp4_peak_probe(hb_ctx* ctx, int rounds, float* tflops);
 
 /* ---- a whole MoE layer for any number of rows (the expert-dispatch scheduler) ---- */
 /* router → routed experts → always-on shared expert (one more NVFP4 record, NULL = none) → combine, like hb_moe_layer_decode, for
- * any M: M ≤ 64 rows run on the decode operators (bf16 activations), more rows on the grouped tensor-core GEMM (hb_moe_prefill:
- * NVFP4 activations unless the context has HB_FLAG_PREFILL_A16) when the shape allows it (H, I multiples of 256), else on the
- * decode operators 64 rows at a time — the reference engine's own switch (engine/src/qwen/qwen_engine.cpp:825, :873).
+ * any M.  By default every row count runs on the decode operators (bf16 activations, W4A16 — the reference's default arithmetic,
+ * engine/include/hive/qwen/fn_moe.h:50-52), 64 rows at a time above 64 rows, so a row's result never depends on how many rows
+ * the call has.  A context created with HB_FLAG_LAYER_A4 sends calls of more than 64 rows to the grouped tensor-core GEMM
+ * (hb_moe_prefill with NVFP4 activations, W4A4) when the shape allows it (H, I multiples of 256) — the reference engine's own
+ * switch (engine/src/qwen/qwen_engine.cpp:825, :873) with its opt-in arithmetic.
  * ws ≥ hb_moe_layer_ws_bytes(M, K, E, H, I). */
 HB_API size_t hb_moe_layer_ws_bytes(int M, int K, int E, int H, int I);
 HB_API int hb_moe_layer(hb_ctx* ctx, const float* logits, int ld, int M, int E, int K, int renorm, int logits_bf16, const float* bias,

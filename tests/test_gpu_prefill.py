@@ -143,30 +143,73 @@ def test_moe_prefill_bf16_activations_equals_decode_operator(E, oracle):
     assert np.max(np.abs(out.cpu().numpy() - orc) / rms) <= 2e-2
 
 
+def test_w4a4_distance_from_w4a16(E, oracle):
+    """How far the grouped GEMM's arithmetic (NVFP4 activations, W4A4) is from the reference's default (bf16 activations, W4A16) on
+    the same rows, at the DeepSeek-shaped expert size: the reference's own gate for its W4A4 option is cosine > 0.98 per row
+    (engine/tests/test_fn_moe_pf.cu:419).  The W4A16 side is both this library's decode operator and the CPU oracle."""
+    dev = torch.device("cuda")
+    H, I, E_, K, M = 7168, 2048, 4, 2, 96
+    rng = np.random.default_rng(419)
+    recs = random_records(oracle, H, I, E_, 419)
+    keep = upload(recs, dev)
+    tab = E.rec_table(keep)
+    ids_np = np.stack([rng.permutation(E_)[:K] for _ in range(M)]).astype(np.int32)
+    w_np = rng.random((M, K), dtype=np.float32)
+    ids, w = torch.tensor(ids_np, device=dev), torch.tensor(w_np, device=dev)
+    x = torch.tensor((rng.standard_normal((M, H)) * np.exp(rng.standard_normal((M, 1)))).astype(np.float32)).to(torch.bfloat16).to(dev)
+    a4 = E.fn_moe_prefill(tab, 0, E_, ids, w, x, H, I).double()
+    a16 = torch.cat([E.moe_decode_routed_f32(ids[m0:m0 + 64], w[m0:m0 + 64], tab, 0, E_, x[m0:m0 + 64], H, I) for m0 in range(0, M, 64)]).double()
+    torch.cuda.synchronize()
+    E.context().check_device()
+    cos = (a4 * a16).sum(1) / (a4.norm(dim=1) * a16.norm(dim=1) + 1e-30)
+    rel = (a4 - a16).abs().max(1).values / (a16.pow(2).mean(1).sqrt() + 1e-30)
+    print(f"W4A4 vs W4A16 over {M} rows: cosine min {float(cos.min()):.5f} mean {float(cos.mean()):.5f}; max |diff| / row RMS {float(rel.max()):.3f}")
+    assert float(cos.min()) > 0.98
+    # the oracle's W4A16 expert on two of the rows says the same about the W4A4 results
+    for m in (0, M - 1):
+        ref = sum(np.float64(w_np[m, k]) * oracle.expert_forward(recs[ids_np[m, k]], H, I, x[m].float().cpu().numpy(), 1.0, 0.0).astype(np.float64) for k in range(K))
+        g = a4[m].cpu().numpy()
+        assert float((g * ref).sum() / (np.linalg.norm(g) * np.linalg.norm(ref))) > 0.98
+
+
 def test_moe_layer_dispatches_by_row_count(E, oracle):
-    """hb_moe_layer: ≤ 64 rows are the decode layer bit for bit; more rows equal router → shared expert through the grouped GEMM →
-    routed experts with the fused combine, composed by hand from the same operators."""
+    """hb_moe_layer: without HB_FLAG_LAYER_A4 every row count is the decode layer bit for bit (W4A16, rows independent of the batch);
+    with the flag, more than 64 rows equal router → shared expert through the W4A4 grouped GEMM → routed experts with the fused
+    combine, composed by hand from the same operators, and ≤ 64 rows are still the decode layer."""
     dev = torch.device("cuda")
     H, I, E_, K = 512, 256, 8, 2
     rng = np.random.default_rng(31)
     recs = random_records(oracle, H, I, E_ + 1, 31)
     keep = upload(recs, dev)
     tab = E.rec_table(keep[:E_])
-    for M in (20, 150):
-        x = torch.tensor(rng.standard_normal((M, H)).astype(np.float32)).to(torch.bfloat16).to(dev)
-        lg = torch.tensor(rng.standard_normal((M, E_ + 1)).astype(np.float32), device=dev)
-        ids, w, out = E.moe_layer(lg, x, tab, 0, E_, K, H, I, shared_rec=keep[E_], gate_col=E_)
-        if M <= 64:
-            ids2, w2, out2 = E.moe_layer_decode(lg, x, tab, 0, E_, K, H, I, shared_rec=keep[E_], gate_col=E_)
-        else:
-            ids2, w2 = E.router_softmax_topk(lg, K, True, True, E=E_)
-            sh = E.fn_moe_prefill(E.rec_table([keep[E_]]), 0, 1, torch.zeros((M, 1), dtype=torch.int32, device=dev),
-                                  torch.ones((M, 1), dtype=torch.float32, device=dev), x, H, I)
-            out2 = E.fn_moe_prefill(tab, 0, E_, ids2, w2, x, H, I, shared=sh.to(torch.bfloat16), lg=lg, col=E_)
+    ctx_a4 = E.Context(flags=32)                                        # HB_FLAG_LAYER_A4
+    try:
+        for M in (20, 150):
+            x = torch.tensor(rng.standard_normal((M, H)).astype(np.float32)).to(torch.bfloat16).to(dev)
+            lg = torch.tensor(rng.standard_normal((M, E_ + 1)).astype(np.float32), device=dev)
+            # default context: the decode operators at every row count — each row equals the row run alone in a 64-row slice
+            ids, w, out = E.moe_layer(lg, x, tab, 0, E_, K, H, I, shared_rec=keep[E_], gate_col=E_)
+            for m0 in range(0, M, 64):
+                sl = slice(m0, min(M, m0 + 64))
+                ids2, w2, out2 = E.moe_layer_decode(lg[sl], x[sl], tab, 0, E_, K, H, I, shared_rec=keep[E_], gate_col=E_)
+                assert torch.equal(ids[sl], ids2) and torch.equal(w[sl], w2), M
+                assert torch.equal(out[sl].view(torch.int16), out2.view(torch.int16)), M
+            # opt-in context
+            ids, w, out = E.moe_layer(lg, x, tab, 0, E_, K, H, I, shared_rec=keep[E_], gate_col=E_, ctx=ctx_a4)
+            if M <= 64:
+                ids2, w2, out2 = E.moe_layer_decode(lg, x, tab, 0, E_, K, H, I, shared_rec=keep[E_], gate_col=E_)
+            else:
+                ids2, w2 = E.router_softmax_topk(lg, K, True, True, E=E_)
+                sh = E.fn_moe_prefill(E.rec_table([keep[E_]]), 0, 1, torch.zeros((M, 1), dtype=torch.int32, device=dev),
+                                      torch.ones((M, 1), dtype=torch.float32, device=dev), x, H, I)
+                out2 = E.fn_moe_prefill(tab, 0, E_, ids2, w2, x, H, I, shared=sh.to(torch.bfloat16), lg=lg, col=E_)
+            torch.cuda.synchronize()
+            E.context().check_device(); ctx_a4.check_device()
+            assert torch.equal(ids, ids2) and torch.equal(w, w2), M
+            assert torch.equal(out.view(torch.int16), out2.view(torch.int16)), M
+    finally:
         torch.cuda.synchronize()
-        E.context().check_device()
-        assert torch.equal(ids, ids2) and torch.equal(w, w2), M
-        assert torch.equal(out.view(torch.int16), out2.view(torch.int16)), M
+        ctx_a4.close()
 
 
 def test_moe_prefill_degenerate_inputs(E, oracle):
