@@ -38,6 +38,7 @@ int hb_create(const hb_config* cfg, hb_ctx** out) {
     if (cudaMemcpy(c->dev_err + kErrWaitPolls, &polls, 4, cudaMemcpyHostToDevice) != cudaSuccess) { cudaFree(c->dev_err); delete c; cudaGetLastError(); return HB_ERR_CUDA; }
   }
   int r = hbk_moe_decode_setup(c);
+  if (r == HB_OK) r = hbk_nvfp4_setup(c);
   if (r == HB_OK) r = hbk_dense_setup(c);
   if (r == HB_OK) r = hbk_moe_prefill_setup(c);
   if (r != HB_OK) { cudaFree(c->dev_err); delete c; return r; }

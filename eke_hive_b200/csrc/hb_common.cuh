@@ -13,8 +13,9 @@
 #include "../../include/hive_b200.h"
 
 // Words of the context's 256-byte device block besides the error word [0]: [16] a counter the decode prep kernel owns, [17] the
-// poll limit of waits on flags that other ranks set (hb_config.wait_polls).
+// poll limit of waits on flags that other ranks set (hb_config.wait_polls), [18..19] counters of the prefill plan kernel.
 constexpr int kErrWaitPolls = 17;
+constexpr int kErrPlanMeet = 18;      // [18], [19]: the meeting counters of the prefill plan kernel
 
 struct hb_ctx {
   int device = 0;

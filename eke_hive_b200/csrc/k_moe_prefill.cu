@@ -1,14 +1,15 @@
 // Routed-expert prefill (rows > 64): one grouped W4A4 GEMM pass over every expert that received rows, on the 5th-generation tensor
 // cores.  Mirrors hive::qwen::fn_moe_prefill with its NVFP4-activation switch on (engine/src/qwen/fn_moe_pf.cu:439-446, :858-941):
 //
-//   count / scan / fill   the (row, k) pairs sorted by expert (the order inside an expert is irrelevant: a pair's result depends only
-//                         on its own row) and a list of 128-pair tiles
-//   quantise x            per-row dynamic NVFP4 (hb_a4_quant's rule), then the quantised rows copied into expert order
+//   plan                  the (row, k) pairs sorted by expert (the order inside an expert is irrelevant: a pair's result depends only
+//                         on its own row) and a list of 128-pair tiles — one launch of a few CTAs that meet once (pf_plan_kernel)
+//   quantise x            per-row dynamic NVFP4 (hb_a4_quant's rule); a row is quantised once and written straight into the slots of
+//                         its pairs, so the GEMM's activation tiles are contiguous
 //   gate|up GEMM          tile = 128 pairs × (128 gate + 128 up rows of I); block-scaled FP4 MMA, fp32 accumulators in tensor memory;
 //                         epilogue g = bf16(acc·gx·g1), u = bf16(acc·gx·g3), y = bf16(silu(g)·u)
 //   quantise y            per pair
 //   down GEMM             tile = 128 pairs × 256 rows of H; part[pair] = bf16(acc·(gy·g2))
-//   reduce                out[row] = Σ_k part·w in k order (or the fused shared-expert combine)
+//   sum                   out[row] = Σ_k part·w in k order (or the fused shared-expert combine)
 //
 // GEMM kernel: persistent CTAs of 15 warps.  One warp moves the e2m1 codes of both operands with TMA (`cp.async.bulk.tensor`, 128-byte
 // swizzle: the K-major layout the MMA reads).  The activation rows of a tile are contiguous because the quantised rows are first
@@ -46,13 +47,13 @@ static_assert(PF_SF_COL0 + 48 * PF_ST <= PF_TMEM_COLS, "tensor memory");
 static_assert(PF_STAGE % 1024 == 0, "stage buffers must keep the 1024-byte alignment of the swizzle atom");
 static_assert(PF_SMEM <= 227 * 1024, "shared memory");
 
-struct PfTile { int e, slot0, m; };
+struct TileRef { int slot0, rows, expert; };   // 128 consecutive slots (or fewer) of one expert's run of the sorted pairs
 
 enum { PF_PLAIN = 0, PF_GU = 1, PF_DOWN = 2 };
 
 struct PfGemmArgs {
   // work list
-  const PfTile* tiles; const int* n_tiles;     // n_tiles == nullptr: one implicit tile list of ceil(M / 128) tiles over rows [0, M)
+  const TileRef* tiles; const int* n_tiles;     // n_tiles == nullptr: one implicit tile list of ceil(M / 128) tiles over rows [0, M)
   int M;                                       // PLAIN only
   const int* perm;                             // pair of a sorted slot (DOWN scatters its rows by it)
   // A operand (quantised activations, tile rows contiguous): codes come through the kernel's tensor-map parameter
@@ -72,9 +73,9 @@ struct PfGemmArgs {
 constexpr uint32_t PF_IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(PF_BN >> 3) << 17) | ((uint32_t)(PF_BM >> 4) << 24);
 
 // ---- the grouped GEMM ---------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ PfTile pf_tile(const PfGemmArgs& a, int ti) {
+__device__ __forceinline__ TileRef pf_tile(const PfGemmArgs& a, int ti) {
   if (a.tiles) return a.tiles[ti];
-  PfTile t; t.e = 0; t.slot0 = ti * PF_BM; t.m = min(PF_BM, a.M - ti * PF_BM);
+  TileRef t; t.expert = 0; t.slot0 = ti * PF_BM; t.rows = min(PF_BM, a.M - ti * PF_BM);
   return t;
 }
 __device__ __forceinline__ uint4 pf_pack8(const float* v) {
@@ -137,11 +138,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
       bool ok = true;
       for (long long w = blockIdx.x; w < work && ok; w += gridDim.x) {
         const int ti = (int)(w / n_nt), nt = (int)(w - (long long)ti * n_nt);
-        const PfTile tl = pf_tile(a, ti);
+        const TileRef tl = pf_tile(a, ti);
         const CUtensorMap *m0 = &tmB0, *m1 = &tmB0;
         int r0 = nt * 256, r1 = nt * 256 + 128;                               // B rows of the tile's two 128-row boxes
-        if (MODE == PF_GU) { m0 = a.tmB + (size_t)tl.e * 6; m1 = m0 + 1; r0 = r1 = nt * 128; }
-        if (MODE == PF_DOWN) m0 = m1 = a.tmB + (size_t)tl.e * 6 + 2;
+        if (MODE == PF_GU) { m0 = a.tmB + (size_t)tl.expert * 6; m1 = m0 + 1; r0 = r1 = nt * 128; }
+        if (MODE == PF_DOWN) m0 = m1 = a.tmB + (size_t)tl.expert * 6 + 2;
         if (MODE != PF_PLAIN) { tmap_acquire(m0); if (m1 != m0) tmap_acquire(m1); }
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const uint32_t stage = it % PF_ST;
@@ -169,11 +170,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
       Rows r = {nullptr, nullptr, nullptr};
       if (w >= work) return r;
       const int ti = (int)(w / n_nt), nt = (int)(w - (long long)ti * n_nt);
-      const PfTile tl = pf_tile(a, ti);
-      r.pa = a.as + (size_t)(tl.slot0 + min(lt, tl.m - 1)) * rows;          // rows past the tile's end repeat its last row (never stored)
+      const TileRef tl = pf_tile(a, ti);
+      r.pa = a.as + (size_t)(tl.slot0 + min(lt, tl.rows - 1)) * rows;          // rows past the tile's end repeat its last row (never stored)
       if (MODE == PF_PLAIN) { r.pb = a.bs + (size_t)(nt * 256 + lt) * rows; r.pc = r.pb + 128 * rows; }
       else {
-        const uint8_t* rec = a.tab[tl.e];
+        const uint8_t* rec = a.tab[tl.expert];
         if (MODE == PF_GU) { r.pb = rec + a.L.s1 + (size_t)(nt * 128 + lt) * rows; r.pc = rec + a.L.s3 + (size_t)(nt * 128 + lt) * rows; }
         else { r.pb = rec + a.L.s2 + (size_t)(nt * 256 + lt) * rows; r.pc = r.pb + 128 * rows; }
       }
@@ -265,14 +266,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
     bool ok = true;
     for (long long w = blockIdx.x; w < work && ok; w += gridDim.x, ++tcount) {
       const int ti = (int)(w / n_nt), nt = (int)(w - (long long)ti * n_nt);
-      const PfTile tl = pf_tile(a, ti);
-      const bool valid = m < tl.m;
-      const int slot = tl.slot0 + min(m, tl.m - 1);
+      const TileRef tl = pf_tile(a, ti);
+      const bool valid = m < tl.rows;
+      const int slot = tl.slot0 + min(m, tl.rows - 1);
       float f0 = 0.f, f1 = 0.f, f2 = 0.f;
       size_t orow = 0;
       if (MODE == PF_PLAIN) { f0 = a.ag[slot] * a.bg; orow = (size_t)slot; }
       else {
-        const float* g = reinterpret_cast<const float*>(a.tab[tl.e] + a.L.g);
+        const float* g = reinterpret_cast<const float*>(a.tab[tl.expert] + a.L.g);
         if (MODE == PF_GU) { f0 = a.ag[slot]; f1 = g[0]; f2 = g[1]; orow = (size_t)slot; }
         else { f0 = a.ag[slot] * g[2]; orow = (size_t)a.perm[slot]; }
       }
@@ -378,66 +379,82 @@ __global__ void __launch_bounds__(128, 1) pf_peak_kernel(int n_rounds, uint32_t*
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, PF_TMEM_COLS); }
 }
 
-// ---- sort by expert ----------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ bool pf_live(const int32_t* ids, int p, int E, const uint8_t* const* tab, int* e_out) {
-  const int e = ids[p];
-  *e_out = e;
-  return e >= 0 && e < E && tab[e] != nullptr;                               // ids outside [0, E) and absent records contribute nothing
-}
-__global__ void pf_count_kernel(const int32_t* __restrict__ ids, int P, int E, const uint8_t* const* __restrict__ tab, int* __restrict__ cnt) {
-  const int p = blockIdx.x * blockDim.x + threadIdx.x;
-  int e;
-  if (p < P && pf_live(ids, p, E, tab, &e)) atomicAdd(&cnt[e], 1);
-}
-// one block, E ≤ 1024: exclusive prefix sums of the pair counts (→ fill cursors) and of the tile counts (→ the tile list)
-__global__ void __launch_bounds__(1024) pf_scan_kernel(const int* __restrict__ cnt, int E, int* __restrict__ cursor, PfTile* __restrict__ tiles,
-                                                       int* __restrict__ n_tiles, int* __restrict__ n_slots) {
-  __shared__ int wsum_c[32], wsum_t[32];
-  const int e = threadIdx.x, lane = e & 31, wp = e >> 5;
-  const int c = e < E ? cnt[e] : 0, t = (c + PF_BM - 1) / PF_BM;
-  int ic = c, itl = t;                                                       // inclusive scans inside the warp
-  for (int o = 1; o < 32; o <<= 1) {
-    const int uc = __shfl_up_sync(0xffffffffu, ic, o), ut = __shfl_up_sync(0xffffffffu, itl, o);
-    if (lane >= o) { ic += uc; itl += ut; }
+// ---- the plan of a call: pairs sorted by expert, and the tile list ---------------------------------------------------------------
+// One launch of up to 64 CTAs that meet once in the middle (all are resident: the grid is smaller than the machine).  A CTA owns a
+// contiguous slice of the pairs.  First half: a histogram of its slice over the experts in shared memory, stored as row `cta` of a
+// [CTAs][E] table.  After the meeting every CTA adds up the table's columns for itself — the column total gives the expert's run
+// (an exclusive scan over the experts, done redundantly by every CTA), the rows above its own give where its slice's share of the run
+// starts — and places its pairs with shared-memory cursors.  No global atomics on the data, no separate scan launch, and a pair's
+// slot depends only on which CTA holds it and on the order inside that CTA (any order inside an expert's run gives the same
+// results: a pair's output depends on its own row alone).  CTA 0 also writes the tile list.  pos_of[p] = slot of pair p, or -1 for
+// a pair that contributes nothing (id outside [0, E), or no record for the expert on this GPU).
+constexpr int PLAN_THREADS = 1024, PLAN_MAX_CTAS = 64;
+struct PlanArgs {
+  const int32_t* ids; int P, E; const uint8_t* const* tab;
+  int* hist;                       // [CTAs][E]
+  int* perm; int* pos_of; TileRef* tiles; int* n_tiles; int* n_slots;
+  unsigned int* meet;              // two context-owned counters, zero between launches
+  uint32_t* err;
+};
+__global__ void __launch_bounds__(PLAN_THREADS) pf_plan_kernel(const PlanArgs a) {
+  __shared__ int cur[1024];
+  __shared__ int wsum[2][32];
+  const int G = gridDim.x, cta = blockIdx.x, t = threadIdx.x, lane = t & 31, wp = t >> 5;
+  const int per = (a.P + G - 1) / G, p0 = min(a.P, cta * per), p1 = min(a.P, p0 + per);
+  auto expert_of = [&](int p) -> int { const int e = a.ids[p]; return (e >= 0 && e < a.E && a.tab[e] != nullptr) ? e : -1; };
+  cur[t] = 0;
+  __syncthreads();
+  for (int p = p0 + t; p < p1; p += PLAN_THREADS) { const int e = expert_of(p); if (e >= 0) atomicAdd(&cur[e], 1); }
+  __syncthreads();
+  if (t < a.E) a.hist[(size_t)cta * a.E + t] = cur[t];
+  // ---- the meeting
+  __threadfence();
+  __syncthreads();
+  if (t == 0) {
+    atomicAdd(a.meet, 1u);
+    uint32_t spins = 0;
+    while (*reinterpret_cast<volatile unsigned int*>(a.meet) < (unsigned)G) {
+      if (++spins > (1u << 24)) { atomicOr(a.err, 0x4000u); break; }
+      __nanosleep(64);
+    }
+    __threadfence();
+    if (atomicAdd(a.meet + 1, 1u) == (unsigned)G - 1) { a.meet[0] = 0u; a.meet[1] = 0u; }   // the last one through clears both for the next launch
   }
-  if (lane == 31) { wsum_c[wp] = ic; wsum_t[wp] = itl; }
+  __syncthreads();
+  // ---- column sums, the scan over the experts, this CTA's cursors
+  int tot = 0, above = 0;
+  if (t < a.E) {
+    for (int g = 0; g < G; ++g) { const int h = __ldcg(a.hist + (size_t)g * a.E + t); if (g < cta) above += h; tot += h; }
+  }
+  const int nt = (tot + PF_BM - 1) / PF_BM;
+  int ic = tot, it = nt;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int uc = __shfl_up_sync(0xffffffffu, ic, o), ut = __shfl_up_sync(0xffffffffu, it, o);
+    if (lane >= o) { ic += uc; it += ut; }
+  }
+  if (lane == 31) { wsum[0][wp] = ic; wsum[1][wp] = it; }
   __syncthreads();
   if (wp == 0) {
-    int vc = wsum_c[lane], vt = wsum_t[lane];
+    int vc = wsum[0][lane], vt = wsum[1][lane];
     for (int o = 1; o < 32; o <<= 1) {
       const int uc = __shfl_up_sync(0xffffffffu, vc, o), ut = __shfl_up_sync(0xffffffffu, vt, o);
       if (lane >= o) { vc += uc; vt += ut; }
     }
-    wsum_c[lane] = vc; wsum_t[lane] = vt;
+    wsum[0][lane] = vc; wsum[1][lane] = vt;
   }
   __syncthreads();
-  const int off = ic - c + (wp ? wsum_c[wp - 1] : 0), toff = itl - t + (wp ? wsum_t[wp - 1] : 0);
-  if (e < E) {
-    cursor[e] = off;
-    for (int i = 0; i < t; ++i) { PfTile tl; tl.e = e; tl.slot0 = off + i * PF_BM; tl.m = min(PF_BM, c - i * PF_BM); tiles[toff + i] = tl; }
+  const int run0 = ic - tot + (wp ? wsum[0][wp - 1] : 0), tile0 = it - nt + (wp ? wsum[1][wp - 1] : 0);
+  cur[t] = run0 + above;
+  if (cta == 0) {
+    for (int i = 0; i < nt; ++i) { TileRef tl; tl.expert = t; tl.slot0 = run0 + i * PF_BM; tl.rows = min(PF_BM, tot - i * PF_BM); a.tiles[tile0 + i] = tl; }
+    if (t == PLAN_THREADS - 1) { *a.n_tiles = wsum[1][31]; *a.n_slots = wsum[0][31]; }
   }
-  if (e == 1023) { *n_tiles = wsum_t[31]; *n_slots = wsum_c[31]; }
-}
-__global__ void pf_fill_kernel(const int32_t* __restrict__ ids, int P, int E, const uint8_t* const* __restrict__ tab, int* __restrict__ cursor,
-                               int* __restrict__ perm) {
-  const int p = blockIdx.x * blockDim.x + threadIdx.x;
-  int e;
-  if (p < P && pf_live(ids, p, E, tab, &e)) perm[atomicAdd(&cursor[e], 1)] = p;
-}
-
-// the quantised activation rows in expert order: slot s ← row perm[s] / K (codes, scales and the row's global)
-__global__ void pf_gather_q_kernel(const int* __restrict__ perm, const int* __restrict__ cnt_total, int K, int Hd, const uint8_t* __restrict__ xq,
-                                   const uint8_t* __restrict__ xs, const float* __restrict__ xg, uint8_t* __restrict__ q, uint8_t* __restrict__ sc,
-                                   float* __restrict__ g) {
-  const int n_slots = *cnt_total;
-  const int per_row = Hd / 32 + Hd / 256;                                    // 16-byte pieces of a row: codes then scales
-  for (int slot = blockIdx.x; slot < n_slots; slot += gridDim.x) {
-    const size_t row = (size_t)(perm[slot] / K);
-    for (int i = threadIdx.x; i < per_row; i += blockDim.x) {
-      if (i < Hd / 32) reinterpret_cast<uint4*>(q + (size_t)slot * (Hd / 2))[i] = __ldg(reinterpret_cast<const uint4*>(xq + row * (Hd / 2)) + i);
-      else reinterpret_cast<uint4*>(sc + (size_t)slot * (Hd / 16))[i - Hd / 32] = __ldg(reinterpret_cast<const uint4*>(xs + row * (Hd / 16)) + (i - Hd / 32));
-    }
-    if (threadIdx.x == 0) g[slot] = xg[row];
+  __syncthreads();
+  for (int p = p0 + t; p < p1; p += PLAN_THREADS) {
+    const int e = expert_of(p);
+    int pos = -1;
+    if (e >= 0) { pos = atomicAdd(&cur[e], 1); a.perm[pos] = p; }
+    a.pos_of[p] = pos;
   }
 }
 
@@ -462,42 +479,68 @@ __global__ void pf_tmaps_kernel(const __grid_constant__ PfMapSet tpl, const uint
   asm volatile("fence.proxy.tensormap::generic.release.gpu;" ::: "memory");
 }
 
-// ---- reduce --------------------------------------------------------------------------------------------------------------------------
+// ---- the sum over a row's pairs -----------------------------------------------------------------------------------------------------
 // out[row] = Σ_k part[row·K + k]·w[row, k], fp32 in k order, overwritten — or the shared-expert combine on top of it:
-// out = bf16(bf16(Σ) + bf16(bf16(sigmoid(bf16 gate logit))·shared)); lg == NULL: no gate
-__global__ void pf_reduce_kernel(const __nv_bfloat16* __restrict__ part, const int32_t* __restrict__ ids, const float* __restrict__ w, int M, int K, int E,
-                                 const uint8_t* const* __restrict__ tab, int H, float* __restrict__ out, const __nv_bfloat16* __restrict__ shared,
-                                 const float* __restrict__ lg, int ld, int col, __nv_bfloat16* __restrict__ cout) {
-  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;      // 8 columns of one row per thread (H is a multiple of 256)
-  if (i >= (size_t)M * H) return;
-  const int m = (int)(i / H), n = (int)(i % H);
-  float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int k = 0; k < K; ++k) {
-    const int p = m * K + k;
-    int e;
-    if (!pf_live(ids, p, E, tab, &e)) continue;
-    const uint4 v = __ldcs(reinterpret_cast<const uint4*>(part + (size_t)p * H + n));
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-    const float wv = w[p];
+// out = bf16(bf16(Σ) + bf16(bf16(sigmoid(bf16 gate logit))·shared)); lg == NULL: no gate.  A CTA takes whole rows: the row's weights
+// and which of its pairs contributed (pos_of ≥ 0) are looked up once per row, then every thread streams 8 columns at a time.
+constexpr int SUM_ROWS = 4;              // rows a CTA of pf_sum_pairs_kernel works on at once
+__global__ void __launch_bounds__(256) pf_sum_pairs_kernel(const __nv_bfloat16* __restrict__ part, const int* __restrict__ pos_of, const float* __restrict__ w, int M,
+                                                           int K, int H, float* __restrict__ out, const __nv_bfloat16* __restrict__ shared,
+                                                           const float* __restrict__ lg, int ld, int col, __nv_bfloat16* __restrict__ cout) {
+  __shared__ float wk[SUM_ROWS][32];
+  __shared__ uint32_t live[SUM_ROWS];
+  __shared__ float gate_s[SUM_ROWS];
+  const int chunks = H / 8;                                                   // 8 columns (16 bytes of bf16) per step of a thread
+  for (int m0 = blockIdx.x * SUM_ROWS; m0 < M; m0 += gridDim.x * SUM_ROWS) {
+    const int nr = min(SUM_ROWS, M - m0);
+    if ((int)threadIdx.x < nr * 32) {
+      const int r = threadIdx.x >> 5, k = threadIdx.x & 31;
+      const bool on = k < K && pos_of[(size_t)(m0 + r) * K + k] >= 0;
+      wk[r][k] = k < K ? w[(size_t)(m0 + r) * K + k] : 0.f;
+      const uint32_t mask = __ballot_sync(0xffffffffu, on);
+      if (k == 0) {
+        live[r] = mask;
+        gate_s[r] = cout && lg ? bf16r(1.f / (1.f + expf(-bf16r(lg[(size_t)(m0 + r) * ld + col])))) : 1.f;
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nr * chunks; i += 256) {
+      const int r = i / chunks, n = (i - r * chunks) * 8, m = m0 + r;
+      const uint32_t lv = live[r];
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int k0 = 0; k0 < K; k0 += 4) {                                     // four pairs' pieces are fetched together, then added in k order
+        uint4 v[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { a[2 * j] += __uint_as_float(u[j] << 16) * wv; a[2 * j + 1] += __uint_as_float(u[j] & 0xffff0000u) * wv; }
-  }
-  if (!cout) {
-    *reinterpret_cast<float4*>(out + i) = make_float4(a[0], a[1], a[2], a[3]);
-    *reinterpret_cast<float4*>(out + i + 4) = make_float4(a[4], a[5], a[6], a[7]);
-    return;
-  }
-  float g = 1.f;
-  if (lg) g = bf16r(1.f / (1.f + expf(-bf16r(lg[(size_t)m * ld + col]))));
-  const uint4 sv = *reinterpret_cast<const uint4*>(shared + i);
-  const uint32_t su[4] = {sv.x, sv.y, sv.z, sv.w};
-  float r[8];
+        for (int j = 0; j < 4; ++j)
+          if (k0 + j < K && ((lv >> (k0 + j)) & 1u)) v[j] = __ldcs(reinterpret_cast<const uint4*>(part + ((size_t)m * K + k0 + j) * H + n));
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    r[2 * j] = bf16r(a[2 * j]) + bf16r(g * __uint_as_float(su[j] << 16));
-    r[2 * j + 1] = bf16r(a[2 * j + 1]) + bf16r(g * __uint_as_float(su[j] & 0xffff0000u));
+        for (int j = 0; j < 4; ++j) {
+          if (k0 + j >= K || !((lv >> (k0 + j)) & 1u)) continue;
+          const uint32_t u[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+          const float wv = wk[r][k0 + j];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) { acc[2 * c] += __uint_as_float(u[c] << 16) * wv; acc[2 * c + 1] += __uint_as_float(u[c] & 0xffff0000u) * wv; }
+        }
+      }
+      const size_t o = (size_t)m * H + n;
+      if (!cout) {
+        *reinterpret_cast<float4*>(out + o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        *reinterpret_cast<float4*>(out + o + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      } else {
+        const float gate = gate_s[r];
+        const uint4 sv = *reinterpret_cast<const uint4*>(shared + o);
+        const uint32_t su[4] = {sv.x, sv.y, sv.z, sv.w};
+        float rr[8];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          rr[2 * c] = bf16r(acc[2 * c]) + bf16r(gate * __uint_as_float(su[c] << 16));
+          rr[2 * c + 1] = bf16r(acc[2 * c + 1]) + bf16r(gate * __uint_as_float(su[c] & 0xffff0000u));
+        }
+        *reinterpret_cast<uint4*>(cout + o) = pf_pack8(rr);
+      }
+    }
+    __syncthreads();
   }
-  *reinterpret_cast<uint4*>(cout + i) = pf_pack8(r);
 }
 
 }  // namespace hb
@@ -506,19 +549,18 @@ using namespace hb;
 
 namespace {
 struct PfWs {
-  int* cnt; int* cursor; int* n_tiles; PfTile* tiles; int* perm; CUtensorMap* tmB; __nv_bfloat16* y; __nv_bfloat16* part;
-  uint8_t *xq, *xs, *yq, *ys, *xq_s, *xs_s; float *xg, *yg, *xg_s;
+  int* hist; int* n_slots; int* n_tiles; TileRef* tiles; int* perm; int* pos_of; CUtensorMap* tmB; __nv_bfloat16* y; __nv_bfloat16* part;
+  uint8_t *yq, *ys, *xq_s, *xs_s; float *yg, *xg_s;
 };
 size_t pf_carve(void* ws, int S, int K, int E, int H, int I, PfWs* w) {
   size_t off = 0;
   auto take = [&](size_t b) { void* r = ws ? static_cast<char*>(ws) + off : nullptr; off += hb_align256(b); return r; };
   const size_t P = (size_t)S * K;
   PfWs t;
-  t.cnt = (int*)take((size_t)(E + 1) * 4); t.cursor = (int*)take((size_t)E * 4); t.n_tiles = (int*)take(4);
-  t.tiles = (PfTile*)take((P / PF_BM + E) * sizeof(PfTile)); t.perm = (int*)take(P * 4);
+  t.hist = (int*)take((size_t)PLAN_MAX_CTAS * E * 4); t.n_slots = (int*)take(4); t.n_tiles = (int*)take(4);
+  t.tiles = (TileRef*)take((P / PF_BM + E) * sizeof(TileRef)); t.perm = (int*)take(P * 4); t.pos_of = (int*)take(P * 4);
   t.tmB = (CUtensorMap*)take((size_t)E * 6 * sizeof(CUtensorMap));
   t.y = (__nv_bfloat16*)take(P * I * 2); t.part = (__nv_bfloat16*)take(P * H * 2);
-  t.xq = (uint8_t*)take((size_t)S * H / 2); t.xs = (uint8_t*)take((size_t)S * H / 16); t.xg = (float*)take((size_t)S * 4);
   t.xq_s = (uint8_t*)take(P * H / 2); t.xs_s = (uint8_t*)take(P * H / 16); t.xg_s = (float*)take(P * 4);
   t.yq = (uint8_t*)take(P * I / 2); t.ys = (uint8_t*)take(P * I / 16); t.yg = (float*)take(P * 4);
   if (w) *w = t;
@@ -567,8 +609,8 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
   if (M <= 0) return HB_OK;
   HB_REQUIRE(ctx, rec_tab && ids && w && x_bf16 && (out || cmb), HB_ERR_INVALID, "moe_prefill: NULL argument");
   HB_REQUIRE(ctx, !cmb || (cmb->shared && cmb->out), HB_ERR_INVALID, "moe_prefill: combine without shared rows or output");
-  HB_REQUIRE(ctx, hb_moe_prefill_supported(H, I) && S >= 1 && K >= 1 && E >= 1 && E <= 1024 && li >= 0, HB_ERR_UNSUPPORTED,
-             "moe_prefill: H=%d I=%d (multiples of 256) E=%d (≤ 1024) K=%d S=%d", H, I, E, K, S);
+  HB_REQUIRE(ctx, hb_moe_prefill_supported(H, I) && S >= 1 && K >= 1 && K <= 32 && E >= 1 && E <= 1024 && li >= 0, HB_ERR_UNSUPPORTED,
+             "moe_prefill: H=%d I=%d (multiples of 256) E=%d (≤ 1024) K=%d (≤ 32) S=%d", H, I, E, K, S);
   HB_REQUIRE(ctx, (long long)S * K < (1ll << 30), HB_ERR_UNSUPPORTED, "moe_prefill: S·K too large");
   HB_REQUIRE(ctx, ws && hb_aligned(ws, 256), HB_ERR_WORKSPACE, "moe_prefill: ws NULL or not 256-byte aligned");
   HB_REQUIRE(ctx, hb_aligned(x_bf16, 16) && hb_aligned(out, 16) && (!cmb || (hb_aligned(cmb->shared, 16) && hb_aligned(cmb->out, 16))), HB_ERR_INVALID,
@@ -612,13 +654,13 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
   for (int s0 = 0; s0 < M; s0 += S) {
     const int n = M - s0 < S ? M - s0 : S, P = n * K;
     const int32_t* sid = ids + (size_t)s0 * K;
-    HB_CUDA(ctx, cudaMemsetAsync(W.cnt, 0, (size_t)E * 4, st));
-    if ((r = hb_launch(ctx, "pf_count", false, pf_count_kernel, dim3((P + 255) / 256), dim3(256), 0, st, sid, P, E, lt, W.cnt))) return r;
-    if ((r = hb_launch(ctx, "pf_scan", false, pf_scan_kernel, dim3(1), dim3(1024), 0, st, (const int*)W.cnt, E, W.cursor, W.tiles, W.n_tiles, W.cnt + E))) return r;
-    if ((r = hb_launch(ctx, "pf_fill", false, pf_fill_kernel, dim3((P + 255) / 256), dim3(256), 0, st, sid, P, E, lt, W.cursor, W.perm))) return r;
-    if ((r = hbk_a4_quant(ctx, x + (size_t)s0 * H, H, n, H, W.xq, W.xs, W.xg, st))) return r;
-    if ((r = hb_launch(ctx, "pf_gather_q", false, pf_gather_q_kernel, dim3(ctx->sm_count * 8), dim3(256), 0, st, (const int*)W.perm, (const int*)(W.cnt + E), K, H,
-                       (const uint8_t*)W.xq, (const uint8_t*)W.xs, (const float*)W.xg, W.xq_s, W.xs_s, W.xg_s))) return r;
+    PlanArgs pl{sid, P, E, lt, W.hist, W.perm, W.pos_of, W.tiles, W.n_tiles, W.n_slots, reinterpret_cast<unsigned int*>(ctx->dev_err) + kErrPlanMeet, ctx->dev_err};
+    int plan_ctas = (P + 2047) / 2048;
+    if (plan_ctas > PLAN_MAX_CTAS) plan_ctas = PLAN_MAX_CTAS;
+    if (plan_ctas > ctx->sm_count) plan_ctas = ctx->sm_count;                   // the CTAs meet inside the kernel: all must be resident
+    if ((r = hb_launch(ctx, "pf_plan", false, pf_plan_kernel, dim3(plan_ctas), dim3(PLAN_THREADS), 0, st, pl))) return r;
+    // x quantised once per row and written straight into its pairs' slots
+    if ((r = hbk_quant_rows_scatter(ctx, x + (size_t)s0 * H, H, n, H, W.pos_of, K, W.xq_s, W.xs_s, W.xg_s, st))) return r;
     PfGemmArgs a{};
     a.tiles = W.tiles; a.n_tiles = W.n_tiles; a.perm = W.perm; a.tab = lt; a.L = L; a.tmB = W.tmB; a.limit = limit; a.err = ctx->dev_err;
     a.as = W.xs_s; a.ag = W.xg_s; a.Kd = H; a.N = I; a.out = W.y; a.ldo = I;
@@ -626,10 +668,9 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
     if ((r = hbk_a4_quant(ctx, W.y, I, P, I, W.yq, W.ys, W.yg, st))) return r;
     a.as = W.ys; a.ag = W.yg; a.Kd = I; a.N = H; a.out = W.part; a.ldo = H;
     if ((r = pf_launch<PF_DOWN>(ctx, "pf_gemm_down", a, tm_y, tm_y, st))) return r;
-    const size_t pairs2 = (size_t)n * H / 8;
     const __nv_bfloat16* sh = cmb ? reinterpret_cast<const __nv_bfloat16*>(cmb->shared) + (size_t)s0 * H : nullptr;
-    if ((r = hb_launch(ctx, "pf_reduce", false, pf_reduce_kernel, dim3((unsigned)((pairs2 + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16*)W.part, sid,
-                       w + (size_t)s0 * K, n, K, E, lt, H, cmb ? (float*)nullptr : out + (size_t)s0 * H, sh,
+    if ((r = hb_launch(ctx, "pf_sum_pairs", false, pf_sum_pairs_kernel, dim3((unsigned)((n + SUM_ROWS - 1) / SUM_ROWS < ctx->sm_count * 8 ? (n + SUM_ROWS - 1) / SUM_ROWS : ctx->sm_count * 8)), dim3(256), 0, st,
+                       (const __nv_bfloat16*)W.part, (const int*)W.pos_of, w + (size_t)s0 * K, n, K, H, cmb ? (float*)nullptr : out + (size_t)s0 * H, sh,
                        cmb && cmb->lg ? cmb->lg + (size_t)s0 * cmb->ld : (const float*)nullptr, cmb ? cmb->ld : 0, cmb ? cmb->col : 0,
                        cmb ? reinterpret_cast<__nv_bfloat16*>(cmb->out) + (size_t)s0 * H : (__nv_bfloat16*)nullptr)))
       return r;

@@ -87,83 +87,135 @@ __global__ void __launch_bounds__(256) nvfp4_gemv_kernel(const uint8_t* __restri
   }
 }
 
-// ---- fp32 → NVFP4, the device rule of the reference's requant kernels (no per-block scale search)
-__global__ void amax_f32_kernel(const float* __restrict__ w, size_t n, float* __restrict__ amax) {
+// ---- fp32 → NVFP4 (the device rule of the reference's requant kernels: one global scale from the tensor's largest magnitude, block
+// scale = e4m3(block amax · gs / 6), code = e2m1(v · gs / scale); no per-block scale search).  Four lanes share a block of 16: a lane
+// loads ONE float4 (a warp reads 512 contiguous bytes), the block's amax is two shuffles away, the four lanes work out the same scale
+// and each turns its own four values into 16 bits of codes (a warp writes 64 contiguous bytes).
+__global__ void __launch_bounds__(256) tensor_absmax_kernel(const float4* __restrict__ w4, size_t n4, float* __restrict__ amax) {
+  __shared__ float part[8];
   float m = 0.f;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) m = fmaxf(m, fabsf(w[i]));
-  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<int*>(amax), __float_as_int(m));   // non-negative floats order like ints
-}
-__global__ void nvfp4_quant_kernel(const float* __restrict__ w, size_t n_blocks16, const float* __restrict__ amax, uint8_t* __restrict__ q,
-                                   uint8_t* __restrict__ s, float* __restrict__ g_mul) {
-  const float am = *amax;
-  const float gs = am > 0.f ? __fdiv_rn(448.f * 6.f, am) : 1.f;
-  if (blockIdx.x == 0 && threadIdx.x == 0) *g_mul = am > 0.f ? __fdiv_rn(am, 448.f * 6.f) : 1.f;
-  const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (b >= n_blocks16) return;
-  float f[16], m = 0.f;
-  const float4* src = reinterpret_cast<const float4*>(w + b * 16);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float4 v = src[j];
-    f[4 * j] = v.x; f[4 * j + 1] = v.y; f[4 * j + 2] = v.z; f[4 * j + 3] = v.w;
-    m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n4; i += (size_t)gridDim.x * 256) {
+    const float4 v = __ldg(w4 + i);
+    m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
   }
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 8) {
+    m = part[threadIdx.x];
+    for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffu, m, o));
+    if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(m));   // one atomic per block; magnitudes order like their bits
+  }
+}
+__global__ void __launch_bounds__(256) nvfp4_encode_kernel(const float4* __restrict__ w4, size_t n4, const float* __restrict__ amax, uint16_t* __restrict__ q16,
+                                                           uint8_t* __restrict__ s, float* __restrict__ g_mul) {
+  const float am = *amax;
+  const bool live = am > 0.f;
+  const float gs = live ? __fdiv_rn(448.f * 6.f, am) : 1.f;
+  if (blockIdx.x == 0 && threadIdx.x == 0) *g_mul = live ? __fdiv_rn(am, 448.f * 6.f) : 1.f;
+  const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;                   // one float4 per thread; n4 is a multiple of 4, whole quads stay in range together
+  if (i >= n4) return;
+  const float4 v = __ldg(w4 + i);
+  float m = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+  const unsigned quad = 0xfu << (threadIdx.x & 28);
+  m = fmaxf(m, __shfl_xor_sync(quad, m, 1));
+  m = fmaxf(m, __shfl_xor_sync(quad, m, 2));
   const __nv_fp8_storage_t sc = __nv_cvt_float_to_fp8(__fdiv_rn(__fmul_rn(m, gs), 6.f), __NV_SATFINITE, __NV_E4M3);
   const float sd = e4m3_to_f32(sc);
-  s[b] = (uint8_t)sc;
-  uint32_t lo = 0, hi = 0;
+  if ((threadIdx.x & 3) == 0) s[i >> 2] = (uint8_t)sc;
+  const float f[4] = {v.x, v.y, v.z, v.w};
+  uint32_t c = 0;
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    const uint32_t v = sd > 0.f ? ((uint32_t)__nv_cvt_float_to_fp4(__fdiv_rn(__fmul_rn(f[j], gs), sd), __NV_E2M1, cudaRoundNearest) & 0xFu) : 0u;
-    if (j < 8) lo |= v << (4 * j); else hi |= v << (4 * (j - 8));
-  }
-  reinterpret_cast<uint2*>(q)[b] = make_uint2(lo, hi);
+  for (int j = 0; j < 4; ++j)
+    if (sd > 0.f) c |= ((uint32_t)__nv_cvt_float_to_fp4(__fdiv_rn(__fmul_rn(f[j], gs), sd), __NV_E2M1, cudaRoundNearest) & 0xFu) << (4 * j);
+  q16[i] = (uint16_t)c;
 }
 
-// ---- per-row dynamic NVFP4 activation quantisation: one warp per row
-__global__ void a4_quant_kernel(const __nv_bfloat16* __restrict__ x, int ld, int n, int K, uint8_t* __restrict__ q, uint8_t* __restrict__ s,
-                                float* __restrict__ g) {
-  const int row = (int)(((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
-  if (row >= n) return;
-  const __nv_bfloat16* xr = x + (size_t)row * ld;
-  const int nb = K / 16;
-  const bool vec = (reinterpret_cast<uintptr_t>(xr) & 15) == 0;              // 16-byte loads when the row allows them
-  auto load16 = [&](int b, float* v) {
-    if (vec) {
-      const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(xr + b * 16)), u1 = __ldg(reinterpret_cast<const uint4*>(xr + b * 16) + 1);
-      const uint32_t w[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+// ---- per-row dynamic NVFP4 quantisation of bf16 rows (the rule of the reference's activation quantiser: gx = amax / (6·448), block
+// scale = e4m3((block amax / 6) / gx), code = e2m1(v · (1/gx) / scale)), written to any number of destination rows at once.
+// A CTA takes one row at a time: the row is staged in shared memory once, the quantised row (codes, scales) is built there, and then
+// copied to each place it is wanted — with a destination list this is quantise + gather-into-expert-order in one pass (a row is
+// quantised once however many experts it goes to, and the quantised row never makes a round trip through global memory).
+//   dest == nullptr: row r goes to slot r.  Else: row r goes to slots dest[r·nd + j], j < nd, negative entries skipped.
+constexpr int QS_THREADS = 256;
+// TG threads work on a row together (256 for long rows, 64 for short ones: 256 / TG rows are then in progress in a CTA, each group
+// with its own staging buffers and its own named barrier).
+template <int TG>
+__global__ void __launch_bounds__(QS_THREADS) quant_rows_scatter_kernel(const __nv_bfloat16* __restrict__ x, int ld, int n, int Kd, const int* __restrict__ dest, int nd,
+                                                                        uint8_t* __restrict__ q, uint8_t* __restrict__ s, float* __restrict__ g) {
+  constexpr int NG = QS_THREADS / TG;
+  extern __shared__ __align__(16) uint8_t qs_sm[];
+  __shared__ float red[NG][TG / 32];
+  __shared__ int dst_s[NG][32];
+  const int grp = threadIdx.x / TG, t = threadIdx.x % TG, lane = t & 31, wp = t >> 5, bar = 1 + grp;
+  const size_t stage = (size_t)Kd * 2 + Kd / 2 + (Kd / 16 + 15) / 16 * 16;
+  uint32_t* row32 = reinterpret_cast<uint32_t*>(qs_sm + grp * stage);         // Kd bf16 values
+  uint8_t* codes = reinterpret_cast<uint8_t*>(row32) + (size_t)Kd * 2;       // Kd / 2 bytes
+  uint8_t* scl = codes + Kd / 2;                                             // Kd / 16 bytes
+  const int nb = Kd / 16;
+  for (int r = blockIdx.x * NG + grp; r < n; r += gridDim.x * NG) {
+    const __nv_bfloat16* xr = x + (size_t)r * ld;
+    float a = 0.f;
+    if ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) {
+      for (int i = t; i < Kd / 8; i += TG) {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(xr) + i);
+        reinterpret_cast<uint4*>(row32)[i] = u;
+        const uint32_t wv[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { v[2 * j] = __uint_as_float(w[j] << 16); v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u); }
+        for (int j = 0; j < 4; ++j) a = fmaxf(a, fmaxf(fabsf(__uint_as_float(wv[j] << 16)), fabsf(__uint_as_float(wv[j] & 0xffff0000u))));
+      }
     } else {
-#pragma unroll
-      for (int j = 0; j < 16; ++j) v[j] = __bfloat162float(xr[b * 16 + j]);
+      for (int i = t; i < Kd; i += TG) {
+        const __nv_bfloat16 v = xr[i];
+        reinterpret_cast<__nv_bfloat16*>(row32)[i] = v;
+        a = fmaxf(a, fabsf(__bfloat162float(v)));
+      }
     }
-  };
-  float a = 0.f;
-  for (int b = lane; b < nb; b += 32) {
-    float v[16];
-    load16(b, v);
+    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    if (lane == 0) red[grp][wp] = a;
+    if (dest && t < nd) dst_s[grp][t] = dest[(size_t)r * nd + t];
+    named_bar_sync(bar, TG);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) a = fmaxf(a, fabsf(v[j]));
-  }
-  for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-  const float gx = a > 0.f ? __fdiv_rn(a, 6.f * 448.f) : 1.f, inv = __fdiv_rn(1.f, gx);
-  if (lane == 0) g[row] = gx;
-  for (int b = lane; b < nb; b += 32) {
-    float v[16], ab = 0.f;
-    load16(b, v);
+    for (int i = 0; i < TG / 32; ++i) a = fmaxf(a, red[grp][i]);
+    const float gx = a > 0.f ? __fdiv_rn(a, 6.f * 448.f) : 1.f, inv = __fdiv_rn(1.f, gx);
+    for (int b = t; b < nb; b += TG) {
+      float v[16], ab = 0.f;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) ab = fmaxf(ab, fabsf(v[j]));
-    const __nv_fp8_storage_t se = __nv_cvt_float_to_fp8(__fmul_rn(__fdiv_rn(ab, 6.f), inv), __NV_SATFINITE, __NV_E4M3);
-    const float sv = e4m3_to_f32(se);
-    const float f = sv > 0.f ? __fdiv_rn(inv, sv) : 0.f;
-    uint32_t o[2] = {0u, 0u};
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t u = row32[b * 8 + j];
+        v[2 * j] = __uint_as_float(u << 16); v[2 * j + 1] = __uint_as_float(u & 0xffff0000u);
+        ab = fmaxf(ab, fmaxf(fabsf(v[2 * j]), fabsf(v[2 * j + 1])));
+      }
+      const __nv_fp8_storage_t se = __nv_cvt_float_to_fp8(__fmul_rn(__fdiv_rn(ab, 6.f), inv), __NV_SATFINITE, __NV_E4M3);
+      const float sv = e4m3_to_f32(se), f = sv > 0.f ? __fdiv_rn(inv, sv) : 0.f;
+      uint32_t lo = 0u, hi = 0u;
 #pragma unroll
-    for (int j = 0; j < 16; ++j)
-      o[j / 8] |= ((uint32_t)__nv_cvt_float_to_fp4(__fmul_rn(v[j], f), __NV_E2M1, cudaRoundNearest) & 0xFu) << (4 * (j % 8));
-    *reinterpret_cast<uint2*>(q + (size_t)row * (K / 2) + (size_t)b * 8) = make_uint2(o[0], o[1]);
-    s[(size_t)row * nb + b] = (uint8_t)se;
+      for (int j = 0; j < 8; ++j) {
+        lo |= ((uint32_t)__nv_cvt_float_to_fp4(__fmul_rn(v[j], f), __NV_E2M1, cudaRoundNearest) & 0xFu) << (4 * j);
+        hi |= ((uint32_t)__nv_cvt_float_to_fp4(__fmul_rn(v[8 + j], f), __NV_E2M1, cudaRoundNearest) & 0xFu) << (4 * j);
+      }
+      reinterpret_cast<uint2*>(codes)[b] = make_uint2(lo, hi);
+      scl[b] = (uint8_t)se;
+    }
+    named_bar_sync(bar, TG);
+    // the quantised row leaves for its destinations: 16-byte pieces when the row length allows (Kd a multiple of 256), else bytes
+    const int ndest = dest ? nd : 1;
+    for (int j = 0; j < ndest; ++j) {
+      const int slot = dest ? dst_s[grp][j] : r;
+      if (slot < 0) continue;
+      uint8_t* qd = q + (size_t)slot * (Kd / 2);
+      uint8_t* sd = s + (size_t)slot * nb;
+      if (Kd % 256 == 0 && ((reinterpret_cast<uintptr_t>(qd) | reinterpret_cast<uintptr_t>(sd)) & 15) == 0) {
+        for (int i = t; i < Kd / 32 + Kd / 256; i += TG) {
+          if (i < Kd / 32) reinterpret_cast<uint4*>(qd)[i] = reinterpret_cast<const uint4*>(codes)[i];
+          else reinterpret_cast<uint4*>(sd)[i - Kd / 32] = reinterpret_cast<const uint4*>(scl)[i - Kd / 32];
+        }
+      } else {
+        for (int i = t; i < nb; i += TG) { reinterpret_cast<uint2*>(qd)[i] = reinterpret_cast<const uint2*>(codes)[i]; sd[i] = scl[i]; }
+      }
+      if (t == 0) g[slot] = gx;
+    }
+    named_bar_sync(bar, TG);                                                  // the staging buffers are reused by the group's next row
   }
 }
 
@@ -189,19 +241,37 @@ int hbk_nvfp4_gemv(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int
 }
 
 int hbk_nvfp4_quantize(hb_ctx* ctx, const float* w, int N, int K, uint8_t* q, uint8_t* s, float* g_mul, float* amax, cudaStream_t st) {
-  const size_t n = (size_t)N * K, nb = n / 16;
+  const size_t n4 = (size_t)N * K / 4;                                       // K is a multiple of 16
   cudaError_t e = cudaMemsetAsync(amax, 0, 4, st);
   if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "memset amax: %s", cudaGetErrorString(e));
-  size_t blocks = (n / 4 + 255) / 256, cap = (size_t)ctx->sm_count * 8;
-  if (blocks > cap) blocks = cap;
-  if (blocks < 1) blocks = 1;
-  int r = hb_launch(ctx, "amax_f32", false, amax_f32_kernel, dim3((unsigned)blocks), dim3(256), 0, st, w, n, amax);
+  size_t blocks = (n4 + 255) / 256, cap = (size_t)ctx->sm_count * 8;
+  int r = hb_launch(ctx, "tensor_absmax", false, tensor_absmax_kernel, dim3((unsigned)(blocks < cap ? blocks : cap)), dim3(256), 0, st,
+                    reinterpret_cast<const float4*>(w), n4, amax);
   if (r) return r;
-  return hb_launch(ctx, "nvfp4_quant", false, nvfp4_quant_kernel, dim3((unsigned)((nb + 255) / 256)), dim3(256), 0, st, w, nb, (const float*)amax, q, s,
-                   g_mul);
+  return hb_launch(ctx, "nvfp4_encode", false, nvfp4_encode_kernel, dim3((unsigned)blocks), dim3(256), 0, st, reinterpret_cast<const float4*>(w), n4,
+                   (const float*)amax, reinterpret_cast<uint16_t*>(q), s, g_mul);
+}
+
+int hbk_quant_rows_scatter(hb_ctx* ctx, const void* x, int ld, int n, int K, const int* dest, int nd, uint8_t* q, uint8_t* s, float* g, cudaStream_t st) {
+  HB_REQUIRE(ctx, nd >= 1 && nd <= 32, HB_ERR_UNSUPPORTED, "quant_rows: %d destinations per row (at most 32)", nd);
+  const bool small = K <= 4096;                                              // short rows: four at a time per CTA
+  const size_t stage = (size_t)K * 2 + K / 2 + (K / 16 + 15) / 16 * 16, smem = stage * (small ? 4 : 1);
+  HB_REQUIRE(ctx, smem <= 96 * 1024, HB_ERR_UNSUPPORTED, "quant_rows: rows of %d values do not fit the staging buffer", K);
+  const int per = small ? 4 : 1;
+  int grid = ctx->sm_count * 4;
+  if (grid > (n + per - 1) / per) grid = (n + per - 1) / per;
+  const char* name = dest ? "quant_rows_scatter" : "a4_quant";
+  const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  if (small) return hb_launch(ctx, name, false, quant_rows_scatter_kernel<64>, dim3(grid), dim3(QS_THREADS), smem, st, xb, ld, n, K, dest, nd, q, s, g);
+  return hb_launch(ctx, name, false, quant_rows_scatter_kernel<256>, dim3(grid), dim3(QS_THREADS), smem, st, xb, ld, n, K, dest, nd, q, s, g);
 }
 
 int hbk_a4_quant(hb_ctx* ctx, const void* x, int ld, int n, int K, uint8_t* q, uint8_t* s, float* g, cudaStream_t st) {
-  return hb_launch(ctx, "a4_quant", false, a4_quant_kernel, dim3((n + 7) / 8), dim3(256), 0, st, reinterpret_cast<const __nv_bfloat16*>(x), ld, n, K,
-                   q, s, g);
+  return hbk_quant_rows_scatter(ctx, x, ld, n, K, nullptr, 1, q, s, g, st);
+}
+
+int hbk_nvfp4_setup(hb_ctx* ctx) {
+  HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(quant_rows_scatter_kernel<64>), cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+  HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(quant_rows_scatter_kernel<256>), cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+  return HB_OK;
 }

@@ -95,11 +95,12 @@ def test_composed_expert_pass_matches_oracle(E, oracle):
     for r, wt in zip(rows, w):
         want[r] = oracle.expert_forward(rec, H, I, x[r], float(wt), 0.0, 1)
     # The composed pass rounds the weights to bf16 (the oracle multiplies exact e2m1·e4m3 products and applies the global scale after
-    # the sum) and rounds gate, up and y to bf16 from slightly different sums, so a result can land a bf16 value or two away: two
-    # bf16 steps of the element (2^-6 relative) on top of 1e-2 × row RMS.
+    # the sum) and rounds gate, up and y to bf16 from slightly different sums: a y value that lands on the neighbouring bf16 value
+    # is spread over the whole output row by the down product, and a result can itself land a bf16 value or two away — two bf16
+    # steps of the element (2^-6 relative) on top of 3e-2 × row RMS, and the rows must point the same way.
     g64, w64 = got[rows].astype(np.float64), want[rows].astype(np.float64)
     rms = np.sqrt((w64 ** 2).mean(axis=1, keepdims=True))
-    assert np.all(np.abs(g64 - w64) <= 2.0 ** -6 * np.abs(w64) + 1e-2 * rms), float((np.abs(g64 - w64) / rms).max())
+    assert np.all(np.abs(g64 - w64) <= 2.0 ** -6 * np.abs(w64) + 3e-2 * rms), float((np.abs(g64 - w64) / rms).max())
     cos = (g64 * w64).sum(1) / (np.linalg.norm(g64, axis=1) * np.linalg.norm(w64, axis=1))
     assert cos.min() > 0.9999
     assert not got[[0, 2, 3]].any()
