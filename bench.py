@@ -475,6 +475,30 @@ def run_ours(args):
                       "records_per_layer": head["records_per_layer"]},
             "per_batch": [results[b] for b in sorted(results)], "roofline": roofline, "e2e": e2e, "gpu_launches": head["launches_per_step"] * args.steps,
             "clocks": clocks, "kernels": prof, "setup_s": setup_s, "parity": parity}
+    if not args.batch and not args.layers and not args.no_extras:
+        # the other workloads the path is judged on, each a bounded measurement with its own sampled-row check: the GLM-shaped decode
+        # layer (strong scaling, skewed routing) and the DeepSeek-shaped prefill layer at every N, the dense low-bit GEMVs at N = 1
+        del layers, tab
+        torch.cuda.empty_cache()
+        from oracle import oracle as O
+        per_config = {}
+        trace("extras: glm")
+        per_config["glm_b8_zipf"] = glm_measure(args, torch, dist, E, O, ctx, dev, rank, world)
+        trace("extras: prefill")
+        pa = argparse.Namespace(**vars(args)); pa.steps = 5; pa.warmup = 3
+        pl, prc = prefill_measure(pa, torch, dist, E, O, ctx, dev, rank, world, with_dense=(world == 1))
+        per_config["prefill_t8192"] = {k: pl.get(k) for k in ("value", "unit", "ms_per_layer", "layer_TFLOPs", "scaling", "config", "roofline", "roofline_hbm", "exchange",
+                                                              "parity", "w4a4_vs_w4a16", "dense_gemm_a4", "kernels")}
+        line["per_config"] = per_config
+        line["prefill"] = {"tokens_per_s": pl["value"], "ms_per_layer": pl["ms_per_layer"], "frac_of_measured_fp4_peak": pl["roofline"]["frac"],
+                           "peak_TFLOPs": pl["roofline"]["peak"], "dense_gemm_a4": pl.get("dense_gemm_a4"), "parity_ok": pl["parity"]["ok"]}
+        if world == 1:
+            trace("extras: dense")
+            da = argparse.Namespace(**vars(args)); da.steps = 20
+            dl = dense_measure(da, torch, E, ctx, dev)
+            line["dense"] = {"per_case": dl["per_case"], "roofline": dl["roofline"]}
+        if not (per_config["glm_b8_zipf"].get("parity", {"ok": True})["ok"] and pl["parity"]["ok"]):
+            parity["ok"] = False
     if world == 1 and not args.no_cpu:
         try:
             _, _, _, _, info = cpu_reference(head_B, 0, 1, args.cpu_budget)
@@ -514,10 +538,127 @@ def _timed(torch, fn, n):
     return e0.elapsed_time(e1) / n
 
 
+def glm_measure(args, torch, dist, E, O, ctx, dev, rank, world):
+    """The GLM-shaped decode workload, strong scaling: hidden 4096, 160 routed experts top-8 + 1 shared, intermediate 1536, 8 tokens per
+    step IN ALL (8 / N per rank), sigmoid router over N(0,1) logits plus a per-expert Zipf(1.1) log-weight bias (hot experts), clamp
+    10.  Experts are sharded over the ranks; 6 layers' records (larger than L2) are cycled.  Returns a dict for the bench line."""
+    H, I, Ex, K, L, Btot, scale, limit = 4096, 1536, 160, 8, 6, 8, 2.5, 10.0
+    if Btot % world:
+        return {"skipped": f"{Btot} rows do not split over {world} ranks"}
+    B = Btot // world
+    e_lo, e_hi = rank * Ex // world, (rank + 1) * Ex // world
+    experts = list(range(e_lo, e_hi))
+    layers = Layers(E, H, I, L, experts, CFG["sigma"], CFG["seed"] + 3, dev)
+    n_loc = len(experts)
+    tab_host = np.zeros((L, Ex), np.int64)
+    for li in range(L):
+        for j, gid in enumerate(experts):
+            tab_host[li, gid] = layers.ptr(li, j)
+    tab = torch.from_numpy(tab_host.reshape(-1)).to(dev)
+    shared_ptr = [layers.ptr(li, n_loc) for li in range(L)]
+    rng = np.random.default_rng(11)                                   # the same global batch on every rank
+    zipf = 1.0 / np.arange(1, Ex + 1) ** 1.1
+    bias_h = np.log(zipf / zipf.sum())[rng.permutation(Ex)].astype(np.float32)
+    bias = torch.from_numpy(bias_h).to(dev)
+    NS = 2
+    lg_all = rng.normal(0, 1, (NS, L, Btot, Ex)).astype(np.float32)
+    x_all = O.bf16r(rng.normal(0, 1, (NS, L, Btot, H)).astype(np.float32))
+    sl = slice(rank * B, (rank + 1) * B)
+    logits = torch.from_numpy(lg_all[:, :, sl].copy()).to(dev)
+    x = torch.from_numpy(x_all[:, :, sl].copy()).to(torch.bfloat16).to(dev)
+    out = torch.empty((NS, L, B, H), dtype=torch.bfloat16, device=dev)
+    ids = torch.empty((NS, L, B, K), dtype=torch.int32, device=dev); wts = torch.empty((NS, L, B, K), dtype=torch.float32, device=dev)
+    ep = None
+    if world > 1:
+        from eke_hive_b200.ep import ExpertParallelMoE
+        ep = ExpertParallelMoE(E, ctx, H, I, Ex, K, B, world, rank, dev, limit=limit, router="sigmoid", bias=bias, sigmoid_scale=scale)
+
+        def run_layers(s):
+            for li in range(L):
+                ep.layer(logits[s, li], x[s, li], tab, li, shared_ptr[li], -1, ids[s, li], wts[s, li], out[s, li])
+    else:
+        ws = torch.empty(E.moe_decode_ws_bytes(B * (K + 1), H, I), dtype=torch.uint8, device=dev)
+
+        def run_layers(s):
+            for li in range(L):
+                E.moe_layer_decode(logits[s, li], x[s, li], tab, li, Ex, K, H, I, shared_rec=shared_ptr[li], gate_col=-1, bias=bias, sigmoid_scale=scale,
+                                   limit=limit, ids=ids[s, li], w=wts[s, li], out=out[s, li], ws=ws, ctx=ctx)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graphs = []
+    with torch.cuda.stream(side):
+        run_layers(0)
+        side.synchronize()
+        for s_ in range(NS):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                run_layers(s_)
+            graphs.append(g)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    for i in range(4):
+        graphs[i % NS].replay()
+    if world > 1:
+        dist.barrier()
+    it = [0]
+
+    def step():
+        graphs[it[0] % NS].replay(); it[0] += 1
+    ms = _timed(torch, step, max(args.steps, 10))
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
+    ctx.check_device()
+    # parity: this rank's first row of layer 0 and last row of the last layer against the CPU oracle's whole layer (experts remade from seeds)
+    graphs[0].replay(); torch.cuda.synchronize()
+    lay = E.ExpertRecLayout.make(H, I)
+    tmp = torch.empty(lay.total, dtype=torch.uint8, device=dev)
+    err, ids_ok = 0.0, True
+    for li, m in ((0, 0), (L - 1, B - 1)):
+        lg_r = logits[0, li, m:m + 1].cpu().numpy(); x_r = x[0, li, m:m + 1].float().cpu().numpy()
+        rid, rw = O.router_sigmoid_topk(lg_r, bias_h, K, scale)
+        ids_ok = ids_ok and bool(np.array_equal(rid, ids[0, li, m:m + 1].cpu().numpy()))
+        recs = [None] * Ex
+        for e in sorted(set(int(v) for v in rid.reshape(-1))):
+            Layers.fill_record(E, tmp, H, I, li, e, CFG["sigma"], CFG["seed"] + 3); recs[e] = tmp.cpu().numpy().copy()
+        Layers.fill_record(E, tmp, H, I, li, Layers.SHARED_ID, CFG["sigma"], CFG["seed"] + 3); shared = tmp.cpu().numpy().copy()
+        _, _, ref = O.moe_layer(H, I, lg_r, x_r, recs, K, shared_rec=shared, router="sigmoid", bias=bias_h, scale=scale, limit=limit)
+        ref = O.bf16_to_f32(ref)[0].astype(np.float64); got = out[0, li, m].float().cpu().numpy().astype(np.float64)
+        err = max(err, float(np.abs(got - ref).max() / (np.sqrt((ref ** 2).mean()) + 1e-30)))
+    # load balance: pairs per rank of the global batch, records each rank streams per layer
+    gid, _ = O.router_sigmoid_topk(lg_all.reshape(-1, Ex), bias_h, K, scale)
+    gid = gid.reshape(NS * L, Btot * K)
+    bounds = [(r + 1) * Ex // world for r in range(world)]
+    owner = np.searchsorted(bounds, gid, side="right")
+    ppr = np.array([(owner == r).sum() for r in range(world)], np.float64) / (NS * L)
+    rec_r = np.array([np.mean([len(np.unique(row[(owner[j] == r)])) for j, row in enumerate(gid)]) + 1 for r in range(world)])   # + the shared copy
+    us_layer = ms * 1e3 / L
+    rec_bytes_ = 3 * H * I * 9 // 16
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    res = {"workload": "glm-shaped MoE decode: hidden 4096, 160 routed experts top-8 + shared, intermediate 1536, 8 tokens per step in all, sigmoid router + Zipf(1.1) bias",
+           "scaling": "strong", "n_gpus": world, "rows_per_rank": B, "us_per_layer": us_layer, "tokens_per_s": Btot / (us_layer * 1e-6),
+           "records_per_rank_per_layer_max": float(rec_r.max()), "records_per_rank_per_layer_mean": float(rec_r.mean()),
+           "achieved_GBps_per_gpu_max": float(rec_r.max()) * rec_bytes_ / (us_layer * 1e-6) / 1e9, "frac_of_measured_hbm_busiest_gpu": float(rec_r.max()) * rec_bytes_ / (us_layer * 1e-6) / 1e9 / peak,
+           "pairs_per_rank_max": float(ppr.max()), "pairs_per_rank_mean": float(ppr.mean()),
+           "transport": ep.transport if ep is not None else "single GPU",
+           "parity": {"ids_equal": ids_ok, "max_err_x_rms": err, "bar": 2e-2, "ok": bool(ids_ok and err <= 2e-2)}}
+    if world > 1:
+        t = torch.tensor([err, 0.0 if ids_ok else 1.0], dtype=torch.float64, device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res["parity"] = {"ids_equal": bool(t[1].item() == 0.0), "max_err_x_rms": float(t[0].item()), "bar": 2e-2, "ranks_checked": world,
+                         "ok": bool(t[1].item() == 0.0 and t[0].item() <= 2e-2)}
+        torch.cuda.synchronize()
+        ep.close()
+    del graphs, layers
+    torch.cuda.empty_cache()
+    return res
+
+
 def run_prefill(args):
-    """The DeepSeek-shaped prefill workload: one MoE layer, H 7168, I 2048, 256 routed experts (6.3 GB), top-8, T tokens, NVFP4
-    weights and NVFP4 activations; plus a dense W4A4 GEMM and the measured FP4 tensor-pipe ceiling.  Under torchrun (N > 1) the
-    experts are sharded over the ranks and every rank brings T / N tokens (strong scaling on the same total problem)."""
+    """--workload prefill: the DeepSeek-shaped prefill layer alone, its own JSON line (see prefill_measure)."""
     import torch
     import torch.distributed as dist
     import eke_hive_b200 as E
@@ -527,7 +668,21 @@ def run_prefill(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    ctx = E.context()
+    line, rc = prefill_measure(args, torch, dist, E, O, E.context(), dev, rank, world)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+        dist.destroy_process_group()
+    return rc
+
+
+def prefill_measure(args, torch, dist, E, O, ctx, dev, rank, world, with_dense=True):
+    """The DeepSeek-shaped prefill workload: one MoE layer, H 7168, I 2048, 256 routed experts (5.6 GB), top-8, T tokens, NVFP4
+    weights and NVFP4 activations; plus a dense W4A4 GEMM and the measured FP4 tensor-pipe ceiling.  With N > 1 ranks the experts are
+    sharded over the ranks and every rank brings T / N tokens (strong scaling on the same total problem); rows travel by all-to-all-v
+    dispatch and combine (eke_hive_b200/ep.py).  Returns (JSON line as a dict, return code)."""
     H, I, Ex, K, T = 7168, 2048, args.experts, 8, args.tokens
     assert Ex % world == 0 and T % world == 0
     peak = E.fp4_peak_probe(8192)
@@ -562,7 +717,7 @@ def run_prefill(args):
             E.fn_moe_prefill(tab, 0, Ex, ids, w, x, H, I, out=out, ws=ws, S=T, ctx=ctx)
     else:
         from eke_hive_b200.ep import ExpertParallelPrefill
-        epp = ExpertParallelPrefill(E, ctx, H, I, Ex, K, Tl, world, rank, dev)
+        epp = ExpertParallelPrefill(E, ctx, H, I, Ex, K, Tl, world, rank, dev, exchange=os.environ.get("HIVE_B200_PF_EXCHANGE", "a2a"))
 
         def layer():
             ids, w, x = sets[it[0] % 2]; it[0] += 1
@@ -583,12 +738,25 @@ def run_prefill(args):
             "dtype": "e2m1 x e2m1 with ue4m3 block scales, f32 accumulate", "data": "synthetic", "scaling": "strong",
             "config": {"workload": f"deepseek-shaped MoE prefill layer: hidden 7168, {Ex} routed experts top-8, intermediate 2048, T={T}, NVFP4 W4A4",
                        "l2": f"{Ex * rb.total / 1e9:.1f} GB of expert records per layer (larger than L2)",
-                       "parallelism": "single GPU" if world == 1 else f"expert-parallel ep{world}: all-gather of rows and routing, local experts over all rows, reduce-scatter of fp32 sums (NCCL)"},
+                       "parallelism": "single GPU" if world == 1 else f"expert-parallel ep{world}: experts sharded, tokens exchanged by {epp.exchange} (NCCL)"},
             "layer_TFLOPs": flops / (ms * 1e-3) / 1e12,
             "roofline": {"bound": "tensor", "kernel": "pf_gemm_kernel (gate/up + down), this rank's share", "achieved": flops / world / (gemm_us * 1e-6) / 1e12, "peak": peak,
                          "unit": "TFLOP/s", "frac": flops / world / (gemm_us * 1e-6) / 1e12 / peak,
                          "peak_source": "hb_fp4_peak_probe on this GPU (dense FP4, resident operands)", "traffic": None},
             "kernels": prof}
+    if world > 1:
+        # pairs per rank (load balance) and what the exchange moved and cost on this rank
+        owner = torch.bucketize(sets[0][0], torch.tensor([(r + 1) * Ex // world for r in range(world - 1)], dtype=torch.int32, device=dev), right=True)
+        ppr = torch.bincount(owner.reshape(-1).long(), minlength=world).double()
+        dist.all_reduce(ppr)
+        k_ms = sum(v["mean_us"] * v["launches"] for v in prof.values()) / 2 / 1e3          # two profiled layer calls
+        st = dict(epp.stats)
+        t = torch.tensor([float(st["bytes_dispatch"]), float(st["bytes_combine"]), k_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        line["exchange"] = {"kind": epp.exchange, "max_bytes_dispatch_per_rank": float(t[0].item()), "max_bytes_combine_per_rank": float(t[1].item()),
+                            "max_kernels_ms_per_rank": float(t[2].item()), "exchange_and_host_ms": ms - float(t[2].item()),
+                            "exchange_share_of_layer": (ms - float(t[2].item())) / ms,
+                            "pairs_per_rank_max": float(ppr.max().item()), "pairs_per_rank_mean": float(ppr.mean().item())}
     # the same two GEMMs against HBM: at ~256 rows per expert every weight byte serves 256 rows, so even at the FP4 peak the expert
     # records would have to stream at 2·256 / (9/16) flop per byte — more than HBM gives.  Both views are reported.
     hbm = {}
@@ -602,7 +770,7 @@ def run_prefill(args):
                             "peak": hbm_peak, "unit": "GB/s", "frac": wbytes / (gemm_us * 1e-6) / 1e9 / hbm_peak,
                             "note": "expert records read once + quantised activation rows + bf16 outputs; min time at peak %.2f ms vs %.2f ms at the FP4 peak"
                                     % (wbytes / hbm_peak / 1e6, flops / world / peak / 1e9)}
-    if world == 1:
+    if world == 1 and with_dense:
         M, N, Kd = 16384, 8192, 8192
         xq, xs, xg = E.a4_quant(torch.randn((M, Kd), device=dev, generator=g).to(torch.bfloat16))
         W = E.GMat(E.FMT_NVFP4, N, Kd, torch.randint(0, 256, (N, Kd // 2), dtype=torch.uint8, device=dev),
@@ -642,23 +810,20 @@ def run_prefill(args):
     line["parity"] = parity
     line["w4a4_vs_w4a16"] = {"cos_min": cos_min, "max_err_x_rms": dev_max, "gate": "cosine > 0.98", "ok": bool(cos_min > 0.98),
                              "what": "the same rows' W4A4 results against the oracle's W4A16 expert (bf16 activations, the reference's default prefill arithmetic)"}
-    if rank == 0:
-        print(json.dumps(line), flush=True)
     rc = 0 if parity["ok"] and line["w4a4_vs_w4a16"]["ok"] else 3      # a run whose sampled rows miss the oracle fails
-    if world > 1:
-        dist.barrier()
-        torch.cuda.synchronize()
-        dist.destroy_process_group()
-    return rc
+    return line, rc
 
 
 def run_dense(args):
-    """The dense 27B-style MLP decode workload: one FFN layer = fused gate/up GEMV + down GEMV, hidden 5120, FFN 17408, M rows,
-    for the NVFP4, 3-bit and 2-bit group-64 formats; 12 distinct layers' matrices cycled so L2 cannot serve repeats."""
+    """--workload dense: the dense low-bit MLP GEMVs alone, their own JSON line (see dense_measure)."""
     import torch
     import eke_hive_b200 as E
-    dev = torch.device("cuda", 0)
-    ctx = E.context()
+    print(json.dumps(dense_measure(args, torch, E, E.context(), torch.device("cuda", 0))), flush=True)
+
+
+def dense_measure(args, torch, E, ctx, dev, Ms=(1, 8)):
+    """The dense 27B-style MLP decode workload: one FFN layer = fused gate/up GEMV + down GEMV, hidden 5120, FFN 17408, M rows,
+    for the NVFP4, 3-bit and 2-bit group-64 formats; 12 distinct layers' matrices cycled so L2 cannot serve repeats."""
     H, I, n = 5120, 17408, 12
     peaks = {}
     try:
@@ -681,7 +846,7 @@ def run_dense(args):
     res = []
     for fmt, name, bpe in ((E.FMT_NVFP4, "nvfp4", 0.5625), (E.FMT_LB3_G64, "lb3_g64", 0.4375), (E.FMT_LB2_G64, "lb2_g64", 0.3125)):
         gs, us, ds = mk(fmt, I, H), mk(fmt, I, H), mk(fmt, H, I)
-        for M in (1, 8):
+        for M in Ms:
             x = torch.randn((M, H), device=dev).to(torch.bfloat16)
             ws = torch.empty(max(E.dense_gemv_ws_bytes(fmt, I, H, 2), E.dense_gemv_ws_bytes(fmt, H, I, 1)), dtype=torch.uint8, device=dev)
             act = torch.empty((M, I), dtype=torch.bfloat16, device=dev); y = torch.empty((M, H), dtype=torch.bfloat16, device=dev)
@@ -704,12 +869,12 @@ def run_dense(args):
         torch.cuda.empty_cache()
     ctx.check_device()
     head = res[0]
-    print(json.dumps({"metric": "dense_ffn_layer_GBps", "value": head["achieved_GBps"], "unit": "GB/s", "n_gpus": 1, "data": "synthetic",
-                      "config": {"workload": "dense 27B-style MLP decode: hidden 5120, FFN 17408, gate/up + down GEMV, M in {1, 8}",
-                                 "l2": "12 layers' matrices cycled (1.2-1.8 GB, larger than L2)"},
-                      "roofline": {"bound": "hbm", "kernel": "dense_stream_kernel", "achieved": head["achieved_GBps"], "peak": peak, "unit": "GB/s",
-                                   "frac": head["frac_of_measured_hbm"], "traffic": None},
-                      "per_case": res}), flush=True)
+    return {"metric": "dense_ffn_layer_GBps", "value": head["achieved_GBps"], "unit": "GB/s", "n_gpus": 1, "data": "synthetic",
+            "config": {"workload": "dense 27B-style MLP decode: hidden 5120, FFN 17408, gate/up + down GEMV, M in %s" % (list(Ms),),
+                       "l2": "12 layers' matrices cycled (1.2-1.8 GB, larger than L2)"},
+            "roofline": {"bound": "hbm", "kernel": "dense_stream_kernel", "achieved": head["achieved_GBps"], "peak": peak, "unit": "GB/s",
+                         "frac": head["frac_of_measured_hbm"], "traffic": None},
+            "per_case": res}
 
 
 def run_records(args):
@@ -801,6 +966,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=8192, help="--workload prefill: tokens per layer call")
     ap.add_argument("--experts", type=int, default=256, help="--workload prefill: routed experts resident (fewer = a smaller case for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the per_config / prefill / dense sub-measurements of the default run")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for the baseline leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -1,4 +1,4 @@
-"""Expert-parallel decode MoE layer over torch.distributed (one process per GPU, NCCL over NVLink / NVSwitch).
+"""Expert-parallel MoE layers (decode and prefill) over torch.distributed (one process per GPU, NCCL over NVLink / NVSwitch).
 
 The reference engine has no multi-GPU code; this is the sharded form of its MoE layer.  Rank r of G owns the routed experts
 [r·E/G, (r+1)·E/G) of every layer; the router and the shared expert are replicated; every rank brings its own B rows.
@@ -40,8 +40,11 @@ def local_table(E: int, world: int, rank: int, ptr_of) -> list[int]:
 
 class ExpertParallelMoE:
     def __init__(self, ops, ctx, H: int, I: int, E: int, K: int, B: int, world: int, rank: int, device, group=None, renorm=True,
-                 logits_bf16=True, limit=0.0, transport: str | None = None):
+                 logits_bf16=True, limit=0.0, transport: str | None = None, router: str = "softmax", bias=None, sigmoid_scale: float = 1.0):
+        """router: "softmax" (top-k of softmax over bf16-rounded logits, renormalised) or "sigmoid" (GLM: top-k of sigmoid + bias,
+        weights s / Σs · sigmoid_scale; bias fp32 [E] on the device or None)."""
         self.ops, self.ctx, self.H, self.I, self.E, self.K, self.B = ops, ctx, H, I, E, K, B
+        self.router, self.bias, self.sigmoid_scale = router, bias, sigmoid_scale
         self.world, self.rank, self.dev, self.group = world, rank, device, group
         self.renorm, self.logits_bf16, self.limit = renorm, logits_bf16, limit
         # one row's exchange record: bf16 row | int32 ids | fp32 weights, padded to 16 bytes so every field of every gathered
@@ -108,11 +111,20 @@ class ExpertParallelMoE:
         ops, B, H, K = self.ops, self.B, self.H, self.K
         if self.peer is not None:
             # three calls, six kernels: [route + push rows] → [wait + group] → gate/up → down → [reduce + push sums] → [wait + combine]
-            self.peer.route_push(logits, x, ids_out, w_out, self.E, self.renorm, self.logits_bf16)
+            if self.router == "sigmoid":
+                ops.router_topk(logits[:, :self.E].contiguous() if logits.shape[1] != self.E else logits, self.bias, K, self.sigmoid_scale, ctx=self.ctx, ids=ids_out,
+                                w=w_out)
+                self.peer.push_rows(x, ids_out, w_out)
+            else:
+                self.peer.route_push(logits, x, ids_out, w_out, self.E, self.renorm, self.logits_bf16)
             self.peer.layer_local(tab, li, self.E, self.I, shared_ptr, self.shared, self.ws, self.limit)
             self.peer.combine(self.shared if shared_ptr else None, logits if (shared_ptr and gate_col >= 0) else None, max(gate_col, 0), out)
             return out
-        ops.router_softmax_topk(logits, K, self.renorm, self.logits_bf16, E=self.E, ids=ids_out, w=w_out, ctx=self.ctx)
+        if self.router == "sigmoid":
+            ops.router_topk(logits[:, :self.E].contiguous() if logits.shape[1] != self.E else logits, self.bias, K, self.sigmoid_scale, ctx=self.ctx, ids=ids_out,
+                            w=w_out)
+        else:
+            ops.router_softmax_topk(logits, K, self.renorm, self.logits_bf16, E=self.E, ids=ids_out, w=w_out, ctx=self.ctx)
         # pack [row | ids | w] per row (one kernel), one all-gather
         torch.cat([x.view(torch.uint8).view(B, H * 2), ids_out.view(torch.uint8).view(B, K * 4), w_out.view(torch.uint8).view(B, K * 4)], dim=1,
                   out=self.send[:, :H * 2 + K * 8])
@@ -152,44 +164,107 @@ class ExpertParallelMoE:
 class ExpertParallelPrefill:
     """Expert-parallel prefill of one MoE layer: every rank holds T_local rows and the experts [r·E/G, (r+1)·E/G).
 
-        all-gather of rows, ids and weights → the grouped-GEMM operator (fn_moe_prefill) over ALL G·T_local rows with the local
-        experts only (NULL table entries: pairs of experts held elsewhere contribute nothing) → reduce-scatter of the fp32
-        routed sums → combine on the local rows.
+    exchange = "a2a" (default): token dispatch and combine as two all-to-all-v exchanges.
+        dispatch   a row goes ONCE to every rank that owns at least one of its k experts (de-duplicated per destination), as the
+                   bf16 row plus its k ids and weights; the rows for one destination travel in row order
+        experts    the grouped-GEMM operator (fn_moe_prefill) over the received rows with the local experts only (NULL table
+                   entries: a row's pairs of experts held elsewhere contribute nothing) → one fp32 partial sum per received row
+        combine    the partial sums travel back the way the rows came; the home rank adds them in rank order
+      Per direction a rank moves (rows × distinct destination ranks) records instead of every row to every rank, and the
+      operator pass works on the rows that have business on this rank, not on all G·T_local rows.  The split sizes of the
+      exchanges are data-dependent: one small all-gather of the per-destination counts and one host read per layer.
+    exchange = "allgather": all-gather of rows, ids and weights → the operator over ALL G·T_local rows → reduce-scatter of the fp32
+      sums (kept for comparison and for backends without all-to-all).
 
-    Each rank therefore runs 1/G of the pairs; the exchange moves whole rows (bf16 in, fp32 sums out) rather than the exact
-    (row, expert) pairs of an all-to-all dispatch, which keeps the operator pass and its tile list unchanged.  The routed sum
-    of a row is a sum over ranks of per-rank sums in k order: fp32 reassociation only, routing unaffected."""
+    Either way the routed sum of a row is a sum over ranks of per-rank sums in k order: it differs from the single-GPU sum by fp32
+    reassociation only, and routing is unaffected."""
 
-    def __init__(self, ops, ctx, H: int, I: int, E: int, K: int, T_local: int, world: int, rank: int, device, group=None, limit: float = 0.0):
+    def __init__(self, ops, ctx, H: int, I: int, E: int, K: int, T_local: int, world: int, rank: int, device, group=None, limit: float = 0.0,
+                 exchange: str = "a2a"):
         self.ops, self.ctx, self.H, self.I, self.E, self.K, self.T = ops, ctx, H, I, E, K, T_local
-        self.world, self.rank, self.group, self.limit = world, rank, group, limit
+        self.world, self.rank, self.group, self.limit, self.exchange = world, rank, group, limit, exchange
         G = world
-        self.x_all = torch.empty((G * T_local, H), dtype=torch.bfloat16, device=device)
-        self.ids_all = torch.empty((G * T_local, K), dtype=torch.int32, device=device)
-        self.w_all = torch.empty((G * T_local, K), dtype=torch.float32, device=device)
-        self.part = torch.empty((G * T_local, H), dtype=torch.float32, device=device)
+        cap = G * T_local                                               # a rank can receive every row of every rank at worst
+        self.x_all = torch.empty((cap, H), dtype=torch.bfloat16, device=device)
+        self.ids_all = torch.empty((cap, K), dtype=torch.int32, device=device)
+        self.w_all = torch.empty((cap, K), dtype=torch.float32, device=device)
+        self.part = torch.empty((cap, H), dtype=torch.float32, device=device)
         self.routed = torch.empty((T_local, H), dtype=torch.float32, device=device)
         self.reduce_scatter = dist.get_backend(group) != "gloo"
-        ws_bytes = getattr(ops, "moe_prefill_ws_bytes", lambda s, k, e, h, i: 256)(G * T_local, K, E, H, I)
+        ws_bytes = getattr(ops, "moe_prefill_ws_bytes", lambda s, k, e, h, i: 256)(cap, K, E, H, I)
         self.ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
+        if exchange == "a2a":
+            # send side: at most T_local rows per destination
+            self.sx = torch.empty((cap, H), dtype=torch.bfloat16, device=device)
+            self.smeta = torch.empty((cap, 2 * K), dtype=torch.int32, device=device)
+            self.rmeta = torch.empty((cap, 2 * K), dtype=torch.int32, device=device)
+            self.back = torch.empty((cap, H), dtype=torch.float32, device=device)
+            self.counts_all = torch.empty((G, G), dtype=torch.int64, device=device)
+            # owner of expert e = the rank r with r·E//G ≤ e < (r+1)·E//G
+            self.bounds = torch.tensor([(r + 1) * E // G for r in range(G - 1)], dtype=torch.int32, device=device)
+        self.stats = {}
+
+    def _dispatch_plan(self, ids):
+        """(rows to send ordered by destination then row, counts per destination [G] on the device)."""
+        G = self.world
+        valid = (ids >= 0) & (ids < self.E)
+        owner = torch.bucketize(ids, self.bounds, right=True)                       # [T, K] in [0, G)
+        owner = torch.where(valid, owner, torch.full_like(owner, G))                # invalid ids go nowhere
+        wants = torch.zeros((self.T, G + 1), dtype=torch.bool, device=ids.device)
+        wants.scatter_(1, owner.long(), True)
+        wants = wants[:, :G]
+        idx = wants.t().nonzero()                                                   # sorted by destination, then by row
+        return idx[:, 1], wants.sum(0)
 
     def layer(self, ids, w, x, tab, li: int, shared=None, lg=None, col: int = 0, out=None):
         """ids int32 / w fp32 [T_local, K], x bf16 [T_local, H]: this rank's rows; tab: device table [L·E] of local record pointers.
         Returns fp32 routed sums [T_local, H], or with `shared` (bf16 [T_local, H]) the combined bf16 rows written to `out`."""
-        ops, G, T = self.ops, self.world, self.T
-        dist.all_gather_into_tensor(self.x_all, x.contiguous(), group=self.group)
-        dist.all_gather_into_tensor(self.ids_all, ids.contiguous(), group=self.group)
-        dist.all_gather_into_tensor(self.w_all, w.contiguous(), group=self.group)
-        ops.fn_moe_prefill(tab, li, self.E, self.ids_all, self.w_all, self.x_all, self.H, self.I, out=self.part, ws=self.ws, S=G * T, limit=self.limit,
-                           ctx=self.ctx)
-        if self.reduce_scatter:
-            dist.reduce_scatter_tensor(self.routed, self.part, op=dist.ReduceOp.SUM, group=self.group)
+        ops, G, T, K = self.ops, self.world, self.T, self.K
+        if self.exchange == "a2a":
+            rows, counts = self._dispatch_plan(ids)
+            dist.all_gather_into_tensor(self.counts_all.view(-1), counts, group=self.group)
+            c = self.counts_all.cpu()                                               # the one host read of the layer: split sizes
+            send = [int(v) for v in c[self.rank]]
+            recv = [int(v) for v in c[:, self.rank]]
+            ns, nr = sum(send), sum(recv)
+            sx, smeta = self.sx[:ns], self.smeta[:ns]
+            torch.index_select(x, 0, rows, out=sx)
+            smeta[:, :K] = ids.index_select(0, rows)
+            smeta[:, K:] = w.index_select(0, rows).view(torch.int32)
+            xr, mr = self.x_all[:nr], self.rmeta[:nr]
+            dist.all_to_all_single(xr, sx, recv, send, group=self.group)
+            dist.all_to_all_single(mr, smeta, recv, send, group=self.group)
+            part = self.part[:nr]
+            if nr:
+                self.ids_all[:nr] = mr[:, :K]
+                self.w_all[:nr] = mr[:, K:].view(torch.float32)
+                ops.fn_moe_prefill(tab, li, self.E, self.ids_all[:nr], self.w_all[:nr], xr, self.H, self.I, out=part, ws=self.ws, S=max(nr, 1), limit=self.limit,
+                                   ctx=self.ctx)
+            back = self.back[:ns]
+            dist.all_to_all_single(back, part, send, recv, group=self.group)
+            self.routed.zero_()
+            o = 0
+            for g in range(G):                                                      # rank order: the sum is the same on every run
+                if send[g]:
+                    self.routed.index_add_(0, rows[o:o + send[g]], back[o:o + send[g]])   # the rows of one destination are distinct
+                o += send[g]
+            self.stats = {"rows_sent": ns - send[self.rank], "rows_received": nr - recv[self.rank], "rows_local": send[self.rank],
+                          "bytes_dispatch": (ns - send[self.rank]) * (self.H * 2 + K * 8), "bytes_combine": (ns - send[self.rank]) * self.H * 4}
         else:
-            dist.all_reduce(self.part, op=dist.ReduceOp.SUM, group=self.group)
-            self.routed.copy_(self.part[self.rank * T:(self.rank + 1) * T])
+            dist.all_gather_into_tensor(self.x_all, x.contiguous(), group=self.group)
+            dist.all_gather_into_tensor(self.ids_all, ids.contiguous(), group=self.group)
+            dist.all_gather_into_tensor(self.w_all, w.contiguous(), group=self.group)
+            ops.fn_moe_prefill(tab, li, self.E, self.ids_all, self.w_all, self.x_all, self.H, self.I, out=self.part, ws=self.ws, S=G * T, limit=self.limit,
+                               ctx=self.ctx)
+            if self.reduce_scatter:
+                dist.reduce_scatter_tensor(self.routed, self.part, op=dist.ReduceOp.SUM, group=self.group)
+            else:
+                dist.all_reduce(self.part, op=dist.ReduceOp.SUM, group=self.group)
+                self.routed.copy_(self.part[self.rank * T:(self.rank + 1) * T])
+            self.stats = {"rows_sent": (G - 1) * T, "rows_received": (G - 1) * T, "rows_local": T,
+                          "bytes_dispatch": (G - 1) * T * (self.H * 2 + K * 8), "bytes_combine": (G - 1) * T * self.H * 4}
         if shared is None:
             return self.routed
         out = torch.empty((T, self.H), dtype=torch.bfloat16, device=x.device) if out is None else out
         ops.moe_combine(self.routed, shared, lg, col, out=out, ctx=self.ctx)
         return out
-

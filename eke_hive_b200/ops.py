@@ -174,12 +174,12 @@ def router_softmax_topk(logits: torch.Tensor, k: int, renorm: bool = True, logit
     return ids, w
 
 
-def router_topk(logits: torch.Tensor, bias: torch.Tensor | None, k: int, scale: float = 1.0, ctx: Context | None = None):
-    """hive::glm::router_topk: sigmoid scores, selection on score + bias."""
+def router_topk(logits: torch.Tensor, bias: torch.Tensor | None, k: int, scale: float = 1.0, ctx: Context | None = None, ids=None, w=None):
+    """hive::glm::router_topk: sigmoid scores, selection on score + bias.  logits fp32 [M, E] dense."""
     ctx = ctx or context()
     M, E = logits.shape
-    ids = torch.empty((M, k), dtype=torch.int32, device=logits.device)
-    w = torch.empty((M, k), dtype=torch.float32, device=logits.device)
+    ids = torch.empty((M, k), dtype=torch.int32, device=logits.device) if ids is None else ids
+    w = torch.empty((M, k), dtype=torch.float32, device=logits.device) if w is None else w
     ctx.check(_L().hb_route_sigmoid_topk(ctx.handle, _p(logits), _p(bias), M, E, k, scale, _p(ids), _p(w), _stream()))
     return ids, w
 

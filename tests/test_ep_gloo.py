@@ -91,11 +91,20 @@ def _worker(rank, world, port, q):
         err = float(np.max(np.abs(got - ref)) / (np.sqrt(np.mean(ref ** 2)) + 1e-30))
         touched = layer.local_records_touched([layer.ids_all])
         # prefill form: the same rows through the grouped-GEMM operator's stand-in (NVFP4 activations), sharded vs unsharded
-        pf = ep_mod.ExpertParallelPrefill(OracleOps(O, registry), None, H, I, E, K, B, world, rank, torch.device("cpu"))
-        got_pf = pf.layer(ids, w, x, tab, 0).numpy().copy()
         full = torch.tensor([1000 + e for e in range(E)], dtype=torch.int64)
-        ref_pf = OracleOps(O, registry).fn_moe_prefill(full, 0, E, ids, w, x, H, I, out=torch.empty((B, H), dtype=torch.float32)).numpy()
-        err_pf = float(np.max(np.abs(got_pf - ref_pf)) / (np.sqrt(np.mean(ref_pf ** 2)) + 1e-30))
+        ids_pf = ids.clone()
+        ids_pf[0, 0] = -1; ids_pf[1, 1] = E + 2                          # ids outside [0, E) go nowhere and add nothing
+        ref_pf = OracleOps(O, registry).fn_moe_prefill(full, 0, E, ids_pf, w, x, H, I, out=torch.empty((B, H), dtype=torch.float32)).numpy()
+        err_pf, sent = 0.0, {}
+        for exchange in ("a2a", "allgather"):
+            pf = ep_mod.ExpertParallelPrefill(OracleOps(O, registry), None, H, I, E, K, B, world, rank, torch.device("cpu"), exchange=exchange)
+            got_pf = pf.layer(ids_pf, w, x, tab, 0).numpy().copy()
+            err_pf = max(err_pf, float(np.max(np.abs(got_pf - ref_pf)) / (np.sqrt(np.mean(ref_pf ** 2)) + 1e-30)))
+            sent[exchange] = pf.stats["rows_sent"]
+        # the dispatch sends a row to the other rank only when one of its valid ids lives there
+        other = [(int(e) >= 0 and int(e) < E and not (lo <= int(e) < hi)) for e in ids_pf.reshape(-1)]
+        want_sent = int(np.array(other).reshape(B, K).any(axis=1).sum())
+        assert sent["a2a"] == want_sent and sent["allgather"] == (world - 1) * B, (sent, want_sent)
         q.put((rank, ok_ids, err, touched, err_pf))
     finally:
         dist.destroy_process_group()
