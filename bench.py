@@ -717,7 +717,7 @@ def prefill_measure(args, torch, dist, E, O, ctx, dev, rank, world, with_dense=T
             E.fn_moe_prefill(tab, 0, Ex, ids, w, x, H, I, out=out, ws=ws, S=T, ctx=ctx)
     else:
         from eke_hive_b200.ep import ExpertParallelPrefill
-        epp = ExpertParallelPrefill(E, ctx, H, I, Ex, K, Tl, world, rank, dev, exchange=os.environ.get("HIVE_B200_PF_EXCHANGE", "a2a"))
+        epp = ExpertParallelPrefill(E, ctx, H, I, Ex, K, Tl, world, rank, dev, exchange=os.environ.get("HIVE_B200_PF_EXCHANGE", "auto"))
 
         def layer():
             ids, w, x = sets[it[0] % 2]; it[0] += 1

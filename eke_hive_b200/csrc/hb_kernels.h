@@ -13,8 +13,10 @@ int hbk_nvfp4_gemv(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int
                    cudaStream_t st);
 int hbk_nvfp4_quantize(hb_ctx* ctx, const float* w, int N, int K, uint8_t* q, uint8_t* s, float* g_mul, float* amax, cudaStream_t st);
 int hbk_a4_quant(hb_ctx* ctx, const void* x, int ld, int n, int K, uint8_t* q, uint8_t* s, float* g, cudaStream_t st);
-// the same quantisation with each row written to nd slots (dest[row·nd + j], negative = none) instead of its own
-int hbk_quant_rows_scatter(hb_ctx* ctx, const void* x, int ld, int n, int K, const int* dest, int nd, uint8_t* q, uint8_t* s, float* g, cudaStream_t st);
+// the same quantisation with each row written to nd slots (dest[row·nd + j], negative = none) instead of its own; n_dev (optional):
+// device word holding the number of rows to do when that is smaller than n
+int hbk_quant_rows_scatter(hb_ctx* ctx, const void* x, int ld, int n, int K, const int* dest, int nd, uint8_t* q, uint8_t* s, float* g, cudaStream_t st,
+                           const int* n_dev = nullptr);
 int hbk_nvfp4_setup(hb_ctx* ctx);
 
 int hbk_route_softmax_topk(hb_ctx* ctx, const float* logits, int ld, int M, int E, int k, int renorm, int logits_bf16, int32_t* ids, float* w,

@@ -665,7 +665,7 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
     a.tiles = W.tiles; a.n_tiles = W.n_tiles; a.perm = W.perm; a.tab = lt; a.L = L; a.tmB = W.tmB; a.limit = limit; a.err = ctx->dev_err;
     a.as = W.xs_s; a.ag = W.xg_s; a.Kd = H; a.N = I; a.out = W.y; a.ldo = I;
     if ((r = pf_launch<PF_GU>(ctx, "pf_gemm_gu", a, tm_x, tm_x, st))) return r;
-    if ((r = hbk_a4_quant(ctx, W.y, I, P, I, W.yq, W.ys, W.yg, st))) return r;
+    if ((r = hbk_quant_rows_scatter(ctx, W.y, I, P, I, nullptr, 1, W.yq, W.ys, W.yg, st, W.n_slots))) return r;   // only the slots that hold a pair
     a.as = W.ys; a.ag = W.yg; a.Kd = I; a.N = H; a.out = W.part; a.ldo = H;
     if ((r = pf_launch<PF_DOWN>(ctx, "pf_gemm_down", a, tm_y, tm_y, st))) return r;
     const __nv_bfloat16* sh = cmb ? reinterpret_cast<const __nv_bfloat16*>(cmb->shared) + (size_t)s0 * H : nullptr;

@@ -141,8 +141,9 @@ constexpr int QS_THREADS = 256;
 // TG threads work on a row together (256 for long rows, 64 for short ones: 256 / TG rows are then in progress in a CTA, each group
 // with its own staging buffers and its own named barrier).
 template <int TG>
-__global__ void __launch_bounds__(QS_THREADS) quant_rows_scatter_kernel(const __nv_bfloat16* __restrict__ x, int ld, int n, int Kd, const int* __restrict__ dest, int nd,
-                                                                        uint8_t* __restrict__ q, uint8_t* __restrict__ s, float* __restrict__ g) {
+__global__ void __launch_bounds__(QS_THREADS) quant_rows_scatter_kernel(const __nv_bfloat16* __restrict__ x, int ld, int n_cap, const int* __restrict__ n_dev, int Kd,
+                                                                        const int* __restrict__ dest, int nd, uint8_t* __restrict__ q, uint8_t* __restrict__ s,
+                                                                        float* __restrict__ g) {
   constexpr int NG = QS_THREADS / TG;
   extern __shared__ __align__(16) uint8_t qs_sm[];
   __shared__ float red[NG][TG / 32];
@@ -153,8 +154,16 @@ __global__ void __launch_bounds__(QS_THREADS) quant_rows_scatter_kernel(const __
   uint8_t* codes = reinterpret_cast<uint8_t*>(row32) + (size_t)Kd * 2;       // Kd / 2 bytes
   uint8_t* scl = codes + Kd / 2;                                             // Kd / 16 bytes
   const int nb = Kd / 16;
+  const int n = n_dev ? min(n_cap, *n_dev) : n_cap;                           // a row count known only on the device (rows beyond it are not touched)
   for (int r = blockIdx.x * NG + grp; r < n; r += gridDim.x * NG) {
     const __nv_bfloat16* xr = x + (size_t)r * ld;
+    if (dest) {                                                               // a row nobody wants (all its experts live elsewhere) is not even read
+      if (t < nd) dst_s[grp][t] = dest[(size_t)r * nd + t];
+      named_bar_sync(bar, TG);
+      bool wanted = false;
+      for (int j = 0; j < nd; ++j) wanted |= dst_s[grp][j] >= 0;
+      if (!wanted) { named_bar_sync(bar, TG); continue; }
+    }
     float a = 0.f;
     if ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) {
       for (int i = t; i < Kd / 8; i += TG) {
@@ -173,7 +182,6 @@ __global__ void __launch_bounds__(QS_THREADS) quant_rows_scatter_kernel(const __
     }
     for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
     if (lane == 0) red[grp][wp] = a;
-    if (dest && t < nd) dst_s[grp][t] = dest[(size_t)r * nd + t];
     named_bar_sync(bar, TG);
 #pragma unroll
     for (int i = 0; i < TG / 32; ++i) a = fmaxf(a, red[grp][i]);
@@ -252,7 +260,8 @@ int hbk_nvfp4_quantize(hb_ctx* ctx, const float* w, int N, int K, uint8_t* q, ui
                    (const float*)amax, reinterpret_cast<uint16_t*>(q), s, g_mul);
 }
 
-int hbk_quant_rows_scatter(hb_ctx* ctx, const void* x, int ld, int n, int K, const int* dest, int nd, uint8_t* q, uint8_t* s, float* g, cudaStream_t st) {
+int hbk_quant_rows_scatter(hb_ctx* ctx, const void* x, int ld, int n, int K, const int* dest, int nd, uint8_t* q, uint8_t* s, float* g, cudaStream_t st,
+                           const int* n_dev) {
   HB_REQUIRE(ctx, nd >= 1 && nd <= 32, HB_ERR_UNSUPPORTED, "quant_rows: %d destinations per row (at most 32)", nd);
   const bool small = K <= 4096;                                              // short rows: four at a time per CTA
   const size_t stage = (size_t)K * 2 + K / 2 + (K / 16 + 15) / 16 * 16, smem = stage * (small ? 4 : 1);
@@ -262,12 +271,12 @@ int hbk_quant_rows_scatter(hb_ctx* ctx, const void* x, int ld, int n, int K, con
   if (grid > (n + per - 1) / per) grid = (n + per - 1) / per;
   const char* name = dest ? "quant_rows_scatter" : "a4_quant";
   const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
-  if (small) return hb_launch(ctx, name, false, quant_rows_scatter_kernel<64>, dim3(grid), dim3(QS_THREADS), smem, st, xb, ld, n, K, dest, nd, q, s, g);
-  return hb_launch(ctx, name, false, quant_rows_scatter_kernel<256>, dim3(grid), dim3(QS_THREADS), smem, st, xb, ld, n, K, dest, nd, q, s, g);
+  if (small) return hb_launch(ctx, name, false, quant_rows_scatter_kernel<64>, dim3(grid), dim3(QS_THREADS), smem, st, xb, ld, n, n_dev, K, dest, nd, q, s, g);
+  return hb_launch(ctx, name, false, quant_rows_scatter_kernel<256>, dim3(grid), dim3(QS_THREADS), smem, st, xb, ld, n, n_dev, K, dest, nd, q, s, g);
 }
 
 int hbk_a4_quant(hb_ctx* ctx, const void* x, int ld, int n, int K, uint8_t* q, uint8_t* s, float* g, cudaStream_t st) {
-  return hbk_quant_rows_scatter(ctx, x, ld, n, K, nullptr, 1, q, s, g, st);
+  return hbk_quant_rows_scatter(ctx, x, ld, n, K, nullptr, 1, q, s, g, st, nullptr);
 }
 
 int hbk_nvfp4_setup(hb_ctx* ctx) {

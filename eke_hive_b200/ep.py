@@ -164,7 +164,7 @@ class ExpertParallelMoE:
 class ExpertParallelPrefill:
     """Expert-parallel prefill of one MoE layer: every rank holds T_local rows and the experts [r·E/G, (r+1)·E/G).
 
-    exchange = "a2a" (default): token dispatch and combine as two all-to-all-v exchanges.
+    exchange = "a2a": token dispatch and combine as two all-to-all-v exchanges.
         dispatch   a row goes ONCE to every rank that owns at least one of its k experts (de-duplicated per destination), as the
                    bf16 row plus its k ids and weights; the rows for one destination travel in row order
         experts    the grouped-GEMM operator (fn_moe_prefill) over the received rows with the local experts only (NULL table
@@ -173,15 +173,21 @@ class ExpertParallelPrefill:
       Per direction a rank moves (rows × distinct destination ranks) records instead of every row to every rank, and the
       operator pass works on the rows that have business on this rank, not on all G·T_local rows.  The split sizes of the
       exchanges are data-dependent: one small all-gather of the per-destination counts and one host read per layer.
-    exchange = "allgather": all-gather of rows, ids and weights → the operator over ALL G·T_local rows → reduce-scatter of the fp32
-      sums (kept for comparison and for backends without all-to-all).
+    exchange = "allgather" (what "auto", the default, picks — see __init__): all-gather of rows, ids and weights → the operator over
+      ALL G·T_local rows → reduce-scatter of the fp32 sums.
 
     Either way the routed sum of a row is a sum over ranks of per-rank sums in k order: it differs from the single-GPU sum by fp32
     reassociation only, and routing is unaffected."""
 
     def __init__(self, ops, ctx, H: int, I: int, E: int, K: int, T_local: int, world: int, rank: int, device, group=None, limit: float = 0.0,
-                 exchange: str = "a2a"):
+                 exchange: str = "auto"):
         self.ops, self.ctx, self.H, self.I, self.E, self.K, self.T = ops, ctx, H, I, E, K, T_local
+        if exchange == "auto":
+            # The de-duplicated dispatch moves (1 - (1 - 1/G)^K) of what the all-gather moves under even routing (0.66 at 8 ranks and
+            # top-8, 1.0 at 2 ranks), but its split sizes need a host read in the middle of the layer, which lets the GPU run dry.
+            # Measured on 8 B200 over NVSwitch (T = 8192, H = 7168) the all-gather form is the faster one at 2 and at 8 ranks, so it is
+            # what "auto" picks; "a2a" is the form for fabrics where the bytes, not the host read, are the cost.
+            exchange = "allgather"
         self.world, self.rank, self.group, self.limit, self.exchange = world, rank, group, limit, exchange
         G = world
         cap = G * T_local                                               # a rank can receive every row of every rank at worst
@@ -213,8 +219,10 @@ class ExpertParallelPrefill:
         wants = torch.zeros((self.T, G + 1), dtype=torch.bool, device=ids.device)
         wants.scatter_(1, owner.long(), True)
         wants = wants[:, :G]
-        idx = wants.t().nonzero()                                                   # sorted by destination, then by row
-        return idx[:, 1], wants.sum(0)
+        # (destination, row) pairs that are wanted, in destination-then-row order, without a data-dependent shape (which would make
+        # the host wait): a stable sort brings them to the front; the caller cuts the list at the total it reads with the counts
+        order = torch.argsort((~wants.t().reshape(-1)).to(torch.uint8), stable=True)
+        return order % self.T, wants.sum(0)
 
     def layer(self, ids, w, x, tab, li: int, shared=None, lg=None, col: int = 0, out=None):
         """ids int32 / w fp32 [T_local, K], x bf16 [T_local, H]: this rank's rows; tab: device table [L·E] of local record pointers.
@@ -227,6 +235,7 @@ class ExpertParallelPrefill:
             send = [int(v) for v in c[self.rank]]
             recv = [int(v) for v in c[:, self.rank]]
             ns, nr = sum(send), sum(recv)
+            rows = rows[:ns]
             sx, smeta = self.sx[:ns], self.smeta[:ns]
             torch.index_select(x, 0, rows, out=sx)
             smeta[:, :K] = ids.index_select(0, rows)
