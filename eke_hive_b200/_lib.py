@@ -93,6 +93,7 @@ def load() -> C.CDLL:
         "hb_nvfp4_dequant": (i, [vp, vp, vp, f, i, i, vp, vp]),
         "hb_nvfp4_gemv": (i, [vp, vp, vp, f, i, i, vp, i, i, vp, i, vp]),
         "hb_nvfp4_quantize": (i, [vp, vp, i, i, vp, vp, vp, vp, vp]),
+        "hb_requant_nvfp4": (i, [vp, vp, vp, i, i, vp, vp, vp, vp, vp]),
         "hb_a4_quant": (i, [vp, vp, i, i, i, vp, vp, vp, vp]),
         "hb_route_softmax_topk": (i, [vp, vp, i, i, i, i, i, i, vp, vp, vp]),
         "hb_route_sigmoid_topk": (i, [vp, vp, vp, i, i, i, f, vp, vp, vp]),

@@ -158,6 +158,13 @@ int hb_nvfp4_quantize(hb_ctx* ctx, const float* w, int N, int K, uint8_t* q, uin
   return hbk_nvfp4_quantize(ctx, w, N, K, q, s, g_mul, amax, as_stream(stream));
 }
 
+int hb_requant_nvfp4(hb_ctx* ctx, const uint8_t* w_fp8, const float* row_scale, int N, int K, uint8_t* q, uint8_t* s, float* g_mul, float* amax, void* stream) {
+  HB_CTX(ctx); HB_PTR(ctx, w_fp8); HB_PTR(ctx, row_scale); HB_PTR(ctx, q); HB_PTR(ctx, s); HB_PTR(ctx, g_mul); HB_PTR(ctx, amax);
+  HB_REQUIRE(ctx, N > 0 && K > 0 && K % 16 == 0, HB_ERR_UNSUPPORTED, "requant_nvfp4: N=%d K=%d (K %% 16)", N, K);
+  HB_REQUIRE(ctx, hb_aligned(w_fp8, 4) && hb_aligned(q, 8), HB_ERR_INVALID, "requant_nvfp4: w_fp8 must be 4-byte aligned, q 8-byte aligned");
+  return hbk_requant_nvfp4(ctx, w_fp8, row_scale, N, K, q, s, g_mul, amax, as_stream(stream));
+}
+
 int hb_a4_quant(hb_ctx* ctx, const void* x, int ld, int n, int K, uint8_t* q, uint8_t* s, float* g, void* stream) {
   HB_CTX(ctx); HB_PTR(ctx, x); HB_PTR(ctx, q); HB_PTR(ctx, s); HB_PTR(ctx, g);
   HB_REQUIRE(ctx, n > 0 && K > 0 && K % 16 == 0 && ld >= K, HB_ERR_UNSUPPORTED, "a4_quant: n=%d K=%d ld=%d", n, K, ld);

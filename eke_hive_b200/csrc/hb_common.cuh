@@ -28,6 +28,9 @@ struct hb_ctx {
   // tensor maps of the decode layer kernel (k_moe_dtc.cu): device array + the shape they were made for
   void* dtc_maps = nullptr;
   int dtc_H = 0, dtc_I = 0;
+  // streaming down kernels (one per split-K width): whether the planned number of CTAs per SM is really resident, i.e. whether the
+  // CTAs may meet inside the kernel (k_moe_decode.cu)
+  const void* down_fn[8] = {nullptr}; bool down_meet[8] = {false};
   char err[512] = {0};
   // optional per-kernel timing (hb_profile_enable): a start/stop event pair around every launch, aggregated by hb_profile_read
   bool prof_on = false;

@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(kGroupThreads) moe_group_kernel(GroupArgs a) {
     a.ws.pos_of[i] = pos;
   }
   for (int i = threadIdx.x; i < P; i += blockDim.x) a.ws.done[i] = 0;
-  if (threadIdx.x == 0) { a.ws.hdr[0] = misc[65]; a.ws.hdr[1] = misc[64]; a.ws.hdr[2] = 0; }
+  if (threadIdx.x == 0) { a.ws.hdr[0] = misc[65]; a.ws.hdr[1] = misc[64]; a.ws.hdr[2] = 0; a.ws.hdr[3] = 0; }
 }
 
 static size_t group_smem(bool routed, int P, int E, int route = 0) {
@@ -158,7 +158,7 @@ static size_t group_smem(bool routed, int P, int E, int route = 0) {
 
 // ================================================================================================ streaming kernels
 template <int WK, int WM, bool DOWN>
-__global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK, WM, DOWN>::CTAS_PER_SM) moe_stream_kernel(StreamArgs a) {
+__device__ __forceinline__ void moe_stream_roles(const StreamArgs& a) {
   using C = StreamCfg<WK, WM, DOWN>;
   extern __shared__ __align__(128) uint8_t smem[];
   const int S = a.stages, NSLOT = S + 1;
@@ -333,6 +333,29 @@ __global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK
   }
 }
 
+// The streaming kernel: the roles above, and for the down pass of the routed form the sums over each row's pairs at the end.  All CTAs
+// of the grid are resident (the grid is sized by the occupancy the launcher planned), so they can meet: a CTA announces that its
+// partial rows are written, waits (bounded) until every CTA has, and takes its share of the (row, column pair) units.
+template <int WK, int WM, bool DOWN>
+__global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK, WM, DOWN>::CTAS_PER_SM) moe_stream_kernel(const StreamArgs a) {
+  moe_stream_roles<WK, WM, DOWN>(a);
+  if (!DOWN || !a.red_on) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(a.fin, 1u);
+    uint32_t spins = 0;
+    while (*reinterpret_cast<volatile unsigned int*>(a.fin) < gridDim.x) {
+      if (++spins > (1u << 22)) { atomicOr(a.err, 0x8000u); break; }
+      __nanosleep(32);
+    }
+    __threadfence();
+  }
+  __syncthreads();
+  const size_t units = (size_t)a.red.M * a.red.H / 2, step = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < units; i += step) reduce_routed_unit(a.red, i);
+}
+
 // ================================================================================================ reduce / combine
 // Routed form: out[m] = Σ_k w[m,k]·part[pos] in k order; then either fp32 (overwritten) or the shared-expert combine → bf16.
 __global__ void moe_reduce_routed_kernel(ReduceArgs r) {
@@ -489,6 +512,8 @@ size_t hbk_moe_decode_ws_stream_bytes(int n, int H, int I) {
 size_t hbk_moe_decode_ws_bytes(int n, int H, int I) { return hbk_moe_decode_ws_stream_bytes(n, H, I) + hbk_moe_dtc_ws_extra(n < 1 ? 1 : n, H, I); }
 
 int hbk_moe_decode_setup(hb_ctx* ctx) {
+  int n_down = 0;
+  static_assert(sizeof(kWkList) / sizeof(kWkList[0]) <= 8, "hb_ctx::down_fn");
   for (int wk : kWkList) {
     StreamKernel k[2];
     pick_kernel<false>(wk * kSlice, &k[0]);
@@ -497,6 +522,15 @@ int hbk_moe_decode_setup(hb_ctx* ctx) {
       int s, c;
       plan_stream(ctx, kk, &s, &c);
       HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(kk.fn), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kk.smem(s)));
+    }
+    {
+      // may the down kernel's CTAs wait for one another?  Only if the runtime agrees that the planned CTAs per SM fit
+      int s, c, occ = 0;
+      plan_stream(ctx, k[1], &s, &c);
+      HB_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, reinterpret_cast<const void*>(k[1].fn), k[1].threads, k[1].smem(s)));
+      ctx->down_fn[n_down] = reinterpret_cast<const void*>(k[1].fn);
+      ctx->down_meet[n_down] = occ >= c;
+      ++n_down;
     }
   }
   {
@@ -582,6 +616,16 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
     sd.stages = s;
     grid = ctx->sm_count * c;
     if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
+    bool meet = false;
+    for (int j = 0; j < 8; ++j) if (ctx->down_fn[j] == reinterpret_cast<const void*>(kd.fn)) meet = ctx->down_meet[j];
+    if (routed && !red.ep && meet) {
+      // the down pass sums the rows' pairs itself (its CTAs meet at the end): no reduce launch
+      sd.red_on = 1; sd.fin = reinterpret_cast<unsigned int*>(w.hdr + 3);
+      sd.red = ReduceArgs{w.part, w.pos_of, w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
+                          reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), ga.sh_row0, ga.sh_rows,
+                          hbk_ep_push{}};
+      return hb_launch(ctx, "moe_down_reduce", true, kd.fn, dim3(grid), dim3(kd.threads), kd.smem(s), st, sd);
+    }
     if ((r = hb_launch(ctx, "moe_down", true, kd.fn, dim3(grid), dim3(kd.threads), kd.smem(s), st, sd))) return r;
   } else {
     if ((r = hb_launch(ctx, "moe_gate_up_generic", true, moe_generic_kernel<false>, dim3((I + 7) / 8, P), dim3(256), (size_t)H * 4, st, sa))) return r;

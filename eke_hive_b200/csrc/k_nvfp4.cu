@@ -91,11 +91,27 @@ __global__ void __launch_bounds__(256) nvfp4_gemv_kernel(const uint8_t* __restri
 // scale = e4m3(block amax · gs / 6), code = e2m1(v · gs / scale); no per-block scale search).  Four lanes share a block of 16: a lane
 // loads ONE float4 (a warp reads 512 contiguous bytes), the block's amax is two shuffles away, the four lanes work out the same scale
 // and each turns its own four values into 16 bits of codes (a warp writes 64 contiguous bytes).
-__global__ void __launch_bounds__(256) tensor_absmax_kernel(const float4* __restrict__ w4, size_t n4, float* __restrict__ amax) {
+// The source of four consecutive values: an fp32 matrix, or an FP8 (e4m3) matrix with one fp32 scale per row (value = fp8 · row scale,
+// the reference's FP8ROW weights).
+struct SrcF32 {
+  const float4* w4;
+  __device__ __forceinline__ float4 load(size_t i) const { return __ldg(w4 + i); }
+};
+struct SrcFp8Row {
+  const uint32_t* w8; const float* row_scale; int K4;                       // K4 = K / 4 groups per row
+  __device__ __forceinline__ float4 load(size_t i) const {
+    const uint32_t u = __ldg(w8 + i);
+    const float sr = __ldg(row_scale + i / (size_t)K4);
+    return make_float4(__fmul_rn(e4m3_to_f32(u & 0xffu), sr), __fmul_rn(e4m3_to_f32((u >> 8) & 0xffu), sr), __fmul_rn(e4m3_to_f32((u >> 16) & 0xffu), sr),
+                       __fmul_rn(e4m3_to_f32(u >> 24), sr));
+  }
+};
+template <class SRC>
+__global__ void __launch_bounds__(256) tensor_absmax_kernel(const SRC src, size_t n4, float* __restrict__ amax) {
   __shared__ float part[8];
   float m = 0.f;
   for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n4; i += (size_t)gridDim.x * 256) {
-    const float4 v = __ldg(w4 + i);
+    const float4 v = src.load(i);
     m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
   }
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -107,15 +123,16 @@ __global__ void __launch_bounds__(256) tensor_absmax_kernel(const float4* __rest
     if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(m));   // one atomic per block; magnitudes order like their bits
   }
 }
-__global__ void __launch_bounds__(256) nvfp4_encode_kernel(const float4* __restrict__ w4, size_t n4, const float* __restrict__ amax, uint16_t* __restrict__ q16,
+template <class SRC>
+__global__ void __launch_bounds__(256) nvfp4_encode_kernel(const SRC src, size_t n4, const float* __restrict__ amax, uint16_t* __restrict__ q16,
                                                            uint8_t* __restrict__ s, float* __restrict__ g_mul) {
   const float am = *amax;
   const bool live = am > 0.f;
   const float gs = live ? __fdiv_rn(448.f * 6.f, am) : 1.f;
   if (blockIdx.x == 0 && threadIdx.x == 0) *g_mul = live ? __fdiv_rn(am, 448.f * 6.f) : 1.f;
-  const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;                   // one float4 per thread; n4 is a multiple of 4, whole quads stay in range together
+  const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;                   // four values per thread; n4 is a multiple of 4, whole quads stay in range together
   if (i >= n4) return;
-  const float4 v = __ldg(w4 + i);
+  const float4 v = src.load(i);
   float m = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
   const unsigned quad = 0xfu << (threadIdx.x & 28);
   m = fmaxf(m, __shfl_xor_sync(quad, m, 1));
@@ -248,16 +265,21 @@ int hbk_nvfp4_gemv(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float g, int
   return hb_launch(ctx, "nvfp4_gemv", false, fn, grid, block, 0, st, w, s, g, N, K, xb, ldx, M, y, ldy);
 }
 
-int hbk_nvfp4_quantize(hb_ctx* ctx, const float* w, int N, int K, uint8_t* q, uint8_t* s, float* g_mul, float* amax, cudaStream_t st) {
-  const size_t n4 = (size_t)N * K / 4;                                       // K is a multiple of 16
+template <class SRC>
+static int quantize_from(hb_ctx* ctx, const SRC& src, size_t n4, uint8_t* q, uint8_t* s, float* g_mul, float* amax, cudaStream_t st) {
   cudaError_t e = cudaMemsetAsync(amax, 0, 4, st);
   if (e != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "memset amax: %s", cudaGetErrorString(e));
   size_t blocks = (n4 + 255) / 256, cap = (size_t)ctx->sm_count * 8;
-  int r = hb_launch(ctx, "tensor_absmax", false, tensor_absmax_kernel, dim3((unsigned)(blocks < cap ? blocks : cap)), dim3(256), 0, st,
-                    reinterpret_cast<const float4*>(w), n4, amax);
+  int r = hb_launch(ctx, "tensor_absmax", false, tensor_absmax_kernel<SRC>, dim3((unsigned)(blocks < cap ? blocks : cap)), dim3(256), 0, st, src, n4, amax);
   if (r) return r;
-  return hb_launch(ctx, "nvfp4_encode", false, nvfp4_encode_kernel, dim3((unsigned)blocks), dim3(256), 0, st, reinterpret_cast<const float4*>(w), n4,
-                   (const float*)amax, reinterpret_cast<uint16_t*>(q), s, g_mul);
+  return hb_launch(ctx, "nvfp4_encode", false, nvfp4_encode_kernel<SRC>, dim3((unsigned)blocks), dim3(256), 0, st, src, n4, (const float*)amax,
+                   reinterpret_cast<uint16_t*>(q), s, g_mul);
+}
+int hbk_nvfp4_quantize(hb_ctx* ctx, const float* w, int N, int K, uint8_t* q, uint8_t* s, float* g_mul, float* amax, cudaStream_t st) {
+  return quantize_from(ctx, SrcF32{reinterpret_cast<const float4*>(w)}, (size_t)N * K / 4, q, s, g_mul, amax, st);   // K is a multiple of 16
+}
+int hbk_requant_nvfp4(hb_ctx* ctx, const uint8_t* w_fp8, const float* row_scale, int N, int K, uint8_t* q, uint8_t* s, float* g_mul, float* amax, cudaStream_t st) {
+  return quantize_from(ctx, SrcFp8Row{reinterpret_cast<const uint32_t*>(w_fp8), row_scale, K / 4}, (size_t)N * K / 4, q, s, g_mul, amax, st);
 }
 
 int hbk_quant_rows_scatter(hb_ctx* ctx, const void* x, int ld, int n, int K, const int* dest, int nd, uint8_t* q, uint8_t* s, float* g, cudaStream_t st,

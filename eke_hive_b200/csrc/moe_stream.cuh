@@ -44,6 +44,15 @@ inline DecodeWs carve(void* ws, int n, int H, int I) {
   return w;
 }
 
+// Routed reduce of two adjacent columns of one row: Σ_k w·part in k order, then either the fp32 sum or the shared-expert combine.
+struct ReduceArgs {
+  const __nv_bfloat16* part; const int* pos_of; const float* pw; int M, K, H, shared_pairs;
+  const __nv_bfloat16* shared; const float* lg; int ld, col;
+  __nv_bfloat16* out_bf16; float* out_f32;
+  __nv_bfloat16* shared_out = nullptr; int sh_row0 = 0, sh_rows = 0;   // fp32 form: the shared expert's output rows, written apart
+  hbk_ep_push ep = {};                            // ep.world > 0: the routed sums go to the owning ranks' partial buffers
+};
+
 struct StreamArgs {
   const int* hdr; const Group* groups; const int* s_row;
   const __nv_bfloat16* act; int act_ld;        // gate/up: x rows (indexed through s_row); down: y (indexed by sorted position)
@@ -52,6 +61,9 @@ struct StreamArgs {
   uint32_t off_wa, off_sa, off_wb, off_sb, off_g;   // record offsets: gate/up = w1,s1,w3,s3 ; down = w2,s2 (wb/sb unused)
   int stages;
   uint32_t* err;
+  // down kernel, routed form: when red_on, the CTAs meet at the end (fin: two counters in the workspace header, zeroed by the grouping
+  // kernel) and add the rows' pairs up themselves — the k-order sum and the shared-expert combine without a launch of their own
+  int red_on; unsigned int* fin; ReduceArgs red;
 };
 
 template <int WK, int WM, bool DOWN>
@@ -187,14 +199,6 @@ __device__ __forceinline__ void tile_epilogue(const float (&acc)[4], const Group
   }
 }
 
-// Routed reduce of two adjacent columns of one row: Σ_k w·part in k order, then either the fp32 sum or the shared-expert combine.
-struct ReduceArgs {
-  const __nv_bfloat16* part; const int* pos_of; const float* pw; int M, K, H, shared_pairs;
-  const __nv_bfloat16* shared; const float* lg; int ld, col;
-  __nv_bfloat16* out_bf16; float* out_f32;
-  __nv_bfloat16* shared_out = nullptr; int sh_row0 = 0, sh_rows = 0;   // fp32 form: the shared expert's output rows, written apart
-  hbk_ep_push ep = {};                            // ep.world > 0: the routed sums go to the owning ranks' partial buffers
-};
 __device__ __forceinline__ void reduce_routed_unit(const ReduceArgs& r, size_t i) {
   const int m = (int)(i / (r.H / 2)), d = (int)(i % (r.H / 2)) * 2;
   float a0 = 0.f, a1 = 0.f;

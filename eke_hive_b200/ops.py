@@ -15,7 +15,7 @@ import torch
 from . import _lib
 from ._lib import Config, HbError, MoePair, PfCombine, RecLayout
 
-__all__ = ["Context", "context", "ExpertRecLayout", "nvfp4_dequant", "nvfp4_gemv", "nvfp4_quantize", "a4_quant", "router_softmax_topk",
+__all__ = ["Context", "context", "ExpertRecLayout", "nvfp4_dequant", "nvfp4_gemv", "nvfp4_quantize", "requant_nvfp4", "a4_quant", "router_softmax_topk",
            "router_topk", "build_moe_pairs", "moe_combine", "moe_decode_ws_bytes", "moe_decode", "fn_moe_decode_routed", "fn_moe_decode_routed_static", "static_max_pairs", "moe_decode_routed_f32", "moe_layer_decode",
            "moe_decode_supported", "GMat", "dense_gemv", "dense_gemv_gu", "dense_gemv_ws_bytes", "lb_dequant", "dispatch_plan", "moe_layer", "moe_layer_ws_bytes", "PeerExchange", "moe_decode_ep_local", "moe_prefill_supported", "moe_prefill_ws_bytes", "fn_moe_prefill", "nvfp4_gemm_a4", "fp4_peak_probe", "FMT_NVFP4", "FMT_LB3_G64", "FMT_LB2_G64", "expert_dequant", "csf_decode", "record_pack", "record_pack_ws_bytes", "record_jobs", "record_pack_batch", "CSF_OK", "CSF_EXC_INDEX", "CSF_EXC_DELTA", "CSF_EXC_VALUE", "CSF_CODE", "gather_rows", "swiglu_rows", "scatter_add_rows", "add_f32", "make_pairs", "rec_table", "HbError"]
 
@@ -148,6 +148,19 @@ def nvfp4_quantize(w: torch.Tensor, q=None, s=None, g=None, ctx: Context | None 
     g = torch.empty(1, dtype=torch.float32, device=w.device) if g is None else g
     amax = torch.empty(1, dtype=torch.float32, device=w.device)
     ctx.check(_L().hb_nvfp4_quantize(ctx.handle, _p(w), N, K, _p(q), _p(s), _p(g), _p(amax), _stream()))
+    return q, s, g
+
+
+def requant_nvfp4(w_fp8: torch.Tensor, row_scale: torch.Tensor, ctx: Context | None = None):
+    """hive::q27::k::requant_nvfp4: FP8 (e4m3 codes u8 [N, K]) with one fp32 scale per row → (codes u8 [N, K/2], scales u8 [N, K/16],
+    g_mul fp32 [1] on the device)."""
+    ctx = ctx or context()
+    N, K = w_fp8.shape
+    q = torch.empty((N, K // 2), dtype=torch.uint8, device=w_fp8.device)
+    s = torch.empty((N, K // 16), dtype=torch.uint8, device=w_fp8.device)
+    g = torch.empty(1, dtype=torch.float32, device=w_fp8.device)
+    amax = torch.empty(1, dtype=torch.float32, device=w_fp8.device)
+    ctx.check(_L().hb_requant_nvfp4(ctx.handle, _p(w_fp8), _p(row_scale), N, K, _p(q), _p(s), _p(g), _p(amax), _stream()))
     return q, s, g
 
 

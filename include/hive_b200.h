@@ -124,6 +124,12 @@ HB_API int hb_nvfp4_gemv(hb_ctx* ctx, const uint8_t* w, const uint8_t* s, float 
  * g_mul[0] = amax/(448·6); scale = e4m3(m·gs/6); code = e2m1(v·gs/scale).  amax_scratch: 4 device bytes. */
 HB_API int hb_nvfp4_quantize(hb_ctx* ctx, const float* w_f32, int N, int K, uint8_t* q, uint8_t* s, float* g_mul, float* amax_scratch,
                              void* stream);
+/* hive::q27::k::requant_nvfp4 — engine/include/hive/q27/q27_kernels.h:44-46, engine/src/q27/q27_kernels.cu:2492-2542: the NVFP4 copy of an
+ * FP8 row-scaled matrix (w_fp8 e4m3 [N,K], value = fp8 · row_scale[n]): global scale from the largest magnitude, e4m3 scale per 16
+ * values, e2m1 codes, round to nearest.  Unlike the reference's host function this one does not synchronise: the global scale is
+ * left in g_mul[0] on the device (the reference returns it on the host).  amax_scratch: 4 device bytes. */
+HB_API int hb_requant_nvfp4(hb_ctx* ctx, const uint8_t* w_fp8, const float* row_scale, int N, int K, uint8_t* q, uint8_t* s, float* g_mul,
+                            float* amax_scratch, void* stream);
 /* hive::qwen a4_quant_kernel — engine/src/qwen/fn_moe_pf.cu:456-502: per-row dynamic NVFP4 activation quantisation */
 HB_API int hb_a4_quant(hb_ctx* ctx, const void* x_bf16, int ld, int n, int K, uint8_t* q, uint8_t* s, float* g, void* stream);
 

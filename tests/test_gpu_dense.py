@@ -68,6 +68,33 @@ def test_nvfp4_dense_gemv_vs_oracle(E, oracle, N, K, M):
     assert np.max(np.abs(y - ref)) <= 1e-4 * np.max(np.abs(ref))       # products are exact in f16, sums in fp32: only the order differs
 
 
+@pytest.mark.parametrize("fmt", ["nvfp4", "lb3", "lb2"])
+@pytest.mark.parametrize("N,K", [(17408, 5120), (5120, 17408)])
+def test_dense_gemv_full_shapes(E, oracle, fmt, N, K):
+    """The shapes the dense workload is measured on — 17408 × 5120 (gate, up) and 5120 × 17408 (down: the longest K, nine K splits) — at
+    1 and 8 rows, every output row against the CPU oracle (NVFP4: the reference GEMV's restatement; 3-/2-bit: this project's own)."""
+    import torch
+    rng = np.random.default_rng(N // 7 + K)
+    w = rng.normal(0, 0.02, (N, K)).astype(np.float32)
+    x = oracle.bf16r(rng.normal(0, 1, (8, K)).astype(np.float32))
+    if fmt == "nvfp4":
+        q, s, g = oracle.nvfp4_quantize(w, search=False)
+        G = E.GMat(E.FMT_NVFP4, N, K, torch.from_numpy(q).cuda(), torch.from_numpy(s).cuda(), None, g)
+        ref = oracle.gemv_nvfp4(q, s, g, x)
+    else:
+        bits = 3 if fmt == "lb3" else 2
+        q, s, zp = oracle.lb_quantize(w, bits)
+        G = E.GMat(E.FMT_LB3_G64 if bits == 3 else E.FMT_LB2_G64, N, K, torch.from_numpy(q).cuda(), torch.from_numpy(s.view(np.int16)).cuda(),
+                   torch.from_numpy(zp.view(np.int16)).cuda())
+        ref = oracle.lb_gemv(q, s, zp, bits, x)
+    y8 = E.dense_gemv(G, bf16_tensor(x)).cpu().numpy()
+    y1 = E.dense_gemv(G, bf16_tensor(x[:1])).cpu().numpy()
+    E.context().check_device()
+    assert np.isfinite(y8).all()
+    assert rel_rms_err(y8, ref) <= 2e-2
+    assert y1.tobytes() == y8[:1].tobytes()                              # a row alone = the row inside the batch
+
+
 @pytest.mark.parametrize("bits", [2, 3])
 def test_gate_up_fused_activation(E, oracle, bits):
     N, K, M = 256, 1024, 8

@@ -48,6 +48,34 @@ def test_quantize_matches_device_rule(E, oracle):
     assert np.linalg.norm(dq - w) / np.linalg.norm(w) < 0.12
 
 
+def test_requant_fp8_rows_to_nvfp4(E, oracle):
+    """hb_requant_nvfp4 (FP8 codes with one fp32 scale per row → NVFP4): the same bits as the quantisation rule applied to the fp32
+    values the FP8 matrix stands for (code value × row scale, one fp32 multiply), including an all-zero block, a zero row scale
+    and the largest finite e4m3 codes."""
+    import torch
+    rng = np.random.default_rng(27)
+    N, K = 80, 768
+    w8 = rng.integers(0, 256, (N, K), dtype=np.uint8)
+    w8[(w8 & 0x7F) == 0x7F] = 0x3A                              # no NaN codes in weights
+    w8[3, 64:80] = 0                                            # an all-zero block
+    w8[9, :16] = 0x7E                                           # 448, the largest e4m3 value
+    sr = rng.uniform(0.5e-3, 4e-3, N).astype(np.float32)
+    sr[11] = 0.0                                                # a row scaled to nothing
+    sr[12] = -sr[12]                                            # a negative row scale flips the signs
+    f = (oracle.e4m3_table()[w8].astype(np.float32) * sr[:, None]).astype(np.float32)
+    q, s, g = E.requant_nvfp4(torch.from_numpy(w8).cuda(), torch.from_numpy(sr).cuda())
+    q0, s0, g0 = oracle.nvfp4_quantize(f, search=False)
+
+    def no_signed_zero(codes):
+        """nibble 8 (-0) → 0: an FP8 code of -0, or +0 under a negative row scale, is -0.0 in fp32; the hardware converter keeps that
+        sign, the reference's numpy rule (sign = x < 0) drops it.  Both decode to zero."""
+        lo, hi = codes & 0xF, codes >> 4
+        return np.where(lo == 8, 0, lo) | (np.where(hi == 8, 0, hi) << 4)
+    assert np.array_equal(no_signed_zero(q.cpu().numpy()), no_signed_zero(q0)) and np.array_equal(s.cpu().numpy(), s0)
+    assert np.float32(g.item()).tobytes() == np.float32(g0).tobytes()
+    E.context().check_device()
+
+
 def test_a4_quant_bit_exact(E, oracle):
     rng = np.random.default_rng(5)
     x = oracle.bf16r(rng.normal(0, 1, (9, 512)).astype(np.float32))
