@@ -10,7 +10,10 @@ import re
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-LIB_PATH = HERE / "libhive_b200.so"
+import os as _os
+
+# HIVE_B200_LIB selects another build of the same library (the range-checked debug build libhive_b200_bounds.so)
+LIB_PATH = Path(_os.environ["HIVE_B200_LIB"]) if _os.environ.get("HIVE_B200_LIB") else HERE / "libhive_b200.so"
 HEADER = HERE.parent / "include" / "hive_b200.h"
 
 HB_OK = 0

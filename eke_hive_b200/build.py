@@ -1,6 +1,6 @@
 """Builds eke_hive_b200/libhive_b200.so from csrc/*.cu with nvcc for sm_100a (cross-compiles without a GPU).
 
-    python eke_hive_b200/build.py [--force] [--verbose]      (run as a script: importing the package needs the built library)
+    python eke_hive_b200/build.py [--force] [--verbose] [--bounds]      (run as a script: importing the package needs the built library)
 
 Objects are rebuilt only when their source or a header is newer; translation units compile in parallel.
 """
@@ -28,7 +28,14 @@ def _newest_header() -> float:
     return max(h.stat().st_mtime for h in hs)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, bounds: bool = False) -> Path:
+    """bounds=True: the range-checked debug library (every kernel compiled with -DHB_BOUNDS) as libhive_b200_bounds.so, objects in
+    build_bounds/; load it with HIVE_B200_LIB=<path> (see _lib.py)."""
+    global OUT, OBJ, FLAGS
+    if bounds:
+        OUT, OBJ = HERE / "libhive_b200_bounds.so", HERE / "build_bounds"
+        if "-DHB_BOUNDS" not in FLAGS:
+            FLAGS = FLAGS + ["-DHB_BOUNDS"]
     OBJ.mkdir(exist_ok=True)
     srcs = sorted(CSRC.glob("*.cu"))
     hdr = _newest_header()
@@ -62,5 +69,5 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    p = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    p = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, bounds="--bounds" in sys.argv)
     print(p)

@@ -119,7 +119,15 @@ int hb_check_device(hb_ctx* ctx, void* stream) {
   HB_CUDA(ctx, cudaMemcpyAsync(&v, ctx->dev_err, 4, cudaMemcpyDeviceToHost, as_stream(stream)));
   HB_CUDA(ctx, cudaStreamSynchronize(as_stream(stream)));
   if (v == 0) return HB_OK;
+  uint32_t site[2] = {0u, 0u};
+  if (v & 0x80000000u) {                                                       // a range check of the debug build: which one, and the value it saw
+    HB_CUDA(ctx, cudaMemcpyAsync(site, ctx->dev_err + kErrBoundSite, 8, cudaMemcpyDeviceToHost, as_stream(stream)));
+    HB_CUDA(ctx, cudaMemsetAsync(ctx->dev_err + kErrBoundSite, 0, 8, as_stream(stream)));
+    HB_CUDA(ctx, cudaStreamSynchronize(as_stream(stream)));
+  }
   HB_CUDA(ctx, cudaMemsetAsync(ctx->dev_err, 0, 4, as_stream(stream)));
+  if (v & 0x80000000u)
+    return hb_fail(ctx, HB_ERR_DEVICE_FLAG, "device error word 0x%x: range check 0x%x failed with value %d (debug build)", v, site[0], (int)site[1]);
   return hb_fail(ctx, HB_ERR_DEVICE_FLAG, "device error word 0x%x (bits 0x1-0x80: a pipeline wait inside a decode or prefill kernel; 0x400-0x2000: the decode layer kernel's tables and grid barrier; "
                  "0x40000: rows of another rank did not arrive; 0x80000: partial sums of another rank did not arrive; 0x400000: an expert record outside the tensor maps' range)", v);
 }

@@ -15,7 +15,8 @@
 // Words of the context's 256-byte device block besides the error word [0]: [16] a counter the decode prep kernel owns, [17] the
 // poll limit of waits on flags that other ranks set (hb_config.wait_polls), [18..19] counters of the prefill plan kernel.
 constexpr int kErrWaitPolls = 17;
-constexpr int kErrPlanMeet = 18;      // [18], [19]: the meeting counters of the prefill plan kernel
+constexpr int kErrPlanMeet = 18;
+constexpr int kErrBoundSite = 20;     // [20], [21]: first failed range check of a -DHB_BOUNDS build (site code, offending value)      // [18], [19]: the meeting counters of the prefill plan kernel
 
 struct hb_ctx {
   int device = 0;
@@ -161,6 +162,22 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+// Range checks of the debug build (compile with -DHB_BOUNDS: `python eke_hive_b200/build.py --bounds`).  HB_BOUND(err, cond, site, value)
+// is `true` in the normal build.  In the debug build a failed check sets bit 31 of the context's error word, records the first
+// failing site and value in the words behind it, and evaluates to false so that the caller skips the access: a wrong index becomes
+// an HB_ERR_DEVICE_FLAG from hb_check_device instead of a memory fault.
+#ifdef HB_BOUNDS
+__device__ __forceinline__ bool hb_bound_check(uint32_t* err, bool ok, uint32_t site, long long value) {
+  if (!ok && err) {
+    atomicOr(err, 0x80000000u);
+    if (atomicCAS(err + kErrBoundSite, 0u, site) == 0u) err[kErrBoundSite + 1] = (uint32_t)value;
+  }
+  return ok;
+}
+#define HB_BOUND(err, cond, site, value) (hb::hb_bound_check((err), (cond), (site), (long long)(value)))
+#else
+#define HB_BOUND(err, cond, site, value) (true)
+#endif
 __device__ __forceinline__ void named_bar_sync(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 
 // two e2m1 codes (one byte: low nibble = first element) → half2, exact

@@ -132,7 +132,9 @@ __global__ void __launch_bounds__(kGroupThreads) moe_group_kernel(GroupArgs a) {
     const int c = fill[k];
     if (c == 0) continue;
     const uint8_t* rec = routed ? (k == a.E ? a.shared_rec : a.tab[(size_t)a.li * a.E + k]) : recs[k];
-    for (int j = 0; j * kGroupRows < c; ++j) a.ws.groups[ngr[k] + j] = Group{rec, cnt[k] + j * kGroupRows, min(kGroupRows, c - j * kGroupRows)};
+    for (int j = 0; j * kGroupRows < c; ++j)
+      if (HB_BOUND(a.wait_err, ngr[k] + j >= 0 && ngr[k] + j < P, 0x101u, ngr[k] + j))
+        a.ws.groups[ngr[k] + j] = Group{rec, cnt[k] + j * kGroupRows, min(kGroupRows, c - j * kGroupRows)};
   }
   __syncthreads();
   for (int k = threadIdx.x; k < NK; k += blockDim.x) fill[k] = 0;
@@ -141,7 +143,7 @@ __global__ void __launch_bounds__(kGroupThreads) moe_group_kernel(GroupArgs a) {
   for (int i = threadIdx.x; i < P; i += blockDim.x) {
     const int kk = key[i];
     int pos = -1;
-    if (kk >= 0) { pos = cnt[kk] + atomicAdd(&fill[kk], 1); a.ws.s_row[pos] = a.ws.prow[i]; }
+    if (kk >= 0) { pos = cnt[kk] + atomicAdd(&fill[kk], 1); if (HB_BOUND(a.wait_err, pos >= 0 && pos < P, 0x102u, pos)) a.ws.s_row[pos] = a.ws.prow[i]; }
     a.ws.pos_of[i] = pos;
   }
   for (int i = threadIdx.x; i < P; i += blockDim.x) a.ws.done[i] = 0;
@@ -200,6 +202,7 @@ __device__ __forceinline__ void moe_stream_roles(const StreamArgs& a) {
       int cur = -1;
       for (; issued < n_items; ++issued) {
         if (!mbar_wait(&empty[s], ph ^ 1u, a.err, 1u)) break;
+        if (!HB_BOUND(a.err, gi >= 0 && gi < n_groups && tile < tiles, 0x113u, gi)) break;
         if (gi != cur) { g = a.groups[gi]; cur = gi; }
         uint8_t* st = ring + (size_t)s * C::STAGE;
         mbar_expect_tx(&full[s], C::TX);
@@ -228,7 +231,8 @@ __device__ __forceinline__ void moe_stream_roles(const StreamArgs& a) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int tok = tok0 + (c & 1), n = n0 + (c >> 1) * 8;
-        if (tok < grp.n) a.outp[(size_t)(grp.start + tok) * a.H + n] = __float2bfloat16(acc[c] * gl[2]);
+        if (tok < grp.n && HB_BOUND(a.err, grp.start + tok >= 0 && grp.start + tok < a.hdr[1] && n < a.H, 0x111u, grp.start + tok))
+          a.outp[(size_t)(grp.start + tok) * a.H + n] = __float2bfloat16(acc[c] * gl[2]);
       }
     } else {
       float oth[4];
@@ -243,7 +247,8 @@ __device__ __forceinline__ void moe_stream_roles(const StreamArgs& a) {
         if (a.limit > 0.f) { uv = fminf(fmaxf(uv, -a.limit), a.limit); gv = fminf(gv, a.limit); }
         const float yv = gv / (1.f + __expf(-gv)) * uv;
         const int tok = tok0 + c;
-        if (tok < grp.n) a.outp[(size_t)(grp.start + tok) * a.I + i] = __float2bfloat16(yv);
+        if (tok < grp.n && HB_BOUND(a.err, grp.start + tok >= 0 && grp.start + tok < a.hdr[1] && i < a.I, 0x112u, grp.start + tok))
+          a.outp[(size_t)(grp.start + tok) * a.I + i] = __float2bfloat16(yv);
       }
     }
   };
@@ -595,7 +600,7 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
     if (routed) {
       ReduceArgs ra{w.part, w.pos_of, w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
                     reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), ga.sh_row0, ga.sh_rows,
-                  red.ep ? *red.ep : hbk_ep_push{}};
+                  red.ep ? *red.ep : hbk_ep_push{}, ctx->dev_err, P};
       return hbk_moe_fused_launch(ctx, w, x, H, I, limit, L, &ra, st);
     }
     if ((r = hbk_moe_fused_launch(ctx, w, x, H, I, limit, L, nullptr, st))) return r;
@@ -623,7 +628,7 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
       sd.red_on = 1; sd.fin = reinterpret_cast<unsigned int*>(w.hdr + 3);
       sd.red = ReduceArgs{w.part, w.pos_of, w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
                           reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), ga.sh_row0, ga.sh_rows,
-                          hbk_ep_push{}};
+                          hbk_ep_push{}, ctx->dev_err, P};
       return hb_launch(ctx, "moe_down_reduce", true, kd.fn, dim3(grid), dim3(kd.threads), kd.smem(s), st, sd);
     }
     if ((r = hb_launch(ctx, "moe_down", true, kd.fn, dim3(grid), dim3(kd.threads), kd.smem(s), st, sd))) return r;
@@ -635,7 +640,7 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
   if (routed) {
     ReduceArgs ra{w.part, w.pos_of, w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
                   reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), ga.sh_row0, ga.sh_rows,
-                  red.ep ? *red.ep : hbk_ep_push{}};
+                  red.ep ? *red.ep : hbk_ep_push{}, ctx->dev_err, P};
     return hb_launch(ctx, "moe_reduce_routed", true, moe_reduce_routed_kernel, dim3((unsigned)(((size_t)src.M * H / 2 + 255) / 256)), dim3(256), 0, st, ra);
   }
   return hb_launch(ctx, "moe_reduce_list", true, moe_reduce_list_kernel, dim3((H / 2 + 255) / 256, P), dim3(256), 0, st, (const __nv_bfloat16*)w.part,

@@ -954,7 +954,7 @@ int hbk_moe_dtc_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int H, 
   if (r) return r;
   const int sh_row0 = src.sh_row0, sh_rows = src.sh_rows < 0 ? M : src.sh_rows;
   ReduceArgs ra{w.part, w.pos_of, w.pw, M, K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
-                reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), sh_row0, sh_rows, hbk_ep_push{}};
+                reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), sh_row0, sh_rows, hbk_ep_push{}, ctx->dev_err, P};
   DtPrepArgs pa{};
   pa.route = src.route; pa.logits = src.logits; pa.ld = src.ld; pa.renorm = src.renorm; pa.logits_bf16 = src.logits_bf16; pa.bias = src.bias;
   pa.sig_scale = src.sig_scale; pa.ids = const_cast<int32_t*>(src.ids); pa.w = const_cast<float*>(src.w); pa.ld_ids = src.ld_ids ? src.ld_ids : K;

@@ -276,6 +276,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
         const float* g = reinterpret_cast<const float*>(a.tab[tl.expert] + a.L.g);
         if (MODE == PF_GU) { f0 = a.ag[slot]; f1 = g[0]; f2 = g[1]; orow = (size_t)slot; }
         else { f0 = a.ag[slot] * g[2]; orow = (size_t)a.perm[slot]; }
+        HB_BOUND(a.err, tl.expert >= 0 && tl.rows >= 1 && tl.rows <= PF_BM && tl.slot0 >= 0, 0x202u, tl.slot0);
       }
       if (!(ok = mbar_wait(acc_full, tcount & 1, a.err, 0x1000u))) break;
       tc_fence_after();
@@ -453,7 +454,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) pf_plan_kernel(const PlanArgs a)
   for (int p = p0 + t; p < p1; p += PLAN_THREADS) {
     const int e = expert_of(p);
     int pos = -1;
-    if (e >= 0) { pos = atomicAdd(&cur[e], 1); a.perm[pos] = p; }
+    if (e >= 0) { pos = atomicAdd(&cur[e], 1); if (HB_BOUND(a.err, pos >= 0 && pos < a.P, 0x201u, pos)) a.perm[pos] = p; }
     a.pos_of[p] = pos;
   }
 }

@@ -51,6 +51,7 @@ struct ReduceArgs {
   __nv_bfloat16* out_bf16; float* out_f32;
   __nv_bfloat16* shared_out = nullptr; int sh_row0 = 0, sh_rows = 0;   // fp32 form: the shared expert's output rows, written apart
   hbk_ep_push ep = {};                            // ep.world > 0: the routed sums go to the owning ranks' partial buffers
+  uint32_t* err = nullptr; int n_pos = 0;         // debug build (-DHB_BOUNDS): the context's error word and the number of positions of `part`
 };
 
 struct StreamArgs {
@@ -211,6 +212,7 @@ __device__ __forceinline__ void reduce_routed_unit(const ReduceArgs& r, size_t i
       raw[k] = 0u; wv[k] = 0.f; ps[k] = -1;
       if (k0 + k < r.K) {
         ps[k] = r.pos_of[m * r.K + k0 + k];
+        if (ps[k] >= 0 && !HB_BOUND(r.err, ps[k] < r.n_pos, 0x121u, ps[k])) ps[k] = -1;
         if (ps[k] >= 0) { wv[k] = r.pw[m * r.K + k0 + k]; raw[k] = __ldcg(reinterpret_cast<const unsigned int*>(r.part + (size_t)ps[k] * r.H + d)); }
       }
     }

@@ -20,6 +20,18 @@ def test_library_exports_every_declared_symbol(lib):
         assert hasattr(L, n), n
 
 
+def test_debug_library_exports_the_same_symbols(lib):
+    """The range-checked debug build (-DHB_BOUNDS, `python eke_hive_b200/build.py --bounds`) is the same library: when it has been
+    built it exports every declared symbol too."""
+    from pathlib import Path
+    p = Path(lib.__file__).resolve().parent / "libhive_b200_bounds.so"
+    if not p.exists():
+        pytest.skip("debug library not built")
+    L = C.CDLL(str(p))
+    for n in lib.declared_symbols():
+        assert hasattr(L, n), n
+
+
 def test_pair_struct_matches_reference_abi(lib):
     # hive::glm::MoePair {int row; const uint8_t* rec; float w;} on LP64: 24 bytes, rec at 8, w at 16
     assert C.sizeof(lib.MoePair) == 24 and lib.MoePair.rec.offset == 8 and lib.MoePair.w.offset == 16
