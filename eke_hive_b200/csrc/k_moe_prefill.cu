@@ -40,7 +40,7 @@ constexpr int PF_STAGE = PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + PF_SFB_BYTES;
 constexpr int PF_STG_PITCH = 144;        // epilogue staging: 32 rows × 128 bytes per warp, rows padded to 144 bytes (conflict-free 16-byte accesses)
 constexpr int PF_STG_BYTES = 32 * PF_STG_PITCH;
 constexpr int PF_SMEM = PF_ST * PF_STAGE + 1024 + 512 + 8 * PF_STG_BYTES;
-constexpr int PF_THREADS = 15 * 32;     // warps 0-3 and 10-13 epilogue, 4 MMA issue, 5 TMA, 6-9 scale transposition, 14 scale copies into tensor memory
+constexpr int PF_THREADS = 14 * 32;     // warps 0-3 and 10-13 epilogue, 4 MMA issue, 5 TMA, 6-9 scales (global → tensor memory)
 constexpr int PF_TMEM_COLS = 512;
 constexpr int PF_SF_COL0 = 256;         // accumulator: columns [0, 256); scales of stage s: [256 + 48 s, 256 + 48 s + 48)
 static_assert(PF_SF_COL0 + 48 * PF_ST <= PF_TMEM_COLS, "tensor memory");
@@ -111,11 +111,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
   uint64_t* acc_full = empty + PF_ST;                                        // the tile's accumulators are complete
   uint64_t* acc_empty = acc_full + 1;                                        // the epilogue has read them
   uint64_t* mma_done = acc_empty + 1;                                        // the issuing thread's last operation has retired
-  uint64_t* sf_tm = mma_done + 1;                                              // [ST] the stage's scales are in tensor memory
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_tm + PF_ST);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mma_done + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < PF_ST; ++s) { mbar_init(&full[s], 128 + 1); mbar_init(&empty[s], 1); mbar_init(&sf_tm[s], 1); }   // full: 128 scale threads + the TMA thread
+    for (int s = 0; s < PF_ST; ++s) { mbar_init(&full[s], 128 + 1); mbar_init(&empty[s], 1); }   // full: 128 scale threads (scales are in tensor memory) + the TMA thread
     mbar_init(acc_full, 1); mbar_init(acc_empty, 256); mbar_init(mma_done, 1);
     mbar_fence_init();
   }
@@ -156,12 +155,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
       }
     }
   } else if (warp >= 6 && warp < 10) {
-    // ------------------------------------------------------------------------------------------------ scale loaders: thread lt owns row lt of each 128-row block
-    // A row's 16 scale bytes of a stage = 4 MMA k-steps × 4 scales.  tcgen05.cp wants, per k-step, 32 rows × 16 bytes where row l holds
-    // the 4 scales of rows l, l + 32, l + 64, l + 96: each thread loads its three rows (A block, two B blocks) two stages ahead
-    // into registers and stores them as 4-byte words into the transposed places.
-    const int lt = threadIdx.x - 192;
-    const uint32_t dst = (uint32_t)((lt & 31) * 16 + (lt >> 5) * 4);
+    // ------------------------------------------------------------------------------------------------ scales: thread lt owns row lt of each 128-row block
+    // A row's 16 scale bytes of a stage = 4 MMA k-steps × 4 scales (one 32-bit word per k-step).  The tensor core reads the scales
+    // from tensor memory: for the A rows of lane quarter q, word j of row 32 q + l from lane l, column 4 j + q; for the B rows, word j
+    // of row 32 c + l (c = 0..7) from lane l, column 16 + 8 j + c, of EVERY quarter.  Each thread fetches its three rows (A block, two
+    // B blocks) two stages ahead into registers, drops them row-major into the stage's shared-memory slab (consecutive threads,
+    // consecutive 16 bytes: no bank conflicts), and after a barrier among the four warps picks up the eight B rows its own lane needs and
+    // stores everything into its own lane of tensor memory with two tcgen05.st — no tcgen05.cp on the MMA pipe, no transposition.
+    const int q = warp & 3, l = lane, lt = 32 * q + l;                      // a warp reaches the tensor-memory lanes of quarter (warp index mod 4): its rows are those
+    const uint32_t sf_lane = tmem + ((uint32_t)(q * 32) << 16);
     const size_t rows = (size_t)a.Kd / 16;
     uint32_t it = 0;
     bool ok = true;
@@ -198,13 +200,31 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
         const uint32_t stage = it % PF_ST;
         uint4 fa = make_uint4(0, 0, 0, 0), fb = fa, fc = fa;
         fetch(fa, fb, fc);                                                   // the latency of these loads is never waited for
-        if (!(ok = mbar_wait(&empty[stage], ((it / PF_ST) & 1) ^ 1, a.err, 0x4000u))) break;
-        uint32_t* o = reinterpret_cast<uint32_t*>(sm + stage * PF_STAGE + PF_A_BYTES + PF_B_BYTES + dst);
-        o[0] = va.x; o[128] = va.y; o[256] = va.z; o[384] = va.w;            // k-step j of a block sits 512 bytes after k-step j - 1
-        o[512] = vb.x; o[640] = vb.y; o[768] = vb.z; o[896] = vb.w;
-        o[1024] = vc.x; o[1152] = vc.y; o[1280] = vc.z; o[1408] = vc.w;
-        fence_proxy_async_smem();
-        mbar_arrive(&full[stage]);
+        if (!(ok = mbar_wait(&empty[stage], ((it / PF_ST) & 1) ^ 1, a.err, 0x4000u))) break;   // the MMAs that read the stage's slab and scale columns are done
+        tc_fence_after();
+        uint4* slab = reinterpret_cast<uint4*>(sm + stage * PF_STAGE + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES);   // B scales, row-major: [256][16 bytes]
+        slab[lt] = vb; slab[128 + lt] = vc;
+        named_bar_sync(5, 128);
+        uint32_t wa[16], wb[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) wa[i] = 0u;
+        const uint32_t va4[4] = {va.x, va.y, va.z, va.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+          for (int qq = 0; qq < 4; ++qq) if (qq == q) wa[4 * j + qq] = va4[j];
+        }
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 r4 = slab[32 * c + l];
+          wb[c] = r4.x; wb[8 + c] = r4.y; wb[16 + c] = r4.z; wb[24 + c] = r4.w;
+        }
+        const uint32_t sfc = sf_lane + PF_SF_COL0 + stage * 48;
+        tc_st16(sfc, wa);
+        tc_st32(sfc + 16, wb);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&full[stage]);                                           // (the slab is not written again before every thread has arrived here: the MMAs wait for all)
         va = na; vb = nb; vc = nc; na = fa; nb = fb; nc = fc;
       }
     }
@@ -221,8 +241,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
           if (!(ok = mbar_wait(&full[stage], (it / PF_ST) & 1, a.err, 0x400u))) break;
           tc_fence_after();
           const uint32_t sb = base + stage * PF_STAGE, sfc = tmem + PF_SF_COL0 + stage * 48;
-          if (!(ok = mbar_wait(&sf_tm[stage], (it / PF_ST) & 1, a.err, 0x100000u))) break;     // the copy warp has put the scales into tensor memory
-          tc_fence_after();
           const uint64_t ad = tc_desc_sw128(sb), bd = tc_desc_sw128(sb + PF_A_BYTES);
 #pragma unroll
           for (uint32_t j = 0; j < 4; ++j)                                   // 64 k values = 32 bytes further along the swizzled row
@@ -233,27 +251,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
       }
       tc_commit(mma_done);                                                   // nothing of this thread's is in flight when tensor memory is freed
       mbar_wait(mma_done, 0, a.err, 0x800u);
-    }
-  } else if (warp == 14) {
-    // ------------------------------------------------------------------------------------------------ scale copies: one thread, ahead of the MMA thread
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (long long w = blockIdx.x; w < work && ok; w += gridDim.x) {
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const uint32_t stage = it % PF_ST;
-          if (!(ok = mbar_wait(&full[stage], (it / PF_ST) & 1, a.err, 0x200000u))) break;
-          tc_fence_after();
-          const uint32_t sb = base + stage * PF_STAGE, sfc = tmem + PF_SF_COL0 + stage * 48;
-#pragma unroll
-          for (uint32_t j = 0; j < 4; ++j) {
-            tc_cp_sf(sfc + 4 * j, tc_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + j * 512));
-            tc_cp_sf(sfc + 16 + 8 * j, tc_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + j * 512));
-            tc_cp_sf(sfc + 16 + 8 * j + 4, tc_desc_sf(sb + PF_A_BYTES + PF_B_BYTES + PF_SFA_BYTES + 2048 + j * 512));
-          }
-          tc_commit(&sf_tm[stage]);
-        }
-      }
     }
   } else if (warp < 4 || (warp >= 10 && warp < 14)) {
     // ------------------------------------------------------------------------------------------------ epilogue: a warp reads the 32 lanes of its quarter (warp index mod 4);
@@ -276,7 +273,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_gemm_kernel(const PfGemmArgs
         const float* g = reinterpret_cast<const float*>(a.tab[tl.expert] + a.L.g);
         if (MODE == PF_GU) { f0 = a.ag[slot]; f1 = g[0]; f2 = g[1]; orow = (size_t)slot; }
         else { f0 = a.ag[slot] * g[2]; orow = (size_t)a.perm[slot]; }
-        HB_BOUND(a.err, tl.expert >= 0 && tl.rows >= 1 && tl.rows <= PF_BM && tl.slot0 >= 0, 0x202u, tl.slot0);
+        (void)HB_BOUND(a.err, tl.expert >= 0 && tl.rows >= 1 && tl.rows <= PF_BM && tl.slot0 >= 0, 0x202u, tl.slot0);
       }
       if (!(ok = mbar_wait(acc_full, tcount & 1, a.err, 0x1000u))) break;
       tc_fence_after();
