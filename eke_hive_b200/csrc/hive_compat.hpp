@@ -34,7 +34,21 @@ inline hb_ctx* ctx() {
   }
   return c[dev];
 }
+// A second context per device whose hb_moe_prefill keeps bf16 activations (W4A16, the reference's default prefill arithmetic).
+inline hb_ctx* ctx_a16() {
+  static thread_local hb_ctx* c[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!c[dev]) {
+    hb_config cfg{dev, 0, (int)HB_FLAG_PREFILL_A16, 0};
+    const int st = hb_create(&cfg, &c[dev]);
+    if (st != HB_OK) throw Error(st, std::string("hb_create: ") + hb_status_string(st));
+  }
+  return c[dev];
+}
+inline bool& prefill_a4_flag() { static bool on = false; return on; }   // the reference's default: bf16 activations (fn_moe.h:50-52)
 inline void check(int st) { if (st != HB_OK) throw Error(st, hb_last_error(ctx())); }
+inline void check_on(hb_ctx* c, int st) { if (st != HB_OK) throw Error(st, hb_last_error(c)); }
 }  // namespace hive::b200
 
 namespace hive::glm {
@@ -99,19 +113,19 @@ inline void fn_moe_decode_routed(const glm::ExpertRecLayout&, const int32_t* ids
   hb_pf_combine c{shared, lg, ld, col, out};
   b200::check(hb_moe_decode_routed(b200::ctx(), ids, w, M, K, rec_tab, li, E, x, H, I, 0.f, &c, ws, st));
 }
-// Prefill (engine/include/hive/qwen/fn_moe.h:46-61).  This library's grouped GEMM is the NVFP4-activation form (the reference's
-// fn_moe_prefill_set_a4(true)); fn_moe_prefill_a4() therefore reports true and the setter refuses false.
+// Prefill (engine/include/hive/qwen/fn_moe.h:46-61).  As in the reference, bf16 activations (W4A16) are the default and
+// fn_moe_prefill_set_a4(true) opts in to NVFP4 activations (W4A4, the block-scaled tensor-core grouped GEMM).  The W4A16 form here
+// runs the decode operators over sub-chunks of rows: the reference's numbers, at decode-kernel speed.
 inline bool fn_moe_prefill_supported(int H, int I) { return hb_moe_prefill_supported(H, I) > 0; }
-inline bool fn_moe_prefill_a4() { return true; }
-inline void fn_moe_prefill_set_a4(bool on) {
-  if (!on) throw b200::Error(HB_ERR_UNSUPPORTED, "fn_moe_prefill: only the NVFP4-activation (W4A4) grouped GEMM is built; use the decode operators for bf16 activations");
-}
+inline bool fn_moe_prefill_a4() { return b200::prefill_a4_flag(); }
+inline void fn_moe_prefill_set_a4(bool on) { b200::prefill_a4_flag() = on; }
 inline size_t fn_moe_prefill_ws_bytes(int S, int K, int E, int H, int I) { return hb_moe_prefill_ws_bytes(S, K, E, H, I); }
 inline void fn_moe_prefill(const glm::ExpertRecLayout&, const uint8_t* const* tab, int li, int E, const int32_t* ids, const float* w, int M, int K,
                            const __nv_bfloat16* x, int H, int I, float* out, void* ws, int S, cudaStream_t st, const FnPfCombine* cmb = nullptr) {
   hb_pf_combine c{};
   if (cmb) c = hb_pf_combine{cmb->shared, cmb->lg, cmb->ld, cmb->col, cmb->out};
-  b200::check(hb_moe_prefill(b200::ctx(), tab, li, E, ids, w, M, K, x, H, I, 0.f, out, ws, S, st, cmb ? &c : nullptr));
+  hb_ctx* hc = b200::prefill_a4_flag() ? b200::ctx() : b200::ctx_a16();
+  b200::check_on(hc, hb_moe_prefill(hc, tab, li, E, ids, w, M, K, x, H, I, 0.f, out, ws, S, st, cmb ? &c : nullptr));
 }
 inline void router_softmax_topk(const float* logits, int ld, int M, int E, int k, bool renorm, int32_t* ids, float* w, int32_t* ids_host, float* w_host,
                                 cudaStream_t st) {
