@@ -339,14 +339,22 @@ def run_ours(args):
                 dist.barrier()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            marks = [torch.cuda.Event(enable_timing=True) for _ in range(nsteps + 1)] if finish is None else None
             e0.record()
             for i in range(nsteps):
+                if marks:
+                    marks[i].record()
                 fn(i)
+            if marks:
+                marks[nsteps].record()
             if finish:
                 finish()
             e1.record()
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1)
+            if marks:                                            # the spread over the timed steps (events between the steps cost nothing on the device)
+                per = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(nsteps))
+                timed.spread = {"min_ms": per[0], "median_ms": per[len(per) // 2], "max_ms": per[-1]}
             if world > 1:
                 t = torch.tensor([ms], dtype=torch.float64, device=dev)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -357,6 +365,7 @@ def run_ours(args):
             graphs[i % NSETS].replay()
         sampler.active = B == head_B
         ms = timed(args.steps, lambda i: graphs[i % NSETS].replay())
+        spread_B = getattr(timed, "spread", None)
         sampler.active = False
         ctx.check_device()
         ms_step = ms / args.steps
@@ -375,7 +384,7 @@ def run_ours(args):
         bytes_step = L * layer_algorithmic_bytes(H, I, Ex, K, B * world, u_total)
         results[B] = {"batch": B, "ms_per_step": ms_step, "us_per_layer": ms_step * 1e3 / L, "tokens_per_s": B * world * L / (ms_step * 1e-3),
                       "records_per_layer": u_total, "algorithmic_GB_per_step": bytes_step / 1e9, "achieved_GBps": bytes_step / (ms_step * 1e-3) / 1e9,
-                      "launches_per_step": launches_per_step}
+                      "launches_per_step": launches_per_step, "step_spread": spread_B}
 
         if B == head_B:
             # ---- end to end: pinned host inputs → H2D → layers → D2H of the outputs, every step

@@ -359,6 +359,17 @@ __global__ void __launch_bounds__(StreamCfg<WK, WM, DOWN>::THREADS, StreamCfg<WK
   __syncthreads();
   const size_t units = (size_t)a.red.M * a.red.H / 2, step = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < units; i += step) reduce_routed_unit(a.red, i);
+  if (a.red.ep.world > 0) {
+    // expert parallel: the sums were stored into the owning ranks' memory; when the last CTA is through, tell every rank
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(a.red.ep.done, 1u) == gridDim.x - 1) {
+      *a.red.ep.done = 0;
+      __threadfence_system();
+      const uint32_t stepno = *a.red.ep.step + 1u;
+      for (int p = 0; p < a.red.ep.world; ++p) st_release_sys(a.red.ep.flag[p] + a.red.ep.rank, stepno);
+    }
+  }
 }
 
 // ================================================================================================ reduce / combine
@@ -623,13 +634,13 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
     if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
     bool meet = false;
     for (int j = 0; j < 8; ++j) if (ctx->down_fn[j] == reinterpret_cast<const void*>(kd.fn)) meet = ctx->down_meet[j];
-    if (routed && !red.ep && meet) {
+    if (routed && meet) {
       // the down pass sums the rows' pairs itself (its CTAs meet at the end): no reduce launch
       sd.red_on = 1; sd.fin = reinterpret_cast<unsigned int*>(w.hdr + 3);
       sd.red = ReduceArgs{w.part, w.pos_of, w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
                           reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), ga.sh_row0, ga.sh_rows,
-                          hbk_ep_push{}, ctx->dev_err, P};
-      return hb_launch(ctx, "moe_down_reduce", true, kd.fn, dim3(grid), dim3(kd.threads), kd.smem(s), st, sd);
+                          red.ep ? *red.ep : hbk_ep_push{}, ctx->dev_err, P};
+      return hb_launch(ctx, red.ep ? "moe_down_reduce_push" : "moe_down_reduce", true, kd.fn, dim3(grid), dim3(kd.threads), kd.smem(s), st, sd);
     }
     if ((r = hb_launch(ctx, "moe_down", true, kd.fn, dim3(grid), dim3(kd.threads), kd.smem(s), st, sd))) return r;
   } else {
