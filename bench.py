@@ -434,7 +434,7 @@ def run_ours(args):
                    "overlap": "copies on a second stream: step i+1's upload and step i's download overlap compute; all inside the timed region"}
             # ---- per-kernel durations (library event pairs, PDL off, no graph) for the roofline of the dominant kernel
             prof = None
-            if world == 1:
+            if world == 1 or os.environ.get("BENCH_PROFILE_EP"):
                 ctx.profile(True)
                 nprof = max(1, min(args.steps, 8192 // (launches_per_step + 1)))
                 for i in range(nprof):
