@@ -76,10 +76,12 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
 
 // decode layer on the block-scaled tensor cores (k_moe_dtc.cu): routed form only, H and I multiples of 256
 bool hbk_moe_dtc_supported(int H, int I);
-bool hbk_moe_dtc_fits(const hb_ctx* ctx, int n_pairs, int E, int H, int I);   // the launch's work lists fit the CTAs' tables
+bool hbk_moe_dtc_gu_fits(const hb_ctx* ctx, int n_pairs, int E, int H, int I);
 size_t hbk_moe_dtc_ws_extra(int n_pairs, int H, int I);      // bytes it needs after the streaming path's workspace
 int hbk_moe_dtc_setup(hb_ctx* ctx);
-int hbk_moe_dtc_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int H, int I, float limit, const hbk_reduce& red, void* ws, cudaStream_t st);
+// gate/up pass alone on the tensor cores, between the streaming path's grouping kernel and its down kernel
+int hbk_moe_dtc_gu_run(hb_ctx* ctx, const void* x, int x_ld, int M, const uint8_t* const* tab, int n_tab, const uint8_t* shared_rec, int P, int H, int I,
+                       float limit, void* ws, bool rows_arrive_late, cudaStream_t st);
 
 // dense GEMV (k_dense.cu)
 int hbk_dense_setup(hb_ctx* ctx);

@@ -65,6 +65,7 @@ __device__ void block_scan2(int* a, int* b, int n, int* tot_a, int* tot_b, int* 
 __global__ void __launch_bounds__(kGroupThreads) moe_group_kernel(GroupArgs a) {
   extern __shared__ __align__(16) uint8_t gsm[];
   griddep_wait();
+  griddep_launch();                                     // what follows in the stream may start its prologue (each kernel waits for its own inputs)
   if (a.wait_flags) {                                   // the rows, ids and weights this pass reads are pushed by the other ranks
     if ((int)threadIdx.x < a.wait_n && !*reinterpret_cast<volatile uint32_t*>(a.wait_err))
       ep_wait_flag(a.wait_flags + threadIdx.x, *a.wait_step + 1u, a.wait_err, 0x40000u);
@@ -564,11 +565,6 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
   const bool routed = src.ids != nullptr;
   const int P = routed ? src.M * src.K + (src.shared_rec ? src.M : 0) : src.n_pairs;
   if (P <= 0) return HB_OK;
-  // routed form on a shape the tensor-memory layer kernel takes: two launches (prep, layer) instead of the streaming chain below
-  const bool want_tc = (ctx->flags & HB_FLAG_DECODE_TC) != 0;       // library default for now: the streaming chain
-  if (routed && want_tc && !src.ws_stream_only && !red.ep && !src.wait_flags && hbk_moe_dtc_supported(H, I) && !(ctx->flags & (HB_FLAG_FUSED | HB_FLAG_DECODE_MMA_SYNC)) &&
-      hbk_moe_dtc_fits(ctx, P, src.E, H, I))
-    return hbk_moe_dtc_run(ctx, src, x, H, I, limit, red, ws, st);
   DecodeWs w = carve(ws, P, H, I);
   hb_rec_layout L;
   hb_rec_layout_make(H, I, &L);
@@ -627,7 +623,13 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
     sa.stages = s;
     int grid = ctx->sm_count * c;
     if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
-    if ((r = hb_launch(ctx, "moe_gate_up", true, kg.fn, dim3(grid), dim3(kg.threads), kg.smem(s), st, sa))) return r;
+    const bool tc_gu = routed && (ctx->flags & (HB_FLAG_DECODE_TC_GU | HB_FLAG_DECODE_TC)) && !src.ws_stream_only && src.tab && hbk_moe_dtc_supported(H, I) &&
+                       hbk_moe_dtc_gu_fits(ctx, P, src.E, H, I);
+    if (tc_gu) {
+      // gate/up on the block-scaled tensor cores: digit planes of the rows (beside the grouping kernel), then the tensor-memory kernel
+      if ((r = hbk_moe_dtc_gu_run(ctx, x, x_ld, src.M, src.tab + (size_t)src.li * src.E, src.E, src.shared_rec, P, H, I, limit, ws, src.wait_flags != nullptr, st)))
+        return r;
+    } else if ((r = hb_launch(ctx, "moe_gate_up", true, kg.fn, dim3(grid), dim3(kg.threads), kg.smem(s), st, sa))) return r;
     plan_stream(ctx, kd, &s, &c);
     sd.stages = s;
     grid = ctx->sm_count * c;

@@ -82,6 +82,8 @@ struct DtDiv {
 };
 
 struct DtcArgs {
+  int gu_only;          // 1: only the gate/up items run, y leaves as bf16 rows [pos, I] (`y`) for the streaming down kernel; rows and units of a
+                       //    group come from s_row / xs (the streaming path's grouping kernel made the list)
   const int* hdr; const Group* groups; const int* s_row;
   int H, I; float limit;
   DtDiv dIT, dHT, dG;                                    // dividers by the items per group (gate/up, down) and by the grid size
@@ -258,23 +260,29 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
     mbar_fence_init();
   }
   if (warp == DT_W_MMA) { tmem_alloc(tmem_slot, DT_TMEM_COLS); tmem_relinquish(); }
+  // the first variant of each kind's tensor map (the only one when the pitch divides 4096) is made visible to the TMA thread before
+  // the wait: the maps were stamped by an earlier launch that has completed
+  if (threadIdx.x == DT_W_TMA * 32) { tmap_acquire(a.maps); tmap_acquire(a.maps + DT_VMAX); }
   griddep_wait();                                                               // the prep kernel's lists, digit planes and cleared flags
   griddep_launch();
   [[maybe_unused]] const long long t_k1 = clock64();
   const int nIT = a.I / DT_GU_ROWS, nHT = a.H / DT_DN_ROWS;
   DtList lst;
   lst.init(a.hdr[0], a.dIT, a.dHT, a.dG, a.H >> 8, a.I >> 8, (int)blockIdx.x);
-  int n_items = lst.total;
+  int n_items = a.gu_only ? lst.cntGU : lst.total;
   if (n_items > DT_TBL) { if (threadIdx.x == 0) atomicOr(a.err, 0x1000u); n_items = 0; }   // the launcher sizes the grid so that this does not happen
   for (int j = threadIdx.x; j < n_items * kGroupRows; j += DT_THREADS) {       // records, row ranges, activation rows and their digit units
     const int i = j >> 3, c = j & 7;
     const uint32_t info = lst.info(i);
-    const size_t gj = (size_t)(info >> 16) * kGroupRows + c;
-    tbl_row[j] = a.dw.g_row[gj]; tbl_unit[j] = a.dw.g_unit[gj];
-    if (c == 0) {
-      const Group g = a.groups[info >> 16];
-      tbl[i].rec = g.rec; tbl[i].start = g.start; tbl[i].info = info | ((uint32_t)g.n << 1);
+    const Group g = a.groups[info >> 16];
+    if (a.gu_only) {
+      const int row = c < g.n ? a.s_row[g.start + c] : 0;
+      tbl_row[j] = (uint16_t)row; tbl_unit[j] = 0.f;                            // the epilogue fetches the rows' units itself, off the start-up path
+    } else {
+      const size_t gj = (size_t)(info >> 16) * kGroupRows + c;
+      tbl_row[j] = a.dw.g_row[gj]; tbl_unit[j] = a.dw.g_unit[gj];
     }
+    if (c == 0) { tbl[i].rec = g.rec; tbl[i].start = g.start; tbl[i].info = info | ((uint32_t)g.n << 1); }
   }
   tc_fence_before();
   __syncthreads();
@@ -285,7 +293,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
   if (warp == DT_W_TMA) {
     // ------------------------------------------------------------------------------------------------ weight boxes: one thread
     if (lane == 0) {
-      uint32_t it = 0, seen[2] = {0u, 0u};
+      uint32_t it = 0, seen[2] = {1u, 1u};                                      // variant 0 of both kinds: acquired in the prologue
       bool ok = true;
       [[maybe_unused]] long long tw = 0, t_begin = clock64();
       const unsigned long long anchor[2] = {a.meta->anchor[0], a.meta->anchor[1]};
@@ -572,6 +580,11 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
       const int n = ent_n(e), kind = ent_kind(e), t = ent_t(e), g = ent_g(e);
       const float* gp = reinterpret_cast<const float*>(e.rec + a.L.g);
       const float gsc = __ldg(gp + (kind ? 2 : (tl < 64 ? 0 : 1)));               // the record's global scale this thread applies
+      float un[kGroupRows];
+      if (a.gu_only) {
+#pragma unroll
+        for (int c = 0; c < kGroupRows; ++c) un[c] = c < n ? __ldg(a.dw.xs + tbl_row[ii * kGroupRows + c]) : 0.f;
+      }
       DT_TIMED(ta, ok = mbar_wait(&acc_full[set], (ii >> 1) & 1, a.err, 0x80u));
       if (!ok) break;
       const float* units = rowsc + (ii & 15) * 8;
@@ -602,13 +615,17 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
 #pragma unroll
         for (int c = 0; c < kGroupRows; ++c) {
           gu[c] = 0.f;
-          if (c < n) gu[c] = bf16r(val[c] * units[c] * gsc);
+          if (c < n) gu[c] = bf16r(val[c] * (a.gu_only ? un[c] : units[c]) * gsc);
         }
         if (tl >= 64) {
 #pragma unroll
           for (int c = 0; c < kGroupRows; ++c) if (c < n) ex[c * 64 + (tl - 64)] = gu[c];
         }
         named_bar_sync(bar_id, 128);
+        float upv[kGroupRows];
+#pragma unroll
+        for (int c = 0; c < kGroupRows; ++c) upv[c] = (tl < 64 && c < n) ? ex[c * 64 + tl] : 0.f;
+        named_bar_sync(bar_id, 128);                                              // the up values are read: the item after next may overwrite them
         if (tl < 64) {
           // y = bf16(silu(g)·u) of the item's 64 values per row; its digit planes are taken against the largest exponent among the 64
           uint32_t yb[kGroupRows];
@@ -616,13 +633,16 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
           for (int c = 0; c < kGroupRows; ++c) {
             yb[c] = 0u;
             if (c < n) {
-              float gv = gu[c], uv = ex[c * 64 + tl];
+              float gv = gu[c], uv = upv[c];
               if (a.limit > 0.f) { uv = fminf(fmaxf(uv, -a.limit), a.limit); gv = fminf(gv, a.limit); }
-              yb[c] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16(gv / (1.f + __expf(-gv)) * uv));
+              const __nv_bfloat16 yv = __float2bfloat16(gv / (1.f + __expf(-gv)) * uv);
+              yb[c] = (uint32_t)__bfloat16_as_ushort(yv);
+              if (a.gu_only) { a.y[(size_t)(e.start + c) * a.I + t * DT_GU_ROWS + tl] = yv; continue; }   // 64 threads, 128 contiguous bytes per row
               const uint32_t am = __reduce_max_sync(0xffffffffu, yb[c] & 0x7fffu);
               if (lane == 0) flag[8 + (warp & 1) * 8 + c] = (int)am;
             }
           }
+          if (a.gu_only) continue;                                               // (uniform over the kernel) nothing is digitised: the down pass reads bf16
           named_bar_sync(3 + set, 64);
           int ebs[kGroupRows];
 #pragma unroll
@@ -664,6 +684,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
   __syncthreads();
   [[maybe_unused]] const long long t_k3 = clock64();
   if (warp == DT_W_MMA) { tc_fence_after(); tmem_dealloc(tmem, DT_TMEM_COLS); }
+  if (a.gu_only) return;                                                        // y is written; the streaming down kernel takes over
   // ---- every CTA's partial rows are written once all CTAs have come this far: then the k-order sums, one (row, 128 columns) block per
   // group of 64 threads
   if (threadIdx.x == 0) {
@@ -687,152 +708,37 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
   if (threadIdx.x == 0) { DT_TRACE_PUT(20, t_k1 - t_k0); DT_TRACE_PUT(21, t_k2 - t_k1); DT_TRACE_PUT(22, t_k3 - t_k2); DT_TRACE_PUT(23, t_k4 - t_k3); DT_TRACE_PUT(24, clock64() - t_k4); }
 }
 
-// ---- the prep kernel --------------------------------------------------------------------------------------------------------------------
-struct DtPrepArgs {
-  int route; const float* logits; int ld, renorm, logits_bf16; const float* bias; float sig_scale;
-  int32_t* ids; float* w; int ld_ids;
-  int M, K, E; const uint8_t* const* tab; int li; const uint8_t* shared_rec; int sh_row0, sh_rows;
-  const __nv_bfloat16* x; int x_ld; int H, I;
-  DecodeWs ws; DtcWs dw;
-  unsigned int* arrive;          // context-owned counter (zero between calls)
-};
-
-constexpr int DT_PREP_THREADS = 256;      // eight warps: the row's routing, then its digit planes
-
-__device__ void dt_block_scan2(int* a, int* b, int n, int* tot_a, int* tot_b, int* warp_tmp /* [2][32] */) {
-  const int nt = blockDim.x, per = (n + nt - 1) / nt;
-  const int i0 = min(n, (int)threadIdx.x * per), i1 = min(n, i0 + per);
-  int sa = 0, sb = 0;
-  for (int i = i0; i < i1; ++i) { sa += a[i]; sb += b[i]; }
-  int xa = sa, xb = sb;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = nt >> 5;
-  for (int o = 1; o < 32; o <<= 1) {
-    const int ta = __shfl_up_sync(0xffffffffu, xa, o), tb = __shfl_up_sync(0xffffffffu, xb, o);
-    if (lane >= o) { xa += ta; xb += tb; }
-  }
-  if (lane == 31) { warp_tmp[warp] = xa; warp_tmp[32 + warp] = xb; }
-  __syncthreads();
-  if (warp == 0) {
-    int va = lane < nw ? warp_tmp[lane] : 0, vb = lane < nw ? warp_tmp[32 + lane] : 0;
-    const int ia = va, ib = vb;
-    for (int o = 1; o < 32; o <<= 1) {
-      const int ta = __shfl_up_sync(0xffffffffu, va, o), tb = __shfl_up_sync(0xffffffffu, vb, o);
-      if (lane >= o) { va += ta; vb += tb; }
-    }
-    warp_tmp[lane] = va - ia; warp_tmp[32 + lane] = vb - ib;
-    if (lane == 31) { *tot_a = va; *tot_b = vb; }
-  }
-  __syncthreads();
-  int ba = warp_tmp[warp] + xa - sa, bb = warp_tmp[32 + warp] + xb - sb;
-  for (int i = i0; i < i1; ++i) { const int ca = a[i], cb = b[i]; a[i] = ba; b[i] = bb; ba += ca; bb += cb; }
-  __syncthreads();
-}
-
-__global__ void __launch_bounds__(DT_PREP_THREADS) moe_dtc_prep_kernel(const DtPrepArgs a) {
-  extern __shared__ __align__(16) uint8_t psm[];
+// The digit planes of the activation rows alone (the gate/up pass on the tensor cores behind the streaming path's grouping kernel):
+// one CTA per row.  It is launched right behind the grouping kernel, which triggers its dependents as soon as its own wait for the
+// stream's earlier work has returned — so the rows are final when this kernel starts, it runs beside the grouping, and it does its
+// own wait (for the grouping kernel to finish) LAST: the kernel behind it then finds both the planes and the group list complete.
+// wait_first: the rows themselves arrive during the grouping kernel (expert parallel: pushed by other ranks) — wait before reading.
+struct XdigArgs { const __nv_bfloat16* x; int x_ld, H; DtcWs dw; int wait_first; };
+__global__ void __launch_bounds__(256) moe_xdig_kernel(const XdigArgs a) {
   __shared__ int s_red[8];
-  __shared__ int s_last;
   const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  [[maybe_unused]] const long long t_p0 = clock64();
-  [[maybe_unused]] long long t_p1 = 0, t_p2 = 0;
-  griddep_wait();                                                               // logits and activations may come from the kernel before
+  if (a.wait_first) griddep_wait();
   griddep_launch();
-  if (a.route) {
-    // the row's routing: all eight warps (a two-level tournament, router.cuh)
-    int32_t my_id = 0;
-    float my_w = 0.f;
-    route_row_group(a.route, a.logits + (size_t)m * a.ld, a.bias, a.E, a.K, a.renorm, a.logits_bf16, a.sig_scale, reinterpret_cast<float*>(psm), 8, warp, lane, 1,
-                    my_id, my_w);
-    if (warp == 0 && lane < a.K) { a.ids[(size_t)m * a.K + lane] = my_id; a.w[(size_t)m * a.K + lane] = my_w; }
-    if (threadIdx.x == 0) DT_TRACE_PUT(25, clock64() - t_p0);
-  }
-  {
-    // digit planes of row m
-    const uint32_t* xr = reinterpret_cast<const uint32_t*>(a.x + (size_t)m * a.x_ld);
-    uint32_t am = 0;
-    for (int e2 = threadIdx.x; e2 < a.H / 2; e2 += 256) { const uint32_t w2 = __ldg(xr + e2); am = max(am, max(w2 & 0x7fffu, (w2 >> 16) & 0x7fffu)); }
-    for (int o = 16; o > 0; o >>= 1) am = max(am, __shfl_xor_sync(0xffffffffu, am, o));
-    if (lane == 0) s_red[warp] = (int)am;
-    __syncthreads();
+  const uint32_t* xr = reinterpret_cast<const uint32_t*>(a.x + (size_t)m * a.x_ld);
+  uint32_t am = 0;
+  for (int e2 = threadIdx.x; e2 < a.H / 2; e2 += 256) { const uint32_t w2 = __ldg(xr + e2); am = max(am, max(w2 & 0x7fffu, (w2 >> 16) & 0x7fffu)); }
+  for (int o = 16; o > 0; o >>= 1) am = max(am, __shfl_xor_sync(0xffffffffu, am, o));
+  if (lane == 0) s_red[warp] = (int)am;
+  __syncthreads();
 #pragma unroll
-    for (int i = 0; i < 8; ++i) am = max(am, (uint32_t)s_red[i]);
-    const int eb = dt_row_exponent(am);
-    if (threadIdx.x == 0) a.dw.xs[m] = dt_unit(eb);
-    for (int u = threadIdx.x; u < a.H / 8; u += 256) {
-      const uint4 q4 = __ldg(reinterpret_cast<const uint4*>(xr) + u);
-      const uint32_t v4[4] = {q4.x, q4.y, q4.z, q4.w};
-      uint32_t pl[8];
-      dt_digits8(v4, eb, pl);
+  for (int i = 0; i < 8; ++i) am = max(am, (uint32_t)s_red[i]);
+  const int eb = dt_row_exponent(am);
+  if (threadIdx.x == 0) a.dw.xs[m] = dt_unit(eb);
+  for (int u = threadIdx.x; u < a.H / 8; u += 256) {
+    const uint4 q4 = __ldg(reinterpret_cast<const uint4*>(xr) + u);
+    const uint32_t v4[4] = {q4.x, q4.y, q4.z, q4.w};
+    uint32_t pl[8];
+    dt_digits8(v4, eb, pl);
 #pragma unroll
-      for (int p = 0; p < 8; ++p) *reinterpret_cast<uint32_t*>(a.dw.xdig + dt_dig_off((size_t)m, a.H, u * 8, p)) = pl[p];
-    }
+    for (int p = 0; p < 8; ++p) *reinterpret_cast<uint32_t*>(a.dw.xdig + dt_dig_off((size_t)m, a.H, u * 8, p)) = pl[p];
   }
-  __syncthreads();
-  t_p1 = clock64();
-  if (threadIdx.x == 0) { __threadfence(); s_last = atomicAdd(a.arrive, 1u) == gridDim.x - 1 ? 1 : 0; }
-  __syncthreads();
-  t_p2 = clock64();
-  if (threadIdx.x == 0) { DT_TRACE_PUT(26, t_p1 - t_p0); DT_TRACE_PUT(27, t_p2 - t_p1); }
-  if (!s_last) return;
-  // ---- the last CTA: every row's ids and weights are written — sort the pairs by expert into groups of ≤ 8 rows
-  __threadfence();
-  if (threadIdx.x == 0) *a.arrive = 0u;
-  const int P = a.M * a.K + (a.shared_rec ? a.M : 0), NK = a.E + 1;
-  int* key = reinterpret_cast<int*>(psm);                  // [P]
-  int* cnt = key + P;                                      // [NK] → exclusive offsets
-  int* ngr = cnt + NK;                                     // [NK] → exclusive group bases
-  int* fill = ngr + NK;                                    // [NK]
-  int* misc = fill + NK;                                   // [66]
-  for (int k = threadIdx.x; k < NK; k += blockDim.x) { cnt[k] = 0; fill[k] = 0; }
-  __syncthreads();
-  for (int i = threadIdx.x; i < P; i += blockDim.x) {
-    int row, kk = -1;
-    float wv;
-    if (i < a.M * a.K) {
-      row = i / a.K;
-      const size_t src = (size_t)row * a.ld_ids + (i - row * a.K);
-      const int e = __ldcg(a.ids + src);
-      wv = __ldcg(a.w + src);
-      if (e >= 0 && e < a.E && a.tab[(size_t)a.li * a.E + e] != nullptr) kk = e;
-    } else { row = i - a.M * a.K; wv = 1.f; kk = row >= a.sh_row0 && row < a.sh_row0 + a.sh_rows ? a.E : -1; }
-    key[i] = kk; a.ws.prow[i] = row; a.ws.pw[i] = wv;
-    if (kk >= 0) atomicAdd(&cnt[kk], 1);
-  }
-  __syncthreads();
-  for (int k = threadIdx.x; k < NK; k += blockDim.x) { ngr[k] = (cnt[k] + kGroupRows - 1) / kGroupRows; fill[k] = cnt[k]; }
-  __syncthreads();
-  dt_block_scan2(cnt, ngr, NK, &misc[64], &misc[65], misc);
-  for (int k = threadIdx.x; k < NK; k += blockDim.x) {
-    const int c = fill[k];
-    if (c == 0) continue;
-    const uint8_t* rec = k == a.E ? a.shared_rec : a.tab[(size_t)a.li * a.E + k];
-    for (int j = 0; j * kGroupRows < c; ++j) a.ws.groups[ngr[k] + j] = Group{rec, cnt[k] + j * kGroupRows, min(kGroupRows, c - j * kGroupRows)};
-  }
-  __syncthreads();
-  for (int k = threadIdx.x; k < NK; k += blockDim.x) fill[k] = 0;
-  __syncthreads();
-  // positions inside an expert's run: any order gives the same results (the columns of a tile are independent); the shared expert's
-  // rows keep their order.  Each position is also entered, with its row's digit unit, in the per-group arrays the layer kernel
-  // builds its work table from.
-  for (int i = threadIdx.x; i < P; i += blockDim.x) {
-    const int kk = key[i];
-    int pos = -1;
-    if (kk >= 0) {
-      const int row = i < a.M * a.K ? i / a.K : i - a.M * a.K;
-      const int slot = kk == a.E ? row - a.sh_row0 : atomicAdd(&fill[kk], 1);
-      pos = cnt[kk] + slot;
-      a.ws.s_row[pos] = row;
-      const size_t gj = (size_t)(ngr[kk] + (slot >> 3)) * kGroupRows + (slot & 7);
-      a.dw.g_row[gj] = (uint16_t)row;
-      a.dw.g_unit[gj] = __ldcg(a.dw.xs + row);
-    }
-    a.ws.pos_of[i] = pos;
-    a.ws.done[i] = 0;
-    for (int w = 0; w < (((a.I / DT_GU_ROWS) + 7) >> 3) * 2; ++w) reinterpret_cast<uint32_t*>(a.dw.yexp)[(size_t)i * ((((a.I / DT_GU_ROWS) + 7) >> 3) * 2) + w] = 0u;
-  }
-  if (threadIdx.x == 0) { a.ws.hdr[0] = misc[65]; a.ws.hdr[1] = misc[64]; a.ws.hdr[2] = 0; *a.dw.fin = 0u; }
-  __syncthreads();
-  if (threadIdx.x == 0) g_dt_trace_prep_put(clock64() - t_p2);
+  fence_proxy_async_global();                                                  // the planes are read through the async proxy (bulk copies) by the next kernel
+  if (!a.wait_first) griddep_wait();
 }
 
 // Stamps the anchored bases into the tensor-map variants of both matrix kinds (one block; runs when the maps are first needed).
@@ -888,22 +794,18 @@ bool hbk_moe_dtc_supported(int H, int I) {
   return p0 / gcd_int(p0, 4096) <= DT_VMAX && p1 / gcd_int(p1, 4096) <= DT_VMAX;
 }
 
-// whether every CTA's work list fits its table for any routing of P pairs over E experts (+ the shared expert)
-bool hbk_moe_dtc_fits(const hb_ctx* ctx, int P, int E, int H, int I) {
+// the gate/up-only form: a CTA's list holds its share of the gate/up items
+bool hbk_moe_dtc_gu_fits(const hb_ctx* ctx, int P, int E, int H, int I) {
   int grid = ctx->sm_count;
   if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
-  const long long G = P < E + 1 + P / kGroupRows ? P : E + 1 + P / kGroupRows;          // groups: at most one partly filled group per expert
-  // a CTA takes at most its gate/up items plus down items up to the mean number of stages, plus one pass of what is left
-  const long long gu = (G * (I / DT_GU_ROWS) + grid - 1) / grid, stages = (G * (I / DT_GU_ROWS) * (H >> 8) + G * (H / DT_DN_ROWS) * (I >> 8)) / grid;
-  const long long items = gu + stages / (I >> 8) + (G * (H / DT_DN_ROWS) + grid - 1) / grid + 16;
-  return items <= DT_TBL;
+  const long long G = P < E + 1 + P / kGroupRows ? P : E + 1 + P / kGroupRows;
+  return (G * (I / DT_GU_ROWS) + grid - 1) / grid <= DT_TBL;
 }
 
 size_t hbk_moe_dtc_ws_extra(int n, int H, int I) { return hbk_moe_dtc_supported(H, I) ? dtc_carve(nullptr, 0, n, H, I, nullptr) : 0; }
 
 int hbk_moe_dtc_setup(hb_ctx* ctx) {
   HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_dtc_layer_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM));
-  HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_dtc_prep_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
   HB_CUDA(ctx, cudaMalloc(&ctx->dtc_maps, (size_t)2 * DT_VMAX * sizeof(CUtensorMap) + 256));
   HB_CUDA(ctx, cudaMemset(ctx->dtc_maps, 0, (size_t)2 * DT_VMAX * sizeof(CUtensorMap) + 256));
   return HB_OK;
@@ -942,38 +844,28 @@ extern "C" __attribute__((visibility("default"))) int hb_dtc_stage_read(long lon
 }
 #endif
 
-int hbk_moe_dtc_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int H, int I, float limit, const hbk_reduce& red, void* ws, cudaStream_t st) {
-  const int M = src.M, K = src.K, P = M * K + (src.shared_rec ? M : 0);
-  if (P <= 0) return HB_OK;
+// The gate/up pass alone, behind the streaming path's grouping kernel (which wrote hdr / groups / s_row into the workspace `w`):
+// digit planes of the M rows of x (row pitch x_ld), then the layer kernel in its gate/up-only form writing y bf16 into w.y.
+int hbk_moe_dtc_gu_run(hb_ctx* ctx, const void* x, int x_ld, int M, const uint8_t* const* tab, int n_tab, const uint8_t* shared_rec, int P, int H, int I,
+                       float limit, void* ws, bool rows_arrive_late, cudaStream_t st) {
   DecodeWs w = carve(ws, P, H, I);
   DtcWs dw;
   dtc_carve(ws, hbk_moe_decode_ws_bytes(P, H, I) - hbk_moe_dtc_ws_extra(P, H, I), P, H, I, &dw);
   hb_rec_layout L;
   hb_rec_layout_make(H, I, &L);
-  int r = dtc_maps_for(ctx, src.tab + (size_t)src.li * src.E, src.E, src.shared_rec, H, I, st);
+  int r = dtc_maps_for(ctx, tab, n_tab, shared_rec, H, I, st);
   if (r) return r;
-  const int sh_row0 = src.sh_row0, sh_rows = src.sh_rows < 0 ? M : src.sh_rows;
-  ReduceArgs ra{w.part, w.pos_of, w.pw, M, K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
-                reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), sh_row0, sh_rows, hbk_ep_push{}, ctx->dev_err, P};
-  DtPrepArgs pa{};
-  pa.route = src.route; pa.logits = src.logits; pa.ld = src.ld; pa.renorm = src.renorm; pa.logits_bf16 = src.logits_bf16; pa.bias = src.bias;
-  pa.sig_scale = src.sig_scale; pa.ids = const_cast<int32_t*>(src.ids); pa.w = const_cast<float*>(src.w); pa.ld_ids = src.ld_ids ? src.ld_ids : K;
-  pa.M = M; pa.K = K; pa.E = src.E; pa.tab = src.tab; pa.li = src.li; pa.shared_rec = src.shared_rec; pa.sh_row0 = sh_row0; pa.sh_rows = src.shared_rec ? sh_rows : 0;
-  pa.x = reinterpret_cast<const __nv_bfloat16*>(x); pa.x_ld = src.x_ld ? src.x_ld : H; pa.H = H; pa.I = I; pa.ws = w; pa.dw = dw;
-  pa.arrive = ctx->dev_err + 16;
-  const size_t group_b = ((size_t)P + 3 * (size_t)(src.E + 1) + 66) * 4;
-  const size_t route_b = src.route ? RouteScratch::floats(src.E, K, 8) * 4 : 0;
-  const size_t prep_smem = group_b > route_b ? group_b : route_b;
-  HB_REQUIRE(ctx, prep_smem <= 96 * 1024, HB_ERR_UNSUPPORTED, "moe_decode: %d pairs over %d experts need %zu bytes of sort scratch", P, src.E, prep_smem);
-  if ((r = hb_launch(ctx, src.route ? "moe_dtc_route_prep" : "moe_dtc_prep", true, moe_dtc_prep_kernel, dim3(M), dim3(DT_PREP_THREADS), prep_smem, st, pa))) return r;
+  XdigArgs xa{reinterpret_cast<const __nv_bfloat16*>(x), x_ld, H, dw, rows_arrive_late ? 1 : 0};
+  if ((r = hb_launch(ctx, "moe_xdig", true, moe_xdig_kernel, dim3(M), dim3(256), 0, st, xa))) return r;
   DtcArgs a{};
+  a.gu_only = 1;
   a.hdr = w.hdr; a.groups = w.groups; a.s_row = w.s_row; a.H = H; a.I = I; a.limit = limit; a.L = L;
   a.maps = reinterpret_cast<const CUtensorMap*>(ctx->dtc_maps); a.meta = reinterpret_cast<const DtcMeta*>(a.maps + 2 * DT_VMAX);
   a.pitch[0] = H / 2; a.pitch[1] = I / 2; a.gstep[0] = gcd_int(H / 2, 4096); a.gstep[1] = gcd_int(I / 2, 4096);
   for (int k = 0; k < 2; ++k) { a.pshift[k] = -1; for (int b = 7; b <= 12; ++b) if (a.pitch[k] == (1 << b)) a.pshift[k] = b; }
-  a.dw = dw; a.y = w.y; a.part = w.part; a.done = reinterpret_cast<unsigned int*>(w.done); a.red = ra; a.err = ctx->dev_err;
+  a.dw = dw; a.y = w.y; a.part = w.part; a.done = reinterpret_cast<unsigned int*>(w.done); a.err = ctx->dev_err;
   int grid = ctx->sm_count;
   if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
   a.dIT.set((uint32_t)(I / DT_GU_ROWS)); a.dHT.set((uint32_t)(H / DT_DN_ROWS)); a.dG.set((uint32_t)grid);
-  return hb_launch(ctx, "moe_dtc_layer", true, moe_dtc_layer_kernel, dim3(grid), dim3(DT_THREADS), (size_t)DT_SMEM, st, a);
+  return hb_launch(ctx, "moe_gate_up_tc", true, moe_dtc_layer_kernel, dim3(grid), dim3(DT_THREADS), (size_t)DT_SMEM, st, a);
 }

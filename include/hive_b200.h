@@ -48,8 +48,9 @@ typedef struct hb_config {
 #define HB_FLAG_NO_PDL 1   /* launch every kernel fully serialised (no programmatic dependent launch) */
 #define HB_FLAG_FUSED 2    /* decode: run gate/up, down and reduce as ONE persistent kernel (experimental; default: three kernels chained by PDL) */
 #define HB_FLAG_DECODE_MMA_SYNC 8 /* decode: run the routed operators on the register-dequantisation (mma.sync) streaming kernels */
-#define HB_FLAG_DECODE_TC 16      /* decode: run the routed operators on the tensor-memory layer kernel (tcgen05 block-scaled FP4 over exact
-                                     digit planes of the bf16 activations).  Neither flag: the library picks (see hb_moe_decode_supported). */
+#define HB_FLAG_DECODE_TC 16      /* same as HB_FLAG_DECODE_TC_GU (kept for callers that set it) */
+#define HB_FLAG_DECODE_TC_GU 64   /* decode, routed operators: the gate/up pass runs on the tensor-memory kernel (exact digit planes of the activations,
+                                     block-scaled FP4 MMAs), grouping and down pass on the streaming kernels */
 #define HB_FLAG_LAYER_A4 32       /* hb_moe_layer may run calls of more than 64 rows on the W4A4 grouped GEMM (activations quantised to NVFP4 — the
                                      reference's lossy opt-in, fn_moe_prefill_set_a4).  Without it hb_moe_layer keeps bf16 activations at every
                                      row count: the same numbers as the decode operators, never a silent change of arithmetic */

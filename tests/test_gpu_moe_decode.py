@@ -16,9 +16,10 @@ def E():
     return E
 
 
-@pytest.fixture(params=[8, 16], ids=["mma_sync", "tensor_memory"])
+@pytest.fixture(params=[8, 64], ids=["mma_sync", "tensor_memory_gate_up"])
 def eng(request, E):
-    """A context pinned to one of the two decode engines of the routed operators (HB_FLAG_DECODE_MMA_SYNC, HB_FLAG_DECODE_TC)."""
+    """A context pinned to one of the decode engines of the routed operators (HB_FLAG_DECODE_MMA_SYNC: the streaming kernels throughout;
+    HB_FLAG_DECODE_TC_GU: gate/up on the tensor-memory kernel between the streaming path's grouping and down kernels)."""
     c = E.Context(flags=request.param)
     yield c
     c.close()
@@ -78,7 +79,7 @@ def test_routed_fast_path_vs_oracle(E, oracle, H, I, Ex, K, M):
     # the register-dequantisation kernels forced (HB_FLAG_DECODE_MMA_SYNC = 8) and their single persistent kernel form
     # (HB_FLAG_FUSED = 2), which performs the same arithmetic in the same order: bit-identical to the three-kernel form
     outs = []
-    for flags in (8, 2, 16):
+    for flags in (8, 2):
         c = E.Context(flags=flags)
         o = E.fn_moe_decode_routed(torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), E.rec_table(drecs), 0, Ex, bf16_tensor(x), H, I,
                                    shared=bf16_tensor(shared), lg=torch.from_numpy(lg).cuda(), col=1, ctx=c)
@@ -88,15 +89,18 @@ def test_routed_fast_path_vs_oracle(E, oracle, H, I, Ex, K, M):
         c.close()
     assert rel_rms_err(outs[0].float().cpu().numpy(), ref) <= TOL
     assert torch.equal(outs[0], outs[1])
-    # the tensor-memory layer kernel (HB_FLAG_DECODE_TC = 16): same inputs, same tolerance, and bit-identical run to run
-    assert rel_rms_err(outs[2].float().cpu().numpy(), ref) <= TOL
-    c = E.Context(flags=16)
-    o2 = E.fn_moe_decode_routed(torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), E.rec_table(drecs), 0, Ex, bf16_tensor(x), H, I,
-                                shared=bf16_tensor(shared), lg=torch.from_numpy(lg).cuda(), col=1, ctx=c)
-    torch.cuda.synchronize()
-    c.check_device()
-    assert torch.equal(outs[2], o2)
-    c.close()
+    # gate/up on the tensor-memory kernel, the rest on the streaming kernels (HB_FLAG_DECODE_TC_GU = 64): tolerance, and bit-identical
+    # run to run
+    o64 = []
+    for _ in range(2):
+        c = E.Context(flags=64)
+        o64.append(E.fn_moe_decode_routed(torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), E.rec_table(drecs), 0, Ex, bf16_tensor(x), H, I,
+                                          shared=bf16_tensor(shared), lg=torch.from_numpy(lg).cuda(), col=1, ctx=c))
+        torch.cuda.synchronize()
+        c.check_device()
+        c.close()
+    assert rel_rms_err(o64[0].float().cpu().numpy(), ref) <= TOL
+    assert torch.equal(o64[0], o64[1])
 
 
 def test_pair_list_accumulates_in_pair_order(E, oracle):
@@ -206,6 +210,29 @@ def test_batch_invariance_and_weight_linearity(E, oracle):
     acc = oracle.moe_routed(H, I, ids_np[[0, 15]], w_np[[0, 15]], host, x[[0, 15]].float().cpu().numpy(), 0.0, 0)
     assert rel_rms_err(full[[0, 15]].cpu().numpy(), acc) <= TOL
     E.context().check_device()
+
+
+def test_routed_rows_do_not_depend_on_the_batch(E, oracle, eng):
+    """Routed form, every engine: a row run alone gives the bits it gives inside a batch of 12 (its expert groups then hold other rows
+    too), and a second run of the batch repeats the first bit for bit."""
+    import torch
+    H, I, Ex, K, M = 2048, 512, 24, 6, 12
+    rng = np.random.default_rng(77)
+    recs = random_records(oracle, H, I, 6, seed=9)
+    drecs = upload(recs)
+    drecs = [drecs[i % 6].clone() for i in range(Ex)]
+    tab = E.rec_table(drecs)
+    x = bf16_tensor(oracle.bf16r((rng.normal(0, 1, (M, H)) * np.exp(rng.normal(0, 1, (M, 1)))).astype(np.float32)))
+    ids_np, w_np = _routing(rng, M, Ex, K)
+    ids = torch.from_numpy(ids_np).cuda(); w = torch.from_numpy(w_np).cuda()
+    full = E.moe_decode_routed_f32(ids, w, tab, 0, Ex, x, H, I, ctx=eng)
+    again = E.moe_decode_routed_f32(ids, w, tab, 0, Ex, x, H, I, ctx=eng)
+    assert torch.equal(full, again)
+    for m in (0, 5, 11):
+        one = E.moe_decode_routed_f32(ids[m:m + 1].contiguous(), w[m:m + 1].contiguous(), tab, 0, Ex, x[m:m + 1].contiguous(), H, I, ctx=eng)
+        assert torch.equal(one[0], full[m]), m
+    torch.cuda.synchronize()
+    eng.check_device()
 
 
 def test_decode_argument_errors(E):
