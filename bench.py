@@ -468,15 +468,18 @@ def run_ours(args):
     peak = float(peaks.get("hbm_gbs", 6650.0))
     peak_src = "measured copy bandwidth of this pool (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s (earlier measurement on this pool)"
     roofline = None
-    if world == 1 and prof and "moe_gate_up" in prof:
+    gu_key = "moe_gate_up_tc" if prof and "moe_gate_up_tc" in prof else "moe_gate_up"
+    if world == 1 and prof and gu_key in prof:
         U = head["records_per_layer"]
         gu_bytes = U * (2 * H * I * 9 // 16) + head_B * H * 2                     # gate+up halves of U records + the activation rows
-        ach = gu_bytes / (prof["moe_gate_up"]["mean_us"] * 1e-6) / 1e9
-        roofline = {"bound": "hbm", "kernel": "moe_gate_up (moe_stream_kernel<8,1,false>)", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                    "peak_source": peak_src, "traffic": gu_bytes, "traffic_source": "algorithmic (an ncu capture of this kernel on a 4-layer case read 1.018 x algorithmic DRAM bytes; not measured in this run)", "algorithmic_bytes_per_launch": gu_bytes, "mean_us": prof["moe_gate_up"]["mean_us"]}
+        ach = gu_bytes / (prof[gu_key]["mean_us"] * 1e-6) / 1e9
+        gu_label = ("moe_gate_up_tc (moe_dtc_layer_kernel, gate/up form: tcgen05 block-scaled FP4 MMAs over digit planes of the activations)"
+                    if gu_key == "moe_gate_up_tc" else "moe_gate_up (moe_stream_kernel<8,1,false>)")
+        roofline = {"bound": "hbm", "kernel": gu_label, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                    "peak_source": peak_src, "traffic": gu_bytes, "traffic_source": "algorithmic (an ncu capture of this kernel on a 4-layer case read 1.018 x algorithmic DRAM bytes; not measured in this run)", "algorithmic_bytes_per_launch": gu_bytes, "mean_us": prof[gu_key]["mean_us"]}
     clocks = sampler.result()
     line = {"metric": "moe_layer_tokens_per_s", "value": head["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 products of e2m1·e4m3 weights and bf16 activations, f32 accumulate",
+            "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e2m1·e4m3 weights x bf16 activations, exact products (gate/up: FP4 MMAs over base-8 digit planes of the activations; down: f16 mma.sync), f32 accumulate",
             "data": "synthetic", "config": {"workload": WORKLOAD, "batch_tokens_per_gpu": head_B, "layers": L,
                                             "l2": "inputs larger than L2: every step streams %.1f GB of distinct expert records" % head["algorithmic_GB_per_step"],
                                             "parallelism": "single GPU" if world == 1 else f"expert-parallel ep{world}: experts sharded, rows+routing gathered, fp32 sums sent to the row's rank; transport: {ep_transport}"},

@@ -59,6 +59,7 @@ struct hbk_pair_src {
   int route = 0;                                                             // 0 = ids / w given, 1 = softmax, 2 = sigmoid + bias
   const float* logits = nullptr; int ld = 0, renorm = 0, logits_bf16 = 0;
   const float* bias = nullptr; float sig_scale = 1.f;
+  int pairs_hint = 0;                                                        // pairs of the enclosing call when this one is a sub-chunk of it: the engine is picked as for the whole
   bool ws_stream_only = false;                                               // ws holds hbk_moe_decode_ws_stream_bytes only: the streaming chain must run
 };
 // What the last kernel does with the per-pair outputs.

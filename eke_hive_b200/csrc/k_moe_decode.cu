@@ -62,6 +62,8 @@ __device__ void block_scan2(int* a, int* b, int n, int* tot_a, int* tot_b, int* 
   __syncthreads();
 }
 
+constexpr int kTcGuMinPairs = 40;                   // unpinned contexts: pairs per call from which gate/up runs on the tensor-memory kernel
+
 __global__ void __launch_bounds__(kGroupThreads) moe_group_kernel(GroupArgs a) {
   extern __shared__ __align__(16) uint8_t gsm[];
   griddep_wait();
@@ -623,8 +625,12 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
     sa.stages = s;
     int grid = ctx->sm_count * c;
     if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
-    const bool tc_gu = routed && (ctx->flags & (HB_FLAG_DECODE_TC_GU | HB_FLAG_DECODE_TC)) && !src.ws_stream_only && src.tab && hbk_moe_dtc_supported(H, I) &&
-                       hbk_moe_dtc_gu_fits(ctx, P, src.E, H, I);
+    // Which gate/up engine: a context may pin either (HB_FLAG_DECODE_MMA_SYNC / HB_FLAG_DECODE_TC_GU).  Unpinned, the tensor-memory
+    // kernel takes calls of kTcGuMinPairs pairs or more — below that its start-up (tensor-memory allocation, work table, first TMA
+    // boxes) costs more than its faster stream saves (measured: 30.6 vs 27.6 µs per layer at 11 pairs, 73 vs 81 µs at 176).
+    const bool tc_ok = routed && !src.ws_stream_only && src.tab && hbk_moe_dtc_supported(H, I) && hbk_moe_dtc_gu_fits(ctx, P, src.E, H, I) &&
+                       !(ctx->flags & HB_FLAG_DECODE_MMA_SYNC);
+    const bool tc_gu = tc_ok && ((ctx->flags & (HB_FLAG_DECODE_TC_GU | HB_FLAG_DECODE_TC)) || (P > src.pairs_hint ? P : src.pairs_hint) >= kTcGuMinPairs);
     if (tc_gu) {
       // gate/up on the block-scaled tensor cores: digit planes of the rows (beside the grouping kernel), then the tensor-memory kernel
       if ((r = hbk_moe_dtc_gu_run(ctx, x, x_ld, src.M, src.tab + (size_t)src.li * src.E, src.E, src.shared_rec, P, H, I, limit, ws, src.wait_flags != nullptr, st)))

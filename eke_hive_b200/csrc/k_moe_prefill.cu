@@ -622,6 +622,7 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
     for (int m0 = 0; m0 < M; m0 += rows) {
       const int n = M - m0 < rows ? M - m0 : rows;
       hbk_pair_src src; src.ids = ids + (size_t)m0 * K; src.w = w + (size_t)m0 * K; src.M = n; src.K = K; src.tab = rec_tab; src.li = li; src.E = E;
+      src.pairs_hint = M * K;                                               // every sub-chunk runs on the engine the whole call would get
       hbk_reduce red;
       if (cmb) {
         red.shared = reinterpret_cast<const __nv_bfloat16*>(cmb->shared) + (size_t)m0 * H; red.lg = cmb->lg ? cmb->lg + (size_t)m0 * cmb->ld : nullptr;

@@ -47,10 +47,13 @@ typedef struct hb_config {
 } hb_config;
 #define HB_FLAG_NO_PDL 1   /* launch every kernel fully serialised (no programmatic dependent launch) */
 #define HB_FLAG_FUSED 2    /* decode: run gate/up, down and reduce as ONE persistent kernel (experimental; default: three kernels chained by PDL) */
-#define HB_FLAG_DECODE_MMA_SYNC 8 /* decode: run the routed operators on the register-dequantisation (mma.sync) streaming kernels */
+#define HB_FLAG_DECODE_MMA_SYNC 8 /* decode: run the routed operators on the register-dequantisation (mma.sync) streaming kernels at every size */
 #define HB_FLAG_DECODE_TC 16      /* same as HB_FLAG_DECODE_TC_GU (kept for callers that set it) */
 #define HB_FLAG_DECODE_TC_GU 64   /* decode, routed operators: the gate/up pass runs on the tensor-memory kernel (exact digit planes of the activations,
-                                     block-scaled FP4 MMAs), grouping and down pass on the streaming kernels */
+                                     block-scaled FP4 MMAs) at every size, grouping and down pass on the streaming kernels.  With neither flag the
+                                     library picks by the number of pairs of the call (40 or more: tensor memory); both engines meet the same
+                                     tolerance, and a row's bits do not depend on its batch as long as the engine does not change — pin one
+                                     with a flag where that matters */
 #define HB_FLAG_LAYER_A4 32       /* hb_moe_layer may run calls of more than 64 rows on the W4A4 grouped GEMM (activations quantised to NVFP4 — the
                                      reference's lossy opt-in, fn_moe_prefill_set_a4).  Without it hb_moe_layer keeps bf16 activations at every
                                      row count: the same numbers as the decode operators, never a silent change of arithmetic */
@@ -174,7 +177,8 @@ HB_API int hb_moe_decode_routed(hb_ctx* ctx, const int32_t* ids, const float* w,
  *     value: harmless).  No call allocates or frees memory;
  *   - every call on a device uses the same array and finds the previous call's contents in it (what must start at zero is
  *     cleared by the kernels themselves); calls that overlap on the GPU race on it — keep them on one stream;
- *   - it always runs the streaming kernels, whatever decode engine the context's flags select. */
+ *   - it always runs the streaming kernels (its result is bit-identical to hb_moe_decode_routed on a context pinned with
+ *     HB_FLAG_DECODE_MMA_SYNC, and within the common tolerance of what an unpinned context computes). */
 HB_API int hb_moe_decode_static_max_pairs(int H, int I);
 HB_API int hb_moe_decode_routed_static(hb_ctx* ctx, const int32_t* ids, const float* w, int M, int K, const uint8_t* const* rec_tab, int li, int E,
                                        const void* x_bf16, int H, int I, float limit, const hb_pf_combine* cmb, void* stream);
