@@ -82,7 +82,7 @@ size_t hbk_moe_dtc_ws_extra(int n_pairs, int H, int I);      // bytes it needs a
 int hbk_moe_dtc_setup(hb_ctx* ctx);
 // gate/up pass alone on the tensor cores, between the streaming path's grouping kernel and its down kernel
 int hbk_moe_dtc_gu_run(hb_ctx* ctx, const void* x, int x_ld, int M, const uint8_t* const* tab, int n_tab, const uint8_t* shared_rec, int P, int H, int I,
-                       float limit, void* ws, bool rows_arrive_late, cudaStream_t st);
+                       float limit, void* ws, const uint32_t* wait_flags, int wait_n, const uint32_t* wait_step, cudaStream_t st);
 
 // dense GEMV (k_dense.cu)
 int hbk_dense_setup(hb_ctx* ctx);

@@ -633,7 +633,7 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
     const bool tc_gu = tc_ok && ((ctx->flags & (HB_FLAG_DECODE_TC_GU | HB_FLAG_DECODE_TC)) || (P > src.pairs_hint ? P : src.pairs_hint) >= kTcGuMinPairs);
     if (tc_gu) {
       // gate/up on the block-scaled tensor cores: digit planes of the rows (beside the grouping kernel), then the tensor-memory kernel
-      if ((r = hbk_moe_dtc_gu_run(ctx, x, x_ld, src.M, src.tab + (size_t)src.li * src.E, src.E, src.shared_rec, P, H, I, limit, ws, src.wait_flags != nullptr, st)))
+      if ((r = hbk_moe_dtc_gu_run(ctx, x, x_ld, src.M, src.tab + (size_t)src.li * src.E, src.E, src.shared_rec, P, H, I, limit, ws, src.wait_flags, src.wait_n, src.wait_step, st)))
         return r;
     } else if ((r = hb_launch(ctx, "moe_gate_up", true, kg.fn, dim3(grid), dim3(kg.threads), kg.smem(s), st, sa))) return r;
     plan_stream(ctx, kd, &s, &c);

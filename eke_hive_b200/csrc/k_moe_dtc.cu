@@ -27,6 +27,7 @@
 // Every wait is bounded and reports through the context's error word.
 #include "moe_stream.cuh"
 #include "router.cuh"
+#include "ep.cuh"
 #include "tc_common.cuh"
 
 namespace hb {
@@ -712,13 +713,17 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
 // one CTA per row.  It is launched right behind the grouping kernel, which triggers its dependents as soon as its own wait for the
 // stream's earlier work has returned — so the rows are final when this kernel starts, it runs beside the grouping, and it does its
 // own wait (for the grouping kernel to finish) LAST: the kernel behind it then finds both the planes and the group list complete.
-// wait_first: the rows themselves arrive during the grouping kernel (expert parallel: pushed by other ranks) — wait before reading.
-struct XdigArgs { const __nv_bfloat16* x; int x_ld, H; DtcWs dw; int wait_first; };
+// wait_flags: the rows are pushed by other ranks (expert parallel) — every CTA waits, bounded, for the same flags the grouping kernel
+// waits for before it reads its row.
+struct XdigArgs { const __nv_bfloat16* x; int x_ld, H; DtcWs dw; const uint32_t* wait_flags; int wait_n; const uint32_t* wait_step; uint32_t* err; };
 __global__ void __launch_bounds__(256) moe_xdig_kernel(const XdigArgs a) {
   __shared__ int s_red[8];
   const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (a.wait_first) griddep_wait();
   griddep_launch();
+  if (a.wait_flags) {
+    if ((int)threadIdx.x < a.wait_n && !*reinterpret_cast<volatile uint32_t*>(a.err)) ep_wait_flag(a.wait_flags + threadIdx.x, *a.wait_step + 1u, a.err, 0x40000u);
+    __syncthreads();
+  }
   const uint32_t* xr = reinterpret_cast<const uint32_t*>(a.x + (size_t)m * a.x_ld);
   uint32_t am = 0;
   for (int e2 = threadIdx.x; e2 < a.H / 2; e2 += 256) { const uint32_t w2 = __ldg(xr + e2); am = max(am, max(w2 & 0x7fffu, (w2 >> 16) & 0x7fffu)); }
@@ -738,7 +743,7 @@ __global__ void __launch_bounds__(256) moe_xdig_kernel(const XdigArgs a) {
     for (int p = 0; p < 8; ++p) *reinterpret_cast<uint32_t*>(a.dw.xdig + dt_dig_off((size_t)m, a.H, u * 8, p)) = pl[p];
   }
   fence_proxy_async_global();                                                  // the planes are read through the async proxy (bulk copies) by the next kernel
-  if (!a.wait_first) griddep_wait();
+  griddep_wait();
 }
 
 // Stamps the anchored bases into the tensor-map variants of both matrix kinds (one block; runs when the maps are first needed).
@@ -847,7 +852,7 @@ extern "C" __attribute__((visibility("default"))) int hb_dtc_stage_read(long lon
 // The gate/up pass alone, behind the streaming path's grouping kernel (which wrote hdr / groups / s_row into the workspace `w`):
 // digit planes of the M rows of x (row pitch x_ld), then the layer kernel in its gate/up-only form writing y bf16 into w.y.
 int hbk_moe_dtc_gu_run(hb_ctx* ctx, const void* x, int x_ld, int M, const uint8_t* const* tab, int n_tab, const uint8_t* shared_rec, int P, int H, int I,
-                       float limit, void* ws, bool rows_arrive_late, cudaStream_t st) {
+                       float limit, void* ws, const uint32_t* wait_flags, int wait_n, const uint32_t* wait_step, cudaStream_t st) {
   DecodeWs w = carve(ws, P, H, I);
   DtcWs dw;
   dtc_carve(ws, hbk_moe_decode_ws_bytes(P, H, I) - hbk_moe_dtc_ws_extra(P, H, I), P, H, I, &dw);
@@ -855,7 +860,7 @@ int hbk_moe_dtc_gu_run(hb_ctx* ctx, const void* x, int x_ld, int M, const uint8_
   hb_rec_layout_make(H, I, &L);
   int r = dtc_maps_for(ctx, tab, n_tab, shared_rec, H, I, st);
   if (r) return r;
-  XdigArgs xa{reinterpret_cast<const __nv_bfloat16*>(x), x_ld, H, dw, rows_arrive_late ? 1 : 0};
+  XdigArgs xa{reinterpret_cast<const __nv_bfloat16*>(x), x_ld, H, dw, wait_flags, wait_n, wait_step, ctx->dev_err};
   if ((r = hb_launch(ctx, "moe_xdig", true, moe_xdig_kernel, dim3(M), dim3(256), 0, st, xa))) return r;
   DtcArgs a{};
   a.gu_only = 1;
