@@ -222,7 +222,7 @@ def parity_check(E_mod, torch, H, I, Ex, K, L, B, logits, x, ids, out, n_rows=2)
     touch regenerated from their seeds.  Returns {ids_equal, max_err_x_rms, rows, layers}; the caller fails the run above 2e-2."""
     from oracle import oracle as O
     rows = sorted({0, B - 1})[:n_rows]
-    worst, ids_equal = 0.0, True
+    worst, beyond, ids_equal = 0.0, 0.0, True
     layers = sorted({0, L - 1})
     for li in layers:
         lg = logits[0, li][rows].float().cpu().numpy()
@@ -244,9 +244,16 @@ def parity_check(E_mod, torch, H, I, Ex, K, L, B, logits, x, ids, out, n_rows=2)
         ref = O.bf16_to_f32(ref).astype(np.float64)
         got = out[0, li][rows].float().cpu().numpy().astype(np.float64)
         rms = np.sqrt(np.mean(ref ** 2, axis=-1)) + 1e-30
-        worst = max(worst, float(np.max(np.max(np.abs(got - ref), axis=-1) / rms)))
-    return {"ids_equal": ids_equal, "max_err_x_rms": worst, "rows": rows, "layers": layers, "bar": 2e-2,
-            "what": "device routing vs the oracle router; layer outputs vs the CPU oracle's layer on the same inputs, touched experts regenerated from their seeds"}
+        diff = np.abs(got - ref)
+        worst = max(worst, float(np.max(np.max(diff, axis=-1) / rms)))
+        # The outputs are bf16 by the operator's contract: where the fp32 sums differ only by their order (sharded runs add per-rank sums),
+        # a result may land on the neighbouring bf16 value, and one bf16 step of a 4-sigma element is already 1.6-3 % of the row RMS.
+        # `beyond` is what is left of the difference after one such step of the reference value.
+        step = np.where(ref != 0, 2.0 ** (np.floor(np.log2(np.maximum(np.abs(ref), 1e-300))) - 7), 0.0)
+        beyond = max(beyond, float(np.max(np.max(np.maximum(diff - step, 0.0), axis=-1) / rms)))
+    return {"ids_equal": ids_equal, "max_err_x_rms": worst, "max_err_beyond_one_bf16_step_x_rms": beyond, "rows": rows, "layers": layers, "bar": 2e-2,
+            "what": "device routing vs the oracle router; layer outputs (bf16) vs the CPU oracle's layer on the same inputs, touched experts regenerated "
+                    "from their seeds; ok = routing equal and the error beyond one bf16 step of the reference value within the bar"}
 
 
 def run_ours(args):
@@ -448,11 +455,22 @@ def run_ours(args):
             torch.cuda.synchronize()
             ctx.check_device()
             parity = parity_check(E, torch, H, I, Ex, K, L, B, logits, x, ids, out)
+            first = out[0].clone()
+            graphs[0].replay()
+            torch.cuda.synchronize()
+            parity["run_to_run_equal"] = bool(torch.equal(first, out[0]))      # the same graph on the same inputs: the same bits
+            if not parity["run_to_run_equal"]:
+                parity["run_to_run_max_diff_x_rms"] = float(((first.float() - out[0].float()).abs().max() / (out[0].float().pow(2).mean().sqrt() + 1e-30)).item())
             if world > 1:
-                t = torch.tensor([parity["max_err_x_rms"], 0.0 if parity["ids_equal"] else 1.0], dtype=torch.float64, device=dev)
+                t = torch.tensor([parity["max_err_x_rms"], 0.0 if parity["ids_equal"] else 1.0, parity["max_err_beyond_one_bf16_step_x_rms"]], dtype=torch.float64,
+                                 device=dev)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 parity["max_err_x_rms"] = float(t[0].item()); parity["ids_equal"] = bool(t[1].item() == 0.0); parity["ranks_checked"] = world
-            parity["ok"] = bool(parity["ids_equal"] and parity["max_err_x_rms"] <= parity["bar"])
+                parity["max_err_beyond_one_bf16_step_x_rms"] = float(t[2].item())
+                t2 = torch.tensor([0.0 if parity["run_to_run_equal"] else 1.0], dtype=torch.float64, device=dev)
+                dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+                parity["run_to_run_equal"] = bool(t2.item() == 0.0)
+            parity["ok"] = bool(parity["ids_equal"] and parity["run_to_run_equal"] and parity["max_err_beyond_one_bf16_step_x_rms"] <= parity["bar"])
         if world > 1:
             torch.cuda.synchronize()
             ep.close()
@@ -624,7 +642,7 @@ def glm_measure(args, torch, dist, E, O, ctx, dev, rank, world):
     graphs[0].replay(); torch.cuda.synchronize()
     lay = E.ExpertRecLayout.make(H, I)
     tmp = torch.empty(lay.total, dtype=torch.uint8, device=dev)
-    err, ids_ok = 0.0, True
+    err, raw, ids_ok = 0.0, 0.0, True
     for li, m in ((0, 0), (L - 1, B - 1)):
         lg_r = logits[0, li, m:m + 1].cpu().numpy(); x_r = x[0, li, m:m + 1].float().cpu().numpy()
         rid, rw = O.router_sigmoid_topk(lg_r, bias_h, K, scale)
@@ -635,7 +653,9 @@ def glm_measure(args, torch, dist, E, O, ctx, dev, rank, world):
         Layers.fill_record(E, tmp, H, I, li, Layers.SHARED_ID, CFG["sigma"], CFG["seed"] + 3); shared = tmp.cpu().numpy().copy()
         _, _, ref = O.moe_layer(H, I, lg_r, x_r, recs, K, shared_rec=shared, router="sigmoid", bias=bias_h, scale=scale, limit=limit)
         ref = O.bf16_to_f32(ref)[0].astype(np.float64); got = out[0, li, m].float().cpu().numpy().astype(np.float64)
-        err = max(err, float(np.abs(got - ref).max() / (np.sqrt((ref ** 2).mean()) + 1e-30)))
+        step = np.where(ref != 0, 2.0 ** (np.floor(np.log2(np.maximum(np.abs(ref), 1e-300))) - 7), 0.0)      # one bf16 step of the reference value (see parity_check)
+        raw = max(raw, float(np.abs(got - ref).max() / (np.sqrt((ref ** 2).mean()) + 1e-30)))
+        err = max(err, float(np.maximum(np.abs(got - ref) - step, 0.0).max() / (np.sqrt((ref ** 2).mean()) + 1e-30)))
     # load balance: pairs per rank of the global batch, records each rank streams per layer
     gid, _ = O.router_sigmoid_topk(lg_all.reshape(-1, Ex), bias_h, K, scale)
     gid = gid.reshape(NS * L, Btot * K)
@@ -657,11 +677,11 @@ def glm_measure(args, torch, dist, E, O, ctx, dev, rank, world):
            "achieved_GBps_per_gpu_max": float(rec_r.max()) * rec_bytes_ / (us_layer * 1e-6) / 1e9, "frac_of_measured_hbm_busiest_gpu": float(rec_r.max()) * rec_bytes_ / (us_layer * 1e-6) / 1e9 / peak,
            "pairs_per_rank_max": float(ppr.max()), "pairs_per_rank_mean": float(ppr.mean()),
            "transport": ep.transport if ep is not None else "single GPU",
-           "parity": {"ids_equal": ids_ok, "max_err_x_rms": err, "bar": 2e-2, "ok": bool(ids_ok and err <= 2e-2)}}
+           "parity": {"ids_equal": ids_ok, "max_err_x_rms": raw, "max_err_beyond_one_bf16_step_x_rms": err, "bar": 2e-2, "ok": bool(ids_ok and err <= 2e-2)}}
     if world > 1:
-        t = torch.tensor([err, 0.0 if ids_ok else 1.0], dtype=torch.float64, device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        res["parity"] = {"ids_equal": bool(t[1].item() == 0.0), "max_err_x_rms": float(t[0].item()), "bar": 2e-2, "ranks_checked": world,
-                         "ok": bool(t[1].item() == 0.0 and t[0].item() <= 2e-2)}
+        t = torch.tensor([err, 0.0 if ids_ok else 1.0, raw], dtype=torch.float64, device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res["parity"] = {"ids_equal": bool(t[1].item() == 0.0), "max_err_x_rms": float(t[2].item()), "max_err_beyond_one_bf16_step_x_rms": float(t[0].item()),
+                         "bar": 2e-2, "ranks_checked": world, "ok": bool(t[1].item() == 0.0 and t[0].item() <= 2e-2)}
         torch.cuda.synchronize()
         ep.close()
     del graphs, layers

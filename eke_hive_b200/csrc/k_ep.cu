@@ -58,45 +58,39 @@ __global__ void __launch_bounds__(512) ep_push_rows_kernel(const __nv_bfloat16* 
   if (threadIdx.x == 0) st_release_sys(peers.ag_flag[pi] + rank, step);
 }
 
-// Router and push in one launch, one CTA per ROW: the row is routed by all eight warps (the two-level tournament of router.cuh: the
-// one-warp router's ids and weights, bit for bit), its ids / w are stored for the caller, and its record [row | ids | w] is written
-// into every rank's gather buffer.  The CTA that finishes last (a counter owned by the exchange object) raises this rank's flag at
-// every destination.  Dynamic shared memory: RouteScratch::floats(E, K, 8) words.
-constexpr int EP_ROUTE_THREADS = 256;
-__global__ void __launch_bounds__(EP_ROUTE_THREADS) ep_route_push_kernel(const float* __restrict__ logits, int ld, int E, int K, int renorm, int logits_bf16,
-                                                                         const __nv_bfloat16* __restrict__ x, int ldx, int32_t* __restrict__ ids_out,
-                                                                         float* __restrict__ w_out, int B, int H, int rec_bytes, EpPeers peers, int rank, int G,
-                                                                         const uint32_t* __restrict__ step_ctr, unsigned int* __restrict__ done) {
+// Router and push in one launch: every CTA (one per destination rank) routes all B rows itself — the routing is a deterministic
+// function of the logits, so the G copies agree — and sends rows, ids and weights to its rank.  CTA 0 also stores ids / w for
+// the caller.  Dynamic shared memory: (warps·E + 2·B·K) words.
+__global__ void __launch_bounds__(512) ep_route_push_kernel(const float* __restrict__ logits, int ld, int E, int K, int renorm, int logits_bf16,
+                                                            const __nv_bfloat16* __restrict__ x, int ldx, int32_t* __restrict__ ids_out,
+                                                            float* __restrict__ w_out, int B, int H, int rec_bytes, EpPeers peers, int rank,
+                                                            const uint32_t* __restrict__ step_ctr) {
   extern __shared__ float ep_sm[];
-  __shared__ uint32_t meta[32];                                            // the row's ids then weights (K ≤ 16 each)
   griddep_wait();                                                          // the previous step's combine has advanced the step counter
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, m = blockIdx.x;
-  int32_t id = 0;
-  float wv = 0.f;
-  route_row_group(1, logits + (size_t)m * ld, nullptr, E, K, renorm, logits_bf16, 1.f, ep_sm, EP_ROUTE_THREADS / 32, warp, lane, 1, id, wv);
-  if (warp == 0 && lane < K) {
-    ids_out[(size_t)m * K + lane] = id; w_out[(size_t)m * K + lane] = wv;
-    meta[lane] = (uint32_t)id; meta[K + lane] = __float_as_uint(wv);
-  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  int32_t* ids_s = reinterpret_cast<int32_t*>(ep_sm + (size_t)nw * E);
+  float* w_s = reinterpret_cast<float*>(ids_s + B * K);
+  for (int m = warp; m < B; m += nw)
+    route_softmax_row(logits + (size_t)m * ld, E, K, renorm, logits_bf16, ep_sm + (size_t)warp * E, lane, ids_s + m * K, w_s + m * K);
   __syncthreads();
+  const int pi = blockIdx.x;
+  if (pi == 0)
+    for (int i = threadIdx.x; i < B * K; i += blockDim.x) { ids_out[i] = ids_s[i]; w_out[i] = w_s[i]; }
   const uint32_t step = *step_ctr + 1u;
-  const int xc = H / 8;                                                    // 16-byte pieces of the row's activations
-  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)m * ldx);
-  for (int i = threadIdx.x; i < G * xc; i += EP_ROUTE_THREADS) {
-    const int p = i / xc, c = i - p * xc;
-    reinterpret_cast<uint4*>(peers.recv[p] + ((size_t)rank * B + m) * rec_bytes)[c] = __ldg(src + c);
+  uint8_t* dst = peers.recv[pi] + (size_t)rank * B * rec_bytes;
+  const int xc = H / 8;
+  for (int i = threadIdx.x; i < B * xc; i += blockDim.x) {
+    const int r = i / xc, c = i - r * xc;
+    reinterpret_cast<uint4*>(dst + (size_t)r * rec_bytes)[c] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)r * ldx) + c);
   }
-  for (int i = threadIdx.x; i < G * 2 * K; i += EP_ROUTE_THREADS) {
-    const int p = i / (2 * K), c = i - p * 2 * K;
-    reinterpret_cast<uint32_t*>(peers.recv[p] + ((size_t)rank * B + m) * rec_bytes + (size_t)H * 2)[c] = meta[c];
+  for (int i = threadIdx.x; i < B * 2 * K; i += blockDim.x) {
+    const int r = i / (2 * K), c = i - r * 2 * K;
+    const uint32_t v = c < K ? (uint32_t)ids_s[r * K + c] : __float_as_uint(w_s[r * K + c - K]);
+    reinterpret_cast<uint32_t*>(dst + (size_t)r * rec_bytes + (size_t)H * 2)[c] = v;
   }
   __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {          // the last row of this rank is on its way: tell every rank
-    *done = 0;
-    __threadfence_system();
-    for (int p = 0; p < G; ++p) st_release_sys(peers.ag_flag[p] + rank, step);
-  }
+  if (threadIdx.x == 0) st_release_sys(peers.ag_flag[pi] + rank, step);
 }
 
 // one CTA: thread r waits for rank r's flag
@@ -256,11 +250,11 @@ int hb_ep_route_push(hb_ep* e, const float* logits, int ld, int E, int renorm, i
   hb_ctx* ctx = e->ctx;
   HB_REQUIRE(ctx, logits && x_bf16 && ids_out && w_out && ldx >= e->H && ldx % 8 == 0 && hb_aligned(x_bf16, 16), HB_ERR_INVALID, "ep_route_push: bad arguments");
   HB_REQUIRE(ctx, E >= 1 && ld >= E && e->K <= 16 && e->K <= E, HB_ERR_INVALID, "ep_route_push: E=%d ld=%d K=%d", E, ld, e->K);
-  const size_t smem = RouteScratch::floats(E, e->K, EP_ROUTE_THREADS / 32) * 4;
+  const size_t smem = ((size_t)16 * E + 2 * (size_t)e->B * e->K) * 4;
   HB_REQUIRE(ctx, smem <= 48 * 1024, HB_ERR_UNSUPPORTED, "ep_route_push: E=%d too large for the fused router (route with hb_route_softmax_topk, then hb_ep_push_rows)", E);
-  return hb_launch(ctx, "ep_route_push", true, ep_route_push_kernel, dim3(e->B), dim3(EP_ROUTE_THREADS), smem, reinterpret_cast<cudaStream_t>(stream), logits, ld,
-                   E, e->K, renorm, logits_bf16, reinterpret_cast<const __nv_bfloat16*>(x_bf16), ldx, ids_out, w_out, e->B, e->H, e->rec_bytes, e->peers, e->rank,
-                   e->world, (const uint32_t*)e->step_ctr, e->done + kEpMaxRanks + 2);
+  return hb_launch(ctx, "ep_route_push", true, ep_route_push_kernel, dim3(e->world), dim3(512), smem, reinterpret_cast<cudaStream_t>(stream), logits, ld, E,
+                   e->K, renorm, logits_bf16, reinterpret_cast<const __nv_bfloat16*>(x_bf16), ldx, ids_out, w_out, e->B, e->H, e->rec_bytes, e->peers, e->rank,
+                   (const uint32_t*)e->step_ctr);
 }
 
 int hb_ep_layer_local(hb_ep* e, const uint8_t* const* rec_tab, int li, int E, int I, float limit, const uint8_t* shared_rec, void* shared_out_bf16, void* ws,

@@ -648,8 +648,10 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
     if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
     bool meet = false;
     for (int j = 0; j < 8; ++j) if (ctx->down_fn[j] == reinterpret_cast<const void*>(kd.fn)) meet = ctx->down_meet[j];
-    if (routed && meet) {
-      // the down pass sums the rows' pairs itself (its CTAs meet at the end): no reduce launch
+    if (routed && meet && !red.ep) {
+      // the down pass sums the rows' pairs itself (its CTAs meet at the end): no reduce launch.  (Expert parallel keeps the separate
+      // reduce kernel: pushing the sums to the other ranks from the down kernel's tail measured 2 µs slower per layer at 2 ranks and more
+      // at 8 — the stores start only after every CTA of the long kernel has arrived.)
       sd.red_on = 1; sd.fin = reinterpret_cast<unsigned int*>(w.hdr + 3);
       sd.red = ReduceArgs{w.part, w.pos_of, w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
                           reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), ga.sh_row0, ga.sh_rows,
