@@ -30,6 +30,7 @@ struct GroupArgs {
   // optional routing stage (routed form): logits → ids / w by one warp per row before the grouping
   int route; const float* logits; int ld, renorm, logits_bf16; const float* bias; float sig_scale;
   int32_t* ids_out; float* w_out;
+  int group_rows;       // rows per group (≤ kGroupRows)
 };
 
 // Exclusive scan of two int arrays of length n in shared memory, by the whole block (blockDim.x == kGroupThreads).
@@ -124,7 +125,8 @@ __global__ void __launch_bounds__(kGroupThreads) moe_group_kernel(GroupArgs a) {
   }
   for (int i = threadIdx.x; i < P; i += blockDim.x) if (key[i] >= 0) atomicAdd(&cnt[key[i]], 1);
   __syncthreads();
-  for (int k = threadIdx.x; k < NK; k += blockDim.x) ngr[k] = (cnt[k] + kGroupRows - 1) / kGroupRows;
+  const int GR = a.group_rows;                          // rows per group: 8 for the streaming gate/up kernel, 2 for the tensor-memory one
+  for (int k = threadIdx.x; k < NK; k += blockDim.x) ngr[k] = (cnt[k] + GR - 1) / GR;
   __syncthreads();
   // keep the counts: the scan overwrites cnt with offsets, so copy them into fill's slot first (fill is re-zeroed after)
   for (int k = threadIdx.x; k < NK; k += blockDim.x) fill[k] = cnt[k];
@@ -135,9 +137,9 @@ __global__ void __launch_bounds__(kGroupThreads) moe_group_kernel(GroupArgs a) {
     const int c = fill[k];
     if (c == 0) continue;
     const uint8_t* rec = routed ? (k == a.E ? a.shared_rec : a.tab[(size_t)a.li * a.E + k]) : recs[k];
-    for (int j = 0; j * kGroupRows < c; ++j)
+    for (int j = 0; j * GR < c; ++j)
       if (HB_BOUND(a.wait_err, ngr[k] + j >= 0 && ngr[k] + j < P, 0x101u, ngr[k] + j))
-        a.ws.groups[ngr[k] + j] = Group{rec, cnt[k] + j * kGroupRows, min(kGroupRows, c - j * kGroupRows)};
+        a.ws.groups[ngr[k] + j] = Group{rec, cnt[k] + j * GR, min(GR, c - j * GR)};
   }
   __syncthreads();
   for (int k = threadIdx.x; k < NK; k += blockDim.x) fill[k] = 0;
@@ -576,6 +578,21 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
   ga.tab = src.tab; ga.li = src.li; ga.E = src.E; ga.shared_rec = src.shared_rec; ga.ws = w;
   ga.ld_ids = src.ld_ids ? src.ld_ids : src.K; ga.sh_row0 = src.sh_row0; ga.sh_rows = src.sh_rows < 0 ? src.M : src.sh_rows;
   ga.wait_flags = src.wait_flags; ga.wait_n = src.wait_n; ga.wait_step = src.wait_step; ga.wait_err = ctx->dev_err;
+  // Which gate/up engine: a context may pin either (HB_FLAG_DECODE_MMA_SYNC / HB_FLAG_DECODE_TC_GU).  Unpinned, the tensor-memory
+  // kernel takes calls of kTcGuMinPairs pairs or more — below that its start-up (tensor-memory allocation, work table, first TMA
+  // boxes) costs more than its faster stream saves (measured: 30.6 vs 27.6 µs per layer at 11 pairs, 73 vs 81 µs at 176).
+  // Expert parallel (rows of all ranks, most pairs dead on this rank): what counts is this rank's share of the pairs, and with many
+  // gathered rows the digit planes of rows this rank has nothing for cost more than the faster stream saves (measured at 8 ranks ×
+  // 16 rows: 109 vs 99 µs per layer; at 2 ranks: 101 vs 108 µs) — unpinned contexts take the tensor-memory kernel up to 32 rows.
+  bool tc_gu = false;
+  if (routed && !src.ws_stream_only && src.tab && hbk_moe_decode_fast(H, I) && hbk_moe_dtc_supported(H, I) && hbk_moe_dtc_gu_fits(ctx, P, src.E, H, I) &&
+      !(ctx->flags & (HB_FLAG_DECODE_MMA_SYNC | HB_FLAG_FUSED))) {
+    const int ranks = red.ep ? red.ep->world : 1;
+    const int pairs_eff = (P > src.pairs_hint ? P : src.pairs_hint) / ranks;
+    const bool auto_tc = pairs_eff >= kTcGuMinPairs && (ranks == 1 || src.M <= 32);
+    tc_gu = (ctx->flags & (HB_FLAG_DECODE_TC_GU | HB_FLAG_DECODE_TC)) || auto_tc;
+  }
+  ga.group_rows = tc_gu ? 2 : kGroupRows;
   const int x_ld = src.x_ld ? src.x_ld : H;
   if (src.route && ga.ld_ids != src.K) return hb_fail(ctx, HB_ERR_INVALID, "moe_decode: in-kernel routing writes dense ids / w rows");
   int route = src.route;
@@ -625,18 +642,6 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
     sa.stages = s;
     int grid = ctx->sm_count * c;
     if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
-    // Which gate/up engine: a context may pin either (HB_FLAG_DECODE_MMA_SYNC / HB_FLAG_DECODE_TC_GU).  Unpinned, the tensor-memory
-    // kernel takes calls of kTcGuMinPairs pairs or more — below that its start-up (tensor-memory allocation, work table, first TMA
-    // boxes) costs more than its faster stream saves (measured: 30.6 vs 27.6 µs per layer at 11 pairs, 73 vs 81 µs at 176).
-    const bool tc_ok = routed && !src.ws_stream_only && src.tab && hbk_moe_dtc_supported(H, I) && hbk_moe_dtc_gu_fits(ctx, P, src.E, H, I) &&
-                       !(ctx->flags & HB_FLAG_DECODE_MMA_SYNC);
-    // Expert parallel (rows of all ranks, most pairs dead on this rank): what counts is this rank's share of the pairs, and with many
-    // gathered rows the digit planes of rows this rank has nothing for cost more than the faster stream saves (measured at 8 ranks ×
-    // 16 rows: 109 vs 99 µs per layer; at 2 ranks: 101 vs 108 µs) — unpinned contexts take the tensor-memory kernel up to 32 rows.
-    const int ranks = red.ep ? red.ep->world : 1;
-    const int pairs_eff = (P > src.pairs_hint ? P : src.pairs_hint) / ranks;
-    const bool auto_tc = pairs_eff >= kTcGuMinPairs && (ranks == 1 || src.M <= 32);
-    const bool tc_gu = tc_ok && ((ctx->flags & (HB_FLAG_DECODE_TC_GU | HB_FLAG_DECODE_TC)) || auto_tc);
     if (tc_gu) {
       // gate/up on the block-scaled tensor cores: digit planes of the rows (beside the grouping kernel), then the tensor-memory kernel
       if ((r = hbk_moe_dtc_gu_run(ctx, x, x_ld, src.M, src.tab + (size_t)src.li * src.E, src.E, src.shared_rec, P, H, I, limit, ws, src.wait_flags, src.wait_n, src.wait_step, st)))

@@ -32,9 +32,10 @@
 
 namespace hb {
 
-constexpr int DT_ST = 8;                       // pipeline stages
+constexpr int DT_ST = 10;                       // pipeline stages
 constexpr int DT_A = 16384;                    // weight tile of a stage: 128 rows × 128 bytes (256 k values)
-constexpr int DT_B = 8192;                     // digit planes of a stage: up to 64 rows × 128 bytes
+constexpr int DT_B = 2048;                     // digit planes of a stage: 2 activation rows × 8 planes × 128 bytes (the grouping kernel makes groups of ≤ 2 rows
+                                               // for this kernel: most experts of a decode batch get one or two rows, and a small slot leaves room for more stages)
 constexpr int DT_STAGE = DT_A + DT_B;
 constexpr int DT_RAWD = 3;                     // windows the scale fetch runs ahead of its use
 constexpr int DT_RAW = (DT_RAWD + 1) * 2048;   // ring of fetched scale rows: 128 rows × 16 bytes per window
@@ -45,7 +46,7 @@ constexpr int DT_SMEM = 1024 + DT_ST * DT_STAGE + DT_RAW + 2 * DT_EX + DT_SFBC +
 constexpr int DT_THREADS = 16 * 32;            // warps 0-7 epilogues (two sets of four), then one warp each: MMA issue, weight TMA, digit copies,
                                                // (one idle); warps 12-15 fetch the scales and store them into tensor memory
 constexpr int DT_W_MMA = 8, DT_W_TMA = 9, DT_W_DIG = 10, DT_W_SC0 = 12;   // warp 11 idles: the scale warps must be warps 0-3 modulo 4
-constexpr int DT_TMEM_COLS = 512;              // accumulators 2 × 64, weight scales 8 × 16, digit-plane scales 8 × 16
+constexpr int DT_TMEM_COLS = 512;              // accumulators 2 × 64, then 32 columns per stage (16 of weight scales), then 16 columns of 1.0
 constexpr int DT_SFA_COL0 = 128;               // per stage 32 columns: 16 of weight scales, 16 of digit-plane scales (down items)
 constexpr int DT_SFB1_COL = DT_SFA_COL0 + DT_ST * 32;   // 16 columns of 1.0: the digit-plane scales of gate/up items
 constexpr int DT_VMAX = 32;                    // tensor-map variants per matrix kind (see DtcMeta)
@@ -270,7 +271,8 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
   const int nIT = a.I / DT_GU_ROWS, nHT = a.H / DT_DN_ROWS;
   DtList lst;
   lst.init(a.hdr[0], a.dIT, a.dHT, a.dG, a.H >> 8, a.I >> 8, (int)blockIdx.x);
-  int n_items = a.gu_only ? lst.cntGU : lst.total;
+  int n_items = a.gu_only ? lst.cntGU : 0;                                      // only the gate/up form is dispatched (the digit-plane slot holds two rows)
+  if (!a.gu_only && threadIdx.x == 0) atomicOr(a.err, 0x1000u);
   if (n_items > DT_TBL) { if (threadIdx.x == 0) atomicOr(a.err, 0x1000u); n_items = 0; }   // the launcher sizes the grid so that this does not happen
   for (int j = threadIdx.x; j < n_items * kGroupRows; j += DT_THREADS) {       // records, row ranges, activation rows and their digit units
     const int i = j >> 3, c = j & 7;
@@ -283,7 +285,10 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
       const size_t gj = (size_t)(info >> 16) * kGroupRows + c;
       tbl_row[j] = a.dw.g_row[gj]; tbl_unit[j] = a.dw.g_unit[gj];
     }
-    if (c == 0) { tbl[i].rec = g.rec; tbl[i].start = g.start; tbl[i].info = info | ((uint32_t)g.n << 1); }
+    if (c == 0) {
+      if (g.n > DT_B / 1024) atomicOr(a.err, 0x1000u);                            // the grouping kernel was asked for groups of ≤ 2 rows
+      tbl[i].rec = g.rec; tbl[i].start = g.start; tbl[i].info = info | ((uint32_t)min(g.n, DT_B / 1024) << 1);
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -332,124 +337,28 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
       DT_TRACE_PUT(0, tw); DT_TRACE_PUT(1, clock64() - t_begin); DT_TRACE_PUT(2, (long long)it);
     }
   } else if (warp == DT_W_DIG) {
-    // ------------------------------------------------------------------------------------------------ digit planes: one warp.  Items are taken four at a time: the
-    // eight lanes of quad j serve item base + j (lane c of the quad: row c of the item's group), so what the four items need
-    // before their copies can start is fetched and worked out side by side, and the next four items' fetches are in flight
-    // while this four's copies are issued.
-    uint32_t it = 0;
-    bool ok = true;
-    [[maybe_unused]] long long tw = 0, tr = 0;
-    // the 64-value slices of a y row were digitised against their own exponents (I / 64 bytes per row, rows padded to 8 bytes)
-    uint2 pre[4] = {make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u)};
-    int pre_item = -1;
-    const int nw8 = (nIT + 7) >> 3, nw4 = (nIT + 3) >> 2, ql = lane & 7, quad = lane >> 3;
-    auto fetch_exps = [&](const DtEnt& e, int item) {
-      if (ql < ent_n(e)) {
-        const uint2* p8 = reinterpret_cast<const uint2*>(a.dw.yexp + (size_t)(e.start + ql) * (nw8 * 8));
-#pragma unroll
-        for (int w = 0; w < 4; ++w) pre[w] = w < nw8 ? __ldcg(p8 + w) : make_uint2(0u, 0u);
-      }
-      pre_item = item;
-    };
-    // a row is complete when none of its I / 64 exponent bytes is zero (the prep kernel clears them, a biased exponent is never 0)
-    auto row_complete = [&](int item) {
-      if (pre_item != item) return false;
-      const uint32_t wds[8] = {pre[0].x, pre[0].y, pre[1].x, pre[1].y, pre[2].x, pre[2].y, pre[3].x, pre[3].y};
-      bool all = true;
-#pragma unroll
-      for (int w = 0; w < 8; ++w) if (w < nw4 && __vcmpeq4(wds[w], 0u)) all = false;
-      return all;
-    };
-    for (int base0 = 0; base0 < n_items && ok; base0 += 4) {
-      const int my = base0 + quad;
-      const bool valid = my < n_items;
-      const DtEnt e = tbl[valid ? my : base0];
-      const int k = ent_kind(e), n = ent_n(e), nkb = (k ? a.I : a.H) >> 8;
-      const bool act = valid && ql < n;
-      const uint8_t* src = nullptr;
-      bool ready = true;
-      // what an item's copies need: the source of the row's planes; its unit for the epilogue; for a down item the block-scale codes
-      // that bring the slices of a y row onto one reference, 8 binades under the row's largest exponent (e4m3 reaches 2^8 up and
-      // 2^-9 down from there)
-      auto meta = [&]() {
-        float unit;
-        if (k) {
-          src = a.dw.ydig + (size_t)(e.start + ql) * nkb * 1024;
-          // four exponents per word, handled bytewise: e4m3 code of 2^(ex - eref) = (ex - eref + 7) << 3 for the normal range
-          const uint32_t wds[8] = {pre[0].x, pre[0].y, pre[1].x, pre[1].y, pre[2].x, pre[2].y, pre[3].x, pre[3].y};
-          uint32_t m4 = 0u;
-#pragma unroll
-          for (int w = 0; w < 8; ++w) if (w < nw4) m4 = __vmaxu4(m4, wds[w]);
-          const int emax = (int)max(max(m4 & 0xffu, (m4 >> 8) & 0xffu), max((m4 >> 16) & 0xffu, m4 >> 24));
-          const int eref = max(emax, 30) - 8;
-          const uint32_t off4 = 0x01010101u * (uint32_t)(eref - 7);                // ex - off = ex - eref + 7
-          uint32_t* codes = reinterpret_cast<uint32_t*>(sfbc + (my & 15) * 256 + ql * 32);
-#pragma unroll
-          for (int w = 0; w < 8; ++w) {
-            if (w < nw4) {
-              const uint32_t t4 = __vsubus4(wds[w], off4);                        // max(ex - eref + 7, 0) per byte, ≤ 15
-              uint32_t c4 = t4 << 3;
-              if (__vcmpeq4(t4, 0u)) {                                            // a slice 2^15 or more under the row's largest: subnormal codes 2^-7 … 2^-9, or nothing
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                  const int d = (int)((wds[w] >> (8 * b)) & 0xffu) - eref;
-                  if (d < -6) c4 = (c4 & ~(0xffu << (8 * b))) | ((d >= -9 ? (uint32_t)(1 << (d + 9)) : 0u) << (8 * b));
-                }
-              }
-              codes[w] = c4;
-            }
-          }
-          unit = dt_unit(eref);
-        } else {
-          src = a.dw.xdig + (size_t)tbl_row[my * 8 + ql] * nkb * 1024;
-          unit = tbl_unit[my * 8 + ql];
-        }
-        rowsc[(my & 15) * 8 + ql] = unit;
-      };
-      if (act) {
-        if (k && !row_complete(my)) ready = false;
-        else meta();
-      }
-      // the next four items' exponents
-      if (my + 4 < n_items) { const DtEnt e4 = tbl[my + 4]; if (ent_kind(e4) && ready) fetch_exps(e4, my + 4); }
-      for (int j = 0; j < 4 && base0 + j < n_items && ok; ++j) {
-        // item base + j: wait for its y rows if they were not complete above
-        if (quad == j && act && !ready) {
-          [[maybe_unused]] const long long t_ = clock64();
-          uint32_t spins = 0;
-          for (;;) {
-            fetch_exps(e, my);
-            if (row_complete(my)) break;
-            if (++spins > (1u << 22)) { atomicOr(a.err, 0x20u); ok = false; break; }
-            __nanosleep(40);
-          }
-          if (ok) meta();
-          if (my + 4 < n_items) { const DtEnt e4 = tbl[my + 4]; if (ent_kind(e4)) fetch_exps(e4, my + 4); }
-#ifdef HB_DTC_TRACE
-          tr += clock64() - t_;
-#endif
-        }
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        const int jk = __shfl_sync(0xffffffffu, k, 8 * j), jn = __shfl_sync(0xffffffffu, n, 8 * j), jnkb = __shfl_sync(0xffffffffu, nkb, 8 * j);
-        if (jk) fence_proxy_async_global();                                     // the planes were written with ordinary stores, the copies below read them through the async proxy
-        for (int kb = 0; kb < jnkb; ++kb, ++it) {
+    // ------------------------------------------------------------------------------------------------ digit planes: one thread walks the items' stages in ring
+    // order — wait for the slot, announce the bytes, copy the 1 KB plane atoms of the group's one or two rows (a row's planes of
+    // consecutive k windows are contiguous in global memory).  (In order, by one thread: a wait by parity tells apart only
+    // neighbouring phases of a slot, so nobody may wait for a slot more than one ring cycle ahead.)
+    if (lane == 0) {
+      const int nkb = a.H >> 8;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int ii = 0; ii < n_items && ok; ++ii) {
+        const int n = ent_n(tbl[ii]);
+        const uint8_t* s0 = a.dw.xdig + (size_t)tbl_row[ii * kGroupRows] * nkb * 1024;
+        const uint8_t* s1 = n > 1 ? a.dw.xdig + (size_t)tbl_row[ii * kGroupRows + 1] * nkb * 1024 : nullptr;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
           const uint32_t stage = it % DT_ST;
-          if (lane == 0) DT_TIMED(tw, ok = mbar_wait(&empty[stage], ((it / DT_ST) & 1) ^ 1, a.err, 0x2u));
-          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-          if (!ok) break;
-          if (lane == 0) {
-            DT_STAMP(it, 3);
-            mbar_arrive(&bmeta[stage]);                                           // the scale warps may read this item's codes
-            mbar_expect_tx(&full[stage], (uint32_t)jn * 1024u);
-          }
-          __syncwarp();
-          if (quad == j && act) bulk_g2s(sm + stage * DT_STAGE + DT_A + ql * 1024, src + (size_t)kb * 1024, 1024, &full[stage]);
-          if (lane == 0) DT_STAMP(it, 7);
+          if (!(ok = mbar_wait(&empty[stage], ((it / DT_ST) & 1) ^ 1, a.err, 0x2u))) break;
+          uint8_t* dst = sm + stage * DT_STAGE + DT_A;
+          mbar_expect_tx(&full[stage], (uint32_t)n * 1024u);
+          bulk_g2s(dst, s0 + (size_t)kb * 1024, 1024, &full[stage]);
+          if (s1) bulk_g2s(dst + 1024, s1 + (size_t)kb * 1024, 1024, &full[stage]);
         }
       }
     }
-    if (lane == 0) { DT_TRACE_PUT(3, tw); DT_TRACE_PUT(4, tr); }
   } else if (warp >= DT_W_SC0) {
     // ------------------------------------------------------------------------------------------------ weight scales: thread r owns row r of each A tile
     // A row's 16 scale bytes of a window = 4 k-steps × 4 scales.  In tensor memory the scales of a k-step take four columns; the
@@ -803,7 +712,7 @@ bool hbk_moe_dtc_supported(int H, int I) {
 bool hbk_moe_dtc_gu_fits(const hb_ctx* ctx, int P, int E, int H, int I) {
   int grid = ctx->sm_count;
   if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
-  const long long G = P < E + 1 + P / kGroupRows ? P : E + 1 + P / kGroupRows;
+  const long long G = P < E + 1 + P / 2 ? P : E + 1 + P / 2;              // groups of ≤ 2 rows: at most one odd group per expert
   return (G * (I / DT_GU_ROWS) + grid - 1) / grid <= DT_TBL;
 }
 
