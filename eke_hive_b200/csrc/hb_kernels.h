@@ -83,6 +83,10 @@ int hbk_moe_dtc_setup(hb_ctx* ctx);
 // gate/up pass alone on the tensor cores, between the streaming path's grouping kernel and its down kernel
 int hbk_moe_dtc_gu_run(hb_ctx* ctx, const void* x, int x_ld, int M, const uint8_t* const* tab, int n_tab, const uint8_t* shared_rec, int P, int H, int I,
                        float limit, void* ws, const uint32_t* wait_flags, int wait_n, const uint32_t* wait_step, cudaStream_t st);
+// down pass on the tensor cores behind it (digit planes of y, 128-row tiles of w2); with `red` it sums the rows' pairs itself
+namespace hb { struct ReduceArgs; }
+bool hbk_moe_dtc_down_fits(const hb_ctx* ctx, int n_pairs, int E, int H, int I);
+int hbk_moe_dtc_down_run(hb_ctx* ctx, int P, int H, int I, void* ws, const hb::ReduceArgs* red, unsigned int* fin, cudaStream_t st);
 
 // dense GEMV (k_dense.cu)
 int hbk_dense_setup(hb_ctx* ctx);

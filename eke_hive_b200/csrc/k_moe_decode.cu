@@ -647,6 +647,12 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
       if ((r = hbk_moe_dtc_gu_run(ctx, x, x_ld, src.M, src.tab + (size_t)src.li * src.E, src.E, src.shared_rec, P, H, I, limit, ws, src.wait_flags, src.wait_n, src.wait_step, st)))
         return r;
     } else if ((r = hb_launch(ctx, "moe_gate_up", true, kg.fn, dim3(grid), dim3(kg.threads), kg.smem(s), st, sa))) return r;
+    if (tc_gu && routed && !red.ep && (ctx->flags & HB_FLAG_DECODE_TC_DOWN) && hbk_moe_dtc_down_fits(ctx, P, src.E, H, I)) {
+      const ReduceArgs ra{w.part, w.pos_of, w.pw, src.M, src.K, H, src.shared_rec ? 1 : 0, reinterpret_cast<const __nv_bfloat16*>(red.shared), red.lg, red.ld, red.col,
+                          reinterpret_cast<__nv_bfloat16*>(red.out_bf16), red.out_f32, reinterpret_cast<__nv_bfloat16*>(red.shared_out), ga.sh_row0, ga.sh_rows,
+                          hbk_ep_push{}, ctx->dev_err, P};
+      return hbk_moe_dtc_down_run(ctx, P, H, I, ws, &ra, reinterpret_cast<unsigned int*>(w.hdr + 3), st);
+    }
     plan_stream(ctx, kd, &s, &c);
     sd.stages = s;
     grid = ctx->sm_count * c;

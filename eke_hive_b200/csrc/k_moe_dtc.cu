@@ -59,9 +59,10 @@ static_assert(DT_ROWS <= kGroupRows, "groups of the grouping kernel");
 struct DtcMeta { unsigned long long anchor; };
 
 struct DtcWs {
-  uint8_t* xdig;        // [rows][H/256][8 planes][128 bytes], swizzled
+  uint8_t* xdig;        // [rows][K/256][8 planes][128 bytes], swizzled
   float* xs;            // [rows] unit of a row's digits (a power of two)
 };
+struct DtcWs2 { DtcWs x, y; };   // planes of the activation rows (K = H) and of the y rows (K = I)
 
 // Division of a 32-bit unsigned number by a divisor fixed for the whole launch: multiply-high and shift (exact for n < 2^31).
 struct DtDiv {
@@ -75,14 +76,18 @@ struct DtDiv {
 };
 
 struct DtcArgs {
-  const int* hdr; const Group* groups; const int* s_row;  // the grouping kernel's list: hdr[0] groups, rows of a group = s_row[start .. start + n)
-  int H, I; float limit;
+  const int* hdr; const Group* groups;                    // the grouping kernel's list: hdr[0] groups
+  const int* s_row;                                       // gate/up: rows of a group = s_row[start .. start + n); down (nullptr): positions start .. start + n
+  int down;                                               // 0: gate/up (A tile = 64 gate + 64 up rows, out = y); 1: down (A tile = 128 rows of w2, out = per-pair rows)
+  int K, out_ld; float limit;                             // K: inner dimension (H | I); out_ld: row length of the output (I | H)
   DtDiv dIT, dG;                                          // dividers by the items per group and by the grid size
-  hb_rec_layout L;
+  uint32_t off_w, off_s0, off_s1, off_g;                  // record offsets: the matrix of the tile's first half, the scales of both halves, the global scales
+  int row2, trows;                                        // matrix rows from the first 64-row box of an item to the second; matrix rows an item advances per half
   const CUtensorMap* maps; const DtcMeta* meta;           // maps[variant]
   int pitch, gstep, pshift;                               // pshift: log2(pitch) when the pitch divides 4096, else -1
-  DtcWs dw;
-  __nv_bfloat16* y;                                       // out: bf16 [position, I]
+  DtcWs dw;                                               // the digit planes of the B operand's rows
+  __nv_bfloat16* out;                                     // bf16 [position, out_ld]
+  unsigned int* fin; ReduceArgs red; int red_on;          // down: the sums over each row's pairs after the CTAs have met
   uint32_t* err;
 };
 
@@ -144,8 +149,9 @@ __device__ __forceinline__ size_t dt_dig_off(size_t r, int K, int k0, int p) {
 }
 
 // ---- the work list of a CTA -----------------------------------------------------------------------------------------------------------
-// Item j of the launch = (group j / (I/64), rows [64 t, 64 t + 64) of I with t = j mod (I/64)); it goes to CTA j mod grid, so the items
-// of one group run on different CTAs at the same time.  Entry x of CTA c is item c + x·grid: computed directly.
+// Item j of the launch = (group j / T, tile t = j mod T); gate/up: T = I/64, the tile = rows [64 t, 64 t + 64) of gate and of up; down:
+// T = H/128, the tile = rows [128 t, 128 t + 128) of w2.  It goes to CTA j mod grid, so the items of one group run on different CTAs
+// at the same time.  Entry x of CTA c is item c + x·grid: computed directly.
 struct DtEnt { const uint8_t* rec; int start; uint32_t info; };      // info: bits 1-4 rows of the group, bits 5-15 t, bits 16-31 g
 static_assert(sizeof(DtEnt) == 16, "DtEnt layout");
 __device__ __forceinline__ int ent_n(const DtEnt& e) { return (int)((e.info >> 1) & 15u); }
@@ -202,7 +208,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
     const int i = j / DT_ROWS, c = j - i * DT_ROWS;
     const int item = c0 + i * grid, gi = (int)a.dIT.div((uint32_t)item);
     const Group g = a.groups[gi];
-    tbl_row[j] = (uint16_t)(c < g.n ? a.s_row[g.start + c] : 0);
+    tbl_row[j] = (uint16_t)(c < g.n ? (a.s_row ? a.s_row[g.start + c] : g.start + c) : 0);
     if (c == 0) {
       if (g.n > DT_ROWS) atomicOr(a.err, 0x1000u);                               // the grouping kernel was asked for groups of ≤ DT_ROWS rows
       tbl[i].rec = g.rec; tbl[i].start = g.start;
@@ -213,7 +219,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const int nkb = a.H >> 8;                                                     // stages per item
+  const int nkb = a.K >> 8;                                                     // stages per item
 
   if (warp == DT_W_TMA) {
     // ------------------------------------------------------------------------------------------------ weight boxes: one thread
@@ -222,10 +228,9 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
       bool ok = true;
       [[maybe_unused]] long long tw = 0, t_begin = clock64();
       const unsigned long long anchor = a.meta->anchor;
-      const int up_rows = (int)((a.L.w3 - a.L.w1) / (unsigned long long)a.pitch);
       for (int ii = 0; ii < n_items && ok; ++ii) {
         const DtEnt e = tbl[ii];
-        const unsigned long long addr = reinterpret_cast<unsigned long long>(e.rec) + a.L.w1, delta = addr - anchor;
+        const unsigned long long addr = reinterpret_cast<unsigned long long>(e.rec) + a.off_w, delta = addr - anchor;
         unsigned long long row;
         int v = 0;
         if (a.pshift >= 0) row = delta >> a.pshift;                               // the pitch divides 4096: every matrix is a whole number of rows above the anchor
@@ -238,7 +243,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
         if (addr < anchor || row + (1ull << 24) >= (1ull << 31)) { atomicOr(a.err, 0x400000u); break; }
         const CUtensorMap* map = a.maps + v;
         if (!((seen >> v) & 1u)) { tmap_acquire(map); seen |= 1u << v; }
-        const int r0 = (int)row + ent_t(e) * DT_GU_ROWS, r1 = r0 + up_rows;
+        const int r0 = (int)row + ent_t(e) * a.trows, r1 = r0 + a.row2;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const uint32_t stage = it % DT_ST;
           DT_TIMED(tw, ok = mbar_wait(&empty[stage], ((it / DT_ST) & 1) ^ 1, a.err, 0x1u));
@@ -246,8 +251,8 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
           DT_STAMP(it, 0);
           const uint32_t sb = base + stage * DT_STAGE;
           mbar_expect_tx(&full[stage], DT_A);
-          tma_load_2d(sb, map, kb * 128, r0, &full[stage]);                       // 64 gate rows
-          tma_load_2d(sb + DT_A / 2, map, kb * 128, r1, &full[stage]);            // 64 up rows
+          tma_load_2d(sb, map, kb * 128, r0, &full[stage]);                       // 64 gate rows | rows 0-63 of the w2 tile
+          tma_load_2d(sb + DT_A / 2, map, kb * 128, r1, &full[stage]);            // 64 up rows | rows 64-127
           DT_STAMP(it, 1);
         }
       }
@@ -291,7 +296,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
         prow = nullptr;
         if (pii < n_items) {
           const DtEnt e = tbl[pii++];
-          prow = e.rec + (r < 64 ? a.L.s1 : a.L.s3) + (size_t)(ent_t(e) * DT_GU_ROWS + (r & 63)) * (a.H / 16);
+          prow = e.rec + (r < 64 ? a.off_s0 : a.off_s1) + (size_t)(ent_t(e) * a.trows + (r & 63)) * (a.K / 16);
           pkb = 0;
         }
       }
@@ -386,7 +391,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
     for (int ii = set; ii < n_items && ok; ii += 2) {
       const DtEnt e = tbl[ii];
       const int n = ent_n(e), t = ent_t(e);
-      const float gsc = __ldg(reinterpret_cast<const float*>(e.rec + a.L.g) + (tl < 64 ? 0 : 1));   // the record's global scale this thread applies
+      const float gsc = __ldg(reinterpret_cast<const float*>(e.rec + a.off_g) + (a.down ? 2 : tl < 64 ? 0 : 1));   // the record's global scale this thread applies
       float un[DT_ROWS];                                                         // units of the rows' digits: fetched while the MMAs run
 #pragma unroll
       for (int c = 0; c < DT_ROWS; ++c) un[c] = c < n ? __ldg(a.dw.xs + tbl_row[ii * DT_ROWS + c]) : 0.f;
@@ -411,6 +416,13 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
       float gu[DT_ROWS];
 #pragma unroll
       for (int c = 0; c < DT_ROWS; ++c) gu[c] = c < n ? bf16r(val[c] * un[c] * gsc) : 0.f;
+      if (a.down) {
+        // a pair's row of the down projection, bf16 (the routing weight is applied where the pairs are summed): 128 threads, 256 contiguous bytes
+#pragma unroll
+        for (int c = 0; c < DT_ROWS; ++c)
+          if (c < n) a.out[(size_t)(e.start + c) * a.out_ld + t * 128 + tl] = __float2bfloat16(gu[c]);
+        continue;
+      }
       if (tl >= 64) {
 #pragma unroll
         for (int c = 0; c < DT_ROWS; ++c) if (c < n) ex[c * 64 + (tl - 64)] = gu[c];
@@ -427,7 +439,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
           if (c < n) {
             float gv = gu[c], uv = upv[c];
             if (a.limit > 0.f) { uv = fminf(fmaxf(uv, -a.limit), a.limit); gv = fminf(gv, a.limit); }
-            a.y[(size_t)(e.start + c) * a.I + t * DT_GU_ROWS + tl] = __float2bfloat16(gv / (1.f + __expf(-gv)) * uv);
+            a.out[(size_t)(e.start + c) * a.out_ld + t * DT_GU_ROWS + tl] = __float2bfloat16(gv / (1.f + __expf(-gv)) * uv);
           }
         }
       }
@@ -437,6 +449,23 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
   tc_fence_before();
   __syncthreads();
   if (warp == DT_W_MMA) { tc_fence_after(); tmem_dealloc(tmem, DT_TMEM_COLS); }
+  if (!a.red_on) return;
+  // Down pass of the routed form: the sums over each row's pairs.  One CTA per SM and no more CTAs than SMs — all are resident, so
+  // they can meet: a CTA announces that its rows are written, waits (bounded) until every CTA has, and takes its share of the
+  // (row, column pair) units.
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(a.fin, 1u);
+    uint32_t spins = 0;
+    while (*reinterpret_cast<volatile unsigned int*>(a.fin) < gridDim.x) {
+      if (++spins > (1u << 22)) { atomicOr(a.err, 0x8000u); break; }
+      __nanosleep(32);
+    }
+    __threadfence();
+  }
+  __syncthreads();
+  const size_t units = (size_t)a.red.M * a.red.H / 2, step = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < units; i += step) reduce_routed_unit(a.red, i);
 }
 
 // The digit planes of the activation rows alone (the gate/up pass on the tensor cores behind the streaming path's grouping kernel):
@@ -445,18 +474,20 @@ __global__ void __launch_bounds__(DT_THREADS, 1) moe_dtc_layer_kernel(const DtcA
 // own wait (for the grouping kernel to finish) LAST: the kernel behind it then finds both the planes and the group list complete.
 // wait_flags: the rows are pushed by other ranks (expert parallel) — every CTA waits, bounded, for the same flags the grouping kernel
 // waits for before it reads its row.
-struct XdigArgs { const __nv_bfloat16* x; int x_ld, H; DtcWs dw; const uint32_t* wait_flags; int wait_n; const uint32_t* wait_step; uint32_t* err; };
+// wait_first: the rows are the previous kernel's output (the y rows between the two passes): wait for it before reading.
+struct XdigArgs { const __nv_bfloat16* x; int x_ld, H; DtcWs dw; const uint32_t* wait_flags; int wait_n; const uint32_t* wait_step; uint32_t* err; int wait_first; };
 __global__ void __launch_bounds__(256) moe_xdig_kernel(const XdigArgs a) {
   __shared__ int s_red[8];
   const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   griddep_launch();
+  if (a.wait_first) griddep_wait();
   if (a.wait_flags) {
     if ((int)threadIdx.x < a.wait_n && !*reinterpret_cast<volatile uint32_t*>(a.err)) ep_wait_flag(a.wait_flags + threadIdx.x, *a.wait_step + 1u, a.err, 0x40000u);
     __syncthreads();
   }
   const uint32_t* xr = reinterpret_cast<const uint32_t*>(a.x + (size_t)m * a.x_ld);
   uint32_t am = 0;
-  for (int e2 = threadIdx.x; e2 < a.H / 2; e2 += 256) { const uint32_t w2 = __ldg(xr + e2); am = max(am, max(w2 & 0x7fffu, (w2 >> 16) & 0x7fffu)); }
+  for (int e2 = threadIdx.x; e2 < a.H / 2; e2 += 256) { const uint32_t w2 = __ldcg(xr + e2); am = max(am, max(w2 & 0x7fffu, (w2 >> 16) & 0x7fffu)); }
   for (int o = 16; o > 0; o >>= 1) am = max(am, __shfl_xor_sync(0xffffffffu, am, o));
   if (lane == 0) s_red[warp] = (int)am;
   __syncthreads();
@@ -465,7 +496,7 @@ __global__ void __launch_bounds__(256) moe_xdig_kernel(const XdigArgs a) {
   const int eb = dt_row_exponent(am);
   if (threadIdx.x == 0) a.dw.xs[m] = dt_unit(eb);
   for (int u = threadIdx.x; u < a.H / 8; u += 256) {
-    const uint4 q4 = __ldg(reinterpret_cast<const uint4*>(xr) + u);
+    const uint4 q4 = __ldcg(reinterpret_cast<const uint4*>(xr) + u);
     const uint32_t v4[4] = {q4.x, q4.y, q4.z, q4.w};
     uint32_t pl[8];
     dt_digits8(v4, eb, pl);
@@ -473,7 +504,7 @@ __global__ void __launch_bounds__(256) moe_xdig_kernel(const XdigArgs a) {
     for (int p = 0; p < 8; ++p) *reinterpret_cast<uint32_t*>(a.dw.xdig + dt_dig_off((size_t)m, a.H, u * 8, p)) = pl[p];
   }
   fence_proxy_async_global();                                                  // the planes are read through the async proxy (bulk copies) by the next kernel
-  griddep_wait();
+  if (!a.wait_first) griddep_wait();
 }
 
 // Stamps the anchored base into the variants of the tensor map (one block; runs when the maps are first needed).
@@ -510,57 +541,83 @@ using namespace hb;
 namespace {
 int gcd_int(int a, int b) { while (b) { const int t = a % b; a = b; b = t; } return a; }
 
-size_t dtc_carve(void* ws, size_t off, int n, int H, DtcWs* w) {
+size_t dtc_carve(void* ws, size_t off, int n, int H, int I, DtcWs2* w) {
   auto take = [&](size_t b) { void* r = ws ? static_cast<char*>(ws) + off : nullptr; off += al256(b); return r; };
-  DtcWs t;
-  t.xdig = (uint8_t*)take((size_t)n * 4 * H); t.xs = (float*)take((size_t)n * 4);
+  DtcWs2 t;
+  t.x.xdig = (uint8_t*)take((size_t)n * 4 * H); t.x.xs = (float*)take((size_t)n * 4);
+  t.y.xdig = (uint8_t*)take((size_t)n * 4 * I); t.y.xs = (float*)take((size_t)n * 4);
   if (w) *w = t;
   return off;
 }
+constexpr size_t kMapSetBytes = (size_t)DT_VMAX * sizeof(CUtensorMap) + 256;   // the variants of one map and its DtcMeta
+int dtc_grid(const hb_ctx* ctx) {
+  int grid = ctx->sm_count;
+  if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
+  return grid;
+}
+long long dtc_groups(int P, int E) { return P < E + 1 + P / DT_ROWS ? P : E + 1 + P / DT_ROWS; }   // groups of ≤ DT_ROWS rows: at most one partly filled group per expert
 }  // namespace
 
 bool hbk_moe_dtc_supported(int H, int I) {
   if (H <= 0 || I <= 0 || H % 256 || I % 256 || I / DT_GU_ROWS > 2047) return false;
-  const int p0 = H / 2;
-  return p0 / gcd_int(p0, 4096) <= DT_VMAX;
+  const int p0 = H / 2, p1 = I / 2;
+  return p0 / gcd_int(p0, 4096) <= DT_VMAX && p1 / gcd_int(p1, 4096) <= DT_VMAX && H / 128 <= 2047;
 }
 
 // a CTA's list holds its share of the items
 bool hbk_moe_dtc_gu_fits(const hb_ctx* ctx, int P, int E, int H, int I) {
-  int grid = ctx->sm_count;
-  if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
-  const long long G = P < E + 1 + P / DT_ROWS ? P : E + 1 + P / DT_ROWS;  // groups of ≤ DT_ROWS rows: at most one partly filled group per expert
+  const int grid = dtc_grid(ctx);
+  const long long G = dtc_groups(P, E);
   return G < 65536 && (G * (I / DT_GU_ROWS) + grid - 1) / grid <= DT_TBL;
 }
+bool hbk_moe_dtc_down_fits(const hb_ctx* ctx, int P, int E, int H, int I) {
+  const int grid = dtc_grid(ctx);
+  const long long G = dtc_groups(P, E);
+  return G < 65536 && P < 65536 && (G * (H / 128) + grid - 1) / grid <= DT_TBL && grid <= ctx->sm_count;
+}
 
-size_t hbk_moe_dtc_ws_extra(int n, int H, int I) { return hbk_moe_dtc_supported(H, I) ? dtc_carve(nullptr, 0, n, H, nullptr) : 0; }
+size_t hbk_moe_dtc_ws_extra(int n, int H, int I) { return hbk_moe_dtc_supported(H, I) ? dtc_carve(nullptr, 0, n, H, I, nullptr) : 0; }
 
 int hbk_moe_dtc_setup(hb_ctx* ctx) {
   HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_dtc_layer_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM));
-  HB_CUDA(ctx, cudaMalloc(&ctx->dtc_maps, (size_t)DT_VMAX * sizeof(CUtensorMap) + 256));
-  HB_CUDA(ctx, cudaMemset(ctx->dtc_maps, 0, (size_t)DT_VMAX * sizeof(CUtensorMap) + 256));
+  HB_CUDA(ctx, cudaMalloc(&ctx->dtc_maps, 2 * kMapSetBytes));
+  HB_CUDA(ctx, cudaMemset(ctx->dtc_maps, 0, 2 * kMapSetBytes));
   return HB_OK;
 }
 
-// the tensor map for H, anchored below the records of `tab`: made on first use and whenever the shape changes
+// the tensor maps of both passes (row pitch H/2 for gate and up, I/2 for down), anchored below the records of `tab`: made on first
+// use and whenever the shape changes
 static int dtc_maps_for(hb_ctx* ctx, const uint8_t* const* tab, int n_tab, const uint8_t* shared_rec, int H, int I, cudaStream_t st) {
   if (ctx->dtc_H == H && ctx->dtc_I == I) return HB_OK;
   TcEncodeFn fn = tc_encode_fn();
   HB_REQUIRE(ctx, fn, HB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  DtcMapTpl tpl;
-  const int pitch = H / 2;
-  const cuuint64_t dims[2] = {(cuuint64_t)pitch, (cuuint64_t)1 << 31}, strides[1] = {(cuuint64_t)pitch};
-  const cuuint32_t box[2] = {128u, DT_GU_ROWS}, estr[2] = {1, 1};
-  const CUresult cr = fn(&tpl.t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, ctx->dtc_maps, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  HB_REQUIRE(ctx, cr == CUDA_SUCCESS, HB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for pitch %d", (int)cr, pitch);
-  CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(ctx->dtc_maps);
-  DtcMeta* meta = reinterpret_cast<DtcMeta*>(maps + DT_VMAX);
-  const int r = hb_launch(ctx, "moe_dtc_anchor", false, moe_dtc_anchor_kernel, dim3(1), dim3(256), 0, st, tpl, tab, n_tab, shared_rec, pitch, gcd_int(pitch, 4096),
-                          maps, meta);
-  if (r) return r;
+  for (int kind = 0; kind < 2; ++kind) {
+    DtcMapTpl tpl;
+    const int pitch = (kind ? I : H) / 2;
+    const cuuint64_t dims[2] = {(cuuint64_t)pitch, (cuuint64_t)1 << 31}, strides[1] = {(cuuint64_t)pitch};
+    const cuuint32_t box[2] = {128u, 64u}, estr[2] = {1, 1};
+    CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(static_cast<char*>(ctx->dtc_maps) + kind * kMapSetBytes);
+    const CUresult cr = fn(&tpl.t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, maps, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    HB_REQUIRE(ctx, cr == CUDA_SUCCESS, HB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for pitch %d", (int)cr, pitch);
+    DtcMeta* meta = reinterpret_cast<DtcMeta*>(maps + DT_VMAX);
+    const int r = hb_launch(ctx, "moe_dtc_anchor", false, moe_dtc_anchor_kernel, dim3(1), dim3(256), 0, st, tpl, tab, n_tab, shared_rec, pitch,
+                            gcd_int(pitch, 4096), maps, meta);
+    if (r) return r;
+  }
   ctx->dtc_H = H; ctx->dtc_I = I;
   return HB_OK;
+}
+
+// what both passes share: the list, the map set of the pass, the dividers
+static void dtc_args_common(hb_ctx* ctx, const DecodeWs& w, int kind, int K, int items_per_group, DtcArgs* a) {
+  a->hdr = w.hdr; a->groups = w.groups; a->down = kind; a->K = K; a->err = ctx->dev_err;
+  a->maps = reinterpret_cast<const CUtensorMap*>(static_cast<const char*>(ctx->dtc_maps) + kind * kMapSetBytes);
+  a->meta = reinterpret_cast<const DtcMeta*>(a->maps + DT_VMAX);
+  a->pitch = K / 2; a->gstep = gcd_int(K / 2, 4096);
+  a->pshift = -1;
+  for (int b = 7; b <= 12; ++b) if (a->pitch == (1 << b)) a->pshift = b;
+  a->dIT.set((uint32_t)items_per_group); a->dG.set((uint32_t)dtc_grid(ctx));
 }
 
 #ifdef HB_DTC_TRACE
@@ -577,23 +634,42 @@ extern "C" __attribute__((visibility("default"))) int hb_dtc_stage_read(long lon
 int hbk_moe_dtc_gu_run(hb_ctx* ctx, const void* x, int x_ld, int M, const uint8_t* const* tab, int n_tab, const uint8_t* shared_rec, int P, int H, int I,
                        float limit, void* ws, const uint32_t* wait_flags, int wait_n, const uint32_t* wait_step, cudaStream_t st) {
   DecodeWs w = carve(ws, P, H, I);
-  DtcWs dw;
-  dtc_carve(ws, hbk_moe_decode_ws_bytes(P, H, I) - hbk_moe_dtc_ws_extra(P, H, I), P, H, &dw);
+  DtcWs2 dw;
+  dtc_carve(ws, hbk_moe_decode_ws_bytes(P, H, I) - hbk_moe_dtc_ws_extra(P, H, I), P, H, I, &dw);
   hb_rec_layout L;
   hb_rec_layout_make(H, I, &L);
   int r = dtc_maps_for(ctx, tab, n_tab, shared_rec, H, I, st);
   if (r) return r;
-  XdigArgs xa{reinterpret_cast<const __nv_bfloat16*>(x), x_ld, H, dw, wait_flags, wait_n, wait_step, ctx->dev_err};
+  XdigArgs xa{reinterpret_cast<const __nv_bfloat16*>(x), x_ld, H, dw.x, wait_flags, wait_n, wait_step, ctx->dev_err, 0};
   if ((r = hb_launch(ctx, "moe_xdig", true, moe_xdig_kernel, dim3(M), dim3(256), 0, st, xa))) return r;
   DtcArgs a{};
-  a.hdr = w.hdr; a.groups = w.groups; a.s_row = w.s_row; a.H = H; a.I = I; a.limit = limit; a.L = L;
-  a.maps = reinterpret_cast<const CUtensorMap*>(ctx->dtc_maps); a.meta = reinterpret_cast<const DtcMeta*>(a.maps + DT_VMAX);
-  a.pitch = H / 2; a.gstep = gcd_int(H / 2, 4096);
-  a.pshift = -1;
-  for (int b = 7; b <= 12; ++b) if (a.pitch == (1 << b)) a.pshift = b;
-  a.dw = dw; a.y = w.y; a.err = ctx->dev_err;
-  int grid = ctx->sm_count;
-  if (ctx->max_ctas > 0 && grid > ctx->max_ctas) grid = ctx->max_ctas;
-  a.dIT.set((uint32_t)(I / DT_GU_ROWS)); a.dG.set((uint32_t)grid);
-  return hb_launch(ctx, "moe_gate_up_tc", true, moe_dtc_layer_kernel, dim3(grid), dim3(DT_THREADS), (size_t)DT_SMEM, st, a);
+  dtc_args_common(ctx, w, 0, H, I / DT_GU_ROWS, &a);
+  a.s_row = w.s_row; a.out_ld = I; a.limit = limit;
+  a.off_w = (uint32_t)L.w1; a.off_s0 = (uint32_t)L.s1; a.off_s1 = (uint32_t)L.s3; a.off_g = (uint32_t)L.g;
+  a.row2 = (int)((L.w3 - L.w1) / (size_t)(H / 2)); a.trows = DT_GU_ROWS;
+  a.dw = dw.x; a.out = w.y;
+  return hb_launch(ctx, "moe_gate_up_tc", true, moe_dtc_layer_kernel, dim3(dtc_grid(ctx)), dim3(DT_THREADS), (size_t)DT_SMEM, st, a);
+}
+
+// The down pass the same way: digit planes of the P rows of y (launched behind the gate/up kernel; rows past the list's end hold
+// nothing anyone reads), then the tensor-memory kernel over 128-row tiles of w2 writing the per-pair rows; with `red` it also sums
+// the rows' pairs after its CTAs have met (fin: a counter the grouping kernel zeroed).
+int hbk_moe_dtc_down_run(hb_ctx* ctx, int P, int H, int I, void* ws, const ReduceArgs* red, unsigned int* fin, cudaStream_t st) {
+  DecodeWs w = carve(ws, P, H, I);
+  DtcWs2 dw;
+  dtc_carve(ws, hbk_moe_decode_ws_bytes(P, H, I) - hbk_moe_dtc_ws_extra(P, H, I), P, H, I, &dw);
+  hb_rec_layout L;
+  hb_rec_layout_make(H, I, &L);
+  HB_REQUIRE(ctx, ctx->dtc_H == H && ctx->dtc_I == I, HB_ERR_INVALID, "moe_decode: the down pass on the tensor cores follows the gate/up pass of the same shape");
+  XdigArgs xa{w.y, I, I, dw.y, nullptr, 0, nullptr, ctx->dev_err, 1};
+  int r = hb_launch(ctx, "moe_ydig", true, moe_xdig_kernel, dim3(P), dim3(256), 0, st, xa);
+  if (r) return r;
+  DtcArgs a{};
+  dtc_args_common(ctx, w, 1, I, H / 128, &a);
+  a.s_row = nullptr; a.out_ld = H; a.limit = 0.f;
+  a.off_w = (uint32_t)L.w2; a.off_s0 = (uint32_t)L.s2; a.off_s1 = (uint32_t)(L.s2 + (size_t)64 * (I / 16)); a.off_g = (uint32_t)L.g;
+  a.row2 = 64; a.trows = 128;
+  a.dw = dw.y; a.out = w.part;
+  if (red) { a.red = *red; a.fin = fin; a.red_on = 1; }
+  return hb_launch(ctx, red ? "moe_down_reduce_tc" : "moe_down_tc", true, moe_dtc_layer_kernel, dim3(dtc_grid(ctx)), dim3(DT_THREADS), (size_t)DT_SMEM, st, a);
 }

@@ -54,6 +54,8 @@ typedef struct hb_config {
                                      library picks by the number of pairs of the call (40 or more: tensor memory); both engines meet the same
                                      tolerance, and a row's bits do not depend on its batch as long as the engine does not change — pin one
                                      with a flag where that matters */
+#define HB_FLAG_DECODE_TC_DOWN 128 /* decode, routed operators on one GPU: where the gate/up pass runs on the tensor-memory kernel, the down pass does too
+                                     (digit planes of y between the passes; the sums over a row's pairs in the kernel's tail) */
 #define HB_FLAG_LAYER_A4 32       /* hb_moe_layer may run calls of more than 64 rows on the W4A4 grouped GEMM (activations quantised to NVFP4 — the
                                      reference's lossy opt-in, fn_moe_prefill_set_a4).  Without it hb_moe_layer keeps bf16 activations at every
                                      row count: the same numbers as the decode operators, never a silent change of arithmetic */

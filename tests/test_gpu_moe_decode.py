@@ -16,7 +16,7 @@ def E():
     return E
 
 
-@pytest.fixture(params=[8, 64], ids=["mma_sync", "tensor_memory_gate_up"])
+@pytest.fixture(params=[8, 64, 192], ids=["mma_sync", "tensor_memory_gate_up", "tensor_memory_both"])
 def eng(request, E):
     """A context pinned to one of the decode engines of the routed operators (HB_FLAG_DECODE_MMA_SYNC: the streaming kernels throughout;
     HB_FLAG_DECODE_TC_GU: gate/up on the tensor-memory kernel between the streaming path's grouping and down kernels)."""
