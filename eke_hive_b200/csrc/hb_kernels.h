@@ -88,6 +88,11 @@ namespace hb { struct ReduceArgs; }
 bool hbk_moe_dtc_down_fits(const hb_ctx* ctx, int n_pairs, int E, int H, int I);
 int hbk_moe_dtc_down_run(hb_ctx* ctx, int P, int H, int I, void* ws, const hb::ReduceArgs* red, unsigned int* fin, cudaStream_t st);
 
+// the anchored weight maps of both passes (made on first use per shape), for kernels that stream raw code boxes of the records
+int hbk_moe_dtc_maps(hb_ctx* ctx, const uint8_t* const* tab, int n_tab, const uint8_t* shared_rec, int H, int I, cudaStream_t st);
+void hbk_moe_dtc_map_set(const hb_ctx* ctx, int kind, const void** maps, const unsigned long long** anchor);   // kind 0: w1/w3 (pitch H/2), 1: w2 (pitch I/2)
+int hbk_moe_dtc_vmax();
+
 // dense GEMV (k_dense.cu)
 int hbk_dense_setup(hb_ctx* ctx);
 int hbk_moe_prefill_setup(hb_ctx* ctx);

@@ -620,6 +620,17 @@ static void dtc_args_common(hb_ctx* ctx, const DecodeWs& w, int kind, int K, int
   a->dIT.set((uint32_t)items_per_group); a->dG.set((uint32_t)dtc_grid(ctx));
 }
 
+// the same maps for the prefill GEMM with bf16 activations, which streams raw code boxes through them
+int hbk_moe_dtc_maps(hb_ctx* ctx, const uint8_t* const* tab, int n_tab, const uint8_t* shared_rec, int H, int I, cudaStream_t st) {
+  return dtc_maps_for(ctx, tab, n_tab, shared_rec, H, I, st);
+}
+void hbk_moe_dtc_map_set(const hb_ctx* ctx, int kind, const void** maps, const unsigned long long** anchor) {
+  const CUtensorMap* m = reinterpret_cast<const CUtensorMap*>(static_cast<const char*>(ctx->dtc_maps) + kind * kMapSetBytes);
+  *maps = m;
+  *anchor = &reinterpret_cast<const DtcMeta*>(m + DT_VMAX)->anchor;
+}
+int hbk_moe_dtc_vmax() { return DT_VMAX; }
+
 #ifdef HB_DTC_TRACE
 extern "C" __attribute__((visibility("default"))) int hb_dtc_trace_read(long long* out, int n) {
   return (int)cudaMemcpyFromSymbol(out, g_dt_trace, (size_t)n * 8);

@@ -47,7 +47,10 @@ static_assert(PF_SF_COL0 + 48 * PF_ST <= PF_TMEM_COLS, "tensor memory");
 static_assert(PF_STAGE % 1024 == 0, "stage buffers must keep the 1024-byte alignment of the swizzle atom");
 static_assert(PF_SMEM <= 227 * 1024, "shared memory");
 
-struct TileRef { int slot0, rows, expert; };   // 128 consecutive slots (or fewer) of one expert's run of the sorted pairs
+struct TileRef { int slot0, rows, expert; };   // 128 consecutive slots (or fewer) of one expert's run of the sorted pairs (256 for the bf16-activation GEMM)
+}  // namespace hb
+#include "pf_a16.cuh"
+namespace hb {
 
 enum { PF_PLAIN = 0, PF_GU = 1, PF_DOWN = 2 };
 
@@ -389,6 +392,7 @@ __global__ void __launch_bounds__(128, 1) pf_peak_kernel(int n_rounds, uint32_t*
 constexpr int PLAN_THREADS = 1024, PLAN_MAX_CTAS = 64;
 struct PlanArgs {
   const int32_t* ids; int P, E; const uint8_t* const* tab;
+  int bm;                          // pairs per tile
   int* hist;                       // [CTAs][E]
   int* perm; int* pos_of; TileRef* tiles; int* n_tiles; int* n_slots;
   unsigned int* meet;              // two context-owned counters, zero between launches
@@ -424,7 +428,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) pf_plan_kernel(const PlanArgs a)
   if (t < a.E) {
     for (int g = 0; g < G; ++g) { const int h = __ldcg(a.hist + (size_t)g * a.E + t); if (g < cta) above += h; tot += h; }
   }
-  const int nt = (tot + PF_BM - 1) / PF_BM;
+  const int nt = (tot + a.bm - 1) / a.bm;
   int ic = tot, it = nt;
   for (int o = 1; o < 32; o <<= 1) {
     const int uc = __shfl_up_sync(0xffffffffu, ic, o), ut = __shfl_up_sync(0xffffffffu, it, o);
@@ -444,7 +448,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) pf_plan_kernel(const PlanArgs a)
   const int run0 = ic - tot + (wp ? wsum[0][wp - 1] : 0), tile0 = it - nt + (wp ? wsum[1][wp - 1] : 0);
   cur[t] = run0 + above;
   if (cta == 0) {
-    for (int i = 0; i < nt; ++i) { TileRef tl; tl.expert = t; tl.slot0 = run0 + i * PF_BM; tl.rows = min(PF_BM, tot - i * PF_BM); a.tiles[tile0 + i] = tl; }
+    for (int i = 0; i < nt; ++i) { TileRef tl; tl.expert = t; tl.slot0 = run0 + i * a.bm; tl.rows = min(a.bm, tot - i * a.bm); a.tiles[tile0 + i] = tl; }
     if (t == PLAN_THREADS - 1) { *a.n_tiles = wsum[1][31]; *a.n_slots = wsum[0][31]; }
   }
   __syncthreads();
@@ -584,11 +588,81 @@ int pf_launch(hb_ctx* ctx, const char* name, const PfGemmArgs& a, const CUtensor
 }
 }  // namespace
 
+namespace {
+// map of a bf16 matrix [n_rows][row_len] with boxes of 64 values × 64 rows under the 128-byte swizzle
+int a16_make_map(hb_ctx* ctx, CUtensorMap* m, const void* base, size_t row_len, size_t n_rows) {
+  TcEncodeFn fn = tc_encode_fn();
+  HB_REQUIRE(ctx, fn, HB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {(cuuint64_t)row_len, (cuuint64_t)n_rows}, strides[1] = {(cuuint64_t)row_len * 2};
+  const cuuint32_t box[2] = {64u, 64u}, estr[2] = {1, 1};
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  HB_REQUIRE(ctx, r == CUDA_SUCCESS, HB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for %zu rows of %zu bf16 at %p", (int)r, n_rows, row_len, base);
+  return HB_OK;
+}
+
+// bf16 activations on the tensor cores: plan (tiles of ≤ 256 pairs) → slot-ordered copy of the rows → gate/up GEMM → down GEMM → sums.
+// The copy of the rows lives in the buffer of the per-pair down rows: the gate/up GEMM has read it before the down GEMM writes there.
+int pf_a16_run(hb_ctx* ctx, const uint8_t* const* lt, int E, const int32_t* ids, const float* w, int M, int K, const __nv_bfloat16* x, int H, int I, float limit,
+               float* out, const PfWs& W, int S, cudaStream_t st, const hb_pf_combine* cmb) {
+  hb_rec_layout L;
+  hb_rec_layout_make(H, I, &L);
+  int r = hbk_moe_dtc_maps(ctx, lt, E, nullptr, H, I, st);
+  if (r) return r;
+  const size_t Pcap = (size_t)S * K;
+  CUtensorMap tm_x, tm_y;
+  if ((r = a16_make_map(ctx, &tm_x, W.part, (size_t)H, Pcap))) return r;
+  if ((r = a16_make_map(ctx, &tm_y, W.y, (size_t)I, Pcap))) return r;
+  const int grid = ctx->max_ctas > 0 && ctx->max_ctas < ctx->sm_count ? ctx->max_ctas : ctx->sm_count;
+  auto common = [&](int kind, A16Args* a) {
+    const void* maps; const unsigned long long* anchor;
+    hbk_moe_dtc_map_set(ctx, kind, &maps, &anchor);
+    const int Kd = kind ? I : H;
+    a->tiles = W.tiles; a->n_tiles = W.n_tiles; a->perm = W.perm; a->tab = lt; a->down = kind; a->K = Kd; a->n_out = kind ? H : I;
+    a->maps = reinterpret_cast<const CUtensorMap*>(maps); a->anchor = anchor; a->vmax = hbk_moe_dtc_vmax();
+    a->pitch = Kd / 2;
+    int g = a->pitch, b = 4096;
+    while (b) { const int t2 = g % b; g = b; b = t2; }
+    a->gstep = g; a->pshift = -1;
+    for (int sft = 7; sft <= 12; ++sft) if (a->pitch == (1 << sft)) a->pshift = sft;
+    a->off_g = (uint32_t)L.g; a->limit = limit; a->err = ctx->dev_err;
+  };
+  for (int s0 = 0; s0 < M; s0 += S) {
+    const int n = M - s0 < S ? M - s0 : S, P = n * K;
+    PlanArgs pl{ids + (size_t)s0 * K, P, E, lt, A16_BN, W.hist, W.perm, W.pos_of, W.tiles, W.n_tiles, W.n_slots,
+                reinterpret_cast<unsigned int*>(ctx->dev_err) + kErrPlanMeet, ctx->dev_err};
+    int plan_ctas = (P + 2047) / 2048;
+    if (plan_ctas > PLAN_MAX_CTAS) plan_ctas = PLAN_MAX_CTAS;
+    if (plan_ctas > ctx->sm_count) plan_ctas = ctx->sm_count;
+    if ((r = hb_launch(ctx, "pf_plan", false, pf_plan_kernel, dim3(plan_ctas), dim3(PLAN_THREADS), 0, st, pl))) return r;
+    if ((r = hb_launch(ctx, "a16_gather", false, a16_gather_kernel, dim3(P < ctx->sm_count * 16 ? P : ctx->sm_count * 16), dim3(256), 0, st, x + (size_t)s0 * H,
+                       (const int*)W.perm, (const int*)W.n_slots, K, H, W.part)))
+      return r;
+    A16Args a{};
+    common(0, &a);
+    a.off_w = (uint32_t)L.w1; a.off_s0 = (uint32_t)L.s1; a.off_s1 = (uint32_t)L.s3; a.row2 = (int)((L.w3 - L.w1) / (size_t)(H / 2)); a.trows = 64; a.out = W.y;
+    if ((r = hb_launch(ctx, "a16_gemm_gu", false, a16_gemm_kernel, dim3(grid), dim3(A16_THREADS), (size_t)A16_SMEM, st, a, tm_x))) return r;
+    A16Args d{};
+    common(1, &d);
+    d.off_w = (uint32_t)L.w2; d.off_s0 = (uint32_t)L.s2; d.off_s1 = (uint32_t)L.s2; d.row2 = 64; d.trows = 128; d.out = W.part;
+    if ((r = hb_launch(ctx, "a16_gemm_down", false, a16_gemm_kernel, dim3(grid), dim3(A16_THREADS), (size_t)A16_SMEM, st, d, tm_y))) return r;
+    const __nv_bfloat16* sh = cmb ? reinterpret_cast<const __nv_bfloat16*>(cmb->shared) + (size_t)s0 * H : nullptr;
+    if ((r = hb_launch(ctx, "pf_sum_pairs", false, pf_sum_pairs_kernel, dim3((unsigned)((n + SUM_ROWS - 1) / SUM_ROWS < ctx->sm_count * 8 ? (n + SUM_ROWS - 1) / SUM_ROWS : ctx->sm_count * 8)), dim3(256), 0, st,
+                       (const __nv_bfloat16*)W.part, (const int*)W.pos_of, w + (size_t)s0 * K, n, K, H, cmb ? (float*)nullptr : out + (size_t)s0 * H, sh,
+                       cmb && cmb->lg ? cmb->lg + (size_t)s0 * cmb->ld : (const float*)nullptr, cmb ? cmb->ld : 0, cmb ? cmb->col : 0,
+                       cmb ? reinterpret_cast<__nv_bfloat16*>(cmb->out) + (size_t)s0 * H : (__nv_bfloat16*)nullptr)))
+      return r;
+  }
+  return HB_OK;
+}
+}  // namespace
+
 int hbk_moe_prefill_setup(hb_ctx* ctx) {
   HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(pf_gemm_kernel<PF_PLAIN>), cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
   HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(pf_gemm_kernel<PF_GU>), cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
   HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(pf_gemm_kernel<PF_DOWN>), cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
   HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(pf_peak_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, PF_STAGE + 2048));
+  HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(a16_gemm_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, A16_SMEM));
   return HB_OK;
 }
 
@@ -614,8 +688,15 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
   HB_REQUIRE(ctx, hb_aligned(x_bf16, 16) && hb_aligned(out, 16) && (!cmb || (hb_aligned(cmb->shared, 16) && hb_aligned(cmb->out, 16))), HB_ERR_INVALID,
              "moe_prefill: x, out, shared rows and combined output must be 16-byte aligned");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if ((ctx->flags & HB_FLAG_PREFILL_A16) && M > 64 && !(ctx->flags & HB_FLAG_PREFILL_A16_ROWS) && hbk_moe_dtc_supported(H, I)) {
+    // bf16 activations, more rows than a decode batch: the kind::f16 grouped GEMM over dequantised weight tiles
+    PfWs W;
+    pf_carve(ws, S, K, E, H, I, &W);
+    return pf_a16_run(ctx, rec_tab + (size_t)li * E, E, ids, w, M, K, reinterpret_cast<const __nv_bfloat16*>(x_bf16), H, I, limit, out, W, S, st, cmb);
+  }
   if (ctx->flags & HB_FLAG_PREFILL_A16) {
-    // bf16 activations: the decode operators over sub-chunks of rows (their scratch fits inside this operator's workspace)
+    // bf16 activations, few rows (or HB_FLAG_PREFILL_A16_ROWS): the decode operators over sub-chunks of rows (their scratch fits inside
+    // this operator's workspace)
     int rows = HB_MAX_PAIRS / K < S ? HB_MAX_PAIRS / K : S;
     HB_REQUIRE(ctx, rows >= 1 && hb_moe_decode_supported(H, I) > 0, HB_ERR_UNSUPPORTED, "moe_prefill (bf16 activations): K=%d H=%d I=%d", K, H, I);
     while (rows > 1 && hbk_moe_decode_ws_bytes(rows * K, H, I) > hb_moe_prefill_ws_bytes(S, K, E, H, I)) rows /= 2;
@@ -653,7 +734,7 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
   for (int s0 = 0; s0 < M; s0 += S) {
     const int n = M - s0 < S ? M - s0 : S, P = n * K;
     const int32_t* sid = ids + (size_t)s0 * K;
-    PlanArgs pl{sid, P, E, lt, W.hist, W.perm, W.pos_of, W.tiles, W.n_tiles, W.n_slots, reinterpret_cast<unsigned int*>(ctx->dev_err) + kErrPlanMeet, ctx->dev_err};
+    PlanArgs pl{sid, P, E, lt, PF_BM, W.hist, W.perm, W.pos_of, W.tiles, W.n_tiles, W.n_slots, reinterpret_cast<unsigned int*>(ctx->dev_err) + kErrPlanMeet, ctx->dev_err};
     int plan_ctas = (P + 2047) / 2048;
     if (plan_ctas > PLAN_MAX_CTAS) plan_ctas = PLAN_MAX_CTAS;
     if (plan_ctas > ctx->sm_count) plan_ctas = ctx->sm_count;                   // the CTAs meet inside the kernel: all must be resident

@@ -59,8 +59,11 @@ typedef struct hb_config {
 #define HB_FLAG_LAYER_A4 32       /* hb_moe_layer may run calls of more than 64 rows on the W4A4 grouped GEMM (activations quantised to NVFP4 — the
                                      reference's lossy opt-in, fn_moe_prefill_set_a4).  Without it hb_moe_layer keeps bf16 activations at every
                                      row count: the same numbers as the decode operators, never a silent change of arithmetic */
-#define HB_FLAG_PREFILL_A16 4u /* hb_moe_prefill keeps bf16 activations (W4A16, the reference's default prefill arithmetic): rows run through
-                                  the decode kernels in sub-chunks — exact, but the expert records are streamed once per sub-chunk */
+#define HB_FLAG_PREFILL_A16 4u /* hb_moe_prefill keeps bf16 activations (W4A16, the reference's default prefill arithmetic).  Calls of more than 64
+                                  rows run a grouped GEMM on the tensor cores (kind::f16 MMAs over weight tiles dequantised exactly to bf16, fp32
+                                  sums); calls of up to 64 rows run the decode kernels */
+#define HB_FLAG_PREFILL_A16_ROWS 256u /* with HB_FLAG_PREFILL_A16: every call runs the decode kernels over sub-chunks of rows — bit-identical to
+                                  hb_moe_decode_routed(_f32) on the same rows, but the expert records are streamed once per sub-chunk */
 
 /* Expert record layout, byte-identical to hive::glm::ExpertRecLayout::make (engine/include/hive/glm/glm_moe.h:13-22):
  * [w1 gate e2m1 [I,H/2]][s1 e4m3 [I,H/16]][w3 up][s3][w2 down e2m1 [H,I/2]][s2 e4m3 [H,I/16]][g1 g3 g2 fp32], total 4096-aligned. */
@@ -274,7 +277,9 @@ HB_API size_t hb_moe_prefill_ws_bytes(int S, int K, int E, int H, int I);
  * records contribute nothing.  Rows are processed in sub-chunks of S; ws ≥ hb_moe_prefill_ws_bytes(S, K, E, H, I).  E ≤ 1024.
  * Block scales are read as unsigned e4m3 (the sign bit of a scale byte must be clear, as every NVFP4 writer leaves it).
  * With HB_FLAG_PREFILL_A16 in the context's flags the activations stay bf16 (W4A16: the decode operators' arithmetic and rounding
- * points, bit-identical to hb_moe_decode_routed(_f32) on the same rows), at decode-kernel speed. */
+ * points).  Calls of more than 64 rows run the kind::f16 grouped GEMM (exact products, fp32 sums in the tensor core's order: the
+ * decode operators' results up to summation order); calls of up to 64 rows, and every call with HB_FLAG_PREFILL_A16_ROWS, run the
+ * decode kernels and are bit-identical to hb_moe_decode_routed(_f32) on the same rows. */
 HB_API int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, const int32_t* ids, const float* w, int M, int K,
                           const void* x_bf16, int H, int I, float limit, float* out, void* ws, int S, void* stream, const hb_pf_combine* cmb);
 /* The same GEMM on one dense NVFP4 matrix: y[m,n] = xg[m]·W.g·Σ_k xq[m,k]·xs[m,k/16]·W[n,k], fp32 [M, ldy].  xq / xs / xg as written by

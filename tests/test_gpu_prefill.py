@@ -119,8 +119,8 @@ def test_moe_prefill_combine_matches_separate(E, oracle):
 
 
 def test_moe_prefill_bf16_activations_equals_decode_operator(E, oracle):
-    """HB_FLAG_PREFILL_A16: hb_moe_prefill with bf16 activations is the decode arithmetic on sub-chunks of rows — bit-identical to
-    hb_moe_decode_routed_f32 on the same rows, and within the expert-output gate of the W4A16 oracle."""
+    """HB_FLAG_PREFILL_A16 | HB_FLAG_PREFILL_A16_ROWS: hb_moe_prefill with bf16 activations as the decode arithmetic on sub-chunks of
+    rows — bit-identical to hb_moe_decode_routed_f32 on the same rows, and within the expert-output gate of the W4A16 oracle."""
     dev = torch.device("cuda")
     H, I, E_, K, M = 512, 256, 8, 2, 150
     rng = np.random.default_rng(21)
@@ -131,7 +131,7 @@ def test_moe_prefill_bf16_activations_equals_decode_operator(E, oracle):
     w_np = rng.random((M, K), dtype=np.float32)
     ids, w = torch.tensor(ids_np, device=dev), torch.tensor(w_np, device=dev)
     x = torch.tensor(rng.standard_normal((M, H)).astype(np.float32)).to(torch.bfloat16).to(dev)
-    ctx16 = E.Context(flags=4)
+    ctx16 = E.Context(flags=4 | 256)
     out = E.fn_moe_prefill(tab, 0, E_, ids, w, x, H, I, S=64, ctx=ctx16)
     ref = E.moe_decode_routed_f32(ids, w, tab, 0, E_, x, H, I)
     torch.cuda.synchronize()
@@ -141,6 +141,65 @@ def test_moe_prefill_bf16_activations_equals_decode_operator(E, oracle):
     orc = oracle.moe_routed(H, I, ids_np, w_np, recs, xs, 0.0, 0)
     rms = np.sqrt((orc.astype(np.float64) ** 2).mean(axis=1, keepdims=True)) + 1e-12
     assert np.max(np.abs(out.cpu().numpy() - orc) / rms) <= 2e-2
+
+
+@pytest.mark.parametrize("H,I,E_,K,M,S,limit", [(512, 256, 8, 2, 150, 150, 0.0), (256, 256, 4, 2, 700, 700, 0.0), (2048, 512, 16, 4, 300, 128, 7.0),
+                                                  (7168, 2048, 3, 2, 70, 70, 0.0)])
+def test_moe_prefill_bf16_activations_on_tensor_cores(E, oracle, H, I, E_, K, M, S, limit):
+    """HB_FLAG_PREFILL_A16 with more than 64 rows: the kind::f16 grouped GEMM over exactly dequantised weight tiles.  Same products and
+    rounding points as the decode operators, fp32 sums in another order: within the expert-output gate of the W4A16 oracle
+    (2e-2 × row RMS), and much closer than that to the decode operators; the same bits on a second run."""
+    dev = torch.device("cuda")
+    rng = np.random.default_rng(H + I + M + 5)
+    recs = random_records(oracle, H, I, E_, H + M + 5)
+    keep = upload(recs, dev)
+    tab = E.rec_table(keep)
+    ids_np = np.stack([rng.permutation(E_)[:K] for _ in range(M)]).astype(np.int32)
+    ids_np[3, 0] = -1
+    ids_np[5, 1] = E_ + 3
+    w_np = rng.random((M, K), dtype=np.float32)
+    ids, w = torch.tensor(ids_np, device=dev), torch.tensor(w_np, device=dev)
+    x = torch.tensor((rng.standard_normal((M, H)) * np.exp(rng.standard_normal((M, 1)))).astype(np.float32)).to(torch.bfloat16).to(dev)
+    ctx16 = E.Context(flags=4)
+    out = E.fn_moe_prefill(tab, 0, E_, ids, w, x, H, I, S=S, limit=limit, ctx=ctx16)
+    again = E.fn_moe_prefill(tab, 0, E_, ids, w, x, H, I, S=S, limit=limit, ctx=ctx16)
+    torch.cuda.synchronize()
+    ctx16.check_device()
+    assert torch.equal(out, again)
+    dec = torch.cat([E.moe_decode_routed_f32(ids[m0:m0 + 64], w[m0:m0 + 64], tab, 0, E_, x[m0:m0 + 64], H, I, limit=limit) for m0 in range(0, M, 64)])
+    rms_d = dec.double().pow(2).mean(1, keepdim=True).sqrt() + 1e-12
+    assert float(((out.double() - dec.double()).abs() / rms_d).max()) <= 3e-2            # bf16 rounding flips of g, u, y and the down rows (one bf16 step of an element of several row RMS)
+    rows = list(range(0, M, max(1, M // 24)))                                            # the oracle on a sample of rows
+    orc = oracle.moe_routed(H, I, ids_np[rows], w_np[rows], recs, x.float().cpu().numpy()[rows], limit, 0)
+    rms = np.sqrt((orc.astype(np.float64) ** 2).mean(axis=1, keepdims=True)) + 1e-12
+    # the expert-output gate, plus one bf16 step of the value itself: the per-pair down rows are rounded to bf16 before they are summed,
+    # and with fp32 sums in another order an element of several row RMS lands one step away (2^-8 of its size, more than 2e-2 RMS)
+    assert np.all(np.abs(out.cpu().numpy()[rows] - orc) <= 2e-2 * rms + 2.0 ** -7 * np.abs(orc))
+    assert np.max(np.abs(out.cpu().numpy()[rows] - orc) / rms) <= 4e-2
+    ctx16.close()
+
+
+def test_moe_prefill_bf16_activations_combine(E, oracle):
+    """The fused shared-expert combine behind the bf16-activation GEMM equals hb_moe_combine on its routed sums."""
+    dev = torch.device("cuda")
+    H, I, E_, K, M = 512, 256, 8, 2, 200
+    rng = np.random.default_rng(31)
+    recs = random_records(oracle, H, I, E_, 31)
+    keep = upload(recs, dev)
+    tab = E.rec_table(keep)
+    ids = torch.tensor(np.stack([rng.permutation(E_)[:K] for _ in range(M)]).astype(np.int32), device=dev)
+    w = torch.tensor(rng.random((M, K), dtype=np.float32), device=dev)
+    x = torch.tensor(rng.standard_normal((M, H)).astype(np.float32)).to(torch.bfloat16).to(dev)
+    shared = torch.tensor(rng.standard_normal((M, H)).astype(np.float32)).to(torch.bfloat16).to(dev)
+    lg = torch.tensor(rng.standard_normal((M, 3)).astype(np.float32), device=dev)
+    ctx16 = E.Context(flags=4)
+    routed = E.fn_moe_prefill(tab, 0, E_, ids, w, x, H, I, ctx=ctx16)
+    fused = E.fn_moe_prefill(tab, 0, E_, ids, w, x, H, I, shared=shared, lg=lg, col=1, ctx=ctx16)
+    sep = E.moe_combine(routed, shared, lg, 1)
+    torch.cuda.synchronize()
+    ctx16.check_device()
+    assert torch.equal(fused.view(torch.int16), sep.view(torch.int16))
+    ctx16.close()
 
 
 def test_w4a4_distance_from_w4a16(E, oracle):
