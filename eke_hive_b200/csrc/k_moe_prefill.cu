@@ -392,7 +392,8 @@ __global__ void __launch_bounds__(128, 1) pf_peak_kernel(int n_rounds, uint32_t*
 constexpr int PLAN_THREADS = 1024, PLAN_MAX_CTAS = 64;
 struct PlanArgs {
   const int32_t* ids; int P, E; const uint8_t* const* tab;
-  int bm;                          // pairs per tile
+  int bm;                          // pairs per tile, at most
+  int even;                        // 1: an expert's run is cut into its ceil(run / bm) tiles of equal size instead of full tiles and a rest
   int* hist;                       // [CTAs][E]
   int* perm; int* pos_of; TileRef* tiles; int* n_tiles; int* n_slots;
   unsigned int* meet;              // two context-owned counters, zero between launches
@@ -448,7 +449,8 @@ __global__ void __launch_bounds__(PLAN_THREADS) pf_plan_kernel(const PlanArgs a)
   const int run0 = ic - tot + (wp ? wsum[0][wp - 1] : 0), tile0 = it - nt + (wp ? wsum[1][wp - 1] : 0);
   cur[t] = run0 + above;
   if (cta == 0) {
-    for (int i = 0; i < nt; ++i) { TileRef tl; tl.expert = t; tl.slot0 = run0 + i * a.bm; tl.rows = min(a.bm, tot - i * a.bm); a.tiles[tile0 + i] = tl; }
+    const int tper = a.even && nt > 0 ? (tot + nt - 1) / nt : a.bm;
+    for (int i = 0; i < nt; ++i) { TileRef tl; tl.expert = t; tl.slot0 = run0 + i * tper; tl.rows = min(tper, tot - i * tper); a.tiles[tile0 + i] = tl; }
     if (t == PLAN_THREADS - 1) { *a.n_tiles = wsum[1][31]; *a.n_slots = wsum[0][31]; }
   }
   __syncthreads();
@@ -629,7 +631,7 @@ int pf_a16_run(hb_ctx* ctx, const uint8_t* const* lt, int E, const int32_t* ids,
   };
   for (int s0 = 0; s0 < M; s0 += S) {
     const int n = M - s0 < S ? M - s0 : S, P = n * K;
-    PlanArgs pl{ids + (size_t)s0 * K, P, E, lt, A16_BN, W.hist, W.perm, W.pos_of, W.tiles, W.n_tiles, W.n_slots,
+    PlanArgs pl{ids + (size_t)s0 * K, P, E, lt, A16_BN, 1, W.hist, W.perm, W.pos_of, W.tiles, W.n_tiles, W.n_slots,
                 reinterpret_cast<unsigned int*>(ctx->dev_err) + kErrPlanMeet, ctx->dev_err};
     int plan_ctas = (P + 2047) / 2048;
     if (plan_ctas > PLAN_MAX_CTAS) plan_ctas = PLAN_MAX_CTAS;
@@ -640,11 +642,11 @@ int pf_a16_run(hb_ctx* ctx, const uint8_t* const* lt, int E, const int32_t* ids,
       return r;
     A16Args a{};
     common(0, &a);
-    a.off_w = (uint32_t)L.w1; a.off_s0 = (uint32_t)L.s1; a.off_s1 = (uint32_t)L.s3; a.row2 = (int)((L.w3 - L.w1) / (size_t)(H / 2)); a.trows = 64; a.out = W.y;
+    a.off_w = (uint32_t)L.w1; a.off_s0 = (uint32_t)L.s1; a.off_s1 = (uint32_t)L.s3; a.row2 = (int)((L.w3 - L.w1) / (size_t)(H / 2)); a.out = W.y;
     if ((r = hb_launch(ctx, "a16_gemm_gu", false, a16_gemm_kernel, dim3(grid), dim3(A16_THREADS), (size_t)A16_SMEM, st, a, tm_x))) return r;
     A16Args d{};
     common(1, &d);
-    d.off_w = (uint32_t)L.w2; d.off_s0 = (uint32_t)L.s2; d.off_s1 = (uint32_t)L.s2; d.row2 = 64; d.trows = 128; d.out = W.part;
+    d.off_w = (uint32_t)L.w2; d.off_s0 = (uint32_t)L.s2; d.off_s1 = (uint32_t)L.s2; d.row2 = 64; d.out = W.part;
     if ((r = hb_launch(ctx, "a16_gemm_down", false, a16_gemm_kernel, dim3(grid), dim3(A16_THREADS), (size_t)A16_SMEM, st, d, tm_y))) return r;
     const __nv_bfloat16* sh = cmb ? reinterpret_cast<const __nv_bfloat16*>(cmb->shared) + (size_t)s0 * H : nullptr;
     if ((r = hb_launch(ctx, "pf_sum_pairs", false, pf_sum_pairs_kernel, dim3((unsigned)((n + SUM_ROWS - 1) / SUM_ROWS < ctx->sm_count * 8 ? (n + SUM_ROWS - 1) / SUM_ROWS : ctx->sm_count * 8)), dim3(256), 0, st,
@@ -656,6 +658,12 @@ int pf_a16_run(hb_ctx* ctx, const uint8_t* const* lt, int E, const int32_t* ids,
   return HB_OK;
 }
 }  // namespace
+
+#ifdef HB_A16_TRACE
+extern "C" __attribute__((visibility("default"))) int hb_a16_trace_read(long long* out, int n) {
+  return (int)cudaMemcpyFromSymbol(out, g_a16_trace, (size_t)n * 8);
+}
+#endif
 
 int hbk_moe_prefill_setup(hb_ctx* ctx) {
   HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(pf_gemm_kernel<PF_PLAIN>), cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
@@ -734,7 +742,7 @@ int hb_moe_prefill(hb_ctx* ctx, const uint8_t* const* rec_tab, int li, int E, co
   for (int s0 = 0; s0 < M; s0 += S) {
     const int n = M - s0 < S ? M - s0 : S, P = n * K;
     const int32_t* sid = ids + (size_t)s0 * K;
-    PlanArgs pl{sid, P, E, lt, PF_BM, W.hist, W.perm, W.pos_of, W.tiles, W.n_tiles, W.n_slots, reinterpret_cast<unsigned int*>(ctx->dev_err) + kErrPlanMeet, ctx->dev_err};
+    PlanArgs pl{sid, P, E, lt, PF_BM, 0, W.hist, W.perm, W.pos_of, W.tiles, W.n_tiles, W.n_slots, reinterpret_cast<unsigned int*>(ctx->dev_err) + kErrPlanMeet, ctx->dev_err};
     int plan_ctas = (P + 2047) / 2048;
     if (plan_ctas > PLAN_MAX_CTAS) plan_ctas = PLAN_MAX_CTAS;
     if (plan_ctas > ctx->sm_count) plan_ctas = ctx->sm_count;                   // the CTAs meet inside the kernel: all must be resident
