@@ -338,9 +338,10 @@ int hb_moe_layer(hb_ctx* ctx, const float* logits, int ld, int M, int E, int K, 
   layer_carve(ws, M, K, E, H, I, &W);
   const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
   __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(out);
-  if (M <= kDecodeRows || !(ctx->flags & HB_FLAG_LAYER_A4) || hb_moe_prefill_supported(H, I) <= 0) {
-    // decode operators, 64 rows at a time (one pass when M ≤ 64): per-row results do not depend on the batch.  More rows go to the
-    // W4A4 grouped GEMM only when the context asked for that arithmetic
+  if (M <= kDecodeRows || !(ctx->flags & (HB_FLAG_LAYER_A4 | HB_FLAG_PREFILL_A16)) || hb_moe_prefill_supported(H, I) <= 0) {
+    // decode operators, 64 rows at a time (one pass when M ≤ 64): per-row results do not depend on the batch.  More rows go to a
+    // grouped GEMM only when the context asked for one: HB_FLAG_PREFILL_A16 keeps bf16 activations (the same arithmetic, fp32 sums in
+    // the tensor core's order), HB_FLAG_LAYER_A4 quantises the activations (W4A4); with both, hb_moe_prefill keeps bf16 activations
     for (int m0 = 0; m0 < M; m0 += kDecodeRows) {
       const int n = M - m0 < kDecodeRows ? M - m0 : kDecodeRows;
       const int r = hb_moe_layer_decode(ctx, logits + (size_t)m0 * ld, ld, n, E, K, renorm, logits_bf16, bias, sigmoid_scale, rec_tab, li, shared_rec, gate_col,

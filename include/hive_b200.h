@@ -62,6 +62,8 @@ typedef struct hb_config {
 #define HB_FLAG_PREFILL_A16 4u /* hb_moe_prefill keeps bf16 activations (W4A16, the reference's default prefill arithmetic).  Calls of more than 64
                                   rows run a grouped GEMM on the tensor cores (kind::f16 MMAs over weight tiles dequantised exactly to bf16, fp32
                                   sums); calls of up to 64 rows run the decode kernels */
+                               /* hb_moe_layer on such a context sends calls of more than 64 rows through the same GEMM (router → shared expert →
+                                  routed experts with the fused combine); without it hb_moe_layer runs the decode kernels at every row count */
 #define HB_FLAG_PREFILL_A16_ROWS 256u /* with HB_FLAG_PREFILL_A16: every call runs the decode kernels over sub-chunks of rows — bit-identical to
                                   hb_moe_decode_routed(_f32) on the same rows, but the expert records are streamed once per sub-chunk */
 

@@ -271,6 +271,53 @@ def test_moe_layer_dispatches_by_row_count(E, oracle):
         ctx_a4.close()
 
 
+def test_moe_prefill_bf16_activations_nothing_routed(E, oracle):
+    """More than 64 rows none of which has a usable expert: the bf16-activation GEMM runs over an empty tile list and the sums are zero."""
+    dev = torch.device("cuda")
+    H, I, E_, K, M = 256, 256, 4, 2, 100
+    recs = random_records(oracle, H, I, E_, 5)
+    keep = upload(recs, dev)
+    tab = E.rec_table(keep)
+    ids = torch.full((M, K), -1, dtype=torch.int32, device=dev)
+    ids[::3, 1] = E_ + 2
+    w = torch.ones((M, K), dtype=torch.float32, device=dev)
+    x = torch.randn((M, H), device=dev).to(torch.bfloat16)
+    ctx16 = E.Context(flags=4)
+    out = E.fn_moe_prefill(tab, 0, E_, ids, w, x, H, I, ctx=ctx16)
+    torch.cuda.synchronize()
+    ctx16.check_device()
+    assert float(out.abs().max()) == 0.0
+    ctx16.close()
+
+
+def test_moe_layer_with_bf16_activation_gemm(E, oracle):
+    """hb_moe_layer on a context with HB_FLAG_PREFILL_A16: more than 64 rows go router → shared expert → routed experts through the
+    bf16-activation grouped GEMM.  Routing is the decode layer's bit for bit; the outputs are the decode layer's up to the order of
+    the fp32 sums (a bf16 step of the output here and there), and within the gate of the oracle's layer."""
+    dev = torch.device("cuda")
+    H, I, E_, K, M = 512, 256, 8, 2, 150
+    rng = np.random.default_rng(41)
+    recs = random_records(oracle, H, I, E_ + 1, 41)
+    keep = upload(recs, dev)
+    tab = E.rec_table(keep[:E_])
+    x = torch.tensor(rng.standard_normal((M, H)).astype(np.float32)).to(torch.bfloat16).to(dev)
+    lg = torch.tensor(rng.standard_normal((M, E_ + 1)).astype(np.float32), device=dev)
+    ctx16 = E.Context(flags=4)
+    try:
+        ids, w, out = E.moe_layer(lg, x, tab, 0, E_, K, H, I, shared_rec=keep[E_], gate_col=E_, ctx=ctx16)
+        ids2, w2, out2 = E.moe_layer(lg, x, tab, 0, E_, K, H, I, shared_rec=keep[E_], gate_col=E_)          # decode operators
+        torch.cuda.synchronize()
+        ctx16.check_device(); E.context().check_device()
+        assert torch.equal(ids, ids2) and torch.equal(w, w2)
+        d = (out.double() - out2.double()).abs()
+        rms = out2.double().pow(2).mean(1, keepdim=True).sqrt() + 1e-12
+        assert float((d / rms).max()) <= 3e-2
+        assert float((d > 0).double().mean()) < 0.2                        # most elements are the same bits
+    finally:
+        torch.cuda.synchronize()
+        ctx16.close()
+
+
 def test_moe_prefill_degenerate_inputs(E, oracle):
     """Nothing to do is not an error: zero rows, and rows whose every id is invalid or points at an absent record (output zeros)."""
     dev = torch.device("cuda")
