@@ -168,7 +168,15 @@ def test_moe_prefill_bf16_activations_on_tensor_cores(E, oracle, H, I, E_, K, M,
     assert torch.equal(out, again)
     dec = torch.cat([E.moe_decode_routed_f32(ids[m0:m0 + 64], w[m0:m0 + 64], tab, 0, E_, x[m0:m0 + 64], H, I, limit=limit) for m0 in range(0, M, 64)])
     rms_d = dec.double().pow(2).mean(1, keepdim=True).sqrt() + 1e-12
-    assert float(((out.double() - dec.double()).abs() / rms_d).max()) <= 3e-2            # bf16 rounding flips of g, u, y and the down rows (one bf16 step of an element of several row RMS)
+    dd = (out.double() - dec.double()).abs() / rms_d
+    assert float(dd.max()) <= 3e-2                            # bf16 rounding flips of g, u, y and the down rows (one bf16 step of an element of several row RMS)
+    # the reference's own comparison of its W4A16 GEMM path with its decode path (engine/tests/test_fn_moe_pf.cu:172-181): per-row cosine
+    # above 0.99999 and no more than M outputs further than 1e-2 × RMS apart — its case sums 10 terms per output, so one term's bf16 flip
+    # stays below 1e-2 × RMS; with the 2 terms of these cases a flip of a large element does not, hence the rate beside the count
+    cos = (out.double() * dec.double()).sum(1) / (out.double().norm(dim=1) * dec.double().norm(dim=1) + 1e-30)
+    live = dec.double().norm(dim=1) > 0
+    assert float(cos[live].min()) > 0.99999, float(cos[live].min())
+    assert int((dd > 1e-2).sum()) <= max(M, int(1e-3 * M * H)), int((dd > 1e-2).sum())
     rows = list(range(0, M, max(1, M // 24)))                                            # the oracle on a sample of rows
     orc = oracle.moe_routed(H, I, ids_np[rows], w_np[rows], recs, x.float().cpu().numpy()[rows], limit, 0)
     rms = np.sqrt((orc.astype(np.float64) ** 2).mean(axis=1, keepdims=True)) + 1e-12
