@@ -47,7 +47,8 @@ def test_golden_routed_layer_generic_path(E, oracle, golden):
 
 
 @pytest.mark.parametrize("H,I,Ex,K,M", [(256, 256, 8, 2, 3), (2048, 512, 64, 8, 1), (2048, 512, 16, 4, 16), (1024, 768, 12, 3, 9),
-                                          (512, 1536, 6, 2, 5), (4096, 256, 4, 2, 2), (768, 3072, 4, 2, 3)])
+                                          (512, 1536, 6, 2, 5), (4096, 256, 4, 2, 2), (768, 3072, 4, 2, 3),
+                                          (256, 256, 24, 17, 3)])          # last: more than 16 experts per row (the sums run over every k)
 def test_routed_fast_path_vs_oracle(E, oracle, H, I, Ex, K, M):
     import torch
     assert E.moe_decode_supported(H, I) == 2
