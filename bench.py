@@ -518,10 +518,14 @@ def run_ours(args):
         pa = argparse.Namespace(**vars(args)); pa.steps = 5; pa.warmup = 3
         pl, prc = prefill_measure(pa, torch, dist, E, O, ctx, dev, rank, world, with_dense=(world == 1))
         per_config["prefill_t8192"] = {k: pl.get(k) for k in ("value", "unit", "ms_per_layer", "layer_TFLOPs", "scaling", "config", "roofline", "roofline_hbm", "exchange",
-                                                              "parity", "w4a4_vs_w4a16", "dense_gemm_a4", "kernels")}
+                                                              "parity", "w4a4_vs_w4a16", "w4a16", "dense_gemm_a4", "kernels")}
         line["per_config"] = per_config
         line["prefill"] = {"tokens_per_s": pl["value"], "ms_per_layer": pl["ms_per_layer"], "frac_of_measured_fp4_peak": pl["roofline"]["frac"],
                            "peak_TFLOPs": pl["roofline"]["peak"], "dense_gemm_a4": pl.get("dense_gemm_a4"), "parity_ok": pl["parity"]["ok"]}
+        if pl.get("w4a16"):
+            w16 = pl["w4a16"]      # the same layer with bf16 activations (the reference's default prefill arithmetic) on the kind::f16 grouped GEMM
+            line["prefill"]["w4a16"] = {"tokens_per_s": w16["tokens_per_s"], "ms_per_layer": w16["ms_per_layer"], "frac_of_measured_bf16_peak": w16["roofline"]["frac"],
+                                        "peak_TFLOPs": w16["roofline"]["peak"], "parity_ok": w16["parity"]["ok"], "max_err_x_rms": w16["parity"]["max_err_x_rms"]}
         if world == 1:
             trace("extras: dense")
             da = argparse.Namespace(**vars(args)); da.steps = 20
