@@ -583,13 +583,14 @@ int hbk_moe_decode_run(hb_ctx* ctx, const hbk_pair_src& src, const void* x, int 
   // boxes) costs more than its faster stream saves (measured: 30.6 vs 27.6 µs per layer at 11 pairs, 73 vs 81 µs at 176).
   // Expert parallel (rows of all ranks, most pairs dead on this rank): what counts is this rank's share of the pairs, and with many
   // gathered rows the digit planes of rows this rank has nothing for cost more than the faster stream saves (measured at 8 ranks ×
-  // 16 rows: 109 vs 99 µs per layer; at 2 ranks: 101 vs 108 µs) — unpinned contexts take the tensor-memory kernel up to 32 rows.
+  // 16 rows: 109 vs 99 µs per layer; at 4 ranks × 16 rows: 99 vs 103 µs; at 2 ranks: 101 vs 108 µs) — unpinned contexts take the
+  // tensor-memory kernel up to 64 gathered rows.
   bool tc_gu = false;
   if (routed && !src.ws_stream_only && src.tab && hbk_moe_decode_fast(H, I) && hbk_moe_dtc_supported(H, I) && hbk_moe_dtc_gu_fits(ctx, P, src.E, H, I) &&
       !(ctx->flags & (HB_FLAG_DECODE_MMA_SYNC | HB_FLAG_FUSED))) {
     const int ranks = red.ep ? red.ep->world : 1;
     const int pairs_eff = (P > src.pairs_hint ? P : src.pairs_hint) / ranks;
-    const bool auto_tc = pairs_eff >= kTcGuMinPairs && (ranks == 1 || src.M <= 32);
+    const bool auto_tc = pairs_eff >= kTcGuMinPairs && (ranks == 1 || src.M <= 64);
     tc_gu = (ctx->flags & (HB_FLAG_DECODE_TC_GU | HB_FLAG_DECODE_TC)) || auto_tc;
   }
   ga.group_rows = tc_gu ? 2 : kGroupRows;
