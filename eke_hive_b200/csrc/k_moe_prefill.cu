@@ -19,6 +19,10 @@
 // `tcgen05.mma kind::mxf4nvf4` (block 16, ue4m3 scales: both operands' block scales are applied by the tensor core) and commits to
 // the stage's mbarrier.  Four warps read the accumulators back with `tcgen05.ld` and run the epilogue.  Every wait is bounded; on a
 // timeout the kernel records a site code in the context's error word, drains its copies, frees its tensor memory and returns.
+//
+// With bf16 activations (HB_FLAG_PREFILL_A16, the reference's default prefill arithmetic, fn_moe_pf.cu:118-437) the same plan feeds
+// another pair of GEMMs: tcgen05 kind::f16 over weight tiles dequantised exactly to bf16, the pairs as the B operand (pf_a16.cuh);
+// no quantisation passes, a slot-ordered copy of the activation rows instead.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
