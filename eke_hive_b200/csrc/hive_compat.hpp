@@ -115,7 +115,8 @@ inline void fn_moe_decode_routed(const glm::ExpertRecLayout&, const int32_t* ids
 }
 // Prefill (engine/include/hive/qwen/fn_moe.h:46-61).  As in the reference, bf16 activations (W4A16) are the default and
 // fn_moe_prefill_set_a4(true) opts in to NVFP4 activations (W4A4, the block-scaled tensor-core grouped GEMM).  The W4A16 form here
-// runs the decode operators over sub-chunks of rows: the reference's numbers, at decode-kernel speed.
+// is a kind::f16 tensor-core grouped GEMM over exactly dequantised weight tiles for calls of more than 64 rows, and the decode
+// operators below that.
 inline bool fn_moe_prefill_supported(int H, int I) { return hb_moe_prefill_supported(H, I) > 0; }
 inline bool fn_moe_prefill_a4() { return b200::prefill_a4_flag(); }
 inline void fn_moe_prefill_set_a4(bool on) { b200::prefill_a4_flag() = on; }
