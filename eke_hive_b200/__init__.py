@@ -5,7 +5,9 @@ the reference engine's operator interface (hive::glm / hive::qwen free functions
 for device memory, streams and torch.distributed.  Importing the package loads the shared library and fails if it is
 missing; nothing here computes on the CPU.
 """
-from ._lib import HbError, load
+from ._lib import FLAGS, HbError, load
+
+globals().update(FLAGS)          # the HB_FLAG_* context flags of include/hive_b200.h, by name
 
 lib = load()
 

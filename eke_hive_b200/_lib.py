@@ -17,7 +17,16 @@ LIB_PATH = Path(_os.environ["HIVE_B200_LIB"]) if _os.environ.get("HIVE_B200_LIB"
 HEADER = HERE.parent / "include" / "hive_b200.h"
 
 HB_OK = 0
-HB_FLAG_NO_PDL = 1
+
+
+def _header_flags() -> dict:
+    """The HB_FLAG_* context flags as include/hive_b200.h defines them (one source for the C and the Python side)."""
+    import re
+    return {m.group(1): int(m.group(2)) for m in re.finditer(r"^#define (HB_FLAG_\w+) (\d+)u?\b", HEADER.read_text(), re.M)}
+
+
+FLAGS = _header_flags()
+globals().update(FLAGS)          # HB_FLAG_NO_PDL, HB_FLAG_PREFILL_A16, HB_FLAG_DECODE_TC_GU, …
 
 
 class HbError(RuntimeError):

@@ -32,6 +32,16 @@ def test_debug_library_exports_the_same_symbols(lib):
         assert hasattr(L, n), n
 
 
+def test_context_flags_are_the_headers(lib):
+    """The Python mirror takes the HB_FLAG_* values from the header; they are distinct bits, and the ones the tests and the benchmark
+    pass as numbers have the values used there."""
+    import eke_hive_b200 as E
+    vals = list(E.FLAGS.values())
+    assert len(vals) >= 9 and all(v > 0 and v & (v - 1) == 0 for v in vals) and len(set(vals)) == len(vals)
+    assert (E.HB_FLAG_PREFILL_A16, E.HB_FLAG_PREFILL_A16_ROWS, E.HB_FLAG_LAYER_A4) == (4, 256, 32)
+    assert (E.HB_FLAG_DECODE_MMA_SYNC, E.HB_FLAG_DECODE_TC_GU, E.HB_FLAG_DECODE_TC_DOWN, E.HB_FLAG_FUSED, E.HB_FLAG_NO_PDL) == (8, 64, 128, 2, 1)
+
+
 def test_pair_struct_matches_reference_abi(lib):
     # hive::glm::MoePair {int row; const uint8_t* rec; float w;} on LP64: 24 bytes, rec at 8, w at 16
     assert C.sizeof(lib.MoePair) == 24 and lib.MoePair.rec.offset == 8 and lib.MoePair.w.offset == 16
